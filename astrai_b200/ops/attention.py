@@ -1,0 +1,64 @@
+"""Attention entry points.
+
+``dense_attention`` serves training and the no-cache forward: q ``[B,S,Hq,D]``, k/v ``[B,L,Hkv,D]``, optional
+bool mask (True = attend) or causal flag - the contract of ``astrai/extension/backend/attention.py:256-303``
+for ``fwd=None``.  The packed prefill / paged decode entry points used by the inference engine live in
+:mod:`astrai_b200.ops.paged_attention`.
+"""
+
+from __future__ import annotations
+
+import os
+from typing import Optional
+
+import torch
+import torch.nn.functional as F
+from torch import Tensor
+
+from astrai_b200.ops import reference
+
+_SDPA_BACKENDS = None
+
+
+def _sdpa_ctx():
+    """Library attention for the dense training path: cuDNN fused attention first, then flash, then the rest."""
+    global _SDPA_BACKENDS
+    from torch.nn.attention import SDPBackend, sdpa_kernel
+
+    if _SDPA_BACKENDS is None:
+        order = os.environ.get("ASTRAI_B200_SDPA", "cudnn,flash,efficient,math").split(",")
+        table = {
+            "cudnn": SDPBackend.CUDNN_ATTENTION, "flash": SDPBackend.FLASH_ATTENTION,
+            "efficient": SDPBackend.EFFICIENT_ATTENTION, "math": SDPBackend.MATH,
+        }
+        _SDPA_BACKENDS = [table[o] for o in order if o in table]
+    return sdpa_kernel(_SDPA_BACKENDS, set_priority=True)
+
+
+def dense_attention(q: Tensor, k: Tensor, v: Tensor, mask: Optional[Tensor] = None, causal: bool = False,
+                    scale: Optional[float] = None) -> Tensor:
+    """Softmax attention with GQA head sharing; returns ``[B,S,Hq,Dv]``."""
+    if not q.is_cuda:
+        return reference.attention(q, k, v, mask, causal, scale)
+    hq, hkv = q.shape[2], k.shape[2]
+    qt, kt, vt = q.transpose(1, 2), k.transpose(1, 2), v.transpose(1, 2)
+    with _sdpa_ctx():
+        out = F.scaled_dot_product_attention(
+            qt, kt, vt, attn_mask=mask, is_causal=causal and mask is None, scale=scale, enable_gqa=hq != hkv
+        )
+    return out.transpose(1, 2)
+
+
+def attention(q: Tensor, k: Tensor, v: Tensor, kv_cache=None, layer_id: int = 0, attn_mask: Optional[Tensor] = None,
+              is_causal: bool = False, fwd: Optional[str] = None) -> Tensor:
+    """Single entry used by the model blocks (signature of the reference's ``attention(...)``,
+    ``astrai/extension/backend/attention.py:256-303``).
+
+    ``fwd=None``: dense ``[B,S,H,D]`` tensors, no cache.  ``fwd in {"prefill","decode"}``: packed ``[T,H,D]``
+    tensors plus a :class:`~astrai_b200.ops.kv.KVCache`; new K/V are appended to the pool first.
+    """
+    if fwd is None:
+        return dense_attention(q, k, v, attn_mask, is_causal)
+    from astrai_b200.ops.paged_attention import cached_attention
+
+    return cached_attention(q, k, v, kv_cache, layer_id, attn_mask, is_causal, fwd)

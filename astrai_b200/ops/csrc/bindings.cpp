@@ -1,0 +1,229 @@
+// torch.ops.astrai_b200.* : tensor-level entry points of the sm_100a kernels.
+// Only this file sees torch headers; kernels live in torch-free .cu files (launchers.h).
+#include <ATen/ATen.h>
+#include <ATen/cuda/CUDAContext.h>
+#include <c10/cuda/CUDAGuard.h>
+#include <torch/library.h>
+
+#include <map>
+
+#include "launchers.h"
+
+namespace {
+
+using at::Tensor;
+
+inline cudaStream_t stream() { return at::cuda::getCurrentCUDAStream().stream(); }
+inline bool is_bf16(const Tensor& t) {
+  TORCH_CHECK(t.scalar_type() == at::kBFloat16 || t.scalar_type() == at::kFloat, "expected bf16 or fp32 tensor");
+  return t.scalar_type() == at::kBFloat16;
+}
+#define CHECK_CUDA_CONTIG(t) TORCH_CHECK((t).is_cuda() && (t).is_contiguous(), #t " must be a contiguous CUDA tensor")
+
+std::tuple<Tensor, Tensor> rmsnorm_fwd(const Tensor& x, const Tensor& w, double eps) {
+  CHECK_CUDA_CONTIG(x);
+  CHECK_CUDA_CONTIG(w);
+  TORCH_CHECK(x.scalar_type() == w.scalar_type(), "rmsnorm: x and weight dtypes differ");
+  const c10::cuda::CUDAGuard guard(x.device());
+  const int cols = (int)x.size(-1);
+  const long long rows = x.numel() / cols;
+  Tensor y = at::empty_like(x);
+  Tensor rstd = at::empty({rows}, x.options().dtype(at::kFloat));
+  ab::rmsnorm_fwd(x.data_ptr(), w.data_ptr(), y.data_ptr(), rstd.data_ptr<float>(), rows, cols, (float)eps,
+                  is_bf16(x), stream());
+  return {y, rstd};
+}
+
+std::tuple<Tensor, Tensor> rmsnorm_bwd(const Tensor& g, const Tensor& x, const Tensor& w, const Tensor& rstd) {
+  CHECK_CUDA_CONTIG(g);
+  CHECK_CUDA_CONTIG(x);
+  const c10::cuda::CUDAGuard guard(x.device());
+  const int cols = (int)x.size(-1);
+  const long long rows = x.numel() / cols;
+  Tensor dx = at::empty_like(x);
+  Tensor dw = at::empty({cols}, x.options().dtype(at::kFloat));
+  const int parts = ab::rmsnorm_bwd_parts(rows, cols);
+  Tensor partial = at::empty({parts > 0 ? parts : 1, cols}, dw.options());
+  ab::rmsnorm_bwd(g.data_ptr(), x.data_ptr(), w.data_ptr(), rstd.data_ptr<float>(), dx.data_ptr(),
+                  dw.data_ptr<float>(), partial.data_ptr<float>(), rows, cols, is_bf16(x), stream());
+  return {dx, dw};
+}
+
+// x, out: [tokens, heads, rot_dim] views with unit last stride; freqs: [tokens, rot_dim/2, 2] fp32 contiguous.
+void rope(const Tensor& x, Tensor& out, const Tensor& freqs, bool inverse) {
+  TORCH_CHECK(x.is_cuda() && x.dim() == 3 && out.dim() == 3 && x.stride(2) == 1 && out.stride(2) == 1, "rope: bad layout");
+  TORCH_CHECK(freqs.is_contiguous() && freqs.scalar_type() == at::kFloat, "rope: freqs must be contiguous fp32");
+  TORCH_CHECK(x.size(2) % 8 == 0 && freqs.numel() == x.size(0) * x.size(2), "rope: rot_dim must be a multiple of 8 and match freqs");
+  TORCH_CHECK(x.stride(0) % 8 == 0 && x.stride(1) % 8 == 0 && out.stride(0) % 8 == 0 && out.stride(1) % 8 == 0 &&
+                  (reinterpret_cast<uintptr_t>(x.data_ptr()) & 15) == 0 &&
+                  (reinterpret_cast<uintptr_t>(out.data_ptr()) & 15) == 0,
+              "rope: views must keep 16-byte alignment");
+  TORCH_CHECK(x.scalar_type() == out.scalar_type(), "rope: dtype mismatch");
+  const c10::cuda::CUDAGuard guard(x.device());
+  ab::rope_apply(x.data_ptr(), out.data_ptr(), freqs.data_ptr<float>(), x.size(0), (int)x.size(1), (int)x.size(2),
+                 x.stride(0), (int)x.stride(1), out.stride(0), (int)out.stride(1), inverse, is_bf16(x), stream());
+}
+
+// gate, up: [rows, F] views sharing one row stride (for example the two halves of a [rows, 2F] GEMM output).
+Tensor swiglu_fwd(const Tensor& gate, const Tensor& up) {
+  TORCH_CHECK(gate.is_cuda() && gate.dim() == 2 && gate.stride(1) == 1 && up.stride(1) == 1 &&
+                  gate.stride(0) == up.stride(0) && gate.size(1) % 8 == 0 && gate.stride(0) % 8 == 0,
+              "swiglu: bad layout");
+  const c10::cuda::CUDAGuard guard(gate.device());
+  Tensor y = at::empty({gate.size(0), gate.size(1)}, gate.options());
+  ab::swiglu_fwd(gate.data_ptr(), up.data_ptr(), y.data_ptr(), gate.size(0), (int)gate.size(1), gate.stride(0),
+                 is_bf16(gate), stream());
+  return y;
+}
+
+// returns [rows, 2F]: columns [0,F) = d gate, [F,2F) = d up
+Tensor swiglu_bwd(const Tensor& dy, const Tensor& gate, const Tensor& up) {
+  CHECK_CUDA_CONTIG(dy);
+  const c10::cuda::CUDAGuard guard(gate.device());
+  const long long rows = gate.size(0);
+  const int f = (int)gate.size(1);
+  Tensor d = at::empty({rows, 2 * (long long)f}, gate.options());
+  char* base = static_cast<char*>(d.data_ptr());
+  ab::swiglu_bwd(dy.data_ptr(), gate.data_ptr(), up.data_ptr(), base, base + (size_t)f * d.element_size(), rows, f,
+                 gate.stride(0), 2LL * f, is_bf16(gate), stream());
+  return d;
+}
+
+Tensor embedding_fwd(const Tensor& ids, const Tensor& table) {
+  CHECK_CUDA_CONTIG(ids);
+  CHECK_CUDA_CONTIG(table);
+  TORCH_CHECK(ids.scalar_type() == at::kLong && table.size(1) % 8 == 0, "embedding: ids int64, dim % 8 == 0");
+  const c10::cuda::CUDAGuard guard(table.device());
+  auto shape = ids.sizes().vec();
+  shape.push_back(table.size(1));
+  Tensor out = at::empty(shape, table.options());
+  ab::embedding_fwd(ids.data_ptr<int64_t>() ? (const long long*)ids.data_ptr<int64_t>() : nullptr, table.data_ptr(),
+                    out.data_ptr(), ids.numel(), (int)table.size(1), table.size(0), is_bf16(table), stream());
+  return out;
+}
+
+void embedding_bwd_(const Tensor& ids, const Tensor& g, Tensor& grad_table) {
+  CHECK_CUDA_CONTIG(ids);
+  CHECK_CUDA_CONTIG(g);
+  CHECK_CUDA_CONTIG(grad_table);
+  TORCH_CHECK(grad_table.scalar_type() == at::kFloat, "embedding_bwd_: fp32 accumulation buffer expected");
+  const c10::cuda::CUDAGuard guard(g.device());
+  ab::embedding_bwd((const long long*)ids.data_ptr<int64_t>(), g.data_ptr(), grad_table.data_ptr<float>(), ids.numel(),
+                    (int)grad_table.size(1), grad_table.size(0), is_bf16(g), stream());
+}
+
+// logits [rows, V] (unit column stride).  Writes the gradient over `logits` when in_place_grad (scaled by grad_scale[0]).
+std::tuple<Tensor, Tensor> ce_rows(Tensor& logits, const Tensor& targets, double smoothing, int64_t ignore_index,
+                                   const c10::optional<Tensor>& grad_scale, bool in_place_grad) {
+  TORCH_CHECK(logits.is_cuda() && logits.dim() == 2 && logits.stride(1) == 1, "ce_rows: logits must be [rows, V]");
+  CHECK_CUDA_CONTIG(targets);
+  TORCH_CHECK(targets.scalar_type() == at::kLong && targets.numel() == logits.size(0), "ce_rows: targets int64 [rows]");
+  TORCH_CHECK(!in_place_grad || grad_scale.has_value(), "ce_rows: grad_scale required for the gradient");
+  const c10::cuda::CUDAGuard guard(logits.device());
+  const long long rows = logits.size(0);
+  Tensor loss = at::empty({rows}, logits.options().dtype(at::kFloat));
+  Tensor logprob = at::empty({rows}, loss.options());
+  ab::ce_rows(logits.data_ptr(), in_place_grad ? logits.data_ptr() : nullptr, (const long long*)targets.data_ptr<int64_t>(),
+              loss.data_ptr<float>(), logprob.data_ptr<float>(),
+              grad_scale.has_value() ? grad_scale->data_ptr<float>() : nullptr, rows, (int)logits.size(1),
+              logits.stride(0), (float)smoothing, ignore_index, is_bf16(logits), stream());
+  return {loss, logprob};
+}
+
+void logprob_bwd_(Tensor& logits, const Tensor& targets, const Tensor& logprob, const Tensor& g_rows) {
+  TORCH_CHECK(logits.is_cuda() && logits.dim() == 2 && logits.stride(1) == 1, "logprob_bwd_: logits must be [rows, V]");
+  const c10::cuda::CUDAGuard guard(logits.device());
+  ab::logprob_bwd(logits.data_ptr(), logits.data_ptr(), (const long long*)targets.data_ptr<int64_t>(),
+                  logprob.data_ptr<float>(), g_rows.data_ptr<float>(), logits.size(0), (int)logits.size(1),
+                  logits.stride(0), is_bf16(logits), stream());
+}
+
+void sumsq_(const Tensor& x, Tensor& out) {
+  CHECK_CUDA_CONTIG(x);
+  const c10::cuda::CUDAGuard guard(x.device());
+  ab::sumsq_accum(x.data_ptr(), x.numel(), out.data_ptr<float>(), is_bf16(x), stream());
+}
+
+void clip_coef_(const Tensor& sumsq, double max_norm, double pre_scale, Tensor& coef, Tensor& norm) {
+  const c10::cuda::CUDAGuard guard(sumsq.device());
+  ab::clip_coef(sumsq.data_ptr<float>(), (float)max_norm, (float)pre_scale, coef.data_ptr<float>(),
+                norm.data_ptr<float>(), stream());
+}
+
+void adamw_(Tensor& p, const c10::optional<Tensor>& master, Tensor& g, Tensor& m, Tensor& v, double lr, double b1,
+            double b2, double eps, double wd, int64_t step, const c10::optional<Tensor>& gscale, bool zero_grad) {
+  CHECK_CUDA_CONTIG(p);
+  CHECK_CUDA_CONTIG(g);
+  TORCH_CHECK(g.scalar_type() == at::kFloat && m.scalar_type() == at::kFloat && v.scalar_type() == at::kFloat,
+              "adamw_: gradient and moments are fp32");
+  TORCH_CHECK(g.numel() == p.numel() && m.numel() == p.numel() && v.numel() == p.numel(), "adamw_: size mismatch");
+  const c10::cuda::CUDAGuard guard(p.device());
+  ab::adamw_step(p.data_ptr(), master.has_value() ? master->data_ptr<float>() : nullptr, g.data_ptr<float>(),
+                 m.data_ptr<float>(), v.data_ptr<float>(), p.numel(), (float)lr, (float)b1, (float)b2, (float)eps,
+                 (float)wd, (int)step, gscale.has_value() ? gscale->data_ptr<float>() : nullptr, zero_grad, is_bf16(p),
+                 stream());
+}
+
+void axpy_f32_(Tensor& dst, const Tensor& src, double alpha) {
+  CHECK_CUDA_CONTIG(dst);
+  CHECK_CUDA_CONTIG(src);
+  TORCH_CHECK(dst.scalar_type() == at::kFloat && dst.numel() == src.numel(), "axpy_f32_: fp32 destination, equal sizes");
+  const c10::cuda::CUDAGuard guard(dst.device());
+  ab::axpy_f32(dst.data_ptr<float>(), src.data_ptr(), dst.numel(), (float)alpha, is_bf16(src), stream());
+}
+
+Tensor& status_tensor(const at::Device& dev) {
+  static std::map<int, Tensor> per_device;
+  auto it = per_device.find(dev.index());
+  if (it == per_device.end())
+    it = per_device.emplace(dev.index(), at::zeros({4}, at::TensorOptions().device(dev).dtype(at::kInt))).first;
+  return it->second;
+}
+
+Tensor kernel_status(const Tensor& like) { return status_tensor(like.device()); }
+
+// D[M,N] (+)= op(A) x op(B).  A is [M,K] (a_kmajor) or [K,M]; B is [N,K] (b_kmajor) or [K,N]; all 2-D, unit column stride.
+Tensor gemm(const Tensor& A, const Tensor& B, const c10::optional<Tensor>& D_in, bool a_kmajor, bool b_kmajor,
+            bool out_f32, bool accumulate) {
+  TORCH_CHECK(A.is_cuda() && B.is_cuda() && A.dim() == 2 && B.dim() == 2 && A.stride(1) == 1 && B.stride(1) == 1,
+              "gemm: operands must be 2-D CUDA tensors with unit column stride");
+  TORCH_CHECK(A.scalar_type() == at::kBFloat16 && B.scalar_type() == at::kBFloat16, "gemm: bf16 operands");
+  const c10::cuda::CUDAGuard guard(A.device());
+  const int M = (int)(a_kmajor ? A.size(0) : A.size(1)), K = (int)(a_kmajor ? A.size(1) : A.size(0));
+  const int N = (int)(b_kmajor ? B.size(0) : B.size(1)), Kb = (int)(b_kmajor ? B.size(1) : B.size(0));
+  TORCH_CHECK(K == Kb, "gemm: inner dimensions differ (", K, " vs ", Kb, ")");
+  Tensor D;
+  if (D_in.has_value()) {
+    D = *D_in;
+    TORCH_CHECK(D.dim() == 2 && D.size(0) == M && D.size(1) == N && D.stride(1) == 1, "gemm: bad output shape");
+    TORCH_CHECK(D.scalar_type() == (out_f32 ? at::kFloat : at::kBFloat16), "gemm: output dtype mismatch");
+  } else {
+    TORCH_CHECK(!accumulate, "gemm: accumulate needs an output tensor");
+    D = at::empty({M, N}, A.options().dtype(out_f32 ? at::kFloat : at::kBFloat16));
+  }
+  const int rc = ab::gemm_bf16(A.data_ptr(), B.data_ptr(), D.data_ptr(), M, N, K, A.stride(0), B.stride(0), D.stride(0),
+                               a_kmajor, b_kmajor, out_f32, accumulate, status_tensor(A.device()).data_ptr<int>(), stream());
+  TORCH_CHECK(rc == 0, "gemm_bf16 launch failed with code ", rc,
+              " (-1: operand not 16-byte aligned / stride not a multiple of 8, -2: tensor map, -4/-5: launch)");
+  return D;
+}
+
+}  // namespace
+
+TORCH_LIBRARY(astrai_b200, m) {
+  m.def("rmsnorm_fwd(Tensor x, Tensor w, float eps) -> (Tensor, Tensor)", &rmsnorm_fwd);
+  m.def("rmsnorm_bwd(Tensor g, Tensor x, Tensor w, Tensor rstd) -> (Tensor, Tensor)", &rmsnorm_bwd);
+  m.def("rope(Tensor x, Tensor(a!) out, Tensor freqs, bool inverse) -> ()", &rope);
+  m.def("swiglu_fwd(Tensor gate, Tensor up) -> Tensor", &swiglu_fwd);
+  m.def("swiglu_bwd(Tensor dy, Tensor gate, Tensor up) -> Tensor", &swiglu_bwd);
+  m.def("embedding_fwd(Tensor ids, Tensor table) -> Tensor", &embedding_fwd);
+  m.def("embedding_bwd_(Tensor ids, Tensor g, Tensor(a!) grad_table) -> ()", &embedding_bwd_);
+  m.def("ce_rows(Tensor(a!) logits, Tensor targets, float smoothing, int ignore_index, Tensor? grad_scale, bool in_place_grad) -> (Tensor, Tensor)", &ce_rows);
+  m.def("logprob_bwd_(Tensor(a!) logits, Tensor targets, Tensor logprob, Tensor g_rows) -> ()", &logprob_bwd_);
+  m.def("sumsq_(Tensor x, Tensor(a!) out) -> ()", &sumsq_);
+  m.def("clip_coef_(Tensor sumsq, float max_norm, float pre_scale, Tensor(a!) coef, Tensor(b!) norm) -> ()", &clip_coef_);
+  m.def("adamw_(Tensor(a!) p, Tensor? master, Tensor(b!) g, Tensor(c!) m, Tensor(d!) v, float lr, float b1, float b2, float eps, float wd, int step, Tensor? gscale, bool zero_grad) -> ()", &adamw_);
+  m.def("axpy_f32_(Tensor(a!) dst, Tensor src, float alpha) -> ()", &axpy_f32_);
+  m.def("kernel_status(Tensor like) -> Tensor", &kernel_status);
+  m.def("gemm(Tensor A, Tensor B, Tensor? D, bool a_kmajor, bool b_kmajor, bool out_f32, bool accumulate) -> Tensor", &gemm);
+}

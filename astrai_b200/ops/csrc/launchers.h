@@ -1,0 +1,44 @@
+// Host-callable launchers of the CUDA kernels.  No torch types here: the binding file converts tensors to
+// pointers, so the .cu files compile in seconds and can be linked into other hosts.
+#pragma once
+#include <cuda_runtime.h>
+
+namespace ab {
+
+void rmsnorm_fwd(const void* x, const void* w, void* y, float* rstd, long long rows, int cols, float eps,
+                 bool is_bf16, cudaStream_t st);
+int rmsnorm_bwd_parts(long long rows, int cols);
+void rmsnorm_bwd(const void* g, const void* x, const void* w, const float* rstd, void* dx, float* dw, float* partial,
+                 long long rows, int cols, bool is_bf16, cudaStream_t st);
+void rope_apply(const void* x, void* out, const float* freqs, long long tokens, int heads, int rot_dim,
+                long long x_tok_stride, int x_head_stride, long long o_tok_stride, int o_head_stride, bool inverse,
+                bool is_bf16, cudaStream_t st);
+void swiglu_fwd(const void* gate, const void* up, void* y, long long rows, int f, long long in_stride, bool is_bf16,
+                cudaStream_t st);
+void swiglu_bwd(const void* dy, const void* gate, const void* up, void* dgate, void* dup, long long rows, int f,
+                long long in_stride, long long out_stride, bool is_bf16, cudaStream_t st);
+void embedding_fwd(const long long* ids, const void* table, void* out, long long tokens, int dim, long long vocab,
+                   bool is_bf16, cudaStream_t st);
+void embedding_bwd(const long long* ids, const void* g, float* grad_table, long long tokens, int dim, long long vocab,
+                   bool is_bf16, cudaStream_t st);
+
+void ce_rows(const void* logits, void* dlogits, const long long* targets, float* loss, float* logprob,
+             const float* grad_scale, long long rows, int V, long long ld, float smoothing, long long ignore_index,
+             bool is_bf16, cudaStream_t st);
+void logprob_bwd(const void* logits, void* dlogits, const long long* targets, const float* logprob,
+                 const float* g_rows, long long rows, int V, long long ld, bool is_bf16, cudaStream_t st);
+void sumsq_accum(const void* x, long long n, float* out, bool is_bf16, cudaStream_t st);
+void clip_coef(const float* sumsq, float max_norm, float pre_scale, float* coef, float* norm_out, cudaStream_t st);
+void adamw_step(void* p, float* master, float* g, float* m, float* v, long long n, float lr, float b1, float b2,
+                float eps, float wd, int step, const float* gscale, bool zero_grad, bool p_bf16, cudaStream_t st);
+void axpy_f32(float* dst, const void* src, long long n, float alpha, bool src_bf16, cudaStream_t st);
+
+// tcgen05 GEMM: D[M,N] (+)= A * B with bf16 operands and fp32 accumulation in tensor memory.
+//   a_kmajor: A is [M,K] row-major (true) or stored as [K,M] row-major (false)
+//   b_kmajor: B is [N,K] row-major (true) or stored as [K,N] row-major (false)
+//   out_f32 : D is fp32 (else bf16); accumulate: D += result (read-modify-write in the epilogue)
+// lda/ldb/ldd are row strides in elements of the stored matrices.  Returns 0, or a negative code on a bad argument.
+int gemm_bf16(const void* A, const void* B, void* D, int M, int N, int K, long long lda, long long ldb, long long ldd,
+              bool a_kmajor, bool b_kmajor, bool out_f32, bool accumulate, int* status, cudaStream_t st);
+
+}  // namespace ab
