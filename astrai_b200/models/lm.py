@@ -37,6 +37,8 @@ def _init_module(m: nn.Module):
 
 @ModelFactory.register("autoregressive_lm")
 class AutoRegressiveLM(AutoModel):
+    supports_fused_head = True  # forward(..., return_logits=False) feeds a fused projection + loss
+
     def __init__(self, config: AutoRegressiveLMConfig):
         super().__init__(config)
         rope_dim = config.qk_rope_head_dim if config.attn_type == "mla" else config.hidden_size // config.num_attention_heads

@@ -5,6 +5,7 @@
 #include <c10/cuda/CUDAGuard.h>
 #include <torch/library.h>
 
+#include <atomic>
 #include <map>
 
 #include "launchers.h"
@@ -12,6 +13,11 @@
 namespace {
 
 using at::Tensor;
+
+// Number of kernels of this library launched by this process (each binding adds what it launches).
+std::atomic<long long> g_launches{0};
+inline void count(int n = 1) { g_launches.fetch_add(n, std::memory_order_relaxed); }
+int64_t launch_count() { return g_launches.load(); }
 
 inline cudaStream_t stream() { return at::cuda::getCurrentCUDAStream().stream(); }
 inline bool is_bf16(const Tensor& t) {
@@ -29,6 +35,7 @@ std::tuple<Tensor, Tensor> rmsnorm_fwd(const Tensor& x, const Tensor& w, double 
   const long long rows = x.numel() / cols;
   Tensor y = at::empty_like(x);
   Tensor rstd = at::empty({rows}, x.options().dtype(at::kFloat));
+  count();
   ab::rmsnorm_fwd(x.data_ptr(), w.data_ptr(), y.data_ptr(), rstd.data_ptr<float>(), rows, cols, (float)eps,
                   is_bf16(x), stream());
   return {y, rstd};
@@ -44,6 +51,7 @@ std::tuple<Tensor, Tensor> rmsnorm_bwd(const Tensor& g, const Tensor& x, const T
   Tensor dw = at::empty({cols}, x.options().dtype(at::kFloat));
   const int parts = ab::rmsnorm_bwd_parts(rows, cols);
   Tensor partial = at::empty({parts > 0 ? parts : 1, cols}, dw.options());
+  count(2);
   ab::rmsnorm_bwd(g.data_ptr(), x.data_ptr(), w.data_ptr(), rstd.data_ptr<float>(), dx.data_ptr(),
                   dw.data_ptr<float>(), partial.data_ptr<float>(), rows, cols, is_bf16(x), stream());
   return {dx, dw};
@@ -60,6 +68,7 @@ void rope(const Tensor& x, Tensor& out, const Tensor& freqs, bool inverse) {
               "rope: views must keep 16-byte alignment");
   TORCH_CHECK(x.scalar_type() == out.scalar_type(), "rope: dtype mismatch");
   const c10::cuda::CUDAGuard guard(x.device());
+  count();
   ab::rope_apply(x.data_ptr(), out.data_ptr(), freqs.data_ptr<float>(), x.size(0), (int)x.size(1), (int)x.size(2),
                  x.stride(0), (int)x.stride(1), out.stride(0), (int)out.stride(1), inverse, is_bf16(x), stream());
 }
@@ -71,6 +80,7 @@ Tensor swiglu_fwd(const Tensor& gate, const Tensor& up) {
               "swiglu: bad layout");
   const c10::cuda::CUDAGuard guard(gate.device());
   Tensor y = at::empty({gate.size(0), gate.size(1)}, gate.options());
+  count();
   ab::swiglu_fwd(gate.data_ptr(), up.data_ptr(), y.data_ptr(), gate.size(0), (int)gate.size(1), gate.stride(0),
                  is_bf16(gate), stream());
   return y;
@@ -84,6 +94,7 @@ Tensor swiglu_bwd(const Tensor& dy, const Tensor& gate, const Tensor& up) {
   const int f = (int)gate.size(1);
   Tensor d = at::empty({rows, 2 * (long long)f}, gate.options());
   char* base = static_cast<char*>(d.data_ptr());
+  count();
   ab::swiglu_bwd(dy.data_ptr(), gate.data_ptr(), up.data_ptr(), base, base + (size_t)f * d.element_size(), rows, f,
                  gate.stride(0), 2LL * f, is_bf16(gate), stream());
   return d;
@@ -97,6 +108,7 @@ Tensor embedding_fwd(const Tensor& ids, const Tensor& table) {
   auto shape = ids.sizes().vec();
   shape.push_back(table.size(1));
   Tensor out = at::empty(shape, table.options());
+  count();
   ab::embedding_fwd(ids.data_ptr<int64_t>() ? (const long long*)ids.data_ptr<int64_t>() : nullptr, table.data_ptr(),
                     out.data_ptr(), ids.numel(), (int)table.size(1), table.size(0), is_bf16(table), stream());
   return out;
@@ -108,6 +120,7 @@ void embedding_bwd_(const Tensor& ids, const Tensor& g, Tensor& grad_table) {
   CHECK_CUDA_CONTIG(grad_table);
   TORCH_CHECK(grad_table.scalar_type() == at::kFloat, "embedding_bwd_: fp32 accumulation buffer expected");
   const c10::cuda::CUDAGuard guard(g.device());
+  count();
   ab::embedding_bwd((const long long*)ids.data_ptr<int64_t>(), g.data_ptr(), grad_table.data_ptr<float>(), ids.numel(),
                     (int)grad_table.size(1), grad_table.size(0), is_bf16(g), stream());
 }
@@ -123,6 +136,7 @@ std::tuple<Tensor, Tensor> ce_rows(Tensor& logits, const Tensor& targets, double
   const long long rows = logits.size(0);
   Tensor loss = at::empty({rows}, logits.options().dtype(at::kFloat));
   Tensor logprob = at::empty({rows}, loss.options());
+  count();
   ab::ce_rows(logits.data_ptr(), in_place_grad ? logits.data_ptr() : nullptr, (const long long*)targets.data_ptr<int64_t>(),
               loss.data_ptr<float>(), logprob.data_ptr<float>(),
               grad_scale.has_value() ? grad_scale->data_ptr<float>() : nullptr, rows, (int)logits.size(1),
@@ -133,6 +147,7 @@ std::tuple<Tensor, Tensor> ce_rows(Tensor& logits, const Tensor& targets, double
 void logprob_bwd_(Tensor& logits, const Tensor& targets, const Tensor& logprob, const Tensor& g_rows) {
   TORCH_CHECK(logits.is_cuda() && logits.dim() == 2 && logits.stride(1) == 1, "logprob_bwd_: logits must be [rows, V]");
   const c10::cuda::CUDAGuard guard(logits.device());
+  count();
   ab::logprob_bwd(logits.data_ptr(), logits.data_ptr(), (const long long*)targets.data_ptr<int64_t>(),
                   logprob.data_ptr<float>(), g_rows.data_ptr<float>(), logits.size(0), (int)logits.size(1),
                   logits.stride(0), is_bf16(logits), stream());
@@ -141,11 +156,13 @@ void logprob_bwd_(Tensor& logits, const Tensor& targets, const Tensor& logprob, 
 void sumsq_(const Tensor& x, Tensor& out) {
   CHECK_CUDA_CONTIG(x);
   const c10::cuda::CUDAGuard guard(x.device());
+  count();
   ab::sumsq_accum(x.data_ptr(), x.numel(), out.data_ptr<float>(), is_bf16(x), stream());
 }
 
 void clip_coef_(const Tensor& sumsq, double max_norm, double pre_scale, Tensor& coef, Tensor& norm) {
   const c10::cuda::CUDAGuard guard(sumsq.device());
+  count();
   ab::clip_coef(sumsq.data_ptr<float>(), (float)max_norm, (float)pre_scale, coef.data_ptr<float>(),
                 norm.data_ptr<float>(), stream());
 }
@@ -158,6 +175,7 @@ void adamw_(Tensor& p, const c10::optional<Tensor>& master, Tensor& g, Tensor& m
               "adamw_: gradient and moments are fp32");
   TORCH_CHECK(g.numel() == p.numel() && m.numel() == p.numel() && v.numel() == p.numel(), "adamw_: size mismatch");
   const c10::cuda::CUDAGuard guard(p.device());
+  count();
   ab::adamw_step(p.data_ptr(), master.has_value() ? master->data_ptr<float>() : nullptr, g.data_ptr<float>(),
                  m.data_ptr<float>(), v.data_ptr<float>(), p.numel(), (float)lr, (float)b1, (float)b2, (float)eps,
                  (float)wd, (int)step, gscale.has_value() ? gscale->data_ptr<float>() : nullptr, zero_grad, is_bf16(p),
@@ -169,6 +187,7 @@ void axpy_f32_(Tensor& dst, const Tensor& src, double alpha) {
   CHECK_CUDA_CONTIG(src);
   TORCH_CHECK(dst.scalar_type() == at::kFloat && dst.numel() == src.numel(), "axpy_f32_: fp32 destination, equal sizes");
   const c10::cuda::CUDAGuard guard(dst.device());
+  count();
   ab::axpy_f32(dst.data_ptr<float>(), src.data_ptr(), dst.numel(), (float)alpha, is_bf16(src), stream());
 }
 
@@ -201,6 +220,7 @@ Tensor gemm(const Tensor& A, const Tensor& B, const c10::optional<Tensor>& D_in,
     TORCH_CHECK(!accumulate, "gemm: accumulate needs an output tensor");
     D = at::empty({M, N}, A.options().dtype(out_f32 ? at::kFloat : at::kBFloat16));
   }
+  count();
   const int rc = ab::gemm_bf16(A.data_ptr(), B.data_ptr(), D.data_ptr(), M, N, K, A.stride(0), B.stride(0), D.stride(0),
                                a_kmajor, b_kmajor, out_f32, accumulate, status_tensor(A.device()).data_ptr<int>(), stream());
   TORCH_CHECK(rc == 0, "gemm_bf16 launch failed with code ", rc,
@@ -225,5 +245,6 @@ TORCH_LIBRARY(astrai_b200, m) {
   m.def("adamw_(Tensor(a!) p, Tensor? master, Tensor(b!) g, Tensor(c!) m, Tensor(d!) v, float lr, float b1, float b2, float eps, float wd, int step, Tensor? gscale, bool zero_grad) -> ()", &adamw_);
   m.def("axpy_f32_(Tensor(a!) dst, Tensor src, float alpha) -> ()", &axpy_f32_);
   m.def("kernel_status(Tensor like) -> Tensor", &kernel_status);
+  m.def("launch_count() -> int", &launch_count);
   m.def("gemm(Tensor A, Tensor B, Tensor? D, bool a_kmajor, bool b_kmajor, bool out_f32, bool accumulate) -> Tensor", &gemm);
 }

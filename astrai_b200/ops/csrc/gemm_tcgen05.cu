@@ -361,17 +361,27 @@ EncodeFn encode_fn() {
 }
 
 // 2-D bf16 tensor map: `inner` contiguous elements per row, `outer` rows, row stride ld elements.
+thread_local int g_last_map_error = 0;
+
 bool make_map(CUtensorMap* out, const void* ptr, long long inner, long long outer, long long ld, int box_inner,
               int box_outer) {
   EncodeFn fn = encode_fn();
-  if (!fn) return false;
+  if (!fn) {
+    g_last_map_error = -1;
+    return false;
+  }
+  // The driver entry point needs a current context; a fresh thread (autograd worker) has none until its first
+  // runtime call, so make one here (only on a cache miss).
+  cudaFree(nullptr);
   cuuint64_t dims[2] = {(cuuint64_t)inner, (cuuint64_t)outer};
   cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
   cuuint32_t box[2] = {(cuuint32_t)box_inner, (cuuint32_t)box_outer};
   cuuint32_t estr[2] = {1, 1};
-  return fn(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, estr,
-            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+  const CUresult res = fn(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, estr,
+                          CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                          CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  g_last_map_error = (int)res;
+  return res == CUDA_SUCCESS;
 }
 
 struct MapCache {
@@ -426,8 +436,9 @@ int gemm_bf16(const void* A, const void* B, void* D, int M, int N, int K, long l
   CUtensorMap ma, mb;
   // K-major operand: stored [rows=MN, cols=K]; box 64(K) x tile rows.  MN-major: stored [rows=K, cols=MN]; box 64(MN) x BK.
   const bool oka = a_kmajor ? cache().get(&ma, A, K, M, lda, BK, BM) : cache().get(&ma, A, M, K, lda, 64, BK);
+  if (!oka) return -1000 - g_last_map_error;  // tensor map of A rejected: -1000 - CUresult
   const bool okb = b_kmajor ? cache().get(&mb, B, K, N, ldb, BK, BN) : cache().get(&mb, B, N, K, ldb, 64, BK);
-  if (!oka || !okb) return -2;
+  if (!okb) return -2000 - g_last_map_error;  // tensor map of B rejected: -2000 - CUresult
   const int sel = (a_kmajor ? 8 : 0) | (b_kmajor ? 4 : 0) | (out_f32 ? 2 : 0) | (accumulate ? 1 : 0);
   switch (sel) {
 #define AB_CASE(i, a, b, f, c) \

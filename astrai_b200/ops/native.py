@@ -62,6 +62,11 @@ def kernel_status(device) -> int:
     return int(require().kernel_status(like).max().item())
 
 
+def launch_count() -> int:
+    """Kernels of this library launched by this process so far."""
+    return int(require().launch_count())
+
+
 KERNEL_NAMES = (
     "gemm", "rmsnorm_fwd", "rmsnorm_bwd", "rope", "swiglu_fwd", "swiglu_bwd", "embedding_fwd", "embedding_bwd_",
     "ce_rows", "logprob_bwd_", "sumsq_", "clip_coef_", "adamw_", "axpy_f32_",

@@ -1,0 +1,15 @@
+from astrai_b200.parallel.executor import (
+    AccumOptimizer, AccumScheduler, BaseExecutor, DDPExecutor, ExecutorFactory, FSDPExecutor, GradientState,
+    NoneExecutor, broadcast_state_dict, create_ref_model,
+)
+from astrai_b200.parallel.flat import FlatParamEngine, FlatUnit
+from astrai_b200.parallel.setup import (
+    find_free_port, get_current_device, get_rank, get_world_size, only_on_rank, setup_parallel, spawn_parallel_fn,
+)
+
+__all__ = [
+    "AccumOptimizer", "AccumScheduler", "BaseExecutor", "DDPExecutor", "ExecutorFactory", "FSDPExecutor",
+    "FlatParamEngine", "FlatUnit", "GradientState", "NoneExecutor", "broadcast_state_dict", "create_ref_model",
+    "find_free_port", "get_current_device", "get_rank", "get_world_size", "only_on_rank", "setup_parallel",
+    "spawn_parallel_fn",
+]

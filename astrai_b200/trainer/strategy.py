@@ -1,0 +1,340 @@
+"""Training objectives: next-token (seq), masked SFT, DPO and GRPO (offline and online).
+
+Loss definitions are the reference's (``astrai/trainer/strategy.py:312-665``).  Two things differ by design:
+
+* the vocabulary projection is fused with the loss (``ops.linear_cross_entropy`` / ``ops.linear_token_logprobs``)
+  whenever the model can return hidden states without logits, so no ``[B*S, V]`` fp32 tensor is ever stored;
+* metric values stay on the device until somebody reads them (:class:`DeferredMetrics`), which removes the
+  reference's device->host sync on every micro-batch (``strategy.py:219-222``, ``trainer.py:86``).
+"""
+
+from __future__ import annotations
+
+from typing import TYPE_CHECKING, Callable, Dict, List, Optional, TypedDict, Union
+
+import torch
+import torch.nn as nn
+import torch.nn.functional as F
+from torch import Tensor
+
+from astrai_b200 import ops
+from astrai_b200.factory import BaseFactory
+from astrai_b200.parallel.executor import broadcast_state_dict
+
+if TYPE_CHECKING:
+    from astrai_b200.trainer.rollout import RolloutResult
+
+
+class DeferredMetrics(dict):
+    """A dict of scalars whose tensor values turn into Python floats only when read."""
+
+    @staticmethod
+    def _value(v):
+        return float(v.detach().float().item()) if isinstance(v, Tensor) else v
+
+    def __getitem__(self, key):
+        v = self._value(dict.__getitem__(self, key))
+        dict.__setitem__(self, key, v)
+        return v
+
+    def get(self, key, default=None):
+        return self[key] if key in self else default
+
+    def items(self):
+        return [(k, self[k]) for k in dict.keys(self)]
+
+    def values(self):
+        return [self[k] for k in dict.keys(self)]
+
+    def resolved(self) -> Dict[str, float]:
+        return dict(self.items())
+
+
+class LossOutput(TypedDict):
+    loss: Tensor
+    metrics: Dict[str, float]
+
+
+class LogprobsOutput(TypedDict):
+    logprobs: Tensor
+    aux_loss: Optional[Tensor]
+    router_stats: Optional[list]
+
+
+def move_to_device(batch: Dict[str, Tensor], device) -> Dict[str, Tensor]:
+    return {k: (v.to(device, non_blocking=True) if isinstance(v, Tensor) else v) for k, v in batch.items()}
+
+
+def _fused_head(model) -> Optional[nn.Module]:
+    """The module whose ``lm_head`` can be fused with the loss, or None (wrapped or foreign models)."""
+    inner = getattr(model, "module", model)
+    if getattr(inner, "supports_fused_head", False) and hasattr(inner, "lm_head"):
+        return inner
+    return None
+
+
+def token_logprobs(model, input_ids: Tensor, input_mask: Optional[Tensor], position_ids: Optional[Tensor] = None):
+    """Log-probability of ``input_ids[:, 1:]`` under the model, shape ``[B, S-1]`` fp32, plus the forward outputs."""
+    ids_in, ids_out = input_ids[:, :-1], input_ids[:, 1:]
+    if input_mask is not None:
+        input_mask = input_mask[:, :, :-1, :-1] if input_mask.dim() == 4 else input_mask[:, :-1]
+    inner = _fused_head(model)
+    if inner is not None and ids_in.is_cuda:
+        out = model(ids_in, input_mask, return_logits=False)
+        lp = ops.linear_token_logprobs(out["hidden_states"], inner.lm_head.weight, ids_out)
+    else:
+        out = model(ids_in, input_mask)
+        lp = torch.log_softmax(out["logits"].float(), dim=-1).gather(-1, ids_out.unsqueeze(-1)).squeeze(-1)
+    return lp, out
+
+
+def get_logprobs(model, input_ids: Tensor, attn_mask: Tensor, loss_mask: Tensor, reduction: str) -> LogprobsOutput:
+    """Masked (and optionally reduced) next-token log-probabilities (reference ``strategy.py:33-84``)."""
+    if reduction not in ("mean", "sum", "none"):
+        raise ValueError(f"reduction must be one of ['mean', 'sum', 'none'], got '{reduction}'")
+    lp, out = token_logprobs(model, input_ids, attn_mask)
+    m = loss_mask[:, 1:].to(lp.dtype)
+    if reduction == "sum":
+        lp = (lp * m).sum(-1)
+    elif reduction == "mean":
+        lp = (lp * m).sum(-1) / m.sum(-1).clamp(min=1.0)
+    else:
+        lp = lp * m
+    return {"logprobs": lp, "aux_loss": out.get("aux_loss"), "router_stats": out.get("router_stats")}
+
+
+def make_doc_boundary_mask(position_ids: Tensor) -> Tensor:
+    """``[B,1,S,S]`` bool: causal and within one packed document (a document starts where positions do not grow)."""
+    b, s = position_ids.shape
+    starts = position_ids[:, 1:] <= position_ids[:, :-1]
+    doc = F.pad(starts.long().cumsum(dim=1), (1, 0))
+    same = doc[:, :, None] == doc[:, None, :]
+    causal = torch.ones(s, s, dtype=torch.bool, device=position_ids.device).tril()
+    return (same & causal)[:, None]
+
+
+def causal_padding_mask(key_valid: Tensor) -> Tensor:
+    """``[B,1,S,S]`` bool: causal AND key is a real token."""
+    s = key_valid.shape[-1]
+    causal = torch.ones(s, s, dtype=torch.bool, device=key_valid.device).tril()
+    return key_valid.bool()[:, None, None, :] & causal[None, None]
+
+
+def moe_diagnostics(router_stats_list) -> Dict[str, Tensor]:
+    """Router entropy, dead-expert fraction and load imbalance (mean / max), averaged over MoE layers; device tensors."""
+    rows: List[Tensor] = []
+    for stats in router_stats_list or ():
+        probs = stats["probs"].float()
+        e = probs.shape[-1]
+        probs = probs.reshape(-1, e)
+        if e == 0 or probs.numel() == 0:
+            continue
+        idx = stats["topk_indices"].reshape(-1)
+        entropy = -(probs * probs.clamp_min(1e-8).log()).sum(-1).mean()
+        counts = torch.zeros(e, dtype=torch.float32, device=probs.device).scatter_add_(
+            0, idx, torch.ones_like(idx, dtype=torch.float32))
+        ratios = counts / counts.mean().clamp(min=1.0)
+        rows.append(torch.stack([entropy, (counts == 0).float().mean(), (ratios - 1).abs().mean(), ratios.max()]))
+    if not rows:
+        return {}
+    avg = torch.stack(rows).mean(0)
+    names = ("router_entropy", "dead_expert_fraction", "load_imbalance_mean", "load_imbalance_max")
+    return {n: avg[i] for i, n in enumerate(names)}
+
+
+class BaseStrategy:
+    """Turns a batch into ``{"loss": tensor, "metrics": {...}}``; online mode when a rollout runner is injected."""
+
+    def __init__(self, model: Union[nn.Module, Callable[..., Dict[str, Tensor]]], device, **kwargs):
+        self.model, self.device = model, device
+        self.executor = kwargs.pop("executor", None)
+        self.moe_aux_loss_coef = kwargs.pop("moe_aux_loss_coef", 0.01)
+        self.strategy_kwargs = kwargs
+        self._moe_metrics: Dict[str, float] = DeferredMetrics()
+        self._rollout_runner = None
+
+    def compute_loss(self, batch) -> Tensor:
+        return self.compute_loss_output(batch)["loss"]
+
+    def compute_loss_output(self, batch) -> LossOutput:
+        out = self.compute_loss(batch)
+        return out if isinstance(out, dict) else {"loss": out, "metrics": DeferredMetrics(loss=out.detach())}
+
+    def _loss_output(self, task_loss: Tensor, metrics: Dict[str, Tensor], aux_loss: Optional[Tensor] = None,
+                     router_stats=None) -> LossOutput:
+        total = task_loss
+        if aux_loss is not None:
+            weighted = self.moe_aux_loss_coef * aux_loss
+            total = total + weighted
+            metrics["moe_aux_loss"], metrics["moe_aux_loss_weighted"] = aux_loss, weighted
+            diag = DeferredMetrics(moe_diagnostics(router_stats))
+            diag["aux_loss"] = aux_loss.detach()
+            self._moe_metrics = diag
+        metrics["loss"] = total
+        return {"loss": total, "metrics": DeferredMetrics({k: (v.detach() if isinstance(v, Tensor) else v) for k, v in metrics.items()})}
+
+    def supports_online(self) -> bool:
+        return False
+
+    def set_rollout_runner(self, runner):
+        self._rollout_runner = runner
+
+    def prepare_from_rollout(self, result: "RolloutResult") -> Dict[str, Tensor]:
+        raise NotImplementedError(f"{type(self).__name__} does not support online rollout")
+
+    def _on_rollout_refresh(self):
+        pass
+
+    def on_optimizer_step(self):
+        if self._rollout_runner is not None:
+            self._rollout_runner.step()
+
+    def __call__(self, batch) -> LossOutput:
+        if self._rollout_runner is None:
+            return self.compute_loss_output(batch)
+        result, fresh = self._rollout_runner(batch)
+        if fresh:
+            self._on_rollout_refresh()
+        return self.compute_loss_output(self.prepare_from_rollout(result))
+
+
+class StrategyFactory(BaseFactory["BaseStrategy"]):
+    pass
+
+
+class _TokenCEStrategy(BaseStrategy):
+    def __init__(self, model, device, label_smoothing: float = 0.0, **kwargs):
+        super().__init__(model, device, **kwargs)
+        self.label_smoothing = label_smoothing
+
+    def _ce(self, input_ids, targets, ignore_index=-100, **fwd):
+        inner = _fused_head(self.model)
+        if inner is not None and input_ids.is_cuda:
+            out = self.model(input_ids=input_ids, return_logits=False, **fwd)
+            loss = ops.linear_cross_entropy(out["hidden_states"], inner.lm_head.weight, targets,
+                                            self.label_smoothing, ignore_index)
+        else:
+            out = self.model(input_ids=input_ids, **fwd)
+            loss = ops.cross_entropy(out["logits"], targets, self.label_smoothing, ignore_index)
+        return self._loss_output(loss, {"task_loss": loss}, out.get("aux_loss"), out.get("router_stats"))
+
+
+@StrategyFactory.register("seq")
+class SEQStrategy(_TokenCEStrategy):
+    """Next-token cross-entropy over every position (mean), optional label smoothing."""
+
+    def compute_loss_output(self, batch) -> LossOutput:
+        batch = move_to_device(batch, self.device)
+        return self._ce(batch["input_ids"], batch["target_ids"])
+
+
+@StrategyFactory.register("sft")
+class SFTStrategy(_TokenCEStrategy):
+    """Cross-entropy on positions where ``loss_mask`` is set; attention stays inside each packed document."""
+
+    def compute_loss_output(self, batch) -> LossOutput:
+        batch = move_to_device(batch, self.device)
+        pos = batch["position_ids"]
+        targets = batch["target_ids"].masked_fill(~batch["loss_mask"].bool(), -100)
+        return self._ce(batch["input_ids"], targets, position_ids=pos, input_mask=make_doc_boundary_mask(pos))
+
+
+@StrategyFactory.register("dpo")
+class DPOStrategy(BaseStrategy):
+    """``-logsigmoid(beta * ((pi_c - pi_r) - (ref_c - ref_r)))``; token id 0 is padding."""
+
+    def __init__(self, model, device, ref_model, beta: float = 0.1, reduction: str = "sum", **kwargs):
+        super().__init__(model, device, **kwargs)
+        self.ref_model, self.beta, self.reduction = ref_model, beta, reduction
+
+    def compute_loss_output(self, batch) -> LossOutput:
+        batch = move_to_device(batch, self.device)
+        n = batch["chosen"].shape[0]
+        ids = torch.cat([batch["chosen"], batch["rejected"]], dim=0)
+        loss_mask = torch.cat([batch["chosen_mask"], batch["rejected_mask"]], dim=0)
+        mask = causal_padding_mask(ids.ne(0))
+        pol = get_logprobs(self.model, ids, mask, loss_mask, self.reduction)
+        with torch.no_grad():
+            ref = get_logprobs(self.ref_model, ids, mask, loss_mask, self.reduction)["logprobs"]
+        pi = pol["logprobs"]
+        margin = (pi[:n] - pi[n:]) - (ref[:n] - ref[n:])
+        loss = -F.logsigmoid(self.beta * margin).mean()
+        return self._loss_output(loss, {"dpo_loss": loss}, pol["aux_loss"], pol.get("router_stats"))
+
+    def supports_online(self) -> bool:
+        return True
+
+    def prepare_from_rollout(self, result: "RolloutResult") -> Dict[str, Tensor]:
+        rows = torch.arange(result.responses.shape[0], device=result.responses.device)
+        best, worst = result.rewards.argmax(-1), result.rewards.argmin(-1)
+        return {
+            "chosen": result.responses[rows, best], "chosen_mask": result.response_mask[rows, best].float(),
+            "rejected": result.responses[rows, worst], "rejected_mask": result.response_mask[rows, worst].float(),
+        }
+
+
+@StrategyFactory.register("grpo")
+class GRPOStrategy(BaseStrategy):
+    """Group-relative PPO on response tokens with a k1-style KL penalty to a frozen reference model."""
+
+    def __init__(self, model, device, old_model, ref_model, clip_eps: float = 0.2, kl_coef: float = 0.01,
+                 group_size: int = 4, **kwargs):
+        super().__init__(model, device, **kwargs)
+        self.old_model, self.ref_model = old_model, ref_model
+        self.clip_eps, self.kl_coef, self.group_size = clip_eps, kl_coef, group_size
+
+    def sync_old_model(self):
+        sd = self.executor.unwrap_model(self.model)
+        if self.executor.use_distributed:
+            sd = broadcast_state_dict(sd)
+        if sd is not None:
+            self.old_model.load_state_dict(sd)
+
+    def compute_loss_output(self, batch) -> LossOutput:
+        batch = move_to_device(batch, self.device)
+        prompts, responses, masks, rewards = batch["prompts"], batch["responses"], batch["masks"], batch["rewards"]
+        b, g, rlen = responses.shape
+        resp = responses.reshape(b * g, rlen)
+        rmask = masks.reshape(b * g, rlen)
+        prompt = prompts[:, None].expand(-1, g, -1).reshape(b * g, -1)
+        pmask = batch.get("prompt_mask")
+        pmask = prompts.ne(0) if pmask is None else pmask
+        pmask = pmask[:, None].expand(-1, g, -1).reshape(b * g, -1)
+        plen = prompt.shape[1]
+        seq = torch.cat([prompt, resp], dim=-1)
+        loss_mask = torch.cat([torch.zeros_like(prompt, dtype=torch.bool), rmask.bool()], dim=-1)
+        attn = causal_padding_mask(torch.cat([pmask.bool(), rmask.bool()], dim=-1))
+
+        def response_logprobs(model):
+            out = get_logprobs(model, seq, attn, loss_mask, "none")
+            return out["logprobs"][:, plen - 1:].reshape(b, g, -1), out
+
+        lp_pol, pol = response_logprobs(self.model)
+        with torch.no_grad():
+            lp_old, _ = response_logprobs(self.old_model)
+            lp_ref, _ = response_logprobs(self.ref_model)
+        tok = rmask.reshape(b, g, -1).float()
+        count = tok.sum().clamp(min=1.0)
+        eps = 1e-8
+        adv = ((rewards - rewards.mean(-1, keepdim=True)) / (rewards.std(-1, keepdim=True, unbiased=False) + eps))[..., None]
+        ratio = torch.exp(lp_pol - lp_old)
+        surrogate = -torch.min(ratio * adv, ratio.clamp(1 - self.clip_eps, 1 + self.clip_eps) * adv)
+        policy_loss = (surrogate * tok).sum() / count
+        r = torch.exp(lp_ref - lp_pol)
+        kl = self.kl_coef * ((r - torch.log(r + eps) - 1.0) * tok).sum() / count
+        return self._loss_output(policy_loss + kl, {"policy_loss": policy_loss, "kl_loss": kl},
+                                 pol["aux_loss"], pol.get("router_stats"))
+
+    def supports_online(self) -> bool:
+        return True
+
+    def prepare_from_rollout(self, result: "RolloutResult") -> Dict[str, Tensor]:
+        return {"prompts": result.prompts, "prompt_mask": result.prompt_mask, "responses": result.responses,
+                "masks": result.response_mask, "rewards": result.rewards}
+
+    def _on_rollout_refresh(self):
+        self.sync_old_model()
+
+
+StrategyFactory.register("online_grpo")(GRPOStrategy)
+StrategyFactory.register("online_dpo")(DPOStrategy)

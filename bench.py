@@ -1,0 +1,366 @@
+"""Headline benchmark: 1B-class dense decoder pre-training, FSDP, bf16, synthetic packed tokens.
+
+    python bench.py --gpus N --steps K --warmup W [--impl ours|reference]
+
+Model / recipe: 24 layers, d_model 2048, 16 query / 4 KV heads (head_dim 128), SwiGLU FFN 5632, vocab 32000, tied
+embeddings, RoPE; seq 2048, batch_per_device 4, grad_accum 8 (one "step" = one optimizer step = 65 536 tokens per GPU),
+AdamW (lr 1e-4, wd 0.1), label smoothing 0.05, gradient clipping at 1.0.  Weak scaling: per-GPU work is fixed.
+
+Two measurements per run, both over exactly K optimizer steps after W warm-up steps, bracketed by barrier +
+``torch.cuda.synchronize()``, timed with CUDA events, max over ranks:
+  * ``value``   - the training step driven directly with token batches already resident on the device;
+  * ``e2e``     - the same recipe through the public ``Trainer(TrainConfig).train()`` call: every micro-batch is
+                  collated on the host, pinned, copied host->device inside the timed region, and the loss / gradient
+                  norm are read back device->host every optimizer step.
+``--impl reference`` runs the unmodified reference package (installed under ``baseline/_ref``) through its own
+``Trainer`` on the same model, data shape and recipe.  One JSON line is printed by rank 0.
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import tempfile
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+MODEL = dict(vocab_size=32000, hidden_size=2048, num_hidden_layers=24, rms_norm_eps=1e-6, intermediate_size=5632,
+             tie_word_embeddings=True, max_position_embeddings=2048, rope_theta=10000.0, num_attention_heads=16,
+             num_key_value_heads=4)
+SEQ, BPD, ACCUM = 2048, 4, 8
+LR, WD, SMOOTH, CLIP = 1e-4, 0.1, 0.05, 1.0
+BASELINE_VALUE = None  # the reference publishes no training throughput
+
+
+# ----------------------------------------------------------------------------------------------- clocks sampling
+class ClockSampler:
+    """Samples SM clocks and throttle reasons of this rank's GPU with nvidia-smi while the timed region runs."""
+
+    FIELDS = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index, self.proc, self.path = index, None, None
+
+    def start(self):
+        try:
+            fd, self.path = tempfile.mkstemp(suffix=".csv")
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "200", "-i", str(self.index)],
+                stdout=fd, stderr=subprocess.DEVNULL)
+            os.close(fd)
+        except Exception:
+            self.proc = None
+
+    def stop(self) -> dict:
+        out = {"sm_mhz": None, "sm_max_mhz": None, "reasons": []}
+        if self.proc is None:
+            return out
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except Exception:
+            self.proc.kill()
+        clocks, reasons = [], set()
+        names = ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")
+        try:
+            for line in open(self.path):
+                parts = [p.strip() for p in line.split(",")]
+                if len(parts) < 6 or not parts[0].isdigit():
+                    continue
+                clocks.append(int(parts[0]))
+                out["sm_max_mhz"] = int(parts[1])
+                for n, v in zip(names, parts[2:6]):
+                    if v.lower().startswith("active"):
+                        reasons.add(n)
+            os.unlink(self.path)
+        except Exception:
+            pass
+        if clocks:
+            out["sm_mhz"] = statistics.median(clocks)
+        out["reasons"] = sorted(reasons)
+        out["samples"] = len(clocks)
+        return out
+
+
+# ----------------------------------------------------------------------------------------------- shared pieces
+def _dist_env():
+    rank = int(os.environ.get("RANK", 0))
+    world = int(os.environ.get("WORLD_SIZE", 1))
+    local = int(os.environ.get("LOCAL_RANK", rank))
+    return rank, world, local
+
+
+def _max_over_ranks(ms: float) -> float:
+    import torch
+    import torch.distributed as dist
+
+    if dist.is_available() and dist.is_initialized() and dist.get_world_size() > 1:
+        t = torch.tensor([ms], dtype=torch.float64, device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+    return ms
+
+
+def _barrier_sync():
+    import torch
+    import torch.distributed as dist
+
+    if dist.is_available() and dist.is_initialized() and dist.get_world_size() > 1:
+        dist.barrier()
+    torch.cuda.synchronize()
+
+
+class _HostTokens:
+    """Map-style dataset of packed uniform token ids living in host memory (seq strategy layout)."""
+
+    def __init__(self, n, seq, vocab, seed=0):
+        import torch
+
+        g = torch.Generator().manual_seed(seed)
+        self.data = torch.randint(0, vocab, (n, seq + 1), generator=g)
+
+    def __len__(self):
+        return self.data.shape[0]
+
+    def __getitem__(self, i):
+        row = self.data[i]
+        return {"input_ids": row[:-1], "target_ids": row[1:]}
+
+
+class _StepTimer:
+    """Trainer callback: CUDA-event brackets around optimizer steps [W, W+K) counted in micro-batches."""
+
+    def __init__(self, warmup, steps, accum, sampler=None):
+        self.begin_at, self.end_at = warmup * accum, (warmup + steps) * accum
+        self.seen = 0
+        self.ms = None
+        self.sampler = sampler
+        self.launches = None
+        self.count_fn = None
+        self.host_syncs = []
+
+    def on_batch_begin(self, context):
+        import torch
+
+        if self.seen == self.begin_at:
+            _barrier_sync()
+            if self.sampler:
+                self.sampler.start()
+            if self.count_fn:
+                self._count0 = self.count_fn()
+            self._e0 = torch.cuda.Event(enable_timing=True)
+            self._e1 = torch.cuda.Event(enable_timing=True)
+            self._e0.record()
+        elif self.seen == self.end_at:
+            self._e1.record()
+            _barrier_sync()
+            self.ms = _max_over_ranks(self._e0.elapsed_time(self._e1))
+            if self.count_fn:
+                self.launches = self.count_fn() - self._count0
+            self.clocks = self.sampler.stop() if self.sampler else None
+            context.request_stop()
+        self.seen += 1
+
+    def on_optimizer_step(self, context):
+        # the step's results are read on the host every optimizer step (device->host inside the timed region)
+        _ = context.loss
+        _ = context.grad_norm
+
+
+def _quiet_progress(callbacks):
+    """Progress bars go to stderr so that stdout carries the JSON line only."""
+    for cb in callbacks:
+        if type(cb).__name__ == "ProgressBarCallback":
+            cb.file = sys.stderr
+
+
+def _emit(args, world, value_ms, e2e_ms, launches, clocks, impl, extra_cfg=None, note=None):
+    tokens_per_step = world * BPD * ACCUM * SEQ
+    value = tokens_per_step * args.steps / (value_ms / 1e3) if value_ms else None
+    e2e = tokens_per_step * args.steps / (e2e_ms / 1e3) if e2e_ms else None
+    line = {
+        "metric": "train tok/s/box (1B dense FSDP)", "value": value if value is not None else e2e, "unit": "tokens/s",
+        "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": (value_ms or e2e_ms) / args.steps, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None if not BASELINE_VALUE else (value or e2e) / BASELINE_VALUE, "dtype": "bf16",
+        "data": "synthetic uniform token ids, random-init weights", "impl": impl,
+        "config": {"model": "1B dense decoder (24L d2048 16q/4kv hd128 ffn5632 v32000 tied)", "global_batch": world * BPD * ACCUM,
+                   "seq_len": SEQ, "batch_per_device": BPD, "grad_accum": ACCUM, "parallelism": f"fsdp{world}",
+                   "optimizer": "AdamW lr1e-4 wd0.1", "label_smoothing": SMOOTH, "max_grad_norm": CLIP,
+                   "l2": "per-step working set (activations, weights, gradients > 10 GB) far exceeds the 126 MB L2; no explicit flush",
+                   **(extra_cfg or {})},
+        "clocks": clocks or {"sm_mhz": None, "sm_max_mhz": None, "reasons": []},
+        "e2e": {"value": e2e, "unit": "tokens/s", "ms_per_step": (e2e_ms / args.steps) if e2e_ms else None,
+                "h2d_bytes_per_step": ACCUM * BPD * SEQ * 8 * 2, "d2h_bytes_per_step": 8},
+        "gpu_launches": launches,
+    }
+    if note:
+        line["note"] = note
+    print(json.dumps(line), flush=True)
+
+
+# ----------------------------------------------------------------------------------------------- our arm
+def run_ours(args):
+    import torch
+
+    from astrai_b200.config import AutoRegressiveLMConfig, TrainConfig
+    from astrai_b200.models import AutoRegressiveLM
+    from astrai_b200.ops import native
+    from astrai_b200.optim import FusedAdamW
+    from astrai_b200.parallel.setup import setup_parallel
+    from astrai_b200.trainer import SchedulerFactory, Trainer
+    from astrai_b200.trainer.train_context import TrainContextBuilder
+
+    rank, world, local = _dist_env()
+    native.require()
+    cfg = AutoRegressiveLMConfig(**MODEL)
+    total_steps = args.warmup + args.steps
+
+    def model_fn():
+        torch.manual_seed(1234)
+        return AutoRegressiveLM(cfg).to(torch.bfloat16)
+
+    def make_config(dataset, ckpt_dir):
+        return TrainConfig(
+            model_fn=model_fn, strategy="seq", dataset=dataset,
+            optimizer_fn=lambda m: FusedAdamW(m.parameters(), lr=LR, betas=(0.9, 0.999), weight_decay=WD),
+            scheduler_fn=lambda o: SchedulerFactory.create("cosine", o, warmup_steps=2, lr_decay_steps=10_000),
+            batch_per_device=BPD, grad_accum_steps=ACCUM, max_grad_norm=CLIP, ckpt_dir=ckpt_dir, ckpt_interval=10**9,
+            metrics=["loss", "lr", "grad_norm"], pin_memory=True, nprocs=world, parallel_mode="fsdp",
+            strategy_kwargs={"label_smoothing": SMOOTH}, master_addr=os.environ.get("MASTER_ADDR", "127.0.0.1"),
+            master_port=os.environ.get("MASTER_PORT", "29511"), executor_kwargs={"comm": args.comm},
+        )
+
+    results = {}
+    with setup_parallel(rank, world, local, "nccl", os.environ.get("MASTER_ADDR", "127.0.0.1"),
+                        os.environ.get("MASTER_PORT", "29511"), "cuda"):
+        dev = torch.device("cuda", local)
+        # ---- (1) device-resident inputs: the step itself --------------------------------------------------------
+        n_micro = total_steps * ACCUM
+        ds = _HostTokens(64, SEQ, MODEL["vocab_size"], seed=rank)
+        trainer = Trainer(make_config(ds, tempfile.mkdtemp(prefix="bench_ckpt_")), callbacks=[])
+        trainer.callbacks = [cb for cb in trainer.callbacks if type(cb).__name__ in ("GradientClippingCallback",)]
+        ctx = TrainContextBuilder(trainer.train_config).build()
+        ctx.model.train()
+        pool = [{k: torch.stack([ds[(i * BPD + j) % len(ds)][k] for j in range(BPD)]).to(dev) for k in ("input_ids", "target_ids")}
+                for i in range(16)]
+        sampler = ClockSampler(local) if rank == 0 else None
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        for i in range(n_micro):
+            if i == args.warmup * ACCUM:
+                _barrier_sync()
+                if sampler:
+                    sampler.start()
+                c0 = native.launch_count()
+                e0.record()
+            with ctx.executor.accumulate(ctx.model):
+                trainer._micro_batch(ctx, pool[i % len(pool)])
+        e1.record()
+        _barrier_sync()
+        results["value_ms"] = _max_over_ranks(e0.elapsed_time(e1))
+        results["launches"] = native.launch_count() - c0
+        results["clocks"] = sampler.stop() if sampler else None
+        results["final_loss"] = ctx.loss
+        assert native.kernel_status(dev) == 0, "a kernel's bounded wait expired"
+        del ctx, trainer, pool
+        torch.cuda.empty_cache()
+        # ---- (2) end to end through Trainer.train(): host data, pinned H2D per micro-batch, D2H per step -----------
+        if not args.skip_e2e:
+            host = _HostTokens((n_micro + 2) * BPD, SEQ, MODEL["vocab_size"], seed=100 + rank)
+            timer = _StepTimer(args.warmup, args.steps, ACCUM)
+            t2 = Trainer(make_config(host, tempfile.mkdtemp(prefix="bench_ckpt_")), callbacks=[timer])
+            # keep the stock callbacks except the ones that write 2 GB checkpoints at exit
+            t2.callbacks = [cb for cb in t2.callbacks if type(cb).__name__ not in ("CheckpointCallback", "MetricCallback")]
+            _quiet_progress(t2.callbacks)
+            t2.train()
+            results["e2e_ms"] = timer.ms
+    if rank == 0:
+        _emit(args, world, results["value_ms"], results.get("e2e_ms"), results["launches"], results["clocks"], "ours",
+              {"comm": args.comm, "final_loss": round(float(results["final_loss"]), 4)})
+
+
+# ----------------------------------------------------------------------------------------------- reference arm
+def run_reference(args):
+    ref_root = os.path.join(ROOT, "baseline", "_ref")
+    if not os.path.isdir(os.path.join(ref_root, "astrai")):
+        print(json.dumps({"impl": "reference", "unavailable": "baseline/_ref/astrai is missing (offline install not present)"}))
+        return
+    sys.path.insert(0, ref_root)
+    try:
+        import torch
+        from astrai.config import AutoRegressiveLMConfig, TrainConfig
+        from astrai.model import AutoRegressiveLM
+        from astrai.trainer import SchedulerFactory, Trainer
+    except Exception as exc:  # noqa: BLE001
+        print(json.dumps({"impl": "reference", "unavailable": f"reference import failed: {type(exc).__name__}: {exc}"[:300]}))
+        return
+
+    rank, world, local = _dist_env()
+    cfg = AutoRegressiveLMConfig(**MODEL)
+    total_steps = args.warmup + args.steps
+    n_micro = total_steps * ACCUM
+    sampler = ClockSampler(local) if rank == 0 else None
+    timer = _StepTimer(args.warmup, args.steps, ACCUM, sampler)
+
+    def model_fn():
+        torch.manual_seed(1234)
+        return AutoRegressiveLM(cfg).to(torch.bfloat16)  # the reference's train script casts the model to bf16
+
+    def attempt(tied: bool):
+        cfg.tie_word_embeddings = tied
+        host = _HostTokens((n_micro + 2) * BPD * 1, SEQ, MODEL["vocab_size"], seed=100 + rank)
+        tc = TrainConfig(
+            model_fn=model_fn, strategy="seq", dataset=host,
+            optimizer_fn=lambda m: torch.optim.AdamW(m.parameters(), lr=LR, weight_decay=WD, fused=True),
+            scheduler_fn=lambda o: SchedulerFactory.create("cosine", o, warmup_steps=2, lr_decay_steps=10_000),
+            batch_per_device=BPD, grad_accum_steps=ACCUM, max_grad_norm=CLIP,
+            ckpt_dir=tempfile.mkdtemp(prefix="ref_ckpt_"), ckpt_interval=10**9, metrics=["loss", "lr", "grad_norm"],
+            pin_memory=True, nprocs=world, parallel_mode="fsdp", strategy_kwargs={"label_smoothing": SMOOTH},
+            master_addr=os.environ.get("MASTER_ADDR", "127.0.0.1"), master_port=os.environ.get("MASTER_PORT", "29512"),
+        )
+        tr = Trainer(tc, callbacks=[timer])
+        # stock callbacks stay, except the two that serialise a 2 GB checkpoint when training stops
+        tr.callbacks = [cb for cb in tr.callbacks if type(cb).__name__ not in ("CheckpointCallback", "MetricCallback")]
+        _quiet_progress(tr.callbacks)
+        tr.train()
+
+    note = None
+    try:
+        attempt(True)
+    except Exception as exc:  # noqa: BLE001
+        if world > 1 and timer.ms is None:
+            note = f"tied embeddings failed under the reference's FSDP ({type(exc).__name__}); ran untied"
+            timer.seen = 0
+            attempt(False)
+        else:
+            raise
+    if rank == 0:
+        _emit(args, world, None, timer.ms, 0, getattr(timer, "clocks", None), "reference", note=note)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=6)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--comm", default=os.environ.get("ASTRAI_B200_FSDP_COMM", "nccl"), choices=["nccl", "p2p"])
+    ap.add_argument("--skip-e2e", action="store_true")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 1)
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()
