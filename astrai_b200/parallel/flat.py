@@ -145,9 +145,12 @@ class FlatParamEngine:
 
     def _fuse(self, unit: FlatUnit, parts: List[nn.Parameter]):
         """A [sum(rows), cols] view over adjacent 2-D parameters (None if they are not back to back)."""
-        idx = [unit.params.index(p) for p in parts if any(p is q for q in unit.params)]
-        if len(idx) != len(parts):
-            return None
+        idx = []
+        for p in parts:
+            where = [i for i, q in enumerate(unit.params) if q is p]
+            if not where:
+                return None
+            idx.append(where[0])
         cols = parts[0].shape[1]
         start = unit.offsets[idx[0]]
         expect = start

@@ -118,21 +118,24 @@ def _barrier_sync():
     torch.cuda.synchronize()
 
 
-class _HostTokens:
+def _host_tokens(n, seq, vocab, seed=0):
     """Map-style dataset of packed uniform token ids living in host memory (seq strategy layout)."""
+    import torch
+    from torch.utils.data import Dataset
 
-    def __init__(self, n, seq, vocab, seed=0):
-        import torch
+    class HostTokens(Dataset):
+        def __init__(self):
+            g = torch.Generator().manual_seed(seed)
+            self.data = torch.randint(0, vocab, (n, seq + 1), generator=g)
 
-        g = torch.Generator().manual_seed(seed)
-        self.data = torch.randint(0, vocab, (n, seq + 1), generator=g)
+        def __len__(self):
+            return self.data.shape[0]
 
-    def __len__(self):
-        return self.data.shape[0]
+        def __getitem__(self, i):
+            row = self.data[i]
+            return {"input_ids": row[:-1], "target_ids": row[1:]}
 
-    def __getitem__(self, i):
-        row = self.data[i]
-        return {"input_ids": row[:-1], "target_ids": row[1:]}
+    return HostTokens()
 
 
 class _StepTimer:
@@ -245,7 +248,7 @@ def run_ours(args):
         dev = torch.device("cuda", local)
         # ---- (1) device-resident inputs: the step itself --------------------------------------------------------
         n_micro = total_steps * ACCUM
-        ds = _HostTokens(64, SEQ, MODEL["vocab_size"], seed=rank)
+        ds = _host_tokens(64, SEQ, MODEL["vocab_size"], seed=rank)
         trainer = Trainer(make_config(ds, tempfile.mkdtemp(prefix="bench_ckpt_")), callbacks=[])
         trainer.callbacks = [cb for cb in trainer.callbacks if type(cb).__name__ in ("GradientClippingCallback",)]
         ctx = TrainContextBuilder(trainer.train_config).build()
@@ -274,7 +277,7 @@ def run_ours(args):
         torch.cuda.empty_cache()
         # ---- (2) end to end through Trainer.train(): host data, pinned H2D per micro-batch, D2H per step -----------
         if not args.skip_e2e:
-            host = _HostTokens((n_micro + 2) * BPD, SEQ, MODEL["vocab_size"], seed=100 + rank)
+            host = _host_tokens((n_micro + 2) * BPD, SEQ, MODEL["vocab_size"], seed=100 + rank)
             timer = _StepTimer(args.warmup, args.steps, ACCUM)
             t2 = Trainer(make_config(host, tempfile.mkdtemp(prefix="bench_ckpt_")), callbacks=[timer])
             # keep the stock callbacks except the ones that write 2 GB checkpoints at exit
@@ -316,7 +319,7 @@ def run_reference(args):
 
     def attempt(tied: bool):
         cfg.tie_word_embeddings = tied
-        host = _HostTokens((n_micro + 2) * BPD * 1, SEQ, MODEL["vocab_size"], seed=100 + rank)
+        host = _host_tokens((n_micro + 2) * BPD * 1, SEQ, MODEL["vocab_size"], seed=100 + rank)
         tc = TrainConfig(
             model_fn=model_fn, strategy="seq", dataset=host,
             optimizer_fn=lambda m: torch.optim.AdamW(m.parameters(), lr=LR, weight_decay=WD, fused=True),
