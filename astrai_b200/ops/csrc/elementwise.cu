@@ -156,13 +156,21 @@ __global__ void rmsnorm_bwd_small_kernel(const T* __restrict__ g, const T* __res
   }
 }
 
-// out[c] = sum_p partial[p, c]
+// out[c] = sum_p partial[p, c].  Block (32, 8): 32 adjacent columns, 8 row-lanes striding over the parts.
 __global__ void colsum_kernel(const float* __restrict__ partial, float* __restrict__ out, int parts, int cols) {
-  const int c = blockIdx.x * blockDim.x + threadIdx.x;
-  if (c >= cols) return;
+  __shared__ float acc[8][33];
+  const int c = blockIdx.x * 32 + threadIdx.x;
   float s = 0.f;
-  for (int p = 0; p < parts; ++p) s += partial[(long long)p * cols + c];
-  out[c] = s;
+  if (c < cols)
+    for (int p = threadIdx.y; p < parts; p += 8) s += partial[(long long)p * cols + c];
+  acc[threadIdx.y][threadIdx.x] = s;
+  __syncthreads();
+  if (threadIdx.y == 0 && c < cols) {
+    float t = 0.f;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) t += acc[j][threadIdx.x];
+    out[c] = t;
+  }
 }
 
 template <typename T>
@@ -190,7 +198,7 @@ void rmsnorm_fwd(const void* x, const void* w, void* y, float* rstd, long long r
 }
 
 int rmsnorm_bwd_parts(long long rows, int cols) {
-  if (cols % 8 == 0 && cols >= 512 && cols <= 16384) return (int)(rows < 592 ? rows : 592);  // 148 SMs x 4
+  if (cols % 8 == 0 && cols >= 512 && cols <= 16384) return (int)(rows < 296 ? rows : 296);  // 148 SMs x 2
   return 0;  // small path accumulates with atomics into a zeroed dw
 }
 
@@ -206,7 +214,7 @@ static void rmsnorm_bwd_t(const void* g, const void* x, const void* w, const flo
     else if (nvec <= 512) rmsnorm_bwd_kernel<T, 2><<<parts, 256, 0, st>>>(G, X, W, rstd, DX, partial, rows, cols);
     else if (nvec <= 1024) rmsnorm_bwd_kernel<T, 4><<<parts, 256, 0, st>>>(G, X, W, rstd, DX, partial, rows, cols);
     else rmsnorm_bwd_kernel<T, 8><<<parts, 256, 0, st>>>(G, X, W, rstd, DX, partial, rows, cols);
-    colsum_kernel<<<ceil_div(cols, 256), 256, 0, st>>>(partial, dw, parts, cols);
+    colsum_kernel<<<ceil_div(cols, 32), dim3(32, 8), 0, st>>>(partial, dw, parts, cols);
   } else {
     cudaMemsetAsync(dw, 0, sizeof(float) * cols, st);
     const int wpb = 8;

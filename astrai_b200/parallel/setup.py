@@ -154,8 +154,11 @@ def _spawn_local(func, world_size, backend, addr, port, device_type, start_metho
         for s, h in previous.items():
             if callable(h) and h is not on_signal:
                 signal.signal(s, h)
-        for p in ctx.processes:
-            p.join()
+        for p in ctx.processes:  # a rank that ignores SIGTERM (or is wedged) is killed after a grace period
+            p.join(timeout=15 if stop.is_set() else None)
+            if p.is_alive():
+                p.kill()
+                p.join()
 
 
 def spawn_parallel_fn(func: Callable, world_size: int, backend: str = "nccl", master_addr: str = "127.0.0.1",

@@ -36,13 +36,15 @@ class Trainer:
 
     def _default_callbacks(self) -> List[TrainCallback]:
         c = self.train_config
+        # Clipping runs first so that the metric log and the progress bar of a step show that step's gradient norm
+        # (the reference lists it last, which makes the logged norm lag one step behind).
         return [
             CallbackFactory.create("gradient_checkpointing", modules=c.gradient_checkpointing_modules),
+            CallbackFactory.create("gradient_clipping", c.max_grad_norm),
             CallbackFactory.create("checkpoint", c.ckpt_dir, c.ckpt_interval),
             CallbackFactory.create("metric", ckpt_dir=c.ckpt_dir, save_interval=c.ckpt_interval, metrics=c.metrics,
                                    val_step=c.val_step),
             CallbackFactory.create("progress_bar", c.n_epoch),
-            CallbackFactory.create("gradient_clipping", c.max_grad_norm),
         ]
 
     def _fire(self, hook: str, context: TrainContext):
