@@ -16,11 +16,15 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include <stdlib.h>
+
 #include <map>
 #include <mutex>
 #include <tuple>
 
 #include "launchers.h"
+#include "tcgen05.cuh"
+#include "tma_host.h"
 
 namespace ab {
 namespace {
@@ -29,82 +33,11 @@ constexpr int BM = 128, BN = 256, BK = 64, STAGES = 4, UMMA_K = 16;
 constexpr int A_BYTES = BM * BK * 2, B_BYTES = BN * BK * 2, STAGE_BYTES = A_BYTES + B_BYTES;
 constexpr int NUM_THREADS = 192;
 constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*align slack*/ + 256 /*barriers*/;
-constexpr unsigned long long WAIT_LIMIT_NS = 2000000000ull;
 
 enum : int { ERR_PRODUCER = 1, ERR_MMA_FULL = 2, ERR_MMA_TMEM = 3, ERR_EPILOGUE = 4 };
 
-__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
-__device__ __forceinline__ unsigned long long gtime() {
-  unsigned long long t;
-  asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
-  return t;
-}
-__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
-  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
-}
-__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
-  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
-  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
-}
-__device__ __forceinline__ bool mbar_try(uint32_t bar, uint32_t parity) {
-  uint32_t ok;
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-      "selp.u32 %0, 1, 0, p;\n\t}"
-      : "=r"(ok)
-      : "r"(bar), "r"(parity)
-      : "memory");
-  return ok != 0;
-}
-// Bounded wait.  Returns false after WAIT_LIMIT_NS or as soon as another role raised the abort flag.
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
-  if (mbar_try(bar, parity)) return true;
-  const unsigned long long t0 = gtime();
-  for (uint32_t spin = 1;; ++spin) {
-    if (mbar_try(bar, parity)) return true;
-    if ((spin & 63u) == 0) {
-      if (*abort_flag) return false;
-      if (gtime() - t0 > WAIT_LIMIT_NS) return false;
-    }
-  }
-}
-__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int x, int y) {
-  asm volatile(
-      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];" ::"r"(
-          dst),
-      "l"(map), "r"(bar), "r"(x), "r"(y)
-      : "memory");
-}
-__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void tc_commit(uint32_t bar) {
-  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
-}
-__device__ __forceinline__ void tc_mma(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
-                                       uint32_t accumulate) {
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "setp.ne.b32 p, %4, 0;\n\t"
-      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, {%5, %5, %5, %5}, p;\n\t}" ::"r"(d_tmem),
-      "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(0u)
-      : "memory");
-}
-__device__ __forceinline__ void tc_ld32(uint32_t taddr, uint32_t (&r)[32]) {
-  asm volatile(
-      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
-      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, %17, %18, %19, %20, %21, %22, "
-      "%23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
-      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
-        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
-        "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
-        "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
-      : "r"(taddr)
-      : "memory");
-}
-__device__ __forceinline__ void tc_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+using namespace tc;
+using namespace tmah;
 
 // Shared-memory matrix descriptor for a 128-byte-swizzled tile (version 1, base offset 0).
 //   K-major : rows of 64 bf16 (128 B); 8-row groups 1024 B apart (SBO); LBO unused (1).
@@ -346,67 +279,6 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
 }
 
 // ------------------------------------------------------------------ host side
-using EncodeFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
-                              const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
-                              CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-EncodeFn encode_fn() {
-  static EncodeFn fn = [] {
-    void* p = nullptr;
-    cudaDriverEntryPointQueryResult q;
-    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) != cudaSuccess) p = nullptr;
-    return reinterpret_cast<EncodeFn>(p);
-  }();
-  return fn;
-}
-
-// 2-D bf16 tensor map: `inner` contiguous elements per row, `outer` rows, row stride ld elements.
-thread_local int g_last_map_error = 0;
-
-bool make_map(CUtensorMap* out, const void* ptr, long long inner, long long outer, long long ld, int box_inner,
-              int box_outer) {
-  EncodeFn fn = encode_fn();
-  if (!fn) {
-    g_last_map_error = -1;
-    return false;
-  }
-  // The driver entry point needs a current context; a fresh thread (autograd worker) has none until its first
-  // runtime call, so make one here (only on a cache miss).
-  cudaFree(nullptr);
-  cuuint64_t dims[2] = {(cuuint64_t)inner, (cuuint64_t)outer};
-  cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
-  cuuint32_t box[2] = {(cuuint32_t)box_inner, (cuuint32_t)box_outer};
-  cuuint32_t estr[2] = {1, 1};
-  const CUresult res = fn(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, estr,
-                          CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
-                          CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-  g_last_map_error = (int)res;
-  return res == CUDA_SUCCESS;
-}
-
-struct MapCache {
-  using Key = std::tuple<const void*, long long, long long, long long, int, int>;
-  std::map<Key, CUtensorMap> maps;
-  std::mutex mu;
-  bool get(CUtensorMap* out, const void* ptr, long long inner, long long outer, long long ld, int bi, int bo) {
-    Key k{ptr, inner, outer, ld, bi, bo};
-    std::lock_guard<std::mutex> g(mu);
-    auto it = maps.find(k);
-    if (it == maps.end()) {
-      CUtensorMap m;
-      if (!make_map(&m, ptr, inner, outer, ld, bi, bo)) return false;
-      if (maps.size() > 4096) maps.clear();
-      it = maps.emplace(k, m).first;
-    }
-    *out = it->second;
-    return true;
-  }
-};
-MapCache& cache() {
-  static MapCache c;
-  return c;
-}
-
 template <bool A_K, bool B_K, bool OUT_F32, bool ACCUM>
 int launch(const CUtensorMap& ma, const CUtensorMap& mb, void* D, int M, int N, int K, long long ldd, int* status,
            cudaStream_t st) {
@@ -433,6 +305,12 @@ int gemm_bf16(const void* A, const void* B, void* D, int M, int N, int K, long l
   if (M <= 0 || N <= 0 || K <= 0) return 0;
   if ((reinterpret_cast<uintptr_t>(A) & 15) || (reinterpret_cast<uintptr_t>(B) & 15) || (lda % 8) || (ldb % 8))
     return -1;  // TMA needs 16-byte aligned bases and row strides
+  static const bool force_single = [] {
+    const char* e = getenv("ASTRAI_B200_GEMM_1CTA");
+    return e && e[0] == '1';
+  }();
+  if (M >= 256 && !force_single)
+    return gemm_bf16_2cta(A, B, D, M, N, K, lda, ldb, ldd, a_kmajor, b_kmajor, out_f32, accumulate, status, st);
   CUtensorMap ma, mb;
   // K-major operand: stored [rows=MN, cols=K]; box 64(K) x tile rows.  MN-major: stored [rows=K, cols=MN]; box 64(MN) x BK.
   const bool oka = a_kmajor ? cache().get(&ma, A, K, M, lda, BK, BM) : cache().get(&ma, A, M, K, lda, 64, BK);

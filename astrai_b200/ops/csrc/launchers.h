@@ -41,4 +41,9 @@ void axpy_f32(float* dst, const void* src, long long n, float alpha, bool src_bf
 int gemm_bf16(const void* A, const void* B, void* D, int M, int N, int K, long long lda, long long ldb, long long ldd,
               bool a_kmajor, bool b_kmajor, bool out_f32, bool accumulate, int* status, cudaStream_t st);
 
+// Same contract, computed by CTA pairs (cta_group::2, 256x256 tiles).  Used by gemm_bf16 for M >= 256.
+int gemm_bf16_2cta(const void* A, const void* B, void* D, int M, int N, int K, long long lda, long long ldb,
+                   long long ldd, bool a_kmajor, bool b_kmajor, bool out_f32, bool accumulate, int* status,
+                   cudaStream_t st);
+
 }  // namespace ab
