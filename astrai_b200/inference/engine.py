@@ -1,0 +1,148 @@
+"""User-facing generation API over the continuous-batching scheduler.
+
+Reference: ``astrai/inference/engine.py:18-242`` (``generate`` for a string, a list, or a streaming generator;
+``generate_async``; ``get_stats``; ``shutdown``; 300 s timeout on blocking calls).
+"""
+
+from __future__ import annotations
+
+import asyncio
+import gc
+import threading
+from typing import Any, AsyncGenerator, Dict, Generator, List, Optional, Tuple, Union
+
+import torch
+
+from astrai_b200.inference.cache import PagePool
+from astrai_b200.inference.scheduler import InferenceScheduler
+from astrai_b200.inference.task import STOP
+
+
+class GenerateResult:
+    """Thread-safe accumulator: the scheduler thread appends text pieces, callers drain or wait for completion."""
+
+    def __init__(self, count: int = 1):
+        self._cond = threading.Condition()
+        self._event = threading.Event()
+        self.tokens: List[Tuple[int, Any]] = []
+        self.results: List[str] = [""] * count
+        self._done = [False] * count
+        self._completed, self._total = 0, count
+
+    def append(self, token, idx: int = 0):
+        with self._cond:
+            self.tokens.append((idx, token))
+            if token is STOP:
+                if not self._done[idx]:
+                    self._done[idx] = True
+                    self._completed += 1
+                    self._cond.notify_all()
+            else:
+                self.results[idx] += token
+            self._event.set()
+
+    def pop_all(self) -> List[Tuple[int, Any]]:
+        with self._cond:
+            out, self.tokens = self.tokens, []
+            if not out:
+                self._event.clear()
+            return out
+
+    def wait(self, timeout: Optional[float] = None) -> bool:
+        return self._event.wait(timeout=timeout)
+
+    def wait_completion(self, timeout: float = 300.0):
+        with self._cond:
+            if not self._cond.wait_for(lambda: self._completed >= self._total, timeout=timeout):
+                raise TimeoutError(f"Generation timeout after {timeout}s ({self._completed}/{self._total} completed)")
+
+    def get_results(self) -> List[str]:
+        with self._cond:
+            return list(self.results)
+
+
+class InferenceEngine:
+    def __init__(self, model, tokenizer, max_batch_size: int = 1, max_seq_len: Optional[int] = None,
+                 cache: Optional[PagePool] = None, enable_cuda_graph: bool = True, backend=None, **scheduler_kwargs):
+        self.model, self.tokenizer = model, tokenizer
+        self.scheduler = InferenceScheduler(model=model, tokenizer=tokenizer, max_batch_size=max_batch_size,
+                                            max_seq_len=max_seq_len, cache=cache, enable_cuda_graph=enable_cuda_graph,
+                                            backend=backend, **scheduler_kwargs)
+        self.scheduler.start()
+
+    def __enter__(self):
+        return self
+
+    def __exit__(self, *exc):
+        self.shutdown()
+        return False
+
+    def generate(self, prompt: Union[str, List[str]], stream: bool = False, max_tokens: Optional[int] = None,
+                 temperature: float = 1.0, top_p: float = 1.0, top_k: int = 50, frequency_penalty: float = 0.0,
+                 rep_window: int = 64) -> Union[Generator, str, List[str]]:
+        batch = isinstance(prompt, list)
+        prompts = prompt if batch else [prompt]
+        if max_tokens is not None and max_tokens <= 0:
+            if stream:
+                return iter(())
+            return [""] * len(prompts) if batch else ""
+        return self._generate(prompts, batch, stream, max_tokens, temperature, top_p, top_k, frequency_penalty, rep_window)
+
+    def generate_async(self, prompt: str, max_tokens: Optional[int] = None, temperature: float = 1.0, top_p: float = 1.0,
+                       top_k: int = 50, frequency_penalty: float = 0.0, rep_window: int = 64) -> AsyncGenerator[str, None]:
+        gen = self._generate([prompt], False, True, max_tokens, temperature, top_p, top_k, frequency_penalty, rep_window)
+
+        async def agen():
+            loop = asyncio.get_event_loop()
+            while True:
+                piece = await loop.run_in_executor(None, next, gen, None)
+                if piece is None:
+                    return
+                yield piece
+
+        return agen()
+
+    def _generate(self, prompts, batch, stream, max_tokens, temperature, top_p, top_k, frequency_penalty, rep_window):
+        result = GenerateResult(count=len(prompts))
+        task_ids = [
+            self.scheduler.add_task(prompt=p, max_tokens=max_tokens, temperature=temperature, top_p=top_p, top_k=top_k,
+                                    frequency_penalty=frequency_penalty, rep_window=rep_window,
+                                    stream_callback=lambda tok, i=i: result.append(tok, i))
+            for i, p in enumerate(prompts)
+        ]
+        if not stream:
+            try:
+                result.wait_completion()
+            finally:
+                for tid in task_ids:
+                    self.scheduler.remove_task(tid)
+            out = result.get_results()
+            return out if batch else out[0]
+
+        def gen():
+            open_streams = len(prompts)
+            closed = [False] * len(prompts)
+            while open_streams > 0:
+                for idx, tok in result.pop_all():
+                    if tok is STOP:
+                        if not closed[idx]:
+                            closed[idx] = True
+                            open_streams -= 1
+                    else:
+                        yield (idx, tok) if batch else tok
+                if open_streams > 0:
+                    result.wait(timeout=0.05)
+
+        return gen()
+
+    def get_stats(self) -> Dict[str, Any]:
+        return self.scheduler.get_stats()
+
+    backend_name = property(lambda self: self.scheduler.backend_name)
+    cuda_graph_enabled = property(lambda self: self.scheduler.cuda_graph_enabled)
+
+    def shutdown(self):
+        self.scheduler.stop()
+        if torch.cuda.is_available():
+            torch.cuda.empty_cache()
+        gc.collect()

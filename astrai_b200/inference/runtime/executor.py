@@ -1,0 +1,216 @@
+"""Model forwards of the serving loop: packed ragged prefill, batched decode (CUDA-graph replay), sampling.
+
+Counterpart of ``astrai/inference/runtime/executor.py:24-421``.  Differences: one packed prefill forward serves
+requests of DIFFERENT prompt lengths and different cached-prefix lengths (the reference runs one forward per
+``(prompt_len, start_pos)`` group); only the last position of each request goes through the vocabulary projection;
+sampling parameters and their host-side facts (largest k, any p < 1, any penalty) are cached per task set so a decode
+step performs exactly one device->host transfer (the sampled ids).
+"""
+
+from __future__ import annotations
+
+import logging
+import time
+from contextlib import contextmanager
+from dataclasses import dataclass
+from typing import List, Optional
+
+import torch
+from torch import Tensor
+
+from astrai_b200.inference.cache import PagePool, TaskCacheManager
+from astrai_b200.inference.runtime.graph import CudaGraphContext
+from astrai_b200.inference.runtime.sample import sample
+from astrai_b200.inference.task import Task
+from astrai_b200.inference.workspace import InferenceWorkspace
+
+logger = logging.getLogger(__name__)
+
+
+@contextmanager
+def timed(label: str, log: Optional[logging.Logger] = None):
+    """CUDA-event timer, active only when the logger is at DEBUG (``ASTR_LOG_LEVEL=DEBUG``)."""
+    log = log or logger
+    if not log.isEnabledFor(logging.DEBUG):
+        yield
+        return
+    cuda = torch.cuda.is_available()
+    if cuda:
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+    else:
+        tic = time.perf_counter()
+    yield
+    if cuda:
+        b.record()
+        torch.cuda.synchronize()
+        ms = a.elapsed_time(b)
+    else:
+        ms = (time.perf_counter() - tic) * 1000
+    log.debug("%s %.2fms", label, ms)
+
+
+@dataclass
+class SamplingBatchInfo:
+    temperatures: Tensor
+    top_ks: Tensor
+    top_ps: Tensor
+    freq_penalties: Tensor
+    has_freq: bool
+    hints: dict
+
+
+@dataclass
+class DecodeSteadyState:
+    task_sig: tuple
+    positions: List[int]
+    sampling_info: SamplingBatchInfo
+
+
+def build_sampling_info(tasks: List[Task], device) -> SamplingBatchInfo:
+    pin = str(device).startswith("cuda")
+
+    def col(values, dtype):
+        return torch.tensor(values, dtype=dtype, pin_memory=pin).to(device, non_blocking=True)
+
+    temps = [t.temperature for t in tasks]
+    ks = [t.top_k for t in tasks]
+    ps = [t.top_p for t in tasks]
+    fs = [t.frequency_penalty for t in tasks]
+    hints = {"max_k": max([0] + ks), "top_p_active": any(p < 1.0 for p in ps), "has_freq": any(f != 0 for f in fs),
+             "greedy": all(t == 0 for t in temps)}
+    return SamplingBatchInfo(col(temps, torch.float32), col(ks, torch.int32), col(ps, torch.float32),
+                             col(fs, torch.float32), hints["has_freq"], hints)
+
+
+class Executor:
+    def __init__(self, model, kv_cache: PagePool, task_cache: TaskCacheManager, device=None, dtype=None,
+                 enable_cuda_graph: bool = True, max_prefill_tokens: Optional[int] = None):
+        self.model, self.kv_cache, self.task_cache = model, kv_cache, task_cache
+        p = next(model.parameters())
+        self.device = torch.device(device) if device is not None else p.device
+        self.dtype = dtype or p.dtype
+        cfg = model.config
+        head_dim = cfg.hidden_size // cfg.num_attention_heads
+        self.max_prefill_tokens = max_prefill_tokens or kv_cache.max_batch_size * kv_cache.max_seq_len
+        self._workspace = InferenceWorkspace(kv_cache.max_batch_size, kv_cache.max_seq_len, cfg.num_attention_heads,
+                                             head_dim, self.device, self.dtype, n_kv_heads=cfg.num_key_value_heads,
+                                             max_prefill_tokens=min(self.max_prefill_tokens, 1 << 20))
+        self._decode_cache: Optional[DecodeSteadyState] = None
+        self._graph_ctx = CudaGraphContext()
+        self._graph_supported = (self.device.type == "cuda" and self.dtype == torch.bfloat16
+                                 and head_dim in (32, 64, 128, 256) and cfg.num_attention_heads // cfg.num_key_value_heads <= 8)
+        if enable_cuda_graph and self._graph_supported:
+            self._graph_ctx.set_enabled(True)
+            self._warmup()
+
+    workspace = property(lambda self: self._workspace)
+
+    @property
+    def cuda_graph_enabled(self) -> bool:
+        return self._graph_ctx.enabled and self._graph_supported
+
+    def _warmup(self):
+        """Run a short prefill and capture one decode graph per power-of-two batch size (and the maximum)."""
+        tc, ws, b_max = self.task_cache, self._workspace, self.kv_cache.max_batch_size
+        sizes = sorted({1 << i for i in range(b_max.bit_length()) if (1 << i) <= b_max} | {b_max})
+        with torch.inference_mode():
+            for b in sizes:
+                ids = [f"_warmup_{b}_{i}" for i in range(b)]
+                if not all(tc.task_alloc(t, [0]) for t in ids):
+                    for t in ids:
+                        tc.task_free(t)
+                    continue
+                for step in range(3):  # live, capture, replay
+                    for t in ids:
+                        tc.task_extend(t, step)
+                    kv = tc.bind(ids, ws)
+                    ws.put_long(ws.position_ids, [step] * b)
+                    tokens = ws.fill_input_ids([0] * b)
+                    self._graph_ctx.forward(self.model, key=(b,), input_ids=tokens, kv_cache=kv,
+                                            position_ids=ws.position_ids[:b], fwd="decode")
+                for t in ids:
+                    tc.task_free(t)
+                torch.cuda.synchronize()
+
+    # -- sampling ---------------------------------------------------------------------------------------------------------
+    def _sample(self, logits: Tensor, tasks: List[Task], return_logprobs: bool, info: Optional[SamplingBatchInfo] = None):
+        info = info or build_sampling_info(tasks, self.device)
+        hist = hist_mask = None
+        if info.has_freq:
+            rows = [t.prompt_ids[-t.rep_window:] + t.output_ids for t in tasks]
+            width = max((len(r) for r in rows), default=0)
+            hist = torch.zeros(len(tasks), width, dtype=torch.long)
+            hist_mask = torch.zeros(len(tasks), width, dtype=torch.bool)
+            for i, r in enumerate(rows):
+                hist[i, : len(r)] = torch.tensor(r, dtype=torch.long)
+                hist_mask[i, : len(r)] = True
+            hist, hist_mask = hist.to(self.device), hist_mask.to(self.device)
+        out = sample(logits, temperature=info.temperatures, top_k=info.top_ks, top_p=info.top_ps,
+                     frequency_penalty=info.freq_penalties, input_ids=hist, input_mask=hist_mask,
+                     return_logprobs=return_logprobs, hints=info.hints)
+        if not return_logprobs:
+            return out.tolist()
+        tokens, logp = out
+        tokens, logp = tokens.tolist(), logp.tolist()
+        for t, lp in zip(tasks, logp):
+            t.output_logprobs.append(float(lp))
+        return list(zip(tokens, logp))
+
+    # -- prefill ------------------------------------------------------------------------------------------------------------
+    def execute_prefill(self, tasks: List[Task], prompt_len: Optional[int] = None, start_pos: Optional[int] = None,
+                        return_logprobs: bool = False):
+        """Packed prefill of ``tasks`` (any mix of lengths).  Each request recomputes positions ``[start, len)`` where
+        ``start = min(cached prefix, len - 1)`` unless ``start_pos`` forces one value for all."""
+        tasks = sorted(tasks, key=lambda t: t.task_id)
+        ids = [t.task_id for t in tasks]
+        lens = [len(t.prompt_ids) for t in tasks]
+        if start_pos is not None:
+            starts = [start_pos] * len(tasks)
+        else:
+            starts = [min(self.task_cache.task_cached(t.task_id), n - 1) for t, n in zip(tasks, lens)]
+        if any(s >= n for s, n in zip(starts, lens)):
+            return [], []
+        flat_ids = [tok for t, s in zip(tasks, starts) for tok in t.prompt_ids[s:]]
+        flat_pos = [p for s, n in zip(starts, lens) for p in range(s, n)]
+        pin = self.device.type == "cuda"
+        input_ids = torch.tensor(flat_ids, dtype=torch.long, pin_memory=pin).to(self.device, non_blocking=True)
+        position_ids = torch.tensor(flat_pos, dtype=torch.long, pin_memory=pin).to(self.device, non_blocking=True)
+        last, acc = [], 0
+        for s, n in zip(starts, lens):
+            acc += n - s
+            last.append(acc - 1)
+        with torch.inference_mode(), timed(f"execute_prefill b={len(tasks)} tokens={len(flat_ids)}", logger):
+            kv = self.task_cache.bind(ids, self._workspace, start_positions=starts)
+            fused = getattr(self.model, "supports_fused_head", False)
+            out = self.model(input_ids, position_ids=position_ids, kv_cache=kv, fwd="prefill",
+                             **({"return_logits": False} if fused else {}))
+            rows = torch.tensor(last, dtype=torch.long, device=self.device)
+            logits = self.model.lm_head(out["hidden_states"][rows]) if fused else out["logits"][rows]
+        return tasks, self._sample(logits, tasks, return_logprobs)
+
+    # -- decode -------------------------------------------------------------------------------------------------------------
+    def execute_decode(self, tasks: List[Task], return_logprobs: bool = False):
+        if not tasks:
+            return []
+        b, ws = len(tasks), self._workspace
+        tokens = ws.fill_input_ids([t.output_ids[-1] if t.output_ids else t.prompt_ids[-1] for t in tasks])
+        ids = [t.task_id for t in tasks]
+        positions = [t.next_pos for t in tasks]
+        kv = self.task_cache.bind(ids, ws)
+        sig = tuple(ids)
+        steady = self.task_cache.bind_was_steady and self._decode_cache is not None and self._decode_cache.task_sig == sig
+        if steady:
+            info = self._decode_cache.sampling_info
+            ws.position_ids[:b] += 1
+        else:
+            info = build_sampling_info(tasks, self.device)
+            ws.put_long(ws.position_ids, positions)
+        self._decode_cache = DecodeSteadyState(sig, positions, info)
+        with torch.inference_mode(), timed(f"execute_decode forward b={b}", logger):
+            kwargs = dict(input_ids=tokens, kv_cache=kv, position_ids=ws.position_ids[:b], fwd="decode")
+            if self.cuda_graph_enabled:
+                out = self._graph_ctx.forward(self.model, key=(b,), **kwargs)
+            else:
+                out = self.model(**kwargs)
+        return self._sample(out["logits"], tasks, return_logprobs, info=info)

@@ -1,0 +1,226 @@
+"""Continuous-batching scheduler: cleanup -> refill -> prefill new requests -> decode the rest, on a daemon thread.
+
+Loop structure, radix-cache bookkeeping and the synchronous ``run_batch`` path follow
+``astrai/inference/scheduler.py:25-400``.  Differences: the KV pool is paged (16-token pages) with the radix prefix
+index by default; all requests that need prefill in a step run in ONE packed forward regardless of their lengths,
+bounded by ``max_prefill_tokens``; requests that cannot be given cache pages wait instead of failing.
+"""
+
+from __future__ import annotations
+
+import logging
+import threading
+import uuid
+from typing import Any, Dict, List, Optional, Tuple
+
+import torch
+
+from astrai_b200.inference.cache import PagePool, TaskCacheManager
+from astrai_b200.inference.metrics import MetricsCollector
+from astrai_b200.inference.runtime.executor import Executor
+from astrai_b200.inference.task import STOP, Task, TaskManager, TaskStatus
+
+logger = logging.getLogger(__name__)
+
+
+class InferenceScheduler:
+    def __init__(self, model, tokenizer, max_batch_size: int = 16, max_seq_len: Optional[int] = None, device=None,
+                 dtype=None, cache: Optional[PagePool] = None, enable_cuda_graph: bool = True, backend=None,
+                 page_size: int = 16, kv_cache_tokens: Optional[int] = None, paged: bool = True,
+                 max_prefill_tokens: int = 8192):
+        cfg = model.config
+        if max_seq_len is None:
+            max_seq_len = cfg.max_position_embeddings
+        if max_seq_len is None:
+            raise ValueError("max_seq_len must be provided either as argument or in model config (config.max_position_embeddings)")
+        self.max_seq_len = max_seq_len
+        p = next(model.parameters())
+        self.device = torch.device(device) if device is not None else p.device
+        self.dtype = dtype or p.dtype
+        self._cache = cache if cache is not None else PagePool.for_model(
+            cfg, max_batch_size, max_seq_len, self.device, self.dtype, page_size=page_size, n_tokens=kv_cache_tokens, paged=paged)
+        self._metrics = MetricsCollector()
+        self._task_cache = TaskCacheManager(self._cache)
+        self._task_mgr = TaskManager(tokenizer, max_batch_size, max_seq_len, metrics=self._metrics)
+        self._executor = Executor(model, self._cache, self._task_cache, self.device, self.dtype, enable_cuda_graph,
+                                  max_prefill_tokens=max_prefill_tokens)
+        self.max_prefill_tokens = max_prefill_tokens
+        self._backend_name = "tcgen05" if self.device.type == "cuda" else "torch_native"
+        self._stop_event = threading.Event()
+        self._loop_thread: Optional[threading.Thread] = None
+
+    # -- public surface -----------------------------------------------------------------------------------------------------
+    def add_task(self, prompt, **kwargs) -> str:
+        return self._task_mgr.add_task(prompt, **kwargs)
+
+    def remove_task(self, task_id: str):
+        for task in self._task_mgr.remove_task(task_id):
+            self._task_cache.task_free(task.task_id)
+
+    def get_stats(self) -> Dict[str, Any]:
+        return self._task_mgr.get_stats()
+
+    backend_name = property(lambda self: self._backend_name)
+    cuda_graph_enabled = property(lambda self: self._executor.cuda_graph_enabled)
+    metrics = property(lambda self: self._metrics)
+    cache = property(lambda self: self._cache)
+
+    # -- one scheduling step -------------------------------------------------------------------------------------------------
+    def _prefill_batches(self, tasks: List[Task]) -> List[List[Task]]:
+        """Greedy split of the prefill set so that no packed forward exceeds the token budget."""
+        batches, cur, used = [], [], 0
+        for t in tasks:
+            need = len(t.prompt_ids) - min(self._task_cache.task_cached(t.task_id), len(t.prompt_ids) - 1)
+            if cur and used + need > self.max_prefill_tokens:
+                batches.append(cur)
+                cur, used = [], 0
+            cur.append(t)
+            used += need
+        if cur:
+            batches.append(cur)
+        return batches
+
+    def _step(self, tasks: List[Task], return_logprobs: bool = False) -> Tuple[List[Task], List[Task]]:
+        """Advance every task by one token.  Returns (tasks that produced a token, tasks aborted for lack of room)."""
+        produced: List[Task] = []
+        fresh = [t for t in tasks if not t.prefill_done and t.prompt_ids]
+        done_now = set()
+        for group in self._prefill_batches(fresh):
+            for t in group:
+                t.input_tokens = len(t.prompt_ids)
+            starts = {t.task_id: min(self._task_cache.task_cached(t.task_id), len(t.prompt_ids) - 1) for t in group}
+            with self._metrics.record([t.task_id for t in group], "prefill"):
+                ordered, outs = self._executor.execute_prefill(group, return_logprobs=return_logprobs)
+            for t, o in zip(ordered, outs):
+                t.output_ids.append(o[0] if return_logprobs else o)
+                t.output_tokens += 1
+                t.mark_prefill_done()
+                done_now.add(t.task_id)
+                produced.append(t)
+                # pages fully covered by the prompt become shareable from the first recomputed page on
+                self._task_cache.task_record_hashes(t.task_id, t.prompt_ids, starts[t.task_id] // self._cache.page_size)
+        decode, aborted = [], []
+        for t in tasks:
+            if t.task_id in done_now or not t.prefill_done:
+                continue
+            if self._task_cache.task_extend(t.task_id, t.next_pos):
+                decode.append(t)
+            else:
+                t.status = TaskStatus.ABORTED
+                aborted.append(t)
+        if decode:
+            with self._metrics.record([t.task_id for t in decode], "decode"):
+                outs = self._executor.execute_decode(decode, return_logprobs=return_logprobs)
+            for t, o in zip(decode, outs):
+                t.output_ids.append(o[0] if return_logprobs else o)
+                t.output_tokens += 1
+                t.advance_kv()
+                produced.append(t)
+        return produced, aborted
+
+    def _retire(self, stop_ids):
+        for task in self._task_mgr.remove_finished_tasks(stop_ids):
+            if task.status == TaskStatus.FINISHED:
+                ids = self._task_cache.task_cacheable_ids(task.task_id, task.prompt_ids, task.output_ids)
+                self._task_cache.task_record_hashes(task.task_id, ids)
+            self._task_cache.task_free(task.task_id)
+
+    def _refill(self):
+        room = self._task_mgr.max_batch_size - len(self._task_mgr.get_active_tasks())
+        if room <= 0:
+            return
+        rejected = []
+        for task in self._task_mgr.pull_candidates(room):
+            if self._task_cache.task_alloc(task.task_id, task.prompt_ids):
+                self._task_mgr.activate(task)
+            else:
+                rejected.append(task)
+        if rejected:
+            self._task_mgr.return_to_waiting(rejected)
+
+    def _run_generation_loop(self):
+        tok = self._task_mgr.tokenizer
+        stop_ids = set(tok.stop_ids)
+        try:
+            while not self._stop_event.is_set():
+                self._retire(stop_ids)
+                self._refill()
+                active = self._task_mgr.get_active_tasks()
+                if not active:
+                    if not self._task_mgr.has_work():
+                        self._task_mgr.wait_for_tasks(timeout=1.0)
+                    else:
+                        self._stop_event.wait(0.001)  # waiting requests do not fit yet
+                    continue
+                decoded, aborted = self._step(active)
+                for t in aborted:
+                    self._task_mgr.invoke_callback(t.task_id, STOP)
+                for t in decoded:
+                    text = t.decode_new_token(tok)
+                    if text:
+                        self._task_mgr.invoke_callback(t.task_id, text)
+                    if t.is_finished(stop_ids):
+                        self._task_mgr.invoke_callback(t.task_id, STOP)
+        except Exception as exc:  # noqa: BLE001 - every waiter must be released
+            self._stop_event.set()
+            logger.error("Scheduler loop crashed: %s", exc, exc_info=True)
+            self._abort_and_clear(free_waiting=False)
+
+    def start(self):
+        if self._loop_thread is not None and self._loop_thread.is_alive():
+            return
+        self._stop_event.clear()
+        self._loop_thread = threading.Thread(target=self._run_generation_loop, daemon=True, name="astrai-b200-scheduler")
+        self._loop_thread.start()
+
+    def stop(self):
+        self._stop_event.set()
+        self._task_mgr.wake()
+        if self._loop_thread is not None:
+            self._loop_thread.join(timeout=5.0)
+        self._loop_thread = None
+        self._abort_and_clear(free_waiting=True)
+
+    def _abort_and_clear(self, free_waiting: bool):
+        for t in self._task_mgr.get_active_tasks():
+            self._task_mgr.invoke_callback(t.task_id, STOP)
+            self._task_cache.task_free(t.task_id)
+        for t in self._task_mgr.get_waiting_tasks():
+            self._task_mgr.invoke_callback(t.task_id, STOP)
+            if free_waiting:
+                self._task_cache.task_free(t.task_id)
+        self._task_mgr.clear_queues()
+
+    # -- synchronous path (RL rollout) -------------------------------------------------------------------------------------------
+    def run_batch(self, prompt_ids_list: List[List[int]], *, max_tokens: Optional[int] = None, temperature: float = 1.0,
+                  top_p: float = 1.0, top_k: int = 50, frequency_penalty: float = 0.0, rep_window: int = 64,
+                  return_logprobs: bool = False):
+        """Generate for already tokenised prompts on the calling thread; prompts that do not fit yield empty results."""
+        stop_ids = set(self._task_mgr.tokenizer.stop_ids)
+        tasks: List[Optional[Task]] = []
+        for ids in prompt_ids_list:
+            room = self.max_seq_len - len(ids)
+            budget = room if max_tokens is None else min(max_tokens, room)
+            if len(ids) >= self.max_seq_len or budget <= 0:
+                tasks.append(None)
+                continue
+            task = Task(f"batch_{uuid.uuid4().hex[:8]}", list(ids), budget, temperature, top_p, top_k, frequency_penalty, rep_window)
+            if not self._task_cache.task_alloc(task.task_id, task.prompt_ids):
+                tasks.append(None)
+                continue
+            task.input_tokens = len(task.prompt_ids)
+            self._metrics.register(task.task_id)
+            tasks.append(task)
+        try:
+            live = [t for t in tasks if t is not None]
+            while live:
+                decoded, _ = self._step(live, return_logprobs=return_logprobs)
+                live = [t for t in decoded if not t.is_finished(stop_ids)]
+        finally:
+            for t in tasks:
+                if t is not None:
+                    self._metrics.mark_finished(t.task_id, t.input_tokens, t.output_tokens)
+                    self._task_cache.task_free(t.task_id)
+        if return_logprobs:
+            return [([], []) if t is None else (list(t.output_ids), list(t.output_logprobs)) for t in tasks]
+        return [[] if t is None else list(t.output_ids) for t in tasks]

@@ -228,6 +228,53 @@ Tensor gemm(const Tensor& A, const Tensor& B, const c10::optional<Tensor>& D_in,
   return D;
 }
 
+// k_new/v_new [T, Hkv, D] contiguous bf16; k_buf/v_buf [n_slots, Hkv, D]; loc int32 [T]
+void kv_append_(const Tensor& k_new, const Tensor& v_new, Tensor& k_buf, Tensor& v_buf, const Tensor& loc) {
+  CHECK_CUDA_CONTIG(k_new);
+  CHECK_CUDA_CONTIG(v_new);
+  CHECK_CUDA_CONTIG(k_buf);
+  CHECK_CUDA_CONTIG(v_buf);
+  CHECK_CUDA_CONTIG(loc);
+  TORCH_CHECK(k_new.scalar_type() == at::kBFloat16 && k_buf.scalar_type() == at::kBFloat16, "kv_append_: bf16 only");
+  TORCH_CHECK(loc.scalar_type() == at::kInt && loc.numel() == k_new.size(0), "kv_append_: loc must be int32 [tokens]");
+  const int row = (int)(k_buf.size(1) * k_buf.size(2));
+  TORCH_CHECK(row % 8 == 0 && k_new.numel() == k_new.size(0) * row && v_new.numel() == k_new.numel(), "kv_append_: row mismatch");
+  const c10::cuda::CUDAGuard guard(k_buf.device());
+  count();
+  ab::kv_append(k_new.data_ptr(), v_new.data_ptr(), k_buf.data_ptr(), v_buf.data_ptr(), loc.data_ptr<int>(), k_new.size(0),
+                row, k_buf.size(0), stream());
+}
+
+int64_t paged_decode_splits(int64_t batch, int64_t n_kv_heads, int64_t max_len, int64_t max_splits) {
+  return ab::paged_decode_splits((int)batch, (int)n_kv_heads, max_len, (int)max_splits);
+}
+
+// q [B, Hq, D]; scratch: o_part [>=B, Hq, max_splits, D] f32, ml_part [>=B, Hq, max_splits, 2] f32, counters int32 [>=B*Hkv] (zero)
+void paged_decode_(const Tensor& q, const Tensor& k_buf, const Tensor& v_buf, const Tensor& req_to_token,
+                   const Tensor& req_pool_indices, const Tensor& seq_lens, double scale, int64_t splits, Tensor& o_part,
+                   Tensor& ml_part, Tensor& counters, Tensor& out) {
+  CHECK_CUDA_CONTIG(q);
+  CHECK_CUDA_CONTIG(k_buf);
+  CHECK_CUDA_CONTIG(v_buf);
+  CHECK_CUDA_CONTIG(req_to_token);
+  CHECK_CUDA_CONTIG(out);
+  TORCH_CHECK(q.scalar_type() == at::kBFloat16 && k_buf.scalar_type() == at::kBFloat16 && out.scalar_type() == at::kBFloat16, "paged_decode_: bf16 only");
+  TORCH_CHECK(req_to_token.scalar_type() == at::kInt && req_pool_indices.scalar_type() == at::kInt && seq_lens.scalar_type() == at::kLong,
+              "paged_decode_: req_to_token/req_pool_indices int32, seq_lens int64");
+  const int B = (int)q.size(0), Hq = (int)q.size(1), D = (int)q.size(2), Hkv = (int)k_buf.size(1);
+  const int max_splits = (int)o_part.size(2);
+  TORCH_CHECK(o_part.scalar_type() == at::kFloat && o_part.size(0) >= B && o_part.size(1) == Hq && o_part.size(3) == D, "paged_decode_: bad o_part scratch");
+  TORCH_CHECK(ml_part.scalar_type() == at::kFloat && ml_part.size(0) >= B && ml_part.size(2) == max_splits, "paged_decode_: bad ml_part scratch");
+  TORCH_CHECK(counters.scalar_type() == at::kInt && counters.numel() >= (int64_t)B * Hkv, "paged_decode_: bad counters scratch");
+  const c10::cuda::CUDAGuard guard(q.device());
+  count();
+  const int rc = ab::paged_decode(q.data_ptr(), k_buf.data_ptr(), v_buf.data_ptr(), req_to_token.data_ptr<int>(),
+                                  req_pool_indices.data_ptr<int>(), (const long long*)seq_lens.data_ptr<int64_t>(),
+                                  o_part.data_ptr<float>(), ml_part.data_ptr<float>(), counters.data_ptr<int>(), out.data_ptr(),
+                                  B, Hq, Hkv, D, (int)req_to_token.size(1), k_buf.size(0), (float)scale, (int)splits, max_splits, stream());
+  TORCH_CHECK(rc == 0, "paged_decode launch failed with code ", rc, " (-1: GQA group > 8, -2: splits, -3: head_dim not in {32,64,128,256})");
+}
+
 }  // namespace
 
 TORCH_LIBRARY(astrai_b200, m) {
@@ -246,5 +293,8 @@ TORCH_LIBRARY(astrai_b200, m) {
   m.def("axpy_f32_(Tensor(a!) dst, Tensor src, float alpha) -> ()", &axpy_f32_);
   m.def("kernel_status(Tensor like) -> Tensor", &kernel_status);
   m.def("launch_count() -> int", &launch_count);
+  m.def("kv_append_(Tensor k_new, Tensor v_new, Tensor(a!) k_buf, Tensor(b!) v_buf, Tensor loc) -> ()", &kv_append_);
+  m.def("paged_decode_splits(int batch, int n_kv_heads, int max_len, int max_splits) -> int", &paged_decode_splits);
+  m.def("paged_decode_(Tensor q, Tensor k_buf, Tensor v_buf, Tensor req_to_token, Tensor req_pool_indices, Tensor seq_lens, float scale, int splits, Tensor(a!) o_part, Tensor(b!) ml_part, Tensor(c!) counters, Tensor(d!) out) -> ()", &paged_decode_);
   m.def("gemm(Tensor A, Tensor B, Tensor? D, bool a_kmajor, bool b_kmajor, bool out_f32, bool accumulate) -> Tensor", &gemm);
 }

@@ -33,6 +33,15 @@ void adamw_step(void* p, float* master, float* g, float* m, float* v, long long 
                 float eps, float wd, int step, const float* gscale, bool zero_grad, bool p_bf16, cudaStream_t st);
 void axpy_f32(float* dst, const void* src, long long n, float alpha, bool src_bf16, cudaStream_t st);
 
+// Inference attention over a slot-addressed KV pool (paged_attention.cu).
+void kv_append(const void* k_new, const void* v_new, void* k_buf, void* v_buf, const int* loc, long long tokens,
+               int row_elems, long long n_slots, cudaStream_t st);
+int paged_decode_splits(int batch, int n_kv_heads, long long max_len, int max_splits);
+int paged_decode(const void* q, const void* k_buf, const void* v_buf, const int* req_to_token,
+                 const int* req_pool_indices, const long long* seq_lens, float* o_part, float* ml_part, int* counters,
+                 void* out, int batch, int n_q_heads, int n_kv_heads, int head_dim, int max_ctx, long long n_slots,
+                 float scale, int splits, int max_splits, cudaStream_t st);
+
 // tcgen05 GEMM: D[M,N] (+)= A * B with bf16 operands and fp32 accumulation in tensor memory.
 //   a_kmajor: A is [M,K] row-major (true) or stored as [K,M] row-major (false)
 //   b_kmajor: B is [N,K] row-major (true) or stored as [K,N] row-major (false)

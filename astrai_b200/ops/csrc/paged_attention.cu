@@ -1,0 +1,237 @@
+// Inference attention kernels over a slot-addressed (paged) KV pool.
+//
+//   kv_append     : scatter this step's K/V rows into the pool (slot = out_cache_loc[token]).
+//   paged_decode  : flash-decoding.  One CTA per (kv head, request, KV split); the G query heads that share a kv
+//                   head are processed together so every K/V byte is read once per split (GQA head packing).
+//                   Partials (un-normalised O, running max, sum) go to a caller-provided scratch; the LAST CTA to
+//                   finish a (request, kv head) merges its splits and writes bf16 output - no second launch.
+// Replaces the reference's decode_split_kv_mma + decode_combine pair (csrc/kernels/attention/decode_split_kv_mma.cuh:20-183,
+// decode_split_kv.cuh:115-144).  Decode is HBM-bound (~4 FLOP per KV byte), so the math stays on the CUDA cores and
+// the kernel is shaped for bytes in flight: 16-byte loads, several tokens per warp iteration, unrolled.
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "common.cuh"
+#include "launchers.h"
+
+namespace ab {
+
+__global__ void kv_append_kernel(const __nv_bfloat16* __restrict__ k_new, const __nv_bfloat16* __restrict__ v_new,
+                                 __nv_bfloat16* __restrict__ k_buf, __nv_bfloat16* __restrict__ v_buf,
+                                 const int* __restrict__ loc, long long tokens, int row_elems, long long n_slots) {
+  const int vec = row_elems >> 3;
+  const long long total = tokens * vec;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total;
+       i += (long long)gridDim.x * blockDim.x) {
+    const long long t = i / vec;
+    const int c = (int)(i % vec) * 8;
+    const long long slot = loc[t];
+    if (slot < 0 || slot >= n_slots) continue;  // never write outside the pool
+    *reinterpret_cast<uint4*>(k_buf + slot * row_elems + c) = *reinterpret_cast<const uint4*>(k_new + t * row_elems + c);
+    *reinterpret_cast<uint4*>(v_buf + slot * row_elems + c) = *reinterpret_cast<const uint4*>(v_new + t * row_elems + c);
+  }
+}
+
+void kv_append(const void* k_new, const void* v_new, void* k_buf, void* v_buf, const int* loc, long long tokens,
+               int row_elems, long long n_slots, cudaStream_t st) {
+  if (tokens == 0) return;
+  const long long total = tokens * (row_elems / 8);
+  const int grid = (int)((total + 255) / 256 < 148 * 8 ? (total + 255) / 256 : 148 * 8);
+  kv_append_kernel<<<grid, 256, 0, st>>>((const __nv_bfloat16*)k_new, (const __nv_bfloat16*)v_new, (__nv_bfloat16*)k_buf,
+                                         (__nv_bfloat16*)v_buf, loc, tokens, row_elems, n_slots);
+}
+
+constexpr int DEC_WARPS = 4;
+constexpr int MAXG = 8;
+
+__device__ __forceinline__ void load8(const __nv_bfloat16* p, float (&f)[8]) {
+  const uint4 raw = *reinterpret_cast<const uint4*>(p);
+  const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const float2 t = __bfloat1622float2(h[i]);
+    f[2 * i] = t.x;
+    f[2 * i + 1] = t.y;
+  }
+}
+
+// D = head dim (32/64/128/256).  LPT lanes cooperate on one token (8 dims each); a warp handles 32/LPT tokens at once.
+template <int D>
+__global__ void __launch_bounds__(DEC_WARPS * 32)
+paged_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ k_buf,
+                    const __nv_bfloat16* __restrict__ v_buf, const int* __restrict__ req_to_token,
+                    const int* __restrict__ req_pool_indices, const long long* __restrict__ seq_lens,
+                    float* __restrict__ o_part, float* __restrict__ ml_part, int* __restrict__ counters,
+                    __nv_bfloat16* __restrict__ out, int n_q_heads, int n_kv_heads, int max_ctx, long long n_slots,
+                    float scale, int max_splits) {
+  constexpr int LPT = D / 8;
+  constexpr int TPW = 32 / LPT;  // tokens per warp iteration
+  const int kvh = blockIdx.x, b = blockIdx.y, split = blockIdx.z, splits = gridDim.z;
+  const int G = n_q_heads / n_kv_heads;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int sub = lane / LPT, dl = lane % LPT;  // token sub-group inside the warp, dim chunk of this lane
+  const long long len = seq_lens[b];
+  const int* table = req_to_token + (long long)req_pool_indices[b] * max_ctx;
+  const long long chunk = ((len + splits - 1) / splits + 15) / 16 * 16;
+  const long long t_begin = (long long)split * chunk;
+  const long long t_end = t_begin + chunk < len ? t_begin + chunk : len;
+
+  float qf[MAXG][8], acc[MAXG][8], m[MAXG], l[MAXG];
+#pragma unroll
+  for (int g = 0; g < MAXG; ++g) {
+    m[g] = -INFINITY;
+    l[g] = 0.f;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) acc[g][j] = 0.f, qf[g][j] = 0.f;
+    if (g < G) {
+      load8(q + ((long long)b * n_q_heads + kvh * G + g) * D + dl * 8, qf[g]);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) qf[g][j] *= scale;
+    }
+  }
+
+  const long long row = (long long)n_kv_heads * D;
+  for (long long t0 = t_begin + (long long)warp * TPW; t0 < t_end; t0 += (long long)DEC_WARPS * TPW) {
+    const long long t = t0 + sub;
+    const bool valid = t < t_end;
+    long long slot = valid ? (long long)table[t] : 0;
+    if (slot < 0 || slot >= n_slots) slot = 0;  // a corrupt table entry must not fault; its score is masked below
+    const bool live = valid && table[valid ? t : t_begin] >= 0;
+    float kf[8], vf[8];
+    load8(k_buf + slot * row + (long long)kvh * D + dl * 8, kf);
+    load8(v_buf + slot * row + (long long)kvh * D + dl * 8, vf);
+#pragma unroll
+    for (int g = 0; g < MAXG; ++g) {
+      if (g < G) {
+        float s = 0.f;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) s += qf[g][j] * kf[j];
+#pragma unroll
+        for (int o = LPT / 2; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+        if (!live) s = -INFINITY;
+        const float nm = fmaxf(m[g], s);
+        const float alpha = (nm == -INFINITY) ? 1.f : __expf(m[g] - nm);
+        const float p = (nm == -INFINITY) ? 0.f : __expf(s - nm);
+        l[g] = l[g] * alpha + p;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) acc[g][j] = acc[g][j] * alpha + p * vf[j];
+        m[g] = nm;
+      }
+    }
+  }
+
+  // merge the TPW token sub-groups of the warp (same dims live LPT lanes apart)
+#pragma unroll
+  for (int g = 0; g < MAXG; ++g) {
+    if (g < G) {
+#pragma unroll
+      for (int o = LPT; o < 32; o <<= 1) {
+        const float om = __shfl_xor_sync(0xffffffffu, m[g], o);
+        const float ol = __shfl_xor_sync(0xffffffffu, l[g], o);
+        const float nm = fmaxf(m[g], om);
+        const float a = (nm == -INFINITY) ? 1.f : __expf(m[g] - nm);
+        const float bsc = (nm == -INFINITY) ? 1.f : __expf(om - nm);
+        l[g] = l[g] * a + ol * bsc;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          const float oa = __shfl_xor_sync(0xffffffffu, acc[g][j], o);
+          acc[g][j] = acc[g][j] * a + oa * bsc;
+        }
+        m[g] = nm;
+      }
+    }
+  }
+
+  // merge the warps through shared memory
+  __shared__ float s_acc[DEC_WARPS][MAXG][D];
+  __shared__ float s_ml[DEC_WARPS][MAXG][2];
+  __shared__ int s_last;
+  if (sub == 0) {
+    for (int g = 0; g < G; ++g) {
+#pragma unroll
+      for (int j = 0; j < 8; ++j) s_acc[warp][g][dl * 8 + j] = acc[g][j];
+      if (dl == 0) s_ml[warp][g][0] = m[g], s_ml[warp][g][1] = l[g];
+    }
+  }
+  __syncthreads();
+  for (int idx = threadIdx.x; idx < G * D; idx += blockDim.x) {
+    const int g = idx / D, d = idx % D;
+    float mm = -INFINITY;
+#pragma unroll
+    for (int w = 0; w < DEC_WARPS; ++w) mm = fmaxf(mm, s_ml[w][g][0]);
+    float o = 0.f, ll = 0.f;
+#pragma unroll
+    for (int w = 0; w < DEC_WARPS; ++w) {
+      const float sc = (mm == -INFINITY) ? 0.f : __expf(s_ml[w][g][0] - mm);
+      o += s_acc[w][g][d] * sc;
+      ll += s_ml[w][g][1] * sc;
+    }
+    const long long head = (long long)b * n_q_heads + kvh * G + g;
+    o_part[(head * max_splits + split) * D + d] = o;
+    if (d == 0) {
+      ml_part[(head * max_splits + split) * 2] = mm;
+      ml_part[(head * max_splits + split) * 2 + 1] = ll;
+    }
+  }
+
+  // the last CTA of this (request, kv head) combines the splits
+  __threadfence();
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    const int done = atomicAdd(&counters[b * n_kv_heads + kvh], 1);
+    s_last = (done == splits - 1);
+    if (s_last) counters[b * n_kv_heads + kvh] = 0;  // ready for the next launch (graph replay included)
+  }
+  __syncthreads();
+  if (!s_last) return;
+  __threadfence();
+  for (int idx = threadIdx.x; idx < G * D; idx += blockDim.x) {
+    const int g = idx / D, d = idx % D;
+    const long long head = (long long)b * n_q_heads + kvh * G + g;
+    float mm = -INFINITY;
+    for (int s = 0; s < splits; ++s) mm = fmaxf(mm, ml_part[(head * max_splits + s) * 2]);
+    float o = 0.f, ll = 0.f;
+    for (int s = 0; s < splits; ++s) {
+      const float sc = (mm == -INFINITY) ? 0.f : __expf(ml_part[(head * max_splits + s) * 2] - mm);
+      o += o_part[(head * max_splits + s) * D + d] * sc;
+      ll += ml_part[(head * max_splits + s) * 2 + 1] * sc;
+    }
+    out[head * D + d] = __float2bfloat16_rn(ll > 0.f ? o / ll : 0.f);
+  }
+}
+
+int paged_decode_splits(int batch, int n_kv_heads, long long max_len, int max_splits) {
+  const long long base = (long long)batch * n_kv_heads;
+  long long s = (148 * 4 + base - 1) / base;     // aim for about four CTAs per SM
+  const long long by_len = (max_len + 127) / 128;  // at least 128 tokens per split
+  if (s > by_len) s = by_len;
+  if (s > max_splits) s = max_splits;
+  return (int)(s < 1 ? 1 : s);
+}
+
+int paged_decode(const void* q, const void* k_buf, const void* v_buf, const int* req_to_token,
+                 const int* req_pool_indices, const long long* seq_lens, float* o_part, float* ml_part, int* counters,
+                 void* out, int batch, int n_q_heads, int n_kv_heads, int head_dim, int max_ctx, long long n_slots,
+                 float scale, int splits, int max_splits, cudaStream_t st) {
+  if (batch == 0) return 0;
+  if (n_q_heads % n_kv_heads || n_q_heads / n_kv_heads > MAXG) return -1;
+  if (splits < 1 || splits > max_splits) return -2;
+  const dim3 grid(n_kv_heads, batch, splits), block(DEC_WARPS * 32);
+#define AB_DEC(DD)                                                                                                   \
+  paged_decode_kernel<DD><<<grid, block, 0, st>>>((const __nv_bfloat16*)q, (const __nv_bfloat16*)k_buf,              \
+                                                  (const __nv_bfloat16*)v_buf, req_to_token, req_pool_indices,       \
+                                                  seq_lens, o_part, ml_part, counters, (__nv_bfloat16*)out,          \
+                                                  n_q_heads, n_kv_heads, max_ctx, n_slots, scale, max_splits)
+  switch (head_dim) {
+    case 32: AB_DEC(32); break;
+    case 64: AB_DEC(64); break;
+    case 128: AB_DEC(128); break;
+    case 256: AB_DEC(256); break;
+    default: return -3;
+  }
+#undef AB_DEC
+  return cudaGetLastError() == cudaSuccess ? 0 : -5;
+}
+
+}  // namespace ab
