@@ -36,7 +36,13 @@ inline bool make_map(CUtensorMap* out, const void* ptr, long long inner, long lo
   }
   // The driver entry point needs a current context; a fresh thread (autograd worker) has none until its first
   // runtime call, so make one here (only on a cache miss).
-  cudaFree(nullptr);
+  // Once per thread is enough, and it must not run while the stream is being captured into a CUDA graph
+  // (the warm-up pass before a capture has already bound the context).
+  static thread_local bool context_bound = false;
+  if (!context_bound) {
+    cudaFree(nullptr);
+    context_bound = true;
+  }
   cuuint64_t dims[2] = {(cuuint64_t)inner, (cuuint64_t)outer};
   cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
   cuuint32_t box[2] = {(cuuint32_t)box_inner, (cuuint32_t)box_outer};

@@ -1,4 +1,12 @@
 from astrai_b200.optim.base import CompositeOptimizer, OptimizerFactory
 from astrai_b200.optim.fused_adamw import FusedAdamW
+from astrai_b200.optim.matrix import (
+    Mano, ManoAdamW, Muon, MuonAdamW, NAdamW, Nora, NoraNAdamW, OptimizerParameterGroups, newton_schulz, nora_direction,
+    nora_lr_scale, partition_optimizer_parameters,
+)
 
-__all__ = ["CompositeOptimizer", "FusedAdamW", "OptimizerFactory"]
+__all__ = [
+    "CompositeOptimizer", "FusedAdamW", "Mano", "ManoAdamW", "Muon", "MuonAdamW", "NAdamW", "Nora", "NoraNAdamW",
+    "OptimizerFactory", "OptimizerParameterGroups", "newton_schulz", "nora_direction", "nora_lr_scale",
+    "partition_optimizer_parameters",
+]
