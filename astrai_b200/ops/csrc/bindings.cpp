@@ -275,6 +275,65 @@ void paged_decode_(const Tensor& q, const Tensor& k_buf, const Tensor& v_buf, co
   TORCH_CHECK(rc == 0, "paged_decode launch failed with code ", rc, " (-1: GQA group > 8, -2: splits, -3: head_dim not in {32,64,128,256})");
 }
 
+// ---- fused FSDP over peer memory.  Pointer lists are raw device addresses of the same symmetric buffer on each rank.
+ab::CommPeers peers_from(const std::vector<int64_t>& ptrs) {
+  TORCH_CHECK(ptrs.size() >= 1 && ptrs.size() <= 8, "peer pointer list must have 1..8 entries");
+  ab::CommPeers p{};
+  for (size_t i = 0; i < ptrs.size(); ++i) p.ptr[i] = reinterpret_cast<void*>(ptrs[i]);
+  return p;
+}
+
+void fsdp_reduce_scatter_(std::vector<int64_t> grad_ptrs, int64_t mc_ptr, std::vector<int64_t> flag_ptrs, int64_t rank,
+                          int64_t shard_off, Tensor& out, Tensor& sumsq, int64_t unit, int64_t max_units, int64_t epoch,
+                          double timeout_s, int64_t max_ctas) {
+  CHECK_CUDA_CONTIG(out);
+  TORCH_CHECK(out.scalar_type() == at::kFloat && sumsq.scalar_type() == at::kFloat, "fsdp_reduce_scatter_: fp32 buffers");
+  TORCH_CHECK(grad_ptrs.size() == flag_ptrs.size(), "fsdp_reduce_scatter_: pointer lists differ in length");
+  const c10::cuda::CUDAGuard guard(out.device());
+  count();
+  const int rc = ab::fsdp_reduce_scatter(peers_from(grad_ptrs), reinterpret_cast<const float*>(mc_ptr), peers_from(flag_ptrs),
+                                         (int)grad_ptrs.size(), (int)rank, shard_off, out.numel(), out.data_ptr<float>(),
+                                         sumsq.data_ptr<float>(), (int)unit, (int)max_units, (int)epoch,
+                                         (unsigned long long)(timeout_s * 1e9), status_tensor(out.device()).data_ptr<int>(),
+                                         (int)max_ctas, stream());
+  TORCH_CHECK(rc == 0, "fsdp_reduce_scatter launch failed with code ", rc);
+}
+
+void fsdp_adamw_allgather_(std::vector<int64_t> param_ptrs, int64_t mc_ptr, std::vector<int64_t> flag_ptrs, int64_t rank,
+                           int64_t shard_off, const c10::optional<Tensor>& master, const Tensor& g, Tensor& m, Tensor& v,
+                           double lr, double b1, double b2, double eps, double wd, int64_t step,
+                           const c10::optional<Tensor>& gscale, int64_t unit, int64_t max_units, int64_t epoch,
+                           Tensor& block_counter, int64_t max_ctas) {
+  CHECK_CUDA_CONTIG(g);
+  TORCH_CHECK(g.scalar_type() == at::kFloat && m.scalar_type() == at::kFloat && v.scalar_type() == at::kFloat,
+              "fsdp_adamw_allgather_: gradient and moments are fp32");
+  TORCH_CHECK(m.numel() == g.numel() && v.numel() == g.numel(), "fsdp_adamw_allgather_: size mismatch");
+  TORCH_CHECK(block_counter.scalar_type() == at::kInt && block_counter.numel() >= 1, "fsdp_adamw_allgather_: counter");
+  const c10::cuda::CUDAGuard guard(g.device());
+  count();
+  const int rc = ab::fsdp_adamw_allgather(peers_from(param_ptrs), reinterpret_cast<void*>(mc_ptr), peers_from(flag_ptrs),
+                                          (int)param_ptrs.size(), (int)rank, shard_off, g.numel(),
+                                          master.has_value() ? master->data_ptr<float>() : nullptr, g.data_ptr<float>(),
+                                          m.data_ptr<float>(), v.data_ptr<float>(), (float)lr, (float)b1, (float)b2,
+                                          (float)eps, (float)wd, (int)step,
+                                          gscale.has_value() ? gscale->data_ptr<float>() : nullptr, (int)unit,
+                                          (int)max_units, (int)epoch, block_counter.data_ptr<int>(), (int)max_ctas, stream());
+  TORCH_CHECK(rc == 0, "fsdp_adamw_allgather launch failed with code ", rc);
+}
+
+void comm_wait_flags_(const Tensor& local_flags, int64_t kind, int64_t world, int64_t skip_rank, int64_t unit,
+                      int64_t max_units, int64_t epoch, double timeout_s) {
+  TORCH_CHECK(local_flags.is_cuda() && local_flags.scalar_type() == at::kInt, "comm_wait_flags_: int32 CUDA flags");
+  const c10::cuda::CUDAGuard guard(local_flags.device());
+  count();
+  const int rc = ab::comm_wait_flags(local_flags.data_ptr<int>(), (int)kind, (int)world, (int)skip_rank, (int)unit,
+                                     (int)max_units, (int)epoch, (unsigned long long)(timeout_s * 1e9),
+                                     status_tensor(local_flags.device()).data_ptr<int>(), stream());
+  TORCH_CHECK(rc == 0, "comm_wait_flags launch failed with code ", rc);
+}
+
+void kernel_status_reset(const Tensor& like) { status_tensor(like.device()).zero_(); }
+
 }  // namespace
 
 TORCH_LIBRARY(astrai_b200, m) {
@@ -296,5 +355,9 @@ TORCH_LIBRARY(astrai_b200, m) {
   m.def("kv_append_(Tensor k_new, Tensor v_new, Tensor(a!) k_buf, Tensor(b!) v_buf, Tensor loc) -> ()", &kv_append_);
   m.def("paged_decode_splits(int batch, int n_kv_heads, int max_len, int max_splits) -> int", &paged_decode_splits);
   m.def("paged_decode_(Tensor q, Tensor k_buf, Tensor v_buf, Tensor req_to_token, Tensor req_pool_indices, Tensor seq_lens, float scale, int splits, Tensor(a!) o_part, Tensor(b!) ml_part, Tensor(c!) counters, Tensor(d!) out) -> ()", &paged_decode_);
+  m.def("fsdp_reduce_scatter_(int[] grad_ptrs, int mc_ptr, int[] flag_ptrs, int rank, int shard_off, Tensor(a!) out, Tensor(b!) sumsq, int unit, int max_units, int epoch, float timeout_s, int max_ctas) -> ()", &fsdp_reduce_scatter_);
+  m.def("fsdp_adamw_allgather_(int[] param_ptrs, int mc_ptr, int[] flag_ptrs, int rank, int shard_off, Tensor? master, Tensor g, Tensor(a!) m, Tensor(b!) v, float lr, float b1, float b2, float eps, float wd, int step, Tensor? gscale, int unit, int max_units, int epoch, Tensor(c!) block_counter, int max_ctas) -> ()", &fsdp_adamw_allgather_);
+  m.def("comm_wait_flags_(Tensor local_flags, int kind, int world, int skip_rank, int unit, int max_units, int epoch, float timeout_s) -> ()", &comm_wait_flags_);
+  m.def("kernel_status_reset(Tensor like) -> ()", &kernel_status_reset);
   m.def("gemm(Tensor A, Tensor B, Tensor? D, bool a_kmajor, bool b_kmajor, bool out_f32, bool accumulate) -> Tensor", &gemm);
 }

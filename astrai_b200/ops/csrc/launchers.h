@@ -55,4 +55,23 @@ int gemm_bf16_2cta(const void* A, const void* B, void* D, int M, int N, int K, l
                    long long ldd, bool a_kmajor, bool b_kmajor, bool out_f32, bool accumulate, int* status,
                    cudaStream_t st);
 
+// ---- communication kernels over peer memory (comm_fsdp.cu, comm.cuh)
+struct CommPeers { void* ptr[8]; };  // the same buffer on every rank of the node, indexed by rank
+
+// Reduce-scatter of one flat gradient unit + squared-norm partial.  `grads.ptr[r]` is the unit's fp32 gradient buffer
+// on rank r; the caller owns elements [shard_off, shard_off+n).  `mc_grads` (may be null) is the NVSwitch multicast
+// address of the same buffer: when given, one multimem.ld_reduce replaces the per-rank loads.  `flags.ptr[r]` is the
+// int32 flag array of rank r ([kind][8][max_units]).  `timeout_ns` bounds the wait for the peers' gradients.
+int fsdp_reduce_scatter(const CommPeers& grads, const float* mc_grads, const CommPeers& flags, int world, int rank,
+                        long long shard_off, long long n, float* out, float* sumsq, int unit, int max_units, int epoch,
+                        unsigned long long timeout_ns, int* status, int max_ctas, cudaStream_t st);
+// AdamW on the owned shard + store of the new bf16 parameters into every rank's parameter buffer + "written" flag.
+int fsdp_adamw_allgather(const CommPeers& params, void* mc_params, const CommPeers& flags, int world, int rank,
+                         long long shard_off, long long n, float* master, const float* g, float* m, float* v, float lr,
+                         float b1, float b2, float eps, float wd, int step, const float* gscale, int unit,
+                         int max_units, int epoch, int* block_counter, int max_ctas, cudaStream_t st);
+// Wait (bounded) until every rank except `skip_rank` has published `epoch` for (kind, unit) in this rank's flag array.
+int comm_wait_flags(const int* local_flags, int kind, int world, int skip_rank, int unit, int max_units, int epoch,
+                    unsigned long long timeout_ns, int* status, cudaStream_t st);
+
 }  // namespace ab

@@ -36,12 +36,15 @@ class FusedAdamW(Optimizer):
         self._engine = None
         self._scale: Optional[torch.Tensor] = None
         self._sharded = False
+        self._fused = None
         self._unit_state: Dict[str, Dict[str, Any]] = {}
         self.zeroed_in_step = False
 
     # -- flat binding (called by the executor before every step) --------------------------------------------------
-    def bind_flat(self, engine, scale: Optional[torch.Tensor], sharded: bool):
-        self._engine, self._scale, self._sharded = engine, scale, sharded
+    def bind_flat(self, engine, scale: Optional[torch.Tensor], sharded: bool, fused=None):
+        """``fused``: a :class:`~astrai_b200.parallel.fused_fsdp.FusedFSDP`; its kernel then applies the update and
+        scatters the new parameters to every rank in the same launch."""
+        self._engine, self._scale, self._sharded, self._fused = engine, scale, sharded, fused
 
     def _unit_buffers(self, unit):
         rank = self._engine.rank if self._sharded else 0
@@ -89,6 +92,9 @@ class FusedAdamW(Optimizer):
                 p_flat, g_flat = self._unit_buffers(unit)
                 st = self._state_for(unit, p_flat)
                 st["step"] += 1
+                if self._fused is not None and self._sharded:
+                    self._fused.adamw_allgather(unit, st, hp, self._scale)
+                    continue
                 ops.adamw_(p_flat, g_flat, st["exp_avg"], st["exp_avg_sq"], step=st["step"], master=st["master"],
                            grad_scale=self._scale, zero_grad=False, **hp)
             for p in loose:

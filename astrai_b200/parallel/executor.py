@@ -257,13 +257,14 @@ class FlatExecutor(BaseExecutor):
         self._pending_units: List[FlatUnit] = []
         self.grad_scale: Optional[torch.Tensor] = None
         self.last_grad_norm: Optional[torch.Tensor] = None
+        self._norm_done = False
 
     # -- set-up -------------------------------------------------------------------------------------------------
     def _prepare_model(self, model: nn.Module) -> nn.Module:
         if not _wants_flat(self.impl, model):
             return self._prepare_torch(model)
         self.engine = FlatParamEngine(model, get_world_size() if self.sharded else 1, get_rank() if self.sharded else 0,
-                                      allocator=self._allocator())
+                                      allocator=self._allocator(model))
         model._flat_engine = self.engine
         model._flat_executor = self
         self._init_comm(model)
@@ -275,7 +276,7 @@ class FlatExecutor(BaseExecutor):
     def _prepare_torch(self, model: nn.Module) -> nn.Module:
         return model
 
-    def _allocator(self):
+    def _allocator(self, model: nn.Module):
         return None
 
     def _init_comm(self, model: nn.Module):
@@ -334,11 +335,20 @@ class FlatExecutor(BaseExecutor):
             return self._clip_torch(model, max_norm)
         from astrai_b200 import ops
 
-        sumsq = self.engine.grad_sumsq(sharded=self.sharded)
+        sumsq = self._grad_sumsq()
         if self.sharded and self.use_distributed:
             dist.all_reduce(sumsq)
+        self._norm_done = True
         self.grad_scale, self.last_grad_norm = ops.clip_coef(sumsq, max_norm, self._averaging_scale())
-        return float(self.last_grad_norm.item())
+        norm = float(self.last_grad_norm.item())
+        self._after_norm_sync()
+        return norm
+
+    def _grad_sumsq(self) -> torch.Tensor:
+        return self.engine.grad_sumsq(sharded=self.sharded)
+
+    def _after_norm_sync(self):
+        pass
 
     def _clip_torch(self, model, max_norm):
         return super().clip_grad_norm(model, max_norm)
@@ -355,17 +365,25 @@ class FlatExecutor(BaseExecutor):
     def _before_optimizer_step(self, optimizer):
         if self.engine is None:
             return
+        self._ensure_step_barrier()
         if getattr(optimizer, "supports_flat", False):
-            optimizer.bind_flat(self.engine, self._effective_scale(), sharded=self.sharded)
+            optimizer.bind_flat(self.engine, self._effective_scale(), sharded=self.sharded, fused=self._fused_runtime())
         else:
             if self.sharded:
                 raise RuntimeError("the sharded flat runtime needs an optimizer with flat support (FusedAdamW)")
             self.engine.materialize_grads(self._effective_scale())
 
+    def _ensure_step_barrier(self):
+        pass
+
+    def _fused_runtime(self):
+        return None
+
     def _after_optimizer_step(self, optimizer):
         if self.engine is None:
             return
         self.grad_scale = None
+        self._norm_done = False
         if not getattr(optimizer, "supports_flat", False):
             self.engine.drop_grads()
         self._after_flat_update()
@@ -470,11 +488,12 @@ class FSDPExecutor(FlatExecutor):
     sharded = True
 
     def __init__(self, grad_accum_steps: int = 1, impl: str = "auto", overlap: bool = True, comm: str = "nccl",
-                 mesh: Optional[Any] = None, mp_policy: Optional[Any] = None, reshard_after_forward: bool = False):
+                 comm_timeout_s: float = 120.0, mesh: Optional[Any] = None, mp_policy: Optional[Any] = None, reshard_after_forward: bool = False):
         super().__init__(grad_accum_steps, impl, overlap)
-        if comm not in ("nccl", "p2p"):
-            raise ValueError("comm must be 'nccl' or 'p2p'")
+        if comm not in ("nccl", "p2p", "nvls"):
+            raise ValueError("comm must be 'nccl', 'p2p' or 'nvls'")
         self.comm = comm
+        self.comm_timeout_s = float(comm_timeout_s)
         self._mesh, self._mp_policy, self._reshard_after_forward = mesh, mp_policy, reshard_after_forward
         self._gather_events: Dict[str, Any] = {}
         self._fused = None
@@ -546,12 +565,14 @@ class FSDPExecutor(FlatExecutor):
         return out if get_rank() == 0 else None
 
     # -- flat path --------------------------------------------------------------------------------------------------
-    def _allocator(self):
-        if self.comm != "p2p" or not self.use_distributed:
+    def _allocator(self, model: nn.Module):
+        if self.comm == "nccl" or not self.use_distributed:
             return None
-        from astrai_b200.parallel.fused_fsdp import SymmetricAllocator
+        from astrai_b200.parallel.fused_fsdp import SymmetricAllocator, arena_bytes_for
+        from astrai_b200.parallel.symm import SymmetricArena
 
-        self._symm = SymmetricAllocator()
+        dev = next(model.parameters()).device
+        self._symm = SymmetricAllocator(SymmetricArena(arena_bytes_for(model, get_world_size()), dev))
         return self._symm.alloc
 
     def _init_comm(self, model):
@@ -563,10 +584,11 @@ class FSDPExecutor(FlatExecutor):
         if self.use_distributed:
             for u in eng.units:  # rank 0's initial weights everywhere
                 dist.broadcast(u.param_buf, src=0)
-            if self.comm == "p2p":
+            if self.comm != "nccl":
                 from astrai_b200.parallel.fused_fsdp import FusedFSDP
 
-                self._fused = FusedFSDP(eng, self._symm)
+                self._fused = FusedFSDP(eng, self._symm, mode=self.comm, timeout_s=self.comm_timeout_s)
+                self._symm.arena.barrier()  # every rank's buffers hold the broadcast weights before anyone proceeds
 
     def _averaging_scale(self) -> float:
         return 1.0 / get_world_size() if self.use_distributed else 1.0
@@ -604,12 +626,34 @@ class FSDPExecutor(FlatExecutor):
                     ev.record(stream)
                     self._gather_events[u.name] = ev
 
+    def _fused_runtime(self):
+        return self._fused
+
+    def _grad_sumsq(self) -> torch.Tensor:
+        if self._fused is not None:
+            return self._fused.take_sumsq()
+        return super()._grad_sumsq()
+
+    def _after_norm_sync(self):
+        if self._fused is not None:
+            self._fused.check()
+
+    def _ensure_step_barrier(self):
+        """The fused kernels write into peers' parameter buffers: every rank must have finished its backward pass and
+        its reads of the peers' gradients first.  The norm all-reduce is that barrier; run it if nobody clipped."""
+        if self._fused is not None and not self._norm_done:
+            self.clip_grad_norm(None, None)
+
     def _before_unit_forward(self, unit: FlatUnit):
+        if self._fused is not None:
+            self._fused.wait_params(unit)
         ev = self._gather_events.pop(unit.name, None)
         if ev is not None:
             torch.cuda.current_stream().wait_event(ev)
 
     def _wait_all_gathers(self):
+        if self._fused is not None:
+            self._fused.wait_all_params()
         for ev in self._gather_events.values():
             torch.cuda.current_stream().wait_event(ev)
         self._gather_events.clear()

@@ -1,0 +1,46 @@
+"""Multi-GPU tests (need >= 2 CUDA devices; each case runs as torchrun child processes on 127.0.0.1).
+
+NVLS is switched off in NCCL for these runs and the fused kernels use plain peer loads / stores.
+"""
+
+import json
+import os
+import subprocess
+import sys
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def _need_gpus(n):
+    if not torch.cuda.is_available() or torch.cuda.device_count() < n:
+        pytest.skip(f"needs {n} GPUs")
+
+
+def _torchrun(nproc, script, extra, port, timeout=420):
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0", MASTER_ADDR="127.0.0.1")
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={nproc}",
+           "--master-addr", "127.0.0.1", "--master-port", str(port), script, *extra]
+    proc = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=timeout, cwd=ROOT)
+    assert proc.returncode == 0, proc.stdout[-3000:] + proc.stderr[-3000:]
+
+
+def test_fused_p2p_fsdp_matches_nccl_fsdp(tmp_path):
+    _need_gpus(2)
+    script = os.path.join(ROOT, "tests", "workers", "fsdp_compare.py")
+    res = {}
+    for i, comm in enumerate(("nccl", "p2p")):
+        out = str(tmp_path / f"{comm}.json")
+        _torchrun(2, script, ["--comm", comm, "--out", out], 29620 + i)
+        res[comm] = json.load(open(out))
+    a, b = res["nccl"], res["p2p"]
+    assert b["status"] == 0
+    for x, y in zip(a["losses"], b["losses"]):
+        assert abs(x - y) < 2e-2, (a, b)
+    for x, y in zip(a["norms"], b["norms"]):
+        assert abs(x - y) / max(abs(x), 1e-6) < 2e-2, (a, b)
+    assert abs(a["checksum"] - b["checksum"]) / a["checksum"] < 1e-3
