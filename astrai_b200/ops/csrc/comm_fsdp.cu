@@ -56,22 +56,38 @@ fsdp_rs_kernel(CommPeers grads, const float* __restrict__ mc_grads, CommPeers fl
 
   float acc = 0.f;
   const long long nvec = n >> 2;
-  for (long long i = (long long)blockIdx.x * THREADS + threadIdx.x; i < nvec; i += (long long)gridDim.x * THREADS) {
-    float4 s;
+  constexpr int U = 4;  // independent 16-byte loads in flight per rank and thread (NVLink latency is ~2 us)
+  const long long stride = (long long)gridDim.x * THREADS;
+  for (long long i0 = (long long)blockIdx.x * THREADS + threadIdx.x; i0 < nvec; i0 += stride * U) {
+    float4 s[U];
     if (MC) {
-      s = mc_ld_reduce_f4(mc_grads + shard_off + 4 * i);
+#pragma unroll
+      for (int u = 0; u < U; ++u)
+        if (i0 + u * stride < nvec) s[u] = mc_ld_reduce_f4(mc_grads + shard_off + 4 * (i0 + u * stride));
     } else {
-      s = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+      for (int u = 0; u < U; ++u) s[u] = make_float4(0.f, 0.f, 0.f, 0.f);
 #pragma unroll
       for (int p = 0; p < MAX_RANKS; ++p) {
         if (p < world) {
-          const float4 v = ld_sys_f4(reinterpret_cast<const float*>(grads.ptr[p]) + shard_off + 4 * i);
-          s.x += v.x, s.y += v.y, s.z += v.z, s.w += v.w;
+          float4 v[U];
+#pragma unroll
+          for (int u = 0; u < U; ++u)
+            if (i0 + u * stride < nvec)
+              v[u] = ld_sys_f4(reinterpret_cast<const float*>(grads.ptr[p]) + shard_off + 4 * (i0 + u * stride));
+#pragma unroll
+          for (int u = 0; u < U; ++u)
+            if (i0 + u * stride < nvec) s[u].x += v[u].x, s[u].y += v[u].y, s[u].z += v[u].z, s[u].w += v[u].w;
         }
       }
     }
-    reinterpret_cast<float4*>(out)[i] = s;
-    acc += s.x * s.x + s.y * s.y + s.z * s.z + s.w * s.w;
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      if (i0 + u * stride < nvec) {
+        reinterpret_cast<float4*>(out)[i0 + u * stride] = s[u];
+        acc += s[u].x * s[u].x + s[u].y * s[u].y + s[u].z * s[u].z + s[u].w * s[u].w;
+      }
+    }
   }
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);

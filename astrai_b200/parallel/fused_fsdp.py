@@ -61,7 +61,7 @@ class FusedFSDP:
     MAX_UNITS = 512
 
     def __init__(self, engine, allocator: SymmetricAllocator, mode: str = "p2p", timeout_s: float = 120.0,
-                 max_ctas: int = 32):
+                 max_ctas: int = 64):
         if mode not in ("p2p", "nvls"):
             raise ValueError("mode must be 'p2p' or 'nvls'")
         self.engine, self.alloc, self.arena = engine, allocator, allocator.arena

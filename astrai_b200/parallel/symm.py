@@ -55,7 +55,12 @@ class _ArenaBase:
     def alloc(self, numel: int, dtype: torch.dtype, zero: bool = True) -> SymmBuffer:
         nbytes = numel * torch.empty((), dtype=dtype).element_size()
         off = self._carve(nbytes)
-        t = self._local_bytes()[off:off + nbytes].view(dtype)
+        # A tensor of its own over the arena's storage (not a view of it): views of one base share a version
+        # counter, and an in-place update of one flat buffer would then invalidate autograd's saved views of another.
+        base = self._local_bytes()
+        item = nbytes // max(numel, 1) if numel else 1
+        t = torch.empty(0, dtype=dtype, device=base.device).set_(
+            base.untyped_storage(), (base.storage_offset() + off) // item, (numel,), (1,))
         if zero:
             t.zero_()
         return SymmBuffer(t, off, [p + off for p in self._base_ptrs()], (self._mc_base() + off) if self._mc_base() else 0)
