@@ -275,6 +275,44 @@ void paged_decode_(const Tensor& q, const Tensor& k_buf, const Tensor& v_buf, co
   TORCH_CHECK(rc == 0, "paged_decode launch failed with code ", rc, " (-1: GQA group > 8, -2: splits, -3: head_dim not in {32,64,128,256})");
 }
 
+// q [Tq, Hq, D], k / v [Tk, Hkv, D] packed along tokens (a dense [B,S,H,D] batch is the same memory).
+std::tuple<Tensor, Tensor> flash_fwd(const Tensor& q, const Tensor& k, const Tensor& v, const c10::optional<Tensor>& cu_q,
+                                     const c10::optional<Tensor>& cu_k, int64_t batch, int64_t sq, int64_t sk,
+                                     int64_t max_q, bool causal, double scale) {
+  auto ok = [](const Tensor& t) {
+    return t.is_cuda() && t.dim() == 3 && t.scalar_type() == at::kBFloat16 && t.stride(2) == 1 && t.stride(1) == t.size(2) &&
+           t.stride(0) % 8 == 0 && (reinterpret_cast<uintptr_t>(t.data_ptr()) & 15) == 0;
+  };
+  TORCH_CHECK(ok(q) && ok(k) && ok(v), "flash_fwd: q/k/v must be bf16 [tokens, heads, D] with adjacent heads, 16-byte aligned");
+  TORCH_CHECK(k.size(0) == v.size(0) && k.size(1) == v.size(1) && q.size(2) == k.size(2) && k.size(2) == v.size(2), "flash_fwd: shape mismatch");
+  const int D = (int)q.size(2);
+  TORCH_CHECK(D == 64 || D == 128, "flash_fwd: head_dim must be 64 or 128");
+  const int* cq = nullptr;
+  const int* ck = nullptr;
+  if (cu_q.has_value()) {
+    TORCH_CHECK(cu_q->is_cuda() && cu_q->scalar_type() == at::kInt && cu_q->numel() == batch + 1, "flash_fwd: cu_q int32 [batch+1]");
+    cq = cu_q->data_ptr<int>();
+  } else {
+    TORCH_CHECK(batch * sq == q.size(0), "flash_fwd: batch * sq must equal the number of query tokens");
+  }
+  if (cu_k.has_value()) {
+    TORCH_CHECK(cu_k->is_cuda() && cu_k->scalar_type() == at::kInt && cu_k->numel() == batch + 1, "flash_fwd: cu_k int32 [batch+1]");
+    ck = cu_k->data_ptr<int>();
+  } else {
+    TORCH_CHECK(batch * sk == k.size(0), "flash_fwd: batch * sk must equal the number of key tokens");
+  }
+  const c10::cuda::CUDAGuard guard(q.device());
+  Tensor out = at::empty({q.size(0), q.size(1), q.size(2)}, q.options());
+  Tensor lse = at::empty({q.size(1), q.size(0)}, q.options().dtype(at::kFloat));
+  count();
+  const int rc = ab::flash_fwd(q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(), lse.data_ptr<float>(), cq, ck,
+                               (int)batch, (int)sq, (int)sk, (int)max_q, q.size(0), k.size(0), (int)q.size(1), (int)k.size(1), D,
+                               q.stride(0), k.stride(0), v.stride(0), out.stride(0), (float)scale, causal,
+                               status_tensor(q.device()).data_ptr<int>(), stream());
+  TORCH_CHECK(rc == 0, "flash_fwd launch failed with code ", rc);
+  return {out, lse};
+}
+
 // ---- fused FSDP over peer memory.  Pointer lists are raw device addresses of the same symmetric buffer on each rank.
 ab::CommPeers peers_from(const std::vector<int64_t>& ptrs) {
   TORCH_CHECK(ptrs.size() >= 1 && ptrs.size() <= 8, "peer pointer list must have 1..8 entries");
@@ -359,5 +397,6 @@ TORCH_LIBRARY(astrai_b200, m) {
   m.def("fsdp_adamw_allgather_(int[] param_ptrs, int mc_ptr, int[] flag_ptrs, int rank, int shard_off, Tensor? master, Tensor g, Tensor(a!) m, Tensor(b!) v, float lr, float b1, float b2, float eps, float wd, int step, Tensor? gscale, int unit, int max_units, int epoch, Tensor(c!) block_counter, int max_ctas) -> ()", &fsdp_adamw_allgather_);
   m.def("comm_wait_flags_(Tensor local_flags, int kind, int world, int skip_rank, int unit, int max_units, int epoch, float timeout_s) -> ()", &comm_wait_flags_);
   m.def("kernel_status_reset(Tensor like) -> ()", &kernel_status_reset);
+  m.def("flash_fwd(Tensor q, Tensor k, Tensor v, Tensor? cu_q, Tensor? cu_k, int batch, int sq, int sk, int max_q, bool causal, float scale) -> (Tensor, Tensor)", &flash_fwd);
   m.def("gemm(Tensor A, Tensor B, Tensor? D, bool a_kmajor, bool b_kmajor, bool out_f32, bool accumulate) -> Tensor", &gemm);
 }

@@ -1,0 +1,353 @@
+// Flash attention forward on tcgen05 (sm_100a): O = softmax(scale * Q K^T + mask) V, fp32 accumulation in TMEM.
+//
+// One CTA per (128-row Q tile, query head, sequence); 6 warps with fixed roles:
+//   warp 0     : TMA producer - Q tile once, then K and V tiles of 128 keys through two 2-stage rings
+//   warp 1     : MMA issuer   - S(j) = Q K(j)^T into one of two TMEM score buffers, O += P(j) V(j) into the TMEM
+//                output accumulator; S(j+1) is issued BEFORE waiting for P(j), so the tensor cores work on the next
+//                scores while the softmax warps are busy with the current ones
+//   warps 2..5 : softmax + epilogue - one thread per query row: tcgen05.ld of the 128 scores of its row (no
+//                shuffles), running max / sum in the exp2 domain, bf16 probabilities written to shared memory in
+//                the 128-byte-swizzled K-major layout the PV MMA reads, O rescaled in TMEM only when the running
+//                max grew by more than 2^8 (the stale max is exact after the final 1/l normalisation)
+// Layouts: tokens are packed along the first dim, q [Tq, Hq, D], k/v [Tk, Hkv, D] (unit stride in D, heads adjacent);
+// sequences are given by cu_seqlens (varlen) or a fixed length (dense).  Causal masking is lower-right aligned
+// (query i of a sequence sees keys <= i + k_len - q_len), which covers training (k_len == q_len) and prefill on top
+// of a cached prefix.  GQA: query head h reads kv head h / (Hq / Hkv).
+// Takes the place of F.scaled_dot_product_attention / flash_attn in the reference's training and prefill paths
+// (astrai/extension/backend/attention.py:453-468, 663-669) and of its mma.sync prefill kernel
+// (csrc/kernels/attention/prefill_split_q_mma.cuh:19-157).
+// Every mbarrier wait is bounded; a wait that runs out raises the CTA's abort flag, records a code in `status`,
+// and all roles fall through to the common exit where TMEM is freed.
+#include <cuda.h>
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "launchers.h"
+#include "tcgen05.cuh"
+#include "tma_host.h"
+
+namespace ab {
+namespace {
+
+using namespace tc;
+using namespace tmah;
+
+constexpr int BQ = 128, BKV = 128, FA_THREADS = 192, KV_STAGES = 2;
+constexpr int BLK_BYTES = 128 * 128;  // one [128 rows x 64 bf16] swizzled block
+enum : int { ERR_FA_PRODUCER = 31, ERR_FA_MMA = 32, ERR_FA_SOFTMAX = 33 };
+
+template <int D>
+struct FwdCfg {
+  static constexpr int NB = D / 64;
+  static constexpr int TILE_BYTES = 128 * D * 2;
+  static constexpr int P_BYTES = 128 * 128 * 2;
+  static constexpr int SMEM = TILE_BYTES * (1 + 2 * KV_STAGES) + P_BYTES + 1024 + 256;
+};
+
+struct SeqInfo {
+  int q_start, q_len, k_start, k_len;
+};
+__device__ __forceinline__ SeqInfo seq_info(const int* cu_q, const int* cu_k, int b, int sq, int sk) {
+  SeqInfo s;
+  s.q_start = cu_q ? cu_q[b] : b * sq;
+  s.q_len = cu_q ? cu_q[b + 1] - cu_q[b] : sq;
+  s.k_start = cu_k ? cu_k[b] : b * sk;
+  s.k_len = cu_k ? cu_k[b + 1] - cu_k[b] : sk;
+  return s;
+}
+
+template <int D>
+__global__ void __launch_bounds__(FA_THREADS, 1)
+flash_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
+                 const __grid_constant__ CUtensorMap map_v, __nv_bfloat16* __restrict__ O, float* __restrict__ lse,
+                 const int* __restrict__ cu_q, const int* __restrict__ cu_k, int sq, int sk, int Hq, int Hkv,
+                 long long o_row_stride, long long total_q, float scale_log2, int causal, int* __restrict__ status) {
+  using C = FwdCfg<D>;
+  const SeqInfo si = seq_info(cu_q, cu_k, blockIdx.z, sq, sk);
+  const int n_q_tiles = (si.q_len + BQ - 1) / BQ;
+  const int qt = n_q_tiles - 1 - (int)blockIdx.x;  // heaviest (last) causal tiles first
+  if (qt < 0) return;
+  const int h = blockIdx.y, kvh = h / (Hq / Hkv);
+  const int q0 = qt * BQ, off = si.k_len - si.q_len;
+  int kv_end = si.k_len;
+  if (causal) kv_end = min(si.k_len, q0 + BQ + off);
+  if (kv_end < 0) kv_end = 0;
+  const int n_kv = (kv_end + BKV - 1) / BKV;
+
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  uint8_t* aligned = smem_raw + (base - smem_u32(smem_raw));
+  const uint32_t q_smem = base;
+  const uint32_t k_smem = base + C::TILE_BYTES;
+  const uint32_t v_smem = k_smem + KV_STAGES * C::TILE_BYTES;
+  const uint32_t p_smem = v_smem + KV_STAGES * C::TILE_BYTES;
+  uint8_t* p_ptr = aligned + (p_smem - base);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(aligned + (p_smem - base) + C::P_BYTES);
+  const uint32_t bar0 = smem_u32(bars);
+  // barriers: 0 q_full | 1,2 k_full | 3,4 k_empty | 5,6 v_full | 7,8 v_empty | 9,10 s_full | 11 p_full | 12 p_empty
+  auto BAR = [&](int i) { return bar0 + 8u * i; };
+  uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(bars + 13);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_holder + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  if (threadIdx.x == 0) {
+    for (int i = 0; i < 13; ++i) mbar_init(BAR(i), i == 11 ? 4 : 1);
+    *abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    fence_async_smem();
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_holder)), "r"(512u)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_holder;
+  const uint32_t tmem_o = tmem_base + 256;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------------ TMA producer
+    if (lane == 0 && n_kv > 0) {
+      mbar_expect_tx(BAR(0), C::TILE_BYTES);
+#pragma unroll
+      for (int kb = 0; kb < C::NB; ++kb) tma_load_2d(q_smem + kb * BLK_BYTES, &map_q, BAR(0), h * D + kb * 64, si.q_start + q0);
+      bool ok = true;
+      for (int j = 0; j < n_kv && ok; ++j) {
+        const int st = j & 1;
+        const uint32_t ph = ((j >> 1) & 1) ^ 1u;
+        if (!mbar_wait(BAR(3 + st), ph, abort_flag)) { ok = false; break; }
+        mbar_expect_tx(BAR(1 + st), C::TILE_BYTES);
+#pragma unroll
+        for (int kb = 0; kb < C::NB; ++kb)
+          tma_load_2d(k_smem + st * C::TILE_BYTES + kb * BLK_BYTES, &map_k, BAR(1 + st), kvh * D + kb * 64, si.k_start + j * BKV);
+        if (!mbar_wait(BAR(7 + st), ph, abort_flag)) { ok = false; break; }
+        mbar_expect_tx(BAR(5 + st), C::TILE_BYTES);
+#pragma unroll
+        for (int kb = 0; kb < C::NB; ++kb)
+          tma_load_2d(v_smem + st * C::TILE_BYTES + kb * BLK_BYTES, &map_v, BAR(5 + st), kvh * D + kb * 64, si.k_start + j * BKV);
+      }
+      if (!ok) {
+        atomicMax(status, ERR_FA_PRODUCER);
+        *abort_flag = 1;
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------------ MMA issuer
+    if (lane == 0 && n_kv > 0) {
+      constexpr uint32_t idesc_s = idesc_bf16(128, 128, false, false);
+      constexpr uint32_t idesc_pv = idesc_bf16(128, D, false, true);
+      bool ok = mbar_wait(BAR(0), 0, abort_flag);
+      auto issue_s = [&](int j) -> bool {
+        const int st = j & 1;
+        if (!mbar_wait(BAR(1 + st), (j >> 1) & 1, abort_flag)) return false;
+        tc_fence_after();
+        const uint32_t d = tmem_base + (uint32_t)(j & 1) * 128;
+#pragma unroll
+        for (int kb = 0; kb < C::NB; ++kb) {
+          const uint64_t da = smem_desc_sw128(q_smem + kb * BLK_BYTES, true, 0);
+          const uint64_t db = smem_desc_sw128(k_smem + st * C::TILE_BYTES + kb * BLK_BYTES, true, 0);
+#pragma unroll
+          for (int k = 0; k < 4; ++k) tc_mma(d, da + 2 * k, db + 2 * k, idesc_s, (kb | k) ? 1u : 0u);
+        }
+        tc_commit(BAR(3 + st));        // K stage free
+        tc_commit(BAR(9 + (j & 1)));   // scores ready
+        return true;
+      };
+      if (ok) ok = issue_s(0);
+      for (int j = 0; j < n_kv && ok; ++j) {
+        if (j + 1 < n_kv && !issue_s(j + 1)) { ok = false; break; }
+        const int st = j & 1;
+        if (!mbar_wait(BAR(11), j & 1, abort_flag) || !mbar_wait(BAR(5 + st), (j >> 1) & 1, abort_flag)) { ok = false; break; }
+        tc_fence_after();
+        const uint64_t dv = smem_desc_sw128(v_smem + st * C::TILE_BYTES, false, BLK_BYTES);
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {
+          const uint64_t dp = smem_desc_sw128(p_smem + (k >> 2) * BLK_BYTES, true, 0) + 2 * (k & 3);
+          tc_mma(tmem_o, dp, dv + (uint64_t)(k * 128), idesc_pv, (j | k) ? 1u : 0u);
+        }
+        tc_commit(BAR(7 + st));  // V stage free
+        tc_commit(BAR(12));      // P consumed, O updated
+      }
+      if (!ok) {
+        atomicMax(status, ERR_FA_MMA);
+        *abort_flag = 1;
+      }
+    }
+  } else {
+    // ------------------------------------------------------------------ softmax + epilogue (one thread per row)
+    const int quarter = warp & 3;
+    const int row = quarter * 32 + lane;
+    const uint32_t t_lane = tmem_base + ((uint32_t)(quarter * 32) << 16);
+    const int q_idx = q0 + row;
+    float m_run = -INFINITY, l_run = 0.f;
+    bool ok = true;
+    for (int j = 0; j < n_kv; ++j) {
+      const int buf = j & 1;
+      ok = __all_sync(0xffffffffu, mbar_wait(BAR(9 + buf), (j >> 1) & 1, abort_flag));
+      if (!ok) break;
+      tc_fence_after();
+      uint32_t s[4][32];
+#pragma unroll
+      for (int c = 0; c < 4; ++c) tc_ld32(t_lane + buf * 128 + c * 32, s[c]);
+      tc_wait_ld();
+      const int k0 = j * BKV;
+      const bool need_mask = (k0 + BKV > si.k_len) || (causal && (k0 + BKV - 1 > q0 + off));
+      if (need_mask) {
+        int limit = si.k_len;
+        if (causal) limit = min(limit, q_idx + off + 1);
+#pragma unroll
+        for (int c = 0; c < 4; ++c)
+#pragma unroll
+          for (int i = 0; i < 32; ++i)
+            if (k0 + c * 32 + i >= limit) s[c][i] = __float_as_uint(-INFINITY);
+      }
+      float mx = -INFINITY;
+#pragma unroll
+      for (int c = 0; c < 4; ++c)
+#pragma unroll
+        for (int i = 0; i < 32; ++i) mx = fmaxf(mx, __uint_as_float(s[c][i]));
+      const float m_new = fmaxf(m_run, mx * scale_log2);
+      const bool grow = __any_sync(0xffffffffu, m_new > m_run + 8.f);
+      float alpha = 1.f, m_use = m_run;
+      if (grow) {
+        m_use = m_new;
+        alpha = (m_run == -INFINITY) ? 0.f : ex2(m_run - m_new);
+      }
+      const float m_safe = (m_use == -INFINITY) ? 0.f : m_use;
+      float rowsum = 0.f;
+      uint32_t pk[64];
+#pragma unroll
+      for (int c = 0; c < 4; ++c)
+#pragma unroll
+        for (int i = 0; i < 32; i += 2) {
+          const float p0 = ex2(fmaf(__uint_as_float(s[c][i]), scale_log2, -m_safe));
+          const float p1 = ex2(fmaf(__uint_as_float(s[c][i + 1]), scale_log2, -m_safe));
+          rowsum += p0 + p1;
+          const __nv_bfloat162 hh = __floats2bfloat162_rn(p0, p1);
+          pk[c * 16 + (i >> 1)] = *reinterpret_cast<const uint32_t*>(&hh);
+        }
+      if (j > 0) {  // PV(j-1) must have read P and updated O before either is touched
+        ok = __all_sync(0xffffffffu, mbar_wait(BAR(12), (j - 1) & 1, abort_flag));
+        if (!ok) break;
+        tc_fence_after();
+        if (grow) {
+#pragma unroll 1
+          for (int c = 0; c < D / 32; ++c) {
+            uint32_t o[32];
+            tc_ld32(t_lane + 256 + c * 32, o);
+            tc_wait_ld();
+#pragma unroll
+            for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
+            tc_st32(t_lane + 256 + c * 32, o);
+          }
+          tc_wait_st();
+        }
+      }
+      l_run = l_run * alpha + rowsum;
+      m_run = m_use;
+      // P row -> shared memory, K-major 128B-swizzled: 16-byte chunk cc of 64-column block kb at (cc ^ (row % 8))
+      uint8_t* prow = p_ptr + (row >> 3) * 1024 + (row & 7) * 128;
+#pragma unroll
+      for (int c = 0; c < 16; ++c) {
+        const int kb = c >> 3, cc = c & 7;
+        *reinterpret_cast<uint4*>(prow + kb * BLK_BYTES + ((cc ^ (row & 7)) << 4)) =
+            make_uint4(pk[4 * c], pk[4 * c + 1], pk[4 * c + 2], pk[4 * c + 3]);
+      }
+      fence_async_smem();
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(BAR(11));
+    }
+    if (ok && n_kv > 0) {
+      ok = __all_sync(0xffffffffu, mbar_wait(BAR(12), (n_kv - 1) & 1, abort_flag));
+      if (ok) tc_fence_after();
+    }
+    if (ok) {
+      const float inv_l = l_run > 0.f ? 1.f / l_run : 0.f;
+      const bool live = q_idx < si.q_len;
+      const long long tok = (long long)si.q_start + q_idx;
+      __nv_bfloat16* orow = O + tok * o_row_stride + (long long)h * D;
+#pragma unroll 1
+      for (int c = 0; c < D / 32; ++c) {
+        uint32_t o[32];
+        if (n_kv > 0) {
+          tc_ld32(t_lane + 256 + c * 32, o);
+          tc_wait_ld();
+        } else {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) o[i] = 0u;
+        }
+        if (live) {
+#pragma unroll
+          for (int v4 = 0; v4 < 4; ++v4) {
+            uint4 pkd;
+            uint32_t* pw = reinterpret_cast<uint32_t*>(&pkd);
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+              const __nv_bfloat162 hh = __floats2bfloat162_rn(__uint_as_float(o[8 * v4 + 2 * q]) * inv_l,
+                                                              __uint_as_float(o[8 * v4 + 2 * q + 1]) * inv_l);
+              pw[q] = *reinterpret_cast<const uint32_t*>(&hh);
+            }
+            reinterpret_cast<uint4*>(orow + c * 32)[v4] = pkd;
+          }
+        }
+      }
+      if (live && lse != nullptr)
+        lse[(long long)h * total_q + tok] = (l_run > 0.f) ? (m_run + log2f(l_run)) * 0.6931471805599453f : -INFINITY;
+    } else {
+      if (lane == 0) {
+        atomicMax(status, ERR_FA_SOFTMAX);
+        *abort_flag = 1;
+      }
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(512u) : "memory");
+  }
+}
+
+template <int D>
+int launch_fwd(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, void* O, float* lse, const int* cu_q,
+               const int* cu_k, int batch, int sq, int sk, int max_q, int Hq, int Hkv, long long o_row_stride,
+               long long total_q, float scale, bool causal, int* status, cudaStream_t st) {
+  auto kern = flash_fwd_kernel<D>;
+  static bool configured = false;
+  if (!configured) {
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, FwdCfg<D>::SMEM) != cudaSuccess) return -4;
+    configured = true;
+  }
+  const dim3 grid((max_q + BQ - 1) / BQ, Hq, batch);
+  kern<<<grid, FA_THREADS, FwdCfg<D>::SMEM, st>>>(mq, mk, mv, (__nv_bfloat16*)O, lse, cu_q, cu_k, sq, sk, Hq, Hkv,
+                                                  o_row_stride, total_q, scale * 1.4426950408889634f, causal ? 1 : 0,
+                                                  status);
+  return cudaGetLastError() == cudaSuccess ? 0 : -5;
+}
+
+}  // namespace
+
+int flash_fwd(const void* q, const void* k, const void* v, void* out, float* lse, const int* cu_q, const int* cu_k,
+              int batch, int sq, int sk, int max_q, long long total_q, long long total_k, int Hq, int Hkv, int D,
+              long long q_row_stride, long long k_row_stride, long long v_row_stride, long long o_row_stride, float scale,
+              bool causal, int* status, cudaStream_t st) {
+  if (batch <= 0 || total_q <= 0) return 0;
+  if (Hkv <= 0 || Hq % Hkv) return -1;
+  if (D != 64 && D != 128) return -3;
+  CUtensorMap mq, mk, mv;
+  if (!cache().get(&mq, q, (long long)Hq * D, total_q, q_row_stride, 64, 128)) return -1000 - g_last_map_error;
+  if (!cache().get(&mk, k, (long long)Hkv * D, total_k, k_row_stride, 64, 128)) return -2000 - g_last_map_error;
+  if (!cache().get(&mv, v, (long long)Hkv * D, total_k, v_row_stride, 64, 128)) return -3000 - g_last_map_error;
+  if (D == 128)
+    return launch_fwd<128>(mq, mk, mv, out, lse, cu_q, cu_k, batch, sq, sk, max_q, Hq, Hkv, o_row_stride, total_q, scale,
+                           causal, status, st);
+  return launch_fwd<64>(mq, mk, mv, out, lse, cu_q, cu_k, batch, sq, sk, max_q, Hq, Hkv, o_row_stride, total_q, scale,
+                        causal, status, st);
+}
+
+}  // namespace ab

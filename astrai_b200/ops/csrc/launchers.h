@@ -55,6 +55,14 @@ int gemm_bf16_2cta(const void* A, const void* B, void* D, int M, int N, int K, l
                    long long ldd, bool a_kmajor, bool b_kmajor, bool out_f32, bool accumulate, int* status,
                    cudaStream_t st);
 
+// Flash attention forward (flash_fwd.cu).  Packed layouts q [total_q, Hq, D], k/v [total_k, Hkv, D] with unit stride
+// in D and adjacent heads; row strides in elements.  cu_q / cu_k: int32 [batch+1] sequence boundaries or null (then
+// every sequence has sq / sk tokens).  lse [Hq, total_q] fp32 (natural log) may be null.  D in {64, 128}.
+int flash_fwd(const void* q, const void* k, const void* v, void* out, float* lse, const int* cu_q, const int* cu_k,
+              int batch, int sq, int sk, int max_q, long long total_q, long long total_k, int Hq, int Hkv, int D,
+              long long q_row_stride, long long k_row_stride, long long v_row_stride, long long o_row_stride, float scale,
+              bool causal, int* status, cudaStream_t st);
+
 // ---- communication kernels over peer memory (comm_fsdp.cu, comm.cuh)
 struct CommPeers { void* ptr[8]; };  // the same buffer on every rank of the node, indexed by rank
 

@@ -1,0 +1,74 @@
+"""tcgen05 flash attention (forward and backward) against a plain fp32 PyTorch statement of the same math."""
+
+import math
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def _ref_attention(q, k, v, causal, scale):
+    """q [Sq,Hq,D], k/v [Sk,Hkv,D] fp32; lower-right aligned causal mask.  Returns (out [Sq,Hq,D], lse [Hq,Sq])."""
+    sq, hq, _ = q.shape
+    sk, hkv, _ = k.shape
+    kk = k.repeat_interleave(hq // hkv, dim=1)
+    vv = v.repeat_interleave(hq // hkv, dim=1)
+    s = torch.einsum("qhd,khd->hqk", q, kk) * scale
+    if causal:
+        i = torch.arange(sq, device=q.device)[:, None]
+        j = torch.arange(sk, device=q.device)[None, :]
+        s = s.masked_fill(~(j <= i + (sk - sq)), float("-inf"))
+    lse = torch.logsumexp(s, dim=-1)
+    p = torch.softmax(s, dim=-1)
+    p = torch.nan_to_num(p, nan=0.0)
+    return torch.einsum("hqk,khd->qhd", p, vv), lse
+
+
+def _native():
+    from astrai_b200.ops import native
+
+    native.require()
+    return torch.ops.astrai_b200
+
+
+@pytest.mark.parametrize("d", [128, 64])
+@pytest.mark.parametrize("causal", [True, False])
+@pytest.mark.parametrize("b,s,hq,hkv", [(2, 256, 4, 2), (1, 384, 2, 2), (3, 200, 4, 1)])
+def test_flash_fwd_dense(d, causal, b, s, hq, hkv):
+    ops = _native()
+    torch.manual_seed(0)
+    q = torch.randn(b * s, hq, d, device="cuda", dtype=torch.bfloat16)
+    k = torch.randn(b * s, hkv, d, device="cuda", dtype=torch.bfloat16)
+    v = torch.randn(b * s, hkv, d, device="cuda", dtype=torch.bfloat16)
+    scale = 1.0 / math.sqrt(d)
+    out, lse = ops.flash_fwd(q, k, v, None, None, b, s, s, s, causal, scale)
+    for i in range(b):
+        sl = slice(i * s, (i + 1) * s)
+        ref, ref_lse = _ref_attention(q[sl].float(), k[sl].float(), v[sl].float(), causal, scale)
+        assert (out[sl].float() - ref).abs().max().item() < 2e-2
+        assert (lse[:, sl] - ref_lse).abs().max().item() < 2e-2
+    from astrai_b200.ops import native
+
+    assert native.kernel_status(q.device) == 0
+
+
+@pytest.mark.parametrize("d", [128, 64])
+def test_flash_fwd_varlen_with_prefix(d):
+    ops = _native()
+    torch.manual_seed(1)
+    hq, hkv = 4, 2
+    q_lens, k_lens = [130, 1, 77, 256], [130, 300, 200, 256]  # k_len >= q_len: queries sit at the end of their keys
+    cu_q = torch.tensor([0] + list(torch.tensor(q_lens).cumsum(0)), dtype=torch.int32, device="cuda")
+    cu_k = torch.tensor([0] + list(torch.tensor(k_lens).cumsum(0)), dtype=torch.int32, device="cuda")
+    q = torch.randn(sum(q_lens), hq, d, device="cuda", dtype=torch.bfloat16)
+    k = torch.randn(sum(k_lens), hkv, d, device="cuda", dtype=torch.bfloat16)
+    v = torch.randn(sum(k_lens), hkv, d, device="cuda", dtype=torch.bfloat16)
+    scale = 1.0 / math.sqrt(d)
+    out, lse = ops.flash_fwd(q, k, v, cu_q, cu_k, len(q_lens), 0, 0, max(q_lens), True, scale)
+    for i in range(len(q_lens)):
+        qs = slice(int(cu_q[i]), int(cu_q[i + 1]))
+        ks = slice(int(cu_k[i]), int(cu_k[i + 1]))
+        ref, ref_lse = _ref_attention(q[qs].float(), k[ks].float(), v[ks].float(), True, scale)
+        assert (out[qs].float() - ref).abs().max().item() < 2e-2, i
+        assert (lse[:, qs] - ref_lse).abs().max().item() < 2e-2, i
