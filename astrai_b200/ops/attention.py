@@ -2,7 +2,8 @@
 
 ``dense_attention`` serves training and the no-cache forward: q ``[B,S,Hq,D]``, k/v ``[B,L,Hkv,D]``, optional
 bool mask (True = attend) or causal flag - the contract of ``astrai/extension/backend/attention.py:256-303``
-for ``fwd=None``.  The packed prefill / paged decode entry points used by the inference engine live in
+for ``fwd=None``.  Unmasked and causal calls run on the tcgen05 flash kernels (:mod:`astrai_b200.ops.flash`);
+an arbitrary boolean mask goes to the library SDPA kernel.  The packed prefill / paged decode entry points used by the inference engine live in
 :mod:`astrai_b200.ops.paged_attention`.
 """
 
@@ -15,9 +16,15 @@ import torch
 import torch.nn.functional as F
 from torch import Tensor
 
-from astrai_b200.ops import reference
+from astrai_b200.ops import flash, reference
 
 _SDPA_BACKENDS = None
+
+
+def _use_flash() -> bool:
+    """The tcgen05 kernels serve every unmasked / causal call; ``ASTRAI_B200_ATTN=sdpa`` selects the library path
+    (kept as the comparison baseline and for arbitrary boolean masks)."""
+    return os.environ.get("ASTRAI_B200_ATTN", "flash") != "sdpa"
 
 
 def _sdpa_ctx():
@@ -40,6 +47,8 @@ def dense_attention(q: Tensor, k: Tensor, v: Tensor, mask: Optional[Tensor] = No
     """Softmax attention with GQA head sharing; returns ``[B,S,Hq,Dv]``."""
     if not q.is_cuda:
         return reference.attention(q, k, v, mask, causal, scale)
+    if mask is None and _use_flash() and flash.supported(q, k, v):
+        return flash.flash_attention(q, k, v, causal=causal, scale=scale)
     hq, hkv = q.shape[2], k.shape[2]
     qt, kt, vt = q.transpose(1, 2), k.transpose(1, 2), v.transpose(1, 2)
     with _sdpa_ctx():

@@ -313,6 +313,35 @@ std::tuple<Tensor, Tensor> flash_fwd(const Tensor& q, const Tensor& k, const Ten
   return {out, lse};
 }
 
+std::tuple<Tensor, Tensor, Tensor> flash_bwd(const Tensor& q, const Tensor& k, const Tensor& v, const Tensor& out,
+                                             const Tensor& dout, const Tensor& lse, const c10::optional<Tensor>& cu_q,
+                                             const c10::optional<Tensor>& cu_k, int64_t batch, int64_t sq, int64_t sk,
+                                             int64_t max_q, int64_t max_k, bool causal, double scale) {
+  auto ok = [](const Tensor& t) {
+    return t.is_cuda() && t.dim() == 3 && t.scalar_type() == at::kBFloat16 && t.stride(2) == 1 && t.stride(1) == t.size(2) &&
+           t.stride(0) % 8 == 0 && (reinterpret_cast<uintptr_t>(t.data_ptr()) & 15) == 0;
+  };
+  TORCH_CHECK(ok(q) && ok(k) && ok(v) && ok(out) && ok(dout), "flash_bwd: tensors must be bf16 [tokens, heads, D] with adjacent heads");
+  TORCH_CHECK(lse.is_cuda() && lse.is_contiguous() && lse.scalar_type() == at::kFloat && lse.numel() == q.size(0) * q.size(1), "flash_bwd: lse [Hq, tokens] fp32");
+  const int D = (int)q.size(2);
+  TORCH_CHECK(D == 64 || D == 128, "flash_bwd: head_dim must be 64 or 128");
+  const int* cq = cu_q.has_value() ? cu_q->data_ptr<int>() : nullptr;
+  const int* ck = cu_k.has_value() ? cu_k->data_ptr<int>() : nullptr;
+  const c10::cuda::CUDAGuard guard(q.device());
+  Tensor dq = at::empty({q.size(0), q.size(1), q.size(2)}, q.options());
+  Tensor dk = at::empty({k.size(0), k.size(1), k.size(2)}, k.options());
+  Tensor dv = at::empty({k.size(0), k.size(1), k.size(2)}, k.options());
+  Tensor delta = at::empty({q.size(1), q.size(0)}, q.options().dtype(at::kFloat));
+  count(3);
+  const int rc = ab::flash_bwd(q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(), dout.data_ptr(), lse.data_ptr<float>(),
+                               delta.data_ptr<float>(), dq.data_ptr(), dk.data_ptr(), dv.data_ptr(), cq, ck, (int)batch, (int)sq,
+                               (int)sk, (int)max_q, (int)max_k, q.size(0), k.size(0), (int)q.size(1), (int)k.size(1), D,
+                               q.stride(0), k.stride(0), v.stride(0), out.stride(0), dout.stride(0), dq.stride(0), dk.stride(0),
+                               (float)scale, causal, status_tensor(q.device()).data_ptr<int>(), stream());
+  TORCH_CHECK(rc == 0, "flash_bwd launch failed with code ", rc);
+  return {dq, dk, dv};
+}
+
 // ---- fused FSDP over peer memory.  Pointer lists are raw device addresses of the same symmetric buffer on each rank.
 ab::CommPeers peers_from(const std::vector<int64_t>& ptrs) {
   TORCH_CHECK(ptrs.size() >= 1 && ptrs.size() <= 8, "peer pointer list must have 1..8 entries");
@@ -398,5 +427,6 @@ TORCH_LIBRARY(astrai_b200, m) {
   m.def("comm_wait_flags_(Tensor local_flags, int kind, int world, int skip_rank, int unit, int max_units, int epoch, float timeout_s) -> ()", &comm_wait_flags_);
   m.def("kernel_status_reset(Tensor like) -> ()", &kernel_status_reset);
   m.def("flash_fwd(Tensor q, Tensor k, Tensor v, Tensor? cu_q, Tensor? cu_k, int batch, int sq, int sk, int max_q, bool causal, float scale) -> (Tensor, Tensor)", &flash_fwd);
+  m.def("flash_bwd(Tensor q, Tensor k, Tensor v, Tensor out, Tensor dout, Tensor lse, Tensor? cu_q, Tensor? cu_k, int batch, int sq, int sk, int max_q, int max_k, bool causal, float scale) -> (Tensor, Tensor, Tensor)", &flash_bwd);
   m.def("gemm(Tensor A, Tensor B, Tensor? D, bool a_kmajor, bool b_kmajor, bool out_f32, bool accumulate) -> Tensor", &gemm);
 }

@@ -1,0 +1,605 @@
+// Flash attention backward on tcgen05 (sm_100a), as two deterministic kernels (no atomics) plus a row-dot pre-pass:
+//
+//   flash_delta      : delta[h, t] = sum_d dO[t,h,d] * O[t,h,d]
+//   flash_bwd_dkdv   : one CTA per (128-key tile, kv head, sequence).  K and V stay resident in shared memory; the CTA
+//                      walks over the query heads of its GQA group and over 64-query sub-tiles:
+//                        S^T = K Q^T, dP^T = V dO^T        (tcgen05, M=128 keys, N=64 queries, double-buffered in TMEM)
+//                        P^T = exp2(S^T c - lse), dS^T = P^T (dP^T - delta) scale      (one thread per key row)
+//                        dV += P^T dO, dK += dS^T Q        (tcgen05, accumulators live in TMEM for the whole CTA)
+//   flash_bwd_dq     : one CTA per (128-query tile, query head, sequence).  Q and dO stay resident; the CTA walks over
+//                      64-key sub-tiles: S = Q K^T, dP = dO V^T, dS = P (dP - delta) scale, dQ += dS K.
+// P^T / dS^T / dS are written by the row threads into shared memory in the 128-byte-swizzled K-major layout and consumed
+// as the A operand of the accumulating MMAs; dO, Q and K are consumed as MN-major B operands straight from the tiles TMA
+// delivered (no transposes are materialised).  Recomputing S and dP in the second kernel costs two extra GEMMs per tile
+// pair and buys a backward pass without fp32 atomics, with a fixed summation order.
+// Layouts, masking and GQA conventions are those of flash_fwd.cu.  Replaces the backward of
+// F.scaled_dot_product_attention in the reference's training path (astrai/extension/backend/attention.py:453-468).
+// All mbarrier waits are bounded; on expiry the CTA records a code in `status` and leaves through the common exit.
+#include <cuda.h>
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "launchers.h"
+#include "tcgen05.cuh"
+#include "tma_host.h"
+
+namespace ab {
+namespace {
+
+using namespace tc;
+using namespace tmah;
+
+constexpr int BWD_THREADS = 192, SUB = 64, QDO_STAGES = 3;
+constexpr int BLK128 = 128 * 128;  // [128 rows x 64 cols] swizzled block
+constexpr int BLK64 = 64 * 128;    // [64 rows x 64 cols] swizzled block
+constexpr float LOG2E = 1.4426950408889634f;
+enum : int { ERR_BWD_PRODUCER = 41, ERR_BWD_MMA = 42, ERR_BWD_ROWS = 43 };
+
+struct SeqInfoB {
+  int q_start, q_len, k_start, k_len;
+};
+__device__ __forceinline__ SeqInfoB seq_info_b(const int* cu_q, const int* cu_k, int b, int sq, int sk) {
+  SeqInfoB s;
+  s.q_start = cu_q ? cu_q[b] : b * sq;
+  s.q_len = cu_q ? cu_q[b + 1] - cu_q[b] : sq;
+  s.k_start = cu_k ? cu_k[b] : b * sk;
+  s.k_len = cu_k ? cu_k[b + 1] - cu_k[b] : sk;
+  return s;
+}
+
+// ------------------------------------------------------------------------------------------------ delta pre-pass
+template <int D>
+__global__ void flash_delta_kernel(const __nv_bfloat16* __restrict__ dO, const __nv_bfloat16* __restrict__ O,
+                                   float* __restrict__ delta, long long total_q, int Hq, long long do_stride,
+                                   long long o_stride) {
+  // one warp per (token, head); D/8 lanes carry 16 bytes each
+  const long long w = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  const int lane = threadIdx.x & 31;
+  if (w >= total_q * Hq) return;
+  const long long t = w / Hq;
+  const int h = (int)(w % Hq);
+  float acc = 0.f;
+  if (lane < D / 8) {
+    const uint4 a = *reinterpret_cast<const uint4*>(dO + t * do_stride + (long long)h * D + lane * 8);
+    const uint4 b = *reinterpret_cast<const uint4*>(O + t * o_stride + (long long)h * D + lane * 8);
+    const __nv_bfloat162* pa = reinterpret_cast<const __nv_bfloat162*>(&a);
+    const __nv_bfloat162* pb = reinterpret_cast<const __nv_bfloat162*>(&b);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const float2 x = __bfloat1622float2(pa[i]), y = __bfloat1622float2(pb[i]);
+      acc += x.x * y.x + x.y * y.y;
+    }
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+  if (lane == 0) delta[(long long)h * total_q + t] = acc;
+}
+
+// Row r of a [128 x 64] bf16 tile (K-major, 128B swizzle): eight 16-byte chunks.
+__device__ __forceinline__ void store_row64(uint8_t* tile, int r, const uint32_t (&pk)[32]) {
+  uint8_t* prow = tile + (r >> 3) * 1024 + (r & 7) * 128;
+#pragma unroll
+  for (int c = 0; c < 8; ++c)
+    *reinterpret_cast<uint4*>(prow + ((c ^ (r & 7)) << 4)) = make_uint4(pk[4 * c], pk[4 * c + 1], pk[4 * c + 2], pk[4 * c + 3]);
+}
+
+__device__ __forceinline__ uint32_t pack2(float a, float b) {
+  const __nv_bfloat162 h = __floats2bfloat162_rn(a, b);
+  return *reinterpret_cast<const uint32_t*>(&h);
+}
+
+// Write one accumulator row (D fp32 columns starting at TMEM address taddr) as bf16 to `dst`.
+template <int D>
+__device__ __forceinline__ void store_acc_row(uint32_t taddr, __nv_bfloat16* dst, bool live, bool have) {
+#pragma unroll 1
+  for (int c = 0; c < D / 32; ++c) {
+    uint32_t o[32];
+    if (have) {
+      tc_ld32(taddr + c * 32, o);
+      tc_wait_ld();
+    } else {
+#pragma unroll
+      for (int i = 0; i < 32; ++i) o[i] = 0u;
+    }
+    if (live) {
+#pragma unroll
+      for (int v4 = 0; v4 < 4; ++v4) {
+        uint4 pkd;
+        uint32_t* pw = reinterpret_cast<uint32_t*>(&pkd);
+#pragma unroll
+        for (int q = 0; q < 4; ++q) pw[q] = pack2(__uint_as_float(o[8 * v4 + 2 * q]), __uint_as_float(o[8 * v4 + 2 * q + 1]));
+        reinterpret_cast<uint4*>(dst + c * 32)[v4] = pkd;
+      }
+    }
+  }
+}
+
+// ------------------------------------------------------------------------------------------------ dK / dV
+template <int D>
+struct DkvCfg {
+  static constexpr int NB = D / 64;
+  static constexpr int KV_BYTES = 128 * D * 2;   // resident K or V tile
+  static constexpr int QS_BYTES = SUB * D * 2;   // one 64-row Q or dO stage
+  static constexpr int PT_BYTES = 128 * SUB * 2; // P^T or dS^T tile
+  static constexpr int SMEM = 2 * KV_BYTES + 2 * QDO_STAGES * QS_BYTES + 2 * PT_BYTES + 2 * 2 * SUB * 4 + 1024 + 256;
+};
+
+template <int D>
+__global__ void __launch_bounds__(BWD_THREADS, 1)
+flash_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_do,
+                      const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v,
+                      const float* __restrict__ lse, const float* __restrict__ delta, __nv_bfloat16* __restrict__ dK,
+                      __nv_bfloat16* __restrict__ dV, const int* __restrict__ cu_q, const int* __restrict__ cu_k, int sq,
+                      int sk, int Hq, int Hkv, long long dk_row_stride, long long total_q, float scale, int causal,
+                      int* __restrict__ status) {
+  using C = DkvCfg<D>;
+  const SeqInfoB si = seq_info_b(cu_q, cu_k, blockIdx.z, sq, sk);
+  const int k0 = (int)blockIdx.x * 128;
+  if (k0 >= si.k_len) return;
+  const int kvh = blockIdx.y, G = Hq / Hkv, off = si.k_len - si.q_len;
+  int q_lo = 0;
+  if (causal) q_lo = max(0, k0 - off) / SUB * SUB;
+  const int n_sub = max(0, (si.q_len - q_lo + SUB - 1) / SUB);
+  const int n_it = n_sub * G;
+
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  uint8_t* aligned = smem_raw + (base - smem_u32(smem_raw));
+  const uint32_t k_smem = base, v_smem = base + C::KV_BYTES;
+  const uint32_t q_smem = v_smem + C::KV_BYTES;                    // QDO_STAGES stages
+  const uint32_t do_smem = q_smem + QDO_STAGES * C::QS_BYTES;      // QDO_STAGES stages
+  const uint32_t pt_smem = do_smem + QDO_STAGES * C::QS_BYTES;
+  const uint32_t dst_smem = pt_smem + C::PT_BYTES;
+  uint8_t* pt_ptr = aligned + (pt_smem - base);
+  uint8_t* dst_ptr = aligned + (dst_smem - base);
+  float* ld_smem = reinterpret_cast<float*>(aligned + (dst_smem - base) + C::PT_BYTES);  // [2 slots][lse2 64 | delta 64]
+  uint64_t* bars = reinterpret_cast<uint64_t*>(reinterpret_cast<uint8_t*>(ld_smem) + 2 * 2 * SUB * 4);
+  const uint32_t bar0 = smem_u32(bars);
+  // 0 kv_full | 1..3 qdo_full | 4..6 qdo_empty | 7,8 s_full | 9 pds_full | 10 pds_empty
+  auto BAR = [&](int i) { return bar0 + 8u * i; };
+  uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(bars + 11);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_holder + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  if (threadIdx.x == 0) {
+    for (int i = 0; i < 11; ++i) mbar_init(BAR(i), i == 9 ? 4 : 1);
+    *abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    fence_async_smem();
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_holder)), "r"(512u)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_holder;
+  const uint32_t tmem_dv = tmem_base + 256, tmem_dk = tmem_base + 384;
+
+  if (warp == 0) {
+    if (lane == 0 && n_it > 0) {
+      mbar_expect_tx(BAR(0), 2 * C::KV_BYTES);
+#pragma unroll
+      for (int kb = 0; kb < C::NB; ++kb) {
+        tma_load_2d(k_smem + kb * BLK128, &map_k, BAR(0), kvh * D + kb * 64, si.k_start + k0);
+        tma_load_2d(v_smem + kb * BLK128, &map_v, BAR(0), kvh * D + kb * 64, si.k_start + k0);
+      }
+      bool ok = true;
+      for (int it = 0; it < n_it && ok; ++it) {
+        const int st = it % QDO_STAGES;
+        const uint32_t ph = ((it / QDO_STAGES) & 1) ^ 1u;
+        if (!mbar_wait(BAR(4 + st), ph, abort_flag)) { ok = false; break; }
+        const int h = kvh * G + it / n_sub, qs = q_lo + (it % n_sub) * SUB;
+        mbar_expect_tx(BAR(1 + st), 2 * C::QS_BYTES);
+#pragma unroll
+        for (int kb = 0; kb < C::NB; ++kb) {
+          tma_load_2d(q_smem + st * C::QS_BYTES + kb * BLK64, &map_q, BAR(1 + st), h * D + kb * 64, si.q_start + qs);
+          tma_load_2d(do_smem + st * C::QS_BYTES + kb * BLK64, &map_do, BAR(1 + st), h * D + kb * 64, si.q_start + qs);
+        }
+      }
+      if (!ok) {
+        atomicMax(status, ERR_BWD_PRODUCER);
+        *abort_flag = 1;
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0 && n_it > 0) {
+      constexpr uint32_t idesc_sc = idesc_bf16(128, SUB, false, false);
+      constexpr uint32_t idesc_acc = idesc_bf16(128, D, false, true);
+      bool ok = mbar_wait(BAR(0), 0, abort_flag);
+      auto issue_scores = [&](int it) -> bool {
+        const int st = it % QDO_STAGES, buf = it & 1;
+        if (!mbar_wait(BAR(1 + st), (it / QDO_STAGES) & 1, abort_flag)) return false;
+        tc_fence_after();
+#pragma unroll
+        for (int kb = 0; kb < C::NB; ++kb) {
+          const uint64_t da = smem_desc_sw128(k_smem + kb * BLK128, true, 0);
+          const uint64_t db = smem_desc_sw128(q_smem + st * C::QS_BYTES + kb * BLK64, true, 0);
+#pragma unroll
+          for (int k = 0; k < 4; ++k) tc_mma(tmem_base + buf * SUB, da + 2 * k, db + 2 * k, idesc_sc, (kb | k) ? 1u : 0u);
+        }
+#pragma unroll
+        for (int kb = 0; kb < C::NB; ++kb) {
+          const uint64_t da = smem_desc_sw128(v_smem + kb * BLK128, true, 0);
+          const uint64_t db = smem_desc_sw128(do_smem + st * C::QS_BYTES + kb * BLK64, true, 0);
+#pragma unroll
+          for (int k = 0; k < 4; ++k) tc_mma(tmem_base + 128 + buf * SUB, da + 2 * k, db + 2 * k, idesc_sc, (kb | k) ? 1u : 0u);
+        }
+        tc_commit(BAR(7 + buf));
+        return true;
+      };
+      if (ok) ok = issue_scores(0);
+      if (ok && n_it > 1) ok = issue_scores(1);
+      for (int it = 0; it < n_it && ok; ++it) {
+        const int st = it % QDO_STAGES;
+        if (!mbar_wait(BAR(9), it & 1, abort_flag)) { ok = false; break; }
+        tc_fence_after();
+        const uint64_t dpt = smem_desc_sw128(pt_smem, true, 0), ddst = smem_desc_sw128(dst_smem, true, 0);
+        const uint64_t ddo = smem_desc_sw128(do_smem + st * C::QS_BYTES, false, BLK64);
+        const uint64_t dq = smem_desc_sw128(q_smem + st * C::QS_BYTES, false, BLK64);
+#pragma unroll
+        for (int k = 0; k < 4; ++k) tc_mma(tmem_dv, dpt + 2 * k, ddo + (uint64_t)(k * 128), idesc_acc, (it | k) ? 1u : 0u);
+#pragma unroll
+        for (int k = 0; k < 4; ++k) tc_mma(tmem_dk, ddst + 2 * k, dq + (uint64_t)(k * 128), idesc_acc, (it | k) ? 1u : 0u);
+        tc_commit(BAR(4 + st));  // Q / dO stage free
+        tc_commit(BAR(10));      // P^T / dS^T consumed, accumulators updated
+        if (it + 2 < n_it && !issue_scores(it + 2)) { ok = false; break; }
+      }
+      if (!ok) {
+        atomicMax(status, ERR_BWD_MMA);
+        *abort_flag = 1;
+      }
+    }
+  } else {
+    const int quarter = warp & 3;
+    const int row = quarter * 32 + lane;        // key row of this thread
+    const uint32_t t_lane = tmem_base + ((uint32_t)(quarter * 32) << 16);
+    const int kidx = k0 + row;
+    const bool key_live = kidx < si.k_len;
+    const float scale_log2 = scale * LOG2E;
+    bool ok = true;
+    for (int it = 0; it < n_it; ++it) {
+      const int buf = it & 1;
+      const int h = kvh * G + it / n_sub, qs = q_lo + (it % n_sub) * SUB;
+      ok = __all_sync(0xffffffffu, mbar_wait(BAR(7 + buf), (it >> 1) & 1, abort_flag));
+      if (!ok) break;
+      tc_fence_after();
+      uint32_t s[2][32], dp[2][32];
+      tc_ld32(t_lane + buf * SUB, s[0]);
+      tc_ld32(t_lane + buf * SUB + 32, s[1]);
+      tc_ld32(t_lane + 128 + buf * SUB, dp[0]);
+      tc_ld32(t_lane + 128 + buf * SUB + 32, dp[1]);
+      tc_wait_ld();
+      // lse / delta of the 64 query columns come straight from global memory (every lane of the warp reads the same
+      // addresses: one broadcast transaction each, L1-resident across the four row warps)
+      const float* lp = lse + (long long)h * total_q + si.q_start + qs;
+      const float* dlp = delta + (long long)h * total_q + si.q_start + qs;
+      const bool vec = (qs + SUB <= si.q_len) && (((reinterpret_cast<uintptr_t>(lp) | reinterpret_cast<uintptr_t>(dlp)) & 15) == 0);
+      const int qmin = causal ? kidx - off : -0x40000000;  // query q sees this key iff q >= kidx - off
+      uint32_t ppk[32], dpk[32];
+#pragma unroll
+      for (int c2 = 0; c2 < 2; ++c2)
+#pragma unroll
+        for (int i = 0; i < 32; i += 4) {
+          const int c = c2 * 32 + i;
+          float lv[4], dv[4];
+          if (vec) {
+            *reinterpret_cast<float4*>(lv) = __ldg(reinterpret_cast<const float4*>(lp + c));
+            *reinterpret_cast<float4*>(dv) = __ldg(reinterpret_cast<const float4*>(dlp + c));
+          } else {
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+              const bool in = qs + c + e < si.q_len;
+              lv[e] = in ? __ldg(lp + c + e) : INFINITY;
+              dv[e] = in ? __ldg(dlp + c + e) : 0.f;
+            }
+          }
+          float pv[4], dsv[4];
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            float pe = ex2(fmaf(__uint_as_float(s[c2][i + e]), scale_log2, -lv[e] * LOG2E));
+            if (!key_live || qs + c + e < qmin) pe = 0.f;
+            pv[e] = pe;
+            dsv[e] = pe * (__uint_as_float(dp[c2][i + e]) - dv[e]) * scale;
+          }
+          ppk[c >> 1] = pack2(pv[0], pv[1]);
+          ppk[(c >> 1) + 1] = pack2(pv[2], pv[3]);
+          dpk[c >> 1] = pack2(dsv[0], dsv[1]);
+          dpk[(c >> 1) + 1] = pack2(dsv[2], dsv[3]);
+        }
+      if (it > 0) {
+        ok = __all_sync(0xffffffffu, mbar_wait(BAR(10), (it - 1) & 1, abort_flag));
+        if (!ok) break;
+      }
+      store_row64(pt_ptr, row, ppk);
+      store_row64(dst_ptr, row, dpk);
+      fence_async_smem();
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(BAR(9));
+    }
+    if (ok && n_it > 0) {
+      ok = __all_sync(0xffffffffu, mbar_wait(BAR(10), (n_it - 1) & 1, abort_flag));
+      if (ok) tc_fence_after();
+    }
+    if (ok) {
+      const long long tok = (long long)si.k_start + kidx;
+      store_acc_row<D>(t_lane + 256, dV + tok * dk_row_stride + (long long)kvh * D, key_live, n_it > 0);
+      store_acc_row<D>(t_lane + 384, dK + tok * dk_row_stride + (long long)kvh * D, key_live, n_it > 0);
+    } else if (lane == 0) {
+      atomicMax(status, ERR_BWD_ROWS);
+      *abort_flag = 1;
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(512u) : "memory");
+  }
+}
+
+// ------------------------------------------------------------------------------------------------ dQ
+template <int D>
+struct DqCfg {
+  static constexpr int NB = D / 64;
+  static constexpr int Q_BYTES = 128 * D * 2;   // resident Q or dO tile
+  static constexpr int KS_BYTES = SUB * D * 2;  // one 64-key K or V stage
+  static constexpr int DS_BYTES = 128 * SUB * 2;
+  static constexpr int SMEM = 2 * Q_BYTES + 2 * QDO_STAGES * KS_BYTES + DS_BYTES + 1024 + 256;
+};
+
+template <int D>
+__global__ void __launch_bounds__(BWD_THREADS, 1)
+flash_bwd_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_do,
+                    const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v,
+                    const float* __restrict__ lse, const float* __restrict__ delta, __nv_bfloat16* __restrict__ dQ,
+                    const int* __restrict__ cu_q, const int* __restrict__ cu_k, int sq, int sk, int Hq, int Hkv,
+                    long long dq_row_stride, long long total_q, float scale, int causal, int* __restrict__ status) {
+  using C = DqCfg<D>;
+  const SeqInfoB si = seq_info_b(cu_q, cu_k, blockIdx.z, sq, sk);
+  const int n_q_tiles = (si.q_len + 127) / 128;
+  const int qt = n_q_tiles - 1 - (int)blockIdx.x;
+  if (qt < 0) return;
+  const int h = blockIdx.y, kvh = h / (Hq / Hkv);
+  const int q0 = qt * 128, off = si.k_len - si.q_len;
+  int kv_end = si.k_len;
+  if (causal) kv_end = min(si.k_len, q0 + 128 + off);
+  if (kv_end < 0) kv_end = 0;
+  const int n_it = (kv_end + SUB - 1) / SUB;
+
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  uint8_t* aligned = smem_raw + (base - smem_u32(smem_raw));
+  const uint32_t q_smem = base, do_smem = base + C::Q_BYTES;
+  const uint32_t k_smem = do_smem + C::Q_BYTES;                 // stages
+  const uint32_t v_smem = k_smem + QDO_STAGES * C::KS_BYTES;    // stages
+  const uint32_t ds_smem = v_smem + QDO_STAGES * C::KS_BYTES;
+  uint8_t* ds_ptr = aligned + (ds_smem - base);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(ds_ptr + C::DS_BYTES);
+  const uint32_t bar0 = smem_u32(bars);
+  // 0 qdo_full | 1..3 k_full | 4..6 k_empty | 7..9 v_full | 10..12 v_empty | 13,14 s_full | 15 ds_full | 16 ds_empty
+  auto BAR = [&](int i) { return bar0 + 8u * i; };
+  uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(bars + 17);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_holder + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  if (threadIdx.x == 0) {
+    for (int i = 0; i < 17; ++i) mbar_init(BAR(i), i == 15 ? 4 : 1);
+    *abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    fence_async_smem();
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_holder)), "r"(512u)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_holder;
+  const uint32_t tmem_dq = tmem_base + 256;
+
+  if (warp == 0) {
+    if (lane == 0 && n_it > 0) {
+      mbar_expect_tx(BAR(0), 2 * C::Q_BYTES);
+#pragma unroll
+      for (int kb = 0; kb < C::NB; ++kb) {
+        tma_load_2d(q_smem + kb * BLK128, &map_q, BAR(0), h * D + kb * 64, si.q_start + q0);
+        tma_load_2d(do_smem + kb * BLK128, &map_do, BAR(0), h * D + kb * 64, si.q_start + q0);
+      }
+      bool ok = true;
+      for (int j = 0; j < n_it && ok; ++j) {
+        const int st = j % QDO_STAGES;
+        const uint32_t ph = ((j / QDO_STAGES) & 1) ^ 1u;
+        if (!mbar_wait(BAR(4 + st), ph, abort_flag)) { ok = false; break; }
+        mbar_expect_tx(BAR(1 + st), C::KS_BYTES);
+#pragma unroll
+        for (int kb = 0; kb < C::NB; ++kb)
+          tma_load_2d(k_smem + st * C::KS_BYTES + kb * BLK64, &map_k, BAR(1 + st), kvh * D + kb * 64, si.k_start + j * SUB);
+        if (!mbar_wait(BAR(10 + st), ph, abort_flag)) { ok = false; break; }
+        mbar_expect_tx(BAR(7 + st), C::KS_BYTES);
+#pragma unroll
+        for (int kb = 0; kb < C::NB; ++kb)
+          tma_load_2d(v_smem + st * C::KS_BYTES + kb * BLK64, &map_v, BAR(7 + st), kvh * D + kb * 64, si.k_start + j * SUB);
+      }
+      if (!ok) {
+        atomicMax(status, ERR_BWD_PRODUCER);
+        *abort_flag = 1;
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0 && n_it > 0) {
+      constexpr uint32_t idesc_sc = idesc_bf16(128, SUB, false, false);
+      constexpr uint32_t idesc_acc = idesc_bf16(128, D, false, true);
+      bool ok = mbar_wait(BAR(0), 0, abort_flag);
+      auto issue_scores = [&](int j) -> bool {
+        const int st = j % QDO_STAGES, buf = j & 1;
+        const uint32_t ph = (j / QDO_STAGES) & 1;
+        if (!mbar_wait(BAR(1 + st), ph, abort_flag) || !mbar_wait(BAR(7 + st), ph, abort_flag)) return false;
+        tc_fence_after();
+#pragma unroll
+        for (int kb = 0; kb < C::NB; ++kb) {
+          const uint64_t da = smem_desc_sw128(q_smem + kb * BLK128, true, 0);
+          const uint64_t db = smem_desc_sw128(k_smem + st * C::KS_BYTES + kb * BLK64, true, 0);
+#pragma unroll
+          for (int k = 0; k < 4; ++k) tc_mma(tmem_base + buf * SUB, da + 2 * k, db + 2 * k, idesc_sc, (kb | k) ? 1u : 0u);
+        }
+#pragma unroll
+        for (int kb = 0; kb < C::NB; ++kb) {
+          const uint64_t da = smem_desc_sw128(do_smem + kb * BLK128, true, 0);
+          const uint64_t db = smem_desc_sw128(v_smem + st * C::KS_BYTES + kb * BLK64, true, 0);
+#pragma unroll
+          for (int k = 0; k < 4; ++k) tc_mma(tmem_base + 128 + buf * SUB, da + 2 * k, db + 2 * k, idesc_sc, (kb | k) ? 1u : 0u);
+        }
+        tc_commit(BAR(10 + st));  // V stage free
+        tc_commit(BAR(13 + buf));
+        return true;
+      };
+      if (ok) ok = issue_scores(0);
+      if (ok && n_it > 1) ok = issue_scores(1);
+      for (int j = 0; j < n_it && ok; ++j) {
+        const int st = j % QDO_STAGES;
+        if (!mbar_wait(BAR(15), j & 1, abort_flag)) { ok = false; break; }
+        tc_fence_after();
+        const uint64_t dds = smem_desc_sw128(ds_smem, true, 0);
+        const uint64_t dk = smem_desc_sw128(k_smem + st * C::KS_BYTES, false, BLK64);
+#pragma unroll
+        for (int k = 0; k < 4; ++k) tc_mma(tmem_dq, dds + 2 * k, dk + (uint64_t)(k * 128), idesc_acc, (j | k) ? 1u : 0u);
+        tc_commit(BAR(4 + st));  // K stage free
+        tc_commit(BAR(16));      // dS consumed, dQ updated
+        if (j + 2 < n_it && !issue_scores(j + 2)) { ok = false; break; }
+      }
+      if (!ok) {
+        atomicMax(status, ERR_BWD_MMA);
+        *abort_flag = 1;
+      }
+    }
+  } else {
+    const int quarter = warp & 3;
+    const int row = quarter * 32 + lane;  // query row of this thread
+    const uint32_t t_lane = tmem_base + ((uint32_t)(quarter * 32) << 16);
+    const int q_idx = q0 + row;
+    const bool q_live = q_idx < si.q_len;
+    const long long tok = (long long)si.q_start + q_idx;
+    const float lse2 = q_live ? lse[(long long)h * total_q + tok] * LOG2E : INFINITY;
+    const float dlt = q_live ? delta[(long long)h * total_q + tok] : 0.f;
+    const float scale_log2 = scale * LOG2E;
+    int limit = si.k_len;
+    if (causal) limit = min(limit, q_idx + off + 1);
+    bool ok = true;
+    for (int j = 0; j < n_it; ++j) {
+      const int buf = j & 1;
+      ok = __all_sync(0xffffffffu, mbar_wait(BAR(13 + buf), (j >> 1) & 1, abort_flag));
+      if (!ok) break;
+      tc_fence_after();
+      uint32_t s[2][32], dp[2][32];
+      tc_ld32(t_lane + buf * SUB, s[0]);
+      tc_ld32(t_lane + buf * SUB + 32, s[1]);
+      tc_ld32(t_lane + 128 + buf * SUB, dp[0]);
+      tc_ld32(t_lane + 128 + buf * SUB + 32, dp[1]);
+      tc_wait_ld();
+      const int kbase = j * SUB;
+      uint32_t dpk[32];
+#pragma unroll
+      for (int c2 = 0; c2 < 2; ++c2)
+#pragma unroll
+        for (int i = 0; i < 32; i += 2) {
+          const int c = c2 * 32 + i;
+          float p0 = ex2(fmaf(__uint_as_float(s[c2][i]), scale_log2, -lse2));
+          float p1 = ex2(fmaf(__uint_as_float(s[c2][i + 1]), scale_log2, -lse2));
+          if (kbase + c >= limit) p0 = 0.f;
+          if (kbase + c + 1 >= limit) p1 = 0.f;
+          dpk[c >> 1] = pack2(p0 * (__uint_as_float(dp[c2][i]) - dlt) * scale, p1 * (__uint_as_float(dp[c2][i + 1]) - dlt) * scale);
+        }
+      if (j > 0) {
+        ok = __all_sync(0xffffffffu, mbar_wait(BAR(16), (j - 1) & 1, abort_flag));
+        if (!ok) break;
+      }
+      store_row64(ds_ptr, row, dpk);
+      fence_async_smem();
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(BAR(15));
+    }
+    if (ok && n_it > 0) {
+      ok = __all_sync(0xffffffffu, mbar_wait(BAR(16), (n_it - 1) & 1, abort_flag));
+      if (ok) tc_fence_after();
+    }
+    if (ok) {
+      store_acc_row<D>(t_lane + 256, dQ + tok * dq_row_stride + (long long)h * D, q_live, n_it > 0);
+    } else if (lane == 0) {
+      atomicMax(status, ERR_BWD_ROWS);
+      *abort_flag = 1;
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(512u) : "memory");
+  }
+}
+
+template <int D>
+int launch_bwd(const void* q, const void* k, const void* v, const void* out, const void* dout, const float* lse,
+               float* delta, void* dq, void* dk, void* dv, const int* cu_q, const int* cu_k, int batch, int sq, int sk,
+               int max_q, int max_k, long long total_q, long long total_k, int Hq, int Hkv, long long q_rs, long long k_rs,
+               long long v_rs, long long o_rs, long long do_rs, long long dq_rs, long long dk_rs, float scale, bool causal,
+               int* status, cudaStream_t st) {
+  CUtensorMap mq64, mdo64, mk128, mv128, mq128, mdo128, mk64, mv64;
+  bool ok = cache().get(&mq64, q, (long long)Hq * D, total_q, q_rs, 64, 64) &&
+            cache().get(&mdo64, dout, (long long)Hq * D, total_q, do_rs, 64, 64) &&
+            cache().get(&mk128, k, (long long)Hkv * D, total_k, k_rs, 64, 128) &&
+            cache().get(&mv128, v, (long long)Hkv * D, total_k, v_rs, 64, 128) &&
+            cache().get(&mq128, q, (long long)Hq * D, total_q, q_rs, 64, 128) &&
+            cache().get(&mdo128, dout, (long long)Hq * D, total_q, do_rs, 64, 128) &&
+            cache().get(&mk64, k, (long long)Hkv * D, total_k, k_rs, 64, 64) &&
+            cache().get(&mv64, v, (long long)Hkv * D, total_k, v_rs, 64, 64);
+  if (!ok) return -1000 - g_last_map_error;
+  auto kern_a = flash_bwd_dkdv_kernel<D>;
+  auto kern_b = flash_bwd_dq_kernel<D>;
+  static bool configured = false;
+  if (!configured) {
+    if (cudaFuncSetAttribute(kern_a, cudaFuncAttributeMaxDynamicSharedMemorySize, DkvCfg<D>::SMEM) != cudaSuccess) return -4;
+    if (cudaFuncSetAttribute(kern_b, cudaFuncAttributeMaxDynamicSharedMemorySize, DqCfg<D>::SMEM) != cudaSuccess) return -4;
+    configured = true;
+  }
+  const long long warps = total_q * Hq;
+  flash_delta_kernel<D><<<(unsigned)((warps * 32 + 255) / 256), 256, 0, st>>>(
+      (const __nv_bfloat16*)dout, (const __nv_bfloat16*)out, delta, total_q, Hq, do_rs, o_rs);
+  const dim3 grid_a((max_k + 127) / 128, Hkv, batch);
+  kern_a<<<grid_a, BWD_THREADS, DkvCfg<D>::SMEM, st>>>(mq64, mdo64, mk128, mv128, lse, delta, (__nv_bfloat16*)dk,
+                                                       (__nv_bfloat16*)dv, cu_q, cu_k, sq, sk, Hq, Hkv, dk_rs, total_q,
+                                                       scale, causal ? 1 : 0, status);
+  const dim3 grid_b((max_q + 127) / 128, Hq, batch);
+  kern_b<<<grid_b, BWD_THREADS, DqCfg<D>::SMEM, st>>>(mq128, mdo128, mk64, mv64, lse, delta, (__nv_bfloat16*)dq, cu_q,
+                                                      cu_k, sq, sk, Hq, Hkv, dq_rs, total_q, scale, causal ? 1 : 0, status);
+  return cudaGetLastError() == cudaSuccess ? 0 : -5;
+}
+
+}  // namespace
+
+int flash_bwd(const void* q, const void* k, const void* v, const void* out, const void* dout, const float* lse,
+              float* delta, void* dq, void* dk, void* dv, const int* cu_q, const int* cu_k, int batch, int sq, int sk,
+              int max_q, int max_k, long long total_q, long long total_k, int Hq, int Hkv, int D, long long q_rs,
+              long long k_rs, long long v_rs, long long o_rs, long long do_rs, long long dq_rs, long long dk_rs, float scale,
+              bool causal, int* status, cudaStream_t st) {
+  if (batch <= 0 || total_q <= 0) return 0;
+  if (Hkv <= 0 || Hq % Hkv) return -1;
+  if (D == 128)
+    return launch_bwd<128>(q, k, v, out, dout, lse, delta, dq, dk, dv, cu_q, cu_k, batch, sq, sk, max_q, max_k, total_q,
+                           total_k, Hq, Hkv, q_rs, k_rs, v_rs, o_rs, do_rs, dq_rs, dk_rs, scale, causal, status, st);
+  if (D == 64)
+    return launch_bwd<64>(q, k, v, out, dout, lse, delta, dq, dk, dv, cu_q, cu_k, batch, sq, sk, max_q, max_k, total_q,
+                          total_k, Hq, Hkv, q_rs, k_rs, v_rs, o_rs, do_rs, dq_rs, dk_rs, scale, causal, status, st);
+  return -3;
+}
+
+}  // namespace ab

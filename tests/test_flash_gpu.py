@@ -72,3 +72,62 @@ def test_flash_fwd_varlen_with_prefix(d):
         ref, ref_lse = _ref_attention(q[qs].float(), k[ks].float(), v[ks].float(), True, scale)
         assert (out[qs].float() - ref).abs().max().item() < 2e-2, i
         assert (lse[:, qs] - ref_lse).abs().max().item() < 2e-2, i
+
+
+def _ref_grads(q, k, v, do, causal, scale):
+    q, k, v = (t.float().detach().requires_grad_(True) for t in (q, k, v))
+    out, _ = _ref_attention(q, k, v, causal, scale)
+    out.backward(do.float())
+    return q.grad, k.grad, v.grad
+
+
+def _close(a, b, tol):
+    denom = b.abs().max().item() + 1e-6
+    return (a.float() - b).abs().max().item() / denom < tol
+
+
+@pytest.mark.parametrize("d", [128, 64])
+@pytest.mark.parametrize("causal", [True, False])
+@pytest.mark.parametrize("b,s,hq,hkv", [(2, 256, 4, 2), (1, 320, 2, 2), (2, 200, 4, 1)])
+def test_flash_bwd_dense(d, causal, b, s, hq, hkv):
+    ops = _native()
+    torch.manual_seed(2)
+    q = torch.randn(b * s, hq, d, device="cuda", dtype=torch.bfloat16)
+    k = torch.randn(b * s, hkv, d, device="cuda", dtype=torch.bfloat16)
+    v = torch.randn(b * s, hkv, d, device="cuda", dtype=torch.bfloat16)
+    do = torch.randn(b * s, hq, d, device="cuda", dtype=torch.bfloat16)
+    scale = 1.0 / math.sqrt(d)
+    out, lse = ops.flash_fwd(q, k, v, None, None, b, s, s, s, causal, scale)
+    dq, dk, dv = ops.flash_bwd(q, k, v, out, do, lse, None, None, b, s, s, s, s, causal, scale)
+    for i in range(b):
+        sl = slice(i * s, (i + 1) * s)
+        rq, rk, rv = _ref_grads(q[sl], k[sl], v[sl], do[sl], causal, scale)
+        assert _close(dv[sl], rv, 2e-2), ("dv", i)
+        assert _close(dk[sl], rk, 2e-2), ("dk", i)
+        assert _close(dq[sl], rq, 2e-2), ("dq", i)
+    from astrai_b200.ops import native
+
+    assert native.kernel_status(q.device) == 0
+
+
+def test_flash_bwd_varlen_with_prefix():
+    ops = _native()
+    torch.manual_seed(3)
+    d, hq, hkv = 128, 4, 2
+    q_lens, k_lens = [130, 1, 77, 256], [130, 300, 200, 256]
+    cu_q = torch.tensor([0] + list(torch.tensor(q_lens).cumsum(0)), dtype=torch.int32, device="cuda")
+    cu_k = torch.tensor([0] + list(torch.tensor(k_lens).cumsum(0)), dtype=torch.int32, device="cuda")
+    q = torch.randn(sum(q_lens), hq, d, device="cuda", dtype=torch.bfloat16)
+    k = torch.randn(sum(k_lens), hkv, d, device="cuda", dtype=torch.bfloat16)
+    v = torch.randn(sum(k_lens), hkv, d, device="cuda", dtype=torch.bfloat16)
+    do = torch.randn_like(q)
+    scale = 1.0 / math.sqrt(d)
+    out, lse = ops.flash_fwd(q, k, v, cu_q, cu_k, 4, 0, 0, max(q_lens), True, scale)
+    dq, dk, dv = ops.flash_bwd(q, k, v, out, do, lse, cu_q, cu_k, 4, 0, 0, max(q_lens), max(k_lens), True, scale)
+    for i in range(4):
+        qs = slice(int(cu_q[i]), int(cu_q[i + 1]))
+        ks = slice(int(cu_k[i]), int(cu_k[i + 1]))
+        rq, rk, rv = _ref_grads(q[qs], k[ks], v[ks], do[qs], True, scale)
+        assert _close(dv[ks], rv, 2e-2), ("dv", i)
+        assert _close(dk[ks], rk, 2e-2), ("dk", i)
+        assert _close(dq[qs], rq, 2e-2), ("dq", i)
