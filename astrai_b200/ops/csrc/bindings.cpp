@@ -331,7 +331,7 @@ std::tuple<Tensor, Tensor, Tensor> flash_bwd(const Tensor& q, const Tensor& k, c
   Tensor dq = at::empty({q.size(0), q.size(1), q.size(2)}, q.options());
   Tensor dk = at::empty({k.size(0), k.size(1), k.size(2)}, k.options());
   Tensor dv = at::empty({k.size(0), k.size(1), k.size(2)}, k.options());
-  Tensor delta = at::empty({q.size(1), q.size(0)}, q.options().dtype(at::kFloat));
+  Tensor delta = at::empty({2, q.size(1), q.size(0)}, q.options().dtype(at::kFloat));  // row dots | lse in log2 units
   count(3);
   const int rc = ab::flash_bwd(q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(), dout.data_ptr(), lse.data_ptr<float>(),
                                delta.data_ptr<float>(), dq.data_ptr(), dk.data_ptr(), dv.data_ptr(), cq, ck, (int)batch, (int)sq,

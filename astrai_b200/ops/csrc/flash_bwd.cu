@@ -4,10 +4,11 @@
 //   flash_bwd_dkdv   : one CTA per (128-key tile, kv head, sequence).  K and V stay resident in shared memory; the CTA
 //                      walks over the query heads of its GQA group and over 64-query sub-tiles:
 //                        S^T = K Q^T, dP^T = V dO^T        (tcgen05, M=128 keys, N=64 queries, double-buffered in TMEM)
-//                        P^T = exp2(S^T c - lse), dS^T = P^T (dP^T - delta) scale      (one thread per key row)
+//                        P^T = exp2(S^T c - lse), dS^T = P^T (dP^T - delta)     (one thread per key row; two warp groups alternate sub-tiles)
 //                        dV += P^T dO, dK += dS^T Q        (tcgen05, accumulators live in TMEM for the whole CTA)
 //   flash_bwd_dq     : one CTA per (128-query tile, query head, sequence).  Q and dO stay resident; the CTA walks over
-//                      64-key sub-tiles: S = Q K^T, dP = dO V^T, dS = P (dP - delta) scale, dQ += dS K.
+//                      64-key sub-tiles: S = Q K^T, dP = dO V^T, dS = P (dP - delta), dQ += dS K.  The softmax scale is applied
+//                      to dK and dQ once, when the accumulators are written out.
 // P^T / dS^T / dS are written by the row threads into shared memory in the 128-byte-swizzled K-major layout and consumed
 // as the A operand of the accumulating MMAs; dO, Q and K are consumed as MN-major B operands straight from the tiles TMA
 // delivered (no transposes are materialised).  Recomputing S and dP in the second kernel costs two extra GEMMs per tile
@@ -30,10 +31,16 @@ namespace {
 using namespace tc;
 using namespace tmah;
 
-constexpr int BWD_THREADS = 192, SUB = 64, QDO_STAGES = 3;
+constexpr int BWD_THREADS = 320, SUB = 64, QDO_STAGES = 3, KV_STAGES_B = 4;  // warp 0 TMA, warp 1 MMA, warps 2..9 rows (two per TMEM quarter)
 constexpr int BLK128 = 128 * 128;  // [128 rows x 64 cols] swizzled block
 constexpr int BLK64 = 64 * 128;    // [64 rows x 64 cols] swizzled block
 constexpr float LOG2E = 1.4426950408889634f;
+// mbarrier slots.  dK/dV kernel: kv_full | qdo_full[S] | qdo_empty[S] | s_full[2] | pds_full[2] | pds_empty[2] | done
+enum : int { A_QF = 1, A_QE = 1 + QDO_STAGES, A_SF = 1 + 2 * QDO_STAGES, A_PF = 3 + 2 * QDO_STAGES, A_PE = 5 + 2 * QDO_STAGES,
+             A_DONE = 7 + 2 * QDO_STAGES, A_NBAR = 8 + 2 * QDO_STAGES };
+// dQ kernel: qdo_full | k_full[S] | k_empty[S] | v_full[S] | v_empty[S] | s_full[2] | ds_full[2] | ds_empty[2] | done
+enum : int { B_KF = 1, B_KE = 1 + KV_STAGES_B, B_VF = 1 + 2 * KV_STAGES_B, B_VE = 1 + 3 * KV_STAGES_B, B_SF = 1 + 4 * KV_STAGES_B,
+             B_DF = 3 + 4 * KV_STAGES_B, B_DE = 5 + 4 * KV_STAGES_B, B_DONE = 7 + 4 * KV_STAGES_B, B_NBAR = 8 + 4 * KV_STAGES_B };
 enum : int { ERR_BWD_PRODUCER = 41, ERR_BWD_MMA = 42, ERR_BWD_ROWS = 43 };
 
 struct SeqInfoB {
@@ -51,8 +58,8 @@ __device__ __forceinline__ SeqInfoB seq_info_b(const int* cu_q, const int* cu_k,
 // ------------------------------------------------------------------------------------------------ delta pre-pass
 template <int D>
 __global__ void flash_delta_kernel(const __nv_bfloat16* __restrict__ dO, const __nv_bfloat16* __restrict__ O,
-                                   float* __restrict__ delta, long long total_q, int Hq, long long do_stride,
-                                   long long o_stride) {
+                                   const float* __restrict__ lse, float* __restrict__ delta, float* __restrict__ lse2,
+                                   long long total_q, int Hq, long long do_stride, long long o_stride) {
   // one warp per (token, head); D/8 lanes carry 16 bytes each
   const long long w = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
   const int lane = threadIdx.x & 31;
@@ -73,7 +80,10 @@ __global__ void flash_delta_kernel(const __nv_bfloat16* __restrict__ dO, const _
   }
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
-  if (lane == 0) delta[(long long)h * total_q + t] = acc;
+  if (lane == 0) {
+    delta[(long long)h * total_q + t] = acc;
+    lse2[(long long)h * total_q + t] = lse[(long long)h * total_q + t] * LOG2E;
+  }
 }
 
 // Row r of a [128 x 64] bf16 tile (K-major, 128B swizzle): eight 16-byte chunks.
@@ -89,11 +99,11 @@ __device__ __forceinline__ uint32_t pack2(float a, float b) {
   return *reinterpret_cast<const uint32_t*>(&h);
 }
 
-// Write one accumulator row (D fp32 columns starting at TMEM address taddr) as bf16 to `dst`.
-template <int D>
-__device__ __forceinline__ void store_acc_row(uint32_t taddr, __nv_bfloat16* dst, bool live, bool have) {
+// Write 32-column chunks [c_begin, c_end) of one accumulator row (fp32 in TMEM at taddr) times `mult` as bf16 to `dst`.
+__device__ __forceinline__ void store_acc_row(uint32_t taddr, __nv_bfloat16* dst, bool live, bool have, int c_begin,
+                                              int c_end, float mult) {
 #pragma unroll 1
-  for (int c = 0; c < D / 32; ++c) {
+  for (int c = c_begin; c < c_end; ++c) {
     uint32_t o[32];
     if (have) {
       tc_ld32(taddr + c * 32, o);
@@ -108,7 +118,8 @@ __device__ __forceinline__ void store_acc_row(uint32_t taddr, __nv_bfloat16* dst
         uint4 pkd;
         uint32_t* pw = reinterpret_cast<uint32_t*>(&pkd);
 #pragma unroll
-        for (int q = 0; q < 4; ++q) pw[q] = pack2(__uint_as_float(o[8 * v4 + 2 * q]), __uint_as_float(o[8 * v4 + 2 * q + 1]));
+        for (int q = 0; q < 4; ++q)
+          pw[q] = pack2(__uint_as_float(o[8 * v4 + 2 * q]) * mult, __uint_as_float(o[8 * v4 + 2 * q + 1]) * mult);
         reinterpret_cast<uint4*>(dst + c * 32)[v4] = pkd;
       }
     }
@@ -122,14 +133,14 @@ struct DkvCfg {
   static constexpr int KV_BYTES = 128 * D * 2;   // resident K or V tile
   static constexpr int QS_BYTES = SUB * D * 2;   // one 64-row Q or dO stage
   static constexpr int PT_BYTES = 128 * SUB * 2; // P^T or dS^T tile
-  static constexpr int SMEM = 2 * KV_BYTES + 2 * QDO_STAGES * QS_BYTES + 2 * PT_BYTES + 2 * 2 * SUB * 4 + 1024 + 256;
+  static constexpr int SMEM = 2 * KV_BYTES + 2 * QDO_STAGES * QS_BYTES + 4 * PT_BYTES + 1024 + 256;
 };
 
 template <int D>
 __global__ void __launch_bounds__(BWD_THREADS, 1)
 flash_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_do,
                       const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v,
-                      const float* __restrict__ lse, const float* __restrict__ delta, __nv_bfloat16* __restrict__ dK,
+                      const float* __restrict__ lse2g, const float* __restrict__ delta, __nv_bfloat16* __restrict__ dK,
                       __nv_bfloat16* __restrict__ dV, const int* __restrict__ cu_q, const int* __restrict__ cu_k, int sq,
                       int sk, int Hq, int Hkv, long long dk_row_stride, long long total_q, float scale, int causal,
                       int* __restrict__ status) {
@@ -150,20 +161,18 @@ flash_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
   const uint32_t q_smem = v_smem + C::KV_BYTES;                    // QDO_STAGES stages
   const uint32_t do_smem = q_smem + QDO_STAGES * C::QS_BYTES;      // QDO_STAGES stages
   const uint32_t pt_smem = do_smem + QDO_STAGES * C::QS_BYTES;
-  const uint32_t dst_smem = pt_smem + C::PT_BYTES;
+  const uint32_t dst_smem = pt_smem + 2 * C::PT_BYTES;  // P^T and dS^T are double-buffered (one buffer per row-warp group)
   uint8_t* pt_ptr = aligned + (pt_smem - base);
   uint8_t* dst_ptr = aligned + (dst_smem - base);
-  float* ld_smem = reinterpret_cast<float*>(aligned + (dst_smem - base) + C::PT_BYTES);  // [2 slots][lse2 64 | delta 64]
-  uint64_t* bars = reinterpret_cast<uint64_t*>(reinterpret_cast<uint8_t*>(ld_smem) + 2 * 2 * SUB * 4);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(dst_ptr + 2 * C::PT_BYTES);
   const uint32_t bar0 = smem_u32(bars);
-  // 0 kv_full | 1..3 qdo_full | 4..6 qdo_empty | 7,8 s_full | 9 pds_full | 10 pds_empty
   auto BAR = [&](int i) { return bar0 + 8u * i; };
-  uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(bars + 11);
+  uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(bars + A_NBAR);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_holder + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   if (threadIdx.x == 0) {
-    for (int i = 0; i < 11; ++i) mbar_init(BAR(i), i == 9 ? 4 : 1);
+    for (int i = 0; i < A_NBAR; ++i) mbar_init(BAR(i), (i == A_PF || i == A_PF + 1) ? 4 : 1);
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     fence_async_smem();
@@ -191,13 +200,13 @@ flash_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
       for (int it = 0; it < n_it && ok; ++it) {
         const int st = it % QDO_STAGES;
         const uint32_t ph = ((it / QDO_STAGES) & 1) ^ 1u;
-        if (!mbar_wait(BAR(4 + st), ph, abort_flag)) { ok = false; break; }
+        if (!mbar_wait(BAR(A_QE + st), ph, abort_flag)) { ok = false; break; }
         const int h = kvh * G + it / n_sub, qs = q_lo + (it % n_sub) * SUB;
-        mbar_expect_tx(BAR(1 + st), 2 * C::QS_BYTES);
+        mbar_expect_tx(BAR(A_QF + st), 2 * C::QS_BYTES);
 #pragma unroll
         for (int kb = 0; kb < C::NB; ++kb) {
-          tma_load_2d(q_smem + st * C::QS_BYTES + kb * BLK64, &map_q, BAR(1 + st), h * D + kb * 64, si.q_start + qs);
-          tma_load_2d(do_smem + st * C::QS_BYTES + kb * BLK64, &map_do, BAR(1 + st), h * D + kb * 64, si.q_start + qs);
+          tma_load_2d(q_smem + st * C::QS_BYTES + kb * BLK64, &map_q, BAR(A_QF + st), h * D + kb * 64, si.q_start + qs);
+          tma_load_2d(do_smem + st * C::QS_BYTES + kb * BLK64, &map_do, BAR(A_QF + st), h * D + kb * 64, si.q_start + qs);
         }
       }
       if (!ok) {
@@ -210,125 +219,131 @@ flash_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
       constexpr uint32_t idesc_sc = idesc_bf16(128, SUB, false, false);
       constexpr uint32_t idesc_acc = idesc_bf16(128, D, false, true);
       bool ok = mbar_wait(BAR(0), 0, abort_flag);
+      const uint32_t k_lo = desc_lo(k_smem, true, 0), v_lo = desc_lo(v_smem, true, 0);
+      const uint32_t q_lo0 = desc_lo(q_smem, true, 0), do_lo0 = desc_lo(do_smem, true, 0);
+      const uint32_t qmn_lo0 = desc_lo(q_smem, false, BLK64), domn_lo0 = desc_lo(do_smem, false, BLK64);
+      const uint32_t pt_lo0 = desc_lo(pt_smem, true, 0), dst_lo0 = desc_lo(dst_smem, true, 0);
       auto issue_scores = [&](int it) -> bool {
         const int st = it % QDO_STAGES, buf = it & 1;
-        if (!mbar_wait(BAR(1 + st), (it / QDO_STAGES) & 1, abort_flag)) return false;
+        if (!mbar_wait(BAR(A_QF + st), (it / QDO_STAGES) & 1, abort_flag)) return false;
         tc_fence_after();
+        const uint32_t q_lo = q_lo0 + st * (C::QS_BYTES >> 4), do_lo = do_lo0 + st * (C::QS_BYTES >> 4);
+        const uint32_t d_s = tmem_base + buf * SUB, d_dp = tmem_base + 128 + buf * SUB;
 #pragma unroll
-        for (int kb = 0; kb < C::NB; ++kb) {
-          const uint64_t da = smem_desc_sw128(k_smem + kb * BLK128, true, 0);
-          const uint64_t db = smem_desc_sw128(q_smem + st * C::QS_BYTES + kb * BLK64, true, 0);
+        for (int kb = 0; kb < C::NB; ++kb)
 #pragma unroll
-          for (int k = 0; k < 4; ++k) tc_mma(tmem_base + buf * SUB, da + 2 * k, db + 2 * k, idesc_sc, (kb | k) ? 1u : 0u);
-        }
-#pragma unroll
-        for (int kb = 0; kb < C::NB; ++kb) {
-          const uint64_t da = smem_desc_sw128(v_smem + kb * BLK128, true, 0);
-          const uint64_t db = smem_desc_sw128(do_smem + st * C::QS_BYTES + kb * BLK64, true, 0);
-#pragma unroll
-          for (int k = 0; k < 4; ++k) tc_mma(tmem_base + 128 + buf * SUB, da + 2 * k, db + 2 * k, idesc_sc, (kb | k) ? 1u : 0u);
-        }
-        tc_commit(BAR(7 + buf));
+          for (int k = 0; k < 4; ++k) {
+            tc_mma_lo(d_s, k_lo + kb * (BLK128 >> 4) + 2 * k, q_lo + kb * (BLK64 >> 4) + 2 * k, idesc_sc, (kb | k) ? 1u : 0u);
+            tc_mma_lo(d_dp, v_lo + kb * (BLK128 >> 4) + 2 * k, do_lo + kb * (BLK64 >> 4) + 2 * k, idesc_sc, (kb | k) ? 1u : 0u);
+          }
+        tc_commit(BAR(A_SF + buf));
         return true;
       };
       if (ok) ok = issue_scores(0);
       if (ok && n_it > 1) ok = issue_scores(1);
       for (int it = 0; it < n_it && ok; ++it) {
         const int st = it % QDO_STAGES;
-        if (!mbar_wait(BAR(9), it & 1, abort_flag)) { ok = false; break; }
+        const int g = it & 1;
+        if (!mbar_wait(BAR(A_PF + g), (it >> 1) & 1, abort_flag)) { ok = false; break; }
         tc_fence_after();
-        const uint64_t dpt = smem_desc_sw128(pt_smem, true, 0), ddst = smem_desc_sw128(dst_smem, true, 0);
-        const uint64_t ddo = smem_desc_sw128(do_smem + st * C::QS_BYTES, false, BLK64);
-        const uint64_t dq = smem_desc_sw128(q_smem + st * C::QS_BYTES, false, BLK64);
+        const uint32_t pt_lo = pt_lo0 + g * (C::PT_BYTES >> 4), dst_lo = dst_lo0 + g * (C::PT_BYTES >> 4);
+        const uint32_t domn_lo = domn_lo0 + st * (C::QS_BYTES >> 4), qmn_lo = qmn_lo0 + st * (C::QS_BYTES >> 4);
 #pragma unroll
-        for (int k = 0; k < 4; ++k) tc_mma(tmem_dv, dpt + 2 * k, ddo + (uint64_t)(k * 128), idesc_acc, (it | k) ? 1u : 0u);
-#pragma unroll
-        for (int k = 0; k < 4; ++k) tc_mma(tmem_dk, ddst + 2 * k, dq + (uint64_t)(k * 128), idesc_acc, (it | k) ? 1u : 0u);
-        tc_commit(BAR(4 + st));  // Q / dO stage free
-        tc_commit(BAR(10));      // P^T / dS^T consumed, accumulators updated
+        for (int k = 0; k < 4; ++k) {
+          tc_mma_lo(tmem_dv, pt_lo + 2 * k, domn_lo + k * 128, idesc_acc, (it | k) ? 1u : 0u);
+          tc_mma_lo(tmem_dk, dst_lo + 2 * k, qmn_lo + k * 128, idesc_acc, (it | k) ? 1u : 0u);
+        }
+        tc_commit(BAR(A_QE + st));  // Q / dO stage free
+        tc_commit(BAR(A_PE + g));  // this group's P^T / dS^T consumed
         if (it + 2 < n_it && !issue_scores(it + 2)) { ok = false; break; }
       }
+      if (ok) tc_commit(BAR(A_DONE));  // every accumulating MMA has retired
       if (!ok) {
         atomicMax(status, ERR_BWD_MMA);
         *abort_flag = 1;
       }
     }
   } else {
-    const int quarter = warp & 3;
+    // Two groups of four warps; group g takes the sub-tiles it = g, g+2, ... with its own TMEM score buffers and its own
+    // P^T / dS^T tiles, so one group's tcgen05.ld / smem-store / barrier latencies overlap the other group's math.
+    const int quarter = warp & 3, g = (warp - 2) >> 2;
     const int row = quarter * 32 + lane;        // key row of this thread
     const uint32_t t_lane = tmem_base + ((uint32_t)(quarter * 32) << 16);
     const int kidx = k0 + row;
     const bool key_live = kidx < si.k_len;
     const float scale_log2 = scale * LOG2E;
+    const int qmin = causal ? kidx - off : -0x40000000;  // query q sees this key iff q >= kidx - off
+    uint8_t* my_pt = pt_ptr + g * C::PT_BYTES;
+    uint8_t* my_dst = dst_ptr + g * C::PT_BYTES;
     bool ok = true;
-    for (int it = 0; it < n_it; ++it) {
-      const int buf = it & 1;
+    for (int it = g; it < n_it; it += 2) {
       const int h = kvh * G + it / n_sub, qs = q_lo + (it % n_sub) * SUB;
-      ok = __all_sync(0xffffffffu, mbar_wait(BAR(7 + buf), (it >> 1) & 1, abort_flag));
+      ok = __all_sync(0xffffffffu, mbar_wait(BAR(A_SF + g), (it >> 1) & 1, abort_flag));
       if (!ok) break;
       tc_fence_after();
-      uint32_t s[2][32], dp[2][32];
-      tc_ld32(t_lane + buf * SUB, s[0]);
-      tc_ld32(t_lane + buf * SUB + 32, s[1]);
-      tc_ld32(t_lane + 128 + buf * SUB, dp[0]);
-      tc_ld32(t_lane + 128 + buf * SUB + 32, dp[1]);
-      tc_wait_ld();
-      // lse / delta of the 64 query columns come straight from global memory (every lane of the warp reads the same
-      // addresses: one broadcast transaction each, L1-resident across the four row warps)
-      const float* lp = lse + (long long)h * total_q + si.q_start + qs;
-      const float* dlp = delta + (long long)h * total_q + si.q_start + qs;
-      const bool vec = (qs + SUB <= si.q_len) && (((reinterpret_cast<uintptr_t>(lp) | reinterpret_cast<uintptr_t>(dlp)) & 15) == 0);
-      const int qmin = causal ? kidx - off : -0x40000000;  // query q sees this key iff q >= kidx - off
+      const float* lp0 = lse2g + (long long)h * total_q + si.q_start + qs;
+      const float* dlp0 = delta + (long long)h * total_q + si.q_start + qs;
+      const bool vec = (qs + SUB <= si.q_len) && (((reinterpret_cast<uintptr_t>(lp0) | reinterpret_cast<uintptr_t>(dlp0)) & 15) == 0);
+      const bool need_mask = (k0 + 128 > si.k_len) || (causal && qs < k0 + 127 - off);
       uint32_t ppk[32], dpk[32];
 #pragma unroll
-      for (int c2 = 0; c2 < 2; ++c2)
+      for (int half = 0; half < 2; ++half) {
+        uint32_t s[32], dp[32];
+        tc_ld32(t_lane + g * SUB + half * 32, s);
+        tc_ld32(t_lane + 128 + g * SUB + half * 32, dp);
+        tc_wait_ld();
+        const int qc = qs + half * 32;
+        const float* lp = lp0 + half * 32;
+        const float* dlp = dlp0 + half * 32;
 #pragma unroll
         for (int i = 0; i < 32; i += 4) {
-          const int c = c2 * 32 + i;
           float lv[4], dv[4];
           if (vec) {
-            *reinterpret_cast<float4*>(lv) = __ldg(reinterpret_cast<const float4*>(lp + c));
-            *reinterpret_cast<float4*>(dv) = __ldg(reinterpret_cast<const float4*>(dlp + c));
+            *reinterpret_cast<float4*>(lv) = __ldg(reinterpret_cast<const float4*>(lp + i));
+            *reinterpret_cast<float4*>(dv) = __ldg(reinterpret_cast<const float4*>(dlp + i));
           } else {
 #pragma unroll
             for (int e = 0; e < 4; ++e) {
-              const bool in = qs + c + e < si.q_len;
-              lv[e] = in ? __ldg(lp + c + e) : INFINITY;
-              dv[e] = in ? __ldg(dlp + c + e) : 0.f;
+              const bool in = qc + i + e < si.q_len;
+              lv[e] = in ? __ldg(lp + i + e) : INFINITY;
+              dv[e] = in ? __ldg(dlp + i + e) : 0.f;
             }
           }
           float pv[4], dsv[4];
 #pragma unroll
           for (int e = 0; e < 4; ++e) {
-            float pe = ex2(fmaf(__uint_as_float(s[c2][i + e]), scale_log2, -lv[e] * LOG2E));
-            if (!key_live || qs + c + e < qmin) pe = 0.f;
+            float pe = ex2(fmaf(__uint_as_float(s[i + e]), scale_log2, -lv[e]));
+            if (need_mask && (!key_live || qc + i + e < qmin)) pe = 0.f;
             pv[e] = pe;
-            dsv[e] = pe * (__uint_as_float(dp[c2][i + e]) - dv[e]) * scale;
+            dsv[e] = pe * (__uint_as_float(dp[i + e]) - dv[e]);
           }
-          ppk[c >> 1] = pack2(pv[0], pv[1]);
-          ppk[(c >> 1) + 1] = pack2(pv[2], pv[3]);
-          dpk[c >> 1] = pack2(dsv[0], dsv[1]);
-          dpk[(c >> 1) + 1] = pack2(dsv[2], dsv[3]);
+          ppk[half * 16 + (i >> 1)] = pack2(pv[0], pv[1]);
+          ppk[half * 16 + (i >> 1) + 1] = pack2(pv[2], pv[3]);
+          dpk[half * 16 + (i >> 1)] = pack2(dsv[0], dsv[1]);
+          dpk[half * 16 + (i >> 1) + 1] = pack2(dsv[2], dsv[3]);
         }
-      if (it > 0) {
-        ok = __all_sync(0xffffffffu, mbar_wait(BAR(10), (it - 1) & 1, abort_flag));
+      }
+      if (it >= 2) {  // the MMAs that read this group's previous tiles must have retired
+        ok = __all_sync(0xffffffffu, mbar_wait(BAR(A_PE + g), ((it >> 1) - 1) & 1, abort_flag));
         if (!ok) break;
       }
-      store_row64(pt_ptr, row, ppk);
-      store_row64(dst_ptr, row, dpk);
+      store_row64(my_pt, row, ppk);
+      store_row64(my_dst, row, dpk);
       fence_async_smem();
       tc_fence_before();
       __syncwarp();
-      if (lane == 0) mbar_arrive(BAR(9));
+      if (lane == 0) mbar_arrive(BAR(A_PF + g));
     }
     if (ok && n_it > 0) {
-      ok = __all_sync(0xffffffffu, mbar_wait(BAR(10), (n_it - 1) & 1, abort_flag));
+      ok = __all_sync(0xffffffffu, mbar_wait(BAR(A_DONE), 0, abort_flag));
       if (ok) tc_fence_after();
     }
+    const int half = g;  // each group writes half of the accumulator columns
     if (ok) {
       const long long tok = (long long)si.k_start + kidx;
-      store_acc_row<D>(t_lane + 256, dV + tok * dk_row_stride + (long long)kvh * D, key_live, n_it > 0);
-      store_acc_row<D>(t_lane + 384, dK + tok * dk_row_stride + (long long)kvh * D, key_live, n_it > 0);
+      constexpr int CH = D / 64;  // 32-column chunks per half
+      store_acc_row(t_lane + 256, dV + tok * dk_row_stride + (long long)kvh * D, key_live, n_it > 0, half * CH, half * CH + CH, 1.f);
+      store_acc_row(t_lane + 384, dK + tok * dk_row_stride + (long long)kvh * D, key_live, n_it > 0, half * CH, half * CH + CH, scale);
     } else if (lane == 0) {
       atomicMax(status, ERR_BWD_ROWS);
       *abort_flag = 1;
@@ -350,14 +365,14 @@ struct DqCfg {
   static constexpr int Q_BYTES = 128 * D * 2;   // resident Q or dO tile
   static constexpr int KS_BYTES = SUB * D * 2;  // one 64-key K or V stage
   static constexpr int DS_BYTES = 128 * SUB * 2;
-  static constexpr int SMEM = 2 * Q_BYTES + 2 * QDO_STAGES * KS_BYTES + DS_BYTES + 1024 + 256;
+  static constexpr int SMEM = 2 * Q_BYTES + 2 * KV_STAGES_B * KS_BYTES + 2 * DS_BYTES + 1024 + 256;
 };
 
 template <int D>
 __global__ void __launch_bounds__(BWD_THREADS, 1)
 flash_bwd_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_do,
                     const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v,
-                    const float* __restrict__ lse, const float* __restrict__ delta, __nv_bfloat16* __restrict__ dQ,
+                    const float* __restrict__ lse2g, const float* __restrict__ delta, __nv_bfloat16* __restrict__ dQ,
                     const int* __restrict__ cu_q, const int* __restrict__ cu_k, int sq, int sk, int Hq, int Hkv,
                     long long dq_row_stride, long long total_q, float scale, int causal, int* __restrict__ status) {
   using C = DqCfg<D>;
@@ -377,19 +392,18 @@ flash_bwd_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
   uint8_t* aligned = smem_raw + (base - smem_u32(smem_raw));
   const uint32_t q_smem = base, do_smem = base + C::Q_BYTES;
   const uint32_t k_smem = do_smem + C::Q_BYTES;                 // stages
-  const uint32_t v_smem = k_smem + QDO_STAGES * C::KS_BYTES;    // stages
-  const uint32_t ds_smem = v_smem + QDO_STAGES * C::KS_BYTES;
+  const uint32_t v_smem = k_smem + KV_STAGES_B * C::KS_BYTES;    // stages
+  const uint32_t ds_smem = v_smem + KV_STAGES_B * C::KS_BYTES;
   uint8_t* ds_ptr = aligned + (ds_smem - base);
-  uint64_t* bars = reinterpret_cast<uint64_t*>(ds_ptr + C::DS_BYTES);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(ds_ptr + 2 * C::DS_BYTES);
   const uint32_t bar0 = smem_u32(bars);
-  // 0 qdo_full | 1..3 k_full | 4..6 k_empty | 7..9 v_full | 10..12 v_empty | 13,14 s_full | 15 ds_full | 16 ds_empty
   auto BAR = [&](int i) { return bar0 + 8u * i; };
-  uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(bars + 17);
+  uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(bars + B_NBAR);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_holder + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   if (threadIdx.x == 0) {
-    for (int i = 0; i < 17; ++i) mbar_init(BAR(i), i == 15 ? 4 : 1);
+    for (int i = 0; i < B_NBAR; ++i) mbar_init(BAR(i), (i == B_DF || i == B_DF + 1) ? 4 : 1);
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     fence_async_smem();
@@ -415,18 +429,18 @@ flash_bwd_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
       }
       bool ok = true;
       for (int j = 0; j < n_it && ok; ++j) {
-        const int st = j % QDO_STAGES;
-        const uint32_t ph = ((j / QDO_STAGES) & 1) ^ 1u;
-        if (!mbar_wait(BAR(4 + st), ph, abort_flag)) { ok = false; break; }
-        mbar_expect_tx(BAR(1 + st), C::KS_BYTES);
+        const int st = j % KV_STAGES_B;
+        const uint32_t ph = ((j / KV_STAGES_B) & 1) ^ 1u;
+        if (!mbar_wait(BAR(B_KE + st), ph, abort_flag)) { ok = false; break; }
+        mbar_expect_tx(BAR(B_KF + st), C::KS_BYTES);
 #pragma unroll
         for (int kb = 0; kb < C::NB; ++kb)
-          tma_load_2d(k_smem + st * C::KS_BYTES + kb * BLK64, &map_k, BAR(1 + st), kvh * D + kb * 64, si.k_start + j * SUB);
-        if (!mbar_wait(BAR(10 + st), ph, abort_flag)) { ok = false; break; }
-        mbar_expect_tx(BAR(7 + st), C::KS_BYTES);
+          tma_load_2d(k_smem + st * C::KS_BYTES + kb * BLK64, &map_k, BAR(B_KF + st), kvh * D + kb * 64, si.k_start + j * SUB);
+        if (!mbar_wait(BAR(B_VE + st), ph, abort_flag)) { ok = false; break; }
+        mbar_expect_tx(BAR(B_VF + st), C::KS_BYTES);
 #pragma unroll
         for (int kb = 0; kb < C::NB; ++kb)
-          tma_load_2d(v_smem + st * C::KS_BYTES + kb * BLK64, &map_v, BAR(7 + st), kvh * D + kb * 64, si.k_start + j * SUB);
+          tma_load_2d(v_smem + st * C::KS_BYTES + kb * BLK64, &map_v, BAR(B_VF + st), kvh * D + kb * 64, si.k_start + j * SUB);
       }
       if (!ok) {
         atomicMax(status, ERR_BWD_PRODUCER);
@@ -438,101 +452,103 @@ flash_bwd_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
       constexpr uint32_t idesc_sc = idesc_bf16(128, SUB, false, false);
       constexpr uint32_t idesc_acc = idesc_bf16(128, D, false, true);
       bool ok = mbar_wait(BAR(0), 0, abort_flag);
+      const uint32_t q_lo = desc_lo(q_smem, true, 0), do_lo = desc_lo(do_smem, true, 0);
+      const uint32_t k_lo0 = desc_lo(k_smem, true, 0), v_lo0 = desc_lo(v_smem, true, 0);
+      const uint32_t kmn_lo0 = desc_lo(k_smem, false, BLK64), ds_lo0 = desc_lo(ds_smem, true, 0);
       auto issue_scores = [&](int j) -> bool {
-        const int st = j % QDO_STAGES, buf = j & 1;
-        const uint32_t ph = (j / QDO_STAGES) & 1;
-        if (!mbar_wait(BAR(1 + st), ph, abort_flag) || !mbar_wait(BAR(7 + st), ph, abort_flag)) return false;
+        const int st = j % KV_STAGES_B, buf = j & 1;
+        const uint32_t ph = (j / KV_STAGES_B) & 1;
+        if (!mbar_wait(BAR(B_KF + st), ph, abort_flag) || !mbar_wait(BAR(B_VF + st), ph, abort_flag)) return false;
         tc_fence_after();
+        const uint32_t k_lo = k_lo0 + st * (C::KS_BYTES >> 4), v_lo = v_lo0 + st * (C::KS_BYTES >> 4);
+        const uint32_t d_s = tmem_base + buf * SUB, d_dp = tmem_base + 128 + buf * SUB;
 #pragma unroll
-        for (int kb = 0; kb < C::NB; ++kb) {
-          const uint64_t da = smem_desc_sw128(q_smem + kb * BLK128, true, 0);
-          const uint64_t db = smem_desc_sw128(k_smem + st * C::KS_BYTES + kb * BLK64, true, 0);
+        for (int kb = 0; kb < C::NB; ++kb)
 #pragma unroll
-          for (int k = 0; k < 4; ++k) tc_mma(tmem_base + buf * SUB, da + 2 * k, db + 2 * k, idesc_sc, (kb | k) ? 1u : 0u);
-        }
-#pragma unroll
-        for (int kb = 0; kb < C::NB; ++kb) {
-          const uint64_t da = smem_desc_sw128(do_smem + kb * BLK128, true, 0);
-          const uint64_t db = smem_desc_sw128(v_smem + st * C::KS_BYTES + kb * BLK64, true, 0);
-#pragma unroll
-          for (int k = 0; k < 4; ++k) tc_mma(tmem_base + 128 + buf * SUB, da + 2 * k, db + 2 * k, idesc_sc, (kb | k) ? 1u : 0u);
-        }
-        tc_commit(BAR(10 + st));  // V stage free
-        tc_commit(BAR(13 + buf));
+          for (int k = 0; k < 4; ++k) {
+            tc_mma_lo(d_s, q_lo + kb * (BLK128 >> 4) + 2 * k, k_lo + kb * (BLK64 >> 4) + 2 * k, idesc_sc, (kb | k) ? 1u : 0u);
+            tc_mma_lo(d_dp, do_lo + kb * (BLK128 >> 4) + 2 * k, v_lo + kb * (BLK64 >> 4) + 2 * k, idesc_sc, (kb | k) ? 1u : 0u);
+          }
+        tc_commit(BAR(B_VE + st));  // V stage free
+        tc_commit(BAR(B_SF + buf));
         return true;
       };
       if (ok) ok = issue_scores(0);
       if (ok && n_it > 1) ok = issue_scores(1);
       for (int j = 0; j < n_it && ok; ++j) {
-        const int st = j % QDO_STAGES;
-        if (!mbar_wait(BAR(15), j & 1, abort_flag)) { ok = false; break; }
+        const int st = j % KV_STAGES_B;
+        const int g = j & 1;
+        if (!mbar_wait(BAR(B_DF + g), (j >> 1) & 1, abort_flag)) { ok = false; break; }
         tc_fence_after();
-        const uint64_t dds = smem_desc_sw128(ds_smem, true, 0);
-        const uint64_t dk = smem_desc_sw128(k_smem + st * C::KS_BYTES, false, BLK64);
+        const uint32_t ds_lo = ds_lo0 + g * (C::DS_BYTES >> 4), kmn_lo = kmn_lo0 + st * (C::KS_BYTES >> 4);
 #pragma unroll
-        for (int k = 0; k < 4; ++k) tc_mma(tmem_dq, dds + 2 * k, dk + (uint64_t)(k * 128), idesc_acc, (j | k) ? 1u : 0u);
-        tc_commit(BAR(4 + st));  // K stage free
-        tc_commit(BAR(16));      // dS consumed, dQ updated
+        for (int k = 0; k < 4; ++k) tc_mma_lo(tmem_dq, ds_lo + 2 * k, kmn_lo + k * 128, idesc_acc, (j | k) ? 1u : 0u);
+        tc_commit(BAR(B_KE + st));  // K stage free
+        tc_commit(BAR(B_DE + g));  // this group's dS consumed
         if (j + 2 < n_it && !issue_scores(j + 2)) { ok = false; break; }
       }
+      if (ok) tc_commit(BAR(B_DONE));
       if (!ok) {
         atomicMax(status, ERR_BWD_MMA);
         *abort_flag = 1;
       }
     }
   } else {
-    const int quarter = warp & 3;
-    const int row = quarter * 32 + lane;  // query row of this thread
+    const int quarter = warp & 3, g = (warp - 2) >> 2;  // group g takes the key sub-tiles j = g, g+2, ...
+    const int row = quarter * 32 + lane;                // query row of this thread
     const uint32_t t_lane = tmem_base + ((uint32_t)(quarter * 32) << 16);
     const int q_idx = q0 + row;
     const bool q_live = q_idx < si.q_len;
     const long long tok = (long long)si.q_start + q_idx;
-    const float lse2 = q_live ? lse[(long long)h * total_q + tok] * LOG2E : INFINITY;
+    const float lse2 = q_live ? lse2g[(long long)h * total_q + tok] : INFINITY;
     const float dlt = q_live ? delta[(long long)h * total_q + tok] : 0.f;
     const float scale_log2 = scale * LOG2E;
     int limit = si.k_len;
     if (causal) limit = min(limit, q_idx + off + 1);
+    uint8_t* my_ds = ds_ptr + g * C::DS_BYTES;
     bool ok = true;
-    for (int j = 0; j < n_it; ++j) {
-      const int buf = j & 1;
-      ok = __all_sync(0xffffffffu, mbar_wait(BAR(13 + buf), (j >> 1) & 1, abort_flag));
+    for (int j = g; j < n_it; j += 2) {
+      ok = __all_sync(0xffffffffu, mbar_wait(BAR(B_SF + g), (j >> 1) & 1, abort_flag));
       if (!ok) break;
       tc_fence_after();
-      uint32_t s[2][32], dp[2][32];
-      tc_ld32(t_lane + buf * SUB, s[0]);
-      tc_ld32(t_lane + buf * SUB + 32, s[1]);
-      tc_ld32(t_lane + 128 + buf * SUB, dp[0]);
-      tc_ld32(t_lane + 128 + buf * SUB + 32, dp[1]);
-      tc_wait_ld();
-      const int kbase = j * SUB;
+      const bool need_mask = (j * SUB + SUB > si.k_len) || (causal && j * SUB + SUB - 1 > q0 + off);
       uint32_t dpk[32];
 #pragma unroll
-      for (int c2 = 0; c2 < 2; ++c2)
+      for (int half = 0; half < 2; ++half) {
+        uint32_t s[32], dp[32];
+        tc_ld32(t_lane + g * SUB + half * 32, s);
+        tc_ld32(t_lane + 128 + g * SUB + half * 32, dp);
+        tc_wait_ld();
+        const int kbase = j * SUB + half * 32;
 #pragma unroll
         for (int i = 0; i < 32; i += 2) {
-          const int c = c2 * 32 + i;
-          float p0 = ex2(fmaf(__uint_as_float(s[c2][i]), scale_log2, -lse2));
-          float p1 = ex2(fmaf(__uint_as_float(s[c2][i + 1]), scale_log2, -lse2));
-          if (kbase + c >= limit) p0 = 0.f;
-          if (kbase + c + 1 >= limit) p1 = 0.f;
-          dpk[c >> 1] = pack2(p0 * (__uint_as_float(dp[c2][i]) - dlt) * scale, p1 * (__uint_as_float(dp[c2][i + 1]) - dlt) * scale);
+          float p0 = ex2(fmaf(__uint_as_float(s[i]), scale_log2, -lse2));
+          float p1 = ex2(fmaf(__uint_as_float(s[i + 1]), scale_log2, -lse2));
+          if (need_mask) {
+            if (kbase + i >= limit) p0 = 0.f;
+            if (kbase + i + 1 >= limit) p1 = 0.f;
+          }
+          dpk[half * 16 + (i >> 1)] = pack2(p0 * (__uint_as_float(dp[i]) - dlt), p1 * (__uint_as_float(dp[i + 1]) - dlt));
         }
-      if (j > 0) {
-        ok = __all_sync(0xffffffffu, mbar_wait(BAR(16), (j - 1) & 1, abort_flag));
+      }
+      if (j >= 2) {
+        ok = __all_sync(0xffffffffu, mbar_wait(BAR(B_DE + g), ((j >> 1) - 1) & 1, abort_flag));
         if (!ok) break;
       }
-      store_row64(ds_ptr, row, dpk);
+      store_row64(my_ds, row, dpk);
       fence_async_smem();
       tc_fence_before();
       __syncwarp();
-      if (lane == 0) mbar_arrive(BAR(15));
+      if (lane == 0) mbar_arrive(BAR(B_DF + g));
     }
     if (ok && n_it > 0) {
-      ok = __all_sync(0xffffffffu, mbar_wait(BAR(16), (n_it - 1) & 1, abort_flag));
+      ok = __all_sync(0xffffffffu, mbar_wait(BAR(B_DONE), 0, abort_flag));
       if (ok) tc_fence_after();
     }
+    const int half = g;
     if (ok) {
-      store_acc_row<D>(t_lane + 256, dQ + tok * dq_row_stride + (long long)h * D, q_live, n_it > 0);
+      constexpr int CH = D / 64;
+      store_acc_row(t_lane + 256, dQ + tok * dq_row_stride + (long long)h * D, q_live, n_it > 0, half * CH, half * CH + CH, scale);
     } else if (lane == 0) {
       atomicMax(status, ERR_BWD_ROWS);
       *abort_flag = 1;
@@ -572,14 +588,15 @@ int launch_bwd(const void* q, const void* k, const void* v, const void* out, con
     configured = true;
   }
   const long long warps = total_q * Hq;
+  float* lse2 = delta + total_q * Hq;  // second half of the scratch: lse in log2 units
   flash_delta_kernel<D><<<(unsigned)((warps * 32 + 255) / 256), 256, 0, st>>>(
-      (const __nv_bfloat16*)dout, (const __nv_bfloat16*)out, delta, total_q, Hq, do_rs, o_rs);
+      (const __nv_bfloat16*)dout, (const __nv_bfloat16*)out, lse, delta, lse2, total_q, Hq, do_rs, o_rs);
   const dim3 grid_a((max_k + 127) / 128, Hkv, batch);
-  kern_a<<<grid_a, BWD_THREADS, DkvCfg<D>::SMEM, st>>>(mq64, mdo64, mk128, mv128, lse, delta, (__nv_bfloat16*)dk,
+  kern_a<<<grid_a, BWD_THREADS, DkvCfg<D>::SMEM, st>>>(mq64, mdo64, mk128, mv128, lse2, delta, (__nv_bfloat16*)dk,
                                                        (__nv_bfloat16*)dv, cu_q, cu_k, sq, sk, Hq, Hkv, dk_rs, total_q,
                                                        scale, causal ? 1 : 0, status);
   const dim3 grid_b((max_q + 127) / 128, Hq, batch);
-  kern_b<<<grid_b, BWD_THREADS, DqCfg<D>::SMEM, st>>>(mq128, mdo128, mk64, mv64, lse, delta, (__nv_bfloat16*)dq, cu_q,
+  kern_b<<<grid_b, BWD_THREADS, DqCfg<D>::SMEM, st>>>(mq128, mdo128, mk64, mv64, lse2, delta, (__nv_bfloat16*)dq, cu_q,
                                                       cu_k, sq, sk, Hq, Hkv, dq_rs, total_q, scale, causal ? 1 : 0, status);
   return cudaGetLastError() == cudaSuccess ? 0 : -5;
 }

@@ -140,18 +140,19 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
       constexpr uint32_t idesc_s = idesc_bf16(128, 128, false, false);
       constexpr uint32_t idesc_pv = idesc_bf16(128, D, false, true);
       bool ok = mbar_wait(BAR(0), 0, abort_flag);
+      const uint32_t q_lo = desc_lo(q_smem, true, 0), k_lo0 = desc_lo(k_smem, true, 0);
+      const uint32_t p_lo = desc_lo(p_smem, true, 0), v_lo0 = desc_lo(v_smem, false, BLK_BYTES);
       auto issue_s = [&](int j) -> bool {
         const int st = j & 1;
         if (!mbar_wait(BAR(1 + st), (j >> 1) & 1, abort_flag)) return false;
         tc_fence_after();
         const uint32_t d = tmem_base + (uint32_t)(j & 1) * 128;
+        const uint32_t k_lo = k_lo0 + st * (C::TILE_BYTES >> 4);
 #pragma unroll
-        for (int kb = 0; kb < C::NB; ++kb) {
-          const uint64_t da = smem_desc_sw128(q_smem + kb * BLK_BYTES, true, 0);
-          const uint64_t db = smem_desc_sw128(k_smem + st * C::TILE_BYTES + kb * BLK_BYTES, true, 0);
+        for (int kb = 0; kb < C::NB; ++kb)
 #pragma unroll
-          for (int k = 0; k < 4; ++k) tc_mma(d, da + 2 * k, db + 2 * k, idesc_s, (kb | k) ? 1u : 0u);
-        }
+          for (int k = 0; k < 4; ++k)
+            tc_mma_lo(d, q_lo + kb * (BLK_BYTES >> 4) + 2 * k, k_lo + kb * (BLK_BYTES >> 4) + 2 * k, idesc_s, (kb | k) ? 1u : 0u);
         tc_commit(BAR(3 + st));        // K stage free
         tc_commit(BAR(9 + (j & 1)));   // scores ready
         return true;
@@ -162,12 +163,10 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
         const int st = j & 1;
         if (!mbar_wait(BAR(11), j & 1, abort_flag) || !mbar_wait(BAR(5 + st), (j >> 1) & 1, abort_flag)) { ok = false; break; }
         tc_fence_after();
-        const uint64_t dv = smem_desc_sw128(v_smem + st * C::TILE_BYTES, false, BLK_BYTES);
+        const uint32_t v_lo = v_lo0 + st * (C::TILE_BYTES >> 4);
 #pragma unroll
-        for (int k = 0; k < 8; ++k) {
-          const uint64_t dp = smem_desc_sw128(p_smem + (k >> 2) * BLK_BYTES, true, 0) + 2 * (k & 3);
-          tc_mma(tmem_o, dp, dv + (uint64_t)(k * 128), idesc_pv, (j | k) ? 1u : 0u);
-        }
+        for (int k = 0; k < 8; ++k)
+          tc_mma_lo(tmem_o, p_lo + (k >> 2) * (BLK_BYTES >> 4) + 2 * (k & 3), v_lo + k * 128, idesc_pv, (j | k) ? 1u : 0u);
         tc_commit(BAR(7 + st));  // V stage free
         tc_commit(BAR(12));      // P consumed, O updated
       }
@@ -204,11 +203,12 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
           for (int i = 0; i < 32; ++i)
             if (k0 + c * 32 + i >= limit) s[c][i] = __float_as_uint(-INFINITY);
       }
-      float mx = -INFINITY;
+      float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};  // one chain per chunk: a single warp needs the ILP
 #pragma unroll
-      for (int c = 0; c < 4; ++c)
+      for (int i = 0; i < 32; ++i)
 #pragma unroll
-        for (int i = 0; i < 32; ++i) mx = fmaxf(mx, __uint_as_float(s[c][i]));
+        for (int c = 0; c < 4; ++c) mx4[c] = fmaxf(mx4[c], __uint_as_float(s[c][i]));
+      const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
       const float m_new = fmaxf(m_run, mx * scale_log2);
       const bool grow = __any_sync(0xffffffffu, m_new > m_run + 8.f);
       float alpha = 1.f, m_use = m_run;
@@ -217,18 +217,19 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
         alpha = (m_run == -INFINITY) ? 0.f : ex2(m_run - m_new);
       }
       const float m_safe = (m_use == -INFINITY) ? 0.f : m_use;
-      float rowsum = 0.f;
+      float rs4[4] = {0.f, 0.f, 0.f, 0.f};
       uint32_t pk[64];
 #pragma unroll
-      for (int c = 0; c < 4; ++c)
+      for (int i = 0; i < 32; i += 2)
 #pragma unroll
-        for (int i = 0; i < 32; i += 2) {
+        for (int c = 0; c < 4; ++c) {
           const float p0 = ex2(fmaf(__uint_as_float(s[c][i]), scale_log2, -m_safe));
           const float p1 = ex2(fmaf(__uint_as_float(s[c][i + 1]), scale_log2, -m_safe));
-          rowsum += p0 + p1;
+          rs4[c] += p0 + p1;
           const __nv_bfloat162 hh = __floats2bfloat162_rn(p0, p1);
           pk[c * 16 + (i >> 1)] = *reinterpret_cast<const uint32_t*>(&hh);
         }
+      const float rowsum = (rs4[0] + rs4[1]) + (rs4[2] + rs4[3]);
       if (j > 0) {  // PV(j-1) must have read P and updated O before either is touched
         ok = __all_sync(0xffffffffu, mbar_wait(BAR(12), (j - 1) & 1, abort_flag));
         if (!ok) break;

@@ -64,7 +64,7 @@ int flash_fwd(const void* q, const void* k, const void* v, void* out, float* lse
               bool causal, int* status, cudaStream_t st);
 
 // Flash attention backward (flash_bwd.cu): dq [total_q,Hq,D], dk/dv [total_k,Hkv,D] bf16; `delta` is fp32 scratch
-// [Hq, total_q]; lse as written by flash_fwd.  Three launches: row-dot pre-pass, dK/dV kernel, dQ kernel.
+// [2, Hq, total_q]; lse as written by flash_fwd.  Three launches: row-dot pre-pass, dK/dV kernel, dQ kernel.
 int flash_bwd(const void* q, const void* k, const void* v, const void* out, const void* dout, const float* lse,
               float* delta, void* dq, void* dk, void* dv, const int* cu_q, const int* cu_k, int batch, int sq, int sk,
               int max_q, int max_k, long long total_q, long long total_k, int Hq, int Hkv, int D, long long q_rs,

@@ -113,6 +113,25 @@ __host__ __device__ constexpr uint32_t idesc_bf16(int M, int N, bool a_mn_major,
          ((uint32_t)(N >> 3) << 17) | ((uint32_t)(M >> 4) << 24);
 }
 
+// Lean MMA issue.  One thread issues every tcgen05.mma of a CTA, and for tiles narrower than N = 256 the tensor core
+// finishes an instruction faster than a dependent chain of ~20 scalar instructions can prepare the next one, so the
+// descriptor arithmetic per instruction is kept to one 32-bit add per operand: a 128B-swizzle descriptor is
+// {lo, DESC_HI} with lo = (smem address >> 4) | (LBO field << 16), and advancing inside a tile only changes lo.
+constexpr uint32_t DESC_HI = (1024u >> 4) | (1u << 14) | (2u << 29);
+__device__ __forceinline__ uint32_t desc_lo(uint32_t saddr, bool kmajor, uint32_t lbo_bytes) {
+  return ((saddr & 0x3FFFFu) >> 4) | ((kmajor ? 1u : (lbo_bytes >> 4)) << 16);
+}
+__device__ __forceinline__ void tc_mma_lo(uint32_t d_tmem, uint32_t a_lo, uint32_t b_lo, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t.reg .b64 da, db;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "mov.b64 da, {%1, %5};\n\t"
+      "mov.b64 db, {%2, %5};\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %3, {%6, %6, %6, %6}, p;\n\t}" ::"r"(d_tmem),
+      "r"(a_lo), "r"(b_lo), "r"(idesc), "r"(accumulate), "r"(DESC_HI), "r"(0u)
+      : "memory");
+}
+
 
 // ---- cluster helpers (2-CTA kernels)
 __device__ __forceinline__ uint32_t cluster_ctarank() {
