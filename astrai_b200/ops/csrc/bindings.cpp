@@ -399,6 +399,65 @@ void comm_wait_flags_(const Tensor& local_flags, int64_t kind, int64_t world, in
   TORCH_CHECK(rc == 0, "comm_wait_flags launch failed with code ", rc);
 }
 
+// ---- tensor-parallel fused GEMMs.  Pointer lists: the same symmetric buffer on every rank.
+void fill_ptrs(void* (&dst)[8], const std::vector<int64_t>& src) {
+  TORCH_CHECK(src.size() >= 1 && src.size() <= 8, "peer pointer list must have 1..8 entries");
+  for (size_t i = 0; i < 8; ++i) dst[i] = i < src.size() ? reinterpret_cast<void*>(src[i]) : nullptr;
+}
+
+void tp_gemm_allgather_(std::vector<int64_t> xfull_ptrs, const Tensor& W, bool w_kmajor, Tensor& Y, std::vector<int64_t> flag_ptrs,
+                        Tensor& chunk_flags, Tensor& chunk_counter, int64_t rank, int64_t unit, int64_t max_units,
+                        int64_t epoch, double timeout_s, int64_t n_copy_ctas) {
+  CHECK_CUDA_CONTIG(W);
+  CHECK_CUDA_CONTIG(Y);
+  TORCH_CHECK(W.scalar_type() == at::kBFloat16 && Y.scalar_type() == at::kBFloat16 && W.dim() == 2 && Y.dim() == 2, "tp_gemm_allgather_: bf16 2-D");
+  TORCH_CHECK(chunk_flags.scalar_type() == at::kInt && chunk_flags.numel() >= 8 && chunk_counter.scalar_type() == at::kInt && chunk_counter.numel() >= 8, "tp_gemm_allgather_: int32[8] flags / counters");
+  const int64_t N = w_kmajor ? W.size(0) : W.size(1), K = w_kmajor ? W.size(1) : W.size(0);
+  TORCH_CHECK(Y.size(1) == N, "tp_gemm_allgather_: output columns must match the weight");
+  ab::TpGemmParams p{};
+  p.world = (int)xfull_ptrs.size(); p.rank = (int)rank; p.unit = (int)unit; p.max_units = (int)max_units; p.epoch = (int)epoch;
+  p.n_copy_ctas = (int)n_copy_ctas; p.timeout_ns = (unsigned long long)(timeout_s * 1e9);
+  fill_ptrs(p.flags, flag_ptrs); fill_ptrs(p.x_full, xfull_ptrs);
+  p.chunk_flags = chunk_flags.data_ptr<int>(); p.chunk_counter = chunk_counter.data_ptr<int>();
+  const c10::cuda::CUDAGuard guard(W.device());
+  count();
+  const int rc = ab::gemm_allgather(W.data_ptr(), w_kmajor, Y.data_ptr(), (int)Y.size(0), (int)N, (int)K, Y.stride(0), p,
+                                    status_tensor(W.device()).data_ptr<int>(), stream());
+  TORCH_CHECK(rc == 0, "gemm_allgather launch failed with code ", rc, " (-2: M must be a multiple of world*128, N of 32, K of 8)");
+}
+
+void tp_gemm_reducescatter_(const Tensor& X, const Tensor& W, bool w_kmajor, std::vector<int64_t> stage_ptrs, Tensor& out,
+                            std::vector<int64_t> flag_ptrs, Tensor& tile_counter, int64_t rank, int64_t unit,
+                            int64_t max_units, int64_t epoch, double timeout_s, bool fuse_reduce) {
+  CHECK_CUDA_CONTIG(X);
+  CHECK_CUDA_CONTIG(W);
+  CHECK_CUDA_CONTIG(out);
+  TORCH_CHECK(X.scalar_type() == at::kBFloat16 && W.scalar_type() == at::kBFloat16 && out.scalar_type() == at::kBFloat16, "tp_gemm_reducescatter_: bf16");
+  const int64_t N = w_kmajor ? W.size(0) : W.size(1), K = w_kmajor ? W.size(1) : W.size(0);
+  TORCH_CHECK(X.dim() == 2 && W.dim() == 2 && X.size(1) == K, "tp_gemm_reducescatter_: inner dimensions differ");
+  TORCH_CHECK(tile_counter.scalar_type() == at::kInt && tile_counter.numel() >= 8, "tp_gemm_reducescatter_: int32[8] counter");
+  ab::TpGemmParams p{};
+  p.world = (int)stage_ptrs.size(); p.rank = (int)rank; p.unit = (int)unit; p.max_units = (int)max_units; p.epoch = (int)epoch;
+  p.fuse_reduce = fuse_reduce ? 1 : 0; p.timeout_ns = (unsigned long long)(timeout_s * 1e9);
+  TORCH_CHECK(out.size(0) * p.world == X.size(0) && out.size(1) == N, "tp_gemm_reducescatter_: output must be [M/world, N]");
+  fill_ptrs(p.flags, flag_ptrs); fill_ptrs(p.stage, stage_ptrs);
+  p.rs_out = out.data_ptr(); p.tile_counter = tile_counter.data_ptr<int>();
+  const c10::cuda::CUDAGuard guard(X.device());
+  count();
+  const int rc = ab::gemm_reducescatter(X.data_ptr(), W.data_ptr(), w_kmajor, (int)X.size(0), (int)N, (int)K, p,
+                                        status_tensor(X.device()).data_ptr<int>(), stream());
+  TORCH_CHECK(rc == 0, "gemm_reducescatter launch failed with code ", rc, " (-2: M must be a multiple of world*128, N of 32, K of 8)");
+}
+
+void tp_reduce_(const Tensor& stage, Tensor& out, int64_t world) {
+  CHECK_CUDA_CONTIG(stage);
+  CHECK_CUDA_CONTIG(out);
+  TORCH_CHECK(stage.scalar_type() == at::kBFloat16 && out.scalar_type() == at::kBFloat16 && stage.numel() == out.numel() * world, "tp_reduce_: stage must hold `world` slots of out");
+  const c10::cuda::CUDAGuard guard(out.device());
+  count();
+  TORCH_CHECK(ab::tp_reduce(stage.data_ptr(), out.data_ptr(), out.size(0), (int)out.size(1), (int)world, stream()) == 0, "tp_reduce launch failed");
+}
+
 void kernel_status_reset(const Tensor& like) { status_tensor(like.device()).zero_(); }
 
 }  // namespace
@@ -428,5 +487,8 @@ TORCH_LIBRARY(astrai_b200, m) {
   m.def("kernel_status_reset(Tensor like) -> ()", &kernel_status_reset);
   m.def("flash_fwd(Tensor q, Tensor k, Tensor v, Tensor? cu_q, Tensor? cu_k, int batch, int sq, int sk, int max_q, bool causal, float scale) -> (Tensor, Tensor)", &flash_fwd);
   m.def("flash_bwd(Tensor q, Tensor k, Tensor v, Tensor out, Tensor dout, Tensor lse, Tensor? cu_q, Tensor? cu_k, int batch, int sq, int sk, int max_q, int max_k, bool causal, float scale) -> (Tensor, Tensor, Tensor)", &flash_bwd);
+  m.def("tp_gemm_allgather_(int[] xfull_ptrs, Tensor W, bool w_kmajor, Tensor(a!) Y, int[] flag_ptrs, Tensor(b!) chunk_flags, Tensor(c!) chunk_counter, int rank, int unit, int max_units, int epoch, float timeout_s, int n_copy_ctas) -> ()", &tp_gemm_allgather_);
+  m.def("tp_gemm_reducescatter_(Tensor X, Tensor W, bool w_kmajor, int[] stage_ptrs, Tensor(a!) out, int[] flag_ptrs, Tensor(b!) tile_counter, int rank, int unit, int max_units, int epoch, float timeout_s, bool fuse_reduce) -> ()", &tp_gemm_reducescatter_);
+  m.def("tp_reduce_(Tensor stage, Tensor(a!) out, int world) -> ()", &tp_reduce_);
   m.def("gemm(Tensor A, Tensor B, Tensor? D, bool a_kmajor, bool b_kmajor, bool out_f32, bool accumulate) -> Tensor", &gemm);
 }

@@ -90,4 +90,26 @@ int fsdp_adamw_allgather(const CommPeers& params, void* mc_params, const CommPee
 int comm_wait_flags(const int* local_flags, int kind, int world, int skip_rank, int unit, int max_units, int epoch,
                     unsigned long long timeout_ns, int* status, cudaStream_t st);
 
+// ---- tensor-parallel GEMMs fused with their collective (gemm_comm.cu)
+struct TpGemmParams {
+  int world, rank, unit, max_units, epoch, n_copy_ctas, fuse_reduce;
+  unsigned long long timeout_ns;
+  void* flags[8];        // flag array of every rank ([kind][8][max_units] int32)
+  void* x_full[8];       // all-gather: the [M, K] activation buffer of every rank (rank r owns row block r of its own)
+  int* chunk_flags;      // all-gather, local int[8]: epoch at which block r landed in the local buffer
+  int* chunk_counter;    // all-gather, local int[8]: copy CTAs finished per block (self-resetting)
+  void* stage[8];        // reduce-scatter: staging buffer of every rank, [world][M/world, N] bf16
+  void* rs_out;          // reduce-scatter: local result [M/world, N] bf16 (written by the fused reduce phase)
+  int* tile_counter;     // reduce-scatter, local int[8]: epilogue-warp arrivals per destination (cleared at launch)
+};
+// Y[M, N] = X_full[M, K] * op(W) where row block r of X_full is pulled from rank r inside the kernel.
+// W is stored [N, K] (w_kmajor) or [K, N]; both contiguous.
+int gemm_allgather(const void* W, bool w_kmajor, void* Y, int M, int N, int K, long long ldy, const TpGemmParams& p,
+                   int* status, cudaStream_t st);
+// Partial product X[M, K] * op(W) scattered to the owners of its row blocks and (fuse_reduce) summed there.
+int gemm_reducescatter(const void* X, const void* W, bool w_kmajor, int M, int N, int K, const TpGemmParams& p,
+                       int* status, cudaStream_t st);
+// out[rows, N] = sum over the `world` slots of stage[world][rows, N].
+int tp_reduce(const void* stage, void* out, long long rows, int N, int world, cudaStream_t st);
+
 }  // namespace ab

@@ -34,3 +34,5 @@ class KVCache:
     q_lens: Optional[List[int]] = None
     kv_lens: Optional[List[int]] = None
     decode_splits: int = 0
+    # prefill: slot of every cached + new key of the batch, request after request (the gather index of the flash path)
+    kv_gather_loc: Optional[Tensor] = None

@@ -2,8 +2,9 @@
 
 Packed layout: ``q [T, Hq, D]``, ``k / v [T, Hkv, D]`` where the batch is concatenated along ``T``.
 * ``fwd="decode"`` (one new token per request): the split-KV paged kernel (``paged_attention.cu``) on CUDA;
-* ``fwd="prefill"`` (ragged, possibly with a cached prefix): per-request attention over K/V gathered from the pool with
-  a lower-right aligned causal mask.  This path currently calls the library SDPA kernel per request group.
+* ``fwd="prefill"`` (ragged, possibly with a cached prefix): K/V of the whole batch are gathered from the pool into
+  packed tensors and ONE varlen launch of the tcgen05 flash kernel (``flash_fwd.cu``, lower-right aligned causal
+  mask) serves every request; head dims other than 64 / 128 and explicit masks take a per-request SDPA loop.
 The CPU statement of both is the same gather + softmax and is what the tests compare against
 (semantics of ``TorchNativeBackend`` in the reference, ``astrai/extension/backend/attention.py:443-498``).
 """
@@ -16,7 +17,7 @@ import torch
 import torch.nn.functional as F
 from torch import Tensor
 
-from astrai_b200.ops import native
+from astrai_b200.ops import flash, native
 from astrai_b200.ops.kv import KVCache
 
 
@@ -96,6 +97,14 @@ def cached_attention(q: Tensor, k: Tensor, v: Tensor, kv_cache: KVCache, layer_i
             kv_cache.decode_counters, out)
         return out
     q_lens, kv_lens = _lens(kv_cache)
+    if (attn_mask is None and fwd == "prefill" and kv_cache.kv_gather_loc is not None and kv_cache.qo_indptr is not None
+            and flash.supported(q, kv_cache.k_buffer[layer_id], kv_cache.v_buffer[layer_id])):
+        # ragged prefill on the tcgen05 flash kernel: gather this batch's keys / values from the pool (cached prefix
+        # included) into packed tensors once, then one varlen launch with lower-right aligned causal masking
+        kk = kv_cache.k_buffer[layer_id].index_select(0, kv_cache.kv_gather_loc)
+        vv = kv_cache.v_buffer[layer_id].index_select(0, kv_cache.kv_gather_loc)
+        return flash.flash_attention_varlen(q, kk, vv, kv_cache.qo_indptr, kv_cache.kv_indptr, max(q_lens), max(kv_lens),
+                                            causal=True, scale=scale)
     rows = kv_cache.req_pool_indices.tolist()
     outs, start = [], 0
     for i, (ql, kl) in enumerate(zip(q_lens, kv_lens)):

@@ -44,3 +44,14 @@ def test_fused_p2p_fsdp_matches_nccl_fsdp(tmp_path):
     for x, y in zip(a["norms"], b["norms"]):
         assert abs(x - y) / max(abs(x), 1e-6) < 2e-2, (a, b)
     assert abs(a["checksum"] - b["checksum"]) / a["checksum"] < 1e-3
+
+
+def test_fused_tensor_parallel_mlp_matches_nccl(tmp_path):
+    _need_gpus(2)
+    out = str(tmp_path / "tp.json")
+    _torchrun(2, os.path.join(ROOT, "tests", "workers", "tp_compare.py"), ["--out", out], 29640)
+    for rank_res in json.load(open(out)):
+        assert rank_res["status"] == 0
+        for key in ("y", "dx", "d_gate_up", "d_down"):
+            assert rank_res[key] < 3e-2, rank_res
+        assert rank_res["y_vs_fp32"] < 5e-2, rank_res
