@@ -458,6 +458,44 @@ void tp_reduce_(const Tensor& stage, Tensor& out, int64_t world) {
   TORCH_CHECK(ab::tp_reduce(stage.data_ptr(), out.data_ptr(), out.size(0), (int)out.size(1), (int)world, stream()) == 0, "tp_reduce launch failed");
 }
 
+// ---- fp8
+bool is_e5m2(const Tensor& t) {
+  TORCH_CHECK(t.scalar_type() == at::kFloat8_e4m3fn || t.scalar_type() == at::kFloat8_e5m2, "expected a float8 tensor");
+  return t.scalar_type() == at::kFloat8_e5m2;
+}
+
+std::tuple<Tensor, Tensor, Tensor> fp8_quantize(const Tensor& x, const Tensor& scale, bool e5m2, bool with_transpose) {
+  TORCH_CHECK(x.is_cuda() && x.dim() == 2 && x.scalar_type() == at::kBFloat16 && x.stride(1) == 1, "fp8_quantize: 2-D bf16 input with unit column stride");
+  TORCH_CHECK(scale.is_cuda() && scale.scalar_type() == at::kFloat && scale.numel() == 1, "fp8_quantize: scale is one fp32 value on the device");
+  const c10::cuda::CUDAGuard guard(x.device());
+  const auto dt = e5m2 ? at::kFloat8_e5m2 : at::kFloat8_e4m3fn;
+  Tensor q = at::empty({x.size(0), x.size(1)}, x.options().dtype(dt));
+  Tensor qt = with_transpose ? at::empty({x.size(1), x.size(0)}, x.options().dtype(dt)) : at::empty({0}, x.options().dtype(dt));
+  Tensor amax = at::zeros({1}, x.options().dtype(at::kFloat));
+  count();
+  const int rc = ab::fp8_quantize(x.data_ptr(), q.data_ptr(), with_transpose ? qt.data_ptr() : nullptr, scale.data_ptr<float>(),
+                                  amax.data_ptr<float>(), (int)x.size(0), (int)x.size(1), x.stride(0), e5m2, stream());
+  TORCH_CHECK(rc == 0, "fp8_quantize launch failed with code ", rc);
+  return {q, qt, amax};
+}
+
+Tensor fp8_gemm(const Tensor& a, const Tensor& b, const Tensor& scale_a, const Tensor& scale_b, const c10::optional<Tensor>& bias) {
+  CHECK_CUDA_CONTIG(a);
+  CHECK_CUDA_CONTIG(b);
+  TORCH_CHECK(a.dim() == 2 && b.dim() == 2 && a.size(1) == b.size(1), "fp8_gemm: A [M,K], B [N,K]");
+  TORCH_CHECK(a.size(1) % 16 == 0, "fp8_gemm: K must be a multiple of 16");
+  TORCH_CHECK(scale_a.scalar_type() == at::kFloat && scale_b.scalar_type() == at::kFloat && scale_a.numel() == 1 && scale_b.numel() == 1, "fp8_gemm: per-tensor fp32 scales");
+  if (bias.has_value()) TORCH_CHECK(bias->scalar_type() == at::kBFloat16 && bias->numel() == b.size(0) && bias->is_contiguous(), "fp8_gemm: bf16 bias [N]");
+  const c10::cuda::CUDAGuard guard(a.device());
+  Tensor out = at::empty({a.size(0), b.size(0)}, a.options().dtype(at::kBFloat16));
+  count();
+  const int rc = ab::gemm_fp8(a.data_ptr(), b.data_ptr(), out.data_ptr(), scale_a.data_ptr<float>(), scale_b.data_ptr<float>(),
+                              bias.has_value() ? bias->data_ptr() : nullptr, (int)a.size(0), (int)b.size(0), (int)a.size(1),
+                              out.stride(0), is_e5m2(a), is_e5m2(b), status_tensor(a.device()).data_ptr<int>(), stream());
+  TORCH_CHECK(rc == 0, "gemm_fp8 launch failed with code ", rc);
+  return out;
+}
+
 void kernel_status_reset(const Tensor& like) { status_tensor(like.device()).zero_(); }
 
 }  // namespace
@@ -490,5 +528,7 @@ TORCH_LIBRARY(astrai_b200, m) {
   m.def("tp_gemm_allgather_(int[] xfull_ptrs, Tensor W, bool w_kmajor, Tensor(a!) Y, int[] flag_ptrs, Tensor(b!) chunk_flags, Tensor(c!) chunk_counter, int rank, int unit, int max_units, int epoch, float timeout_s, int n_copy_ctas) -> ()", &tp_gemm_allgather_);
   m.def("tp_gemm_reducescatter_(Tensor X, Tensor W, bool w_kmajor, int[] stage_ptrs, Tensor(a!) out, int[] flag_ptrs, Tensor(b!) tile_counter, int rank, int unit, int max_units, int epoch, float timeout_s, bool fuse_reduce) -> ()", &tp_gemm_reducescatter_);
   m.def("tp_reduce_(Tensor stage, Tensor(a!) out, int world) -> ()", &tp_reduce_);
+  m.def("fp8_quantize(Tensor x, Tensor scale, bool e5m2, bool with_transpose) -> (Tensor, Tensor, Tensor)", &fp8_quantize);
+  m.def("fp8_gemm(Tensor a, Tensor b, Tensor scale_a, Tensor scale_b, Tensor? bias) -> Tensor", &fp8_gemm);
   m.def("gemm(Tensor A, Tensor B, Tensor? D, bool a_kmajor, bool b_kmajor, bool out_f32, bool accumulate) -> Tensor", &gemm);
 }

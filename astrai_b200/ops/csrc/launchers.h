@@ -112,4 +112,12 @@ int gemm_reducescatter(const void* X, const void* W, bool w_kmajor, int M, int N
 // out[rows, N] = sum over the `world` slots of stage[world][rows, N].
 int tp_reduce(const void* stage, void* out, long long rows, int N, int world, cudaStream_t st);
 
+// ---- fp8 (gemm_fp8.cu).  q = x / *scale (saturating) as E4M3 or E5M2; `qt` (may be null) receives the transposed
+// tensor [cols, rows]; `amax` (may be null, must start at 0) receives max|x|.
+int fp8_quantize(const void* x, void* q, void* qt, const float* scale, float* amax, int rows, int cols, long long ldx,
+                 bool e5m2, cudaStream_t st);
+// D[M,N] bf16 = (A[M,K] . B[N,K]^T) * *scale_a * *scale_b (+ bias[N] bf16); A, B fp8, K a multiple of 16.
+int gemm_fp8(const void* A, const void* B, void* D, const float* scale_a, const float* scale_b, const void* bias, int M,
+             int N, int K, long long ldd, bool a_e5m2, bool b_e5m2, int* status, cudaStream_t st);
+
 }  // namespace ab

@@ -106,6 +106,10 @@ class _LinearFn(Function):
 
 def linear(x: Tensor, weight: Tensor, bias: Optional[Tensor] = None, grad_owner=None) -> Tensor:
     """``x @ weight.T (+ bias)``.  ``grad_owner`` overrides where the wgrad kernel looks for ``main_grad``."""
+    from astrai_b200.ops import fp8
+
+    if fp8.autocast_state().enabled and (fp8.eligible(x, weight) or not x.is_cuda):
+        return fp8.fp8_linear(x, weight, bias)
     if x.is_cuda and x.dtype == torch.bfloat16 and weight.dtype == torch.bfloat16:
         native.require()
         return _LinearFn.apply(x, weight, bias, grad_owner if grad_owner is not None else weight)
