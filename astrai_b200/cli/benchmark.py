@@ -1,0 +1,235 @@
+"""``python -m astrai_b200.cli.benchmark``: inference benchmarks on a random-init model.
+
+* ``prefill`` / ``decode``: the measurements of the reference's ``scripts/tools/benchmark.py:169-286`` (prefill
+  tokens/s of one packed forward; decode tokens/s through the real scheduler, sampler and CUDA graphs).
+* ``serve``: a continuous-batching load test - Poisson arrivals, log-normal prompt lengths, shared prefixes, uniform
+  output lengths - reporting output tokens/s, p50 / p99 time to first token and p50 time per output token.  Requests
+  are injected straight into the scheduler (token ids, no HTTP) from a timer thread; every timestamp is taken on the
+  host when a token is handed to the request's callback.
+
+Presets: ``1b`` = 24 layers, d 2048, 16 query / 4 KV heads, head_dim 128, FFN 5632, vocab 32000 (the training
+benchmark's model); ``ref1b`` = the preset of the reference's benchmark (d 1536, 24 layers, 24q / 4kv, FFN 6912,
+vocab 100000).
+"""
+
+from __future__ import annotations
+
+import json
+import math
+import random
+import threading
+import time
+from typing import Dict, List, Optional
+
+import click
+
+PRESETS = {
+    "1b": dict(vocab_size=32000, hidden_size=2048, num_hidden_layers=24, intermediate_size=5632, num_attention_heads=16,
+               num_key_value_heads=4, max_position_embeddings=8192),
+    "ref1b": dict(vocab_size=100000, hidden_size=1536, num_hidden_layers=24, intermediate_size=6912, num_attention_heads=24,
+                  num_key_value_heads=4, max_position_embeddings=32768),
+    "tiny": dict(vocab_size=4096, hidden_size=256, num_hidden_layers=2, intermediate_size=688, num_attention_heads=4,
+                 num_key_value_heads=2, max_position_embeddings=4096),
+}
+
+
+class _IdTokenizer:
+    """Stands in for a tokenizer when requests are token ids: no stop ids, decode renders ids."""
+
+    stop_ids: List[int] = []
+
+    def encode(self, text):
+        return [int(t) for t in str(text).split()]
+
+    def decode(self, ids, skip_special_tokens=True):
+        return " ".join(str(i) for i in ids)
+
+
+def build_model(preset: str, device: str, dtype):
+    import torch
+
+    from astrai_b200.config import AutoRegressiveLMConfig
+    from astrai_b200.models import AutoRegressiveLM
+
+    cfg = AutoRegressiveLMConfig(rms_norm_eps=1e-6, tie_word_embeddings=True, rope_theta=10000.0, **PRESETS[preset])
+    torch.manual_seed(0)
+    return AutoRegressiveLM(cfg).to(device=device, dtype=dtype).eval()
+
+
+def _pct(values: List[float], q: float) -> Optional[float]:
+    if not values:
+        return None
+    s = sorted(values)
+    return s[min(len(s) - 1, max(0, math.ceil(q * len(s)) - 1))]
+
+
+def make_requests(n: int, rate: float, vocab: int, seed: int, prompt_mean: float = 512.0, sigma: float = 0.6,
+                  prompt_range=(16, 4096), shared_fraction: float = 0.5, n_prefixes: int = 8, prefix_len: int = 1024,
+                  out_range=(64, 512)) -> List[Dict]:
+    """The synthetic request stream: arrival time, prompt ids, output budget."""
+    rng = random.Random(seed)
+    mu = math.log(prompt_mean) - sigma * sigma / 2  # log-normal with the requested mean
+    prefixes = [[rng.randrange(2, vocab) for _ in range(prefix_len)] for _ in range(n_prefixes)]
+    t, reqs = 0.0, []
+    for _ in range(n):
+        t += rng.expovariate(rate)
+        plen = int(min(max(rng.lognormvariate(mu, sigma), prompt_range[0]), prompt_range[1]))
+        if rng.random() < shared_fraction:
+            head = prefixes[rng.randrange(n_prefixes)]
+            ids = (head + [rng.randrange(2, vocab) for _ in range(max(plen - prefix_len, 16))])
+        else:
+            ids = [rng.randrange(2, vocab) for _ in range(plen)]
+        reqs.append({"arrival": t, "ids": ids, "max_tokens": rng.randint(*out_range)})
+    return reqs
+
+
+def run_serve(scheduler, requests: List[Dict], temperature: float, top_p: float, top_k: int, time_scale: float = 1.0) -> Dict:
+    """Replay ``requests`` against a started scheduler; returns the aggregate metrics."""
+    from astrai_b200.inference import STOP
+
+    lock = threading.Lock()
+    records = [{"arrival": None, "first": None, "last": None, "tokens": 0} for _ in requests]
+    done = threading.Event()
+    remaining = [len(requests)]
+
+    def callback_for(i):
+        def cb(token):
+            now = time.perf_counter()
+            rec = records[i]
+            if token is STOP:
+                with lock:
+                    remaining[0] -= 1
+                    if remaining[0] == 0:
+                        done.set()
+                return
+            if rec["first"] is None:
+                rec["first"] = now
+            rec["last"] = now
+            rec["tokens"] += 1
+        return cb
+
+    t0 = time.perf_counter()
+
+    def feeder():
+        for i, req in enumerate(requests):
+            delay = t0 + req["arrival"] * time_scale - time.perf_counter()
+            if delay > 0:
+                time.sleep(delay)
+            records[i]["arrival"] = time.perf_counter()
+            scheduler.add_task(req["ids"], max_tokens=req["max_tokens"], temperature=temperature, top_p=top_p, top_k=top_k,
+                               stream_callback=callback_for(i))
+
+    th = threading.Thread(target=feeder, daemon=True)
+    th.start()
+    th.join()
+    done.wait(timeout=3600)
+    wall = time.perf_counter() - t0
+    ttft = [(r["first"] - r["arrival"]) * 1e3 for r in records if r["first"] is not None]
+    tpot = [(r["last"] - r["first"]) * 1e3 / (r["tokens"] - 1) for r in records if r["tokens"] > 1]
+    out_tokens = sum(r["tokens"] for r in records)
+    return {"requests": len(requests), "completed": sum(1 for r in records if r["tokens"] > 0), "wall_s": wall,
+            "output_tokens": out_tokens, "output_tok_per_s": out_tokens / wall if wall > 0 else None,
+            "ttft_ms_p50": _pct(ttft, 0.5), "ttft_ms_p99": _pct(ttft, 0.99), "tpot_ms_p50": _pct(tpot, 0.5),
+            "prompt_tokens": sum(len(r["ids"]) for r in requests)}
+
+
+@click.group()
+def benchmark():
+    """Inference benchmarks on random-init weights."""
+
+
+@benchmark.command()
+@click.option("--preset", type=click.Choice(sorted(PRESETS)), default="1b")
+@click.option("--device", default="cuda")
+@click.option("--batch_size", type=int, default=8)
+@click.option("--prompt_len", type=int, default=1024)
+@click.option("--trials", type=int, default=5)
+def prefill(preset, device, batch_size, prompt_len, trials):
+    """Tokens/s of packed prefill forwards through the scheduler's executor."""
+    import torch
+
+    from astrai_b200.inference import InferenceScheduler
+
+    model = build_model(preset, device, torch.bfloat16 if device != "cpu" else torch.float32)
+    sched = InferenceScheduler(model, _IdTokenizer(), max_batch_size=batch_size, max_seq_len=prompt_len + 8)
+    g = torch.Generator().manual_seed(0)
+    prompts = [torch.randint(2, model.config.vocab_size, (prompt_len,), generator=g).tolist() for _ in range(batch_size)]
+    times = []
+    for i in range(trials + 3):
+        if device != "cpu":
+            torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        sched.run_batch(prompts, max_tokens=1, temperature=0.0)
+        if device != "cpu":
+            torch.cuda.synchronize()
+        if i >= 3:
+            times.append(time.perf_counter() - t0)
+    best = min(times)
+    click.echo(json.dumps({"benchmark": "prefill", "preset": preset, "batch": batch_size, "prompt_len": prompt_len,
+                           "tok_per_s": batch_size * prompt_len / best, "ms": best * 1e3}))
+
+
+@benchmark.command()
+@click.option("--preset", type=click.Choice(sorted(PRESETS)), default="1b")
+@click.option("--device", default="cuda")
+@click.option("--batch_size", type=int, default=16)
+@click.option("--prompt_len", type=int, default=128)
+@click.option("--gen_len", type=int, default=256)
+@click.option("--cuda_graph/--no-cuda_graph", default=True)
+def decode(preset, device, batch_size, prompt_len, gen_len, cuda_graph):
+    """Decode tokens/s through scheduler + sampler (+ CUDA graphs)."""
+    import torch
+
+    from astrai_b200.inference import InferenceScheduler
+
+    model = build_model(preset, device, torch.bfloat16 if device != "cpu" else torch.float32)
+    sched = InferenceScheduler(model, _IdTokenizer(), max_batch_size=batch_size, max_seq_len=prompt_len + gen_len + 8,
+                               enable_cuda_graph=cuda_graph)
+    g = torch.Generator().manual_seed(0)
+    prompts = [torch.randint(2, model.config.vocab_size, (prompt_len,), generator=g).tolist() for _ in range(batch_size)]
+    sched.run_batch(prompts, max_tokens=8, temperature=0.0)  # warm-up (graph capture included)
+    t0 = time.perf_counter()
+    out = sched.run_batch(prompts, max_tokens=gen_len, temperature=0.0)
+    dt = time.perf_counter() - t0
+    n = sum(len(o[0]) if isinstance(o, tuple) else len(o) for o in out)
+    click.echo(json.dumps({"benchmark": "decode", "preset": preset, "batch": batch_size, "gen_len": gen_len,
+                           "tok_per_s": n / dt, "ms_per_step": dt * 1e3 / max(gen_len, 1)}))
+
+
+@benchmark.command()
+@click.option("--preset", type=click.Choice(sorted(PRESETS)), default="1b")
+@click.option("--device", default="cuda")
+@click.option("--requests", "n_requests", type=int, default=2048)
+@click.option("--rate", type=float, default=32.0, help="Poisson arrival rate (requests / s).")
+@click.option("--max_batch_size", type=int, default=64)
+@click.option("--max_seq_len", type=int, default=8192)
+@click.option("--kv_cache_tokens", type=int, default=None)
+@click.option("--temperature", type=float, default=0.8)
+@click.option("--top_p", type=float, default=0.95)
+@click.option("--top_k", type=int, default=50)
+@click.option("--seed", type=int, default=0)
+@click.option("--time_scale", type=float, default=1.0, help="Stretch (>1) or compress (<1) the arrival times.")
+def serve(preset, device, n_requests, rate, max_batch_size, max_seq_len, kv_cache_tokens, temperature, top_p, top_k, seed,
+          time_scale):
+    """Continuous-batching load test with a paged KV cache (16-token pages) and the radix prefix cache."""
+    import torch
+
+    from astrai_b200.inference import InferenceScheduler
+
+    model = build_model(preset, device, torch.bfloat16 if device != "cpu" else torch.float32)
+    sched = InferenceScheduler(model, _IdTokenizer(), max_batch_size=max_batch_size, max_seq_len=max_seq_len, page_size=16,
+                               kv_cache_tokens=kv_cache_tokens or max_batch_size * 4608, paged=True)
+    reqs = make_requests(n_requests, rate, model.config.vocab_size, seed)
+    sched.run_batch([reqs[0]["ids"][:64]], max_tokens=4, temperature=0.0)  # warm-up
+    sched.start()
+    try:
+        res = run_serve(sched, reqs, temperature, top_p, top_k, time_scale)
+    finally:
+        sched.stop()
+    res.update({"benchmark": "serve", "preset": preset, "rate": rate, "max_batch_size": max_batch_size, "page_size": 16,
+                "sampling": {"temperature": temperature, "top_p": top_p, "top_k": top_k, "seed": seed}})
+    click.echo(json.dumps(res))
+
+
+if __name__ == "__main__":
+    benchmark()

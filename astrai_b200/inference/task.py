@@ -20,15 +20,18 @@ STOP = object()
 class StreamDecoder:
     """Incremental detokeniser (``tokenizers.decoders.DecodeStream``): returns "" while a multi-byte character is open."""
 
-    __slots__ = ("_stream", "_tok")
+    __slots__ = ("_stream", "_tok", "_plain")
 
     def __init__(self, tokenizer):
         from tokenizers.decoders import DecodeStream
 
-        self._tok = tokenizer._tokenizer
-        self._stream = DecodeStream(skip_special_tokens=True)
+        self._tok = getattr(tokenizer, "_tokenizer", None)
+        self._plain = tokenizer if self._tok is None else None  # adapters without a `tokenizers` backend: decode per id
+        self._stream = DecodeStream(skip_special_tokens=True) if self._tok is not None else None
 
     def push(self, token_id: int) -> str:
+        if self._stream is None:
+            return self._plain.decode([token_id]) or ""
         return self._stream.step(self._tok, token_id) or ""
 
 
