@@ -1,0 +1,167 @@
+"""Kernel timing harness: ``python -m astrai_b200.ops.bench_kernels {gemm,skinny,flash,fp8,mma,decode}``.
+
+CUDA events on the launching stream, 3 warm-ups, median of N timed launches, a 256 MB buffer written between timed
+launches to flush the 126 MB L2.  Library kernels (cuBLAS through ``torch.matmul``, cuDNN / flash through SDPA) are
+timed next to ours as the reference point.  The numbers in ``profiles/`` come from these commands.
+"""
+
+from __future__ import annotations
+
+import math
+import sys
+
+import torch
+
+
+def _timer(flush_mb: int = 256):
+    flush = torch.empty(flush_mb << 20, dtype=torch.uint8, device="cuda")
+
+    def timeit(fn, n: int = 20) -> float:
+        for _ in range(3):
+            fn()
+        ts = []
+        for _ in range(n):
+            flush.zero_()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            fn()
+            e1.record()
+            torch.cuda.synchronize()
+            ts.append(e0.elapsed_time(e1))
+        ts.sort()
+        return ts[len(ts) // 2]  # ms
+
+    return timeit
+
+
+def bench_gemm():
+    from astrai_b200 import ops
+
+    t = _timer()
+    m = 8192
+    print("bf16 GEMM, M = 8192 (TFLOP/s): ours fwd / dgrad / wgrad(fp32 accumulate) | cuBLAS fwd")
+    for n, k, name in [(3072, 2048, "qkv"), (2048, 2048, "o_proj"), (11264, 2048, "gate+up"), (2048, 5632, "down"), (32000, 2048, "lm_head")]:
+        x = torch.randn(m, k, device="cuda", dtype=torch.bfloat16)
+        w = torch.randn(n, k, device="cuda", dtype=torch.bfloat16)
+        dy = torch.randn(m, n, device="cuda", dtype=torch.bfloat16)
+        acc = torch.zeros(n, k, device="cuda")
+        fl = 2.0 * m * n * k / 1e9
+        a = fl / t(lambda: ops.gemm(x, w))
+        b = fl / t(lambda: ops.gemm(dy, w, b_kmajor=False))
+        c = fl / t(lambda: ops.gemm(dy, x, out=acc, a_kmajor=False, b_kmajor=False, out_f32=True, accumulate=True))
+        d = fl / t(lambda: torch.matmul(x, w.t()))
+        print(f"  {n:6d} x {k:5d} ({name:8s}): {a:6.0f} / {b:6.0f} / {c:6.0f} | {d:6.0f}")
+
+
+def bench_skinny():
+    from astrai_b200 import ops
+
+    t = _timer()
+    print("decode-sized GEMM (GB/s of weight bytes): ours | cuBLAS")
+    for m in (1, 16, 64):
+        for n, k, name in [(3072, 2048, "qkv"), (2048, 2048, "o_proj"), (11264, 2048, "gate+up"), (2048, 5632, "down"), (32000, 2048, "lm_head")]:
+            x = torch.randn(m, k, device="cuda", dtype=torch.bfloat16)
+            w = torch.randn(n, k, device="cuda", dtype=torch.bfloat16)
+            gb = n * k * 2 / 1e6
+            a = gb / t(lambda: ops.gemm(x, w))
+            b = gb / t(lambda: torch.matmul(x, w.t()))
+            print(f"  M={m:3d} {n:6d} x {k:5d} ({name:8s}): {a:6.0f} | {b:6.0f}")
+
+
+def bench_flash():
+    import torch.nn.functional as F
+    from torch.nn.attention import SDPBackend, sdpa_kernel
+
+    from astrai_b200.ops import native
+
+    native.require()
+    op = torch.ops.astrai_b200
+    t = _timer()
+    b, s, hq, hkv, d = 4, 2048, 16, 4, 128
+    q = torch.randn(b * s, hq, d, device="cuda", dtype=torch.bfloat16)
+    k = torch.randn(b * s, hkv, d, device="cuda", dtype=torch.bfloat16)
+    v = torch.randn_like(k)
+    do = torch.randn_like(q)
+    sc = 1 / math.sqrt(d)
+    fl = 4.0 * b * hq * s * s * d / 2 / 1e9  # causal forward GFLOP
+    tf = t(lambda: op.flash_fwd(q, k, v, None, None, b, s, s, s, True, sc))
+    out, lse = op.flash_fwd(q, k, v, None, None, b, s, s, s, True, sc)
+    tb = t(lambda: op.flash_bwd(q, k, v, out, do, lse, None, None, b, s, s, s, s, True, sc))
+    print(f"flash attention B{b} S{s} {hq}q/{hkv}kv D{d} causal")
+    print(f"  ours : fwd {tf * 1e3:7.1f} us ({fl / tf:5.0f} TFLOP/s)  bwd {tb * 1e3:7.1f} us ({2.5 * fl / tb:5.0f} TFLOP/s at 5 GEMMs)")
+    q4, k4, v4 = (x.view(b, s, -1, d).transpose(1, 2).detach().requires_grad_(True) for x in (q, k, v))
+    with sdpa_kernel([SDPBackend.CUDNN_ATTENTION, SDPBackend.FLASH_ATTENTION], set_priority=True):
+        tf2 = t(lambda: F.scaled_dot_product_attention(q4, k4, v4, is_causal=True, enable_gqa=True))
+        o4 = F.scaled_dot_product_attention(q4, k4, v4, is_causal=True, enable_gqa=True)
+        g4 = torch.randn_like(o4)
+        tb2 = t(lambda: torch.autograd.grad(o4, (q4, k4, v4), g4, retain_graph=True))
+    print(f"  SDPA : fwd {tf2 * 1e3:7.1f} us ({fl / tf2:5.0f} TFLOP/s)  bwd {tb2 * 1e3:7.1f} us ({2.5 * fl / tb2:5.0f} TFLOP/s)")
+    print("  status", native.kernel_status(q.device))
+
+
+def bench_fp8():
+    from astrai_b200 import ops
+    from astrai_b200.ops import fp8
+
+    t = _timer()
+    m = 8192
+    print("fp8 GEMM, M = 8192 (TFLOP/s): ours fp8 | ours bf16 | quantise+transpose GB/s")
+    for n, k in [(3072, 2048), (11264, 2048), (2048, 5632)]:
+        x = torch.randn(m, k, device="cuda", dtype=torch.bfloat16)
+        w = torch.randn(n, k, device="cuda", dtype=torch.bfloat16)
+        one = torch.ones(1, device="cuda")
+        xq, _, _ = fp8.quantize_bf16(x, one, "e4m3")
+        wq, _, _ = fp8.quantize_bf16(w, one, "e4m3")
+        fl = 2.0 * m * n * k / 1e9
+        a = fl / t(lambda: fp8.mm_fp8(xq, wq, one, one))
+        b = fl / t(lambda: ops.gemm(x, w))
+        c = (m * k * 4) / 1e6 / t(lambda: fp8.quantize_bf16(x, one, "e4m3", with_transpose=True))
+        print(f"  {n:6d} x {k:5d}: {a:6.0f} | {b:6.0f} | {c:6.0f}")
+
+
+def bench_mma():
+    from astrai_b200.ops import native
+
+    native.require()
+    like = torch.empty(1, device="cuda")
+    reps = 512
+    print("tcgen05.mma issue probe (M=128, K=16 bf16, A/B from shared memory): clk per instruction, FLOP/clk/SM")
+    for lean in (True, False):
+        for n in (64, 128, 256):
+            torch.ops.astrai_b200.mma_issue_bench(like, n, reps, lean)
+            cyc = int(torch.ops.astrai_b200.mma_issue_bench(like, n, reps, lean).item())
+            per = cyc / (reps * 4)
+            print(f"  N={n:3d} {'lean issue   ' if lean else 'rebuilt descs'}: {per:6.1f} clk  {2 * 128 * n * 16 / per:6.0f} FLOP/clk")
+
+
+def bench_decode():
+    t = _timer()
+    op = torch.ops.astrai_b200
+    from astrai_b200.ops import native
+
+    native.require()
+    print("paged decode attention (GB/s of K/V bytes), page 16, 16q/4kv D128")
+    for b, ctx in [(1, 4096), (16, 2048), (64, 2048), (64, 8192)]:
+        hq, hkv, d = 16, 4, 128
+        n_slots = b * ctx + 1024
+        kb = torch.randn(n_slots, hkv, d, device="cuda", dtype=torch.bfloat16)
+        vb = torch.randn_like(kb)
+        table = torch.arange(b * ctx, dtype=torch.int32, device="cuda").view(b, ctx)
+        rows = torch.arange(b, dtype=torch.int32, device="cuda")
+        seq = torch.full((b,), ctx, dtype=torch.long, device="cuda")
+        q = torch.randn(b, hq, d, device="cuda", dtype=torch.bfloat16)
+        o_part = torch.zeros(b, hq, 32, d, device="cuda")
+        ml = torch.zeros(b, hq, 32, 2, device="cuda")
+        cnt = torch.zeros(b * hkv, dtype=torch.int32, device="cuda")
+        out = torch.empty_like(q)
+        splits = int(op.paged_decode_splits(b, hkv, ctx, 32))
+        ms = t(lambda: op.paged_decode_(q, kb, vb, table, rows, seq, d ** -0.5, splits, o_part, ml, cnt, out))
+        gb = 2 * b * ctx * hkv * d * 2 / 1e6
+        print(f"  B={b:3d} ctx={ctx:5d} splits={splits:2d}: {ms * 1e3:7.1f} us  {gb / ms:6.0f} GB/s")
+
+
+if __name__ == "__main__":
+    table = {"gemm": bench_gemm, "skinny": bench_skinny, "flash": bench_flash, "fp8": bench_fp8, "mma": bench_mma, "decode": bench_decode}
+    which = sys.argv[1:] or list(table)
+    for name in which:
+        table[name]()

@@ -220,6 +220,14 @@ Tensor gemm(const Tensor& A, const Tensor& B, const c10::optional<Tensor>& D_in,
     TORCH_CHECK(!accumulate, "gemm: accumulate needs an output tensor");
     D = at::empty({M, N}, A.options().dtype(out_f32 ? at::kFloat : at::kBFloat16));
   }
+  if (a_kmajor && b_kmajor && !out_f32 && !accumulate && M <= 64 && N >= 128 && K >= 128) {
+    // decode-sized batch: stream the weight through all SMs (weight = MMA M operand, K split over a cluster)
+    count();
+    const int rcs = ab::gemm_skinny(A.data_ptr(), B.data_ptr(), D.data_ptr(), M, N, K, A.stride(0), B.stride(0), D.stride(0),
+                                    status_tensor(A.device()).data_ptr<int>(), stream());
+    TORCH_CHECK(rcs == 0, "gemm_skinny launch failed with code ", rcs);
+    return D;
+  }
   count();
   const int rc = ab::gemm_bf16(A.data_ptr(), B.data_ptr(), D.data_ptr(), M, N, K, A.stride(0), B.stride(0), D.stride(0),
                                a_kmajor, b_kmajor, out_f32, accumulate, status_tensor(A.device()).data_ptr<int>(), stream());
@@ -272,7 +280,7 @@ void paged_decode_(const Tensor& q, const Tensor& k_buf, const Tensor& v_buf, co
                                   req_pool_indices.data_ptr<int>(), (const long long*)seq_lens.data_ptr<int64_t>(),
                                   o_part.data_ptr<float>(), ml_part.data_ptr<float>(), counters.data_ptr<int>(), out.data_ptr(),
                                   B, Hq, Hkv, D, (int)req_to_token.size(1), k_buf.size(0), (float)scale, (int)splits, max_splits, stream());
-  TORCH_CHECK(rc == 0, "paged_decode launch failed with code ", rc, " (-1: GQA group > 8, -2: splits, -3: head_dim not in {32,64,128,256})");
+  TORCH_CHECK(rc == 0, "paged_decode launch failed with code ", rc, " (-1: GQA group not in {1,2,4,8}, -2: splits, -3: head_dim not in {32,64,128,256})");
 }
 
 // q [Tq, Hq, D], k / v [Tk, Hkv, D] packed along tokens (a dense [B,S,H,D] batch is the same memory).
@@ -496,6 +504,15 @@ Tensor fp8_gemm(const Tensor& a, const Tensor& b, const Tensor& scale_a, const T
   return out;
 }
 
+Tensor mma_issue_bench(const Tensor& like, int64_t n, int64_t reps, bool lean) {
+  const c10::cuda::CUDAGuard guard(like.device());
+  Tensor out = at::zeros({1}, like.options().dtype(at::kLong));
+  count();
+  TORCH_CHECK(ab::mma_issue_bench((int)n, (int)reps, lean, reinterpret_cast<long long*>(out.data_ptr<int64_t>()), stream()) == 0,
+              "mma_issue_bench: n must be 64, 128 or 256");
+  return out;
+}
+
 void kernel_status_reset(const Tensor& like) { status_tensor(like.device()).zero_(); }
 
 }  // namespace
@@ -530,5 +547,6 @@ TORCH_LIBRARY(astrai_b200, m) {
   m.def("tp_reduce_(Tensor stage, Tensor(a!) out, int world) -> ()", &tp_reduce_);
   m.def("fp8_quantize(Tensor x, Tensor scale, bool e5m2, bool with_transpose) -> (Tensor, Tensor, Tensor)", &fp8_quantize);
   m.def("fp8_gemm(Tensor a, Tensor b, Tensor scale_a, Tensor scale_b, Tensor? bias) -> Tensor", &fp8_gemm);
+  m.def("mma_issue_bench(Tensor like, int n, int reps, bool lean) -> Tensor", &mma_issue_bench);
   m.def("gemm(Tensor A, Tensor B, Tensor? D, bool a_kmajor, bool b_kmajor, bool out_f32, bool accumulate) -> Tensor", &gemm);
 }

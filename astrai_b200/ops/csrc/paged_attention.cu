@@ -57,7 +57,7 @@ __device__ __forceinline__ void load8(const __nv_bfloat16* p, float (&f)[8]) {
 }
 
 // D = head dim (32/64/128/256).  LPT lanes cooperate on one token (8 dims each); a warp handles 32/LPT tokens at once.
-template <int D>
+template <int D, int GT>  // GT: query heads per kv head (compile-time, so the per-head state lives in registers)
 __global__ void __launch_bounds__(DEC_WARPS * 32)
 paged_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ k_buf,
                     const __nv_bfloat16* __restrict__ v_buf, const int* __restrict__ req_to_token,
@@ -68,7 +68,7 @@ paged_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __
   constexpr int LPT = D / 8;
   constexpr int TPW = 32 / LPT;  // tokens per warp iteration
   const int kvh = blockIdx.x, b = blockIdx.y, split = blockIdx.z, splits = gridDim.z;
-  const int G = n_q_heads / n_kv_heads;
+  constexpr int G = GT;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int sub = lane / LPT, dl = lane % LPT;  // token sub-group inside the warp, dim chunk of this lane
   const long long len = seq_lens[b];
@@ -77,9 +77,9 @@ paged_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __
   const long long t_begin = (long long)split * chunk;
   const long long t_end = t_begin + chunk < len ? t_begin + chunk : len;
 
-  float qf[MAXG][8], acc[MAXG][8], m[MAXG], l[MAXG];
+  float qf[GT][8], acc[GT][8], m[GT], l[GT];
 #pragma unroll
-  for (int g = 0; g < MAXG; ++g) {
+  for (int g = 0; g < GT; ++g) {
     m[g] = -INFINITY;
     l[g] = 0.f;
 #pragma unroll
@@ -92,38 +92,58 @@ paged_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __
   }
 
   const long long row = (long long)n_kv_heads * D;
-  for (long long t0 = t_begin + (long long)warp * TPW; t0 < t_end; t0 += (long long)DEC_WARPS * TPW) {
-    const long long t = t0 + sub;
-    const bool valid = t < t_end;
-    long long slot = valid ? (long long)table[t] : 0;
-    if (slot < 0 || slot >= n_slots) slot = 0;  // a corrupt table entry must not fault; its score is masked below
-    const bool live = valid && table[valid ? t : t_begin] >= 0;
-    float kf[8], vf[8];
-    load8(k_buf + slot * row + (long long)kvh * D + dl * 8, kf);
-    load8(v_buf + slot * row + (long long)kvh * D + dl * 8, vf);
+  // Each lane group takes UNR tokens per trip: all K and V loads of the trip are issued before any of them is used,
+  // so a warp keeps UNR x 2 x 16 bytes per lane in flight (the kernel is bound by HBM latency x bytes in flight).
+  constexpr int UNR = 4;
+  for (long long t0 = t_begin + (long long)warp * TPW * UNR; t0 < t_end; t0 += (long long)DEC_WARPS * TPW * UNR) {
+    uint4 kraw[UNR], vraw[UNR];
+    bool live[UNR];
 #pragma unroll
-    for (int g = 0; g < MAXG; ++g) {
-      if (g < G) {
-        float s = 0.f;
+    for (int u = 0; u < UNR; ++u) {
+      const long long t = t0 + (long long)u * TPW + sub;
+      const bool valid = t < t_end;
+      long long slot = valid ? (long long)table[t] : -1;
+      live[u] = valid && slot >= 0 && slot < n_slots;  // a corrupt table entry must not fault: its score is masked
+      if (!live[u]) slot = 0;
+      kraw[u] = *reinterpret_cast<const uint4*>(k_buf + slot * row + (long long)kvh * D + dl * 8);
+      vraw[u] = *reinterpret_cast<const uint4*>(v_buf + slot * row + (long long)kvh * D + dl * 8);
+    }
 #pragma unroll
-        for (int j = 0; j < 8; ++j) s += qf[g][j] * kf[j];
+    for (int u = 0; u < UNR; ++u) {
+      float kf[8], vf[8];
+      {
+        const __nv_bfloat162* hk = reinterpret_cast<const __nv_bfloat162*>(&kraw[u]);
+        const __nv_bfloat162* hv = reinterpret_cast<const __nv_bfloat162*>(&vraw[u]);
 #pragma unroll
-        for (int o = LPT / 2; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
-        if (!live) s = -INFINITY;
-        const float nm = fmaxf(m[g], s);
-        const float alpha = (nm == -INFINITY) ? 1.f : __expf(m[g] - nm);
-        const float p = (nm == -INFINITY) ? 0.f : __expf(s - nm);
-        l[g] = l[g] * alpha + p;
+        for (int i = 0; i < 4; ++i) {
+          const float2 a = __bfloat1622float2(hk[i]), c = __bfloat1622float2(hv[i]);
+          kf[2 * i] = a.x, kf[2 * i + 1] = a.y, vf[2 * i] = c.x, vf[2 * i + 1] = c.y;
+        }
+      }
 #pragma unroll
-        for (int j = 0; j < 8; ++j) acc[g][j] = acc[g][j] * alpha + p * vf[j];
-        m[g] = nm;
+      for (int g = 0; g < GT; ++g) {
+        if (g < G) {
+          float s = 0.f;
+#pragma unroll
+          for (int j = 0; j < 8; ++j) s += qf[g][j] * kf[j];
+#pragma unroll
+          for (int o = LPT / 2; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+          if (!live[u]) s = -INFINITY;
+          const float nm = fmaxf(m[g], s);
+          const float alpha = (nm == -INFINITY) ? 1.f : __expf(m[g] - nm);
+          const float p = (nm == -INFINITY) ? 0.f : __expf(s - nm);
+          l[g] = l[g] * alpha + p;
+#pragma unroll
+          for (int j = 0; j < 8; ++j) acc[g][j] = acc[g][j] * alpha + p * vf[j];
+          m[g] = nm;
+        }
       }
     }
   }
 
   // merge the TPW token sub-groups of the warp (same dims live LPT lanes apart)
 #pragma unroll
-  for (int g = 0; g < MAXG; ++g) {
+  for (int g = 0; g < GT; ++g) {
     if (g < G) {
 #pragma unroll
       for (int o = LPT; o < 32; o <<= 1) {
@@ -144,8 +164,8 @@ paged_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __
   }
 
   // merge the warps through shared memory
-  __shared__ float s_acc[DEC_WARPS][MAXG][D];
-  __shared__ float s_ml[DEC_WARPS][MAXG][2];
+  __shared__ float s_acc[DEC_WARPS][GT][D];
+  __shared__ float s_ml[DEC_WARPS][GT][2];
   __shared__ int s_last;
   if (sub == 0) {
     for (int g = 0; g < G; ++g) {
@@ -218,18 +238,29 @@ int paged_decode(const void* q, const void* k_buf, const void* v_buf, const int*
   if (n_q_heads % n_kv_heads || n_q_heads / n_kv_heads > MAXG) return -1;
   if (splits < 1 || splits > max_splits) return -2;
   const dim3 grid(n_kv_heads, batch, splits), block(DEC_WARPS * 32);
-#define AB_DEC(DD)                                                                                                   \
-  paged_decode_kernel<DD><<<grid, block, 0, st>>>((const __nv_bfloat16*)q, (const __nv_bfloat16*)k_buf,              \
-                                                  (const __nv_bfloat16*)v_buf, req_to_token, req_pool_indices,       \
-                                                  seq_lens, o_part, ml_part, counters, (__nv_bfloat16*)out,          \
-                                                  n_q_heads, n_kv_heads, max_ctx, n_slots, scale, max_splits)
+  const int G = n_q_heads / n_kv_heads;
+  const int gt = G <= 1 ? 1 : (G <= 2 ? 2 : (G <= 4 ? 4 : 8));
+  if (gt != G) return -1;  // group sizes 1, 2, 4, 8
+#define AB_DEC(DD, GG)                                                                                               \
+  paged_decode_kernel<DD, GG><<<grid, block, 0, st>>>((const __nv_bfloat16*)q, (const __nv_bfloat16*)k_buf,          \
+                                                      (const __nv_bfloat16*)v_buf, req_to_token, req_pool_indices,   \
+                                                      seq_lens, o_part, ml_part, counters, (__nv_bfloat16*)out,      \
+                                                      n_q_heads, n_kv_heads, max_ctx, n_slots, scale, max_splits)
+#define AB_DEC_G(DD)                 \
+  switch (gt) {                      \
+    case 1: AB_DEC(DD, 1); break;    \
+    case 2: AB_DEC(DD, 2); break;    \
+    case 4: AB_DEC(DD, 4); break;    \
+    default: AB_DEC(DD, 8); break;   \
+  }
   switch (head_dim) {
-    case 32: AB_DEC(32); break;
-    case 64: AB_DEC(64); break;
-    case 128: AB_DEC(128); break;
-    case 256: AB_DEC(256); break;
+    case 32: AB_DEC_G(32); break;
+    case 64: AB_DEC_G(64); break;
+    case 128: AB_DEC_G(128); break;
+    case 256: AB_DEC_G(256); break;
     default: return -3;
   }
+#undef AB_DEC_G
 #undef AB_DEC
   return cudaGetLastError() == cudaSuccess ? 0 : -5;
 }
