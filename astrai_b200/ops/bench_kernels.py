@@ -58,7 +58,7 @@ def bench_skinny():
 
     t = _timer()
     print("decode-sized GEMM (GB/s of weight bytes): ours | cuBLAS")
-    for m in (1, 16, 64):
+    for m in (1, 16, 64, 128, 256):
         for n, k, name in [(3072, 2048, "qkv"), (2048, 2048, "o_proj"), (11264, 2048, "gate+up"), (2048, 5632, "down"), (32000, 2048, "lm_head")]:
             x = torch.randn(m, k, device="cuda", dtype=torch.bfloat16)
             w = torch.randn(n, k, device="cuda", dtype=torch.bfloat16)

@@ -220,7 +220,7 @@ Tensor gemm(const Tensor& A, const Tensor& B, const c10::optional<Tensor>& D_in,
     TORCH_CHECK(!accumulate, "gemm: accumulate needs an output tensor");
     D = at::empty({M, N}, A.options().dtype(out_f32 ? at::kFloat : at::kBFloat16));
   }
-  if (a_kmajor && b_kmajor && !out_f32 && !accumulate && M <= 64 && N >= 128 && K >= 128) {
+  if (a_kmajor && b_kmajor && !out_f32 && !accumulate && M <= 256 && N >= 128 && K >= 128) {
     // decode-sized batch: stream the weight through all SMs (weight = MMA M operand, K split over a cluster)
     count();
     const int rcs = ab::gemm_skinny(A.data_ptr(), B.data_ptr(), D.data_ptr(), M, N, K, A.stride(0), B.stride(0), D.stride(0),

@@ -1,10 +1,10 @@
-// Skinny bf16 GEMM for decode-sized batches (M <= 64 tokens): Y[M, N] = X[M, K] . W[N, K]^T on tcgen05.
+// Skinny bf16 GEMM for decode-sized batches (M <= 256 tokens): Y[M, N] = X[M, K] . W[N, K]^T on tcgen05.
 //
 // With a handful of tokens the op is a stream over the weight matrix: what matters is that all 148 SMs pull bytes.
 // The output-stationary 128 x 256 tiles of the training GEMM would give N / 256 CTAs (8 for the 1B model's down
 // projection).  Here the operands are swapped and K is split:
 //   * the WEIGHT is the M operand of the MMA (128 output features per CTA, K-major as stored), the tokens are the N
-//     operand (padded to 16 / 32 / 64 by TMA zero fill), so a CTA's accumulator is Y^T[128 features, tokens] in TMEM;
+//     operand (padded to 16 / 32 / 64 / 128 / 256 by TMA zero fill), so a CTA's accumulator is Y^T[128 features, tokens] in TMEM;
 //   * K is split across the CTAs of a thread-block cluster (1, 2, 4 or 8 CTAs per 128-feature tile, chosen so that
 //     about 148..300 CTAs exist); each CTA runs a 4-stage TMA ring over its slice of K;
 //   * the partial accumulators never touch global memory: every CTA parks its fp32 tile in its own shared memory, the
@@ -34,7 +34,7 @@ constexpr int W_BYTES = BF * BK * 2;  // 16 KB
 constexpr int NUM_THREADS = 192;
 enum : int { ERR_SK_PRODUCER = 71, ERR_SK_MMA = 72, ERR_SK_EPILOGUE = 73 };
 
-template <int TOK>  // padded token count: 16, 32 or 64
+template <int TOK>  // padded token count: 16, 32, 64, 128 or 256
 struct SkCfg {
   static constexpr int X_BYTES = TOK * BK * 2;
   static constexpr int STAGE_BYTES = W_BYTES + X_BYTES;
@@ -88,7 +88,7 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
     fence_async_smem();
   }
   if (warp == 1) {
-    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_holder)), "r"(64u)
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_holder)), "r"((uint32_t)(TOK < 32 ? 32 : TOK))
                  : "memory");
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
   }
@@ -180,11 +180,15 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
     const int vec_total = M * (BF / 4);
     for (int v = split * NUM_THREADS + threadIdx.x; v < vec_total; v += cs * NUM_THREADS) {
       const int t = v / (BF / 4), f4 = (v % (BF / 4)) * 4;
+      // all peers' loads are issued before the first add: distributed-shared-memory latency is paid once per vector
+      float4 p[8];
+#pragma unroll
+      for (int c = 0; c < 8; ++c)
+        if (c < cs) p[c] = ld_dsmem_f4(mapa(red_addr + (uint32_t)(t * BF + f4) * 4u, (uint32_t)c));
       float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-      for (int c = 0; c < cs; ++c) {
-        const float4 p = ld_dsmem_f4(mapa(red_addr + (uint32_t)(t * BF + f4) * 4u, (uint32_t)c));
-        acc.x += p.x, acc.y += p.y, acc.z += p.z, acc.w += p.w;
-      }
+#pragma unroll
+      for (int c = 0; c < 8; ++c)
+        if (c < cs) acc.x += p[c].x, acc.y += p[c].y, acc.z += p[c].z, acc.w += p[c].w;
       const int f = n0 + f4;
       __nv_bfloat16* dst = Y + (long long)t * ldy + f;
       if (f + 4 <= N && ((reinterpret_cast<uintptr_t>(dst) & 7) == 0)) {
@@ -202,7 +206,7 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
   cluster_sync();  // nobody leaves while a peer may still read its shared memory
   if (warp == 1) {
     tc_fence_after();
-    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(64u) : "memory");
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)(TOK < 32 ? 32 : TOK)) : "memory");
   }
 }
 
@@ -234,21 +238,22 @@ int launch_sk(const CUtensorMap& mw, const CUtensorMap& mx, void* Y, int M, int 
 }  // namespace
 
 // CTAs per feature tile (cluster size): enough CTAs to cover the machine, at least two K blocks each.
-int gemm_skinny_splits(int N, int K) {
+int gemm_skinny_splits(int N, int K, int tok) {
   const int tiles = (N + BF - 1) / BF, num_kb = (K + BK - 1) / BK;
+  const int limit = tok <= 64 ? 300 : 148;  // two CTAs fit on an SM up to 64 tokens, one above: stay within one wave
   int cs = 1;
-  while (cs < 8 && tiles * cs * 2 <= 300 && num_kb / (cs * 2) >= 2) cs *= 2;
+  while (cs < 8 && tiles * cs * 2 <= limit && num_kb / (cs * 2) >= 2) cs *= 2;
   return cs;
 }
 
 int gemm_skinny(const void* X, const void* W, void* Y, int M, int N, int K, long long ldx, long long ldw, long long ldy,
                 int* status, cudaStream_t st) {
   if (M <= 0 || N <= 0 || K <= 0) return 0;
-  if (M > 64) return -6;
+  if (M > 256) return -6;
   if ((reinterpret_cast<uintptr_t>(X) & 15) || (reinterpret_cast<uintptr_t>(W) & 15) || (ldx % 8) || (ldw % 8)) return -1;
-  const int tok = M <= 16 ? 16 : (M <= 32 ? 32 : 64);
+  const int tok = M <= 16 ? 16 : (M <= 32 ? 32 : (M <= 64 ? 64 : (M <= 128 ? 128 : 256)));
   const int num_kb = (K + BK - 1) / BK;
-  const int cs = gemm_skinny_splits(N, K);
+  const int cs = gemm_skinny_splits(N, K, tok);
   const int kb_per_split = (num_kb + cs - 1) / cs;
   CUtensorMap mw, mx;
   if (!cache().get(&mw, W, K, N, ldw, BK, BF)) return -1000 - g_last_map_error;
@@ -256,7 +261,9 @@ int gemm_skinny(const void* X, const void* W, void* Y, int M, int N, int K, long
   switch (tok) {
     case 16: return launch_sk<16>(mw, mx, Y, M, N, K, ldy, cs, kb_per_split, status, st);
     case 32: return launch_sk<32>(mw, mx, Y, M, N, K, ldy, cs, kb_per_split, status, st);
-    default: return launch_sk<64>(mw, mx, Y, M, N, K, ldy, cs, kb_per_split, status, st);
+    case 64: return launch_sk<64>(mw, mx, Y, M, N, K, ldy, cs, kb_per_split, status, st);
+    case 128: return launch_sk<128>(mw, mx, Y, M, N, K, ldy, cs, kb_per_split, status, st);
+    default: return launch_sk<256>(mw, mx, Y, M, N, K, ldy, cs, kb_per_split, status, st);
   }
 }
 

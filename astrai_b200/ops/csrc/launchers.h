@@ -120,9 +120,9 @@ int fp8_quantize(const void* x, void* q, void* qt, const float* scale, float* am
 int gemm_fp8(const void* A, const void* B, void* D, const float* scale_a, const float* scale_b, const void* bias, int M,
              int N, int K, long long ldd, bool a_e5m2, bool b_e5m2, int* status, cudaStream_t st);
 
-// Skinny GEMM for M <= 64 (gemm_skinny.cu): Y[M,N] bf16 = X[M,K] . W[N,K]^T with the weight as the MMA's M operand and
+// Skinny GEMM for M <= 256 (gemm_skinny.cu): Y[M,N] bf16 = X[M,K] . W[N,K]^T with the weight as the MMA's M operand and
 // K split over a thread-block cluster (reduction through distributed shared memory; no workspace).
-int gemm_skinny_splits(int N, int K);
+int gemm_skinny_splits(int N, int K, int tok);
 int gemm_skinny(const void* X, const void* W, void* Y, int M, int N, int K, long long ldx, long long ldw, long long ldy,
                 int* status, cudaStream_t st);
 

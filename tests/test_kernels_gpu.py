@@ -324,7 +324,7 @@ def test_engine_on_gpu_graph_replay_matches_eager(tmp_path):
     assert agree or sum(a == b for a, b in zip(logits.argmax(-1).tolist(), ref[1])) >= 10  # bf16 near-ties may flip
 
 
-@pytest.mark.parametrize("m,n,k", [(1, 2048, 2048), (16, 3072, 2048), (17, 2048, 5632), (64, 11264, 2048), (33, 32000, 2048), (5, 384, 200)])
+@pytest.mark.parametrize("m,n,k", [(1, 2048, 2048), (16, 3072, 2048), (17, 2048, 5632), (64, 11264, 2048), (33, 32000, 2048), (5, 384, 200), (100, 3072, 2048), (256, 2048, 5632), (200, 11264, 2048)])
 def test_skinny_gemm_matches_fp32(m, n, k):
     """Decode-sized batches take the split-K kernel with the weight as the MMA's M operand."""
     from astrai_b200 import ops
