@@ -145,10 +145,13 @@ flash_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
                       int sk, int Hq, int Hkv, long long dk_row_stride, long long total_q, float scale, int causal,
                       int* __restrict__ status) {
   using C = DkvCfg<D>;
-  const SeqInfoB si = seq_info_b(cu_q, cu_k, blockIdx.z, sq, sk);
-  const int k0 = (int)blockIdx.x * 128;
+  // grid = (kv heads x sequences, key tiles): blocks are dispatched in linear order, so every key tile 0 (the one
+  // with the most query tiles under a causal mask) starts before any lighter tile - longest work first.
+  const int kvh = (int)blockIdx.x % Hkv;
+  const SeqInfoB si = seq_info_b(cu_q, cu_k, (int)blockIdx.x / Hkv, sq, sk);
+  const int k0 = (int)blockIdx.y * 128;
   if (k0 >= si.k_len) return;
-  const int kvh = blockIdx.y, G = Hq / Hkv, off = si.k_len - si.q_len;
+  const int G = Hq / Hkv, off = si.k_len - si.q_len;
   int q_lo = 0;
   if (causal) q_lo = max(0, k0 - off) / SUB * SUB;
   const int n_sub = max(0, (si.q_len - q_lo + SUB - 1) / SUB);
@@ -376,11 +379,13 @@ flash_bwd_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
                     const int* __restrict__ cu_q, const int* __restrict__ cu_k, int sq, int sk, int Hq, int Hkv,
                     long long dq_row_stride, long long total_q, float scale, int causal, int* __restrict__ status) {
   using C = DqCfg<D>;
-  const SeqInfoB si = seq_info_b(cu_q, cu_k, blockIdx.z, sq, sk);
+  // grid = (query heads x sequences, query tiles), heaviest (last) causal tiles dispatched first
+  const int h = (int)blockIdx.x % Hq;
+  const SeqInfoB si = seq_info_b(cu_q, cu_k, (int)blockIdx.x / Hq, sq, sk);
   const int n_q_tiles = (si.q_len + 127) / 128;
-  const int qt = n_q_tiles - 1 - (int)blockIdx.x;
+  const int qt = n_q_tiles - 1 - (int)blockIdx.y;
   if (qt < 0) return;
-  const int h = blockIdx.y, kvh = h / (Hq / Hkv);
+  const int kvh = h / (Hq / Hkv);
   const int q0 = qt * 128, off = si.k_len - si.q_len;
   int kv_end = si.k_len;
   if (causal) kv_end = min(si.k_len, q0 + 128 + off);
@@ -591,11 +596,11 @@ int launch_bwd(const void* q, const void* k, const void* v, const void* out, con
   float* lse2 = delta + total_q * Hq;  // second half of the scratch: lse in log2 units
   flash_delta_kernel<D><<<(unsigned)((warps * 32 + 255) / 256), 256, 0, st>>>(
       (const __nv_bfloat16*)dout, (const __nv_bfloat16*)out, lse, delta, lse2, total_q, Hq, do_rs, o_rs);
-  const dim3 grid_a((max_k + 127) / 128, Hkv, batch);
+  const dim3 grid_a(Hkv * batch, (max_k + 127) / 128, 1);
   kern_a<<<grid_a, BWD_THREADS, DkvCfg<D>::SMEM, st>>>(mq64, mdo64, mk128, mv128, lse2, delta, (__nv_bfloat16*)dk,
                                                        (__nv_bfloat16*)dv, cu_q, cu_k, sq, sk, Hq, Hkv, dk_rs, total_q,
                                                        scale, causal ? 1 : 0, status);
-  const dim3 grid_b((max_q + 127) / 128, Hq, batch);
+  const dim3 grid_b(Hq * batch, (max_q + 127) / 128, 1);
   kern_b<<<grid_b, BWD_THREADS, DqCfg<D>::SMEM, st>>>(mq128, mdo128, mk64, mv64, lse2, delta, (__nv_bfloat16*)dq, cu_q,
                                                       cu_k, sq, sk, Hq, Hkv, dq_rs, total_q, scale, causal ? 1 : 0, status);
   return cudaGetLastError() == cudaSuccess ? 0 : -5;

@@ -64,11 +64,14 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
                  const int* __restrict__ cu_q, const int* __restrict__ cu_k, int sq, int sk, int Hq, int Hkv,
                  long long o_row_stride, long long total_q, float scale_log2, int causal, int* __restrict__ status) {
   using C = FwdCfg<D>;
-  const SeqInfo si = seq_info(cu_q, cu_k, blockIdx.z, sq, sk);
+  // grid = (query heads x sequences, query tiles): blocks are dispatched in linear order, so the heaviest (last)
+  // causal tile of EVERY head starts before any lighter tile - longest work first across the whole launch.
+  const int h = (int)blockIdx.x % Hq;
+  const SeqInfo si = seq_info(cu_q, cu_k, (int)blockIdx.x / Hq, sq, sk);
   const int n_q_tiles = (si.q_len + BQ - 1) / BQ;
-  const int qt = n_q_tiles - 1 - (int)blockIdx.x;  // heaviest (last) causal tiles first
+  const int qt = n_q_tiles - 1 - (int)blockIdx.y;
   if (qt < 0) return;
-  const int h = blockIdx.y, kvh = h / (Hq / Hkv);
+  const int kvh = h / (Hq / Hkv);
   const int q0 = qt * BQ, off = si.k_len - si.q_len;
   int kv_end = si.k_len;
   if (causal) kv_end = min(si.k_len, q0 + BQ + off);
@@ -324,7 +327,7 @@ int launch_fwd(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& 
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, FwdCfg<D>::SMEM) != cudaSuccess) return -4;
     configured = true;
   }
-  const dim3 grid((max_q + BQ - 1) / BQ, Hq, batch);
+  const dim3 grid(Hq * batch, (max_q + BQ - 1) / BQ, 1);
   kern<<<grid, FA_THREADS, FwdCfg<D>::SMEM, st>>>(mq, mk, mv, (__nv_bfloat16*)O, lse, cu_q, cu_k, sq, sk, Hq, Hkv,
                                                   o_row_stride, total_q, scale * 1.4426950408889634f, causal ? 1 : 0,
                                                   status);
