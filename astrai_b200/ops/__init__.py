@@ -3,6 +3,7 @@
 from astrai_b200.ops import fp8, native, reference
 from astrai_b200.ops.fp8 import DelayedScaling, DynamicScaling, FP8Format, fp8_autocast
 from astrai_b200.ops.attention import dense_attention
+from astrai_b200.ops.backend import ATTN_BACKEND, attn_backend, get_backend
 from astrai_b200.ops.functional import (
     adamw_,
     assume_loss_grad,
@@ -22,7 +23,7 @@ from astrai_b200.ops.functional import (
 )
 
 __all__ = [
-    "DelayedScaling", "DynamicScaling", "FP8Format", "fp8", "fp8_autocast", "adamw_", "assume_loss_grad", "clip_coef", "cross_entropy", "dense_attention", "embedding", "gemm", "linear",
+    "ATTN_BACKEND", "attn_backend", "get_backend", "DelayedScaling", "DynamicScaling", "FP8Format", "fp8", "fp8_autocast", "adamw_", "assume_loss_grad", "clip_coef", "cross_entropy", "dense_attention", "embedding", "gemm", "linear",
     "linear_cross_entropy", "linear_token_logprobs", "native", "qkv_rope", "reference", "rms_norm", "rotary",
     "sumsq", "swiglu", "swiglu_fused",
 ]

@@ -22,9 +22,11 @@ _SDPA_BACKENDS = None
 
 
 def _use_flash() -> bool:
-    """The tcgen05 kernels serve every unmasked / causal call; ``ASTRAI_B200_ATTN=sdpa`` selects the library path
-    (kept as the comparison baseline and for arbitrary boolean masks)."""
-    return os.environ.get("ASTRAI_B200_ATTN", "flash") != "sdpa"
+    """The tcgen05 kernels serve every unmasked / causal call; ``attn_backend("torch_native")`` or
+    ``ASTR_BACKEND=torch_native`` selects the library path (comparison baseline; also used for boolean masks)."""
+    from astrai_b200.ops import backend
+
+    return backend.get_backend("cuda") is backend.ATTN_BACKEND.TCGEN05
 
 
 def _sdpa_ctx():
@@ -47,8 +49,14 @@ def dense_attention(q: Tensor, k: Tensor, v: Tensor, mask: Optional[Tensor] = No
     """Softmax attention with GQA head sharing; returns ``[B,S,Hq,Dv]``."""
     if not q.is_cuda:
         return reference.attention(q, k, v, mask, causal, scale)
-    if mask is None and _use_flash() and flash.supported(q, k, v):
-        return flash.flash_attention(q, k, v, causal=causal, scale=scale)
+    if _use_flash():
+        if mask is None and flash.supported(q, k, v):
+            return flash.flash_attention(q, k, v, causal=causal, scale=scale)
+        from astrai_b200.ops import backend
+
+        if backend.explicit() and backend._current.get() is not None:
+            raise RuntimeError("the tcgen05 attention backend was selected explicitly but does not cover this call "
+                               "(boolean mask, or head_dim outside {64, 128})")
     hq, hkv = q.shape[2], k.shape[2]
     qt, kt, vt = q.transpose(1, 2), k.transpose(1, 2), v.transpose(1, 2)
     with _sdpa_ctx():

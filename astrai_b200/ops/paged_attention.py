@@ -86,7 +86,10 @@ def cached_attention(q: Tensor, k: Tensor, v: Tensor, kv_cache: KVCache, layer_i
         raise ValueError("packed inference tensors must be [tokens, heads, head_dim]")
     _append(k, v, kv_cache, layer_id)
     scale = q.shape[-1] ** -0.5
-    if fwd == "decode" and attn_mask is None and _decode_native_ok(q, kv_cache):
+    from astrai_b200.ops import backend as _backend
+
+    native_on = _backend.get_backend(q.device.type) is _backend.ATTN_BACKEND.TCGEN05
+    if native_on and fwd == "decode" and attn_mask is None and _decode_native_ok(q, kv_cache):
         b = q.shape[0]
         splits = kv_cache.decode_splits or int(torch.ops.astrai_b200.paged_decode_splits(
             b, kv_cache.k_buffer.shape[2], max(kv_cache.max_len, 1), kv_cache.decode_o_part.shape[2]))
@@ -97,7 +100,7 @@ def cached_attention(q: Tensor, k: Tensor, v: Tensor, kv_cache: KVCache, layer_i
             kv_cache.decode_counters, out)
         return out
     q_lens, kv_lens = _lens(kv_cache)
-    if (attn_mask is None and fwd == "prefill" and kv_cache.kv_gather_loc is not None and kv_cache.qo_indptr is not None
+    if (native_on and attn_mask is None and fwd == "prefill" and kv_cache.kv_gather_loc is not None and kv_cache.qo_indptr is not None
             and flash.supported(q, kv_cache.k_buffer[layer_id], kv_cache.v_buffer[layer_id])):
         # ragged prefill on the tcgen05 flash kernel: gather this batch's keys / values from the pool (cached prefix
         # included) into packed tensors once, then one varlen launch with lower-right aligned causal masking

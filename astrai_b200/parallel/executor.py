@@ -572,7 +572,16 @@ class FSDPExecutor(FlatExecutor):
         from astrai_b200.parallel.symm import SymmetricArena
 
         dev = next(model.parameters()).device
-        self._symm = SymmetricAllocator(SymmetricArena(arena_bytes_for(model, get_world_size()), dev))
+        try:
+            arena = SymmetricArena(arena_bytes_for(model, get_world_size()), dev)
+        except Exception as exc:  # noqa: BLE001 - no peer mapping on this machine (every rank fails alike)
+            logger.warning("symmetric memory unavailable (%s); FSDP falls back to NCCL collectives", exc)
+            self.comm = "nccl"
+            return None
+        if self.comm == "nvls" and not arena.has_multicast:
+            logger.warning("no NVSwitch multicast mapping; using plain peer loads / stores")
+            self.comm = "p2p"
+        self._symm = SymmetricAllocator(arena)
         return self._symm.alloc
 
     def _init_comm(self, model):

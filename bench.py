@@ -355,7 +355,8 @@ def main():
     ap.add_argument("--steps", type=int, default=6)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--comm", default=os.environ.get("ASTRAI_B200_FSDP_COMM", "nccl"), choices=["nccl", "p2p", "nvls"])
+    ap.add_argument("--comm", default=os.environ.get("ASTRAI_B200_FSDP_COMM", "p2p"), choices=["nccl", "p2p", "nvls"],
+                    help="FSDP transport: fused peer-memory kernels (p2p / nvls) or NCCL collectives")
     ap.add_argument("--skip-e2e", action="store_true")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 1)

@@ -141,3 +141,23 @@ def test_signal_handler_requests_stop():
         sh.unregister_signal_handlers()
         signal.signal(signal.SIGTERM, signal.SIG_DFL)
         signal.signal(signal.SIGINT, signal.default_int_handler)
+
+
+def test_attention_backend_selection(monkeypatch):
+    from astrai_b200.ops import backend
+
+    monkeypatch.delenv("ASTR_BACKEND", raising=False)
+    monkeypatch.delenv("ASTRAI_B200_ATTN", raising=False)
+    assert backend.get_backend("cpu") is backend.ATTN_BACKEND.TORCH_NATIVE
+    assert backend.get_backend("cuda") is backend.ATTN_BACKEND.TCGEN05 and not backend.explicit()
+    monkeypatch.setenv("ASTR_BACKEND", "torch_native")
+    assert backend.get_backend("cuda") is backend.ATTN_BACKEND.TORCH_NATIVE and backend.explicit()
+    with backend.attn_backend("cuda"):  # the reference's name for its kernel backend
+        assert backend.get_backend("cuda") is backend.ATTN_BACKEND.TCGEN05
+    assert backend.get_backend("cuda") is backend.ATTN_BACKEND.TORCH_NATIVE
+    assert backend.ATTN_BACKEND.parse("flash") is backend.ATTN_BACKEND.TCGEN05
+    import pytest
+
+    with pytest.raises(ValueError):
+        backend.ATTN_BACKEND.parse("metal")
+    assert backend.is_available("torch_native")
