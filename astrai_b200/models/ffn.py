@@ -78,6 +78,32 @@ class DeepSeekMoE(nn.Module):
         self.expert_parallel = None  # set by the EP executor: object with dispatch()/combine()
 
     # ---- routing --------------------------------------------------------------------------------------------
+    def _use_kernels(self, x: Tensor) -> bool:
+        from astrai_b200.ops import moe
+
+        ffn = self.routed_experts[0].gate.weight.shape[0]
+        return (self.expert_parallel is None and moe.available(x, self.n_routed_experts, self.n_activated_experts)
+                and ffn % 64 == 0 and all(type(m.gate).__name__ == "Linear" for m in self.routed_experts))
+
+    def _forward_kernels(self, x: Tensor, with_aux: bool):
+        """Router, dispatch, two grouped GEMMs with SwiGLU in between, and combine on the sm_100a kernels."""
+        from astrai_b200.ops import moe
+
+        e, k = self.n_routed_experts, self.n_activated_experts
+        logits = self.router(x)
+        probs, idx, weights, counts, psum = moe.route(logits, k, self.norm_topk_prob)
+        aux, stats = None, None
+        if with_aux:
+            load = counts.float() / idx.numel()
+            aux = e * (load * (psum / x.shape[0])).sum()
+            stats = {"probs": probs.detach(), "topk_indices": idx}
+        xs, plan = moe.dispatch(x, idx, counts, e)
+        w_gu = torch.stack([torch.cat([m.gate.weight, m.up.weight], dim=0) for m in self.routed_experts])  # [E, 2F, D]
+        w_dn = torch.stack([m.down.weight for m in self.routed_experts])                                   # [E, D, F]
+        h = ops.swiglu_fused(moe.zero_unused_rows(moe.grouped_linear(xs, w_gu, plan), plan))
+        y = moe.zero_unused_rows(moe.grouped_linear(h, w_dn, plan), plan)
+        return moe.combine(y, weights, plan), aux, stats
+
     def route(self, x: Tensor, with_aux: bool):
         e, k = self.n_routed_experts, self.n_activated_experts
         probs = torch.softmax(self.router(x).float(), dim=-1).to(x.dtype)
@@ -124,8 +150,11 @@ class DeepSeekMoE(nn.Module):
         with_aux = self.training and torch.is_grad_enabled()
         shape = x.shape
         flat = x.reshape(-1, shape[-1])
-        weights, idx, aux, stats = self.route(flat, with_aux)
-        out = self._routed(flat, weights, idx)
+        if self._use_kernels(flat):
+            out, aux, stats = self._forward_kernels(flat, with_aux)
+        else:
+            weights, idx, aux, stats = self.route(flat, with_aux)
+            out = self._routed(flat, weights, idx)
         if self.n_shared_experts:
             shared = self.shared_experts[0](flat)["hidden_states"]
             for ex in self.shared_experts[1:]:

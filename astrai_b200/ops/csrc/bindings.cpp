@@ -513,6 +513,120 @@ Tensor mma_issue_bench(const Tensor& like, int64_t n, int64_t reps, bool lean) {
   return out;
 }
 
+// ---- mixture of experts
+std::tuple<Tensor, Tensor, Tensor, Tensor, Tensor> moe_router(const Tensor& logits, int64_t k, bool renorm) {
+  CHECK_CUDA_CONTIG(logits);
+  TORCH_CHECK(logits.dim() == 2, "moe_router: logits [tokens, experts]");
+  const c10::cuda::CUDAGuard guard(logits.device());
+  const int64_t T = logits.size(0), E = logits.size(1);
+  Tensor probs = at::empty_like(logits);
+  Tensor idx = at::empty({T, k}, logits.options().dtype(at::kLong));
+  Tensor w = at::empty({T, k}, logits.options());
+  Tensor counts = at::zeros({E}, logits.options().dtype(at::kInt));
+  Tensor psum = at::zeros({E}, logits.options().dtype(at::kFloat));
+  count();
+  const int rc = ab::moe_router(logits.data_ptr(), probs.data_ptr(), reinterpret_cast<long long*>(idx.data_ptr<int64_t>()), w.data_ptr(),
+                                counts.data_ptr<int>(), psum.data_ptr<float>(), T, (int)E, (int)k, renorm, is_bf16(logits), stream());
+  TORCH_CHECK(rc == 0, "moe_router: experts <= 256 and top-k <= 8 (code ", rc, ")");
+  return {probs, idx, w, counts, psum};
+}
+
+std::tuple<Tensor, Tensor, Tensor, Tensor> moe_plan(const Tensor& counts, int64_t max_tiles) {
+  CHECK_CUDA_CONTIG(counts);
+  TORCH_CHECK(counts.scalar_type() == at::kInt, "moe_plan: int32 counts");
+  const c10::cuda::CUDAGuard guard(counts.device());
+  const int64_t E = counts.numel();
+  Tensor offsets = at::empty({E + 1}, counts.options()), tile_expert = at::empty({max_tiles}, counts.options());
+  Tensor cursors = at::empty({E}, counts.options()), total = at::empty({1}, counts.options());
+  count();
+  TORCH_CHECK(ab::moe_plan(counts.data_ptr<int>(), offsets.data_ptr<int>(), tile_expert.data_ptr<int>(), cursors.data_ptr<int>(),
+                           total.data_ptr<int>(), (int)E, (int)max_tiles, stream()) == 0, "moe_plan launch failed");
+  return {offsets, tile_expert, cursors, total};
+}
+
+std::tuple<Tensor, Tensor> moe_permute(const Tensor& x, const Tensor& idx, const Tensor& counts, const Tensor& offsets, Tensor& cursors,
+                                       int64_t max_rows) {
+  CHECK_CUDA_CONTIG(x);
+  CHECK_CUDA_CONTIG(idx);
+  TORCH_CHECK(x.dim() == 2 && idx.dim() == 2 && idx.scalar_type() == at::kLong && idx.size(0) == x.size(0), "moe_permute: x [T,D], idx [T,K] int64");
+  const c10::cuda::CUDAGuard guard(x.device());
+  Tensor sorted = at::empty({max_rows, x.size(1)}, x.options());
+  Tensor slot_of = at::empty({idx.size(0), idx.size(1)}, x.options().dtype(at::kInt));
+  count(2);
+  const int rc = ab::moe_permute(x.data_ptr(), reinterpret_cast<const long long*>(idx.data_ptr<int64_t>()), counts.data_ptr<int>(),
+                                 offsets.data_ptr<int>(), cursors.data_ptr<int>(), sorted.data_ptr(), slot_of.data_ptr<int>(), x.size(0),
+                                 (int)idx.size(1), (int)x.size(1), (int)counts.numel(), is_bf16(x), stream());
+  TORCH_CHECK(rc == 0, "moe_permute: hidden size must be a multiple of 8 (code ", rc, ")");
+  return {sorted, slot_of};
+}
+
+Tensor moe_combine(const Tensor& y, const Tensor& slot_of, const c10::optional<Tensor>& weights) {
+  CHECK_CUDA_CONTIG(y);
+  CHECK_CUDA_CONTIG(slot_of);
+  const c10::cuda::CUDAGuard guard(y.device());
+  Tensor out = at::empty({slot_of.size(0), y.size(1)}, y.options());
+  count();
+  const int rc = ab::moe_combine(y.data_ptr(), slot_of.data_ptr<int>(), weights.has_value() ? weights->data_ptr() : nullptr, out.data_ptr(),
+                                 slot_of.size(0), (int)slot_of.size(1), (int)y.size(1), is_bf16(y), stream());
+  TORCH_CHECK(rc == 0, "moe_combine launch failed with code ", rc);
+  return out;
+}
+
+std::tuple<Tensor, Tensor> moe_combine_bwd(const Tensor& dout, const Tensor& y, const Tensor& slot_of, const Tensor& weights) {
+  CHECK_CUDA_CONTIG(dout);
+  CHECK_CUDA_CONTIG(y);
+  const c10::cuda::CUDAGuard guard(y.device());
+  Tensor dy = at::zeros_like(y);  // padding rows must stay zero: they enter the expert weight gradients
+  Tensor dw = at::empty({slot_of.size(0), slot_of.size(1)}, y.options().dtype(at::kFloat));
+  count();
+  const int rc = ab::moe_combine_bwd(dout.data_ptr(), y.data_ptr(), slot_of.data_ptr<int>(), weights.data_ptr(), dy.data_ptr(),
+                                     dw.data_ptr<float>(), slot_of.size(0), (int)slot_of.size(1), (int)y.size(1), is_bf16(y), stream());
+  TORCH_CHECK(rc == 0, "moe_combine_bwd launch failed with code ", rc);
+  return {dy, dw};
+}
+
+// x [R, K] sorted rows; w stacked [E, N, K] (w_kmajor) or consumed as [E, Kc, N'] (MN-major: contraction over dim 1)
+Tensor grouped_gemm_rows(const Tensor& x, const Tensor& w, bool w_kmajor, const Tensor& tile_expert) {
+  CHECK_CUDA_CONTIG(x);
+  CHECK_CUDA_CONTIG(w);
+  TORCH_CHECK(x.scalar_type() == at::kBFloat16 && w.scalar_type() == at::kBFloat16 && w.dim() == 3 && x.dim() == 2, "grouped_gemm_rows: bf16 x [R,K], w [E,a,b]");
+  const int64_t E = w.size(0), K = x.size(1);
+  const int64_t N = w_kmajor ? w.size(1) : w.size(2);
+  TORCH_CHECK((w_kmajor ? w.size(2) : w.size(1)) == K, "grouped_gemm_rows: inner dimensions differ");
+  TORCH_CHECK(tile_expert.scalar_type() == at::kInt && tile_expert.numel() * 128 >= x.size(0), "grouped_gemm_rows: tile map too short");
+  const c10::cuda::CUDAGuard guard(x.device());
+  Tensor y = at::empty({x.size(0), N}, x.options());
+  ab::GroupedParams g{};
+  g.tile_expert = tile_expert.data_ptr<int>();
+  g.b_rows_per_expert = (int)w.size(1);
+  g.b_row_offset = 0;
+  g.E = (int)E;
+  count();
+  const int rc = ab::gemm_grouped_rows(x.data_ptr(), w.data_ptr(), y.data_ptr(), (int)x.size(0), (int)N, (int)K, x.stride(0), E * w.size(1),
+                                       w.size(2), y.stride(0), w_kmajor, g, status_tensor(x.device()).data_ptr<int>(), stream());
+  TORCH_CHECK(rc == 0, "gemm_grouped_rows launch failed with code ", rc, " (-2: rows not a multiple of 128, -3: contraction not a multiple of 64)");
+  return y;
+}
+
+// dW [E, N, K] = per-expert dY_e^T X_e over the padded segments given by offsets [E+1]
+Tensor grouped_gemm_wgrad(const Tensor& dy, const Tensor& x, const Tensor& offsets, bool out_f32) {
+  CHECK_CUDA_CONTIG(dy);
+  CHECK_CUDA_CONTIG(x);
+  TORCH_CHECK(dy.scalar_type() == at::kBFloat16 && x.scalar_type() == at::kBFloat16 && dy.size(0) == x.size(0), "grouped_gemm_wgrad: bf16 [R,N], [R,K]");
+  const int64_t E = offsets.numel() - 1, N = dy.size(1), K = x.size(1);
+  const c10::cuda::CUDAGuard guard(x.device());
+  Tensor dw = at::empty({E, N, K}, x.options().dtype(out_f32 ? at::kFloat : at::kBFloat16));
+  ab::GroupedParams g{};
+  g.offsets = offsets.data_ptr<int>();
+  g.d_expert_stride = N * K;
+  g.E = (int)E;
+  count();
+  const int rc = ab::gemm_grouped_wgrad(dy.data_ptr(), x.data_ptr(), dw.data_ptr(), (int)x.size(0), (int)N, (int)K, dy.stride(0), x.stride(0), K,
+                                        out_f32, false, g, status_tensor(x.device()).data_ptr<int>(), stream());
+  TORCH_CHECK(rc == 0, "gemm_grouped_wgrad launch failed with code ", rc);
+  return dw;
+}
+
 void kernel_status_reset(const Tensor& like) { status_tensor(like.device()).zero_(); }
 
 }  // namespace
@@ -548,5 +662,12 @@ TORCH_LIBRARY(astrai_b200, m) {
   m.def("fp8_quantize(Tensor x, Tensor scale, bool e5m2, bool with_transpose) -> (Tensor, Tensor, Tensor)", &fp8_quantize);
   m.def("fp8_gemm(Tensor a, Tensor b, Tensor scale_a, Tensor scale_b, Tensor? bias) -> Tensor", &fp8_gemm);
   m.def("mma_issue_bench(Tensor like, int n, int reps, bool lean) -> Tensor", &mma_issue_bench);
+  m.def("moe_router(Tensor logits, int k, bool renorm) -> (Tensor, Tensor, Tensor, Tensor, Tensor)", &moe_router);
+  m.def("moe_plan(Tensor counts, int max_tiles) -> (Tensor, Tensor, Tensor, Tensor)", &moe_plan);
+  m.def("moe_permute(Tensor x, Tensor idx, Tensor counts, Tensor offsets, Tensor(a!) cursors, int max_rows) -> (Tensor, Tensor)", &moe_permute);
+  m.def("moe_combine(Tensor y, Tensor slot_of, Tensor? weights) -> Tensor", &moe_combine);
+  m.def("moe_combine_bwd(Tensor dout, Tensor y, Tensor slot_of, Tensor weights) -> (Tensor, Tensor)", &moe_combine_bwd);
+  m.def("grouped_gemm_rows(Tensor x, Tensor w, bool w_kmajor, Tensor tile_expert) -> Tensor", &grouped_gemm_rows);
+  m.def("grouped_gemm_wgrad(Tensor dy, Tensor x, Tensor offsets, bool out_f32) -> Tensor", &grouped_gemm_wgrad);
   m.def("gemm(Tensor A, Tensor B, Tensor? D, bool a_kmajor, bool b_kmajor, bool out_f32, bool accumulate) -> Tensor", &gemm);
 }

@@ -120,6 +120,29 @@ int fp8_quantize(const void* x, void* q, void* qt, const float* scale, float* am
 int gemm_fp8(const void* A, const void* B, void* D, const float* scale_a, const float* scale_b, const void* bias, int M,
              int N, int K, long long ldd, bool a_e5m2, bool b_e5m2, int* status, cudaStream_t st);
 
+// ---- mixture of experts (moe.cu, gemm_grouped.cu)
+int moe_router(const void* logits, void* probs, long long* idx, void* weights, int* counts, float* probsum, long long tokens,
+               int E, int K, bool renorm, bool is_bf16, cudaStream_t st);
+int moe_plan(const int* counts, int* offsets, int* tile_expert, int* cursors, int* total, int E, int max_tiles, cudaStream_t st);
+int moe_permute(const void* x, const long long* idx, const int* counts, const int* offsets, int* cursors, void* sorted, int* slot_of,
+                long long tokens, int K, int D, int E, bool is_bf16, cudaStream_t st);
+int moe_combine(const void* y, const int* slot_of, const void* weights, void* out, long long tokens, int K, int D, bool is_bf16,
+                cudaStream_t st);
+int moe_combine_bwd(const void* dout, const void* y, const int* slot_of, const void* weights, void* dy, float* dw, long long tokens,
+                    int K, int D, bool is_bf16, cudaStream_t st);
+struct GroupedParams {
+  const int* tile_expert;     // rows mode: expert of every 128-row tile of the sorted buffer (-1 = unused tile)
+  const int* offsets;         // wgrad mode: padded segment offsets [E+1]
+  int b_rows_per_expert;      // row stride between consecutive experts in the 2-D weight view
+  int b_row_offset;           // first row of the wanted matrix inside an expert's block
+  long long d_expert_stride;  // wgrad mode: elements between consecutive experts in the output
+  int E;
+};
+int gemm_grouped_rows(const void* X, const void* W, void* Y, int R, int N, int K, long long ldx, long long w_rows, long long w_cols,
+                      long long ldy, bool w_kmajor, const GroupedParams& g, int* status, cudaStream_t st);
+int gemm_grouped_wgrad(const void* dY, const void* X, void* D, int R, int N, int K, long long lddy, long long ldx, long long ldd,
+                       bool out_f32, bool accumulate, const GroupedParams& g, int* status, cudaStream_t st);
+
 // Skinny GEMM for M <= 256 (gemm_skinny.cu): Y[M,N] bf16 = X[M,K] . W[N,K]^T with the weight as the MMA's M operand and
 // K split over a thread-block cluster (reduction through distributed shared memory; no workspace).
 int gemm_skinny_splits(int N, int K, int tok);
