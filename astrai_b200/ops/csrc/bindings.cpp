@@ -350,6 +350,111 @@ std::tuple<Tensor, Tensor, Tensor> flash_bwd(const Tensor& q, const Tensor& k, c
   return {dq, dk, dv};
 }
 
+// ---- context-parallel flash attention (zig-zag sequence sharding, see CpAttn in launchers.h).
+// q / out are the rank's 2 * chunk rows per batch entry, k_full / v_full the gathered [batch * S, Hkv, D] keys.
+ab::CpAttn cp_params(int64_t batch, int64_t chunk, int64_t world, int64_t rank, const std::vector<int64_t>& flag_ptrs,
+                     int64_t unit, int64_t max_units, int64_t epoch, double timeout_s) {
+  TORCH_CHECK(world >= 2 && world <= 8 && rank >= 0 && rank < world, "context parallel: world in 2..8, rank in range");
+  TORCH_CHECK(chunk > 0 && chunk % 128 == 0, "context parallel: chunk must be a positive multiple of 128");
+  ab::CpAttn cp;
+  cp.world = (int)world, cp.rank = (int)rank, cp.chunk = (int)chunk, cp.batch = (int)batch;
+  cp.k_vis = (int)((2 * world - rank) * chunk);
+  cp.unit = (int)unit, cp.max_units = (int)max_units, cp.epoch = (int)epoch;
+  cp.timeout_ns = (unsigned long long)(timeout_s * 1e9);
+  TORCH_CHECK(flag_ptrs.empty() || (int64_t)flag_ptrs.size() == world, "context parallel: one flag pointer per rank");
+  for (size_t i = 0; i < flag_ptrs.size(); ++i) cp.flags[i] = reinterpret_cast<void*>(flag_ptrs[i]);
+  return cp;
+}
+
+std::tuple<Tensor, Tensor> cp_flash_fwd(const Tensor& q, const Tensor& k_full, const Tensor& v_full, int64_t batch,
+                                        int64_t chunk, int64_t world, int64_t rank, double scale,
+                                        std::vector<int64_t> kv_src_ptrs, std::vector<int64_t> flag_ptrs, int64_t unit,
+                                        int64_t max_units, int64_t epoch, int64_t n_copy_ctas,
+                                        const c10::optional<Tensor>& chunk_state, double timeout_s) {
+  auto ok = [](const Tensor& t) {
+    return t.is_cuda() && t.dim() == 3 && t.scalar_type() == at::kBFloat16 && t.is_contiguous() &&
+           (reinterpret_cast<uintptr_t>(t.data_ptr()) & 15) == 0;
+  };
+  TORCH_CHECK(ok(q) && ok(k_full) && ok(v_full), "cp_flash_fwd: contiguous bf16 [tokens, heads, D] tensors");
+  const int64_t S = 2 * world * chunk;
+  TORCH_CHECK(q.size(0) == batch * 2 * chunk && k_full.size(0) == batch * S && v_full.sizes() == k_full.sizes(), "cp_flash_fwd: shapes");
+  const int D = (int)q.size(2);
+  ab::CpAttn cp = cp_params(batch, chunk, world, rank, flag_ptrs, unit, max_units, epoch, timeout_s);
+  if (!kv_src_ptrs.empty()) {
+    TORCH_CHECK((int64_t)kv_src_ptrs.size() == world && (int64_t)flag_ptrs.size() == world, "cp_flash_fwd: one source / flag pointer per rank");
+    TORCH_CHECK(chunk_state.has_value() && chunk_state->is_cuda() && chunk_state->scalar_type() == at::kInt && chunk_state->numel() >= 16, "cp_flash_fwd: chunk_state int32 [16]");
+    for (int64_t i = 0; i < world; ++i) cp.kv_src[i] = reinterpret_cast<const void*>(kv_src_ptrs[i]);
+    cp.k_full = k_full.data_ptr(), cp.v_full = v_full.data_ptr();
+    cp.chunk_flags = chunk_state->data_ptr<int>(), cp.chunk_counter = chunk_state->data_ptr<int>() + 8;
+    cp.n_copy_ctas = (int)n_copy_ctas;
+  }
+  const c10::cuda::CUDAGuard guard(q.device());
+  Tensor out = at::empty_like(q);
+  Tensor lse = at::empty({q.size(1), q.size(0)}, q.options().dtype(at::kFloat));
+  count();
+  const int rc = ab::flash_fwd(q.data_ptr(), k_full.data_ptr(), v_full.data_ptr(), out.data_ptr(), lse.data_ptr<float>(), nullptr,
+                               nullptr, (int)batch, (int)(2 * chunk), (int)S, (int)(2 * chunk), q.size(0), k_full.size(0),
+                               (int)q.size(1), (int)k_full.size(1), D, q.stride(0), k_full.stride(0), v_full.stride(0),
+                               out.stride(0), (float)scale, true, status_tensor(q.device()).data_ptr<int>(), stream(), &cp);
+  TORCH_CHECK(rc == 0, "cp_flash_fwd launch failed with code ", rc);
+  return {out, lse};
+}
+
+// Returns dq and, when no staging pointers are given, this rank's partial dk / dv over the gathered keys (zero where it
+// sees nothing); with staging pointers the partials go to their owners and two empty tensors come back.
+std::tuple<Tensor, Tensor, Tensor> cp_flash_bwd(const Tensor& q, const Tensor& k_full, const Tensor& v_full, const Tensor& out,
+                                                const Tensor& dout, const Tensor& lse, int64_t batch, int64_t chunk,
+                                                int64_t world, int64_t rank, double scale, std::vector<int64_t> stage_ptrs,
+                                                std::vector<int64_t> flag_ptrs, int64_t unit, int64_t max_units, int64_t epoch,
+                                                const c10::optional<Tensor>& tile_counter, double timeout_s) {
+  auto ok = [](const Tensor& t) {
+    return t.is_cuda() && t.dim() == 3 && t.scalar_type() == at::kBFloat16 && t.is_contiguous() &&
+           (reinterpret_cast<uintptr_t>(t.data_ptr()) & 15) == 0;
+  };
+  TORCH_CHECK(ok(q) && ok(k_full) && ok(v_full) && ok(out) && ok(dout), "cp_flash_bwd: contiguous bf16 [tokens, heads, D] tensors");
+  const int64_t S = 2 * world * chunk;
+  TORCH_CHECK(q.size(0) == batch * 2 * chunk && k_full.size(0) == batch * S && v_full.sizes() == k_full.sizes(), "cp_flash_bwd: shapes");
+  const int D = (int)q.size(2);
+  ab::CpAttn cp = cp_params(batch, chunk, world, rank, flag_ptrs, unit, max_units, epoch, timeout_s);
+  const bool scatter = !stage_ptrs.empty();
+  if (scatter) {
+    TORCH_CHECK((int64_t)stage_ptrs.size() == world && (int64_t)flag_ptrs.size() == world, "cp_flash_bwd: one staging / flag pointer per rank");
+    TORCH_CHECK(tile_counter.has_value() && tile_counter->is_cuda() && tile_counter->scalar_type() == at::kInt && tile_counter->numel() >= 8, "cp_flash_bwd: tile_counter int32 [8]");
+    for (int64_t i = 0; i < world; ++i) cp.stage[i] = reinterpret_cast<void*>(stage_ptrs[i]);
+    cp.tile_counter = tile_counter->data_ptr<int>();
+  }
+  const c10::cuda::CUDAGuard guard(q.device());
+  Tensor dq = at::empty_like(q);
+  Tensor dk = scatter ? at::empty({0}, q.options()) : at::zeros_like(k_full);
+  Tensor dv = scatter ? at::empty({0}, q.options()) : at::zeros_like(v_full);
+  Tensor delta = at::empty({2, q.size(1), q.size(0)}, q.options().dtype(at::kFloat));
+  count(3);
+  const int rc = ab::flash_bwd(q.data_ptr(), k_full.data_ptr(), v_full.data_ptr(), out.data_ptr(), dout.data_ptr(),
+                               lse.data_ptr<float>(), delta.data_ptr<float>(), dq.data_ptr(), scatter ? nullptr : dk.data_ptr(),
+                               scatter ? nullptr : dv.data_ptr(), nullptr, nullptr, (int)batch, (int)(2 * chunk), (int)S,
+                               (int)(2 * chunk), cp.k_vis, q.size(0), k_full.size(0), (int)q.size(1), (int)k_full.size(1), D,
+                               q.stride(0), k_full.stride(0), v_full.stride(0), out.stride(0), dout.stride(0), dq.stride(0),
+                               k_full.stride(0), (float)scale, true, status_tensor(q.device()).data_ptr<int>(), stream(), &cp);
+  TORCH_CHECK(rc == 0, "cp_flash_bwd launch failed with code ", rc);
+  return {dq, dk, dv};
+}
+
+void cp_dkv_reduce(Tensor dk_local, Tensor dv_local, int64_t batch, int64_t chunk, int64_t world, int64_t rank,
+                   std::vector<int64_t> stage_ptrs, std::vector<int64_t> flag_ptrs, int64_t unit, int64_t max_units,
+                   int64_t epoch, double timeout_s) {
+  TORCH_CHECK(dk_local.is_cuda() && dk_local.is_contiguous() && dk_local.scalar_type() == at::kBFloat16 && dk_local.dim() == 3 &&
+                  dv_local.is_contiguous() && dv_local.sizes() == dk_local.sizes() && dv_local.scalar_type() == at::kBFloat16,
+              "cp_dkv_reduce: contiguous bf16 [batch * 2 * chunk, Hkv, D] outputs");
+  TORCH_CHECK(dk_local.size(0) == batch * 2 * chunk && (int64_t)stage_ptrs.size() == world && (int64_t)flag_ptrs.size() == world, "cp_dkv_reduce: shapes");
+  ab::CpAttn cp = cp_params(batch, chunk, world, rank, flag_ptrs, unit, max_units, epoch, timeout_s);
+  for (int64_t i = 0; i < world; ++i) cp.stage[i] = reinterpret_cast<void*>(stage_ptrs[i]);
+  const c10::cuda::CUDAGuard guard(dk_local.device());
+  count();
+  const int rc = ab::cp_dkv_reduce(dk_local.data_ptr(), dv_local.data_ptr(), (int)batch, (int)(dk_local.size(1) * dk_local.size(2)),
+                                   cp, status_tensor(dk_local.device()).data_ptr<int>(), stream());
+  TORCH_CHECK(rc == 0, "cp_dkv_reduce launch failed with code ", rc);
+}
+
 // ---- fused FSDP over peer memory.  Pointer lists are raw device addresses of the same symmetric buffer on each rank.
 ab::CommPeers peers_from(const std::vector<int64_t>& ptrs) {
   TORCH_CHECK(ptrs.size() >= 1 && ptrs.size() <= 8, "peer pointer list must have 1..8 entries");
@@ -656,6 +761,9 @@ TORCH_LIBRARY(astrai_b200, m) {
   m.def("kernel_status_reset(Tensor like) -> ()", &kernel_status_reset);
   m.def("flash_fwd(Tensor q, Tensor k, Tensor v, Tensor? cu_q, Tensor? cu_k, int batch, int sq, int sk, int max_q, bool causal, float scale) -> (Tensor, Tensor)", &flash_fwd);
   m.def("flash_bwd(Tensor q, Tensor k, Tensor v, Tensor out, Tensor dout, Tensor lse, Tensor? cu_q, Tensor? cu_k, int batch, int sq, int sk, int max_q, int max_k, bool causal, float scale) -> (Tensor, Tensor, Tensor)", &flash_bwd);
+  m.def("cp_flash_fwd(Tensor q, Tensor k_full, Tensor v_full, int batch, int chunk, int world, int rank, float scale, int[] kv_src_ptrs, int[] flag_ptrs, int unit, int max_units, int epoch, int n_copy_ctas, Tensor? chunk_state, float timeout_s) -> (Tensor, Tensor)", &cp_flash_fwd);
+  m.def("cp_flash_bwd(Tensor q, Tensor k_full, Tensor v_full, Tensor out, Tensor dout, Tensor lse, int batch, int chunk, int world, int rank, float scale, int[] stage_ptrs, int[] flag_ptrs, int unit, int max_units, int epoch, Tensor? tile_counter, float timeout_s) -> (Tensor, Tensor, Tensor)", &cp_flash_bwd);
+  m.def("cp_dkv_reduce(Tensor(a!) dk_local, Tensor(b!) dv_local, int batch, int chunk, int world, int rank, int[] stage_ptrs, int[] flag_ptrs, int unit, int max_units, int epoch, float timeout_s) -> ()", &cp_dkv_reduce);
   m.def("tp_gemm_allgather_(int[] xfull_ptrs, Tensor W, bool w_kmajor, Tensor(a!) Y, int[] flag_ptrs, Tensor(b!) chunk_flags, Tensor(c!) chunk_counter, int rank, int unit, int max_units, int epoch, float timeout_s, int n_copy_ctas) -> ()", &tp_gemm_allgather_);
   m.def("tp_gemm_reducescatter_(Tensor X, Tensor W, bool w_kmajor, int[] stage_ptrs, Tensor(a!) out, int[] flag_ptrs, Tensor(b!) tile_counter, int rank, int unit, int max_units, int epoch, float timeout_s, bool fuse_reduce) -> ()", &tp_gemm_reducescatter_);
   m.def("tp_reduce_(Tensor stage, Tensor(a!) out, int world) -> ()", &tp_reduce_);

@@ -21,6 +21,7 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include "flash_cp.cuh"
 #include "launchers.h"
 #include "tcgen05.cuh"
 #include "tma_host.h"
@@ -30,6 +31,7 @@ namespace {
 
 using namespace tc;
 using namespace tmah;
+using namespace cpx;
 
 constexpr int BWD_THREADS = 320, SUB = 64, QDO_STAGES = 3, KV_STAGES_B = 4;  // warp 0 TMA, warp 1 MMA, warps 2..9 rows (two per TMEM quarter)
 constexpr int BLK128 = 128 * 128;  // [128 rows x 64 cols] swizzled block
@@ -143,19 +145,30 @@ flash_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
                       const float* __restrict__ lse2g, const float* __restrict__ delta, __nv_bfloat16* __restrict__ dK,
                       __nv_bfloat16* __restrict__ dV, const int* __restrict__ cu_q, const int* __restrict__ cu_k, int sq,
                       int sk, int Hq, int Hkv, long long dk_row_stride, long long total_q, float scale, int causal,
-                      int* __restrict__ status) {
+                      int* __restrict__ status, const CpAttn cp) {
   using C = DkvCfg<D>;
   // grid = (kv heads x sequences, key tiles): blocks are dispatched in linear order, so every key tile 0 (the one
   // with the most query tiles under a causal mask) starts before any lighter tile - longest work first.
   const int kvh = (int)blockIdx.x % Hkv;
-  const SeqInfoB si = seq_info_b(cu_q, cu_k, (int)blockIdx.x / Hkv, sq, sk);
+  const int bseq = (int)blockIdx.x / Hkv;
+  SeqInfoB si = seq_info_b(cu_q, cu_k, bseq, sq, sk);
+  if (cp.world > 1) si.k_len = cp.k_vis;
   const int k0 = (int)blockIdx.y * 128;
   if (k0 >= si.k_len) return;
-  const int G = Hq / Hkv, off = si.k_len - si.q_len;
-  int q_lo = 0;
-  if (causal) q_lo = max(0, k0 - off) / SUB * SUB;
-  const int n_sub = max(0, (si.q_len - q_lo + SUB - 1) / SUB);
+  const int G = Hq / Hkv;
+  // Query rows come in two ranges with their own causal offset: [0, split) at off_a (context parallel only) and
+  // [split, q_len) at off_b.  Of each range only the 64-row sub-tiles that can see this key tile are visited.
+  const int split = cp.world > 1 ? cp.chunk : 0;
+  const int off_a = cp.rank * cp.chunk, off_b = si.k_len - si.q_len;
+  int lo1 = 0, lo2 = split;
+  if (causal) {
+    lo1 = min(split, max(0, k0 - off_a) / SUB * SUB);
+    lo2 = max(split, max(0, k0 - off_b) / SUB * SUB);
+  }
+  const int n1 = (split - lo1) / SUB;
+  const int n_sub = n1 + max(0, (si.q_len - lo2 + SUB - 1) / SUB);
   const int n_it = n_sub * G;
+  auto sub_start = [&](int idx) { return idx < n1 ? lo1 + idx * SUB : lo2 + (idx - n1) * SUB; };
 
   extern __shared__ uint8_t smem_raw[];
   const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
@@ -204,7 +217,7 @@ flash_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
         const int st = it % QDO_STAGES;
         const uint32_t ph = ((it / QDO_STAGES) & 1) ^ 1u;
         if (!mbar_wait(BAR(A_QE + st), ph, abort_flag)) { ok = false; break; }
-        const int h = kvh * G + it / n_sub, qs = q_lo + (it % n_sub) * SUB;
+        const int h = kvh * G + it / n_sub, qs = sub_start(it % n_sub);
         mbar_expect_tx(BAR(A_QF + st), 2 * C::QS_BYTES);
 #pragma unroll
         for (int kb = 0; kb < C::NB; ++kb) {
@@ -275,12 +288,13 @@ flash_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
     const int kidx = k0 + row;
     const bool key_live = kidx < si.k_len;
     const float scale_log2 = scale * LOG2E;
-    const int qmin = causal ? kidx - off : -0x40000000;  // query q sees this key iff q >= kidx - off
     uint8_t* my_pt = pt_ptr + g * C::PT_BYTES;
     uint8_t* my_dst = dst_ptr + g * C::PT_BYTES;
     bool ok = true;
     for (int it = g; it < n_it; it += 2) {
-      const int h = kvh * G + it / n_sub, qs = q_lo + (it % n_sub) * SUB;
+      const int h = kvh * G + it / n_sub, qs = sub_start(it % n_sub);
+      const int off = qs < split ? off_a : off_b;
+      const int qmin = causal ? kidx - off : -0x40000000;  // query q sees this key iff q >= kidx - off
       ok = __all_sync(0xffffffffu, mbar_wait(BAR(A_SF + g), (it >> 1) & 1, abort_flag));
       if (!ok) break;
       tc_fence_after();
@@ -343,10 +357,24 @@ flash_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
     }
     const int half = g;  // each group writes half of the accumulator columns
     if (ok) {
-      const long long tok = (long long)si.k_start + kidx;
       constexpr int CH = D / 64;  // 32-column chunks per half
-      store_acc_row(t_lane + 256, dV + tok * dk_row_stride + (long long)kvh * D, key_live, n_it > 0, half * CH, half * CH + CH, 1.f);
-      store_acc_row(t_lane + 384, dK + tok * dk_row_stride + (long long)kvh * D, key_live, n_it > 0, half * CH, half * CH + CH, scale);
+      __nv_bfloat16 *dv_row, *dk_row;
+      if (cp.world > 1 && cp.stage[0] != nullptr) {
+        // context parallel: the tile goes to the staging slot [this rank] of the rank that owns these keys
+        const int ch = k0 / cp.chunk, owner = chunk_owner(ch, cp.world);
+        const long long local_row = (ch >= cp.world ? cp.chunk : 0) + (kidx - ch * cp.chunk);
+        const long long row_elems = (long long)Hkv * D, plane = (long long)cp.batch * 2 * cp.chunk * row_elems;
+        __nv_bfloat16* slot = reinterpret_cast<__nv_bfloat16*>(cp.stage[owner]) + (long long)cp.rank * 2 * plane;
+        dk_row = slot + ((long long)bseq * 2 * cp.chunk + local_row) * row_elems + (long long)kvh * D;
+        dv_row = dk_row + plane;
+      } else {
+        const long long tok = (long long)si.k_start + kidx;
+        dv_row = dV + tok * dk_row_stride + (long long)kvh * D;
+        dk_row = dK + tok * dk_row_stride + (long long)kvh * D;
+      }
+      store_acc_row(t_lane + 256, dv_row, key_live, n_it > 0, half * CH, half * CH + CH, 1.f);
+      store_acc_row(t_lane + 384, dk_row, key_live, n_it > 0, half * CH, half * CH + CH, scale);
+      if (cp.world > 1 && cp.stage[0] != nullptr) __threadfence_system();
     } else if (lane == 0) {
       atomicMax(status, ERR_BWD_ROWS);
       *abort_flag = 1;
@@ -358,6 +386,58 @@ flash_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
   if (warp == 1) {
     tc_fence_after();
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(512u) : "memory");
+  }
+  if (cp.world > 1 && cp.stage[0] != nullptr && threadIdx.x == 0 && *abort_flag == 0) {
+    // the last tile this rank owes an owner tells it that the slot is complete
+    const int owner = chunk_owner(k0 / cp.chunk, cp.world);
+    const int expected = (1 + (owner >= cp.rank ? 1 : 0)) * (cp.chunk / 128) * Hkv * cp.batch;
+    const int done = atomicAdd(&cp.tile_counter[owner], 1);
+    if (done == expected - 1) {
+      cp.tile_counter[owner] = 0;
+      __threadfence_system();
+      comm::st_release_sys(flag_slot(cp.flags[owner], KIND_CP_DKV, cp.rank, cp.unit, cp.max_units), cp.epoch);
+    }
+  }
+}
+
+// Owner side of the context-parallel dK / dV scatter: sum the contributors' staging slots.  Local rows [0, c) (chunk
+// `rank`) are seen by every rank, rows [c, 2c) (chunk 2W - 1 - rank) by the ranks 0..rank.
+__global__ void cp_dkv_reduce_kernel(__nv_bfloat16* __restrict__ dk, __nv_bfloat16* __restrict__ dv, long long row_elems,
+                                     const CpAttn cp, int* __restrict__ status) {
+  __shared__ int s_ok;
+  if (threadIdx.x == 0) {
+    int ok = 1;
+    for (int src = 0; src < cp.world && ok; ++src)
+      ok = comm::wait_flag(flag_slot(cp.flags[cp.rank], KIND_CP_DKV, src, cp.unit, cp.max_units), cp.epoch, cp.timeout_ns) ? 1 : 0;
+    if (!ok) atomicMax(status, ERR_CP_REDUCE);
+    s_ok = ok;
+  }
+  __syncthreads();
+  if (!s_ok) return;
+  const long long vec_per_row = row_elems / 8, rows = (long long)cp.batch * 2 * cp.chunk;
+  const long long plane_vec = rows * vec_per_row, total = 2 * plane_vec;
+  const uint4* stage = reinterpret_cast<const uint4*>(cp.stage[cp.rank]);
+  for (long long v = (long long)blockIdx.x * blockDim.x + threadIdx.x; v < total; v += (long long)gridDim.x * blockDim.x) {
+    const long long in_plane = v % plane_vec;
+    const int local_row = (int)((in_plane / vec_per_row) % (2 * cp.chunk));
+    const int n_src = local_row < cp.chunk ? cp.world : cp.rank + 1;
+    float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+    for (int src = 0; src < n_src; ++src) {
+      const uint4 x = comm::ld_sys_u4(stage + (long long)src * total + v);
+      const __nv_bfloat162* px = reinterpret_cast<const __nv_bfloat162*>(&x);
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const float2 f = __bfloat1622float2(px[i]);
+        acc[2 * i] += f.x;
+        acc[2 * i + 1] += f.y;
+      }
+    }
+    uint4 o;
+    uint32_t* po = reinterpret_cast<uint32_t*>(&o);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) po[i] = pack2(acc[2 * i], acc[2 * i + 1]);
+    uint4* out = reinterpret_cast<uint4*>(v < plane_vec ? dk : dv);
+    out[in_plane] = o;
   }
 }
 
@@ -377,16 +457,19 @@ flash_bwd_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
                     const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v,
                     const float* __restrict__ lse2g, const float* __restrict__ delta, __nv_bfloat16* __restrict__ dQ,
                     const int* __restrict__ cu_q, const int* __restrict__ cu_k, int sq, int sk, int Hq, int Hkv,
-                    long long dq_row_stride, long long total_q, float scale, int causal, int* __restrict__ status) {
+                    long long dq_row_stride, long long total_q, float scale, int causal, int* __restrict__ status,
+                    const CpAttn cp) {
   using C = DqCfg<D>;
   // grid = (query heads x sequences, query tiles), heaviest (last) causal tiles dispatched first
   const int h = (int)blockIdx.x % Hq;
-  const SeqInfoB si = seq_info_b(cu_q, cu_k, (int)blockIdx.x / Hq, sq, sk);
+  SeqInfoB si = seq_info_b(cu_q, cu_k, (int)blockIdx.x / Hq, sq, sk);
+  if (cp.world > 1) si.k_len = cp.k_vis;
   const int n_q_tiles = (si.q_len + 127) / 128;
   const int qt = n_q_tiles - 1 - (int)blockIdx.y;
   if (qt < 0) return;
   const int kvh = h / (Hq / Hkv);
-  const int q0 = qt * 128, off = si.k_len - si.q_len;
+  const int q0 = qt * 128;
+  const int off = (cp.world > 1 && q0 < cp.chunk) ? cp.rank * cp.chunk : si.k_len - si.q_len;
   int kv_end = si.k_len;
   if (causal) kv_end = min(si.k_len, q0 + 128 + off);
   if (kv_end < 0) kv_end = 0;
@@ -573,7 +656,7 @@ int launch_bwd(const void* q, const void* k, const void* v, const void* out, con
                float* delta, void* dq, void* dk, void* dv, const int* cu_q, const int* cu_k, int batch, int sq, int sk,
                int max_q, int max_k, long long total_q, long long total_k, int Hq, int Hkv, long long q_rs, long long k_rs,
                long long v_rs, long long o_rs, long long do_rs, long long dq_rs, long long dk_rs, float scale, bool causal,
-               int* status, cudaStream_t st) {
+               int* status, cudaStream_t st, const CpAttn& cp) {
   CUtensorMap mq64, mdo64, mk128, mv128, mq128, mdo128, mk64, mv64;
   bool ok = cache().get(&mq64, q, (long long)Hq * D, total_q, q_rs, 64, 64) &&
             cache().get(&mdo64, dout, (long long)Hq * D, total_q, do_rs, 64, 64) &&
@@ -599,10 +682,10 @@ int launch_bwd(const void* q, const void* k, const void* v, const void* out, con
   const dim3 grid_a(Hkv * batch, (max_k + 127) / 128, 1);
   kern_a<<<grid_a, BWD_THREADS, DkvCfg<D>::SMEM, st>>>(mq64, mdo64, mk128, mv128, lse2, delta, (__nv_bfloat16*)dk,
                                                        (__nv_bfloat16*)dv, cu_q, cu_k, sq, sk, Hq, Hkv, dk_rs, total_q,
-                                                       scale, causal ? 1 : 0, status);
+                                                       scale, causal ? 1 : 0, status, cp);
   const dim3 grid_b(Hq * batch, (max_q + 127) / 128, 1);
   kern_b<<<grid_b, BWD_THREADS, DqCfg<D>::SMEM, st>>>(mq128, mdo128, mk64, mv64, lse2, delta, (__nv_bfloat16*)dq, cu_q,
-                                                      cu_k, sq, sk, Hq, Hkv, dq_rs, total_q, scale, causal ? 1 : 0, status);
+                                                      cu_k, sq, sk, Hq, Hkv, dq_rs, total_q, scale, causal ? 1 : 0, status, cp);
   return cudaGetLastError() == cudaSuccess ? 0 : -5;
 }
 
@@ -612,16 +695,36 @@ int flash_bwd(const void* q, const void* k, const void* v, const void* out, cons
               float* delta, void* dq, void* dk, void* dv, const int* cu_q, const int* cu_k, int batch, int sq, int sk,
               int max_q, int max_k, long long total_q, long long total_k, int Hq, int Hkv, int D, long long q_rs,
               long long k_rs, long long v_rs, long long o_rs, long long do_rs, long long dq_rs, long long dk_rs, float scale,
-              bool causal, int* status, cudaStream_t st) {
+              bool causal, int* status, cudaStream_t st, const CpAttn* cp_in) {
   if (batch <= 0 || total_q <= 0) return 0;
   if (Hkv <= 0 || Hq % Hkv) return -1;
+  CpAttn cp;
+  if (cp_in != nullptr && cp_in->world > 1) {
+    cp = *cp_in;
+    if (cu_q || cu_k || !causal || cp.world > 8 || cp.rank < 0 || cp.rank >= cp.world) return -8;
+    if (cp.chunk <= 0 || cp.chunk % 128 || sq != 2 * cp.chunk || sk != 2 * cp.world * cp.chunk) return -8;
+    if (cp.k_vis != (2 * cp.world - cp.rank) * cp.chunk || max_k != cp.k_vis) return -8;
+    if (cp.stage[0] != nullptr && cp.tile_counter == nullptr) return -9;
+    cp.batch = batch;
+  }
   if (D == 128)
     return launch_bwd<128>(q, k, v, out, dout, lse, delta, dq, dk, dv, cu_q, cu_k, batch, sq, sk, max_q, max_k, total_q,
-                           total_k, Hq, Hkv, q_rs, k_rs, v_rs, o_rs, do_rs, dq_rs, dk_rs, scale, causal, status, st);
+                           total_k, Hq, Hkv, q_rs, k_rs, v_rs, o_rs, do_rs, dq_rs, dk_rs, scale, causal, status, st, cp);
   if (D == 64)
     return launch_bwd<64>(q, k, v, out, dout, lse, delta, dq, dk, dv, cu_q, cu_k, batch, sq, sk, max_q, max_k, total_q,
-                          total_k, Hq, Hkv, q_rs, k_rs, v_rs, o_rs, do_rs, dq_rs, dk_rs, scale, causal, status, st);
+                          total_k, Hq, Hkv, q_rs, k_rs, v_rs, o_rs, do_rs, dq_rs, dk_rs, scale, causal, status, st, cp);
   return -3;
+}
+
+int cp_dkv_reduce(void* dk_local, void* dv_local, int batch, int row_elems, const CpAttn& cp_in, int* status, cudaStream_t st) {
+  if (cp_in.world <= 1 || cp_in.stage[0] == nullptr || row_elems % 8 || batch <= 0) return -1;
+  CpAttn cp = cp_in;
+  cp.batch = batch;
+  const long long total = 2LL * batch * 2 * cp.chunk * (row_elems / 8);
+  const long long want = (total + 255) / 256;
+  const int blocks = (int)(want < 148 * 8 ? want : 148 * 8);
+  cp_dkv_reduce_kernel<<<blocks, 256, 0, st>>>((__nv_bfloat16*)dk_local, (__nv_bfloat16*)dv_local, row_elems, cp, status);
+  return cudaGetLastError() == cudaSuccess ? 0 : -5;
 }
 
 }  // namespace ab

@@ -16,6 +16,10 @@
 // Takes the place of F.scaled_dot_product_attention / flash_attn in the reference's training and prefill paths
 // (astrai/extension/backend/attention.py:453-468, 663-669) and of its mma.sync prefill kernel
 // (csrc/kernels/attention/prefill_split_q_mma.cuh:19-157).
+// Context parallel (CpAttn, world > 1): the keys are the gathered sequence; a few extra CTAs at the front of the grid
+// pull every rank's K / V chunks from peer memory into the local gathered buffer (bulk copies through shared memory,
+// ring order) and publish one flag per source rank, while the attention CTAs start with the chunks that are already
+// local and poll the flag of a chunk's owner before its first TMA load - gather and attention are ONE launch.
 // Every mbarrier wait is bounded; a wait that runs out raises the CTA's abort flag, records a code in `status`,
 // and all roles fall through to the common exit where TMEM is freed.
 #include <cuda.h>
@@ -23,6 +27,7 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include "flash_cp.cuh"
 #include "launchers.h"
 #include "tcgen05.cuh"
 #include "tma_host.h"
@@ -32,6 +37,7 @@ namespace {
 
 using namespace tc;
 using namespace tmah;
+using namespace cpx;
 
 constexpr int BQ = 128, BKV = 128, FA_THREADS = 192, KV_STAGES = 2;
 constexpr int BLK_BYTES = 128 * 128;  // one [128 rows x 64 bf16] swizzled block
@@ -57,22 +63,112 @@ __device__ __forceinline__ SeqInfo seq_info(const int* cu_q, const int* cu_k, in
   return s;
 }
 
+// Gather CTA (one thread works): announce that this rank's K / V source is complete, then, for every source rank in
+// ring order starting with this one, wait (bounded) for its announcement and move this CTA's share of its four
+// segments (K | V) x (first | second chunk) per batch entry into the gathered buffers: up to NS pieces of 32 KB are in
+// flight through shared memory at a time.  The last CTA to finish a source rank publishes chunk_flags[src] = epoch.
+template <int SMEM_BYTES>
+__device__ void gather_kv(const CpAttn& cp, int cta, int row_bytes, int* status) {
+  constexpr int PIECE = 32768;
+  constexpr int NS = (SMEM_BYTES - 1024 - 256) / PIECE;
+  static_assert(NS >= 1, "no room for a copy slot");
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  uint8_t* aligned = smem_raw + (base - smem_u32(smem_raw));
+  uint64_t* bars = reinterpret_cast<uint64_t*>(aligned + NS * PIECE);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(bars + NS);
+  const uint32_t bar0 = smem_u32(bars);
+  for (int s = 0; s < NS; ++s) mbar_init(bar0 + 8u * s, 1);
+  *abort_flag = 0;
+  asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  fence_async_smem();
+
+  const int W = cp.world, r = cp.rank, n_copy = cp.n_copy_ctas;
+  if (cta == 0) {
+    __threadfence_system();
+    for (int p = 0; p < W; ++p) comm::st_release_sys(flag_slot(cp.flags[p], KIND_CP_KV, r, cp.unit, cp.max_units), cp.epoch);
+  }
+  const long long seg_bytes = (long long)cp.chunk * row_bytes;
+  const int pps = (int)((seg_bytes + PIECE - 1) / PIECE);  // pieces per segment
+  const int total = 4 * cp.batch * pps;
+  const long long S = 2LL * W * cp.chunk;
+  uint32_t phase = 0;
+  for (int i = 0; i < W; ++i) {
+    const int src = (r + i) % W;
+    if (i > 0 && !comm::wait_flag(flag_slot(cp.flags[r], KIND_CP_KV, src, cp.unit, cp.max_units), cp.epoch, cp.timeout_ns)) {
+      atomicMax(status, ERR_CP_COPY);
+      return;  // the attention CTAs run out of time on the chunk flag and report as well
+    }
+    const uint8_t* from = reinterpret_cast<const uint8_t*>(cp.kv_src[src]);
+    for (int first = cta; first < total; first += n_copy * NS) {
+      uint8_t* dst[NS];
+      uint32_t bytes[NS];
+      int n = 0;
+      for (; n < NS; ++n) {
+        const int pc = first + n * n_copy;
+        if (pc >= total) break;
+        const int seg = pc / pps, pi = pc % pps;
+        const int kv = seg / (2 * cp.batch), b = (seg >> 1) % cp.batch, half = seg & 1;
+        const long long src_off = (((long long)kv * cp.batch + b) * 2 + half) * seg_bytes + (long long)pi * PIECE;
+        const long long dst_off = ((long long)b * S + (long long)chunk_of(src, half, W) * cp.chunk) * row_bytes + (long long)pi * PIECE;
+        dst[n] = reinterpret_cast<uint8_t*>(kv ? cp.v_full : cp.k_full) + dst_off;
+        bytes[n] = (uint32_t)min((long long)PIECE, seg_bytes - (long long)pi * PIECE);
+        mbar_expect_tx(bar0 + 8u * n, bytes[n]);
+        bulk_load(base + n * PIECE, from + src_off, bytes[n], bar0 + 8u * n);
+      }
+      for (int s = 0; s < n; ++s) {
+        if (!mbar_wait(bar0 + 8u * s, phase, abort_flag)) {
+          atomicMax(status, ERR_CP_COPY);
+          return;
+        }
+        bulk_store(dst[s], base + s * PIECE, bytes[s]);
+      }
+      // barriers of unused slots did not flip: give them the phase the used ones have now
+      for (int s = n; s < NS; ++s) {
+        mbar_arrive(bar0 + 8u * s);
+        if (!mbar_wait(bar0 + 8u * s, phase, abort_flag)) return;
+      }
+      bulk_commit();
+      bulk_wait_read();  // the slots may be overwritten
+      phase ^= 1u;
+    }
+    bulk_wait_all();  // every store of this source rank has landed
+    fence_async_global();
+    __threadfence();
+    const int done = atomicAdd(&cp.chunk_counter[src], 1);
+    if (done == n_copy - 1) {
+      cp.chunk_counter[src] = 0;
+      st_release_gpu(&cp.chunk_flags[src], cp.epoch);
+    }
+  }
+}
+
 template <int D>
 __global__ void __launch_bounds__(FA_THREADS, 1)
 flash_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                  const __grid_constant__ CUtensorMap map_v, __nv_bfloat16* __restrict__ O, float* __restrict__ lse,
                  const int* __restrict__ cu_q, const int* __restrict__ cu_k, int sq, int sk, int Hq, int Hkv,
-                 long long o_row_stride, long long total_q, float scale_log2, int causal, int* __restrict__ status) {
+                 long long o_row_stride, long long total_q, float scale_log2, int causal, int* __restrict__ status,
+                 const CpAttn cp) {
   using C = FwdCfg<D>;
+  const bool gather = cp.world > 1 && cp.kv_src[0] != nullptr;
+  const int n_copy = gather ? cp.n_copy_ctas : 0;
+  if ((int)blockIdx.x < n_copy) {
+    if (blockIdx.y == 0 && threadIdx.x == 0) gather_kv<C::SMEM>(cp, (int)blockIdx.x, Hkv * D * 2, status);
+    return;
+  }
   // grid = (query heads x sequences, query tiles): blocks are dispatched in linear order, so the heaviest (last)
   // causal tile of EVERY head starts before any lighter tile - longest work first across the whole launch.
-  const int h = (int)blockIdx.x % Hq;
-  const SeqInfo si = seq_info(cu_q, cu_k, (int)blockIdx.x / Hq, sq, sk);
+  const int bx = (int)blockIdx.x - n_copy;
+  const int h = bx % Hq;
+  SeqInfo si = seq_info(cu_q, cu_k, bx / Hq, sq, sk);
+  if (cp.world > 1) si.k_len = cp.k_vis;
   const int n_q_tiles = (si.q_len + BQ - 1) / BQ;
   const int qt = n_q_tiles - 1 - (int)blockIdx.y;
   if (qt < 0) return;
   const int kvh = h / (Hq / Hkv);
-  const int q0 = qt * BQ, off = si.k_len - si.q_len;
+  const int q0 = qt * BQ;
+  const int off = (cp.world > 1 && q0 < cp.chunk) ? cp.rank * cp.chunk : si.k_len - si.q_len;
   int kv_end = si.k_len;
   if (causal) kv_end = min(si.k_len, q0 + BQ + off);
   if (kv_end < 0) kv_end = 0;
@@ -118,9 +214,25 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
 #pragma unroll
       for (int kb = 0; kb < C::NB; ++kb) tma_load_2d(q_smem + kb * BLK_BYTES, &map_q, BAR(0), h * D + kb * 64, si.q_start + q0);
       bool ok = true;
-      for (int j = 0; j < n_kv && ok; ++j) {
-        const int st = j & 1;
-        const uint32_t ph = ((j >> 1) & 1) ^ 1u;
+      KvOrder order(n_kv, cp, BKV);
+      uint32_t landed = 0;  // source ranks whose chunks are known to be in the gathered buffer
+      for (int it = 0; it < n_kv && ok; ++it) {
+        const int j = order.next();
+        const int st = it & 1;
+        const uint32_t ph = ((it >> 1) & 1) ^ 1u;
+        if (gather) {
+          const int owner = chunk_owner(j * BKV / cp.chunk, cp.world);
+          if (!((landed >> owner) & 1u)) {
+            const unsigned long long t0 = comm::now_ns();
+            while (ld_acquire_gpu(&cp.chunk_flags[owner]) < cp.epoch) {
+              if (*abort_flag || comm::now_ns() - t0 > cp.timeout_ns) { ok = false; break; }
+              __nanosleep(100);
+            }
+            if (!ok) { atomicMax(status, ERR_CP_CHUNK_WAIT); break; }
+            fence_async_global();
+            landed |= 1u << owner;
+          }
+        }
         if (!mbar_wait(BAR(3 + st), ph, abort_flag)) { ok = false; break; }
         mbar_expect_tx(BAR(1 + st), C::TILE_BYTES);
 #pragma unroll
@@ -186,9 +298,11 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
     const int q_idx = q0 + row;
     float m_run = -INFINITY, l_run = 0.f;
     bool ok = true;
-    for (int j = 0; j < n_kv; ++j) {
-      const int buf = j & 1;
-      ok = __all_sync(0xffffffffu, mbar_wait(BAR(9 + buf), (j >> 1) & 1, abort_flag));
+    KvOrder order(n_kv, cp, BKV);
+    for (int it = 0; it < n_kv; ++it) {
+      const int j = order.next();
+      const int buf = it & 1;
+      ok = __all_sync(0xffffffffu, mbar_wait(BAR(9 + buf), (it >> 1) & 1, abort_flag));
       if (!ok) break;
       tc_fence_after();
       uint32_t s[4][32];
@@ -233,8 +347,8 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
           pk[c * 16 + (i >> 1)] = *reinterpret_cast<const uint32_t*>(&hh);
         }
       const float rowsum = (rs4[0] + rs4[1]) + (rs4[2] + rs4[3]);
-      if (j > 0) {  // PV(j-1) must have read P and updated O before either is touched
-        ok = __all_sync(0xffffffffu, mbar_wait(BAR(12), (j - 1) & 1, abort_flag));
+      if (it > 0) {  // the previous PV must have read P and updated O before either is touched
+        ok = __all_sync(0xffffffffu, mbar_wait(BAR(12), (it - 1) & 1, abort_flag));
         if (!ok) break;
         tc_fence_after();
         if (grow) {
@@ -320,17 +434,18 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
 template <int D>
 int launch_fwd(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, void* O, float* lse, const int* cu_q,
                const int* cu_k, int batch, int sq, int sk, int max_q, int Hq, int Hkv, long long o_row_stride,
-               long long total_q, float scale, bool causal, int* status, cudaStream_t st) {
+               long long total_q, float scale, bool causal, int* status, cudaStream_t st, const CpAttn& cp) {
   auto kern = flash_fwd_kernel<D>;
   static bool configured = false;
   if (!configured) {
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, FwdCfg<D>::SMEM) != cudaSuccess) return -4;
     configured = true;
   }
-  const dim3 grid(Hq * batch, (max_q + BQ - 1) / BQ, 1);
+  const int n_copy = (cp.world > 1 && cp.kv_src[0] != nullptr) ? cp.n_copy_ctas : 0;
+  const dim3 grid(Hq * batch + n_copy, (max_q + BQ - 1) / BQ, 1);
   kern<<<grid, FA_THREADS, FwdCfg<D>::SMEM, st>>>(mq, mk, mv, (__nv_bfloat16*)O, lse, cu_q, cu_k, sq, sk, Hq, Hkv,
                                                   o_row_stride, total_q, scale * 1.4426950408889634f, causal ? 1 : 0,
-                                                  status);
+                                                  status, cp);
   return cudaGetLastError() == cudaSuccess ? 0 : -5;
 }
 
@@ -339,19 +454,32 @@ int launch_fwd(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& 
 int flash_fwd(const void* q, const void* k, const void* v, void* out, float* lse, const int* cu_q, const int* cu_k,
               int batch, int sq, int sk, int max_q, long long total_q, long long total_k, int Hq, int Hkv, int D,
               long long q_row_stride, long long k_row_stride, long long v_row_stride, long long o_row_stride, float scale,
-              bool causal, int* status, cudaStream_t st) {
+              bool causal, int* status, cudaStream_t st, const CpAttn* cp_in) {
   if (batch <= 0 || total_q <= 0) return 0;
   if (Hkv <= 0 || Hq % Hkv) return -1;
   if (D != 64 && D != 128) return -3;
+  CpAttn cp;
+  if (cp_in != nullptr && cp_in->world > 1) {
+    cp = *cp_in;
+    // dense causal only; chunks are whole key tiles; the local rows are the rank's two chunks
+    if (cu_q || cu_k || !causal || cp.world > 8 || cp.rank < 0 || cp.rank >= cp.world) return -8;
+    if (cp.chunk <= 0 || cp.chunk % BKV || sq != 2 * cp.chunk || sk != 2 * cp.world * cp.chunk) return -8;
+    if (cp.k_vis != (2 * cp.world - cp.rank) * cp.chunk) return -8;
+    if (cp.kv_src[0] != nullptr) {
+      if (cp.n_copy_ctas < 1 || cp.n_copy_ctas > 32 || !cp.k_full || !cp.v_full || !cp.chunk_flags || !cp.chunk_counter) return -9;
+      if (k != cp.k_full || v != cp.v_full || k_row_stride != (long long)Hkv * D || v_row_stride != k_row_stride) return -9;
+      cp.batch = batch;
+    }
+  }
   CUtensorMap mq, mk, mv;
   if (!cache().get(&mq, q, (long long)Hq * D, total_q, q_row_stride, 64, 128)) return -1000 - g_last_map_error;
   if (!cache().get(&mk, k, (long long)Hkv * D, total_k, k_row_stride, 64, 128)) return -2000 - g_last_map_error;
   if (!cache().get(&mv, v, (long long)Hkv * D, total_k, v_row_stride, 64, 128)) return -3000 - g_last_map_error;
   if (D == 128)
     return launch_fwd<128>(mq, mk, mv, out, lse, cu_q, cu_k, batch, sq, sk, max_q, Hq, Hkv, o_row_stride, total_q, scale,
-                           causal, status, st);
+                           causal, status, st, cp);
   return launch_fwd<64>(mq, mk, mv, out, lse, cu_q, cu_k, batch, sq, sk, max_q, Hq, Hkv, o_row_stride, total_q, scale,
-                        causal, status, st);
+                        causal, status, st, cp);
 }
 
 }  // namespace ab

@@ -55,21 +55,47 @@ int gemm_bf16_2cta(const void* A, const void* B, void* D, int M, int N, int K, l
                    long long ldd, bool a_kmajor, bool b_kmajor, bool out_f32, bool accumulate, int* status,
                    cudaStream_t st);
 
+// Context-parallel extension of the flash kernels.  The sequence of S = 2 * world * chunk tokens is cut into
+// 2 * world chunks; rank r owns chunks r and 2 * world - 1 - r (zig-zag, so every rank has the same causal work).
+// Its 2 * chunk local query rows attend to the gathered keys [0, k_vis), k_vis = (2 * world - r) * chunk: rows below
+// `chunk` sit at global position r * chunk + i, the others at k_vis - 2 * chunk + i.  world == 1 switches all of it off.
+struct CpAttn {
+  int world = 1, rank = 0, chunk = 0, k_vis = 0, batch = 1;
+  // forward gather, done by copy CTAs inside the attention kernel when kv_src[0] != null:
+  const void* kv_src[8] = {};   // every rank's local [2 (k|v)][batch][2 * chunk][Hkv * D] bf16
+  void* k_full = nullptr;       // local gathered [batch][S][Hkv * D]; the kernel's K / V operands
+  void* v_full = nullptr;
+  void* flags[8] = {};          // flag array of every rank ([kind][8][max_units] int32)
+  int unit = 0, max_units = 1, epoch = 0, n_copy_ctas = 0;
+  int* chunk_flags = nullptr;   // local int[8]: epoch at which rank p's chunks landed in k_full / v_full
+  int* chunk_counter = nullptr; // local int[8]: copy CTAs finished per source rank (self-resetting)
+  unsigned long long timeout_ns = 0;
+  // backward scatter, done by the dK/dV epilogue when stage[0] != null:
+  void* stage[8] = {};          // every rank's [world (src)][2 (dk|dv)][batch][2 * chunk][Hkv * D] bf16
+  int* tile_counter = nullptr;  // local int[8]: tiles written per destination rank (self-resetting)
+};
+
 // Flash attention forward (flash_fwd.cu).  Packed layouts q [total_q, Hq, D], k/v [total_k, Hkv, D] with unit stride
 // in D and adjacent heads; row strides in elements.  cu_q / cu_k: int32 [batch+1] sequence boundaries or null (then
 // every sequence has sq / sk tokens).  lse [Hq, total_q] fp32 (natural log) may be null.  D in {64, 128}.
+// With `cp` (world > 1): dense only, sq = 2 * chunk, sk = S, causal.
 int flash_fwd(const void* q, const void* k, const void* v, void* out, float* lse, const int* cu_q, const int* cu_k,
               int batch, int sq, int sk, int max_q, long long total_q, long long total_k, int Hq, int Hkv, int D,
               long long q_row_stride, long long k_row_stride, long long v_row_stride, long long o_row_stride, float scale,
-              bool causal, int* status, cudaStream_t st);
+              bool causal, int* status, cudaStream_t st, const CpAttn* cp = nullptr);
 
 // Flash attention backward (flash_bwd.cu): dq [total_q,Hq,D], dk/dv [total_k,Hkv,D] bf16; `delta` is fp32 scratch
 // [2, Hq, total_q]; lse as written by flash_fwd.  Three launches: row-dot pre-pass, dK/dV kernel, dQ kernel.
+// With `cp`: dk/dv are this rank's PARTIAL gradients of the gathered keys [batch][S] (rows from k_vis on are not
+// written), or, when cp->stage is set, they are not used and every tile goes to its owner's staging slot.
 int flash_bwd(const void* q, const void* k, const void* v, const void* out, const void* dout, const float* lse,
               float* delta, void* dq, void* dk, void* dv, const int* cu_q, const int* cu_k, int batch, int sq, int sk,
               int max_q, int max_k, long long total_q, long long total_k, int Hq, int Hkv, int D, long long q_rs,
               long long k_rs, long long v_rs, long long o_rs, long long do_rs, long long dq_rs, long long dk_rs, float scale,
-              bool causal, int* status, cudaStream_t st);
+              bool causal, int* status, cudaStream_t st, const CpAttn* cp = nullptr);
+// Owner side of the backward scatter: waits (bounded) for every contributing rank's tiles, then
+// dk_local / dv_local [batch][2 * chunk][Hkv * D] = sum over the contributors' staging slots.
+int cp_dkv_reduce(void* dk_local, void* dv_local, int batch, int row_elems, const CpAttn& cp, int* status, cudaStream_t st);
 
 // ---- communication kernels over peer memory (comm_fsdp.cu, comm.cuh)
 struct CommPeers { void* ptr[8]; };  // the same buffer on every rank of the node, indexed by rank

@@ -24,7 +24,7 @@ import torch.distributed as dist
 
 FLAG_KINDS = 8        # independent flag planes ([kind][8 ranks][max_units] int32 per rank)
 MAX_RANKS = 8
-KIND_GRADS_READY, KIND_PARAMS_WRITTEN, KIND_TP_AG, KIND_TP_RS, KIND_CP, KIND_EP = 0, 1, 2, 3, 4, 5
+KIND_GRADS_READY, KIND_PARAMS_WRITTEN, KIND_TP_AG, KIND_TP_RS, KIND_CP, KIND_EP, KIND_CP_DKV = 0, 1, 2, 3, 4, 5, 6
 
 
 @dataclass
