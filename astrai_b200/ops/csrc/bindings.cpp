@@ -713,6 +713,91 @@ Tensor grouped_gemm_rows(const Tensor& x, const Tensor& w, bool w_kmajor, const 
   return y;
 }
 
+// ---- expert parallel: routing exchange and the grouped GEMM with gather / scatter over peer memory
+void ep_push_counts(const Tensor& counts_local, std::vector<int64_t> counts_all_ptrs, Tensor& row_peer_local,
+                    std::vector<int64_t> flag_ptrs, int64_t rank, int64_t unit, int64_t max_units, int64_t epoch) {
+  TORCH_CHECK(counts_local.is_cuda() && counts_local.scalar_type() == at::kInt && row_peer_local.scalar_type() == at::kInt, "ep_push_counts: int32 tensors");
+  const int world = (int)counts_all_ptrs.size();
+  TORCH_CHECK(world >= 1 && world <= 8 && (int)flag_ptrs.size() == world, "ep_push_counts: one pointer per rank");
+  void* ca[8]; void* fl[8];
+  for (int i = 0; i < world; ++i) ca[i] = reinterpret_cast<void*>(counts_all_ptrs[i]), fl[i] = reinterpret_cast<void*>(flag_ptrs[i]);
+  const c10::cuda::CUDAGuard guard(counts_local.device());
+  count();
+  const int rc = ab::ep_push_counts(counts_local.data_ptr<int>(), (int)counts_local.numel(), ca, row_peer_local.data_ptr<int>(),
+                                    (int)row_peer_local.numel(), fl, world, (int)rank, (int)unit, (int)max_units, (int)epoch, stream());
+  TORCH_CHECK(rc == 0, "ep_push_counts: experts must divide evenly over <= 8 ranks, <= 256 experts, row table a multiple of 128 (code ", rc, ")");
+}
+
+std::tuple<Tensor, Tensor, Tensor> ep_plan(const Tensor& idx, const Tensor& counts_all_local, std::vector<int64_t> row_peer_ptrs,
+                                           int64_t n_experts, int64_t r_cap, std::vector<int64_t> flag_ptrs, int64_t rank,
+                                           int64_t wait_unit, int64_t signal_unit, int64_t max_units, int64_t epoch, double timeout_s) {
+  CHECK_CUDA_CONTIG(idx);
+  TORCH_CHECK(idx.scalar_type() == at::kLong && counts_all_local.scalar_type() == at::kInt, "ep_plan: idx int64, counts int32");
+  const int world = (int)row_peer_ptrs.size();
+  TORCH_CHECK(world >= 1 && world <= 8 && (int)flag_ptrs.size() == world && counts_all_local.numel() >= world * n_experts, "ep_plan: one pointer per rank");
+  void* rp[8]; void* fl[8];
+  for (int i = 0; i < world; ++i) rp[i] = reinterpret_cast<void*>(row_peer_ptrs[i]), fl[i] = reinterpret_cast<void*>(flag_ptrs[i]);
+  const c10::cuda::CUDAGuard guard(idx.device());
+  auto io = idx.options().dtype(at::kInt);
+  Tensor offsets = at::zeros({n_experts / world + 1}, io), tile_expert = at::full({r_cap / 128}, -1, io), total = at::zeros({1}, io);
+  count();
+  const int rc = ab::ep_plan(reinterpret_cast<const long long*>(idx.data_ptr<int64_t>()), idx.numel(), counts_all_local.data_ptr<int>(), rp,
+                             offsets.data_ptr<int>(), tile_expert.data_ptr<int>(), total.data_ptr<int>(), (int)n_experts, (int)r_cap, fl,
+                             world, (int)rank, (int)wait_unit, (int)signal_unit, (int)max_units, (int)epoch,
+                             (unsigned long long)(timeout_s * 1e9), status_tensor(idx.device()).data_ptr<int>(), stream());
+  TORCH_CHECK(rc == 0, "ep_plan launch failed with code ", rc);
+  return {offsets, tile_expert, total};
+}
+
+// Rows mode with the sorted rows pulled from (src_ptrs) or the output rows pushed to (dst_ptrs) peer memory.
+// Gather: `x` is the local sorted buffer the rows land in (its contents on entry do not matter).  Scatter: the result
+// has no local copy and an empty tensor is returned.
+Tensor grouped_gemm_rows_ep(Tensor& x, const Tensor& w, bool w_kmajor, const Tensor& tile_expert, const Tensor& row_peer, int64_t rank,
+                            std::vector<int64_t> src_ptrs, int64_t src_div, const c10::optional<Tensor>& tile_flags, int64_t n_copy_ctas,
+                            std::vector<int64_t> dst_ptrs, const c10::optional<Tensor>& done_counter, std::vector<int64_t> flag_ptrs,
+                            int64_t announce_unit, int64_t wait_unit, int64_t signal_unit, int64_t max_units, int64_t epoch,
+                            double timeout_s) {
+  CHECK_CUDA_CONTIG(x);
+  CHECK_CUDA_CONTIG(w);
+  TORCH_CHECK(x.scalar_type() == at::kBFloat16 && w.scalar_type() == at::kBFloat16 && w.dim() == 3 && x.dim() == 2, "grouped_gemm_rows_ep: bf16 x [R,K], w [E,a,b]");
+  const int64_t E = w.size(0), K = x.size(1);
+  const int64_t N = w_kmajor ? w.size(1) : w.size(2);
+  TORCH_CHECK((w_kmajor ? w.size(2) : w.size(1)) == K, "grouped_gemm_rows_ep: inner dimensions differ");
+  TORCH_CHECK(tile_expert.scalar_type() == at::kInt && tile_expert.numel() * 128 >= x.size(0), "grouped_gemm_rows_ep: tile map too short");
+  TORCH_CHECK(row_peer.is_cuda() && row_peer.scalar_type() == at::kInt && row_peer.numel() >= x.size(0), "grouped_gemm_rows_ep: row table too short");
+  const bool gather = !src_ptrs.empty(), scatter = !dst_ptrs.empty();
+  TORCH_CHECK(gather != scatter, "grouped_gemm_rows_ep: exactly one of gather / scatter");
+  const int world = (int)flag_ptrs.size();
+  TORCH_CHECK(world >= 2 && world <= 8, "grouped_gemm_rows_ep: 2..8 ranks");
+  ab::EpRows ep;
+  ep.world = world, ep.rank = (int)rank, ep.row_peer = row_peer.data_ptr<int>();
+  ep.announce_unit = (int)announce_unit, ep.wait_unit = (int)wait_unit, ep.signal_unit = (int)signal_unit;
+  ep.max_units = (int)max_units, ep.epoch = (int)epoch, ep.timeout_ns = (unsigned long long)(timeout_s * 1e9);
+  for (int i = 0; i < world; ++i) ep.flags[i] = reinterpret_cast<void*>(flag_ptrs[i]);
+  if (gather) {
+    TORCH_CHECK((int)src_ptrs.size() == world && tile_flags.has_value() && tile_flags->scalar_type() == at::kInt && tile_flags->numel() * 128 >= x.size(0), "grouped_gemm_rows_ep: gather needs a source per rank and int32 tile flags");
+    for (int i = 0; i < world; ++i) ep.src[i] = reinterpret_cast<const void*>(src_ptrs[i]);
+    ep.src_div = (int)src_div, ep.tile_flags = tile_flags->data_ptr<int>(), ep.n_copy_ctas = (int)n_copy_ctas;
+  } else {
+    TORCH_CHECK((int)dst_ptrs.size() == world && done_counter.has_value() && done_counter->scalar_type() == at::kInt && done_counter->numel() >= 1, "grouped_gemm_rows_ep: scatter needs a destination per rank and an int32 counter");
+    for (int i = 0; i < world; ++i) ep.dst[i] = reinterpret_cast<void*>(dst_ptrs[i]);
+    ep.done_counter = done_counter->data_ptr<int>();
+  }
+  const c10::cuda::CUDAGuard guard(x.device());
+  Tensor y = scatter ? at::empty({0}, x.options()) : at::empty({x.size(0), N}, x.options());
+  ab::GroupedParams g{};
+  g.tile_expert = tile_expert.data_ptr<int>();
+  g.b_rows_per_expert = (int)w.size(1);
+  g.b_row_offset = 0;
+  g.E = (int)E;
+  count();
+  const int rc = ab::gemm_grouped_rows(x.data_ptr(), w.data_ptr(), scatter ? nullptr : y.data_ptr(), (int)x.size(0), (int)N, (int)K,
+                                       x.stride(0), E * w.size(1), w.size(2), N, w_kmajor, g, status_tensor(x.device()).data_ptr<int>(),
+                                       stream(), &ep);
+  TORCH_CHECK(rc == 0, "grouped_gemm_rows_ep launch failed with code ", rc);
+  return y;
+}
+
 // dW [E, N, K] = per-expert dY_e^T X_e over the padded segments given by offsets [E+1]
 Tensor grouped_gemm_wgrad(const Tensor& dy, const Tensor& x, const Tensor& offsets, bool out_f32) {
   CHECK_CUDA_CONTIG(dy);
@@ -777,5 +862,8 @@ TORCH_LIBRARY(astrai_b200, m) {
   m.def("moe_combine_bwd(Tensor dout, Tensor y, Tensor slot_of, Tensor weights) -> (Tensor, Tensor)", &moe_combine_bwd);
   m.def("grouped_gemm_rows(Tensor x, Tensor w, bool w_kmajor, Tensor tile_expert) -> Tensor", &grouped_gemm_rows);
   m.def("grouped_gemm_wgrad(Tensor dy, Tensor x, Tensor offsets, bool out_f32) -> Tensor", &grouped_gemm_wgrad);
+  m.def("ep_push_counts(Tensor counts_local, int[] counts_all_ptrs, Tensor(a!) row_peer_local, int[] flag_ptrs, int rank, int unit, int max_units, int epoch) -> ()", &ep_push_counts);
+  m.def("ep_plan(Tensor idx, Tensor counts_all_local, int[] row_peer_ptrs, int n_experts, int r_cap, int[] flag_ptrs, int rank, int wait_unit, int signal_unit, int max_units, int epoch, float timeout_s) -> (Tensor, Tensor, Tensor)", &ep_plan);
+  m.def("grouped_gemm_rows_ep(Tensor(a!) x, Tensor w, bool w_kmajor, Tensor tile_expert, Tensor row_peer, int rank, int[] src_ptrs, int src_div, Tensor? tile_flags, int n_copy_ctas, int[] dst_ptrs, Tensor? done_counter, int[] flag_ptrs, int announce_unit, int wait_unit, int signal_unit, int max_units, int epoch, float timeout_s) -> Tensor", &grouped_gemm_rows_ep);
   m.def("gemm(Tensor A, Tensor B, Tensor? D, bool a_kmajor, bool b_kmajor, bool out_f32, bool accumulate) -> Tensor", &gemm);
 }

@@ -10,12 +10,18 @@
 // Expert weights may live in one flat buffer with a fixed row stride per expert (gate|up|down interleaved), so no
 // stacking copy is needed.  Structure and barriers follow gemm_tcgen05.cu (persistent, TMA ring, one MMA lane,
 // double-buffered TMEM accumulator, four epilogue warps); all waits are bounded.
+// Expert parallel (EpRows, rows mode): the sorted rows belong to tokens of other ranks.  Gather: copy CTAs at the front
+// of the grid pull each 128-row tile's rows from the peers' memory (one bulk copy per row through shared memory, two
+// batches in flight), zero the padding and publish a per-tile flag that the TMA producer of the GEMM CTAs polls - the
+// all-to-all dispatch overlaps the expert GEMM tile by tile.  Scatter: the epilogue stores every output row straight
+// into the memory of the rank that owns the token (the combine all-to-all), the last CTA publishes a flag.
 // Replaces the reference's Python loop over experts (astrai/model/components/mlp.py:143-166).
 #include <cuda.h>
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include "flash_cp.cuh"
 #include "launchers.h"
 #include "tcgen05.cuh"
 #include "tma_host.h"
@@ -31,7 +37,89 @@ constexpr int A_BYTES = BM * BK * 2, B_BYTES = BN * BK * 2, STAGE_BYTES = A_BYTE
 constexpr int NUM_THREADS = 192;
 constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 + 256;
 enum : int { MODE_ROWS = 0, MODE_WGRAD = 1 };
-enum : int { ERR_GG_PRODUCER = 81, ERR_GG_MMA = 82, ERR_GG_EPILOGUE = 83 };
+enum : int { ERR_GG_PRODUCER = 81, ERR_GG_MMA = 82, ERR_GG_EPILOGUE = 83, ERR_GG_GATHER = 84, ERR_GG_TILE_WAIT = 85 };
+constexpr int KIND_EP = 5;  // flag plane (astrai_b200/parallel/symm.py)
+
+// Copy CTA of the expert-parallel gather (all threads take part).  Tiles are dealt round-robin to the copy CTAs.
+__device__ void ep_gather(const EpRows& ep, int cta, int n_copy, int R, int K, uint8_t* a_local, const int* tile_expert,
+                          int* status) {
+  using namespace cpx;
+  constexpr int HALF = STAGES * STAGE_BYTES / 2;  // two slots
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  uint8_t* aligned = smem_raw + (base - smem_u32(smem_raw));
+  uint64_t* bars = reinterpret_cast<uint64_t*>(aligned + 2 * HALF);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(bars + 2);
+  __shared__ int s_ok;
+  const uint32_t bar0 = smem_u32(bars);
+  if (threadIdx.x == 0) {
+    mbar_init(bar0, 1);
+    mbar_init(bar0 + 8, 1);
+    *abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    fence_async_smem();
+    if (cta == 0 && ep.announce_unit >= 0) {
+      __threadfence_system();
+      for (int p = 0; p < ep.world; ++p) comm::st_release_sys(flag_slot(ep.flags[p], KIND_EP, ep.rank, ep.announce_unit, ep.max_units), ep.epoch);
+    }
+    int ok = 1;
+    for (int src = 0; src < ep.world && ok; ++src)
+      ok = comm::wait_flag(flag_slot(ep.flags[ep.rank], KIND_EP, src, ep.wait_unit, ep.max_units), ep.epoch, ep.timeout_ns) ? 1 : 0;
+    if (!ok) atomicMax(status, ERR_GG_GATHER);
+    s_ok = ok;
+  }
+  __syncthreads();
+  if (!s_ok) return;  // the GEMM CTAs run out of time on the tile flag and report as well
+  const uint32_t row_bytes = (uint32_t)K * 2u;
+  const int rps = min(128, (int)(HALF / row_bytes));  // rows per slot
+  uint32_t uses[2] = {0, 0};
+  for (int mt = cta; mt < R / 128; mt += n_copy) {
+    if (tile_expert[mt] < 0) continue;
+    const int* rp = ep.row_peer + mt * 128;
+    const int nv = __syncthreads_count(threadIdx.x < 128 && comm::ld_acquire_sys(rp + min((int)threadIdx.x, 127)) >= 0);
+    // padding rows (always the tail of a tile): zeros, so they add nothing to a weight gradient
+    uint4* pad = reinterpret_cast<uint4*>(a_local + ((long long)mt * 128 + nv) * row_bytes);
+    const long long n16 = (long long)(128 - nv) * (row_bytes / 16);
+    for (long long i = threadIdx.x; i < n16; i += blockDim.x) pad[i] = make_uint4(0, 0, 0, 0);
+    fence_async_global();
+    __threadfence();
+    if (threadIdx.x == 0) {
+      const int nb = (nv + rps - 1) / rps;
+      auto issue = [&](int b) {
+        const int slot = b & 1, r0 = b * rps, n = min(rps, nv - r0);
+        mbar_expect_tx(bar0 + 8u * slot, (uint32_t)n * row_bytes);
+        for (int i = 0; i < n; ++i) {
+          const int code = comm::ld_acquire_sys(rp + r0 + i);
+          const uint8_t* from = reinterpret_cast<const uint8_t*>(ep.src[code >> 24]) + (long long)((code & 0xffffff) / ep.src_div) * row_bytes;
+          bulk_load(base + slot * HALF + i * row_bytes, from, row_bytes, bar0 + 8u * slot);
+        }
+      };
+      bool ok = true;
+      if (nb > 0) issue(0);
+      for (int b = 0; b < nb && ok; ++b) {
+        if (b + 1 < nb) {
+          if (b >= 1) bulk_wait_read();  // the store that last used the other slot has read it
+          issue(b + 1);
+        }
+        const int slot = b & 1, r0 = b * rps, n = min(rps, nv - r0);
+        if (!mbar_wait(bar0 + 8u * slot, uses[slot] & 1u, abort_flag)) { ok = false; break; }
+        ++uses[slot];
+        bulk_store(a_local + ((long long)mt * 128 + r0) * row_bytes, base + slot * HALF, (uint32_t)n * row_bytes);
+        bulk_commit();
+      }
+      bulk_wait_all();
+      fence_async_global();
+      __threadfence();
+      if (!ok) {
+        atomicMax(status, ERR_GG_GATHER);
+        s_ok = 0;
+      }
+    }
+    __syncthreads();
+    if (!s_ok) return;
+    if (threadIdx.x == 0) st_release_gpu(&ep.tile_flags[mt], ep.epoch);
+  }
+}
 
 struct Work {
   int m0, n0;       // output tile origin (rows mode: sorted row / output column; wgrad: dW row / dW column)
@@ -66,7 +154,16 @@ __device__ __forceinline__ Work get_work(int t, const GroupedParams& g, int tile
 template <int MODE, bool B_K>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 gemm_grouped_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, void* __restrict__ Dv,
-                    int M, int N, int K, long long ldd, GroupedParams g, int out_f32, int accumulate, int* __restrict__ status) {
+                    int M, int N, int K, long long ldd, GroupedParams g, int out_f32, int accumulate, int* __restrict__ status,
+                    const EpRows ep, uint8_t* __restrict__ a_local) {
+  const bool gather = MODE == MODE_ROWS && ep.src[0] != nullptr;
+  const bool scatter = MODE == MODE_ROWS && ep.dst[0] != nullptr;
+  const int n_copy = gather ? ep.n_copy_ctas : 0;
+  if ((int)blockIdx.x < n_copy) {
+    ep_gather(ep, (int)blockIdx.x, n_copy, M, K, a_local, g.tile_expert, status);
+    return;
+  }
+  const int cta = (int)blockIdx.x - n_copy, n_ctas = (int)gridDim.x - n_copy;
   extern __shared__ uint8_t smem_raw[];
   const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   uint8_t* aligned = smem_raw + (base - smem_u32(smem_raw));
@@ -111,10 +208,21 @@ gemm_grouped_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
-      for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
+      int landed = -1;
+      for (int t = cta; t < num_tiles && ok; t += n_ctas) {
         const Work w = get_work<MODE>(t, g, tiles_m, tiles_n, num_kb);
         if (w.expert < 0) continue;
         const int brow = w.expert * g.b_rows_per_expert + g.b_row_offset;
+        if (gather && landed != w.m0) {  // the copy CTAs must have brought this tile's rows
+          const unsigned long long t0 = comm::now_ns();
+          while (cpx::ld_acquire_gpu(&ep.tile_flags[w.m0 / BM]) < ep.epoch) {
+            if (*abort_flag || comm::now_ns() - t0 > ep.timeout_ns) { ok = false; break; }
+            __nanosleep(100);
+          }
+          if (!ok) { atomicMax(status, ERR_GG_TILE_WAIT); break; }
+          cpx::fence_async_global();
+          landed = w.m0;
+        }
         for (int kb = w.kb_begin; kb < w.kb_end; ++kb) {
           if (!mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag)) {
             ok = false;
@@ -153,7 +261,7 @@ gemm_grouped_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
       int stage = 0, it = 0;
       uint32_t phase = 0;
       bool ok = true;
-      for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
+      for (int t = cta; t < num_tiles && ok; t += n_ctas) {
         const Work w = get_work<MODE>(t, g, tiles_m, tiles_n, num_kb);
         if (w.expert < 0) continue;
         const int buf = it & 1;
@@ -188,7 +296,7 @@ gemm_grouped_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     const int quarter = warp & 3;
     int it = 0;
     bool ok = true;
-    for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
+    for (int t = cta; t < num_tiles && ok; t += n_ctas) {
       const Work w = get_work<MODE>(t, g, tiles_m, tiles_n, num_kb);
       if (w.expert < 0) continue;
       const int buf = it & 1;
@@ -198,8 +306,15 @@ gemm_grouped_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
         break;
       }
       tc_fence_after();
-      const int row = w.m0 + quarter * 32 + lane;
+      int row = w.m0 + quarter * 32 + lane;
       uint8_t* dbase = reinterpret_cast<uint8_t*>(Dv) + (MODE == MODE_WGRAD ? (long long)w.expert * g.d_expert_stride * (out_f32 ? 4 : 2) : 0);
+      bool live = row < M;
+      if (scatter) {  // the row goes to the rank that owns its token; padding rows go nowhere
+        const int code = live ? ep.row_peer[row] : -1;
+        live = code >= 0;
+        dbase = live ? reinterpret_cast<uint8_t*>(ep.dst[code >> 24]) : nullptr;
+        row = code & 0xffffff;
+      }
       const uint32_t taddr0 = tmem_base + ((uint32_t)(quarter * 32) << 16) + buf * BN;
 #pragma unroll 1
       for (int c = 0; c < BN / 32; ++c) {
@@ -207,7 +322,7 @@ gemm_grouped_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
         tc_ld32(taddr0 + c * 32, r);
         tc_wait_ld();
         const int col = w.n0 + c * 32;
-        if (row < M && col < N && !(empty && accumulate)) {
+        if (live && col < N && !(empty && accumulate)) {
           if (out_f32) {
             float* d = reinterpret_cast<float*>(dbase) + (long long)row * ldd + col;
             for (int j = 0; j < 32 && col + j < N; ++j) {
@@ -248,6 +363,7 @@ gemm_grouped_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
       atomicMax(status, ERR_GG_EPILOGUE);
       *abort_flag = 1;
     }
+    if (scatter) __threadfence_system();
   }
 
   tc_fence_before();
@@ -256,11 +372,21 @@ gemm_grouped_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     tc_fence_after();
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(512u) : "memory");
   }
+  if (scatter && threadIdx.x == 0 && *abort_flag == 0) {
+    // the last CTA tells every rank that all of this rank's output rows are in place
+    const int done = atomicAdd(ep.done_counter, 1);
+    if (done == (int)gridDim.x - 1) {
+      *ep.done_counter = 0;
+      __threadfence_system();
+      for (int p = 0; p < ep.world; ++p)
+        comm::st_release_sys(cpx::flag_slot(ep.flags[p], KIND_EP, ep.rank, ep.signal_unit, ep.max_units), ep.epoch);
+    }
+  }
 }
 
 template <int MODE, bool B_K>
 int launch_gg(const CUtensorMap& ma, const CUtensorMap& mb, void* D, int M, int N, int K, long long ldd, const GroupedParams& g,
-              bool out_f32, bool accumulate, int* status, cudaStream_t st) {
+              bool out_f32, bool accumulate, int* status, cudaStream_t st, const EpRows& ep = EpRows(), void* a_local = nullptr) {
   auto kern = gemm_grouped_kernel<MODE, B_K>;
   static bool configured = false;
   static int sms = 0;
@@ -272,8 +398,11 @@ int launch_gg(const CUtensorMap& ma, const CUtensorMap& mb, void* D, int M, int 
     configured = true;
   }
   const int tiles = (MODE == MODE_ROWS ? 1 : g.E) * ((M + BM - 1) / BM) * ((N + BN - 1) / BN);
-  const int grid = tiles < sms ? tiles : sms;
-  kern<<<grid, NUM_THREADS, SMEM_BYTES, st>>>(ma, mb, D, M, N, K, ldd, g, out_f32 ? 1 : 0, accumulate ? 1 : 0, status);
+  const int n_copy = (MODE == MODE_ROWS && ep.src[0] != nullptr) ? ep.n_copy_ctas : 0;
+  int gemm_ctas = sms - n_copy;
+  if (tiles < gemm_ctas) gemm_ctas = tiles;
+  kern<<<gemm_ctas + n_copy, NUM_THREADS, SMEM_BYTES, st>>>(ma, mb, D, M, N, K, ldd, g, out_f32 ? 1 : 0, accumulate ? 1 : 0, status,
+                                                            ep, (uint8_t*)a_local);
   return cudaGetLastError() == cudaSuccess ? 0 : -5;
 }
 
@@ -281,16 +410,26 @@ int launch_gg(const CUtensorMap& ma, const CUtensorMap& mb, void* D, int M, int 
 
 // Y[R, N] = X[R, K] . op(W_e): rows mode.  `w_rows` / `w_cols` describe the 2-D view of the stacked weight buffer.
 int gemm_grouped_rows(const void* X, const void* W, void* Y, int R, int N, int K, long long ldx, long long w_rows, long long w_cols,
-                      long long ldy, bool w_kmajor, const GroupedParams& g, int* status, cudaStream_t st) {
+                      long long ldy, bool w_kmajor, const GroupedParams& g, int* status, cudaStream_t st, const EpRows* ep_in) {
   if (R <= 0 || N <= 0 || K <= 0) return 0;
   if (R % BM) return -2;
   if (!w_kmajor && (K % BK)) return -3;  // MN-major weight: contraction rows of one expert must be whole K blocks
+  EpRows ep;
+  if (ep_in != nullptr && ep_in->world > 1) {
+    ep = *ep_in;
+    if (ep.world > 8 || ep.rank < 0 || ep.rank >= ep.world || ep.row_peer == nullptr) return -6;
+    if (ep.src[0] != nullptr) {  // rows are whole 16-byte multiples, one slot holds at least one row, dense sorted buffer
+      if (ep.n_copy_ctas < 1 || ep.n_copy_ctas > 64 || ep.tile_flags == nullptr || ep.src_div < 1) return -6;
+      if (K % 8 || K * 2 > STAGES * STAGE_BYTES / 2 || ldx != K) return -7;
+    }
+    if (ep.dst[0] != nullptr && (ep.done_counter == nullptr || N % 32 || ldy % 8)) return -7;
+  }
   CUtensorMap ma, mb;
   if (!cache().get(&ma, X, K, R, ldx, BK, BM)) return -1000 - g_last_map_error;
   const bool okb = w_kmajor ? cache().get(&mb, W, w_cols, w_rows, w_cols, BK, BN) : cache().get(&mb, W, w_cols, w_rows, w_cols, 64, BK);
   if (!okb) return -2000 - g_last_map_error;
-  return w_kmajor ? launch_gg<MODE_ROWS, true>(ma, mb, Y, R, N, K, ldy, g, false, false, status, st)
-                  : launch_gg<MODE_ROWS, false>(ma, mb, Y, R, N, K, ldy, g, false, false, status, st);
+  return w_kmajor ? launch_gg<MODE_ROWS, true>(ma, mb, Y, R, N, K, ldy, g, false, false, status, st, ep, const_cast<void*>(X))
+                  : launch_gg<MODE_ROWS, false>(ma, mb, Y, R, N, K, ldy, g, false, false, status, st, ep, const_cast<void*>(X));
 }
 
 // dW_e[N, K] (+)= dY_e^T X_e for every expert; D is the stacked gradient buffer (row stride ldd, expert stride in g).

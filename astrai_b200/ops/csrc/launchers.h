@@ -164,8 +164,41 @@ struct GroupedParams {
   long long d_expert_stride;  // wgrad mode: elements between consecutive experts in the output
   int E;
 };
+// Expert-parallel extension of the rows mode.  Every rank owns E / world experts; the rows of its sorted buffer come
+// from (gather) or go back to (scatter) the ranks whose tokens chose those experts.  row_peer[r] = rank << 24 | index
+// names the peer row behind sorted row r (index = token * top_k + choice), -1 for padding rows.
+//   gather : copy CTAs at the front of the grid pull the rows of the A operand from the peers' `src` buffers (bulk
+//            copies through shared memory), zero the padding, and publish tile_flags[tile] = epoch; the GEMM CTAs poll a
+//            tile's flag before its first TMA load.  The copy CTAs first (optionally) announce `announce_unit` to every
+//            peer and wait for every peer's `wait_unit` flag: "your source rows and my table are complete".
+//   scatter: the epilogue stores output row r into row `index` of the `dst` buffer of rank row_peer[r] >> 24; the last
+//            CTA to finish publishes `signal_unit` to every peer.
+struct EpRows {
+  int world = 1, rank = 0;
+  const int* row_peer = nullptr;
+  const void* src[8] = {};     // gather: every rank's [*, K] bf16 rows; null = no gather
+  int src_div = 1;             // gather: source row = index / src_div
+  int* tile_flags = nullptr;   // gather: local int[R / 128]
+  int n_copy_ctas = 0;
+  void* dst[8] = {};           // scatter: every rank's [*, N] bf16 rows; null = no scatter
+  int* done_counter = nullptr; // scatter: local int (self-resetting)
+  void* flags[8] = {};         // flag array of every rank ([kind][8][max_units] int32)
+  int announce_unit = -1, wait_unit = 0, signal_unit = 0, max_units = 8, epoch = 0;
+  unsigned long long timeout_ns = 0;
+};
 int gemm_grouped_rows(const void* X, const void* W, void* Y, int R, int N, int K, long long ldx, long long w_rows, long long w_cols,
-                      long long ldy, bool w_kmajor, const GroupedParams& g, int* status, cudaStream_t st);
+                      long long ldy, bool w_kmajor, const GroupedParams& g, int* status, cudaStream_t st,
+                      const EpRows* ep = nullptr);
+// Expert-parallel routing exchange (moe_ep.cu).  Step 1, every rank: blank the local row table, copy the local
+// per-expert counts into row `rank` of every peer's counts table, publish `unit`.
+int ep_push_counts(const int* counts_local, int E, void* const* counts_all, int* row_peer_local, int r_cap, void* const* flags,
+                   int world, int rank, int unit, int max_units, int epoch, cudaStream_t st);
+// Step 2, every rank: wait for all counts, lay out every rank's padded expert segments, write the local segment
+// offsets [E / world + 1] / tile -> expert map [r_cap / 128] / row total, and enter this rank's (token, choice) pairs
+// into the row tables of the ranks that own the chosen experts; publish `signal_unit`.
+int ep_plan(const long long* idx, long long pairs, const int* counts_all_local, void* const* row_peer, int* offsets,
+            int* tile_expert, int* total, int E, int r_cap, void* const* flags, int world, int rank, int wait_unit,
+            int signal_unit, int max_units, int epoch, unsigned long long timeout_ns, int* status, cudaStream_t st);
 int gemm_grouped_wgrad(const void* dY, const void* X, void* D, int R, int N, int K, long long lddy, long long ldx, long long ldd,
                        bool out_f32, bool accumulate, const GroupedParams& g, int* status, cudaStream_t st);
 

@@ -55,3 +55,14 @@ def test_fused_tensor_parallel_mlp_matches_nccl(tmp_path):
         for key in ("y", "dx", "d_gate_up", "d_down"):
             assert rank_res[key] < 3e-2, rank_res
         assert rank_res["y_vs_fp32"] < 5e-2, rank_res
+
+
+def test_fused_context_parallel_attention_matches_nccl_and_fp32(tmp_path):
+    _need_gpus(2)
+    out = str(tmp_path / "cp.json")
+    _torchrun(2, os.path.join(ROOT, "tests", "workers", "cp_compare.py"), ["--out", out], 29660)
+    for rank_res in json.load(open(out)):
+        assert rank_res["status"] == 0
+        for key in ("out", "dq", "dk", "dv"):
+            assert rank_res[key] < 2e-2, rank_res
+            assert rank_res[key + "_vs_fp32"] < 4e-2, rank_res
