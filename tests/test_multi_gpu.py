@@ -66,3 +66,13 @@ def test_fused_context_parallel_attention_matches_nccl_and_fp32(tmp_path):
         for key in ("out", "dq", "dk", "dv"):
             assert rank_res[key] < 2e-2, rank_res
             assert rank_res[key + "_vs_fp32"] < 4e-2, rank_res
+
+
+def test_expert_parallel_moe_matches_single_gpu_experts(tmp_path):
+    _need_gpus(2)
+    out = str(tmp_path / "ep.json")
+    _torchrun(2, os.path.join(ROOT, "tests", "workers", "ep_compare.py"), ["--out", out], 29680)
+    for rank_res in json.load(open(out)):
+        assert rank_res["status"] == 0
+        for key in ("out", "dx", "d_gate_up", "d_down", "d_router"):
+            assert rank_res[key] < 3e-2, rank_res
