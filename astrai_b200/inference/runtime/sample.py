@@ -137,6 +137,57 @@ class SamplingPipeline(BaseSamplingStrategy):
         return tokens, logp
 
 
+# ---- fused device path (ops/csrc/sampling.cu): one launch per step instead of topk / sort / cumsum / scatter / multinomial
+_RNG = {"seed": None, "offset": 0}
+
+
+def manual_seed(seed: int):
+    """Seed of the fused sampler's Philox stream (the torch path uses the ``generator`` argument instead)."""
+    _RNG["seed"], _RNG["offset"] = int(seed) & 0x7FFFFFFFFFFFFFFF, 0
+
+
+def _fused_ok(logits: Tensor) -> bool:
+    if not (logits.is_cuda and logits.dim() == 2 and logits.dtype in (torch.float32, torch.bfloat16) and logits.stride(1) == 1):
+        return False
+    from astrai_b200.ops import native
+
+    return native.is_available()
+
+
+def _row_tensor(value: Scalar, rows: int, dtype, device) -> Tensor:
+    if isinstance(value, Tensor):
+        return value.to(device=device, dtype=dtype, non_blocking=True).reshape(-1).expand(rows).contiguous()
+    return torch.full((rows,), value, dtype=dtype, device=device)
+
+
+def _sample_fused(logits, temperature, top_k, top_p, frequency_penalty, input_ids, input_mask, return_logprobs, hints):
+    rows, dev = logits.shape[0], logits.device
+    if "greedy" in hints:
+        greedy = bool(hints["greedy"])
+    elif isinstance(temperature, Tensor):
+        greedy = bool((temperature == 0).all())
+    else:
+        greedy = temperature == 0
+    if "has_freq" in hints:
+        has_freq = bool(hints["has_freq"])
+    elif isinstance(frequency_penalty, Tensor):
+        has_freq = bool((frequency_penalty != 0).any())
+    else:
+        has_freq = frequency_penalty != 0
+    has_freq = has_freq and input_ids is not None
+    if _RNG["seed"] is None:
+        manual_seed(torch.initial_seed())
+    _RNG["offset"] += 1
+    hist = input_ids.to(dev, non_blocking=True).long().contiguous() if has_freq else None
+    mask = input_mask.to(dev, non_blocking=True).bool().contiguous() if (has_freq and input_mask is not None) else None
+    tokens, logp, _work = torch.ops.astrai_b200.sample_rows(
+        logits, _row_tensor(temperature, rows, torch.float32, dev), _row_tensor(top_k, rows, torch.int32, dev),
+        _row_tensor(top_p, rows, torch.float32, dev),
+        _row_tensor(frequency_penalty, rows, torch.float32, dev) if has_freq else None, hist, mask, greedy, _RNG["seed"],
+        _RNG["offset"])
+    return (tokens, logp) if return_logprobs else tokens
+
+
 @torch.inference_mode()
 def sample(logits: Tensor, temperature: Scalar = 1.0, top_k: Scalar = 0, top_p: Scalar = 1.0,
            frequency_penalty: Scalar = 0.0, input_ids: Optional[Tensor] = None, input_mask: Optional[Tensor] = None,
@@ -144,6 +195,9 @@ def sample(logits: Tensor, temperature: Scalar = 1.0, top_k: Scalar = 0, top_p: 
     """One-call sampling.  ``hints`` may carry host-side facts (``max_k``, ``top_p_active``, ``has_freq``, ``greedy``)
     so that no device value has to be inspected."""
     hints = hints or {}
+    if generator is None and filter_value == NEG_INF and _fused_ok(logits):
+        return _sample_fused(logits, temperature, top_k, top_p, frequency_penalty, input_ids, input_mask, return_logprobs,
+                             hints)
     if "has_freq" in hints:
         has_freq = hints["has_freq"]
     elif isinstance(frequency_penalty, Tensor):

@@ -609,6 +609,72 @@ Tensor fp8_gemm(const Tensor& a, const Tensor& b, const Tensor& scale_a, const T
   return out;
 }
 
+// ---- sampling
+std::tuple<Tensor, Tensor, Tensor> sample_rows(const Tensor& logits, const Tensor& temps, const c10::optional<Tensor>& top_k,
+                                               const c10::optional<Tensor>& top_p, const c10::optional<Tensor>& penalty,
+                                               const c10::optional<Tensor>& hist, const c10::optional<Tensor>& hist_mask,
+                                               bool all_greedy, int64_t seed, int64_t offset) {
+  TORCH_CHECK(logits.is_cuda() && logits.dim() == 2 && logits.stride(1) == 1 &&
+                  (logits.scalar_type() == at::kBFloat16 || logits.scalar_type() == at::kFloat), "sample_rows: bf16 / fp32 logits [rows, V]");
+  const int64_t rows = logits.size(0), V = logits.size(1);
+  auto f32 = [&](const Tensor& t) { return t.is_cuda() && t.scalar_type() == at::kFloat && t.is_contiguous() && t.numel() == rows; };
+  TORCH_CHECK(f32(temps), "sample_rows: fp32 temperatures [rows]");
+  if (top_k.has_value()) TORCH_CHECK(top_k->is_cuda() && top_k->scalar_type() == at::kInt && top_k->is_contiguous() && top_k->numel() == rows, "sample_rows: int32 top_k [rows]");
+  if (top_p.has_value()) TORCH_CHECK(f32(*top_p), "sample_rows: fp32 top_p [rows]");
+  if (penalty.has_value()) TORCH_CHECK(f32(*penalty), "sample_rows: fp32 penalty [rows]");
+  int hist_len = 0;
+  if (hist.has_value()) {
+    TORCH_CHECK(hist->is_cuda() && hist->scalar_type() == at::kLong && hist->is_contiguous() && hist->dim() == 2 && hist->size(0) == rows, "sample_rows: int64 history [rows, H]");
+    hist_len = (int)hist->size(1);
+    if (hist_mask.has_value()) TORCH_CHECK(hist_mask->is_cuda() && hist_mask->scalar_type() == at::kBool && hist_mask->is_contiguous() && hist_mask->sizes() == hist->sizes(), "sample_rows: bool history mask [rows, H]");
+  }
+  const c10::cuda::CUDAGuard guard(logits.device());
+  Tensor tok = at::empty({rows}, logits.options().dtype(at::kLong));
+  Tensor logp = at::empty({rows}, logits.options().dtype(at::kFloat));
+  Tensor work = all_greedy ? at::empty({0}, logp.options()) : at::empty({rows, V}, logp.options());
+  count();
+  const int rc = ab::sample_rows(logits.data_ptr(), logits.scalar_type() == at::kBFloat16, logits.stride(0), all_greedy ? nullptr : work.data_ptr<float>(),
+                                 temps.data_ptr<float>(), top_k.has_value() ? top_k->data_ptr<int>() : nullptr,
+                                 top_p.has_value() ? top_p->data_ptr<float>() : nullptr, penalty.has_value() ? penalty->data_ptr<float>() : nullptr,
+                                 hist.has_value() ? reinterpret_cast<const long long*>(hist->data_ptr<int64_t>()) : nullptr,
+                                 hist.has_value() && hist_mask.has_value() ? hist_mask->data_ptr<bool>() : nullptr, hist_len, (int)rows, (int)V,
+                                 all_greedy, (unsigned long long)seed, (unsigned long long)offset,
+                                 reinterpret_cast<long long*>(tok.data_ptr<int64_t>()), logp.data_ptr<float>(), stream());
+  TORCH_CHECK(rc == 0, "sample_rows launch failed with code ", rc);
+  return {tok, logp, work};
+}
+
+// ---- int8: per-row symmetric quantisation and the kind::i8 GEMM
+std::tuple<Tensor, Tensor> int8_quantize_rows(const Tensor& x) {
+  TORCH_CHECK(x.is_cuda() && x.dim() == 2 && x.scalar_type() == at::kBFloat16 && x.stride(1) == 1, "int8_quantize_rows: bf16 [rows, cols]");
+  const c10::cuda::CUDAGuard guard(x.device());
+  Tensor q = at::empty({x.size(0), x.size(1)}, x.options().dtype(at::kChar));
+  Tensor scale = at::empty({x.size(0)}, x.options().dtype(at::kFloat));
+  count();
+  const int rc = ab::int8_quantize_rows(x.data_ptr(), q.data_ptr(), scale.data_ptr<float>(), (int)x.size(0), (int)x.size(1), x.stride(0), stream());
+  TORCH_CHECK(rc == 0, "int8_quantize_rows: columns and row stride must be multiples of 8, 16-byte aligned input (code ", rc, ")");
+  return {q, scale};
+}
+
+Tensor int8_gemm(const Tensor& a, const Tensor& b, const Tensor& row_scale, const Tensor& col_scale, const c10::optional<Tensor>& bias) {
+  CHECK_CUDA_CONTIG(a);
+  CHECK_CUDA_CONTIG(b);
+  TORCH_CHECK(a.scalar_type() == at::kChar && b.scalar_type() == at::kChar && a.dim() == 2 && b.dim() == 2 && a.size(1) == b.size(1), "int8_gemm: int8 A [M,K], B [N,K]");
+  TORCH_CHECK(a.size(1) % 16 == 0, "int8_gemm: K must be a multiple of 16");
+  TORCH_CHECK(row_scale.is_cuda() && row_scale.scalar_type() == at::kFloat && row_scale.is_contiguous() && row_scale.numel() == a.size(0) &&
+                  col_scale.is_cuda() && col_scale.scalar_type() == at::kFloat && col_scale.is_contiguous() && col_scale.numel() == b.size(0),
+              "int8_gemm: fp32 row_scale [M], col_scale [N]");
+  if (bias.has_value()) TORCH_CHECK(bias->scalar_type() == at::kBFloat16 && bias->numel() == b.size(0) && bias->is_contiguous(), "int8_gemm: bf16 bias [N]");
+  const c10::cuda::CUDAGuard guard(a.device());
+  Tensor out = at::empty({a.size(0), b.size(0)}, a.options().dtype(at::kBFloat16));
+  count();
+  const int rc = ab::gemm_int8(a.data_ptr(), b.data_ptr(), out.data_ptr(), row_scale.data_ptr<float>(), col_scale.data_ptr<float>(),
+                               bias.has_value() ? bias->data_ptr() : nullptr, (int)a.size(0), (int)b.size(0), (int)a.size(1),
+                               out.stride(0), status_tensor(a.device()).data_ptr<int>(), stream());
+  TORCH_CHECK(rc == 0, "gemm_int8 launch failed with code ", rc);
+  return out;
+}
+
 Tensor mma_issue_bench(const Tensor& like, int64_t n, int64_t reps, bool lean) {
   const c10::cuda::CUDAGuard guard(like.device());
   Tensor out = at::zeros({1}, like.options().dtype(at::kLong));
@@ -854,6 +920,9 @@ TORCH_LIBRARY(astrai_b200, m) {
   m.def("tp_reduce_(Tensor stage, Tensor(a!) out, int world) -> ()", &tp_reduce_);
   m.def("fp8_quantize(Tensor x, Tensor scale, bool e5m2, bool with_transpose) -> (Tensor, Tensor, Tensor)", &fp8_quantize);
   m.def("fp8_gemm(Tensor a, Tensor b, Tensor scale_a, Tensor scale_b, Tensor? bias) -> Tensor", &fp8_gemm);
+  m.def("sample_rows(Tensor logits, Tensor temps, Tensor? top_k, Tensor? top_p, Tensor? penalty, Tensor? hist, Tensor? hist_mask, bool all_greedy, int seed, int offset) -> (Tensor, Tensor, Tensor)", &sample_rows);
+  m.def("int8_quantize_rows(Tensor x) -> (Tensor, Tensor)", &int8_quantize_rows);
+  m.def("int8_gemm(Tensor a, Tensor b, Tensor row_scale, Tensor col_scale, Tensor? bias) -> Tensor", &int8_gemm);
   m.def("mma_issue_bench(Tensor like, int n, int reps, bool lean) -> Tensor", &mma_issue_bench);
   m.def("moe_router(Tensor logits, int k, bool renorm) -> (Tensor, Tensor, Tensor, Tensor, Tensor)", &moe_router);
   m.def("moe_plan(Tensor counts, int max_tiles) -> (Tensor, Tensor, Tensor, Tensor)", &moe_plan);

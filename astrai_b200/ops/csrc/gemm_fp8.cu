@@ -9,6 +9,10 @@
 //                  fp32 accumulation in TMEM, bf16 output.  Same persistent warp-specialised structure as the bf16
 //                  kernel (TMA 4-stage ring of 128-byte-swizzled tiles, one MMA-issuing lane, double-buffered
 //                  accumulator, four epilogue warps); tcgen05.mma kind::f8f6f4 consumes 32 K-elements per instruction.
+//   gemm_int8      the same kernel instantiated for tcgen05.mma kind::i8: signed 8-bit operands, exact int32 accumulation
+//                  in TMEM, epilogue D = acc * row_scale[m] * col_scale[n] (+ bias) - per-token activation scales and
+//                  per-channel weight scales, both produced by int8_quantize_rows (symmetric, amax / 127 per row).
+//                  The reference has no int8 path.
 // These take the place of the reference's mma.sync m16n8k32 kernels (csrc/kernels/fp8/gemm.cuh:128-619).
 // Every mbarrier wait is bounded; expiry records a code in `status`.
 #include <cuda.h>
@@ -120,6 +124,20 @@ enum : int { ERR_F8_PRODUCER = 61, ERR_F8_MMA = 62, ERR_F8_EPILOGUE = 63 };
 __host__ __device__ constexpr uint32_t idesc_fp8(int M, int N, int a_fmt, int b_fmt) {
   return (1u << 4) | ((uint32_t)a_fmt << 7) | ((uint32_t)b_fmt << 10) | ((uint32_t)(N >> 3) << 17) | ((uint32_t)(M >> 4) << 24);
 }
+// kind::i8 instruction descriptor: int32 accumulator (D format 2), signed 8-bit operands (format 1), both K-major.
+__host__ __device__ constexpr uint32_t idesc_i8(int M, int N) {
+  return (2u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(N >> 3) << 17) | ((uint32_t)(M >> 4) << 24);
+}
+__device__ __forceinline__ void tc_mma_i8(uint32_t d_tmem, uint32_t a_lo, uint32_t b_lo, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t.reg .b64 da, db;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "mov.b64 da, {%1, %5};\n\t"
+      "mov.b64 db, {%2, %5};\n\t"
+      "tcgen05.mma.cta_group::1.kind::i8 [%0], da, db, %3, {%6, %6, %6, %6}, p;\n\t}" ::"r"(d_tmem),
+      "r"(a_lo), "r"(b_lo), "r"(idesc), "r"(accumulate), "r"(DESC_HI), "r"(0u)
+      : "memory");
+}
 __device__ __forceinline__ void tc_mma_f8(uint32_t d_tmem, uint32_t a_lo, uint32_t b_lo, uint32_t idesc, uint32_t accumulate) {
   asm volatile(
       "{\n\t.reg .pred p;\n\t.reg .b64 da, db;\n\t"
@@ -131,6 +149,9 @@ __device__ __forceinline__ void tc_mma_f8(uint32_t d_tmem, uint32_t a_lo, uint32
       : "memory");
 }
 
+// I8 = false: fp8 operands, scale_a / scale_b point at one fp32 scalar each.
+// I8 = true : int8 operands, scale_a is fp32 [M] (per row of A), scale_b fp32 [N] (per row of B = output column).
+template <bool I8>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 gemm_fp8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                 __nv_bfloat16* __restrict__ D, const float* __restrict__ scale_a, const float* __restrict__ scale_b,
@@ -228,7 +249,10 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
           tc_fence_after();
           const uint32_t a_lo = a_lo0 + stage * (STAGE_BYTES >> 4), b_lo = b_lo0 + stage * (STAGE_BYTES >> 4);
 #pragma unroll
-          for (int k = 0; k < BKB / UMMA_K; ++k) tc_mma_f8(d_tmem, a_lo + 2 * k, b_lo + 2 * k, idesc, (kb | k) ? 1u : 0u);
+          for (int k = 0; k < BKB / UMMA_K; ++k) {
+            if (I8) tc_mma_i8(d_tmem, a_lo + 2 * k, b_lo + 2 * k, idesc, (kb | k) ? 1u : 0u);
+            else tc_mma_f8(d_tmem, a_lo + 2 * k, b_lo + 2 * k, idesc, (kb | k) ? 1u : 0u);
+          }
           tc_commit(empty_bar(stage));
           if (++stage == STAGES) stage = 0, phase ^= 1u;
         }
@@ -241,7 +265,11 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
     }
   } else {
     const int quarter = warp & 3;
-    const float sc = (*scale_a) * (*scale_b);
+    const float sc_all = I8 ? 1.f : (*scale_a) * (*scale_b);
+    auto val = [&](uint32_t bits, float sc, int col) {  // accumulator bits -> scaled fp32
+      const float acc = I8 ? (float)(int)bits : __uint_as_float(bits);
+      return acc * (I8 ? sc * scale_b[col] : sc);
+    };
     int it = 0;
     bool ok = true;
     for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x, ++it) {
@@ -254,6 +282,7 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
       }
       tc_fence_after();
       const int row = m0 + quarter * 32 + lane;
+      const float sc = I8 ? (row < M ? scale_a[row] : 0.f) : sc_all;
       const uint32_t taddr0 = tmem_base + ((uint32_t)(quarter * 32) << 16) + buf * BN;
 #pragma unroll 1
       for (int c = 0; c < BN / 32; ++c) {
@@ -271,7 +300,7 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
               uint32_t* pw = reinterpret_cast<uint32_t*>(&pk);
 #pragma unroll
               for (int q = 0; q < 4; ++q) {
-                float lo = __uint_as_float(r[8 * j + 2 * q]) * sc, hi = __uint_as_float(r[8 * j + 2 * q + 1]) * sc;
+                float lo = val(r[8 * j + 2 * q], sc, col + 8 * j + 2 * q), hi = val(r[8 * j + 2 * q + 1], sc, col + 8 * j + 2 * q + 1);
                 if (bias) lo += __bfloat162float(bias[col + 8 * j + 2 * q]), hi += __bfloat162float(bias[col + 8 * j + 2 * q + 1]);
                 const __nv_bfloat162 h = __floats2bfloat162_rn(lo, hi);
                 pw[q] = *reinterpret_cast<const uint32_t*>(&h);
@@ -280,7 +309,7 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
             }
           } else {
             for (int j = 0; j < 32 && col + j < N; ++j) {
-              float f = __uint_as_float(r[j]) * sc;
+              float f = val(r[j], sc, col + j);
               if (bias) f += __bfloat162float(bias[col + j]);
               d[j] = __float2bfloat16_rn(f);
             }
@@ -342,17 +371,53 @@ int fp8_quantize(const void* x, void* q, void* qt, const float* scale, float* am
   return cudaGetLastError() == cudaSuccess ? 0 : -5;
 }
 
-int gemm_fp8(const void* A, const void* B, void* D, const float* scale_a, const float* scale_b, const void* bias, int M,
-             int N, int K, long long ldd, bool a_e5m2, bool b_e5m2, int* status, cudaStream_t st) {
-  if (M <= 0 || N <= 0 || K <= 0) return 0;
-  if ((reinterpret_cast<uintptr_t>(A) & 15) || (reinterpret_cast<uintptr_t>(B) & 15) || (K % 16)) return -1;
+namespace {
+
+// One warp per row: amax over the row, scale = amax / 127 (1 for an all-zero row), q = round(x / scale) in [-127, 127].
+__global__ void int8_quantize_rows_kernel(const __nv_bfloat16* __restrict__ x, int8_t* __restrict__ q, float* __restrict__ scale,
+                                          int rows, int cols, long long ldx) {
+  const int row = (int)(((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5), lane = threadIdx.x & 31;
+  if (row >= rows) return;
+  const __nv_bfloat16* xr = x + (long long)row * ldx;
+  float amax = 0.f;
+  for (int c = lane * 8; c < cols; c += 256) {
+    const uint4 v = *reinterpret_cast<const uint4*>(xr + c);
+    const __nv_bfloat162* p = reinterpret_cast<const __nv_bfloat162*>(&v);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const float2 f = __bfloat1622float2(p[i]);
+      amax = fmaxf(amax, fmaxf(fabsf(f.x), fabsf(f.y)));
+    }
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+  const float sc = amax > 0.f ? amax / 127.f : 1.f, inv = 1.f / sc;
+  if (lane == 0) scale[row] = sc;
+  int8_t* qr = q + (long long)row * cols;
+  for (int c = lane * 8; c < cols; c += 256) {
+    const uint4 v = *reinterpret_cast<const uint4*>(xr + c);
+    const __nv_bfloat162* p = reinterpret_cast<const __nv_bfloat162*>(&v);
+    int8_t o[8];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const float2 f = __bfloat1622float2(p[i]);
+      o[2 * i] = (int8_t)max(-127, min(127, __float2int_rn(f.x * inv)));
+      o[2 * i + 1] = (int8_t)max(-127, min(127, __float2int_rn(f.y * inv)));
+    }
+    *reinterpret_cast<uint2*>(qr + c) = *reinterpret_cast<const uint2*>(o);
+  }
+}
+
+template <bool I8>
+int launch_q8(const void* A, const void* B, void* D, const float* scale_a, const float* scale_b, const void* bias, int M, int N,
+              int K, long long ldd, uint32_t idesc, int* status, cudaStream_t st) {
   CUtensorMap ma, mb;
   if (!make_map_u8(&ma, A, K, M, K, BKB, BM)) return -1000 - g_last_map_error;
   if (!make_map_u8(&mb, B, K, N, K, BKB, BN)) return -2000 - g_last_map_error;
   static bool configured = false;
   static int sms = 0;
   if (!configured) {
-    if (cudaFuncSetAttribute(gemm_fp8_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES) != cudaSuccess) return -4;
+    if (cudaFuncSetAttribute(gemm_fp8_kernel<I8>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES) != cudaSuccess) return -4;
     int dev = 0;
     cudaGetDevice(&dev);
     cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
@@ -360,9 +425,33 @@ int gemm_fp8(const void* A, const void* B, void* D, const float* scale_a, const 
   }
   const int tiles = ((M + BM - 1) / BM) * ((N + BN - 1) / BN);
   const int grid = tiles < sms ? tiles : sms;
-  gemm_fp8_kernel<<<grid, NUM_THREADS, SMEM_BYTES, st>>>(ma, mb, (__nv_bfloat16*)D, scale_a, scale_b, (const __nv_bfloat16*)bias,
-                                                         M, N, K, ldd, idesc_fp8(BM, BN, a_e5m2 ? 1 : 0, b_e5m2 ? 1 : 0), status);
+  gemm_fp8_kernel<I8><<<grid, NUM_THREADS, SMEM_BYTES, st>>>(ma, mb, (__nv_bfloat16*)D, scale_a, scale_b, (const __nv_bfloat16*)bias,
+                                                             M, N, K, ldd, idesc, status);
   return cudaGetLastError() == cudaSuccess ? 0 : -5;
+}
+
+}  // namespace
+
+int int8_quantize_rows(const void* x, void* q, float* scale, int rows, int cols, long long ldx, cudaStream_t st) {
+  if (rows <= 0 || cols <= 0) return 0;
+  if (cols % 8 || ldx % 8 || (reinterpret_cast<uintptr_t>(x) & 15) || (reinterpret_cast<uintptr_t>(q) & 7)) return -1;
+  const long long threads = (long long)rows * 32;
+  int8_quantize_rows_kernel<<<(unsigned)((threads + 255) / 256), 256, 0, st>>>((const __nv_bfloat16*)x, (int8_t*)q, scale, rows, cols, ldx);
+  return cudaGetLastError() == cudaSuccess ? 0 : -5;
+}
+
+int gemm_int8(const void* A, const void* B, void* D, const float* row_scale, const float* col_scale, const void* bias, int M,
+              int N, int K, long long ldd, int* status, cudaStream_t st) {
+  if (M <= 0 || N <= 0 || K <= 0) return 0;
+  if ((reinterpret_cast<uintptr_t>(A) & 15) || (reinterpret_cast<uintptr_t>(B) & 15) || (K % 16)) return -1;
+  return launch_q8<true>(A, B, D, row_scale, col_scale, bias, M, N, K, ldd, idesc_i8(BM, BN), status, st);
+}
+
+int gemm_fp8(const void* A, const void* B, void* D, const float* scale_a, const float* scale_b, const void* bias, int M,
+             int N, int K, long long ldd, bool a_e5m2, bool b_e5m2, int* status, cudaStream_t st) {
+  if (M <= 0 || N <= 0 || K <= 0) return 0;
+  if ((reinterpret_cast<uintptr_t>(A) & 15) || (reinterpret_cast<uintptr_t>(B) & 15) || (K % 16)) return -1;
+  return launch_q8<false>(A, B, D, scale_a, scale_b, bias, M, N, K, ldd, idesc_fp8(BM, BN, a_e5m2 ? 1 : 0, b_e5m2 ? 1 : 0), status, st);
 }
 
 }  // namespace ab

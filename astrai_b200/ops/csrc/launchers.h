@@ -146,6 +146,20 @@ int fp8_quantize(const void* x, void* q, void* qt, const float* scale, float* am
 int gemm_fp8(const void* A, const void* B, void* D, const float* scale_a, const float* scale_b, const void* bias, int M,
              int N, int K, long long ldd, bool a_e5m2, bool b_e5m2, int* status, cudaStream_t st);
 
+// ---- int8 (gemm_fp8.cu).  Symmetric per-row quantisation: scale[r] = max|x[r, :]| / 127, q = round(x / scale).
+int int8_quantize_rows(const void* x, void* q, float* scale, int rows, int cols, long long ldx, cudaStream_t st);
+// D[M,N] bf16 = (A[M,K] . B[N,K]^T in exact int32) * row_scale[m] * col_scale[n] (+ bias[N] bf16); K a multiple of 16.
+int gemm_int8(const void* A, const void* B, void* D, const float* row_scale, const float* col_scale, const void* bias, int M,
+              int N, int K, long long ldd, int* status, cudaStream_t st);
+
+// ---- sampling (sampling.cu): one token per row of logits [rows, V] (bf16 or fp32, row stride ld elements).
+// `work` fp32 [rows, V] receives the final (scaled, filtered, penalised) logits.  top_k / top_p / penalty / hist may be
+// null.  hist int64 [rows, hist_len] with optional bool mask.  `all_greedy`: argmax of the raw logits for every row.
+int sample_rows(const void* logits, bool is_bf16, long long ld, float* work, const float* temps, const int* top_k,
+                const float* top_p, const float* penalty, const long long* hist, const bool* hist_mask, int hist_len,
+                int rows, int V, bool all_greedy, unsigned long long seed, unsigned long long offset, long long* out_tok,
+                float* out_logp, cudaStream_t st);
+
 // ---- mixture of experts (moe.cu, gemm_grouped.cu)
 int moe_router(const void* logits, void* probs, long long* idx, void* weights, int* counts, float* probsum, long long tokens,
                int E, int K, bool renorm, bool is_bf16, cudaStream_t st);
