@@ -609,6 +609,41 @@ Tensor fp8_gemm(const Tensor& a, const Tensor& b, const Tensor& scale_a, const T
   return out;
 }
 
+// ---- block-scaled fp8
+std::tuple<Tensor, Tensor> fp8_quantize_block(const Tensor& x, bool weight) {
+  TORCH_CHECK(x.is_cuda() && x.dim() == 2 && x.scalar_type() == at::kBFloat16 && x.stride(1) == 1 && x.size(1) % 128 == 0,
+              "fp8_quantize_block: bf16 [rows, cols] with cols a multiple of 128");
+  const c10::cuda::CUDAGuard guard(x.device());
+  const int64_t rows = x.size(0), cols = x.size(1);
+  Tensor q = at::empty({rows, cols}, x.options().dtype(at::kFloat8_e4m3fn));
+  Tensor s = weight ? at::empty({(rows + 127) / 128, cols / 128}, x.options().dtype(at::kFloat))
+                    : at::empty({cols / 128, rows}, x.options().dtype(at::kFloat));
+  count();
+  const int rc = weight ? ab::fp8_quantize_weight_block(x.data_ptr(), q.data_ptr(), s.data_ptr<float>(), (int)rows, (int)cols, x.stride(0), stream())
+                        : ab::fp8_quantize_act_block(x.data_ptr(), q.data_ptr(), s.data_ptr<float>(), (int)rows, (int)cols, x.stride(0), stream());
+  TORCH_CHECK(rc == 0, "fp8_quantize_block failed with code ", rc);
+  return {q, s};
+}
+
+Tensor fp8_gemm_block(const Tensor& a, const Tensor& sa_t, const Tensor& b, const Tensor& sb, const c10::optional<Tensor>& bias) {
+  CHECK_CUDA_CONTIG(a);
+  CHECK_CUDA_CONTIG(b);
+  TORCH_CHECK(a.scalar_type() == at::kFloat8_e4m3fn && b.scalar_type() == at::kFloat8_e4m3fn && a.dim() == 2 && b.dim() == 2 && a.size(1) == b.size(1), "fp8_gemm_block: E4M3 A [M,K], B [N,K]");
+  const int64_t M = a.size(0), N = b.size(0), K = a.size(1);
+  TORCH_CHECK(K % 128 == 0, "fp8_gemm_block: K must be a multiple of 128");
+  TORCH_CHECK(sa_t.is_cuda() && sa_t.scalar_type() == at::kFloat && sa_t.is_contiguous() && sa_t.dim() == 2 && sa_t.size(0) == K / 128 && sa_t.size(1) == M, "fp8_gemm_block: sa_t fp32 [K/128, M]");
+  TORCH_CHECK(sb.is_cuda() && sb.scalar_type() == at::kFloat && sb.is_contiguous() && sb.dim() == 2 && sb.size(0) == (N + 127) / 128 && sb.size(1) == K / 128, "fp8_gemm_block: sb fp32 [ceil(N/128), K/128]");
+  if (bias.has_value()) TORCH_CHECK(bias->scalar_type() == at::kBFloat16 && bias->numel() == N && bias->is_contiguous(), "fp8_gemm_block: bf16 bias [N]");
+  const c10::cuda::CUDAGuard guard(a.device());
+  Tensor out = at::empty({M, N}, a.options().dtype(at::kBFloat16));
+  count();
+  const int rc = ab::gemm_fp8_block(a.data_ptr(), b.data_ptr(), out.data_ptr(), sa_t.data_ptr<float>(), sb.data_ptr<float>(),
+                                    bias.has_value() ? bias->data_ptr() : nullptr, (int)M, (int)N, (int)K, out.stride(0),
+                                    status_tensor(a.device()).data_ptr<int>(), stream());
+  TORCH_CHECK(rc == 0, "gemm_fp8_block launch failed with code ", rc);
+  return out;
+}
+
 // ---- sampling
 std::tuple<Tensor, Tensor, Tensor> sample_rows(const Tensor& logits, const Tensor& temps, const c10::optional<Tensor>& top_k,
                                                const c10::optional<Tensor>& top_p, const c10::optional<Tensor>& penalty,
@@ -921,6 +956,8 @@ TORCH_LIBRARY(astrai_b200, m) {
   m.def("fp8_quantize(Tensor x, Tensor scale, bool e5m2, bool with_transpose) -> (Tensor, Tensor, Tensor)", &fp8_quantize);
   m.def("fp8_gemm(Tensor a, Tensor b, Tensor scale_a, Tensor scale_b, Tensor? bias) -> Tensor", &fp8_gemm);
   m.def("sample_rows(Tensor logits, Tensor temps, Tensor? top_k, Tensor? top_p, Tensor? penalty, Tensor? hist, Tensor? hist_mask, bool all_greedy, int seed, int offset) -> (Tensor, Tensor, Tensor)", &sample_rows);
+  m.def("fp8_quantize_block(Tensor x, bool weight) -> (Tensor, Tensor)", &fp8_quantize_block);
+  m.def("fp8_gemm_block(Tensor a, Tensor sa_t, Tensor b, Tensor sb, Tensor? bias) -> Tensor", &fp8_gemm_block);
   m.def("int8_quantize_rows(Tensor x) -> (Tensor, Tensor)", &int8_quantize_rows);
   m.def("int8_gemm(Tensor a, Tensor b, Tensor row_scale, Tensor col_scale, Tensor? bias) -> Tensor", &int8_gemm);
   m.def("mma_issue_bench(Tensor like, int n, int reps, bool lean) -> Tensor", &mma_issue_bench);

@@ -146,6 +146,14 @@ int fp8_quantize(const void* x, void* q, void* qt, const float* scale, float* am
 int gemm_fp8(const void* A, const void* B, void* D, const float* scale_a, const float* scale_b, const void* bias, int M,
              int N, int K, long long ldd, bool a_e5m2, bool b_e5m2, int* status, cudaStream_t st);
 
+// ---- block-scaled fp8 (gemm_fp8_block.cu): E4M3 with one fp32 scale per 1 x 128 activation block / 128 x 128 weight block.
+// sa_t is [cols / 128, rows] (block-major), sb is [ceil(rows / 128), cols / 128]; cols (= K) must be a multiple of 128.
+int fp8_quantize_act_block(const void* x, void* q, float* sa_t, int rows, int cols, long long ldx, cudaStream_t st);
+int fp8_quantize_weight_block(const void* w, void* q, float* sb, int rows, int cols, long long ldw, cudaStream_t st);
+// D[M,N] bf16 = sum over K blocks of sa_t[kb, m] * sb[n / 128, kb] * (A[m, kb] . B[n, kb]) (+ bias[N] bf16).
+int gemm_fp8_block(const void* A, const void* B, void* D, const float* sa_t, const float* sb, const void* bias, int M, int N, int K,
+                   long long ldd, int* status, cudaStream_t st);
+
 // ---- int8 (gemm_fp8.cu).  Symmetric per-row quantisation: scale[r] = max|x[r, :]| / 127, q = round(x / scale).
 int int8_quantize_rows(const void* x, void* q, float* scale, int rows, int cols, long long ldx, cudaStream_t st);
 // D[M,N] bf16 = (A[M,K] . B[N,K]^T in exact int32) * row_scale[m] * col_scale[n] (+ bias[N] bf16); K a multiple of 16.
