@@ -1,4 +1,4 @@
-"""Kernel timing harness: ``python -m astrai_b200.ops.bench_kernels {gemm,skinny,flash,fp8,mma,decode}``.
+"""Kernel timing harness: ``python -m astrai_b200.ops.bench_kernels {gemm,skinny,flash,fp8,quant,sample,mma,decode}``.
 
 CUDA events on the launching stream, 3 warm-ups, median of N timed launches, a 256 MB buffer written between timed
 launches to flush the 126 MB L2.  Library kernels (cuBLAS through ``torch.matmul``, cuDNN / flash through SDPA) are
@@ -119,6 +119,53 @@ def bench_fp8():
         print(f"  {n:6d} x {k:5d}: {a:6.0f} | {b:6.0f} | {c:6.0f}")
 
 
+def bench_quant():
+    """Block-scaled fp8 and int8 GEMMs next to the per-tensor fp8 and bf16 kernels."""
+    from astrai_b200 import ops
+    from astrai_b200.ops import fp8, fp8_block, int8
+
+    t = _timer()
+    m = 8192
+    print("quantised GEMMs, M = 8192 (TFLOP/s or TOP/s): block fp8 | per-tensor fp8 | int8 | bf16 || act quantise GB/s: block fp8 | int8")
+    for n, k in [(3072, 2048), (11264, 2048), (2048, 5632), (8192, 8192)]:
+        x = torch.randn(m, k, device="cuda", dtype=torch.bfloat16)
+        w = torch.randn(n, k, device="cuda", dtype=torch.bfloat16)
+        one = torch.ones(1, device="cuda")
+        xq, _, _ = fp8.quantize_bf16(x, one, "e4m3")
+        wq, _, _ = fp8.quantize_bf16(w, one, "e4m3")
+        xb, sa = fp8_block.quantize_act_block(x)
+        wb, sb = fp8_block.quantize_weight_block(w)
+        xi, si = int8.quantize_rows(x)
+        wi, sw = int8.quantize_rows(w)
+        fl = 2.0 * m * n * k / 1e9
+        a = fl / t(lambda: fp8_block.mm_fp8_block(xb, sa, wb, sb))
+        b = fl / t(lambda: fp8.mm_fp8(xq, wq, one, one))
+        c = fl / t(lambda: int8.mm_int8(xi, si, wi, sw))
+        d = fl / t(lambda: ops.gemm(x, w))
+        e = (m * k * 3) / 1e6 / t(lambda: fp8_block.quantize_act_block(x))
+        f = (m * k * 3) / 1e6 / t(lambda: int8.quantize_rows(x))
+        print(f"  {n:6d} x {k:5d}: {a:6.0f} | {b:6.0f} | {c:6.0f} | {d:6.0f} || {e:6.0f} | {f:6.0f}")
+
+
+def bench_sample():
+    """The fused sampling kernel against the PyTorch pipeline (topk / sort / cumsum / scatter / multinomial)."""
+    import importlib
+
+    S = importlib.import_module("astrai_b200.inference.runtime.sample")
+    t = _timer()
+    print("sampling, top_k=50 top_p=0.9 temperature=0.8 (us per step): fused kernel | torch pipeline")
+    for b, v in [(1, 100000), (16, 100000), (64, 100000), (256, 32000)]:
+        logits = torch.randn(b, v, device="cuda", dtype=torch.bfloat16) * 2
+        temps = torch.full((b,), 0.8, device="cuda")
+        ks = torch.full((b,), 50, device="cuda", dtype=torch.int32)
+        ps = torch.full((b,), 0.9, device="cuda")
+        hints = {"max_k": 50, "top_p_active": True, "has_freq": False, "greedy": False}
+        gen = torch.Generator(device="cuda").manual_seed(1)
+        fused = t(lambda: S.sample(logits, temps, ks, ps, hints=hints))
+        plain = t(lambda: S.sample(logits, temps, ks, ps, hints=hints, generator=gen))
+        print(f"  B={b:3d} V={v:6d}: {fused * 1e3:7.1f} | {plain * 1e3:7.1f}")
+
+
 def bench_mma():
     from astrai_b200.ops import native
 
@@ -161,7 +208,7 @@ def bench_decode():
 
 
 if __name__ == "__main__":
-    table = {"gemm": bench_gemm, "skinny": bench_skinny, "flash": bench_flash, "fp8": bench_fp8, "mma": bench_mma, "decode": bench_decode}
+    table = {"gemm": bench_gemm, "skinny": bench_skinny, "flash": bench_flash, "fp8": bench_fp8, "quant": bench_quant, "sample": bench_sample, "mma": bench_mma, "decode": bench_decode}
     which = sys.argv[1:] or list(table)
     for name in which:
         table[name]()
