@@ -219,11 +219,13 @@ class _EPExpertsFn(torch.autograd.Function):
 
 
 def ep_experts(x: Tensor, idx: Tensor, weights: Tensor, counts: Tensor, w_gate_up: Tensor, w_down: Tensor,
-               ctx: Optional[EPContext] = None, capacity_factor: Optional[float] = None) -> Tensor:
+               ctx: Optional[EPContext] = None, capacity_factor: Optional[float] = 2.0) -> Tensor:
     """Routed-expert output for the local tokens; collective over the expert-parallel group.
 
     ``w_gate_up`` ``[E / W, 2F, H]`` and ``w_down`` ``[E / W, H, F]`` are this rank's experts; ``idx`` / ``counts`` use
-    global expert numbers (rank ``d`` owns ``[d * E / W, (d + 1) * E / W)``).
+    global expert numbers (rank ``d`` owns ``[d * E / W, (d + 1) * E / W)``).  The sorted buffers hold
+    ``capacity_factor`` times the balanced share of rows (``None``: the worst case, every pair of every rank); a step
+    whose routing sends more rows to one rank records error 72 in the kernel status word instead of overflowing.
     """
     ep = ctx or get_context()
     if ep is None:
@@ -247,12 +249,14 @@ class EPMoE(nn.Module):
     """
 
     def __init__(self, dim: int, moe_inter_dim: int, n_experts: int, top_k: int, ep_size: int, ep_rank: int,
-                 norm_topk_prob: bool = True, init_std: float = 0.02, dtype=None, device=None):
+                 norm_topk_prob: bool = True, init_std: float = 0.02, capacity_factor: Optional[float] = 2.0, dtype=None,
+                 device=None):
         super().__init__()
         if n_experts % ep_size:
             raise ValueError("n_experts must be a multiple of ep_size")
         self.dim, self.inter, self.n_experts, self.top_k = dim, moe_inter_dim, n_experts, top_k
         self.ep_size, self.ep_rank, self.norm_topk_prob = ep_size, ep_rank, norm_topk_prob
+        self.capacity_factor = capacity_factor
         local = n_experts // ep_size
         kw = {"dtype": dtype, "device": device}
         self.router = nn.Parameter(torch.empty(n_experts, dim, **kw).normal_(0, init_std))
@@ -273,7 +277,7 @@ class EPMoE(nn.Module):
         flat = x.reshape(-1, shape[-1])
         logits = F.linear(flat, self.router)
         _probs, idx, weights, counts, _psum = moe.route(logits, self.top_k, self.norm_topk_prob)
-        out = ep_experts(flat, idx, weights, counts, self.gate_up, self.down, ctx=ctx)
+        out = ep_experts(flat, idx, weights, counts, self.gate_up, self.down, ctx=ctx, capacity_factor=self.capacity_factor)
         return out.view(shape)
 
 

@@ -277,7 +277,8 @@ def run_ours(args):
         torch.cuda.empty_cache()
         # ---- (2) end to end through Trainer.train(): host data, pinned H2D per micro-batch, D2H per step -----------
         if not args.skip_e2e:
-            host = _host_tokens((n_micro + 2) * BPD, SEQ, MODEL["vocab_size"], seed=100 + rank)
+            # the trainer's sampler deals the dataset out over the ranks: size it so that every rank has all its micro-batches
+            host = _host_tokens((n_micro + 2) * BPD * world, SEQ, MODEL["vocab_size"], seed=100)
             timer = _StepTimer(args.warmup, args.steps, ACCUM)
             t2 = Trainer(make_config(host, tempfile.mkdtemp(prefix="bench_ckpt_")), callbacks=[timer])
             # keep the stock callbacks except the ones that write 2 GB checkpoints at exit
@@ -319,7 +320,8 @@ def run_reference(args):
 
     def attempt(tied: bool):
         cfg.tie_word_embeddings = tied
-        host = _host_tokens((n_micro + 2) * BPD * 1, SEQ, MODEL["vocab_size"], seed=100 + rank)
+        # the reference's sampler deals the dataset out over the ranks too: every rank needs all its micro-batches
+        host = _host_tokens((n_micro + 2) * BPD * world, SEQ, MODEL["vocab_size"], seed=100)
         tc = TrainConfig(
             model_fn=model_fn, strategy="seq", dataset=host,
             optimizer_fn=lambda m: torch.optim.AdamW(m.parameters(), lr=LR, weight_decay=WD, fused=True),
