@@ -3,7 +3,9 @@
 ``dense_attention`` serves training and the no-cache forward: q ``[B,S,Hq,D]``, k/v ``[B,L,Hkv,D]``, optional
 bool mask (True = attend) or causal flag - the contract of ``astrai/extension/backend/attention.py:256-303``
 for ``fwd=None``.  Unmasked and causal calls run on the tcgen05 flash kernels (:mod:`astrai_b200.ops.flash`);
-an arbitrary boolean mask goes to the library SDPA kernel.  The packed prefill / paged decode entry points used by the inference engine live in
+an arbitrary boolean mask goes to the library SDPA kernel.  While a context-parallel context is installed
+(:func:`astrai_b200.parallel.context_parallel.init_context_parallel`) causal calls are the sequence-sharded
+``ring_attention``.  The packed prefill / paged decode entry points used by the inference engine live in
 :mod:`astrai_b200.ops.paged_attention`.
 """
 
@@ -49,6 +51,17 @@ def dense_attention(q: Tensor, k: Tensor, v: Tensor, mask: Optional[Tensor] = No
     """Softmax attention with GQA head sharing; returns ``[B,S,Hq,Dv]``."""
     if not q.is_cuda:
         return reference.attention(q, k, v, mask, causal, scale)
+    if causal and mask is None:
+        # Sequence-sharded training: with a context-parallel context installed the local rows are this rank's zig-zag
+        # share of the sequence and the keys of the other ranks are fetched inside the attention kernel.
+        from astrai_b200.parallel import context_parallel as cpar
+
+        cp = cpar.get_context()
+        if cp is not None:
+            if not cpar.supported(q, k, v):
+                raise RuntimeError("context parallelism is on, but this attention call is outside what the sharded "
+                                   "kernels take (bf16, head_dim 64 / 128, local length a multiple of 256)")
+            return cpar.ring_attention(q, k, v, scale=scale, ctx=cp, comm=getattr(cp, "comm", "p2p"))
     if _use_flash():
         if mask is None and flash.supported(q, k, v):
             return flash.flash_attention(q, k, v, causal=causal, scale=scale)

@@ -12,6 +12,11 @@ staging slot of the rank that owns those keys and the owner sums the slots (``op
 reduce-scatter without a collective call.  ``comm="nccl"`` is the baseline it is measured against: all-gather, the
 same kernels on gathered tensors, reduce-scatter.
 
+Model integration: after :func:`init_context_parallel` every causal dense attention call of the model
+(``ops/attention.py::dense_attention``) is this op; the caller shards ``input_ids`` / ``target_ids`` with
+:func:`zigzag_split` and passes ``position_ids = zigzag_positions(...)`` so that rotary embeddings see global positions.
+Parameters are replicated over the context-parallel ranks, so their gradients are reduced like data-parallel ones.
+
 The reference trains with data parallelism only (``astrai/parallel/setup.py:44-90``) and has no counterpart; sequence
 length there is bounded by one GPU's activation memory.
 """
@@ -60,10 +65,11 @@ def zigzag_positions(seq_len: int, world: int, rank: int, device=None) -> Tensor
 class CPContext:
     """Per-process state of context-parallel attention: arena, flags, epochs, double-buffered K/V source and staging."""
 
-    def __init__(self, arena, rank: int, world: int, timeout_s: float = 60.0, n_copy_ctas: int = 8, group=None):
+    def __init__(self, arena, rank: int, world: int, timeout_s: float = 60.0, n_copy_ctas: int = 8, group=None,
+                 comm: str = "p2p"):
         if not 2 <= world <= symm.MAX_RANKS:
             raise ValueError(f"context parallel world size must be in 2..{symm.MAX_RANKS}")
-        self.arena, self.rank, self.world, self.group = arena, rank, world, group
+        self.arena, self.rank, self.world, self.group, self.comm = arena, rank, world, group, comm
         self.timeout_s, self.n_copy_ctas = float(timeout_s), int(n_copy_ctas)
         self.flags = arena.alloc_flags(1)
         self._src: Dict[Tuple[int, int, int, int], symm.SymmBuffer] = {}

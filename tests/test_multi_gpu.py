@@ -76,3 +76,13 @@ def test_expert_parallel_moe_matches_single_gpu_experts(tmp_path):
         assert rank_res["status"] == 0
         for key in ("out", "dx", "d_gate_up", "d_down", "d_router"):
             assert rank_res[key] < 3e-2, rank_res
+
+
+def test_sequence_sharded_model_step_matches_whole_sequence(tmp_path):
+    _need_gpus(2)
+    out = str(tmp_path / "cpm.json")
+    _torchrun(2, os.path.join(ROOT, "tests", "workers", "cp_model.py"), ["--out", out], 29700)
+    for r in json.load(open(out)):
+        assert r["status"] == 0
+        assert abs(r["loss_cp"] - r["loss_full"]) < 2e-2, r
+        assert r["worst_grad"] < 5e-2, r
