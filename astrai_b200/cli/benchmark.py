@@ -209,8 +209,10 @@ def decode(preset, device, batch_size, prompt_len, gen_len, cuda_graph):
 @click.option("--top_k", type=int, default=50)
 @click.option("--seed", type=int, default=0)
 @click.option("--time_scale", type=float, default=1.0, help="Stretch (>1) or compress (<1) the arrival times.")
+@click.option("--chunked_prefill/--no-chunked_prefill", default=False)
+@click.option("--max_prefill_tokens", type=int, default=8192)
 def serve(preset, device, n_requests, rate, max_batch_size, max_seq_len, kv_cache_tokens, temperature, top_p, top_k, seed,
-          time_scale):
+          time_scale, chunked_prefill, max_prefill_tokens):
     """Continuous-batching load test with a paged KV cache (16-token pages) and the radix prefix cache."""
     import torch
 
@@ -218,7 +220,8 @@ def serve(preset, device, n_requests, rate, max_batch_size, max_seq_len, kv_cach
 
     model = build_model(preset, device, torch.bfloat16 if device != "cpu" else torch.float32)
     sched = InferenceScheduler(model, _IdTokenizer(), max_batch_size=max_batch_size, max_seq_len=max_seq_len, page_size=16,
-                               kv_cache_tokens=kv_cache_tokens or max_batch_size * 4608, paged=True)
+                               kv_cache_tokens=kv_cache_tokens or max_batch_size * 4608, paged=True,
+                               chunked_prefill=chunked_prefill, max_prefill_tokens=max_prefill_tokens)
     reqs = make_requests(n_requests, rate, model.config.vocab_size, seed)
     sched.run_batch([reqs[0]["ids"][:64]], max_tokens=4, temperature=0.0)  # warm-up
     sched.start()
@@ -227,6 +230,7 @@ def serve(preset, device, n_requests, rate, max_batch_size, max_seq_len, kv_cach
     finally:
         sched.stop()
     res.update({"benchmark": "serve", "preset": preset, "rate": rate, "max_batch_size": max_batch_size, "page_size": 16,
+                "chunked_prefill": chunked_prefill, "max_prefill_tokens": max_prefill_tokens,
                 "sampling": {"temperature": temperature, "top_p": top_p, "top_k": top_k, "seed": seed}})
     click.echo(json.dumps(res))
 

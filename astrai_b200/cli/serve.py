@@ -27,6 +27,9 @@ from astrai_b200.cli.common import flatten_sections, load_yaml, merge_config, to
 @click.option("--page_size", type=int, default=16, help="Tokens per KV page (1 = contiguous cache).")
 @click.option("--kv_cache_tokens", type=int, default=None, help="Size of the paged KV pool in tokens.")
 @click.option("--cuda_graph/--no-cuda_graph", default=True)
+@click.option("--chunked_prefill/--no-chunked_prefill", default=False,
+              help="Spread long prompts over several steps (at most --max_prefill_tokens prompt tokens per step).")
+@click.option("--max_prefill_tokens", type=int, default=8192)
 @click.option("--reload", is_flag=True, default=False)
 @click.pass_context
 def serve_command(ctx: click.Context, config: Optional[str], **opts):
@@ -35,7 +38,8 @@ def serve_command(ctx: click.Context, config: Optional[str], **opts):
     from astrai_b200.inference import run_server
 
     engine_kwargs = {"enable_cuda_graph": o["cuda_graph"], "paged": o["page_size"] > 1, "page_size": o["page_size"],
-                     "kv_cache_tokens": o["kv_cache_tokens"]}
+                     "kv_cache_tokens": o["kv_cache_tokens"], "chunked_prefill": o["chunked_prefill"],
+                     "max_prefill_tokens": o["max_prefill_tokens"]}
     run_server(param_path=Path(o["param_path"]), host=o["host"], port=o["port"], reload=o["reload"], device=o["device"],
                dtype=torch_dtype(o["dtype"]), max_batch_size=o["max_batch_size"], max_seq_len=o["max_seq_len"], **engine_kwargs)
 

@@ -182,9 +182,13 @@ class TaskCacheManager:
         return self._states.get(task_id)
 
     def bind(self, task_ids: List[str], workspace: InferenceWorkspace, device=None, start_pos: Optional[int] = None,
-             start_positions: Optional[List[int]] = None) -> KVCache:
+             start_positions: Optional[List[int]] = None, end_positions: Optional[List[int]] = None) -> KVCache:
+        """``end_positions`` (prefill only) stops each request's chunk short of its full length: the keys visible to the
+        chunk are ``[0, end)`` and the query rows ``[start, end)``."""
         states = [self._states[t] for t in task_ids]
         rows, lens = [s.req_idx for s in states], [s.length for s in states]
+        if end_positions is not None:
+            lens = [min(n, e) for n, e in zip(lens, end_positions)]
         sig, prev = tuple(rows), self._bind_state
         decode = start_pos is None and start_positions is None
         steady = (decode and prev is not None and prev.sig == sig and len(prev.seq_lens) == len(lens)

@@ -13,7 +13,7 @@ import logging
 import time
 from contextlib import contextmanager
 from dataclasses import dataclass
-from typing import List, Optional
+from typing import Dict, List, Optional
 
 import torch
 from torch import Tensor
@@ -159,35 +159,48 @@ class Executor:
 
     # -- prefill ------------------------------------------------------------------------------------------------------------
     def execute_prefill(self, tasks: List[Task], prompt_len: Optional[int] = None, start_pos: Optional[int] = None,
-                        return_logprobs: bool = False):
-        """Packed prefill of ``tasks`` (any mix of lengths).  Each request recomputes positions ``[start, len)`` where
-        ``start = min(cached prefix, len - 1)`` unless ``start_pos`` forces one value for all."""
+                        return_logprobs: bool = False, end_positions: Optional[Dict[str, int]] = None):
+        """Packed prefill of ``tasks`` (any mix of lengths).  Each request recomputes positions ``[start, end)`` where
+        ``start`` is where its previous chunk stopped, else ``min(cached prefix, len - 1)``, unless ``start_pos`` forces
+        one value for all; ``end`` is the prompt length unless ``end_positions[task_id]`` stops the chunk earlier
+        (chunked prefill).  Only requests whose chunk reaches the end of the prompt are sampled and returned."""
         tasks = sorted(tasks, key=lambda t: t.task_id)
         ids = [t.task_id for t in tasks]
         lens = [len(t.prompt_ids) for t in tasks]
         if start_pos is not None:
             starts = [start_pos] * len(tasks)
         else:
-            starts = [min(self.task_cache.task_cached(t.task_id), n - 1) for t, n in zip(tasks, lens)]
-        if any(s >= n for s, n in zip(starts, lens)):
+            starts = [t.prefill_pos if t.prefill_pos is not None else min(self.task_cache.task_cached(t.task_id), n - 1)
+                      for t, n in zip(tasks, lens)]
+        ends = [min(n, (end_positions or {}).get(t.task_id, n)) for t, n in zip(tasks, lens)]
+        if any(s >= e for s, e in zip(starts, ends)):
             return [], []
-        flat_ids = [tok for t, s in zip(tasks, starts) for tok in t.prompt_ids[s:]]
-        flat_pos = [p for s, n in zip(starts, lens) for p in range(s, n)]
+        for t, s in zip(tasks, starts):
+            if t.prefill_start is None:
+                t.prefill_start = s
+        flat_ids = [tok for t, s, e in zip(tasks, starts, ends) for tok in t.prompt_ids[s:e]]
+        flat_pos = [p for s, e in zip(starts, ends) for p in range(s, e)]
         pin = self.device.type == "cuda"
         input_ids = torch.tensor(flat_ids, dtype=torch.long, pin_memory=pin).to(self.device, non_blocking=True)
         position_ids = torch.tensor(flat_pos, dtype=torch.long, pin_memory=pin).to(self.device, non_blocking=True)
-        last, acc = [], 0
-        for s, n in zip(starts, lens):
-            acc += n - s
-            last.append(acc - 1)
+        last, acc, complete = [], 0, []
+        for t, s, e, n in zip(tasks, starts, ends, lens):
+            acc += e - s
+            t.prefill_pos = e
+            if e == n:
+                last.append(acc - 1)
+                complete.append(t)
         with torch.inference_mode(), timed(f"execute_prefill b={len(tasks)} tokens={len(flat_ids)}", logger):
-            kv = self.task_cache.bind(ids, self._workspace, start_positions=starts)
+            kv = self.task_cache.bind(ids, self._workspace, start_positions=starts,
+                                      end_positions=ends if end_positions is not None else None)
             fused = getattr(self.model, "supports_fused_head", False)
             out = self.model(input_ids, position_ids=position_ids, kv_cache=kv, fwd="prefill",
                              **({"return_logits": False} if fused else {}))
+            if not complete:
+                return [], []
             rows = torch.tensor(last, dtype=torch.long, device=self.device)
             logits = self.model.lm_head(out["hidden_states"][rows]) if fused else out["logits"][rows]
-        return tasks, self._sample(logits, tasks, return_logprobs)
+        return complete, self._sample(logits, complete, return_logprobs)
 
     # -- decode -------------------------------------------------------------------------------------------------------------
     def execute_decode(self, tasks: List[Task], return_logprobs: bool = False):

@@ -27,7 +27,7 @@ class InferenceScheduler:
     def __init__(self, model, tokenizer, max_batch_size: int = 16, max_seq_len: Optional[int] = None, device=None,
                  dtype=None, cache: Optional[PagePool] = None, enable_cuda_graph: bool = True, backend=None,
                  page_size: int = 16, kv_cache_tokens: Optional[int] = None, paged: bool = True,
-                 max_prefill_tokens: int = 8192):
+                 max_prefill_tokens: int = 8192, chunked_prefill: bool = False):
         cfg = model.config
         if max_seq_len is None:
             max_seq_len = cfg.max_position_embeddings
@@ -45,6 +45,9 @@ class InferenceScheduler:
         self._executor = Executor(model, self._cache, self._task_cache, self.device, self.dtype, enable_cuda_graph,
                                   max_prefill_tokens=max_prefill_tokens)
         self.max_prefill_tokens = max_prefill_tokens
+        # chunked prefill: at most max_prefill_tokens prompt tokens per step over all requests; a long prompt takes
+        # several steps and the running requests keep decoding in between (the reference never mixes the two)
+        self.chunked_prefill = chunked_prefill
         self._backend_name = "tcgen05" if self.device.type == "cuda" else "torch_native"
         self._stop_event = threading.Event()
         self._loop_thread: Optional[threading.Thread] = None
@@ -80,17 +83,35 @@ class InferenceScheduler:
             batches.append(cur)
         return batches
 
+    def _prefill_chunk(self, tasks: List[Task]) -> Tuple[List[Task], Dict[str, int]]:
+        """Chunked prefill: the requests (in arrival order) and chunk ends that fit this step's token budget."""
+        group, ends, left = [], {}, self.max_prefill_tokens
+        for t in tasks:
+            if left <= 0:
+                break
+            n = len(t.prompt_ids)
+            start = t.prefill_pos if t.prefill_pos is not None else min(self._task_cache.task_cached(t.task_id), n - 1)
+            take = min(n - start, left)
+            group.append(t)
+            ends[t.task_id] = start + take
+            left -= take
+        return group, ends
+
     def _step(self, tasks: List[Task], return_logprobs: bool = False) -> Tuple[List[Task], List[Task]]:
         """Advance every task by one token.  Returns (tasks that produced a token, tasks aborted for lack of room)."""
         produced: List[Task] = []
         fresh = [t for t in tasks if not t.prefill_done and t.prompt_ids]
         done_now = set()
-        for group in self._prefill_batches(fresh):
+        if self.chunked_prefill:
+            group, ends = self._prefill_chunk(fresh)
+            plan = [(group, ends)] if group else []
+        else:
+            plan = [(g, None) for g in self._prefill_batches(fresh)]
+        for group, ends in plan:
             for t in group:
                 t.input_tokens = len(t.prompt_ids)
-            starts = {t.task_id: min(self._task_cache.task_cached(t.task_id), len(t.prompt_ids) - 1) for t in group}
             with self._metrics.record([t.task_id for t in group], "prefill"):
-                ordered, outs = self._executor.execute_prefill(group, return_logprobs=return_logprobs)
+                ordered, outs = self._executor.execute_prefill(group, return_logprobs=return_logprobs, end_positions=ends)
             for t, o in zip(ordered, outs):
                 t.output_ids.append(o[0] if return_logprobs else o)
                 t.output_tokens += 1
@@ -98,7 +119,7 @@ class InferenceScheduler:
                 done_now.add(t.task_id)
                 produced.append(t)
                 # pages fully covered by the prompt become shareable from the first recomputed page on
-                self._task_cache.task_record_hashes(t.task_id, t.prompt_ids, starts[t.task_id] // self._cache.page_size)
+                self._task_cache.task_record_hashes(t.task_id, t.prompt_ids, (t.prefill_start or 0) // self._cache.page_size)
         decode, aborted = [], []
         for t in tasks:
             if t.task_id in done_now or not t.prefill_done:
@@ -214,8 +235,15 @@ class InferenceScheduler:
         try:
             live = [t for t in tasks if t is not None]
             while live:
+                before = sum(t.prefill_pos or 0 for t in live)
                 decoded, _ = self._step(live, return_logprobs=return_logprobs)
-                live = [t for t in decoded if not t.is_finished(stop_ids)]
+                produced = {id(t) for t in decoded}
+                # a request without a token this step stays only while its (chunked) prefill is still advancing
+                waiting = [t for t in live if id(t) not in produced and self.chunked_prefill and not t.prefill_done
+                           and t.status != TaskStatus.ABORTED]
+                if not decoded and sum(t.prefill_pos or 0 for t in waiting) == before:
+                    waiting = []
+                live = [t for t in live if (id(t) in produced and not t.is_finished(stop_ids)) or t in waiting]
         finally:
             for t in tasks:
                 if t is not None:

@@ -55,6 +55,8 @@ class Task:
         self.output_tokens = 0
         self._kv_len = 0
         self._decoder: Optional[StreamDecoder] = None
+        self.prefill_pos: Optional[int] = None     # chunked prefill: prompt tokens whose K/V are in the cache so far
+        self.prefill_start: Optional[int] = None   # first position this task computed itself (after the shared prefix)
 
     def mark_prefill_done(self):
         self._kv_len = self.input_tokens

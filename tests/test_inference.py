@@ -142,6 +142,24 @@ def test_run_batch_matches_full_forward(model, tok, paged, page_size):
     assert s.run_batch([[1] * 64, [1, 2]], max_tokens=3, temperature=0.0)[0] == []  # prompt fills the context: skipped
 
 
+@pytest.mark.parametrize("budget", [3, 7, 64])
+def test_chunked_prefill_gives_the_same_tokens(model, tok, budget):
+    """Prompts cut into chunks of at most `budget` tokens per step (decodes of the others running in between) produce
+    exactly what whole-prompt prefill produces."""
+    from astrai_b200.inference import InferenceScheduler
+
+    prompts = [list(range(5, 30)), [20, 21, 22], list(range(5, 17)) + [40, 41], [7]]
+    plain = InferenceScheduler(model, tok, max_batch_size=4, max_seq_len=64, enable_cuda_graph=False, page_size=4, paged=True)
+    want = plain.run_batch(prompts, max_tokens=6, temperature=0.0, return_logprobs=True)
+    chunked = InferenceScheduler(model, tok, max_batch_size=4, max_seq_len=64, enable_cuda_graph=False, page_size=4, paged=True,
+                                 max_prefill_tokens=budget, chunked_prefill=True)
+    got = chunked.run_batch(prompts, max_tokens=6, temperature=0.0, return_logprobs=True)
+    for (o, lp), (o2, lp2) in zip(want, got):
+        assert o == o2
+        assert lp2 == pytest.approx(lp, abs=1e-4)
+    assert chunked.run_batch(prompts, max_tokens=6, temperature=0.0) == [o for o, _ in want]  # prefix pages reused
+
+
 def test_stop_ids_and_max_tokens(model, tok):
     from astrai_b200.inference import InferenceScheduler
 
