@@ -99,7 +99,7 @@ class Executor:
         self._decode_cache: Optional[DecodeSteadyState] = None
         self._graph_ctx = CudaGraphContext()
         self._graph_supported = (self.device.type == "cuda" and self.dtype == torch.bfloat16
-                                 and head_dim in (32, 64, 128, 256) and cfg.num_attention_heads // cfg.num_key_value_heads in (1, 2, 4, 8))
+                                 and head_dim in (32, 64, 128, 256) and 1 <= cfg.num_attention_heads // cfg.num_key_value_heads <= 8)
         if enable_cuda_graph and self._graph_supported:
             self._graph_ctx.set_enabled(True)
             self._warmup()

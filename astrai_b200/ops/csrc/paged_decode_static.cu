@@ -73,8 +73,7 @@ extern "C" int astrai_b200_paged_decode_noalloc(const void* q, const void* k_buf
   if (head_dim != 32 && head_dim != 64 && head_dim != 128 && head_dim != 256)
     return fail(-3, "head_dim must be 32, 64, 128 or 256", head_dim, 256);
   const int group = n_q_heads % n_kv_heads == 0 ? n_q_heads / n_kv_heads : 0;
-  if (group != 1 && group != 2 && group != 4 && group != 8)
-    return fail(-4, "query heads per kv head must be 1, 2, 4 or 8", group, 8);
+  if (group < 1 || group > 8) return fail(-4, "query heads per kv head must be between 1 and 8", group, 8);
   const long long q_elems = (long long)batch * n_q_heads * head_dim;
   if (q_elems > ASTRAI_B200_NOALLOC_MAX_QELEMS)
     return fail(-5, "batch * n_q_heads * head_dim exceeds the built-in scratch", q_elems, ASTRAI_B200_NOALLOC_MAX_QELEMS);

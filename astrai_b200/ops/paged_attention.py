@@ -74,7 +74,7 @@ def _decode_native_ok(q: Tensor, cache: KVCache) -> bool:
     return (
         q.is_cuda and q.dtype == torch.bfloat16 and cache.k_buffer.dtype == torch.bfloat16
         and q.shape[-1] in (32, 64, 128, 256) and cache.decode_o_part is not None and cache.decode_counters is not None
-        and q.shape[1] % cache.k_buffer.shape[2] == 0 and q.shape[1] // cache.k_buffer.shape[2] in (1, 2, 4, 8)
+        and q.shape[1] % cache.k_buffer.shape[2] == 0 and 1 <= q.shape[1] // cache.k_buffer.shape[2] <= 8
     )
 
 

@@ -245,7 +245,7 @@ def test_sumsq_and_clip():
     assert abs(coef.item() - min(1.0, 1.0 / (ref_norm + 1e-6)) * 0.5) < 1e-6
 
 
-@pytest.mark.parametrize("hd,hq,hkv", [(128, 16, 4), (64, 8, 8), (256, 4, 1), (32, 8, 2)])
+@pytest.mark.parametrize("hd,hq,hkv", [(128, 16, 4), (64, 8, 8), (256, 4, 1), (32, 8, 2), (64, 24, 4), (128, 6, 2), (64, 5, 1)])
 @pytest.mark.parametrize("lens", [[1, 17, 300, 2049], [513]])
 def test_paged_decode_matches_fp32(hd, hq, hkv, lens):
     torch.manual_seed(13)
