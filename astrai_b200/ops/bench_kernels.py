@@ -187,9 +187,9 @@ def bench_decode():
     from astrai_b200.ops import native
 
     native.require()
-    print("paged decode attention (GB/s of K/V bytes), page 16, 16q/4kv D128")
-    for b, ctx in [(1, 4096), (16, 2048), (64, 2048), (64, 8192)]:
-        hq, hkv, d = 16, 4, 128
+    print("paged decode attention (GB/s of K/V bytes), page 16; heads q/kv, head dim")
+    for b, ctx, hq, hkv, d in [(1, 4096, 16, 4, 128), (16, 2048, 16, 4, 128), (64, 2048, 16, 4, 128), (64, 8192, 16, 4, 128),
+                               (16, 1152, 24, 4, 64), (64, 2048, 24, 4, 64)]:
         n_slots = b * ctx + 1024
         kb = torch.randn(n_slots, hkv, d, device="cuda", dtype=torch.bfloat16)
         vb = torch.randn_like(kb)
@@ -204,11 +204,15 @@ def bench_decode():
         splits = int(op.paged_decode_splits(b, hkv, ctx, 32))
         ms = t(lambda: op.paged_decode_(q, kb, vb, table, rows, seq, d ** -0.5, splits, o_part, ml, cnt, out))
         gb = 2 * b * ctx * hkv * d * 2 / 1e6
-        print(f"  B={b:3d} ctx={ctx:5d} splits={splits:2d}: {ms * 1e3:7.1f} us  {gb / ms:6.0f} GB/s")
+        if "--sweep" in sys.argv:
+            sweep = {sp: t(lambda: op.paged_decode_(q, kb, vb, table, rows, seq, d ** -0.5, sp, o_part, ml, cnt, out), n=8)
+                     for sp in (1, 2, 3, 4, 6, 8, 10, 12, 16, 24, 32) if sp * 128 <= ctx * 2}
+            print("    splits sweep (us): " + "  ".join(f"{sp}:{v * 1e3:.1f}" for sp, v in sweep.items()))
+        print(f"  B={b:3d} ctx={ctx:5d} {hq}q/{hkv}kv D{d} splits={splits:2d}: {ms * 1e3:7.1f} us  {gb / ms:6.0f} GB/s")
 
 
 if __name__ == "__main__":
     table = {"gemm": bench_gemm, "skinny": bench_skinny, "flash": bench_flash, "fp8": bench_fp8, "quant": bench_quant, "sample": bench_sample, "mma": bench_mma, "decode": bench_decode}
-    which = sys.argv[1:] or list(table)
+    which = [a for a in sys.argv[1:] if not a.startswith("--")] or list(table)
     for name in which:
         table[name]()

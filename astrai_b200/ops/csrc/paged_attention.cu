@@ -57,7 +57,7 @@ __device__ __forceinline__ void load8(const __nv_bfloat16* p, float (&f)[8]) {
 }
 
 // D = head dim (32/64/128/256).  LPT lanes cooperate on one token (8 dims each); a warp handles 32/LPT tokens at once.
-template <int D, int GT>  // GT: compile-time bound (1, 2, 4, 8) of the query heads per kv head: per-head state lives in registers
+template <int D, int GT>  // GT: query heads per kv head, 1..8 (compile-time, so the per-head state lives in registers)
 __global__ void __launch_bounds__(DEC_WARPS * 32)
 paged_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ k_buf,
                     const __nv_bfloat16* __restrict__ v_buf, const int* __restrict__ req_to_token,
@@ -68,7 +68,7 @@ paged_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __
   constexpr int LPT = D / 8;
   constexpr int TPW = 32 / LPT;  // tokens per warp iteration
   const int kvh = blockIdx.x, b = blockIdx.y, split = blockIdx.z, splits = gridDim.z;
-  const int G = n_q_heads / n_kv_heads;  // <= GT; the unrolled per-head code is predicated on g < G
+  constexpr int G = GT;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int sub = lane / LPT, dl = lane % LPT;  // token sub-group inside the warp, dim chunk of this lane
   const long long len = seq_lens[b];
@@ -168,10 +168,13 @@ paged_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __
   __shared__ float s_ml[DEC_WARPS][GT][2];
   __shared__ int s_last;
   if (sub == 0) {
-    for (int g = 0; g < G; ++g) {
 #pragma unroll
-      for (int j = 0; j < 8; ++j) s_acc[warp][g][dl * 8 + j] = acc[g][j];
-      if (dl == 0) s_ml[warp][g][0] = m[g], s_ml[warp][g][1] = l[g];
+    for (int g = 0; g < GT; ++g) {  // compile-time trip count: the per-head arrays must stay in registers
+      if (g < G) {
+#pragma unroll
+        for (int j = 0; j < 8; ++j) s_acc[warp][g][dl * 8 + j] = acc[g][j];
+        if (dl == 0) s_ml[warp][g][0] = m[g], s_ml[warp][g][1] = l[g];
+      }
     }
   }
   __syncthreads();
@@ -239,7 +242,7 @@ int paged_decode(const void* q, const void* k_buf, const void* v_buf, const int*
   if (splits < 1 || splits > max_splits) return -2;
   const dim3 grid(n_kv_heads, batch, splits), block(DEC_WARPS * 32);
   const int G = n_q_heads / n_kv_heads;
-  const int gt = G <= 1 ? 1 : (G <= 2 ? 2 : (G <= 4 ? 4 : 8));
+  const int gt = G;  // one instantiation per group size: the per-head loops unroll without predicates
 #define AB_DEC(DD, GG)                                                                                               \
   paged_decode_kernel<DD, GG><<<grid, block, 0, st>>>((const __nv_bfloat16*)q, (const __nv_bfloat16*)k_buf,          \
                                                       (const __nv_bfloat16*)v_buf, req_to_token, req_pool_indices,   \
@@ -249,7 +252,11 @@ int paged_decode(const void* q, const void* k_buf, const void* v_buf, const int*
   switch (gt) {                      \
     case 1: AB_DEC(DD, 1); break;    \
     case 2: AB_DEC(DD, 2); break;    \
+    case 3: AB_DEC(DD, 3); break;    \
     case 4: AB_DEC(DD, 4); break;    \
+    case 5: AB_DEC(DD, 5); break;    \
+    case 6: AB_DEC(DD, 6); break;    \
+    case 7: AB_DEC(DD, 7); break;    \
     default: AB_DEC(DD, 8); break;   \
   }
   switch (head_dim) {
