@@ -83,10 +83,44 @@ def build_sampling_info(tasks: List[Task], device) -> SamplingBatchInfo:
                              col(fs, torch.float32), hints["has_freq"], hints)
 
 
+def fuse_projection_weights(model) -> int:
+    """Lay the q / k / v weights of every GQA layer and the gate / up weights of every dense MLP out as ONE matrix each
+    (the separate parameters become views of it), so that a decode step launches one projection GEMM where it launched
+    three (or two).  The modules pick the fused matrix up through ``fused_qkv`` / ``fused_gate_up``, exactly as under the
+    flat-buffer training executors; parameter names, shapes and the state dict are unchanged.  Returns the number of
+    fused groups.  Layers with wrapped projections (LoRA) or biases are left alone."""
+    fused = 0
+
+    def plain(*mods) -> bool:
+        return all(type(m).__name__ == "Linear" and getattr(m, "bias", None) is None and m.weight.dim() == 2 for m in mods)
+
+    for mod in model.modules():
+        if hasattr(mod, "fused_qkv") and mod.fused_qkv is None and plain(mod.q_proj, mod.k_proj, mod.v_proj):
+            parts = [mod.q_proj, mod.k_proj, mod.v_proj]
+            attr = "fused_qkv"
+        elif hasattr(mod, "fused_gate_up") and mod.fused_gate_up is None and plain(mod.gate, mod.up):
+            parts = [mod.gate, mod.up]
+            attr = "fused_gate_up"
+        else:
+            continue
+        with torch.no_grad():
+            whole = torch.cat([p.weight.detach() for p in parts], dim=0)
+            row = 0
+            for p in parts:
+                n = p.weight.shape[0]
+                p.weight.data = whole[row:row + n]
+                row += n
+        setattr(mod, attr, whole)
+        fused += 1
+    return fused
+
+
 class Executor:
     def __init__(self, model, kv_cache: PagePool, task_cache: TaskCacheManager, device=None, dtype=None,
                  enable_cuda_graph: bool = True, max_prefill_tokens: Optional[int] = None):
         self.model, self.kv_cache, self.task_cache = model, kv_cache, task_cache
+        if next(model.parameters()).is_cuda and not model.training:
+            fuse_projection_weights(model)
         p = next(model.parameters())
         self.device = torch.device(device) if device is not None else p.device
         self.dtype = dtype or p.dtype

@@ -330,3 +330,24 @@ def test_http_anthropic_formats(client, tok):
     assert json.loads(data[6])["delta"]["stop_reason"] == "stop_sequence"
     app.state.engine = _FakeEngine(tok, ["plain"])
     assert c.post("/v1/messages", json={"messages": [{"role": "user", "content": "x"}]}).json()["stop_reason"] == "end_turn"
+
+
+def test_fused_projection_weights_keep_names_values_and_outputs(model):
+    from astrai_b200.inference.runtime.executor import fuse_projection_weights
+    import copy
+
+    m = copy.deepcopy(model).eval()
+    before = {k: v.clone() for k, v in m.state_dict().items()}
+    ids = torch.tensor([[5, 6, 7, 8, 9]])
+    with torch.no_grad():
+        want = m(ids)["logits"]
+    n = fuse_projection_weights(m)
+    assert n == 2 * len(m.layers)
+    attn = m.layers[0].attention
+    assert attn.fused_qkv.shape[0] == attn.q_proj.weight.shape[0] + 2 * attn.k_proj.weight.shape[0]
+    assert attn.q_proj.weight.data_ptr() == attn.fused_qkv.data_ptr()  # the parameters are views of the fused matrix
+    after = m.state_dict()
+    assert set(after) == set(before) and all(torch.equal(after[k], before[k]) for k in before)
+    with torch.no_grad():
+        assert torch.equal(m(ids)["logits"], want)
+    assert fuse_projection_weights(m) == 0  # idempotent
