@@ -86,7 +86,7 @@ def build_sampling_info(tasks: List[Task], device) -> SamplingBatchInfo:
 def fuse_projection_weights(model) -> int:
     """Lay the q / k / v weights of every GQA layer and the gate / up weights of every dense MLP out as ONE matrix each
     (the separate parameters become views of it), so that a decode step launches one projection GEMM where it launched
-    three (or two).  The modules pick the fused matrix up through ``fused_qkv`` / ``fused_gate_up``, exactly as under the
+    three (or two); stack the routed experts of every MoE layer once for the grouped GEMMs.  The modules pick the fused matrix up through ``fused_qkv`` / ``fused_gate_up``, exactly as under the
     flat-buffer training executors; parameter names, shapes and the state dict are unchanged.  Returns the number of
     fused groups.  Layers with wrapped projections (LoRA) or biases are left alone."""
     fused = 0
@@ -94,6 +94,21 @@ def fuse_projection_weights(model) -> int:
     def plain(*mods) -> bool:
         return all(type(m).__name__ == "Linear" and getattr(m, "bias", None) is None and m.weight.dim() == 2 for m in mods)
 
+    for mod in model.modules():
+        experts = getattr(mod, "routed_experts", None)
+        if experts is not None and getattr(mod, "stacked_experts", 0) is None and len(experts) > 0 and all(
+                plain(m.gate, m.up, m.down) for m in experts):
+            # mixture of experts: one [E, 2F, D] and one [E, D, F] tensor for the grouped GEMMs instead of a stack per call
+            with torch.no_grad():
+                w_gu = torch.stack([torch.cat([m.gate.weight.detach(), m.up.weight.detach()], dim=0) for m in experts])
+                w_dn = torch.stack([m.down.weight.detach() for m in experts])
+                f = experts[0].gate.weight.shape[0]
+                for i, m in enumerate(experts):
+                    m.gate.weight.data, m.up.weight.data, m.down.weight.data = w_gu[i, :f], w_gu[i, f:], w_dn[i]
+                    m.fused_gate_up = w_gu[i]  # the expert's own gate|up matrix is a slice of the stack
+            mod.stacked_experts = (w_gu, w_dn)
+            fused += 1
+            continue
     for mod in model.modules():
         if hasattr(mod, "fused_qkv") and mod.fused_qkv is None and plain(mod.q_proj, mod.k_proj, mod.v_proj):
             parts = [mod.q_proj, mod.k_proj, mod.v_proj]

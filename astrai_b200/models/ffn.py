@@ -76,6 +76,7 @@ class DeepSeekMoE(nn.Module):
         self.shared_experts = nn.ModuleList(MLP(dim, shared_ffn, std) for _ in range(self.n_shared_experts))
         self.routed_experts = nn.ModuleList(MLP(dim, expert_ffn, std) for _ in range(n_routed_experts))
         self.expert_parallel = None  # set by the EP executor: object with dispatch()/combine()
+        self.stacked_experts = None  # set for serving: ([E, 2F, D] gate|up, [E, D, F] down) that the experts' weights view
 
     # ---- routing --------------------------------------------------------------------------------------------
     def _use_kernels(self, x: Tensor) -> bool:
@@ -98,8 +99,11 @@ class DeepSeekMoE(nn.Module):
             aux = e * (load * (psum / x.shape[0])).sum()
             stats = {"probs": probs.detach(), "topk_indices": idx}
         xs, plan = moe.dispatch(x, idx, counts, e)
-        w_gu = torch.stack([torch.cat([m.gate.weight, m.up.weight], dim=0) for m in self.routed_experts])  # [E, 2F, D]
-        w_dn = torch.stack([m.down.weight for m in self.routed_experts])                                   # [E, D, F]
+        if self.stacked_experts is not None and not torch.is_grad_enabled():
+            w_gu, w_dn = self.stacked_experts  # serving: the experts' parameters are views of these two tensors
+        else:
+            w_gu = torch.stack([torch.cat([m.gate.weight, m.up.weight], dim=0) for m in self.routed_experts])  # [E, 2F, D]
+            w_dn = torch.stack([m.down.weight for m in self.routed_experts])                                   # [E, D, F]
         h = ops.swiglu_fused(moe.zero_unused_rows(moe.grouped_linear(xs, w_gu, plan), plan))
         y = moe.zero_unused_rows(moe.grouped_linear(h, w_dn, plan), plan)
         return moe.combine(y, weights, plan), aux, stats

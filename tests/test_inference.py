@@ -351,3 +351,31 @@ def test_fused_projection_weights_keep_names_values_and_outputs(model):
     with torch.no_grad():
         assert torch.equal(m(ids)["logits"], want)
     assert fuse_projection_weights(m) == 0  # idempotent
+
+
+def test_fused_projection_weights_stack_moe_experts():
+    import copy
+    import sys
+
+    sys.path.insert(0, str(__import__("pathlib").Path(__file__).parent))
+    from helpers import tiny_config
+
+    from astrai_b200.inference.runtime.executor import fuse_projection_weights
+    from astrai_b200.models import AutoRegressiveLM
+
+    torch.manual_seed(0)
+    m = AutoRegressiveLM(tiny_config(ffn_type="moe", n_routed_experts=4, n_activated_experts=2, moe_intermediate_size=16,
+                                     n_shared_experts=1)).eval()
+    before = {k: v.clone() for k, v in m.state_dict().items()}
+    ids = torch.tensor([[5, 6, 7, 8, 9, 10]])
+    with torch.no_grad():
+        want = m(ids)["logits"]
+    assert fuse_projection_weights(m) > 0
+    moe_layer = m.layers[0].mlp
+    w_gu, w_dn = moe_layer.stacked_experts
+    assert w_gu.shape[0] == 4 and moe_layer.routed_experts[2].down.weight.data_ptr() == w_dn[2].data_ptr()
+    assert moe_layer.routed_experts[1].gate.weight.data_ptr() == w_gu[1].data_ptr()  # still a view after the MLP pass
+    after = m.state_dict()
+    assert all(torch.equal(after[k], before[k]) for k in before)
+    with torch.no_grad():
+        assert torch.equal(m(ids)["logits"], want)

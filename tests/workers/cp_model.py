@@ -31,7 +31,7 @@ def main():
         b, s = 2, 512 * world
         cfg = AutoRegressiveLMConfig(vocab_size=512, hidden_size=256, num_hidden_layers=2, num_attention_heads=4,
                                      num_key_value_heads=2, intermediate_size=512, max_position_embeddings=s,
-                                     tie_word_embeddings=False)
+                                     tie_word_embeddings=False, rms_norm_eps=1e-6, rope_theta=10000.0)
         torch.manual_seed(21)
         model = AutoRegressiveLM(cfg).to(dev).to(torch.bfloat16)
         g = torch.Generator().manual_seed(3)
