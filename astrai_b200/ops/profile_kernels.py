@@ -122,6 +122,61 @@ def main():
     outr = torch.empty(mt // world, nt, **bf)
     op.tp_gemm_reducescatter_(xs[0].tensor.view(mt, kt), wt, True, st[0].peer_ptrs, outr, fl[0].peer_ptrs, z8(), 0, 1, 64, 1, 0.5, False)
     op.tp_reduce_(st[0].tensor, outr, world)
+    del arena, xs, st, fl
+
+    # ---- quantised GEMMs, sampling, decode with 6 query heads per kv head
+    from astrai_b200.ops import fp8_block, int8, moe
+
+    xb, sa = fp8_block.quantize_act_block(x)
+    wb, sb = fp8_block.quantize_weight_block(w_gu)
+    fp8_block.mm_fp8_block(xb, sa, wb, sb)
+    xi, si = int8.quantize_rows(x)
+    wi, sw = int8.quantize_rows(w_gu)
+    int8.mm_int8(xi, si, wi, sw)
+    logits = torch.randn(64, 100000, **bf)
+    op.sample_rows(logits, torch.full((64,), 0.8, device=dev), torch.full((64,), 50, device=dev, dtype=torch.int32),
+                   torch.full((64,), 0.9, device=dev), None, None, None, False, 1, 1)
+    hq6, hkv6, hd6, nb6, ctx6 = 24, 4, 64, 16, 1152
+    kb6 = torch.randn(nb6 * ctx6, hkv6, hd6, **bf)
+    vb6 = torch.randn_like(kb6)
+    tbl6 = torch.arange(nb6 * ctx6, dtype=torch.int32, device=dev).view(nb6, ctx6)
+    qd6 = torch.randn(nb6, hq6, hd6, **bf)
+    op.paged_decode_(qd6, kb6, vb6, tbl6, torch.arange(nb6, dtype=torch.int32, device=dev),
+                     torch.full((nb6,), ctx6, dtype=torch.long, device=dev), hd6 ** -0.5,
+                     int(op.paged_decode_splits(nb6, hkv6, ctx6, 32)), torch.zeros(nb6, hq6, 32, hd6, device=dev),
+                     torch.zeros(nb6, hq6, 32, 2, device=dev), torch.zeros(nb6 * hkv6, dtype=torch.int32, device=dev),
+                     torch.empty_like(qd6))
+
+    # ---- mixture of experts: router, plan, permute, grouped GEMMs (forward, dgrad, ragged-K wgrad), combine
+    t_moe, e_moe, k_moe, f_moe = 8192, 16, 4, 1408
+    xm = torch.randn(t_moe, d, **bf, requires_grad=True)
+    router = torch.randn(e_moe, d, **bf) * 0.1
+    w1 = (torch.randn(e_moe, 2 * f_moe, d, **bf) * 0.02).requires_grad_(True)
+    w2 = (torch.randn(e_moe, d, f_moe, **bf) * 0.02).requires_grad_(True)
+    _p, idx, wts, counts, _s = moe.route(ops.gemm(xm.detach(), router), k_moe, True)
+    xs_m, plan = moe.dispatch(xm, idx, counts, e_moe)
+    hm = ops.swiglu_fused(moe.zero_unused_rows(moe.grouped_linear(xs_m, w1, plan), plan))
+    ym = moe.zero_unused_rows(moe.grouped_linear(hm, w2, plan), plan)
+    moe.combine(ym, wts, plan).backward(torch.randn(t_moe, d, **bf))
+
+    # ---- context-parallel attention, rank 0 of two emulated ranks (K / V gathered by the copy CTAs of the launch)
+    from astrai_b200.parallel import context_parallel as cpar
+
+    wcp, ccp, bcp, hqc, hkc, dcp = 2, 2048, 1, 16, 4, 128
+    scp, rowc = 2 * wcp * ccp, hkc * dcp
+    arena = LocalArena(cpar.arena_bytes_for(bcp, scp, wcp, hkc, dcp), wcp, dev)
+    cxs = [cpar.CPContext(arena.view(r), r, wcp, timeout_s=0.5) for r in range(wcp)]
+    srcs = [cx.kv_source(bcp, ccp, rowc, 1) for cx in cxs]
+    stages = [cx.stage(bcp, ccp, rowc, 0) for cx in cxs]
+    for r, cx in enumerate(cxs):
+        srcs[r].tensor.normal_()
+        cx.flags.tensor.fill_(1)
+    qc = torch.randn(bcp * 2 * ccp, hqc, dcp, **bf)
+    kf, vf = torch.zeros(bcp * scp, hkc, dcp, **bf), torch.zeros(bcp * scp, hkc, dcp, **bf)
+    oc, lsec = op.cp_flash_fwd(qc, kf, vf, bcp, ccp, wcp, 0, dcp ** -0.5, srcs[0].peer_ptrs, cxs[0].flags.peer_ptrs, 0, 1, 1, 8,
+                               cxs[0].chunk_state, 0.5)
+    op.cp_flash_bwd(qc, kf, vf, oc, torch.randn_like(oc), lsec, bcp, ccp, wcp, 0, dcp ** -0.5, stages[0].peer_ptrs,
+                    cxs[0].flags.peer_ptrs, 0, 1, 2, cxs[0].tile_counter, 0.5)
     torch.cuda.synchronize()
     print("status", native.kernel_status(dev), "launches", native.launch_count())
 
