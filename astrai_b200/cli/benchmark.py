@@ -15,6 +15,7 @@ vocab 100000).
 from __future__ import annotations
 
 import json
+import os
 import math
 import random
 import threading
@@ -83,9 +84,14 @@ def make_requests(n: int, rate: float, vocab: int, seed: int, prompt_mean: float
     return reqs
 
 
-def run_serve(scheduler, requests: List[Dict], temperature: float, top_p: float, top_k: int, time_scale: float = 1.0) -> Dict:
-    """Replay ``requests`` against a started scheduler; returns the aggregate metrics."""
-    from astrai_b200.inference import STOP
+def run_serve(scheduler, requests: List[Dict], temperature: float, top_p: float, top_k: int, time_scale: float = 1.0,
+              stop=None, as_text: bool = False) -> Dict:
+    """Replay ``requests`` against a started scheduler; returns the aggregate metrics.  ``stop`` is the scheduler's
+    end-of-stream sentinel (default: this package's); ``as_text`` submits prompts as space-separated id strings for a
+    scheduler whose ``add_task`` tokenises text."""
+    if stop is None:
+        from astrai_b200.inference import STOP as stop
+    STOP = stop
 
     lock = threading.Lock()
     records = [{"arrival": None, "first": None, "last": None, "tokens": 0} for _ in requests]
@@ -116,7 +122,8 @@ def run_serve(scheduler, requests: List[Dict], temperature: float, top_p: float,
             if delay > 0:
                 time.sleep(delay)
             records[i]["arrival"] = time.perf_counter()
-            scheduler.add_task(req["ids"], max_tokens=req["max_tokens"], temperature=temperature, top_p=top_p, top_k=top_k,
+            prompt = " ".join(map(str, req["ids"])) if as_text else req["ids"]
+            scheduler.add_task(prompt, max_tokens=req["max_tokens"], temperature=temperature, top_p=top_p, top_k=top_k,
                                stream_callback=callback_for(i))
 
     th = threading.Thread(target=feeder, daemon=True)
@@ -131,6 +138,53 @@ def run_serve(scheduler, requests: List[Dict], temperature: float, top_p: float,
             "output_tokens": out_tokens, "output_tok_per_s": out_tokens / wall if wall > 0 else None,
             "ttft_ms_p50": _pct(ttft, 0.5), "ttft_ms_p99": _pct(ttft, 0.99), "tpot_ms_p50": _pct(tpot, 0.5),
             "prompt_tokens": sum(len(r["ids"]) for r in requests)}
+
+
+def _id_tokenizer_dir(vocab: int) -> str:
+    """A tokenizer.json whose tokens are the decimal strings "0" .. str(vocab-1) with matching ids (whitespace split), so
+    that a scheduler which tokenises text sees exactly the requested ids and can stream any sampled id back."""
+    import tempfile
+
+    from tokenizers import Tokenizer, decoders, models, pre_tokenizers
+
+    tk = Tokenizer(models.WordLevel({str(i): i for i in range(vocab)}, unk_token="0"))
+    tk.pre_tokenizer = pre_tokenizers.WhitespaceSplit()
+    tk.decoder = decoders.Fuse()
+    path = tempfile.mkdtemp(prefix="id_tokenizer_")
+    tk.save(os.path.join(path, "tokenizer.json"))
+    with open(os.path.join(path, "tokenizer_config.json"), "w") as fh:
+        json.dump({}, fh)
+    return path
+
+
+def _serve_reference(preset, device, n_requests, rate, max_batch_size, max_seq_len, kv_cache_tokens, temperature, top_p, top_k,
+                     seed, time_scale, backend) -> Dict:
+    """The same load test against the reference's own scheduler, model and paged cache (its public API, stock code path)."""
+    import torch
+    from astrai.config import AutoRegressiveLMConfig  # the reference package
+    from astrai.inference import STOP, InferenceScheduler
+    from astrai.inference.cache.pool import PagePool
+    from astrai.model import AutoRegressiveLM
+    from astrai.tokenize import AutoTokenizer
+
+    cfg = AutoRegressiveLMConfig(rms_norm_eps=1e-6, tie_word_embeddings=True, rope_theta=10000.0, **PRESETS[preset])
+    torch.manual_seed(0)
+    model = AutoRegressiveLM(cfg).to(device=device, dtype=torch.bfloat16).eval()
+    tok = AutoTokenizer.from_pretrained(_id_tokenizer_dir(cfg.vocab_size))
+    pool = PagePool(cfg.num_hidden_layers, cfg.num_key_value_heads, cfg.hidden_size // cfg.num_attention_heads, max_batch_size,
+                    max_seq_len, torch.device(device), torch.bfloat16, page_size=16,
+                    n_tokens=kv_cache_tokens or max_batch_size * 4608)
+    sched = InferenceScheduler(model, tok, max_batch_size=max_batch_size, max_seq_len=max_seq_len, cache=pool, backend=backend)
+    reqs = make_requests(n_requests, rate, cfg.vocab_size, seed)
+    sched.start()
+    try:
+        res = run_serve(sched, reqs, temperature, top_p, top_k, time_scale, stop=STOP, as_text=True)
+    finally:
+        sched.stop()
+    res.update({"benchmark": "serve", "impl": "reference", "backend": backend, "preset": preset, "rate": rate,
+                "max_batch_size": max_batch_size, "page_size": 16,
+                "sampling": {"temperature": temperature, "top_p": top_p, "top_k": top_k, "seed": seed}})
+    return res
 
 
 @click.group()
@@ -211,11 +265,19 @@ def decode(preset, device, batch_size, prompt_len, gen_len, cuda_graph):
 @click.option("--time_scale", type=float, default=1.0, help="Stretch (>1) or compress (<1) the arrival times.")
 @click.option("--chunked_prefill/--no-chunked_prefill", default=False)
 @click.option("--max_prefill_tokens", type=int, default=8192)
+@click.option("--impl", type=click.Choice(["ours", "reference"]), default="ours",
+              help="'reference' drives the unmodified reference package (importable as `astrai`, e.g. PYTHONPATH=baseline/_ref) "
+                   "with the same request stream.")
+@click.option("--ref_backend", type=str, default="flash", help="Attention backend of the reference arm.")
 def serve(preset, device, n_requests, rate, max_batch_size, max_seq_len, kv_cache_tokens, temperature, top_p, top_k, seed,
-          time_scale, chunked_prefill, max_prefill_tokens):
+          time_scale, chunked_prefill, max_prefill_tokens, impl, ref_backend):
     """Continuous-batching load test with a paged KV cache (16-token pages) and the radix prefix cache."""
     import torch
 
+    if impl == "reference":
+        click.echo(json.dumps(_serve_reference(preset, device, n_requests, rate, max_batch_size, max_seq_len, kv_cache_tokens,
+                                               temperature, top_p, top_k, seed, time_scale, ref_backend)))
+        return
     from astrai_b200.inference import InferenceScheduler
 
     model = build_model(preset, device, torch.bfloat16 if device != "cpu" else torch.float32)
