@@ -17,6 +17,7 @@ import torch
 import torch.nn as nn
 from torch import Tensor
 
+from astrai_b200.utils import trace
 from astrai_b200.config.model_config import AutoRegressiveLMConfig
 from astrai_b200.models.automodel import AutoModel, ModelFactory
 from astrai_b200.models.decoder import DecoderBlock
@@ -93,8 +94,12 @@ class AutoRegressiveLM(AutoModel):
         mask = expand_mask(input_mask)
         causal = mask is None
         aux, stats = [], []
-        for layer in self.layers:
-            out = layer(x, rotary, mask, kv_cache, causal, fwd)
+        for i, layer in enumerate(self.layers):
+            if trace.enabled():
+                with trace.range(f"layer{i}"):
+                    out = layer(x, rotary, mask, kv_cache, causal, fwd)
+            else:
+                out = layer(x, rotary, mask, kv_cache, causal, fwd)
             x = out["hidden_states"]
             if out.get("router_stats") is not None:
                 aux.append(out["aux_loss"])

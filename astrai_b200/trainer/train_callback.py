@@ -131,6 +131,16 @@ class CheckpointCallback(TrainCallback):
         self._save(context)
 
 
+@CallbackFactory.register("heartbeat")
+class _HeartbeatCallback(TrainCallback):
+    """Rank-failure detection through store heartbeats (see :mod:`astrai_b200.parallel.watchdog`)."""
+
+    def __new__(cls, *args, **kwargs):
+        from astrai_b200.parallel.watchdog import HeartbeatCallback
+
+        return HeartbeatCallback(*args, **kwargs)
+
+
 @CallbackFactory.register("progress_bar")
 class ProgressBarCallback(TrainCallback):
     def __init__(self, num_epoch: int, log_interval: int = 100, file: Optional[IO[str]] = None):

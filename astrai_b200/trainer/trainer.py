@@ -19,6 +19,7 @@ from typing import List, Optional
 import torch
 import torch.distributed as dist
 
+from astrai_b200.utils import trace
 from astrai_b200 import ops
 from astrai_b200.config import TrainConfig
 from astrai_b200.parallel.setup import spawn_parallel_fn
@@ -60,21 +61,25 @@ class Trainer:
         self._fire("on_batch_begin", context)
         if flat:
             # promise the loss gradient so the fused head bakes 1/accum into dX and accumulates dW in place
-            with ops.assume_loss_grad(scale):
+            with trace.range("forward"), ops.assume_loss_grad(scale):
                 out = context.strategy(batch)
             loss = out["loss"]
-            ex.backward(loss, torch.full_like(loss, scale))
+            with trace.range("backward"):
+                ex.backward(loss, torch.full_like(loss, scale))
         else:
-            out = context.strategy(batch)
+            with trace.range("forward"):
+                out = context.strategy(batch)
             loss = out["loss"]
-            ex.backward(loss * scale)
+            with trace.range("backward"):
+                ex.backward(loss * scale)
         context.loss = loss.detach()
         context.metrics = out["metrics"]
         context.consumed_samples += context.config.batch_per_device * context.world_size
         self._fire("on_batch_end", context)
         if ex.sync_gradients:
             self._fire("on_optimizer_step", context)
-            context.optimizer.step()
+            with trace.range("optimizer"):
+                context.optimizer.step()
             context.strategy.on_optimizer_step()
             context.optimizer.zero_grad()
             if context.scheduler:

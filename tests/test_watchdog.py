@@ -1,0 +1,61 @@
+"""Rank-failure detection with store heartbeats: in-process over a HashStore, and across gloo ranks on the CPU."""
+
+import json
+import os
+import subprocess
+import sys
+import time
+
+import pytest
+import torch.distributed as dist
+
+from astrai_b200.parallel.watchdog import Heartbeat, RankFailure
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def test_missing_beats_and_announced_exit_are_detected():
+    store = dist.HashStore()
+    seen = []
+    a = Heartbeat(0, 3, store=store, timeout_s=0.3, interval_s=0.05, on_failure=seen.extend).start()
+    b = Heartbeat(1, 3, store=store, timeout_s=0.3, interval_s=0.05).start()
+    c = Heartbeat(2, 3, store=store, timeout_s=0.3, interval_s=0.05).start()
+    try:
+        for step in range(1, 4):
+            for h in (a, b, c):
+                h.beat(step)
+            time.sleep(0.05)
+        a.check()  # everyone alive
+        c.leave("done")  # an orderly exit is seen at the next scan, long before the timeout
+        time.sleep(0.2)
+        with pytest.raises(RankFailure) as exc:
+            a.check()
+        assert exc.value.ranks == [2] and "announced" in str(exc.value)
+        b.stop()  # rank 1 goes silent: seen after the timeout
+        deadline = time.time() + 3
+        while 1 not in a.scan() and time.time() < deadline:
+            a.beat()
+            time.sleep(0.05)
+        with pytest.raises(RankFailure) as exc:
+            a.check()
+        assert exc.value.ranks == [1, 2] and sorted(seen) == [1, 2]
+    finally:
+        for h in (a, b, c):
+            h.stop()
+
+
+@pytest.mark.parametrize("mode", ["leave", "silent"])
+def test_survivors_stop_between_steps_when_a_rank_goes_away(tmp_path, mode):
+    out = str(tmp_path / "hb.json")
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=3", "--master-addr", "127.0.0.1",
+           "--master-port", "29790" if mode == "leave" else "29791", os.path.join(ROOT, "tests", "workers", "heartbeat_ranks.py"),
+           "--out", out, "--victim", "1", "--mode", mode]
+    proc = subprocess.run(cmd, env=dict(os.environ, MASTER_ADDR="127.0.0.1", OMP_NUM_THREADS="1"), capture_output=True, text=True,
+                          timeout=300, cwd=ROOT)
+    assert proc.returncode == 0, proc.stdout[-2000:] + proc.stderr[-3000:]
+    res = {r: json.load(open(f"{out}.{r}")) for r in range(3)}
+    assert res[1]["left_at"] == 4 and res[1]["steps"] == 3
+    for r in (0, 2):
+        assert res[r]["detected"] == [1], res  # found on the host, before the next collective was issued
+        assert res[r]["steps"] == 3
+        assert res[r]["seconds"] < (1.5 if mode == "leave" else 6.0)
