@@ -86,3 +86,22 @@ def test_sequence_sharded_model_step_matches_whole_sequence(tmp_path):
         assert r["status"] == 0
         assert abs(r["loss_cp"] - r["loss_full"]) < 2e-2, r
         assert r["worst_grad"] < 5e-2, r
+
+
+def test_fused_nvls_fsdp_matches_nccl_fsdp(tmp_path):
+    """The multimem variants (in-switch reduction for the reduce-scatter, in-switch broadcast for the parameter gather);
+    on a box without an NVSwitch multicast mapping the executor falls back to plain peer loads / stores."""
+    _need_gpus(2)
+    script = os.path.join(ROOT, "tests", "workers", "fsdp_compare.py")
+    res = {}
+    for i, comm in enumerate(("nccl", "nvls")):
+        out = str(tmp_path / f"{comm}.json")
+        _torchrun(2, script, ["--comm", comm, "--out", out], 29630 + i)
+        res[comm] = json.load(open(out))
+    a, b = res["nccl"], res["nvls"]
+    assert b["status"] == 0
+    for x, y in zip(a["losses"], b["losses"]):
+        assert abs(x - y) < 2e-2, (a, b)
+    for x, y in zip(a["norms"], b["norms"]):
+        assert abs(x - y) / max(abs(x), 1e-6) < 2e-2, (a, b)
+    assert abs(a["checksum"] - b["checksum"]) / a["checksum"] < 1e-3
