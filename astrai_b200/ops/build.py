@@ -103,5 +103,18 @@ def build(verbose: bool = False, force: bool = False) -> Path:
     return LIB
 
 
+def build_standalone() -> Path:
+    """Link the torch-free attention check (``csrc/standalone/attn_check.cu`` + the two attention kernels' objects)."""
+    OUT.mkdir(exist_ok=True)
+    objs = [_compile_one(SRC / "flash_fwd.cu", False), _compile_one(SRC / "paged_attention.cu", False)]
+    main_src = SRC / "standalone" / "attn_check.cu"
+    exe = OUT / "attn_check"
+    _run([_nvcc(), *NVCC_FLAGS, "-I", str(SRC), str(main_src), *map(str, objs), "-o", str(exe), "-lcudart"])
+    return exe
+
+
 if __name__ == "__main__":
-    print(build(verbose="-v" in sys.argv, force="--force" in sys.argv))
+    if "--standalone" in sys.argv:
+        print(build_standalone())
+    else:
+        print(build(verbose="-v" in sys.argv, force="--force" in sys.argv))
