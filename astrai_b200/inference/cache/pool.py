@@ -119,7 +119,7 @@ class PagePool:
         splits = 0
         if self.device.type == "cuda":
             base = max(b * self.n_kv_heads, 1)
-            splits = max(1, min(-(-148 * 4 // base), -(-max_len // 128), ws.decode_o_part.shape[2]))
+            splits = max(1, min(148 * 2 // base, -(-max_len // 128), ws.decode_o_part.shape[2]))  # one wave of 2 CTAs per SM
         return KVCache(self._storage.k_buffer, self._storage.v_buffer, self._req_pool.req_to_token, rows, lens_t,
                        out_cache_loc, max_len, kv_indptr, ws.qo_indptr[: b + 1], None, None, ws.decode_o_part,
                        ws.decode_ml_part, ws.decode_out, ws.decode_counters, q_lens=[1] * b, kv_lens=list(seq_lens),

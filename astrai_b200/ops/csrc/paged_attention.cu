@@ -92,12 +92,13 @@ paged_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __
   }
 
   const long long row = (long long)n_kv_heads * D;
-  // Each lane group takes UNR tokens per trip: all K and V loads of the trip are issued before any of them is used,
-  // so a warp keeps UNR x 2 x 16 bytes per lane in flight (the kernel is bound by HBM latency x bytes in flight).
-  constexpr int UNR = 4;
-  for (long long t0 = t_begin + (long long)warp * TPW * UNR; t0 < t_end; t0 += (long long)DEC_WARPS * TPW * UNR) {
-    uint4 kraw[UNR], vraw[UNR];
-    bool live[UNR];
+  // Each lane group takes UNR tokens per trip.  The loads of trip i + 1 (table entries, then K and V rows - two dependent
+  // round trips to memory) are issued BEFORE the arithmetic of trip i, into a second register set, so the memory
+  // latency of a trip hides behind the previous trip's math; within a trip the softmax state of a head is rescaled
+  // once for the UNR tokens together, not once per token.
+  constexpr int UNR = GT >= 7 ? 2 : 4;  // two register sets of UNR rows each: fewer rows when many heads share a lane
+  const long long stride = (long long)DEC_WARPS * TPW * UNR;
+  auto load_trip = [&](long long t0, uint4 (&kraw)[UNR], uint4 (&vraw)[UNR], bool (&live)[UNR]) {
 #pragma unroll
     for (int u = 0; u < UNR; ++u) {
       const long long t = t0 + (long long)u * TPW + sub;
@@ -108,35 +109,72 @@ paged_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __
       kraw[u] = *reinterpret_cast<const uint4*>(k_buf + slot * row + (long long)kvh * D + dl * 8);
       vraw[u] = *reinterpret_cast<const uint4*>(v_buf + slot * row + (long long)kvh * D + dl * 8);
     }
+  };
+  auto compute_trip = [&](const uint4 (&kraw)[UNR], const uint4 (&vraw)[UNR], const bool (&live)[UNR]) {
+    float sc[GT][UNR];
 #pragma unroll
     for (int u = 0; u < UNR; ++u) {
-      float kf[8], vf[8];
-      {
-        const __nv_bfloat162* hk = reinterpret_cast<const __nv_bfloat162*>(&kraw[u]);
-        const __nv_bfloat162* hv = reinterpret_cast<const __nv_bfloat162*>(&vraw[u]);
+      float kf[8];
+      const __nv_bfloat162* hk = reinterpret_cast<const __nv_bfloat162*>(&kraw[u]);
 #pragma unroll
-        for (int i = 0; i < 4; ++i) {
-          const float2 a = __bfloat1622float2(hk[i]), c = __bfloat1622float2(hv[i]);
-          kf[2 * i] = a.x, kf[2 * i + 1] = a.y, vf[2 * i] = c.x, vf[2 * i + 1] = c.y;
-        }
+      for (int i = 0; i < 4; ++i) {
+        const float2 a = __bfloat1622float2(hk[i]);
+        kf[2 * i] = a.x, kf[2 * i + 1] = a.y;
       }
 #pragma unroll
       for (int g = 0; g < GT; ++g) {
-        if (g < G) {
-          float s = 0.f;
+        float s = 0.f;
 #pragma unroll
-          for (int j = 0; j < 8; ++j) s += qf[g][j] * kf[j];
+        for (int j = 0; j < 8; ++j) s += qf[g][j] * kf[j];
 #pragma unroll
-          for (int o = LPT / 2; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
-          if (!live[u]) s = -INFINITY;
-          const float nm = fmaxf(m[g], s);
-          const float alpha = (nm == -INFINITY) ? 1.f : __expf(m[g] - nm);
-          const float p = (nm == -INFINITY) ? 0.f : __expf(s - nm);
-          l[g] = l[g] * alpha + p;
+        for (int o = LPT / 2; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+        sc[g][u] = live[u] ? s : -INFINITY;
+      }
+    }
 #pragma unroll
-          for (int j = 0; j < 8; ++j) acc[g][j] = acc[g][j] * alpha + p * vf[j];
-          m[g] = nm;
-        }
+    for (int g = 0; g < GT; ++g) {
+      float mx = sc[g][0];
+#pragma unroll
+      for (int u = 1; u < UNR; ++u) mx = fmaxf(mx, sc[g][u]);
+      const float nm = fmaxf(m[g], mx);
+      const float alpha = (nm == -INFINITY) ? 1.f : __expf(m[g] - nm);
+      l[g] *= alpha;
+#pragma unroll
+      for (int j = 0; j < 8; ++j) acc[g][j] *= alpha;
+#pragma unroll
+      for (int u = 0; u < UNR; ++u) sc[g][u] = (nm == -INFINITY) ? 0.f : __expf(sc[g][u] - nm);  // now the probabilities
+      m[g] = nm;
+    }
+#pragma unroll
+    for (int u = 0; u < UNR; ++u) {
+      float vf[8];
+      const __nv_bfloat162* hv = reinterpret_cast<const __nv_bfloat162*>(&vraw[u]);
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const float2 c = __bfloat1622float2(hv[i]);
+        vf[2 * i] = c.x, vf[2 * i + 1] = c.y;
+      }
+#pragma unroll
+      for (int g = 0; g < GT; ++g) {
+        l[g] += sc[g][u];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) acc[g][j] = fmaf(sc[g][u], vf[j], acc[g][j]);
+      }
+    }
+  };
+  {
+    uint4 k_a[UNR], v_a[UNR], k_b[UNR], v_b[UNR];
+    bool live_a[UNR], live_b[UNR];
+    long long t0 = t_begin + (long long)warp * TPW * UNR;
+    if (t0 < t_end) load_trip(t0, k_a, v_a, live_a);
+    for (; t0 < t_end; t0 += 2 * stride) {
+      const long long t1 = t0 + stride;
+      const bool second = t1 < t_end;
+      if (second) load_trip(t1, k_b, v_b, live_b);
+      compute_trip(k_a, v_a, live_a);
+      if (second) {
+        if (t1 + stride < t_end) load_trip(t1 + stride, k_a, v_a, live_a);
+        compute_trip(k_b, v_b, live_b);
       }
     }
   }
@@ -226,7 +264,7 @@ paged_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __
 
 int paged_decode_splits(int batch, int n_kv_heads, long long max_len, int max_splits) {
   const long long base = (long long)batch * n_kv_heads;
-  long long s = (148 * 4 + base - 1) / base;     // aim for about four CTAs per SM
+  long long s = (148 * 2) / base;                // two CTAs fit on an SM (register use): aim for one full wave
   const long long by_len = (max_len + 127) / 128;  // at least 128 tokens per split
   if (s > by_len) s = by_len;
   if (s > max_splits) s = max_splits;
