@@ -135,7 +135,8 @@ struct DkvCfg {
   static constexpr int KV_BYTES = 128 * D * 2;   // resident K or V tile
   static constexpr int QS_BYTES = SUB * D * 2;   // one 64-row Q or dO stage
   static constexpr int PT_BYTES = 128 * SUB * 2; // P^T or dS^T tile
-  static constexpr int SMEM = 2 * KV_BYTES + 2 * QDO_STAGES * QS_BYTES + 4 * PT_BYTES + 1024 + 256;
+  static constexpr int ROW_BYTES = 2 * SUB * 4;   // lse (log2 units) and delta of one sub-tile's queries
+  static constexpr int SMEM = 2 * KV_BYTES + 2 * QDO_STAGES * QS_BYTES + 4 * PT_BYTES + 1024 + 256 + QDO_STAGES * ROW_BYTES;
 };
 
 template <int D>
@@ -185,10 +186,14 @@ flash_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
   auto BAR = [&](int i) { return bar0 + 8u * i; };
   uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(bars + A_NBAR);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_holder + 1);
+  // per Q/dO stage: 64 lse values then 64 delta values of the sub-tile's queries, staged by the producer warp so that
+  // the row threads never wait on global memory inside the loop
+  float* row_stats = reinterpret_cast<float*>(dst_ptr + 2 * C::PT_BYTES + 256);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   if (threadIdx.x == 0) {
-    for (int i = 0; i < A_NBAR; ++i) mbar_init(BAR(i), (i == A_PF || i == A_PF + 1) ? 4 : 1);
+    for (int i = 0; i < A_NBAR; ++i)
+      mbar_init(BAR(i), (i == A_PF || i == A_PF + 1) ? 4 : (i >= A_QF && i < A_QF + QDO_STAGES) ? 2 : 1);
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     fence_async_smem();
@@ -205,27 +210,51 @@ flash_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
   const uint32_t tmem_dv = tmem_base + 256, tmem_dk = tmem_base + 384;
 
   if (warp == 0) {
-    if (lane == 0 && n_it > 0) {
-      mbar_expect_tx(BAR(0), 2 * C::KV_BYTES);
-#pragma unroll
-      for (int kb = 0; kb < C::NB; ++kb) {
-        tma_load_2d(k_smem + kb * BLK128, &map_k, BAR(0), kvh * D + kb * 64, si.k_start + k0);
-        tma_load_2d(v_smem + kb * BLK128, &map_v, BAR(0), kvh * D + kb * 64, si.k_start + k0);
-      }
-      bool ok = true;
-      for (int it = 0; it < n_it && ok; ++it) {
-        const int st = it % QDO_STAGES;
-        const uint32_t ph = ((it / QDO_STAGES) & 1) ^ 1u;
-        if (!mbar_wait(BAR(A_QE + st), ph, abort_flag)) { ok = false; break; }
-        const int h = kvh * G + it / n_sub, qs = sub_start(it % n_sub);
-        mbar_expect_tx(BAR(A_QF + st), 2 * C::QS_BYTES);
+    if (n_it > 0) {
+      if (lane == 0) {
+        mbar_expect_tx(BAR(0), 2 * C::KV_BYTES);
 #pragma unroll
         for (int kb = 0; kb < C::NB; ++kb) {
-          tma_load_2d(q_smem + st * C::QS_BYTES + kb * BLK64, &map_q, BAR(A_QF + st), h * D + kb * 64, si.q_start + qs);
-          tma_load_2d(do_smem + st * C::QS_BYTES + kb * BLK64, &map_do, BAR(A_QF + st), h * D + kb * 64, si.q_start + qs);
+          tma_load_2d(k_smem + kb * BLK128, &map_k, BAR(0), kvh * D + kb * 64, si.k_start + k0);
+          tma_load_2d(v_smem + kb * BLK128, &map_v, BAR(0), kvh * D + kb * 64, si.k_start + k0);
         }
       }
-      if (!ok) {
+      // Lane l carries lse and delta of queries 2l, 2l+1 of a sub-tile; the values of sub-tile it + 1 are requested
+      // before the wait for its stage, so their latency is hidden behind the wait.  Queries past the sequence end get
+      // lse = +inf (probability 0) and delta = 0.
+      auto fetch = [&](int it, float2& lv, float2& dv) {
+        const int h = kvh * G + it / n_sub, q = sub_start(it % n_sub) + 2 * lane;
+        const long long o = (long long)h * total_q + si.q_start + q;
+        lv.x = q < si.q_len ? __ldg(lse2g + o) : INFINITY;
+        lv.y = q + 1 < si.q_len ? __ldg(lse2g + o + 1) : INFINITY;
+        dv.x = q < si.q_len ? __ldg(delta + o) : 0.f;
+        dv.y = q + 1 < si.q_len ? __ldg(delta + o + 1) : 0.f;
+      };
+      float2 lv, dv;
+      fetch(0, lv, dv);
+      bool ok = true;
+      for (int it = 0; it < n_it; ++it) {
+        const int st = it % QDO_STAGES;
+        const uint32_t ph = ((it / QDO_STAGES) & 1) ^ 1u;
+        ok = __all_sync(0xffffffffu, mbar_wait(BAR(A_QE + st), ph, abort_flag));
+        if (!ok) break;
+        if (lane == 0) {
+          const int h = kvh * G + it / n_sub, qs = sub_start(it % n_sub);
+          mbar_expect_tx(BAR(A_QF + st), 2 * C::QS_BYTES);
+#pragma unroll
+          for (int kb = 0; kb < C::NB; ++kb) {
+            tma_load_2d(q_smem + st * C::QS_BYTES + kb * BLK64, &map_q, BAR(A_QF + st), h * D + kb * 64, si.q_start + qs);
+            tma_load_2d(do_smem + st * C::QS_BYTES + kb * BLK64, &map_do, BAR(A_QF + st), h * D + kb * 64, si.q_start + qs);
+          }
+        }
+        float* rs = row_stats + st * (2 * SUB);
+        reinterpret_cast<float2*>(rs)[lane] = lv;
+        reinterpret_cast<float2*>(rs + SUB)[lane] = dv;
+        if (it + 1 < n_it) fetch(it + 1, lv, dv);
+        __syncwarp();
+        if (lane == 0) mbar_arrive(BAR(A_QF + st));  // second arrival of the stage: the statistics are in place
+      }
+      if (!ok && lane == 0) {
         atomicMax(status, ERR_BWD_PRODUCER);
         *abort_flag = 1;
       }
@@ -292,15 +321,18 @@ flash_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
     uint8_t* my_dst = dst_ptr + g * C::PT_BYTES;
     bool ok = true;
     for (int it = g; it < n_it; it += 2) {
-      const int h = kvh * G + it / n_sub, qs = sub_start(it % n_sub);
+      const int qs = sub_start(it % n_sub);
       const int off = qs < split ? off_a : off_b;
       const int qmin = causal ? kidx - off : -0x40000000;  // query q sees this key iff q >= kidx - off
       ok = __all_sync(0xffffffffu, mbar_wait(BAR(A_SF + g), (it >> 1) & 1, abort_flag));
       if (!ok) break;
       tc_fence_after();
-      const float* lp0 = lse2g + (long long)h * total_q + si.q_start + qs;
-      const float* dlp0 = delta + (long long)h * total_q + si.q_start + qs;
-      const bool vec = (qs + SUB <= si.q_len) && (((reinterpret_cast<uintptr_t>(lp0) | reinterpret_cast<uintptr_t>(dlp0)) & 15) == 0);
+      // the stage's statistics were published with the second arrival on its full barrier (phase long complete here)
+      const int st = it % QDO_STAGES;
+      ok = __all_sync(0xffffffffu, mbar_wait(BAR(A_QF + st), (it / QDO_STAGES) & 1, abort_flag));
+      if (!ok) break;
+      const float* lp0 = row_stats + st * (2 * SUB);
+      const float* dlp0 = lp0 + SUB;
       const bool need_mask = (k0 + 128 > si.k_len) || (causal && qs < k0 + 127 - off);
       uint32_t ppk[32], dpk[32];
 #pragma unroll
@@ -315,17 +347,8 @@ flash_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
 #pragma unroll
         for (int i = 0; i < 32; i += 4) {
           float lv[4], dv[4];
-          if (vec) {
-            *reinterpret_cast<float4*>(lv) = __ldg(reinterpret_cast<const float4*>(lp + i));
-            *reinterpret_cast<float4*>(dv) = __ldg(reinterpret_cast<const float4*>(dlp + i));
-          } else {
-#pragma unroll
-            for (int e = 0; e < 4; ++e) {
-              const bool in = qc + i + e < si.q_len;
-              lv[e] = in ? __ldg(lp + i + e) : INFINITY;
-              dv[e] = in ? __ldg(dlp + i + e) : 0.f;
-            }
-          }
+          *reinterpret_cast<float4*>(lv) = *reinterpret_cast<const float4*>(lp + i);
+          *reinterpret_cast<float4*>(dv) = *reinterpret_cast<const float4*>(dlp + i);
           float pv[4], dsv[4];
 #pragma unroll
           for (int e = 0; e < 4; ++e) {
