@@ -48,7 +48,7 @@ struct FwdCfg {
   static constexpr int NB = D / 64;
   static constexpr int TILE_BYTES = 128 * D * 2;
   static constexpr int P_BYTES = 128 * 128 * 2;
-  static constexpr int SMEM = TILE_BYTES * (1 + 2 * KV_STAGES) + P_BYTES + 1024 + 256;
+  static constexpr int SMEM = TILE_BYTES * (2 + 2 * KV_STAGES) + P_BYTES + 1024 + 256;  // two Q buffers
 };
 
 struct SeqInfo {
@@ -143,55 +143,70 @@ __device__ void gather_kv(const CpAttn& cp, int cta, int row_bytes, int* status)
   }
 }
 
+// One unit of work of the persistent forward kernel: a 128-row query tile of one head of one sequence.
+struct FwdItem {
+  SeqInfo si;
+  int h, kvh, q0, off, n_kv;
+};
+// Work items are numbered heaviest first: item w covers (head x sequence) w % nbx and the (w / nbx)-th query tile counted
+// from the end of the sequence (under a causal mask the last tile sees the most keys).  Returns false when the sequence
+// has no such tile.
+__device__ __forceinline__ bool fwd_item(int w, int nbx, const int* cu_q, const int* cu_k, int sq, int sk, int Hq, int Hkv,
+                                         int causal, const CpAttn& cp, FwdItem& im) {
+  const int bx = w % nbx, by = w / nbx;
+  im.h = bx % Hq;
+  im.si = seq_info(cu_q, cu_k, bx / Hq, sq, sk);
+  if (cp.world > 1) im.si.k_len = cp.k_vis;
+  const int qt = (im.si.q_len + BQ - 1) / BQ - 1 - by;
+  if (qt < 0) return false;
+  im.kvh = im.h / (Hq / Hkv);
+  im.q0 = qt * BQ;
+  im.off = (cp.world > 1 && im.q0 < cp.chunk) ? cp.rank * cp.chunk : im.si.k_len - im.si.q_len;
+  int kv_end = im.si.k_len;
+  if (causal) kv_end = min(im.si.k_len, im.q0 + BQ + im.off);
+  if (kv_end < 0) kv_end = 0;
+  im.n_kv = (kv_end + BKV - 1) / BKV;
+  return true;
+}
+
+// Persistent kernel: one CTA per SM walks over its share of the work items (round k: item k * P + c for even k,
+// k * P + P - 1 - c for odd k, which evens out the heaviest-first list across the P CTAs).  Q and the O accumulator are
+// double-buffered (shared memory / TMEM), so the loads and the first score MMAs of the next item overlap the epilogue
+// of the current one; all barrier phases run on counters that continue across items.
 template <int D>
 __global__ void __launch_bounds__(FA_THREADS, 1)
 flash_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                  const __grid_constant__ CUtensorMap map_v, __nv_bfloat16* __restrict__ O, float* __restrict__ lse,
-                 const int* __restrict__ cu_q, const int* __restrict__ cu_k, int sq, int sk, int Hq, int Hkv,
-                 long long o_row_stride, long long total_q, float scale_log2, int causal, int* __restrict__ status,
-                 const CpAttn cp) {
+                 const int* __restrict__ cu_q, const int* __restrict__ cu_k, int sq, int sk, int Hq, int Hkv, int nbx,
+                 int n_items, long long o_row_stride, long long total_q, float scale_log2, int causal,
+                 int* __restrict__ status, const CpAttn cp) {
   using C = FwdCfg<D>;
   const bool gather = cp.world > 1 && cp.kv_src[0] != nullptr;
   const int n_copy = gather ? cp.n_copy_ctas : 0;
   if ((int)blockIdx.x < n_copy) {
-    if (blockIdx.y == 0 && threadIdx.x == 0) gather_kv<C::SMEM>(cp, (int)blockIdx.x, Hkv * D * 2, status);
+    if (threadIdx.x == 0) gather_kv<C::SMEM>(cp, (int)blockIdx.x, Hkv * D * 2, status);
     return;
   }
-  // grid = (query heads x sequences, query tiles): blocks are dispatched in linear order, so the heaviest (last)
-  // causal tile of EVERY head starts before any lighter tile - longest work first across the whole launch.
-  const int bx = (int)blockIdx.x - n_copy;
-  const int h = bx % Hq;
-  SeqInfo si = seq_info(cu_q, cu_k, bx / Hq, sq, sk);
-  if (cp.world > 1) si.k_len = cp.k_vis;
-  const int n_q_tiles = (si.q_len + BQ - 1) / BQ;
-  const int qt = n_q_tiles - 1 - (int)blockIdx.y;
-  if (qt < 0) return;
-  const int kvh = h / (Hq / Hkv);
-  const int q0 = qt * BQ;
-  const int off = (cp.world > 1 && q0 < cp.chunk) ? cp.rank * cp.chunk : si.k_len - si.q_len;
-  int kv_end = si.k_len;
-  if (causal) kv_end = min(si.k_len, q0 + BQ + off);
-  if (kv_end < 0) kv_end = 0;
-  const int n_kv = (kv_end + BKV - 1) / BKV;
+  const int P = (int)gridDim.x - n_copy, cta = (int)blockIdx.x - n_copy;
 
   extern __shared__ uint8_t smem_raw[];
   const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   uint8_t* aligned = smem_raw + (base - smem_u32(smem_raw));
-  const uint32_t q_smem = base;
-  const uint32_t k_smem = base + C::TILE_BYTES;
+  const uint32_t q_smem = base;  // two buffers
+  const uint32_t k_smem = base + 2 * C::TILE_BYTES;
   const uint32_t v_smem = k_smem + KV_STAGES * C::TILE_BYTES;
   const uint32_t p_smem = v_smem + KV_STAGES * C::TILE_BYTES;
   uint8_t* p_ptr = aligned + (p_smem - base);
   uint64_t* bars = reinterpret_cast<uint64_t*>(aligned + (p_smem - base) + C::P_BYTES);
   const uint32_t bar0 = smem_u32(bars);
-  // barriers: 0 q_full | 1,2 k_full | 3,4 k_empty | 5,6 v_full | 7,8 v_empty | 9,10 s_full | 11 p_full | 12 p_empty
   auto BAR = [&](int i) { return bar0 + 8u * i; };
-  uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(bars + 13);
+  enum : int { QF = 0, QE = 2, KF = 4, KE = 6, VF = 8, VE = 10, SF = 12, PF = 14, PE = 15, OE = 16, NBAR = 18 };
+  uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(bars + NBAR);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_holder + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   if (threadIdx.x == 0) {
-    for (int i = 0; i < 13; ++i) mbar_init(BAR(i), i == 11 ? 4 : 1);
+    for (int i = 0; i < NBAR; ++i) mbar_init(BAR(i), (i == PF || i >= OE) ? 4 : 1);
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     fence_async_smem();
@@ -204,45 +219,54 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
-  const uint32_t tmem_base = *tmem_holder;
-  const uint32_t tmem_o = tmem_base + 256;
+  const uint32_t tmem_base = *tmem_holder;  // columns: S0 | S1 | O0 | O1, 128 each
 
   if (warp == 0) {
     // ------------------------------------------------------------------ TMA producer
-    if (lane == 0 && n_kv > 0) {
-      mbar_expect_tx(BAR(0), C::TILE_BYTES);
-#pragma unroll
-      for (int kb = 0; kb < C::NB; ++kb) tma_load_2d(q_smem + kb * BLK_BYTES, &map_q, BAR(0), h * D + kb * 64, si.q_start + q0);
+    if (lane == 0) {
       bool ok = true;
-      KvOrder order(n_kv, cp, BKV);
+      uint32_t tq = 0, kc = 0;
       uint32_t landed = 0;  // source ranks whose chunks are known to be in the gathered buffer
-      for (int it = 0; it < n_kv && ok; ++it) {
-        const int j = order.next();
-        const int st = it & 1;
-        const uint32_t ph = ((it >> 1) & 1) ^ 1u;
-        if (gather) {
-          const int owner = chunk_owner(j * BKV / cp.chunk, cp.world);
-          if (!((landed >> owner) & 1u)) {
-            const unsigned long long t0 = comm::now_ns();
-            while (ld_acquire_gpu(&cp.chunk_flags[owner]) < cp.epoch) {
-              if (*abort_flag || comm::now_ns() - t0 > cp.timeout_ns) { ok = false; break; }
-              __nanosleep(100);
+      for (int k = 0; k * P < n_items && ok; ++k) {
+        const int w = k * P + ((k & 1) ? P - 1 - cta : cta);
+        FwdItem im;
+        if (w >= n_items || !fwd_item(w, nbx, cu_q, cu_k, sq, sk, Hq, Hkv, causal, cp, im) || im.n_kv == 0) continue;
+        const uint32_t qb = tq & 1;
+        if (!mbar_wait(BAR(QE + qb), ((tq >> 1) & 1) ^ 1u, abort_flag)) { ok = false; break; }
+        mbar_expect_tx(BAR(QF + qb), C::TILE_BYTES);
+#pragma unroll
+        for (int kb = 0; kb < C::NB; ++kb)
+          tma_load_2d(q_smem + qb * C::TILE_BYTES + kb * BLK_BYTES, &map_q, BAR(QF + qb), im.h * D + kb * 64, im.si.q_start + im.q0);
+        KvOrder order(im.n_kv, cp, BKV);
+        for (int it = 0; it < im.n_kv && ok; ++it, ++kc) {
+          const int j = order.next();
+          const uint32_t st = kc & 1;
+          const uint32_t ph = ((kc >> 1) & 1) ^ 1u;
+          if (gather) {
+            const int owner = chunk_owner(j * BKV / cp.chunk, cp.world);
+            if (!((landed >> owner) & 1u)) {
+              const unsigned long long t0 = comm::now_ns();
+              while (ld_acquire_gpu(&cp.chunk_flags[owner]) < cp.epoch) {
+                if (*abort_flag || comm::now_ns() - t0 > cp.timeout_ns) { ok = false; break; }
+                __nanosleep(100);
+              }
+              if (!ok) { atomicMax(status, ERR_CP_CHUNK_WAIT); break; }
+              fence_async_global();
+              landed |= 1u << owner;
             }
-            if (!ok) { atomicMax(status, ERR_CP_CHUNK_WAIT); break; }
-            fence_async_global();
-            landed |= 1u << owner;
           }
+          if (!mbar_wait(BAR(KE + st), ph, abort_flag)) { ok = false; break; }
+          mbar_expect_tx(BAR(KF + st), C::TILE_BYTES);
+#pragma unroll
+          for (int kb = 0; kb < C::NB; ++kb)
+            tma_load_2d(k_smem + st * C::TILE_BYTES + kb * BLK_BYTES, &map_k, BAR(KF + st), im.kvh * D + kb * 64, im.si.k_start + j * BKV);
+          if (!mbar_wait(BAR(VE + st), ph, abort_flag)) { ok = false; break; }
+          mbar_expect_tx(BAR(VF + st), C::TILE_BYTES);
+#pragma unroll
+          for (int kb = 0; kb < C::NB; ++kb)
+            tma_load_2d(v_smem + st * C::TILE_BYTES + kb * BLK_BYTES, &map_v, BAR(VF + st), im.kvh * D + kb * 64, im.si.k_start + j * BKV);
         }
-        if (!mbar_wait(BAR(3 + st), ph, abort_flag)) { ok = false; break; }
-        mbar_expect_tx(BAR(1 + st), C::TILE_BYTES);
-#pragma unroll
-        for (int kb = 0; kb < C::NB; ++kb)
-          tma_load_2d(k_smem + st * C::TILE_BYTES + kb * BLK_BYTES, &map_k, BAR(1 + st), kvh * D + kb * 64, si.k_start + j * BKV);
-        if (!mbar_wait(BAR(7 + st), ph, abort_flag)) { ok = false; break; }
-        mbar_expect_tx(BAR(5 + st), C::TILE_BYTES);
-#pragma unroll
-        for (int kb = 0; kb < C::NB; ++kb)
-          tma_load_2d(v_smem + st * C::TILE_BYTES + kb * BLK_BYTES, &map_v, BAR(5 + st), kvh * D + kb * 64, si.k_start + j * BKV);
+        ++tq;
       }
       if (!ok) {
         atomicMax(status, ERR_FA_PRODUCER);
@@ -251,40 +275,63 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
     }
   } else if (warp == 1) {
     // ------------------------------------------------------------------ MMA issuer
-    if (lane == 0 && n_kv > 0) {
+    if (lane == 0) {
       constexpr uint32_t idesc_s = idesc_bf16(128, 128, false, false);
       constexpr uint32_t idesc_pv = idesc_bf16(128, D, false, true);
-      bool ok = mbar_wait(BAR(0), 0, abort_flag);
-      const uint32_t q_lo = desc_lo(q_smem, true, 0), k_lo0 = desc_lo(k_smem, true, 0);
+      const uint32_t q_lo0 = desc_lo(q_smem, true, 0), k_lo0 = desc_lo(k_smem, true, 0);
       const uint32_t p_lo = desc_lo(p_smem, true, 0), v_lo0 = desc_lo(v_smem, false, BLK_BYTES);
-      auto issue_s = [&](int j) -> bool {
-        const int st = j & 1;
-        if (!mbar_wait(BAR(1 + st), (j >> 1) & 1, abort_flag)) return false;
-        tc_fence_after();
-        const uint32_t d = tmem_base + (uint32_t)(j & 1) * 128;
-        const uint32_t k_lo = k_lo0 + st * (C::TILE_BYTES >> 4);
-#pragma unroll
-        for (int kb = 0; kb < C::NB; ++kb)
-#pragma unroll
-          for (int k = 0; k < 4; ++k)
-            tc_mma_lo(d, q_lo + kb * (BLK_BYTES >> 4) + 2 * k, k_lo + kb * (BLK_BYTES >> 4) + 2 * k, idesc_s, (kb | k) ? 1u : 0u);
-        tc_commit(BAR(3 + st));        // K stage free
-        tc_commit(BAR(9 + (j & 1)));   // scores ready
-        return true;
-      };
-      if (ok) ok = issue_s(0);
-      for (int j = 0; j < n_kv && ok; ++j) {
-        if (j + 1 < n_kv && !issue_s(j + 1)) { ok = false; break; }
-        const int st = j & 1;
-        if (!mbar_wait(BAR(11), j & 1, abort_flag) || !mbar_wait(BAR(5 + st), (j >> 1) & 1, abort_flag)) { ok = false; break; }
+      bool ok = true;
+      uint32_t tq = 0, kc = 0;
+      bool have_prev = false, prev_first = false;
+      uint32_t prev_kc = 0, prev_tq = 0;
+      // O += P V of tile `prev`: its P must be in shared memory, its V landed, and (first tile of an item) the epilogue
+      // that last used this O buffer must have read it.
+      auto issue_pv = [&]() -> bool {
+        const uint32_t st = prev_kc & 1, ob = prev_tq & 1;
+        if (!mbar_wait(BAR(PF), prev_kc & 1, abort_flag) || !mbar_wait(BAR(VF + st), (prev_kc >> 1) & 1, abort_flag)) return false;
+        if (prev_first && prev_tq >= 2 && !mbar_wait(BAR(OE + ob), ((prev_tq >> 1) - 1) & 1, abort_flag)) return false;
         tc_fence_after();
         const uint32_t v_lo = v_lo0 + st * (C::TILE_BYTES >> 4);
+        const uint32_t d = tmem_base + 256 + ob * 128;
 #pragma unroll
         for (int k = 0; k < 8; ++k)
-          tc_mma_lo(tmem_o, p_lo + (k >> 2) * (BLK_BYTES >> 4) + 2 * (k & 3), v_lo + k * 128, idesc_pv, (j | k) ? 1u : 0u);
-        tc_commit(BAR(7 + st));  // V stage free
-        tc_commit(BAR(12));      // P consumed, O updated
+          tc_mma_lo(d, p_lo + (k >> 2) * (BLK_BYTES >> 4) + 2 * (k & 3), v_lo + k * 128, idesc_pv, (!prev_first || k) ? 1u : 0u);
+        tc_commit(BAR(VE + st));  // V stage free
+        tc_commit(BAR(PE));       // P consumed, O updated
+        return true;
+      };
+      for (int k = 0; k * P < n_items && ok; ++k) {
+        const int w = k * P + ((k & 1) ? P - 1 - cta : cta);
+        FwdItem im;
+        if (w >= n_items || !fwd_item(w, nbx, cu_q, cu_k, sq, sk, Hq, Hkv, causal, cp, im) || im.n_kv == 0) continue;
+        const uint32_t qb = tq & 1;
+        if (!mbar_wait(BAR(QF + qb), (tq >> 1) & 1, abort_flag)) { ok = false; break; }
+        const uint32_t q_lo = q_lo0 + qb * (C::TILE_BYTES >> 4);
+        for (int j = 0; j < im.n_kv; ++j, ++kc) {
+          // scores of tile kc first, then the P V product of the tile before it: the softmax of one tile overlaps the
+          // score MMAs of the next, also across item boundaries
+          const uint32_t st = kc & 1;
+          if (!mbar_wait(BAR(KF + st), (kc >> 1) & 1, abort_flag)) { ok = false; break; }
+          tc_fence_after();
+          const uint32_t d = tmem_base + st * 128;
+          const uint32_t k_lo = k_lo0 + st * (C::TILE_BYTES >> 4);
+#pragma unroll
+          for (int kb = 0; kb < C::NB; ++kb)
+#pragma unroll
+            for (int kk = 0; kk < 4; ++kk)
+              tc_mma_lo(d, q_lo + kb * (BLK_BYTES >> 4) + 2 * kk, k_lo + kb * (BLK_BYTES >> 4) + 2 * kk, idesc_s, (kb | kk) ? 1u : 0u);
+          tc_commit(BAR(KE + st));                         // K stage free
+          if (j == im.n_kv - 1) tc_commit(BAR(QE + qb));   // last use of this Q buffer
+          tc_commit(BAR(SF + st));                         // scores ready
+          if (have_prev && !issue_pv()) { ok = false; break; }
+          have_prev = true;
+          prev_first = j == 0;
+          prev_kc = kc;
+          prev_tq = tq;
+        }
+        ++tq;
       }
+      if (ok && have_prev) ok = issue_pv();
       if (!ok) {
         atomicMax(status, ERR_FA_MMA);
         *abort_flag = 1;
@@ -295,109 +342,119 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
     const int quarter = warp & 3;
     const int row = quarter * 32 + lane;
     const uint32_t t_lane = tmem_base + ((uint32_t)(quarter * 32) << 16);
-    const int q_idx = q0 + row;
-    float m_run = -INFINITY, l_run = 0.f;
     bool ok = true;
-    KvOrder order(n_kv, cp, BKV);
-    for (int it = 0; it < n_kv; ++it) {
-      const int j = order.next();
-      const int buf = it & 1;
-      ok = __all_sync(0xffffffffu, mbar_wait(BAR(9 + buf), (it >> 1) & 1, abort_flag));
-      if (!ok) break;
-      tc_fence_after();
-      uint32_t s[4][32];
-#pragma unroll
-      for (int c = 0; c < 4; ++c) tc_ld32(t_lane + buf * 128 + c * 32, s[c]);
-      tc_wait_ld();
-      const int k0 = j * BKV;
-      const bool need_mask = (k0 + BKV > si.k_len) || (causal && (k0 + BKV - 1 > q0 + off));
-      if (need_mask) {
-        int limit = si.k_len;
-        if (causal) limit = min(limit, q_idx + off + 1);
-#pragma unroll
-        for (int c = 0; c < 4; ++c)
-#pragma unroll
-          for (int i = 0; i < 32; ++i)
-            if (k0 + c * 32 + i >= limit) s[c][i] = __float_as_uint(-INFINITY);
-      }
-      float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};  // one chain per chunk: a single warp needs the ILP
-#pragma unroll
-      for (int i = 0; i < 32; ++i)
-#pragma unroll
-        for (int c = 0; c < 4; ++c) mx4[c] = fmaxf(mx4[c], __uint_as_float(s[c][i]));
-      const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
-      const float m_new = fmaxf(m_run, mx * scale_log2);
-      const bool grow = __any_sync(0xffffffffu, m_new > m_run + 8.f);
-      float alpha = 1.f, m_use = m_run;
-      if (grow) {
-        m_use = m_new;
-        alpha = (m_run == -INFINITY) ? 0.f : ex2(m_run - m_new);
-      }
-      const float m_safe = (m_use == -INFINITY) ? 0.f : m_use;
-      float rs4[4] = {0.f, 0.f, 0.f, 0.f};
-      uint32_t pk[64];
-#pragma unroll
-      for (int i = 0; i < 32; i += 2)
-#pragma unroll
-        for (int c = 0; c < 4; ++c) {
-          const float p0 = ex2(fmaf(__uint_as_float(s[c][i]), scale_log2, -m_safe));
-          const float p1 = ex2(fmaf(__uint_as_float(s[c][i + 1]), scale_log2, -m_safe));
-          rs4[c] += p0 + p1;
-          const __nv_bfloat162 hh = __floats2bfloat162_rn(p0, p1);
-          pk[c * 16 + (i >> 1)] = *reinterpret_cast<const uint32_t*>(&hh);
-        }
-      const float rowsum = (rs4[0] + rs4[1]) + (rs4[2] + rs4[3]);
-      if (it > 0) {  // the previous PV must have read P and updated O before either is touched
-        ok = __all_sync(0xffffffffu, mbar_wait(BAR(12), (it - 1) & 1, abort_flag));
-        if (!ok) break;
-        tc_fence_after();
-        if (grow) {
-#pragma unroll 1
-          for (int c = 0; c < D / 32; ++c) {
-            uint32_t o[32];
-            tc_ld32(t_lane + 256 + c * 32, o);
-            tc_wait_ld();
-#pragma unroll
-            for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
-            tc_st32(t_lane + 256 + c * 32, o);
-          }
-          tc_wait_st();
-        }
-      }
-      l_run = l_run * alpha + rowsum;
-      m_run = m_use;
-      // P row -> shared memory, K-major 128B-swizzled: 16-byte chunk cc of 64-column block kb at (cc ^ (row % 8))
-      uint8_t* prow = p_ptr + (row >> 3) * 1024 + (row & 7) * 128;
-#pragma unroll
-      for (int c = 0; c < 16; ++c) {
-        const int kb = c >> 3, cc = c & 7;
-        *reinterpret_cast<uint4*>(prow + kb * BLK_BYTES + ((cc ^ (row & 7)) << 4)) =
-            make_uint4(pk[4 * c], pk[4 * c + 1], pk[4 * c + 2], pk[4 * c + 3]);
-      }
-      fence_async_smem();
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(BAR(11));
-    }
-    if (ok && n_kv > 0) {
-      ok = __all_sync(0xffffffffu, mbar_wait(BAR(12), (n_kv - 1) & 1, abort_flag));
-      if (ok) tc_fence_after();
-    }
-    if (ok) {
-      const float inv_l = l_run > 0.f ? 1.f / l_run : 0.f;
+    uint32_t tq = 0, kc = 0;
+    for (int k = 0; k * P < n_items && ok; ++k) {
+      const int w = k * P + ((k & 1) ? P - 1 - cta : cta);
+      FwdItem im;
+      if (w >= n_items || !fwd_item(w, nbx, cu_q, cu_k, sq, sk, Hq, Hkv, causal, cp, im)) continue;
+      const SeqInfo& si = im.si;
+      const int q0 = im.q0, off = im.off, n_kv = im.n_kv, h = im.h;
+      const int q_idx = q0 + row;
       const bool live = q_idx < si.q_len;
       const long long tok = (long long)si.q_start + q_idx;
       __nv_bfloat16* orow = O + tok * o_row_stride + (long long)h * D;
+      if (n_kv == 0) {  // no visible key: zero output, lse = -inf
+        if (live) {
+#pragma unroll 1
+          for (int c = 0; c < D / 8; ++c) reinterpret_cast<uint4*>(orow)[c] = make_uint4(0u, 0u, 0u, 0u);
+          if (lse != nullptr) lse[(long long)h * total_q + tok] = -INFINITY;
+        }
+        continue;
+      }
+      const uint32_t t_o = t_lane + 256 + (tq & 1) * 128;
+      float m_run = -INFINITY, l_run = 0.f;
+      KvOrder order(n_kv, cp, BKV);
+      for (int it = 0; it < n_kv; ++it, ++kc) {
+        const int j = order.next();
+        const uint32_t buf = kc & 1;
+        ok = __all_sync(0xffffffffu, mbar_wait(BAR(SF + buf), (kc >> 1) & 1, abort_flag));
+        if (!ok) break;
+        tc_fence_after();
+        uint32_t s[4][32];
+#pragma unroll
+        for (int c = 0; c < 4; ++c) tc_ld32(t_lane + buf * 128 + c * 32, s[c]);
+        tc_wait_ld();
+        const int k0 = j * BKV;
+        const bool need_mask = (k0 + BKV > si.k_len) || (causal && (k0 + BKV - 1 > q0 + off));
+        if (need_mask) {
+          int limit = si.k_len;
+          if (causal) limit = min(limit, q_idx + off + 1);
+#pragma unroll
+          for (int c = 0; c < 4; ++c)
+#pragma unroll
+            for (int i = 0; i < 32; ++i)
+              if (k0 + c * 32 + i >= limit) s[c][i] = __float_as_uint(-INFINITY);
+        }
+        float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};  // one chain per chunk: a single warp needs the ILP
+#pragma unroll
+        for (int i = 0; i < 32; ++i)
+#pragma unroll
+          for (int c = 0; c < 4; ++c) mx4[c] = fmaxf(mx4[c], __uint_as_float(s[c][i]));
+        const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
+        const float m_new = fmaxf(m_run, mx * scale_log2);
+        const bool grow = __any_sync(0xffffffffu, m_new > m_run + 8.f);
+        float alpha = 1.f, m_use = m_run;
+        if (grow) {
+          m_use = m_new;
+          alpha = (m_run == -INFINITY) ? 0.f : ex2(m_run - m_new);
+        }
+        const float m_safe = (m_use == -INFINITY) ? 0.f : m_use;
+        float rs4[4] = {0.f, 0.f, 0.f, 0.f};
+        uint32_t pk[64];
+#pragma unroll
+        for (int i = 0; i < 32; i += 2)
+#pragma unroll
+          for (int c = 0; c < 4; ++c) {
+            const float p0 = ex2(fmaf(__uint_as_float(s[c][i]), scale_log2, -m_safe));
+            const float p1 = ex2(fmaf(__uint_as_float(s[c][i + 1]), scale_log2, -m_safe));
+            rs4[c] += p0 + p1;
+            const __nv_bfloat162 hh = __floats2bfloat162_rn(p0, p1);
+            pk[c * 16 + (i >> 1)] = *reinterpret_cast<const uint32_t*>(&hh);
+          }
+        const float rowsum = (rs4[0] + rs4[1]) + (rs4[2] + rs4[3]);
+        if (kc > 0) {  // the previous P V (of this item or the one before) must have read P before it is overwritten
+          ok = __all_sync(0xffffffffu, mbar_wait(BAR(PE), (kc - 1) & 1, abort_flag));
+          if (!ok) break;
+          tc_fence_after();
+          if (it > 0 && grow) {  // ... and must have updated O before O is rescaled
+#pragma unroll 1
+            for (int c = 0; c < D / 32; ++c) {
+              uint32_t o[32];
+              tc_ld32(t_o + c * 32, o);
+              tc_wait_ld();
+#pragma unroll
+              for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
+              tc_st32(t_o + c * 32, o);
+            }
+            tc_wait_st();
+          }
+        }
+        l_run = l_run * alpha + rowsum;
+        m_run = m_use;
+        // P row -> shared memory, K-major 128B-swizzled: 16-byte chunk cc of 64-column block kb at (cc ^ (row % 8))
+        uint8_t* prow = p_ptr + (row >> 3) * 1024 + (row & 7) * 128;
+#pragma unroll
+        for (int c = 0; c < 16; ++c) {
+          const int kb = c >> 3, cc = c & 7;
+          *reinterpret_cast<uint4*>(prow + kb * BLK_BYTES + ((cc ^ (row & 7)) << 4)) =
+              make_uint4(pk[4 * c], pk[4 * c + 1], pk[4 * c + 2], pk[4 * c + 3]);
+        }
+        fence_async_smem();
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(BAR(PF));
+      }
+      if (!ok) break;
+      ok = __all_sync(0xffffffffu, mbar_wait(BAR(PE), (kc - 1) & 1, abort_flag));  // last P V of the item: O complete
+      if (!ok) break;
+      tc_fence_after();
+      const float inv_l = l_run > 0.f ? 1.f / l_run : 0.f;
 #pragma unroll 1
       for (int c = 0; c < D / 32; ++c) {
         uint32_t o[32];
-        if (n_kv > 0) {
-          tc_ld32(t_lane + 256 + c * 32, o);
-          tc_wait_ld();
-        } else {
-#pragma unroll
-          for (int i = 0; i < 32; ++i) o[i] = 0u;
-        }
+        tc_ld32(t_o + c * 32, o);
+        tc_wait_ld();
         if (live) {
 #pragma unroll
           for (int v4 = 0; v4 < 4; ++v4) {
@@ -413,13 +470,16 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
           }
         }
       }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(BAR(OE + (tq & 1)));  // this O buffer may be overwritten
       if (live && lse != nullptr)
         lse[(long long)h * total_q + tok] = (l_run > 0.f) ? (m_run + log2f(l_run)) * 0.6931471805599453f : -INFINITY;
-    } else {
-      if (lane == 0) {
-        atomicMax(status, ERR_FA_SOFTMAX);
-        *abort_flag = 1;
-      }
+      ++tq;
+    }
+    if (!ok && lane == 0) {
+      atomicMax(status, ERR_FA_SOFTMAX);
+      *abort_flag = 1;
     }
   }
 
@@ -442,8 +502,19 @@ int launch_fwd(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& 
     configured = true;
   }
   const int n_copy = (cp.world > 1 && cp.kv_src[0] != nullptr) ? cp.n_copy_ctas : 0;
-  const dim3 grid(Hq * batch + n_copy, (max_q + BQ - 1) / BQ, 1);
-  kern<<<grid, FA_THREADS, FwdCfg<D>::SMEM, st>>>(mq, mk, mv, (__nv_bfloat16*)O, lse, cu_q, cu_k, sq, sk, Hq, Hkv,
+  static int n_sm = 0;
+  if (n_sm == 0) {
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&n_sm, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n_sm <= 0)
+      n_sm = 148;
+  }
+  // one resident CTA per SM: copy CTAs (context parallel) and persistent attention CTAs together fill the GPU once
+  const int nbx = Hq * batch, n_items = nbx * ((max_q + BQ - 1) / BQ);
+  int n_persist = n_sm - n_copy;
+  if (n_persist < 1) n_persist = 1;
+  if (n_persist > n_items) n_persist = n_items;
+  const dim3 grid(n_persist + n_copy, 1, 1);
+  kern<<<grid, FA_THREADS, FwdCfg<D>::SMEM, st>>>(mq, mk, mv, (__nv_bfloat16*)O, lse, cu_q, cu_k, sq, sk, Hq, Hkv, nbx, n_items,
                                                   o_row_stride, total_q, scale * 1.4426950408889634f, causal ? 1 : 0,
                                                   status, cp);
   return cudaGetLastError() == cudaSuccess ? 0 : -5;
