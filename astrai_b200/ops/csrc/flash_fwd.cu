@@ -39,16 +39,21 @@ using namespace tc;
 using namespace tmah;
 using namespace cpx;
 
-constexpr int BQ = 128, BKV = 128, FA_THREADS = 192, KV_STAGES = 2;
-constexpr int BLK_BYTES = 128 * 128;  // one [128 rows x 64 bf16] swizzled block
+constexpr int BQ = 128, BKV = 64, FA_THREADS = 192, KV_STAGES = 2;
+constexpr int BLK_BYTES = 128 * 128;   // one [128 rows x 64 bf16] swizzled block (Q, P)
+constexpr int KBLK_BYTES = BKV * 128;  // one [64 rows x 64 bf16] swizzled block (K, V)
 enum : int { ERR_FA_PRODUCER = 31, ERR_FA_MMA = 32, ERR_FA_SOFTMAX = 33 };
 
 template <int D>
 struct FwdCfg {
   static constexpr int NB = D / 64;
-  static constexpr int TILE_BYTES = 128 * D * 2;
-  static constexpr int P_BYTES = 128 * 128 * 2;
-  static constexpr int SMEM = TILE_BYTES * (2 + 2 * KV_STAGES) + P_BYTES + 1024 + 256;  // two Q buffers
+  static constexpr int TILE_BYTES = 128 * D * 2;   // Q tile
+  static constexpr int KV_BYTES = BKV * D * 2;     // one K or V stage
+  static constexpr int P_BYTES = 128 * BKV * 2;
+  // Two CTAs share an SM (each holds 256 TMEM columns), so a CTA may use half of the SM's shared memory minus the
+  // per-CTA reservation: 115 712 bytes at head dim 128, which leaves 768 bytes for aligning the tiles to 1024.
+  static constexpr int ALIGN_SLACK = 768;
+  static constexpr int SMEM = TILE_BYTES + 2 * KV_STAGES * KV_BYTES + P_BYTES + 256 + ALIGN_SLACK;
 };
 
 struct SeqInfo {
@@ -169,12 +174,13 @@ __device__ __forceinline__ bool fwd_item(int w, int nbx, const int* cu_q, const 
   return true;
 }
 
-// Persistent kernel: one CTA per SM walks over its share of the work items (round k: item k * P + c for even k,
-// k * P + P - 1 - c for odd k, which evens out the heaviest-first list across the P CTAs).  Q and the O accumulator are
-// double-buffered (shared memory / TMEM), so the loads and the first score MMAs of the next item overlap the epilogue
-// of the current one; all barrier phases run on counters that continue across items.
+// Persistent kernel, two CTAs per SM: each walks over its share of the work items (round k: item k * P + c for even k,
+// k * P + P - 1 - c for odd k, which evens out the heaviest-first list across the P CTAs).  A CTA works on 128 x 64
+// score tiles with half of the SM's shared memory and 256 TMEM columns (S0 | S1 | O); while one CTA's four softmax
+// warps hold the exponential unit, the other CTA's MMAs, loads, barriers and epilogue fill in.  All barrier phases run
+// on counters that continue across items.
 template <int D>
-__global__ void __launch_bounds__(FA_THREADS, 1)
+__global__ void __launch_bounds__(FA_THREADS, 2)
 flash_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                  const __grid_constant__ CUtensorMap map_v, __nv_bfloat16* __restrict__ O, float* __restrict__ lse,
                  const int* __restrict__ cu_q, const int* __restrict__ cu_k, int sq, int sk, int Hq, int Hkv, int nbx,
@@ -192,15 +198,19 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
   extern __shared__ uint8_t smem_raw[];
   const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   uint8_t* aligned = smem_raw + (base - smem_u32(smem_raw));
-  const uint32_t q_smem = base;  // two buffers
-  const uint32_t k_smem = base + 2 * C::TILE_BYTES;
-  const uint32_t v_smem = k_smem + KV_STAGES * C::TILE_BYTES;
-  const uint32_t p_smem = v_smem + KV_STAGES * C::TILE_BYTES;
+  if (base - smem_u32(smem_raw) > (uint32_t)C::ALIGN_SLACK) {  // cannot happen while dynamic shared memory starts 1024-aligned
+    if (threadIdx.x == 0) atomicMax(status, ERR_FA_PRODUCER);
+    return;
+  }
+  const uint32_t q_smem = base;
+  const uint32_t k_smem = base + C::TILE_BYTES;
+  const uint32_t v_smem = k_smem + KV_STAGES * C::KV_BYTES;
+  const uint32_t p_smem = v_smem + KV_STAGES * C::KV_BYTES;
   uint8_t* p_ptr = aligned + (p_smem - base);
   uint64_t* bars = reinterpret_cast<uint64_t*>(aligned + (p_smem - base) + C::P_BYTES);
   const uint32_t bar0 = smem_u32(bars);
   auto BAR = [&](int i) { return bar0 + 8u * i; };
-  enum : int { QF = 0, QE = 2, KF = 4, KE = 6, VF = 8, VE = 10, SF = 12, PF = 14, PE = 15, OE = 16, NBAR = 18 };
+  enum : int { QF = 0, QE = 1, KF = 2, KE = 4, VF = 6, VE = 8, SF = 10, PF = 12, PE = 13, OE = 14, NBAR = 15 };
   uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(bars + NBAR);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_holder + 1);
 
@@ -212,14 +222,14 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
     fence_async_smem();
   }
   if (warp == 1) {
-    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_holder)), "r"(512u)
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_holder)), "r"(256u)
                  : "memory");
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
   }
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
-  const uint32_t tmem_base = *tmem_holder;  // columns: S0 | S1 | O0 | O1, 128 each
+  const uint32_t tmem_base = *tmem_holder;  // columns: S0 (64) | S1 (64) | O (128)
 
   if (warp == 0) {
     // ------------------------------------------------------------------ TMA producer
@@ -231,12 +241,11 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
         const int w = k * P + ((k & 1) ? P - 1 - cta : cta);
         FwdItem im;
         if (w >= n_items || !fwd_item(w, nbx, cu_q, cu_k, sq, sk, Hq, Hkv, causal, cp, im) || im.n_kv == 0) continue;
-        const uint32_t qb = tq & 1;
-        if (!mbar_wait(BAR(QE + qb), ((tq >> 1) & 1) ^ 1u, abort_flag)) { ok = false; break; }
-        mbar_expect_tx(BAR(QF + qb), C::TILE_BYTES);
+        if (!mbar_wait(BAR(QE), (tq & 1) ^ 1u, abort_flag)) { ok = false; break; }
+        mbar_expect_tx(BAR(QF), C::TILE_BYTES);
 #pragma unroll
         for (int kb = 0; kb < C::NB; ++kb)
-          tma_load_2d(q_smem + qb * C::TILE_BYTES + kb * BLK_BYTES, &map_q, BAR(QF + qb), im.h * D + kb * 64, im.si.q_start + im.q0);
+          tma_load_2d(q_smem + kb * BLK_BYTES, &map_q, BAR(QF), im.h * D + kb * 64, im.si.q_start + im.q0);
         KvOrder order(im.n_kv, cp, BKV);
         for (int it = 0; it < im.n_kv && ok; ++it, ++kc) {
           const int j = order.next();
@@ -256,15 +265,15 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
             }
           }
           if (!mbar_wait(BAR(KE + st), ph, abort_flag)) { ok = false; break; }
-          mbar_expect_tx(BAR(KF + st), C::TILE_BYTES);
+          mbar_expect_tx(BAR(KF + st), C::KV_BYTES);
 #pragma unroll
           for (int kb = 0; kb < C::NB; ++kb)
-            tma_load_2d(k_smem + st * C::TILE_BYTES + kb * BLK_BYTES, &map_k, BAR(KF + st), im.kvh * D + kb * 64, im.si.k_start + j * BKV);
+            tma_load_2d(k_smem + st * C::KV_BYTES + kb * KBLK_BYTES, &map_k, BAR(KF + st), im.kvh * D + kb * 64, im.si.k_start + j * BKV);
           if (!mbar_wait(BAR(VE + st), ph, abort_flag)) { ok = false; break; }
-          mbar_expect_tx(BAR(VF + st), C::TILE_BYTES);
+          mbar_expect_tx(BAR(VF + st), C::KV_BYTES);
 #pragma unroll
           for (int kb = 0; kb < C::NB; ++kb)
-            tma_load_2d(v_smem + st * C::TILE_BYTES + kb * BLK_BYTES, &map_v, BAR(VF + st), im.kvh * D + kb * 64, im.si.k_start + j * BKV);
+            tma_load_2d(v_smem + st * C::KV_BYTES + kb * KBLK_BYTES, &map_v, BAR(VF + st), im.kvh * D + kb * 64, im.si.k_start + j * BKV);
         }
         ++tq;
       }
@@ -276,10 +285,10 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
   } else if (warp == 1) {
     // ------------------------------------------------------------------ MMA issuer
     if (lane == 0) {
-      constexpr uint32_t idesc_s = idesc_bf16(128, 128, false, false);
+      constexpr uint32_t idesc_s = idesc_bf16(128, BKV, false, false);
       constexpr uint32_t idesc_pv = idesc_bf16(128, D, false, true);
       const uint32_t q_lo0 = desc_lo(q_smem, true, 0), k_lo0 = desc_lo(k_smem, true, 0);
-      const uint32_t p_lo = desc_lo(p_smem, true, 0), v_lo0 = desc_lo(v_smem, false, BLK_BYTES);
+      const uint32_t p_lo = desc_lo(p_smem, true, 0), v_lo0 = desc_lo(v_smem, false, KBLK_BYTES);
       bool ok = true;
       uint32_t tq = 0, kc = 0;
       bool have_prev = false, prev_first = false;
@@ -287,15 +296,15 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
       // O += P V of tile `prev`: its P must be in shared memory, its V landed, and (first tile of an item) the epilogue
       // that last used this O buffer must have read it.
       auto issue_pv = [&]() -> bool {
-        const uint32_t st = prev_kc & 1, ob = prev_tq & 1;
+        const uint32_t st = prev_kc & 1;
         if (!mbar_wait(BAR(PF), prev_kc & 1, abort_flag) || !mbar_wait(BAR(VF + st), (prev_kc >> 1) & 1, abort_flag)) return false;
-        if (prev_first && prev_tq >= 2 && !mbar_wait(BAR(OE + ob), ((prev_tq >> 1) - 1) & 1, abort_flag)) return false;
+        if (prev_first && prev_tq >= 1 && !mbar_wait(BAR(OE), (prev_tq - 1) & 1, abort_flag)) return false;
         tc_fence_after();
-        const uint32_t v_lo = v_lo0 + st * (C::TILE_BYTES >> 4);
-        const uint32_t d = tmem_base + 256 + ob * 128;
+        const uint32_t v_lo = v_lo0 + st * (C::KV_BYTES >> 4);
+        const uint32_t d = tmem_base + 128;
 #pragma unroll
-        for (int k = 0; k < 8; ++k)
-          tc_mma_lo(d, p_lo + (k >> 2) * (BLK_BYTES >> 4) + 2 * (k & 3), v_lo + k * 128, idesc_pv, (!prev_first || k) ? 1u : 0u);
+        for (int k = 0; k < BKV / 16; ++k)
+          tc_mma_lo(d, p_lo + 2 * k, v_lo + k * 128, idesc_pv, (!prev_first || k) ? 1u : 0u);
         tc_commit(BAR(VE + st));  // V stage free
         tc_commit(BAR(PE));       // P consumed, O updated
         return true;
@@ -304,24 +313,23 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
         const int w = k * P + ((k & 1) ? P - 1 - cta : cta);
         FwdItem im;
         if (w >= n_items || !fwd_item(w, nbx, cu_q, cu_k, sq, sk, Hq, Hkv, causal, cp, im) || im.n_kv == 0) continue;
-        const uint32_t qb = tq & 1;
-        if (!mbar_wait(BAR(QF + qb), (tq >> 1) & 1, abort_flag)) { ok = false; break; }
-        const uint32_t q_lo = q_lo0 + qb * (C::TILE_BYTES >> 4);
+        if (!mbar_wait(BAR(QF), tq & 1, abort_flag)) { ok = false; break; }
+        const uint32_t q_lo = q_lo0;
         for (int j = 0; j < im.n_kv; ++j, ++kc) {
           // scores of tile kc first, then the P V product of the tile before it: the softmax of one tile overlaps the
           // score MMAs of the next, also across item boundaries
           const uint32_t st = kc & 1;
           if (!mbar_wait(BAR(KF + st), (kc >> 1) & 1, abort_flag)) { ok = false; break; }
           tc_fence_after();
-          const uint32_t d = tmem_base + st * 128;
-          const uint32_t k_lo = k_lo0 + st * (C::TILE_BYTES >> 4);
+          const uint32_t d = tmem_base + st * BKV;
+          const uint32_t k_lo = k_lo0 + st * (C::KV_BYTES >> 4);
 #pragma unroll
           for (int kb = 0; kb < C::NB; ++kb)
 #pragma unroll
             for (int kk = 0; kk < 4; ++kk)
-              tc_mma_lo(d, q_lo + kb * (BLK_BYTES >> 4) + 2 * kk, k_lo + kb * (BLK_BYTES >> 4) + 2 * kk, idesc_s, (kb | kk) ? 1u : 0u);
+              tc_mma_lo(d, q_lo + kb * (BLK_BYTES >> 4) + 2 * kk, k_lo + kb * (KBLK_BYTES >> 4) + 2 * kk, idesc_s, (kb | kk) ? 1u : 0u);
           tc_commit(BAR(KE + st));                         // K stage free
-          if (j == im.n_kv - 1) tc_commit(BAR(QE + qb));   // last use of this Q buffer
+          if (j == im.n_kv - 1) tc_commit(BAR(QE));        // last use of this Q tile
           tc_commit(BAR(SF + st));                         // scores ready
           if (have_prev && !issue_pv()) { ok = false; break; }
           have_prev = true;
@@ -362,7 +370,7 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
         }
         continue;
       }
-      const uint32_t t_o = t_lane + 256 + (tq & 1) * 128;
+      const uint32_t t_o = t_lane + 128;
       float m_run = -INFINITY, l_run = 0.f;
       KvOrder order(n_kv, cp, BKV);
       for (int it = 0; it < n_kv; ++it, ++kc) {
@@ -371,9 +379,9 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
         ok = __all_sync(0xffffffffu, mbar_wait(BAR(SF + buf), (kc >> 1) & 1, abort_flag));
         if (!ok) break;
         tc_fence_after();
-        uint32_t s[4][32];
+        uint32_t s[2][32];
 #pragma unroll
-        for (int c = 0; c < 4; ++c) tc_ld32(t_lane + buf * 128 + c * 32, s[c]);
+        for (int c = 0; c < 2; ++c) tc_ld32(t_lane + buf * BKV + c * 32, s[c]);
         tc_wait_ld();
         const int k0 = j * BKV;
         const bool need_mask = (k0 + BKV > si.k_len) || (causal && (k0 + BKV - 1 > q0 + off));
@@ -381,16 +389,19 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
           int limit = si.k_len;
           if (causal) limit = min(limit, q_idx + off + 1);
 #pragma unroll
-          for (int c = 0; c < 4; ++c)
+          for (int c = 0; c < 2; ++c)
 #pragma unroll
             for (int i = 0; i < 32; ++i)
               if (k0 + c * 32 + i >= limit) s[c][i] = __float_as_uint(-INFINITY);
         }
-        float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};  // one chain per chunk: a single warp needs the ILP
+        float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};  // independent chains: a single warp needs the ILP
 #pragma unroll
-        for (int i = 0; i < 32; ++i)
+        for (int i = 0; i < 32; i += 2)
 #pragma unroll
-          for (int c = 0; c < 4; ++c) mx4[c] = fmaxf(mx4[c], __uint_as_float(s[c][i]));
+          for (int c = 0; c < 2; ++c) {
+            mx4[2 * c] = fmaxf(mx4[2 * c], __uint_as_float(s[c][i]));
+            mx4[2 * c + 1] = fmaxf(mx4[2 * c + 1], __uint_as_float(s[c][i + 1]));
+          }
         const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
         const float m_new = fmaxf(m_run, mx * scale_log2);
         const bool grow = __any_sync(0xffffffffu, m_new > m_run + 8.f);
@@ -401,14 +412,15 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
         }
         const float m_safe = (m_use == -INFINITY) ? 0.f : m_use;
         float rs4[4] = {0.f, 0.f, 0.f, 0.f};
-        uint32_t pk[64];
+        uint32_t pk[32];
 #pragma unroll
         for (int i = 0; i < 32; i += 2)
 #pragma unroll
-          for (int c = 0; c < 4; ++c) {
+          for (int c = 0; c < 2; ++c) {
             const float p0 = ex2(fmaf(__uint_as_float(s[c][i]), scale_log2, -m_safe));
             const float p1 = ex2(fmaf(__uint_as_float(s[c][i + 1]), scale_log2, -m_safe));
-            rs4[c] += p0 + p1;
+            rs4[2 * c] += p0;
+            rs4[2 * c + 1] += p1;
             const __nv_bfloat162 hh = __floats2bfloat162_rn(p0, p1);
             pk[c * 16 + (i >> 1)] = *reinterpret_cast<const uint32_t*>(&hh);
           }
@@ -432,14 +444,12 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
         }
         l_run = l_run * alpha + rowsum;
         m_run = m_use;
-        // P row -> shared memory, K-major 128B-swizzled: 16-byte chunk cc of 64-column block kb at (cc ^ (row % 8))
+        // P row -> shared memory, K-major 128B-swizzled: 16-byte chunk cc of the row at (cc ^ (row % 8))
         uint8_t* prow = p_ptr + (row >> 3) * 1024 + (row & 7) * 128;
 #pragma unroll
-        for (int c = 0; c < 16; ++c) {
-          const int kb = c >> 3, cc = c & 7;
-          *reinterpret_cast<uint4*>(prow + kb * BLK_BYTES + ((cc ^ (row & 7)) << 4)) =
-              make_uint4(pk[4 * c], pk[4 * c + 1], pk[4 * c + 2], pk[4 * c + 3]);
-        }
+        for (int cc = 0; cc < 8; ++cc)
+          *reinterpret_cast<uint4*>(prow + ((cc ^ (row & 7)) << 4)) =
+              make_uint4(pk[4 * cc], pk[4 * cc + 1], pk[4 * cc + 2], pk[4 * cc + 3]);
         fence_async_smem();
         tc_fence_before();
         __syncwarp();
@@ -472,7 +482,7 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
       }
       tc_fence_before();
       __syncwarp();
-      if (lane == 0) mbar_arrive(BAR(OE + (tq & 1)));  // this O buffer may be overwritten
+      if (lane == 0) mbar_arrive(BAR(OE));  // O may be overwritten
       if (live && lse != nullptr)
         lse[(long long)h * total_q + tok] = (l_run > 0.f) ? (m_run + log2f(l_run)) * 0.6931471805599453f : -INFINITY;
       ++tq;
@@ -487,7 +497,7 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
   __syncthreads();
   if (warp == 1) {
     tc_fence_after();
-    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(512u) : "memory");
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(256u) : "memory");
   }
 }
 
@@ -508,9 +518,9 @@ int launch_fwd(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& 
     if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&n_sm, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n_sm <= 0)
       n_sm = 148;
   }
-  // one resident CTA per SM: copy CTAs (context parallel) and persistent attention CTAs together fill the GPU once
+  // two resident CTAs per SM: copy CTAs (context parallel) and persistent attention CTAs together fill the GPU once
   const int nbx = Hq * batch, n_items = nbx * ((max_q + BQ - 1) / BQ);
-  int n_persist = n_sm - n_copy;
+  int n_persist = 2 * n_sm - n_copy;
   if (n_persist < 1) n_persist = 1;
   if (n_persist > n_items) n_persist = n_items;
   const dim3 grid(n_persist + n_copy, 1, 1);
@@ -544,8 +554,8 @@ int flash_fwd(const void* q, const void* k, const void* v, void* out, float* lse
   }
   CUtensorMap mq, mk, mv;
   if (!cache().get(&mq, q, (long long)Hq * D, total_q, q_row_stride, 64, 128)) return -1000 - g_last_map_error;
-  if (!cache().get(&mk, k, (long long)Hkv * D, total_k, k_row_stride, 64, 128)) return -2000 - g_last_map_error;
-  if (!cache().get(&mv, v, (long long)Hkv * D, total_k, v_row_stride, 64, 128)) return -3000 - g_last_map_error;
+  if (!cache().get(&mk, k, (long long)Hkv * D, total_k, k_row_stride, 64, BKV)) return -2000 - g_last_map_error;
+  if (!cache().get(&mv, v, (long long)Hkv * D, total_k, v_row_stride, 64, BKV)) return -3000 - g_last_map_error;
   if (D == 128)
     return launch_fwd<128>(mq, mk, mv, out, lse, cu_q, cu_k, batch, sq, sk, max_q, Hq, Hkv, o_row_stride, total_q, scale,
                            causal, status, st, cp);
