@@ -62,16 +62,19 @@ template <int D>
 __global__ void flash_delta_kernel(const __nv_bfloat16* __restrict__ dO, const __nv_bfloat16* __restrict__ O,
                                    const float* __restrict__ lse, float* __restrict__ delta, float* __restrict__ lse2,
                                    long long total_q, int Hq, long long do_stride, long long o_stride) {
-  // one warp per (token, head); D/8 lanes carry 16 bytes each
+  // D/8 lanes carry 16 bytes each of one (token, head) row: a warp covers 32 / (D/8) rows at a time
+  constexpr int LPR = D / 8, RPW = 32 / LPR;  // lanes per row, rows per warp
   const long long w = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
   const int lane = threadIdx.x & 31;
-  if (w >= total_q * Hq) return;
-  const long long t = w / Hq;
-  const int h = (int)(w % Hq);
+  const long long r = w * RPW + lane / LPR;
+  const int sub = lane % LPR;
+  const bool live = r < total_q * Hq;
+  const long long t = live ? r / Hq : 0;
+  const int h = live ? (int)(r % Hq) : 0;
   float acc = 0.f;
-  if (lane < D / 8) {
-    const uint4 a = *reinterpret_cast<const uint4*>(dO + t * do_stride + (long long)h * D + lane * 8);
-    const uint4 b = *reinterpret_cast<const uint4*>(O + t * o_stride + (long long)h * D + lane * 8);
+  if (live) {
+    const uint4 a = *reinterpret_cast<const uint4*>(dO + t * do_stride + (long long)h * D + sub * 8);
+    const uint4 b = *reinterpret_cast<const uint4*>(O + t * o_stride + (long long)h * D + sub * 8);
     const __nv_bfloat162* pa = reinterpret_cast<const __nv_bfloat162*>(&a);
     const __nv_bfloat162* pb = reinterpret_cast<const __nv_bfloat162*>(&b);
 #pragma unroll
@@ -81,8 +84,8 @@ __global__ void flash_delta_kernel(const __nv_bfloat16* __restrict__ dO, const _
     }
   }
 #pragma unroll
-  for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
-  if (lane == 0) {
+  for (int o = LPR / 2; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+  if (live && sub == 0) {
     delta[(long long)h * total_q + t] = acc;
     lse2[(long long)h * total_q + t] = lse[(long long)h * total_q + t] * LOG2E;
   }
@@ -698,7 +701,7 @@ int launch_bwd(const void* q, const void* k, const void* v, const void* out, con
     if (cudaFuncSetAttribute(kern_b, cudaFuncAttributeMaxDynamicSharedMemorySize, DqCfg<D>::SMEM) != cudaSuccess) return -4;
     configured = true;
   }
-  const long long warps = total_q * Hq;
+  const long long warps = (total_q * Hq + (32 / (D / 8)) - 1) / (32 / (D / 8));
   float* lse2 = delta + total_q * Hq;  // second half of the scratch: lse in log2 units
   flash_delta_kernel<D><<<(unsigned)((warps * 32 + 255) / 256), 256, 0, st>>>(
       (const __nv_bfloat16*)dout, (const __nv_bfloat16*)out, lse, delta, lse2, total_q, Hq, do_rs, o_rs);
