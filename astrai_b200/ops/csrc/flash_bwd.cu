@@ -34,15 +34,16 @@ using namespace tmah;
 using namespace cpx;
 
 constexpr int BWD_THREADS = 320, SUB = 64, QDO_STAGES = 3, KV_STAGES_B = 4;  // warp 0 TMA, warp 1 MMA, warps 2..9 rows (two per TMEM quarter)
+constexpr int DQ_GROUPS = 3, V_STAGES_B = 3, DQ_THREADS = 64 + DQ_GROUPS * 128;  // dQ kernel: three row-warp groups, V released earlier than K
 constexpr int BLK128 = 128 * 128;  // [128 rows x 64 cols] swizzled block
 constexpr int BLK64 = 64 * 128;    // [64 rows x 64 cols] swizzled block
 constexpr float LOG2E = 1.4426950408889634f;
 // mbarrier slots.  dK/dV kernel: kv_full | qdo_full[S] | qdo_empty[S] | s_full[2] | pds_full[2] | pds_empty[2] | done
 enum : int { A_QF = 1, A_QE = 1 + QDO_STAGES, A_SF = 1 + 2 * QDO_STAGES, A_PF = 3 + 2 * QDO_STAGES, A_PE = 5 + 2 * QDO_STAGES,
              A_DONE = 7 + 2 * QDO_STAGES, A_NBAR = 8 + 2 * QDO_STAGES };
-// dQ kernel: qdo_full | k_full[S] | k_empty[S] | v_full[S] | v_empty[S] | s_full[2] | ds_full[2] | ds_empty[2] | done
+// dQ kernel: qdo_full | k_full[S] | k_empty[S] | v_full[S] | v_empty[S] | s_full[G] | ds_full[G] | ds_empty[G] | done
 enum : int { B_KF = 1, B_KE = 1 + KV_STAGES_B, B_VF = 1 + 2 * KV_STAGES_B, B_VE = 1 + 3 * KV_STAGES_B, B_SF = 1 + 4 * KV_STAGES_B,
-             B_DF = 3 + 4 * KV_STAGES_B, B_DE = 5 + 4 * KV_STAGES_B, B_DONE = 7 + 4 * KV_STAGES_B, B_NBAR = 8 + 4 * KV_STAGES_B };
+             B_DF = B_SF + DQ_GROUPS, B_DE = B_DF + DQ_GROUPS, B_DONE = B_DE + DQ_GROUPS, B_NBAR = B_DONE + 1 };
 enum : int { ERR_BWD_PRODUCER = 41, ERR_BWD_MMA = 42, ERR_BWD_ROWS = 43 };
 
 struct SeqInfoB {
@@ -474,11 +475,11 @@ struct DqCfg {
   static constexpr int Q_BYTES = 128 * D * 2;   // resident Q or dO tile
   static constexpr int KS_BYTES = SUB * D * 2;  // one 64-key K or V stage
   static constexpr int DS_BYTES = 128 * SUB * 2;
-  static constexpr int SMEM = 2 * Q_BYTES + 2 * KV_STAGES_B * KS_BYTES + 2 * DS_BYTES + 1024 + 256;
+  static constexpr int SMEM = 2 * Q_BYTES + (KV_STAGES_B + V_STAGES_B) * KS_BYTES + DQ_GROUPS * DS_BYTES + 1024 + 256;
 };
 
 template <int D>
-__global__ void __launch_bounds__(BWD_THREADS, 1)
+__global__ void __launch_bounds__(DQ_THREADS, 1)
 flash_bwd_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_do,
                     const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v,
                     const float* __restrict__ lse2g, const float* __restrict__ delta, __nv_bfloat16* __restrict__ dQ,
@@ -507,9 +508,9 @@ flash_bwd_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
   const uint32_t q_smem = base, do_smem = base + C::Q_BYTES;
   const uint32_t k_smem = do_smem + C::Q_BYTES;                 // stages
   const uint32_t v_smem = k_smem + KV_STAGES_B * C::KS_BYTES;    // stages
-  const uint32_t ds_smem = v_smem + KV_STAGES_B * C::KS_BYTES;
+  const uint32_t ds_smem = v_smem + V_STAGES_B * C::KS_BYTES;
   uint8_t* ds_ptr = aligned + (ds_smem - base);
-  uint64_t* bars = reinterpret_cast<uint64_t*>(ds_ptr + 2 * C::DS_BYTES);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(ds_ptr + DQ_GROUPS * C::DS_BYTES);
   const uint32_t bar0 = smem_u32(bars);
   auto BAR = [&](int i) { return bar0 + 8u * i; };
   uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(bars + B_NBAR);
@@ -517,7 +518,7 @@ flash_bwd_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   if (threadIdx.x == 0) {
-    for (int i = 0; i < B_NBAR; ++i) mbar_init(BAR(i), (i == B_DF || i == B_DF + 1) ? 4 : 1);
+    for (int i = 0; i < B_NBAR; ++i) mbar_init(BAR(i), (i >= B_DF && i < B_DF + DQ_GROUPS) ? 4 : 1);
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     fence_async_smem();
@@ -531,7 +532,8 @@ flash_bwd_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_holder;
-  const uint32_t tmem_dq = tmem_base + 256;
+  // columns: S of the three groups (3 x 64) | dP of the three groups (3 x 64) | dQ (128)
+  const uint32_t tmem_dq = tmem_base + 2 * DQ_GROUPS * SUB;
 
   if (warp == 0) {
     if (lane == 0 && n_it > 0) {
@@ -543,18 +545,17 @@ flash_bwd_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
       }
       bool ok = true;
       for (int j = 0; j < n_it && ok; ++j) {
-        const int st = j % KV_STAGES_B;
-        const uint32_t ph = ((j / KV_STAGES_B) & 1) ^ 1u;
-        if (!mbar_wait(BAR(B_KE + st), ph, abort_flag)) { ok = false; break; }
+        const int st = j % KV_STAGES_B, sv = j % V_STAGES_B;
+        if (!mbar_wait(BAR(B_KE + st), ((j / KV_STAGES_B) & 1) ^ 1u, abort_flag)) { ok = false; break; }
         mbar_expect_tx(BAR(B_KF + st), C::KS_BYTES);
 #pragma unroll
         for (int kb = 0; kb < C::NB; ++kb)
           tma_load_2d(k_smem + st * C::KS_BYTES + kb * BLK64, &map_k, BAR(B_KF + st), kvh * D + kb * 64, si.k_start + j * SUB);
-        if (!mbar_wait(BAR(B_VE + st), ph, abort_flag)) { ok = false; break; }
-        mbar_expect_tx(BAR(B_VF + st), C::KS_BYTES);
+        if (!mbar_wait(BAR(B_VE + sv), ((j / V_STAGES_B) & 1) ^ 1u, abort_flag)) { ok = false; break; }
+        mbar_expect_tx(BAR(B_VF + sv), C::KS_BYTES);
 #pragma unroll
         for (int kb = 0; kb < C::NB; ++kb)
-          tma_load_2d(v_smem + st * C::KS_BYTES + kb * BLK64, &map_v, BAR(B_VF + st), kvh * D + kb * 64, si.k_start + j * SUB);
+          tma_load_2d(v_smem + sv * C::KS_BYTES + kb * BLK64, &map_v, BAR(B_VF + sv), kvh * D + kb * 64, si.k_start + j * SUB);
       }
       if (!ok) {
         atomicMax(status, ERR_BWD_PRODUCER);
@@ -570,12 +571,12 @@ flash_bwd_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
       const uint32_t k_lo0 = desc_lo(k_smem, true, 0), v_lo0 = desc_lo(v_smem, true, 0);
       const uint32_t kmn_lo0 = desc_lo(k_smem, false, BLK64), ds_lo0 = desc_lo(ds_smem, true, 0);
       auto issue_scores = [&](int j) -> bool {
-        const int st = j % KV_STAGES_B, buf = j & 1;
-        const uint32_t ph = (j / KV_STAGES_B) & 1;
-        if (!mbar_wait(BAR(B_KF + st), ph, abort_flag) || !mbar_wait(BAR(B_VF + st), ph, abort_flag)) return false;
+        const int st = j % KV_STAGES_B, sv = j % V_STAGES_B, buf = j % DQ_GROUPS;
+        if (!mbar_wait(BAR(B_KF + st), (j / KV_STAGES_B) & 1, abort_flag) || !mbar_wait(BAR(B_VF + sv), (j / V_STAGES_B) & 1, abort_flag))
+          return false;
         tc_fence_after();
-        const uint32_t k_lo = k_lo0 + st * (C::KS_BYTES >> 4), v_lo = v_lo0 + st * (C::KS_BYTES >> 4);
-        const uint32_t d_s = tmem_base + buf * SUB, d_dp = tmem_base + 128 + buf * SUB;
+        const uint32_t k_lo = k_lo0 + st * (C::KS_BYTES >> 4), v_lo = v_lo0 + sv * (C::KS_BYTES >> 4);
+        const uint32_t d_s = tmem_base + buf * SUB, d_dp = tmem_base + (DQ_GROUPS + buf) * SUB;
 #pragma unroll
         for (int kb = 0; kb < C::NB; ++kb)
 #pragma unroll
@@ -583,23 +584,22 @@ flash_bwd_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
             tc_mma_lo(d_s, q_lo + kb * (BLK128 >> 4) + 2 * k, k_lo + kb * (BLK64 >> 4) + 2 * k, idesc_sc, (kb | k) ? 1u : 0u);
             tc_mma_lo(d_dp, do_lo + kb * (BLK128 >> 4) + 2 * k, v_lo + kb * (BLK64 >> 4) + 2 * k, idesc_sc, (kb | k) ? 1u : 0u);
           }
-        tc_commit(BAR(B_VE + st));  // V stage free
+        tc_commit(BAR(B_VE + sv));  // V stage free
         tc_commit(BAR(B_SF + buf));
         return true;
       };
-      if (ok) ok = issue_scores(0);
-      if (ok && n_it > 1) ok = issue_scores(1);
+      for (int j = 0; j < DQ_GROUPS && j < n_it && ok; ++j) ok = issue_scores(j);
       for (int j = 0; j < n_it && ok; ++j) {
         const int st = j % KV_STAGES_B;
-        const int g = j & 1;
-        if (!mbar_wait(BAR(B_DF + g), (j >> 1) & 1, abort_flag)) { ok = false; break; }
+        const int g = j % DQ_GROUPS;
+        if (!mbar_wait(BAR(B_DF + g), (j / DQ_GROUPS) & 1, abort_flag)) { ok = false; break; }
         tc_fence_after();
         const uint32_t ds_lo = ds_lo0 + g * (C::DS_BYTES >> 4), kmn_lo = kmn_lo0 + st * (C::KS_BYTES >> 4);
 #pragma unroll
         for (int k = 0; k < 4; ++k) tc_mma_lo(tmem_dq, ds_lo + 2 * k, kmn_lo + k * 128, idesc_acc, (j | k) ? 1u : 0u);
         tc_commit(BAR(B_KE + st));  // K stage free
         tc_commit(BAR(B_DE + g));  // this group's dS consumed
-        if (j + 2 < n_it && !issue_scores(j + 2)) { ok = false; break; }
+        if (j + DQ_GROUPS < n_it && !issue_scores(j + DQ_GROUPS)) { ok = false; break; }
       }
       if (ok) tc_commit(BAR(B_DONE));
       if (!ok) {
@@ -608,7 +608,7 @@ flash_bwd_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
       }
     }
   } else {
-    const int quarter = warp & 3, g = (warp - 2) >> 2;  // group g takes the key sub-tiles j = g, g+2, ...
+    const int quarter = warp & 3, g = (warp - 2) >> 2;  // group g takes the key sub-tiles j = g, g + 3, ...
     const int row = quarter * 32 + lane;                // query row of this thread
     const uint32_t t_lane = tmem_base + ((uint32_t)(quarter * 32) << 16);
     const int q_idx = q0 + row;
@@ -621,8 +621,8 @@ flash_bwd_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
     if (causal) limit = min(limit, q_idx + off + 1);
     uint8_t* my_ds = ds_ptr + g * C::DS_BYTES;
     bool ok = true;
-    for (int j = g; j < n_it; j += 2) {
-      ok = __all_sync(0xffffffffu, mbar_wait(BAR(B_SF + g), (j >> 1) & 1, abort_flag));
+    for (int j = g; j < n_it; j += DQ_GROUPS) {
+      ok = __all_sync(0xffffffffu, mbar_wait(BAR(B_SF + g), (j / DQ_GROUPS) & 1, abort_flag));
       if (!ok) break;
       tc_fence_after();
       const bool need_mask = (j * SUB + SUB > si.k_len) || (causal && j * SUB + SUB - 1 > q0 + off);
@@ -631,7 +631,7 @@ flash_bwd_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
       for (int half = 0; half < 2; ++half) {
         uint32_t s[32], dp[32];
         tc_ld32(t_lane + g * SUB + half * 32, s);
-        tc_ld32(t_lane + 128 + g * SUB + half * 32, dp);
+        tc_ld32(t_lane + (DQ_GROUPS + g) * SUB + half * 32, dp);
         tc_wait_ld();
         const int kbase = j * SUB + half * 32;
 #pragma unroll
@@ -645,8 +645,8 @@ flash_bwd_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
           dpk[half * 16 + (i >> 1)] = pack2(p0 * (__uint_as_float(dp[i]) - dlt), p1 * (__uint_as_float(dp[i + 1]) - dlt));
         }
       }
-      if (j >= 2) {
-        ok = __all_sync(0xffffffffu, mbar_wait(BAR(B_DE + g), ((j >> 1) - 1) & 1, abort_flag));
+      if (j >= DQ_GROUPS) {
+        ok = __all_sync(0xffffffffu, mbar_wait(BAR(B_DE + g), ((j / DQ_GROUPS) - 1) & 1, abort_flag));
         if (!ok) break;
       }
       store_row64(my_ds, row, dpk);
@@ -659,10 +659,11 @@ flash_bwd_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
       ok = __all_sync(0xffffffffu, mbar_wait(BAR(B_DONE), 0, abort_flag));
       if (ok) tc_fence_after();
     }
-    const int half = g;
     if (ok) {
-      constexpr int CH = D / 64;
-      store_acc_row(t_lane + 256, dQ + tok * dq_row_stride + (long long)h * D, q_live, n_it > 0, half * CH, half * CH + CH, scale);
+      // the 32-column chunks of the accumulator row are shared out over the three groups
+      constexpr int NCH = D / 32;
+      const int c_begin = g == 0 ? 0 : (NCH == 4 ? g + 1 : g), c_end = g == 0 ? (NCH == 4 ? 2 : 1) : min(NCH, c_begin + 1);
+      store_acc_row(t_lane + 2 * DQ_GROUPS * SUB, dQ + tok * dq_row_stride + (long long)h * D, q_live, n_it > 0, c_begin, c_end, scale);
     } else if (lane == 0) {
       atomicMax(status, ERR_BWD_ROWS);
       *abort_flag = 1;
@@ -710,7 +711,7 @@ int launch_bwd(const void* q, const void* k, const void* v, const void* out, con
                                                        (__nv_bfloat16*)dv, cu_q, cu_k, sq, sk, Hq, Hkv, dk_rs, total_q,
                                                        scale, causal ? 1 : 0, status, cp);
   const dim3 grid_b(Hq * batch, (max_q + 127) / 128, 1);
-  kern_b<<<grid_b, BWD_THREADS, DqCfg<D>::SMEM, st>>>(mq128, mdo128, mk64, mv64, lse2, delta, (__nv_bfloat16*)dq, cu_q,
+  kern_b<<<grid_b, DQ_THREADS, DqCfg<D>::SMEM, st>>>(mq128, mdo128, mk64, mv64, lse2, delta, (__nv_bfloat16*)dq, cu_q,
                                                       cu_k, sq, sk, Hq, Hkv, dq_rs, total_q, scale, causal ? 1 : 0, status, cp);
   return cudaGetLastError() == cudaSuccess ? 0 : -5;
 }
