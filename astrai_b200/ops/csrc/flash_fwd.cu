@@ -206,7 +206,6 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
   const uint32_t k_smem = base + C::TILE_BYTES;
   const uint32_t v_smem = k_smem + KV_STAGES * C::KV_BYTES;
   const uint32_t p_smem = v_smem + KV_STAGES * C::KV_BYTES;
-  uint8_t* p_ptr = aligned + (p_smem - base);
   uint64_t* bars = reinterpret_cast<uint64_t*>(aligned + (p_smem - base) + C::P_BYTES);
   const uint32_t bar0 = smem_u32(bars);
   auto BAR = [&](int i) { return bar0 + 8u * i; };
@@ -288,7 +287,7 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
       constexpr uint32_t idesc_s = idesc_bf16(128, BKV, false, false);
       constexpr uint32_t idesc_pv = idesc_bf16(128, D, false, true);
       const uint32_t q_lo0 = desc_lo(q_smem, true, 0), k_lo0 = desc_lo(k_smem, true, 0);
-      const uint32_t p_lo = desc_lo(p_smem, true, 0), v_lo0 = desc_lo(v_smem, false, KBLK_BYTES);
+      const uint32_t v_lo0 = desc_lo(v_smem, false, KBLK_BYTES);
       bool ok = true;
       uint32_t tq = 0, kc = 0;
       bool have_prev = false, prev_first = false;
@@ -304,7 +303,7 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
         const uint32_t d = tmem_base + 128;
 #pragma unroll
         for (int k = 0; k < BKV / 16; ++k)
-          tc_mma_lo(d, p_lo + 2 * k, v_lo + k * 128, idesc_pv, (!prev_first || k) ? 1u : 0u);
+          tc_mma_ts(d, tmem_base + st * BKV + 8 * k, v_lo + k * 128, idesc_pv, (!prev_first || k) ? 1u : 0u);
         tc_commit(BAR(VE + st));  // V stage free
         tc_commit(BAR(PE));       // P consumed, O updated
         return true;
@@ -425,11 +424,11 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
             pk[c * 16 + (i >> 1)] = *reinterpret_cast<const uint32_t*>(&hh);
           }
         const float rowsum = (rs4[0] + rs4[1]) + (rs4[2] + rs4[3]);
-        if (kc > 0) {  // the previous P V (of this item or the one before) must have read P before it is overwritten
+        if (it > 0 && grow) {  // the previous P V must have updated O before O is rescaled
           ok = __all_sync(0xffffffffu, mbar_wait(BAR(PE), (kc - 1) & 1, abort_flag));
           if (!ok) break;
           tc_fence_after();
-          if (it > 0 && grow) {  // ... and must have updated O before O is rescaled
+          {
 #pragma unroll 1
             for (int c = 0; c < D / 32; ++c) {
               uint32_t o[32];
@@ -444,13 +443,11 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
         }
         l_run = l_run * alpha + rowsum;
         m_run = m_use;
-        // P row -> shared memory, K-major 128B-swizzled: 16-byte chunk cc of the row at (cc ^ (row % 8))
-        uint8_t* prow = p_ptr + (row >> 3) * 1024 + (row & 7) * 128;
-#pragma unroll
-        for (int cc = 0; cc < 8; ++cc)
-          *reinterpret_cast<uint4*>(prow + ((cc ^ (row & 7)) << 4)) =
-              make_uint4(pk[4 * cc], pk[4 * cc + 1], pk[4 * cc + 2], pk[4 * cc + 3]);
-        fence_async_smem();
+        // P row -> tensor memory, over the first 32 columns of this tile's score buffer (the scores are in registers by
+        // now): the P V product reads it as its A operand, and the score MMAs of tile kc + 2, issued after that product
+        // by the same thread, overwrite it in order.
+        tc_st32(t_lane + buf * BKV, pk);
+        tc_wait_st();
         tc_fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive(BAR(PF));

@@ -131,7 +131,17 @@ __device__ __forceinline__ void tc_mma_lo(uint32_t d_tmem, uint32_t a_lo, uint32
       "r"(a_lo), "r"(b_lo), "r"(idesc), "r"(accumulate), "r"(DESC_HI), "r"(0u)
       : "memory");
 }
-
+// Same, with the A operand in tensor memory (rows = lanes 0..127, K-major, two 16-bit elements per 32-bit column: one
+// K = 16 step reads 8 columns starting at `a_tmem`).  Used for P / dS tiles that the row threads write with tcgen05.st.
+__device__ __forceinline__ void tc_mma_ts(uint32_t d_tmem, uint32_t a_tmem, uint32_t b_lo, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t.reg .b64 db;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "mov.b64 db, {%2, %5};\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], db, %3, {%6, %6, %6, %6}, p;\n\t}" ::"r"(d_tmem),
+      "r"(a_tmem), "r"(b_lo), "r"(idesc), "r"(accumulate), "r"(DESC_HI), "r"(0u)
+      : "memory");
+}
 
 // ---- cluster helpers (2-CTA kernels)
 __device__ __forceinline__ uint32_t cluster_ctarank() {
