@@ -33,8 +33,8 @@ using namespace tc;
 using namespace tmah;
 using namespace cpx;
 
-constexpr int BWD_THREADS = 320, SUB = 64, QDO_STAGES = 3, KV_STAGES_B = 4;  // warp 0 TMA, warp 1 MMA, warps 2..9 rows (two per TMEM quarter)
-constexpr int DQ_GROUPS = 3, V_STAGES_B = 3, DQ_THREADS = 64 + DQ_GROUPS * 128;  // dQ kernel: three row-warp groups, V released earlier than K
+constexpr int BWD_THREADS = 320, SUB = 64, QDO_STAGES = 4, KV_STAGES_B = 6;  // warp 0 TMA, warp 1 MMA, warps 2..9 rows (two per TMEM quarter)
+constexpr int DQ_GROUPS = 3, V_STAGES_B = 4, DQ_THREADS = 64 + DQ_GROUPS * 128;  // dQ kernel: three row-warp groups, V released earlier than K
 constexpr int BLK128 = 128 * 128;  // [128 rows x 64 cols] swizzled block
 constexpr int BLK64 = 64 * 128;    // [64 rows x 64 cols] swizzled block
 constexpr float LOG2E = 1.4426950408889634f;
@@ -92,14 +92,6 @@ __global__ void flash_delta_kernel(const __nv_bfloat16* __restrict__ dO, const _
   }
 }
 
-// Row r of a [128 x 64] bf16 tile (K-major, 128B swizzle): eight 16-byte chunks.
-__device__ __forceinline__ void store_row64(uint8_t* tile, int r, const uint32_t (&pk)[32]) {
-  uint8_t* prow = tile + (r >> 3) * 1024 + (r & 7) * 128;
-#pragma unroll
-  for (int c = 0; c < 8; ++c)
-    *reinterpret_cast<uint4*>(prow + ((c ^ (r & 7)) << 4)) = make_uint4(pk[4 * c], pk[4 * c + 1], pk[4 * c + 2], pk[4 * c + 3]);
-}
-
 __device__ __forceinline__ uint32_t pack2(float a, float b) {
   const __nv_bfloat162 h = __floats2bfloat162_rn(a, b);
   return *reinterpret_cast<const uint32_t*>(&h);
@@ -138,9 +130,8 @@ struct DkvCfg {
   static constexpr int NB = D / 64;
   static constexpr int KV_BYTES = 128 * D * 2;   // resident K or V tile
   static constexpr int QS_BYTES = SUB * D * 2;   // one 64-row Q or dO stage
-  static constexpr int PT_BYTES = 128 * SUB * 2; // P^T or dS^T tile
   static constexpr int ROW_BYTES = 2 * SUB * 4;   // lse (log2 units) and delta of one sub-tile's queries
-  static constexpr int SMEM = 2 * KV_BYTES + 2 * QDO_STAGES * QS_BYTES + 4 * PT_BYTES + 1024 + 256 + QDO_STAGES * ROW_BYTES;
+  static constexpr int SMEM = 2 * KV_BYTES + 2 * QDO_STAGES * QS_BYTES + 1024 + 256 + QDO_STAGES * ROW_BYTES;
 };
 
 template <int D>
@@ -181,18 +172,15 @@ flash_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
   const uint32_t k_smem = base, v_smem = base + C::KV_BYTES;
   const uint32_t q_smem = v_smem + C::KV_BYTES;                    // QDO_STAGES stages
   const uint32_t do_smem = q_smem + QDO_STAGES * C::QS_BYTES;      // QDO_STAGES stages
-  const uint32_t pt_smem = do_smem + QDO_STAGES * C::QS_BYTES;
-  const uint32_t dst_smem = pt_smem + 2 * C::PT_BYTES;  // P^T and dS^T are double-buffered (one buffer per row-warp group)
-  uint8_t* pt_ptr = aligned + (pt_smem - base);
-  uint8_t* dst_ptr = aligned + (dst_smem - base);
-  uint64_t* bars = reinterpret_cast<uint64_t*>(dst_ptr + 2 * C::PT_BYTES);
+  uint8_t* tail = aligned + (do_smem + QDO_STAGES * C::QS_BYTES - base);  // barriers, TMEM address, statistics ring
+  uint64_t* bars = reinterpret_cast<uint64_t*>(tail);
   const uint32_t bar0 = smem_u32(bars);
   auto BAR = [&](int i) { return bar0 + 8u * i; };
   uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(bars + A_NBAR);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_holder + 1);
   // per Q/dO stage: 64 lse values then 64 delta values of the sub-tile's queries, staged by the producer warp so that
   // the row threads never wait on global memory inside the loop
-  float* row_stats = reinterpret_cast<float*>(dst_ptr + 2 * C::PT_BYTES + 256);
+  float* row_stats = reinterpret_cast<float*>(tail + 256);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   if (threadIdx.x == 0) {
@@ -271,7 +259,6 @@ flash_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
       const uint32_t k_lo = desc_lo(k_smem, true, 0), v_lo = desc_lo(v_smem, true, 0);
       const uint32_t q_lo0 = desc_lo(q_smem, true, 0), do_lo0 = desc_lo(do_smem, true, 0);
       const uint32_t qmn_lo0 = desc_lo(q_smem, false, BLK64), domn_lo0 = desc_lo(do_smem, false, BLK64);
-      const uint32_t pt_lo0 = desc_lo(pt_smem, true, 0), dst_lo0 = desc_lo(dst_smem, true, 0);
       auto issue_scores = [&](int it) -> bool {
         const int st = it % QDO_STAGES, buf = it & 1;
         if (!mbar_wait(BAR(A_QF + st), (it / QDO_STAGES) & 1, abort_flag)) return false;
@@ -295,12 +282,12 @@ flash_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
         const int g = it & 1;
         if (!mbar_wait(BAR(A_PF + g), (it >> 1) & 1, abort_flag)) { ok = false; break; }
         tc_fence_after();
-        const uint32_t pt_lo = pt_lo0 + g * (C::PT_BYTES >> 4), dst_lo = dst_lo0 + g * (C::PT_BYTES >> 4);
+        const uint32_t pt_t = tmem_base + g * SUB, dst_t = tmem_base + 128 + g * SUB;  // P^T / dS^T over the score buffers
         const uint32_t domn_lo = domn_lo0 + st * (C::QS_BYTES >> 4), qmn_lo = qmn_lo0 + st * (C::QS_BYTES >> 4);
 #pragma unroll
         for (int k = 0; k < 4; ++k) {
-          tc_mma_lo(tmem_dv, pt_lo + 2 * k, domn_lo + k * 128, idesc_acc, (it | k) ? 1u : 0u);
-          tc_mma_lo(tmem_dk, dst_lo + 2 * k, qmn_lo + k * 128, idesc_acc, (it | k) ? 1u : 0u);
+          tc_mma_ts(tmem_dv, pt_t + 8 * k, domn_lo + k * 128, idesc_acc, (it | k) ? 1u : 0u);
+          tc_mma_ts(tmem_dk, dst_t + 8 * k, qmn_lo + k * 128, idesc_acc, (it | k) ? 1u : 0u);
         }
         tc_commit(BAR(A_QE + st));  // Q / dO stage free
         tc_commit(BAR(A_PE + g));  // this group's P^T / dS^T consumed
@@ -321,8 +308,6 @@ flash_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
     const int kidx = k0 + row;
     const bool key_live = kidx < si.k_len;
     const float scale_log2 = scale * LOG2E;
-    uint8_t* my_pt = pt_ptr + g * C::PT_BYTES;
-    uint8_t* my_dst = dst_ptr + g * C::PT_BYTES;
     bool ok = true;
     for (int it = g; it < n_it; it += 2) {
       const int qs = sub_start(it % n_sub);
@@ -367,13 +352,12 @@ flash_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
           dpk[half * 16 + (i >> 1) + 1] = pack2(dsv[2], dsv[3]);
         }
       }
-      if (it >= 2) {  // the MMAs that read this group's previous tiles must have retired
-        ok = __all_sync(0xffffffffu, mbar_wait(BAR(A_PE + g), ((it >> 1) - 1) & 1, abort_flag));
-        if (!ok) break;
-      }
-      store_row64(my_pt, row, ppk);
-      store_row64(my_dst, row, dpk);
-      fence_async_smem();
+      // P^T and dS^T go back into tensor memory, over the first 32 columns of this group's S^T and dP^T buffers (both are
+      // in registers by now); the dV / dK MMAs read them as A operands, and the scores of sub-tile it + 2, issued after
+      // those MMAs by the same thread, overwrite them in order.
+      tc_st32(t_lane + g * SUB, ppk);
+      tc_st32(t_lane + 128 + g * SUB, dpk);
+      tc_wait_st();
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(BAR(A_PF + g));
@@ -474,8 +458,8 @@ struct DqCfg {
   static constexpr int NB = D / 64;
   static constexpr int Q_BYTES = 128 * D * 2;   // resident Q or dO tile
   static constexpr int KS_BYTES = SUB * D * 2;  // one 64-key K or V stage
-  static constexpr int DS_BYTES = 128 * SUB * 2;
-  static constexpr int SMEM = 2 * Q_BYTES + (KV_STAGES_B + V_STAGES_B) * KS_BYTES + DQ_GROUPS * DS_BYTES + 1024 + 256;
+  static constexpr int SMEM = 2 * Q_BYTES + (KV_STAGES_B + V_STAGES_B) * KS_BYTES + 1024 + 512;  // 35 barriers need more than 256 bytes
+  static_assert(B_NBAR * 8 + 16 <= 512, "barrier area");
 };
 
 template <int D>
@@ -508,9 +492,7 @@ flash_bwd_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
   const uint32_t q_smem = base, do_smem = base + C::Q_BYTES;
   const uint32_t k_smem = do_smem + C::Q_BYTES;                 // stages
   const uint32_t v_smem = k_smem + KV_STAGES_B * C::KS_BYTES;    // stages
-  const uint32_t ds_smem = v_smem + V_STAGES_B * C::KS_BYTES;
-  uint8_t* ds_ptr = aligned + (ds_smem - base);
-  uint64_t* bars = reinterpret_cast<uint64_t*>(ds_ptr + DQ_GROUPS * C::DS_BYTES);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(aligned + (v_smem + V_STAGES_B * C::KS_BYTES - base));
   const uint32_t bar0 = smem_u32(bars);
   auto BAR = [&](int i) { return bar0 + 8u * i; };
   uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(bars + B_NBAR);
@@ -569,7 +551,7 @@ flash_bwd_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
       bool ok = mbar_wait(BAR(0), 0, abort_flag);
       const uint32_t q_lo = desc_lo(q_smem, true, 0), do_lo = desc_lo(do_smem, true, 0);
       const uint32_t k_lo0 = desc_lo(k_smem, true, 0), v_lo0 = desc_lo(v_smem, true, 0);
-      const uint32_t kmn_lo0 = desc_lo(k_smem, false, BLK64), ds_lo0 = desc_lo(ds_smem, true, 0);
+      const uint32_t kmn_lo0 = desc_lo(k_smem, false, BLK64);
       auto issue_scores = [&](int j) -> bool {
         const int st = j % KV_STAGES_B, sv = j % V_STAGES_B, buf = j % DQ_GROUPS;
         if (!mbar_wait(BAR(B_KF + st), (j / KV_STAGES_B) & 1, abort_flag) || !mbar_wait(BAR(B_VF + sv), (j / V_STAGES_B) & 1, abort_flag))
@@ -594,9 +576,9 @@ flash_bwd_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
         const int g = j % DQ_GROUPS;
         if (!mbar_wait(BAR(B_DF + g), (j / DQ_GROUPS) & 1, abort_flag)) { ok = false; break; }
         tc_fence_after();
-        const uint32_t ds_lo = ds_lo0 + g * (C::DS_BYTES >> 4), kmn_lo = kmn_lo0 + st * (C::KS_BYTES >> 4);
+        const uint32_t ds_t = tmem_base + (DQ_GROUPS + g) * SUB, kmn_lo = kmn_lo0 + st * (C::KS_BYTES >> 4);  // dS over dP
 #pragma unroll
-        for (int k = 0; k < 4; ++k) tc_mma_lo(tmem_dq, ds_lo + 2 * k, kmn_lo + k * 128, idesc_acc, (j | k) ? 1u : 0u);
+        for (int k = 0; k < 4; ++k) tc_mma_ts(tmem_dq, ds_t + 8 * k, kmn_lo + k * 128, idesc_acc, (j | k) ? 1u : 0u);
         tc_commit(BAR(B_KE + st));  // K stage free
         tc_commit(BAR(B_DE + g));  // this group's dS consumed
         if (j + DQ_GROUPS < n_it && !issue_scores(j + DQ_GROUPS)) { ok = false; break; }
@@ -619,7 +601,6 @@ flash_bwd_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
     const float scale_log2 = scale * LOG2E;
     int limit = si.k_len;
     if (causal) limit = min(limit, q_idx + off + 1);
-    uint8_t* my_ds = ds_ptr + g * C::DS_BYTES;
     bool ok = true;
     for (int j = g; j < n_it; j += DQ_GROUPS) {
       ok = __all_sync(0xffffffffu, mbar_wait(BAR(B_SF + g), (j / DQ_GROUPS) & 1, abort_flag));
@@ -645,12 +626,9 @@ flash_bwd_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
           dpk[half * 16 + (i >> 1)] = pack2(p0 * (__uint_as_float(dp[i]) - dlt), p1 * (__uint_as_float(dp[i + 1]) - dlt));
         }
       }
-      if (j >= DQ_GROUPS) {
-        ok = __all_sync(0xffffffffu, mbar_wait(BAR(B_DE + g), ((j / DQ_GROUPS) - 1) & 1, abort_flag));
-        if (!ok) break;
-      }
-      store_row64(my_ds, row, dpk);
-      fence_async_smem();
+      // dS goes back into tensor memory over the first 32 columns of this group's dP buffer and is the A operand of the dQ MMAs
+      tc_st32(t_lane + (DQ_GROUPS + g) * SUB, dpk);
+      tc_wait_st();
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(BAR(B_DF + g));

@@ -36,12 +36,25 @@ __device__ __forceinline__ bool mbar_try(uint32_t bar, uint32_t parity) {
       : "memory");
   return ok != 0;
 }
+// Probe that lets the hardware suspend the thread for up to `ns` nanoseconds while the phase is pending, so a waiting
+// warp does not take issue slots from the warps that share its scheduler.
+__device__ __forceinline__ bool mbar_try_suspend(uint32_t bar, uint32_t parity, uint32_t ns) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity), "r"(ns)
+      : "memory");
+  return ok != 0;
+}
 // Bounded wait.  Returns false after WAIT_LIMIT_NS or as soon as another role raised the abort flag.
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
   if (mbar_try(bar, parity)) return true;
   const unsigned long long t0 = gtime();
   for (uint32_t spin = 1;; ++spin) {
-    if (mbar_try(bar, parity)) return true;
+    if (mbar_try_suspend(bar, parity, 2000u)) return true;
     if ((spin & 63u) == 0) {
       if (*abort_flag) return false;
       if (gtime() - t0 > WAIT_LIMIT_NS) return false;
