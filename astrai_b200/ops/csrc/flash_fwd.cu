@@ -424,11 +424,13 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
             pk[c * 16 + (i >> 1)] = *reinterpret_cast<const uint32_t*>(&hh);
           }
         const float rowsum = (rs4[0] + rs4[1]) + (rs4[2] + rs4[3]);
-        if (it > 0 && grow) {  // the previous P V must have updated O before O is rescaled
+        if (kc > 0) {
+          // Every tile observes the completion of the previous P V product, needed or not: a parity wait is only
+          // sound while the waiter is at most one phase behind the barrier, and the end-of-item wait below relies on it.
           ok = __all_sync(0xffffffffu, mbar_wait(BAR(PE), (kc - 1) & 1, abort_flag));
           if (!ok) break;
           tc_fence_after();
-          {
+          if (it > 0 && grow) {  // that product has updated O, which may now be rescaled
 #pragma unroll 1
             for (int c = 0; c < D / 32; ++c) {
               uint32_t o[32];

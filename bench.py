@@ -20,6 +20,7 @@ from __future__ import annotations
 
 import argparse
 import json
+import math
 import os
 import statistics
 import subprocess
@@ -273,6 +274,9 @@ def run_ours(args):
         results["clocks"] = sampler.stop() if sampler else None
         results["final_loss"] = ctx.loss
         assert native.kernel_status(dev) == 0, "a kernel's bounded wait expired"
+        # a step that produced NaN / Inf runs at low power and high clocks: its timing is not a measurement
+        if not math.isfinite(float(results["final_loss"])):
+            raise RuntimeError(f"training diverged during the benchmark (loss {results['final_loss']}); no number is reported")
         del ctx, trainer, pool
         torch.cuda.empty_cache()
         # ---- (2) end to end through Trainer.train(): host data, pinned H2D per micro-batch, D2H per step -----------

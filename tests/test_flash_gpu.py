@@ -110,6 +110,35 @@ def test_flash_bwd_dense(d, causal, b, s, hq, hkv):
     assert native.kernel_status(q.device) == 0
 
 
+@pytest.mark.parametrize("b,s,hq,hkv,d", [(4, 2048, 16, 4, 128), (3, 1152, 8, 2, 64)])
+def test_flash_many_items_per_cta(b, s, hq, hkv, d):
+    """More work items than resident CTAs (the persistent forward kernel walks several items per CTA, so its barrier
+    phases, Q tile and O accumulator are reused) and long key / query loops in the backward kernels (every ring wraps
+    many times).  Forward and backward against the fp32 statement, sequence by sequence."""
+    ops = _native()
+    torch.manual_seed(5)
+    q = torch.randn(b * s, hq, d, device="cuda", dtype=torch.bfloat16)
+    k = torch.randn(b * s, hkv, d, device="cuda", dtype=torch.bfloat16)
+    v = torch.randn(b * s, hkv, d, device="cuda", dtype=torch.bfloat16)
+    do = torch.randn(b * s, hq, d, device="cuda", dtype=torch.bfloat16)
+    scale = 1.0 / math.sqrt(d)
+    out, lse = ops.flash_fwd(q, k, v, None, None, b, s, s, s, True, scale)
+    dq, dk, dv = ops.flash_bwd(q, k, v, out, do, lse, None, None, b, s, s, s, s, True, scale)
+    assert not torch.isnan(out).any() and not torch.isnan(dq).any() and not torch.isnan(dk).any() and not torch.isnan(dv).any()
+    for i in range(b):
+        sl = slice(i * s, (i + 1) * s)
+        ref, ref_lse = _ref_attention(q[sl].float(), k[sl].float(), v[sl].float(), True, scale)
+        assert (out[sl].float() - ref).abs().max().item() < 2e-2, ("out", i)
+        assert (lse[:, sl] - ref_lse).abs().max().item() < 2e-2, ("lse", i)
+        rq, rk, rv = _ref_grads(q[sl], k[sl], v[sl], do[sl], True, scale)
+        assert _close(dv[sl], rv, 2e-2), ("dv", i)
+        assert _close(dk[sl], rk, 2e-2), ("dk", i)
+        assert _close(dq[sl], rq, 2e-2), ("dq", i)
+    from astrai_b200.ops import native
+
+    assert native.kernel_status(q.device) == 0
+
+
 def test_flash_bwd_varlen_with_prefix():
     ops = _native()
     torch.manual_seed(3)
