@@ -51,6 +51,38 @@ __device__ __forceinline__ TileCoord tile_coord2(int t, int tiles_m, int tiles_n
   return {(g * G + r % rows) * (2 * BM), (r / rows) * BN};
 }
 
+// Work list of one CTA pair.  Full rounds: tile p + r * P of the rasterised order, 256 columns wide.  The tiles left
+// over after the last full round (fewer than P) would keep most pairs idle for a whole tile time; when twice their
+// number still fits into one round they are cut into two 128-column halves, one per pair, so the tail costs about
+// half a tile time instead of one.
+struct Work {
+  int t, n_off, bn;
+};
+struct Schedule {
+  int num_tiles, P, p, full_rounds, rem;
+  bool split;
+  __device__ Schedule(int num_tiles_, int P_, int p_) : num_tiles(num_tiles_), P(P_), p(p_) {
+    full_rounds = num_tiles / P;
+    rem = num_tiles - full_rounds * P;
+    split = rem > 0 && 2 * rem <= P;
+  }
+  __device__ bool get(int i, Work& w) const {
+    if (i < full_rounds) {
+      w = {p + i * P, 0, BN};
+      return true;
+    }
+    if (i > full_rounds) return false;
+    if (split) {
+      if (p >= 2 * rem) return false;
+      w = {full_rounds * P + (p >> 1), (p & 1) * (BN / 2), BN / 2};
+      return true;
+    }
+    if (p >= rem) return false;
+    w = {full_rounds * P + p, 0, BN};
+    return true;
+  }
+};
+
 template <bool A_K, bool B_K, bool OUT_F32, bool ACCUM>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(NUM_THREADS, 1)
 gemm2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, void* __restrict__ Dv,
@@ -106,9 +138,15 @@ gemm2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ 
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
-      for (int t = pair; t < num_tiles && ok; t += num_pairs) {
-        const TileCoord tc = tile_coord2(t, tiles_m, tiles_n);
-        const int m0 = tc.m0 + (int)rank * BM, n0 = tc.n0 + (int)rank * BNH;
+      const Schedule sched(num_tiles, num_pairs, pair);
+      Work wk;
+      for (int wi = 0; ok && sched.get(wi, wk); ++wi) {
+        const TileCoord tc = tile_coord2(wk.t, tiles_m, tiles_n);
+        const bool half = wk.bn != BN;  // each CTA then supplies 64 rows of B instead of 128
+        const int m0 = tc.m0 + (int)rank * BM, n0 = tc.n0 + wk.n_off + (int)rank * (wk.bn / 2);
+        // K-major B: the 128-row box is loaded either way (its first 64 rows are the half tile's); MN-major B: one
+        // 64-column box instead of two
+        const uint32_t stage_tx = (!B_K && half) ? (uint32_t)(A_BYTES + B_BYTES / 2) : (uint32_t)STAGE_BYTES;
         for (int kb = 0; kb < num_kb; ++kb) {
           if (!mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag)) {
             ok = false;
@@ -116,7 +154,7 @@ gemm2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ 
           }
           const uint32_t sa = base + stage * STAGE_BYTES, sb = sa + A_BYTES;
           const uint32_t fb = mapa(full_bar(stage), 0);  // byte counts go to the leader's barrier
-          if (leader) mbar_expect_tx(full_bar(stage), 2 * STAGE_BYTES);
+          if (leader) mbar_expect_tx(full_bar(stage), 2 * stage_tx);
           const int k0 = kb * BK;
           if (A_K) {
             tma_load_2d_cg2(sa, &map_a, fb, k0, m0);
@@ -128,7 +166,8 @@ gemm2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ 
             tma_load_2d_cg2(sb, &map_b, fb, k0, n0);
           } else {
 #pragma unroll
-            for (int j = 0; j < BNH / 64; ++j) tma_load_2d_cg2(sb + j * (BK * 128), &map_b, fb, n0 + 64 * j, k0);
+            for (int j = 0; j < BNH / 64; ++j)
+              if (j == 0 || !half) tma_load_2d_cg2(sb + j * (BK * 128), &map_b, fb, n0 + 64 * j, k0);
           }
           if (++stage == STAGES) stage = 0, phase ^= 1u;
         }
@@ -141,15 +180,18 @@ gemm2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ 
   } else if (warp == 1) {
     // ------------------------------------------------------------ MMA issuer (leader only)
     if (leader && lane == 0) {
-      constexpr uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((A_K ? 0u : 1u) << 15) |
-                                 ((B_K ? 0u : 1u) << 16) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)((2 * BM) >> 4) << 24);
+      constexpr uint32_t idesc_base = (1u << 4) | (1u << 7) | (1u << 10) | ((A_K ? 0u : 1u) << 15) |
+                                      ((B_K ? 0u : 1u) << 16) | ((uint32_t)((2 * BM) >> 4) << 24);
       int stage = 0;
       uint32_t phase = 0;
       int it = 0;
       bool ok = true;
-      for (int t = pair; t < num_tiles && ok; t += num_pairs, ++it) {
+      const Schedule sched(num_tiles, num_pairs, pair);
+      Work wk;
+      for (; ok && sched.get(it, wk); ++it) {
         const int buf = it & 1;
         const uint32_t acc_phase = (it >> 1) & 1;
+        const uint32_t idesc = idesc_base | ((uint32_t)(wk.bn >> 3) << 17);
         if (!mbar_wait(tempty_bar(buf), acc_phase ^ 1u, abort_flag)) {
           atomicMax(status, ERR_MMA_TMEM);
           ok = false;
@@ -185,10 +227,13 @@ gemm2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ 
     const uint32_t tempty_leader0 = mapa(tempty_bar(0), 0), tempty_leader1 = mapa(tempty_bar(1), 0);
     int it = 0;
     bool ok = true;
-    for (int t = pair; t < num_tiles && ok; t += num_pairs, ++it) {
+    const Schedule sched(num_tiles, num_pairs, pair);
+    Work wk;
+    for (; ok && sched.get(it, wk); ++it) {
       const int buf = it & 1;
       const uint32_t acc_phase = (it >> 1) & 1;
-      const TileCoord tc = tile_coord2(t, tiles_m, tiles_n);
+      TileCoord tc = tile_coord2(wk.t, tiles_m, tiles_n);
+      tc.n0 += wk.n_off;
       if (!mbar_wait(tfull_bar(buf), acc_phase, abort_flag)) {
         if (lane == 0) atomicMax(status, ERR_EPILOGUE);
         ok = false;
@@ -198,7 +243,7 @@ gemm2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ 
       const int row = tc.m0 + (int)rank * BM + quarter * 32 + lane;
       const uint32_t taddr0 = tmem_base + ((uint32_t)(quarter * 32) << 16) + buf * BN;
 #pragma unroll 1
-      for (int c = 0; c < BN / 32; ++c) {
+      for (int c = 0; c < wk.bn / 32; ++c) {
         uint32_t r[32];
         tc_ld32(taddr0 + c * 32, r);
         tc_wait_ld();
