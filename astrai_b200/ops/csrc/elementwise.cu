@@ -198,7 +198,9 @@ void rmsnorm_fwd(const void* x, const void* w, void* y, float* rstd, long long r
 }
 
 int rmsnorm_bwd_parts(long long rows, int cols) {
-  if (cols % 8 == 0 && cols >= 512 && cols <= 16384) return (int)(rows < 296 ? rows : 296);  // 148 SMs x 2
+  // one row at a time per 256-thread block with a block-wide reduction in between: four blocks per SM keep enough
+  // loads in flight to cover that latency
+  if (cols % 8 == 0 && cols >= 512 && cols <= 16384) return (int)(rows < 592 ? rows : 592);  // 148 SMs x 4
   return 0;  // small path accumulates with atomics into a zeroed dw
 }
 
