@@ -8,6 +8,7 @@ from typing import Optional, TypedDict
 import torch.nn as nn
 from torch import Tensor
 
+from astrai_b200 import ops
 from astrai_b200.models.attention import AttnFactory
 from astrai_b200.models.ffn import FFNFactory, RouterStats
 from astrai_b200.models.layers import RMSNorm
@@ -48,8 +49,10 @@ class DecoderBlock(nn.Module):
 
     def forward(self, x: Tensor, rotary_emb: Tensor, attention_mask: Optional[Tensor] = None, kv_cache=None,
                 is_causal: bool = False, fwd: Optional[str] = None) -> DecoderOutput:
-        x = x + self.attention(self.input_norm(x), rotary_emb, attention_mask, kv_cache, is_causal, fwd)
-        ffn = self.mlp(self.post_attention_norm(x))
+        attn = self.attention(self.input_norm(x), rotary_emb, attention_mask, kv_cache, is_causal, fwd)
+        # residual add and the norm that follows it as one pass over the rows (one kernel on CUDA)
+        x, h = ops.add_rms_norm(x, attn, self.post_attention_norm.weight, self.post_attention_norm.norm_eps)
+        ffn = self.mlp(h)
         return {
             "hidden_states": x + ffn["hidden_states"],
             "aux_loss": ffn["aux_loss"],

@@ -6,6 +6,7 @@ from astrai_b200.ops.attention import dense_attention
 from astrai_b200.ops.backend import ATTN_BACKEND, attn_backend, get_backend
 from astrai_b200.ops.functional import (
     adamw_,
+    add_rms_norm,
     assume_loss_grad,
     clip_coef,
     cross_entropy,
@@ -23,7 +24,7 @@ from astrai_b200.ops.functional import (
 )
 
 __all__ = [
-    "ATTN_BACKEND", "attn_backend", "get_backend", "DelayedScaling", "DynamicScaling", "FP8Format", "fp8", "fp8_autocast", "adamw_", "assume_loss_grad", "clip_coef", "cross_entropy", "dense_attention", "embedding", "gemm", "linear",
+    "ATTN_BACKEND", "attn_backend", "get_backend", "DelayedScaling", "DynamicScaling", "FP8Format", "fp8", "fp8_autocast", "adamw_", "add_rms_norm", "assume_loss_grad", "clip_coef", "cross_entropy", "dense_attention", "embedding", "gemm", "linear",
     "linear_cross_entropy", "linear_token_logprobs", "native", "qkv_rope", "reference", "rms_norm", "rotary",
     "sumsq", "swiglu", "swiglu_fused",
 ]

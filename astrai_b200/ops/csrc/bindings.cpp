@@ -57,6 +57,46 @@ std::tuple<Tensor, Tensor> rmsnorm_bwd(const Tensor& g, const Tensor& x, const T
   return {dx, dw};
 }
 
+// Residual add fused into the norm: returns (x + res, rmsnorm(x + res) * w, rstd).  Wide rows only.
+std::tuple<Tensor, Tensor, Tensor> add_rmsnorm_fwd(const Tensor& x, const Tensor& res, const Tensor& w, double eps) {
+  CHECK_CUDA_CONTIG(x);
+  CHECK_CUDA_CONTIG(res);
+  CHECK_CUDA_CONTIG(w);
+  TORCH_CHECK(x.scalar_type() == w.scalar_type() && x.scalar_type() == res.scalar_type() && x.sizes() == res.sizes(),
+              "add_rmsnorm: x, res and weight must agree in dtype, x and res in shape");
+  const int cols = (int)x.size(-1);
+  TORCH_CHECK(ab::rmsnorm_wide(cols), "add_rmsnorm: row width must be a multiple of 8 in [512, 16384]");
+  const c10::cuda::CUDAGuard guard(x.device());
+  const long long rows = x.numel() / cols;
+  Tensor xsum = at::empty_like(x), y = at::empty_like(x);
+  Tensor rstd = at::empty({rows}, x.options().dtype(at::kFloat));
+  count();
+  ab::rmsnorm_fwd(x.data_ptr(), w.data_ptr(), y.data_ptr(), rstd.data_ptr<float>(), rows, cols, (float)eps, is_bf16(x),
+                  stream(), res.data_ptr(), xsum.data_ptr());
+  return {xsum, y, rstd};
+}
+
+// Backward of the fused form: dx = rmsnorm_bwd(g, x, w, rstd) + gres.
+std::tuple<Tensor, Tensor> rmsnorm_bwd_add(const Tensor& g, const Tensor& x, const Tensor& w, const Tensor& rstd,
+                                           const Tensor& gres) {
+  CHECK_CUDA_CONTIG(g);
+  CHECK_CUDA_CONTIG(x);
+  CHECK_CUDA_CONTIG(gres);
+  TORCH_CHECK(gres.scalar_type() == x.scalar_type() && gres.sizes() == x.sizes(), "rmsnorm_bwd_add: gres must match x");
+  const int cols = (int)x.size(-1);
+  TORCH_CHECK(ab::rmsnorm_wide(cols), "rmsnorm_bwd_add: row width must be a multiple of 8 in [512, 16384]");
+  const c10::cuda::CUDAGuard guard(x.device());
+  const long long rows = x.numel() / cols;
+  Tensor dx = at::empty_like(x);
+  Tensor dw = at::empty({cols}, x.options().dtype(at::kFloat));
+  const int parts = ab::rmsnorm_bwd_parts(rows, cols);
+  Tensor partial = at::empty({parts > 0 ? parts : 1, cols}, dw.options());
+  count(2);
+  ab::rmsnorm_bwd(g.data_ptr(), x.data_ptr(), w.data_ptr(), rstd.data_ptr<float>(), dx.data_ptr(), dw.data_ptr<float>(),
+                  partial.data_ptr<float>(), rows, cols, is_bf16(x), stream(), gres.data_ptr());
+  return {dx, dw};
+}
+
 // x, out: [tokens, heads, rot_dim] views with unit last stride; freqs: [tokens, rot_dim/2, 2] fp32 contiguous.
 void rope(const Tensor& x, Tensor& out, const Tensor& freqs, bool inverse) {
   TORCH_CHECK(x.is_cuda() && x.dim() == 3 && out.dim() == 3 && x.stride(2) == 1 && out.stride(2) == 1, "rope: bad layout");
@@ -925,6 +965,8 @@ void kernel_status_reset(const Tensor& like) { status_tensor(like.device()).zero
 TORCH_LIBRARY(astrai_b200, m) {
   m.def("rmsnorm_fwd(Tensor x, Tensor w, float eps) -> (Tensor, Tensor)", &rmsnorm_fwd);
   m.def("rmsnorm_bwd(Tensor g, Tensor x, Tensor w, Tensor rstd) -> (Tensor, Tensor)", &rmsnorm_bwd);
+  m.def("add_rmsnorm_fwd(Tensor x, Tensor res, Tensor w, float eps) -> (Tensor, Tensor, Tensor)", &add_rmsnorm_fwd);
+  m.def("rmsnorm_bwd_add(Tensor g, Tensor x, Tensor w, Tensor rstd, Tensor gres) -> (Tensor, Tensor)", &rmsnorm_bwd_add);
   m.def("rope(Tensor x, Tensor(a!) out, Tensor freqs, bool inverse) -> ()", &rope);
   m.def("swiglu_fwd(Tensor gate, Tensor up) -> Tensor", &swiglu_fwd);
   m.def("swiglu_bwd(Tensor dy, Tensor gate, Tensor up) -> Tensor", &swiglu_bwd);

@@ -12,7 +12,9 @@ namespace ab {
 template <typename T, int VPT>
 __global__ void __launch_bounds__(256) rmsnorm_fwd_kernel(const T* __restrict__ x, const T* __restrict__ w,
                                                           T* __restrict__ y, float* __restrict__ rstd_out,
-                                                          int cols, float eps) {
+                                                          int cols, float eps, const T* __restrict__ res,
+                                                          T* __restrict__ xsum) {
+  // With `res` the row normalised is x + res, rounded to T and also written to `xsum` (residual add fused in).
   __shared__ float scratch[32];
   const long long row = blockIdx.x;
   const T* xr = x + row * cols;
@@ -27,6 +29,17 @@ __global__ void __launch_bounds__(256) rmsnorm_fwd_kernel(const T* __restrict__ 
       Vec8<T> t;
       t.load(xr + c * 8);
       t.unpack(v[i]);
+      if (res != nullptr) {
+        Vec8<T> rv;
+        float rf[8];
+        rv.load(res + row * cols + c * 8);
+        rv.unpack(rf);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) rf[j] += v[i][j];
+        rv.pack(rf);
+        rv.store(xsum + row * cols + c * 8);
+        rv.unpack(v[i]);  // the rounded sum is what the unfused path would normalise
+      }
 #pragma unroll
       for (int j = 0; j < 8; ++j) ss += v[i][j] * v[i][j];
     }
@@ -76,7 +89,8 @@ template <typename T, int VPT>
 __global__ void __launch_bounds__(256) rmsnorm_bwd_kernel(const T* __restrict__ g, const T* __restrict__ x,
                                                           const T* __restrict__ w, const float* __restrict__ rstd,
                                                           T* __restrict__ dx, float* __restrict__ dw_partial,
-                                                          long long rows, int cols) {
+                                                          long long rows, int cols, const T* __restrict__ gres) {
+  // With `gres` the gradient that reaches x along the residual branch is added into dx here.
   __shared__ float scratch[32];
   const int nvec = cols >> 3;
   float wf[VPT][8], acc[VPT][8];
@@ -120,6 +134,14 @@ __global__ void __launch_bounds__(256) rmsnorm_bwd_kernel(const T* __restrict__ 
         float o[8];
 #pragma unroll
         for (int j = 0; j < 8; ++j) o[j] = gv[i][j] * wf[i][j] * r - xv[i][j] * k;
+        if (gres != nullptr) {
+          Vec8<T> rv;
+          float rf[8];
+          rv.load(gres + row * cols + c * 8);
+          rv.unpack(rf);
+#pragma unroll
+          for (int j = 0; j < 8; ++j) o[j] += rf[j];
+        }
         Vec8<T> ov;
         ov.pack(o);
         ov.store(dx + row * cols + c * 8);
@@ -175,15 +197,15 @@ __global__ void colsum_kernel(const float* __restrict__ partial, float* __restri
 
 template <typename T>
 static void rmsnorm_fwd_t(const void* x, const void* w, void* y, float* rstd, long long rows, int cols, float eps,
-                          cudaStream_t st) {
+                          cudaStream_t st, const void* res, void* xsum) {
   if (rows == 0) return;
   if (cols % 8 == 0 && cols >= 512 && cols <= 16384) {
     const int nvec = cols / 8;
-    auto X = (const T*)x; auto W = (const T*)w; auto Y = (T*)y;
-    if (nvec <= 256) rmsnorm_fwd_kernel<T, 1><<<rows, 256, 0, st>>>(X, W, Y, rstd, cols, eps);
-    else if (nvec <= 512) rmsnorm_fwd_kernel<T, 2><<<rows, 256, 0, st>>>(X, W, Y, rstd, cols, eps);
-    else if (nvec <= 1024) rmsnorm_fwd_kernel<T, 4><<<rows, 256, 0, st>>>(X, W, Y, rstd, cols, eps);
-    else rmsnorm_fwd_kernel<T, 8><<<rows, 256, 0, st>>>(X, W, Y, rstd, cols, eps);
+    auto X = (const T*)x; auto W = (const T*)w; auto Y = (T*)y; auto R = (const T*)res; auto XS = (T*)xsum;
+    if (nvec <= 256) rmsnorm_fwd_kernel<T, 1><<<rows, 256, 0, st>>>(X, W, Y, rstd, cols, eps, R, XS);
+    else if (nvec <= 512) rmsnorm_fwd_kernel<T, 2><<<rows, 256, 0, st>>>(X, W, Y, rstd, cols, eps, R, XS);
+    else if (nvec <= 1024) rmsnorm_fwd_kernel<T, 4><<<rows, 256, 0, st>>>(X, W, Y, rstd, cols, eps, R, XS);
+    else rmsnorm_fwd_kernel<T, 8><<<rows, 256, 0, st>>>(X, W, Y, rstd, cols, eps, R, XS);
   } else {
     const int wpb = 8;
     rmsnorm_fwd_small_kernel<T><<<ceil_div(rows, wpb), wpb * 32, 0, st>>>((const T*)x, (const T*)w, (T*)y, rstd,
@@ -192,10 +214,12 @@ static void rmsnorm_fwd_t(const void* x, const void* w, void* y, float* rstd, lo
 }
 
 void rmsnorm_fwd(const void* x, const void* w, void* y, float* rstd, long long rows, int cols, float eps,
-                 bool is_bf16, cudaStream_t st) {
-  if (is_bf16) rmsnorm_fwd_t<__nv_bfloat16>(x, w, y, rstd, rows, cols, eps, st);
-  else rmsnorm_fwd_t<float>(x, w, y, rstd, rows, cols, eps, st);
+                 bool is_bf16, cudaStream_t st, const void* res, void* xsum) {
+  if (is_bf16) rmsnorm_fwd_t<__nv_bfloat16>(x, w, y, rstd, rows, cols, eps, st, res, xsum);
+  else rmsnorm_fwd_t<float>(x, w, y, rstd, rows, cols, eps, st, res, xsum);
 }
+
+bool rmsnorm_wide(int cols) { return cols % 8 == 0 && cols >= 512 && cols <= 16384; }
 
 int rmsnorm_bwd_parts(long long rows, int cols) {
   // one row at a time per 256-thread block with a block-wide reduction in between: four blocks per SM keep enough
@@ -206,16 +230,16 @@ int rmsnorm_bwd_parts(long long rows, int cols) {
 
 template <typename T>
 static void rmsnorm_bwd_t(const void* g, const void* x, const void* w, const float* rstd, void* dx, float* dw,
-                          float* partial, long long rows, int cols, cudaStream_t st) {
+                          float* partial, long long rows, int cols, cudaStream_t st, const void* gres) {
   if (rows == 0) return;
   const int parts = rmsnorm_bwd_parts(rows, cols);
   if (parts > 0) {
     const int nvec = cols / 8;
-    auto G = (const T*)g; auto X = (const T*)x; auto W = (const T*)w; auto DX = (T*)dx;
-    if (nvec <= 256) rmsnorm_bwd_kernel<T, 1><<<parts, 256, 0, st>>>(G, X, W, rstd, DX, partial, rows, cols);
-    else if (nvec <= 512) rmsnorm_bwd_kernel<T, 2><<<parts, 256, 0, st>>>(G, X, W, rstd, DX, partial, rows, cols);
-    else if (nvec <= 1024) rmsnorm_bwd_kernel<T, 4><<<parts, 256, 0, st>>>(G, X, W, rstd, DX, partial, rows, cols);
-    else rmsnorm_bwd_kernel<T, 8><<<parts, 256, 0, st>>>(G, X, W, rstd, DX, partial, rows, cols);
+    auto G = (const T*)g; auto X = (const T*)x; auto W = (const T*)w; auto DX = (T*)dx; auto GR = (const T*)gres;
+    if (nvec <= 256) rmsnorm_bwd_kernel<T, 1><<<parts, 256, 0, st>>>(G, X, W, rstd, DX, partial, rows, cols, GR);
+    else if (nvec <= 512) rmsnorm_bwd_kernel<T, 2><<<parts, 256, 0, st>>>(G, X, W, rstd, DX, partial, rows, cols, GR);
+    else if (nvec <= 1024) rmsnorm_bwd_kernel<T, 4><<<parts, 256, 0, st>>>(G, X, W, rstd, DX, partial, rows, cols, GR);
+    else rmsnorm_bwd_kernel<T, 8><<<parts, 256, 0, st>>>(G, X, W, rstd, DX, partial, rows, cols, GR);
     colsum_kernel<<<ceil_div(cols, 32), dim3(32, 8), 0, st>>>(partial, dw, parts, cols);
   } else {
     cudaMemsetAsync(dw, 0, sizeof(float) * cols, st);
@@ -226,9 +250,9 @@ static void rmsnorm_bwd_t(const void* g, const void* x, const void* w, const flo
 }
 
 void rmsnorm_bwd(const void* g, const void* x, const void* w, const float* rstd, void* dx, float* dw, float* partial,
-                 long long rows, int cols, bool is_bf16, cudaStream_t st) {
-  if (is_bf16) rmsnorm_bwd_t<__nv_bfloat16>(g, x, w, rstd, dx, dw, partial, rows, cols, st);
-  else rmsnorm_bwd_t<float>(g, x, w, rstd, dx, dw, partial, rows, cols, st);
+                 long long rows, int cols, bool is_bf16, cudaStream_t st, const void* gres) {
+  if (is_bf16) rmsnorm_bwd_t<__nv_bfloat16>(g, x, w, rstd, dx, dw, partial, rows, cols, st, gres);
+  else rmsnorm_bwd_t<float>(g, x, w, rstd, dx, dw, partial, rows, cols, st, gres);
 }
 
 // ---------------------------------------------------------------- RoPE

@@ -5,11 +5,14 @@
 
 namespace ab {
 
+// `res` / `xsum` (wide rows only: cols % 8 == 0, 512 <= cols <= 16384): normalise x + res and write the sum to xsum.
 void rmsnorm_fwd(const void* x, const void* w, void* y, float* rstd, long long rows, int cols, float eps,
-                 bool is_bf16, cudaStream_t st);
+                 bool is_bf16, cudaStream_t st, const void* res = nullptr, void* xsum = nullptr);
+bool rmsnorm_wide(int cols);
 int rmsnorm_bwd_parts(long long rows, int cols);
+// `gres` (wide rows only): a second gradient of x, added into dx.
 void rmsnorm_bwd(const void* g, const void* x, const void* w, const float* rstd, void* dx, float* dw, float* partial,
-                 long long rows, int cols, bool is_bf16, cudaStream_t st);
+                 long long rows, int cols, bool is_bf16, cudaStream_t st, const void* gres = nullptr);
 void rope_apply(const void* x, void* out, const float* freqs, long long tokens, int heads, int rot_dim,
                 long long x_tok_stride, int x_head_stride, long long o_tok_stride, int o_head_stride, bool inverse,
                 bool is_bf16, cudaStream_t st);

@@ -143,6 +143,44 @@ def rms_norm(x: Tensor, weight: Tensor, eps: float) -> Tensor:
     return reference.rms_norm(x, weight, eps)
 
 
+class _AddRMSNormFn(Function):
+    """``s = x + res; y = rms_norm(s)`` in one pass over the rows; the backward adds the gradient that reaches ``s``
+    directly (the residual branch) into the norm's input gradient inside the same kernel."""
+
+    @staticmethod
+    def forward(ctx, x: Tensor, res: Tensor, w: Tensor, eps: float):
+        s, y, rstd = _ops().add_rmsnorm_fwd(x.contiguous(), res.contiguous(), w.contiguous(), eps)
+        ctx.save_for_backward(s, w, rstd)
+        ctx.w_ref = w
+        return s, y
+
+    @staticmethod
+    def backward(ctx, gs: Tensor, gy: Tensor):
+        s, w, rstd = ctx.saved_tensors
+        if gy is None:
+            return gs, gs, None, None
+        if gs is None:
+            dx, dw = _ops().rmsnorm_bwd(gy.contiguous(), s, w.contiguous(), rstd)
+        else:
+            dx, dw = _ops().rmsnorm_bwd_add(gy.contiguous(), s, w.contiguous(), rstd, gs.contiguous())
+        mg = _main_grad(ctx.w_ref)
+        if mg is not None:
+            mg.add_(dw)
+            return dx, dx, None, None
+        return dx, dx, dw.to(w.dtype), None
+
+
+def add_rms_norm(x: Tensor, res: Tensor, weight: Tensor, eps: float) -> Tuple[Tensor, Tensor]:
+    """``(x + res, rms_norm(x + res, weight))``: the residual add of a pre-norm block fused into the norm that follows it
+    (reference: ``astrai/model/components/decoder_block.py:67-68`` does the add and the norm as two ops)."""
+    cols = x.shape[-1]
+    if (_use_native(x, res, weight) and x.dtype == weight.dtype == res.dtype and x.shape == res.shape
+            and cols % 8 == 0 and 512 <= cols <= 16384):
+        return _AddRMSNormFn.apply(x, res, weight, float(eps))
+    s = x + res
+    return s, rms_norm(s, weight, eps)
+
+
 # --------------------------------------------------------------------------- RoPE
 def _as_tokens(x: Tensor) -> Tensor:
     """[..., H, D] -> [T, H, D] without a copy when the leading dims collapse."""

@@ -338,3 +338,31 @@ def test_skinny_gemm_matches_fp32(m, n, k):
         ref = x.float() @ w.float().t()
         assert (y.float() - ref).abs().max().item() < 2e-2 * ref.abs().max().item() + 1e-2
     assert native.kernel_status(x.device) == 0
+
+
+@pytest.mark.parametrize("rows,cols", [(64, 2048), (37, 1536), (5, 512)])
+def test_add_rms_norm_matches_unfused(rows, cols):
+    """Residual add fused into the norm, forward and backward, against the fp32 statement of the two separate ops."""
+    from astrai_b200 import ops
+
+    torch.manual_seed(11)
+    x = torch.randn(rows, cols, device="cuda", dtype=torch.bfloat16, requires_grad=True)
+    r = torch.randn(rows, cols, device="cuda", dtype=torch.bfloat16, requires_grad=True)
+    w = (1 + 0.1 * torch.randn(cols, device="cuda")).to(torch.bfloat16).requires_grad_(True)
+    s, y = ops.add_rms_norm(x, r, w, 1e-6)
+    gs, gy = torch.randn_like(s), torch.randn_like(y)
+    (s * gs).sum().backward(retain_graph=True)
+    dx_s = x.grad.clone()
+    x.grad = r.grad = w.grad = None
+    ((s * gs).sum() + (y * gy).sum()).backward()
+    xf, rf, wf = (t.detach().float().requires_grad_(True) for t in (x, r, w))
+    sf = xf + rf
+    sf = sf + (sf.to(torch.bfloat16).float() - sf).detach()  # value rounded as the kernel stores it, gradient of the plain sum
+    yf = torch.nn.functional.rms_norm(sf, (cols,), wf, 1e-6)
+    ((sf * gs.float()).sum() + (yf * gy.float()).sum()).backward()
+    assert torch.equal(s, (x.detach().float() + r.detach().float()).to(torch.bfloat16))
+    assert (y.float() - yf).abs().max().item() < 3e-2
+    assert torch.equal(dx_s, gs)  # only the residual branch: the gradient passes through unchanged
+    assert torch.equal(x.grad, r.grad)
+    assert (x.grad.float() - xf.grad).abs().max().item() < 6e-2
+    assert ((w.grad.float() - wf.grad).abs().max() / wf.grad.abs().max()).item() < 2e-2
