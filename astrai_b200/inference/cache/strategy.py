@@ -2,14 +2,15 @@
 
 Semantics of ``astrai/inference/cache/strategy.py:24-318``:
 * ``Allocator``: free pages first, then the least-recently-released cached page (its index entry is evicted);
-* ``RadixCache``: trie whose edges are exact page-sized token tuples; only fully materialised pages are shared;
+  heap of unheld pages + array-threaded ring of retained pages;
+* ``RadixCache``: hash-chained index whose links are exact page-sized token tuples; only fully materialised pages
+  are shared;
 * ``PagedStrategy``: prefix hit -> ``inc_ref`` shared pages, allocate the rest, ``slot = page * page_size + offset``.
 """
 
 from __future__ import annotations
 
 import threading
-from collections import OrderedDict
 from dataclasses import dataclass, field
 from typing import Callable, Dict, List, Optional
 
@@ -27,122 +28,184 @@ class TaskCacheState:
 
 
 class Allocator:
+    """Page accounting for the paged KV pool.
+
+    Three disjoint sets: pages in use (reference count > 0), pages nobody holds, and *retained* pages whose
+    contents a prefix index still points at.  ``alloc`` prefers an unheld page (lowest index first) and otherwise
+    recycles the retained page that was released longest ago, telling ``on_evict`` which one it took.
+
+    Layout: the unheld pages sit in a binary heap; the retained pages form a doubly linked ring threaded through
+    two integer arrays (``_fwd`` / ``_back``, slot ``n_pages`` is the ring's sentinel), so taking a page out of the
+    middle on a cache hit, refreshing it and popping the oldest are all O(1) with no per-page objects.
+    Behaviour follows ``astrai/inference/cache/strategy.py:42-90``.
+    """
+
+    _OUT = -1  # link value of a page that is not on the retained ring
+
     def __init__(self, n_pages: int):
+        import heapq
+
         self.n_pages = n_pages
-        self._free: List[int] = list(range(n_pages - 1, -1, -1))  # pop() hands out the lowest index first
-        self._refs = [0] * n_pages
-        self._lru: "OrderedDict[int, None]" = OrderedDict()
+        self._heap_push, self._heap_pop = heapq.heappush, heapq.heappop
+        self._unheld: List[int] = list(range(n_pages))  # already a valid heap
+        self._holders = [0] * n_pages
+        end = n_pages
+        self._fwd = [self._OUT] * n_pages + [end]
+        self._back = [self._OUT] * n_pages + [end]
+        self._retained = 0
         self.on_evict: Optional[Callable[[int], None]] = None
-        self._lock = threading.Lock()
+        self._mutex = threading.Lock()
+
+    # ring helpers (caller holds the mutex)
+    def _ring_has(self, page: int) -> bool:
+        return self._fwd[page] != self._OUT
+
+    def _ring_unlink(self, page: int):
+        nxt, prv = self._fwd[page], self._back[page]
+        self._fwd[prv], self._back[nxt] = nxt, prv
+        self._fwd[page] = self._back[page] = self._OUT
+        self._retained -= 1
+
+    def _ring_push_newest(self, page: int):
+        end = self.n_pages
+        last = self._back[end]
+        self._fwd[last], self._back[page] = page, last
+        self._fwd[page], self._back[end] = end, page
+        self._retained += 1
 
     def alloc(self) -> int:
-        with self._lock:
-            if self._free:
-                idx = self._free.pop()
-            elif self._lru:
-                idx, _ = self._lru.popitem(last=False)
-                if self.on_evict:
-                    self.on_evict(idx)
+        with self._mutex:
+            if self._unheld:
+                page = self._heap_pop(self._unheld)
+            elif self._retained:
+                page = self._fwd[self.n_pages]  # oldest retained page
+                self._ring_unlink(page)
+                if self.on_evict is not None:
+                    self.on_evict(page)
             else:
                 return -1
-            self._refs[idx] = 1
-            return idx
+            self._holders[page] = 1
+            return page
 
     def free(self, idx: int, keep_cached: bool = False):
-        with self._lock:
-            self._refs[idx] -= 1
-            if self._refs[idx] == 0:
-                if keep_cached:
-                    self._lru[idx] = None
-                else:
-                    self._free.append(idx)
+        with self._mutex:
+            self._holders[idx] -= 1
+            if self._holders[idx] != 0:
+                return
+            if keep_cached:
+                if not self._ring_has(idx):
+                    self._ring_push_newest(idx)
+            else:
+                self._heap_push(self._unheld, idx)
 
     def inc_ref(self, idx: int):
-        with self._lock:
-            self._refs[idx] += 1
-            self._lru.pop(idx, None)
+        with self._mutex:
+            self._holders[idx] += 1
+            if self._ring_has(idx):
+                self._ring_unlink(idx)
 
     def ref_count(self, idx: int) -> int:
-        with self._lock:
-            return self._refs[idx]
+        with self._mutex:
+            return self._holders[idx]
 
     def touch(self, idx: int):
-        with self._lock:
-            if idx in self._lru:
-                self._lru.move_to_end(idx)
+        with self._mutex:
+            if self._ring_has(idx):
+                self._ring_unlink(idx)
+                self._ring_push_newest(idx)
 
     def available(self) -> int:
-        with self._lock:
-            return len(self._free) + len(self._lru)
-
-
-class RadixNode:
-    __slots__ = ("parent", "children", "page_idx", "tokens", "lock_ref")
-
-    def __init__(self, parent=None, tokens=(), page_idx=None):
-        self.parent, self.tokens, self.page_idx = parent, tuple(tokens), page_idx
-        self.children: Dict[tuple, "RadixNode"] = {}
-        self.lock_ref = 0
+        with self._mutex:
+            return len(self._unheld) + self._retained
 
 
 class RadixCache:
+    """Prefix index over whole pages of exact token ids.
+
+    A cached prefix is a chain of *links*: link ``n`` is identified by ``(id of link n-1, tokens of page n)``, link
+    0 hangs off the root id 0.  All links live in one dictionary keyed by that pair, so a lookup is one hash probe per
+    page and there is no tree of node objects; ``_where`` maps a physical page back to its link for eviction.
+    Only pages that are completely filled are ever entered.  Dropping a link makes everything chained behind it
+    unreachable (those pages stay known to ``has_page`` until they are evicted themselves), which is the sharing
+    rule of ``astrai/inference/cache/strategy.py:93-173``.
+    """
+
+    ROOT = 0
+
     def __init__(self, page_size: int):
         self._page_size = page_size
-        self._root = RadixNode()
-        self._page_to_node: Dict[int, RadixNode] = {}
-        self._lock = threading.Lock()
+        self._links: Dict[tuple, int] = {}        # (previous link id, page tokens) -> link id
+        self._page_of: Dict[int, int] = {}        # link id -> physical page (absent: link exists, contents gone)
+        self._key_of: Dict[int, tuple] = {}       # link id -> its key in _links
+        self._where: Dict[int, int] = {}          # physical page -> link id
+        self._next_id = 1
+        self._mutex = threading.Lock()
 
-    def _page_tokens(self, token_ids, i):
-        return tuple(token_ids[i * self._page_size:(i + 1) * self._page_size])
+    def _span(self, token_ids, n: int) -> tuple:
+        return tuple(token_ids[n * self._page_size:(n + 1) * self._page_size])
 
     def lookup(self, token_ids: List[int]) -> List[int]:
-        with self._lock:
-            hits, node = [], self._root
-            for i in range(len(token_ids) // self._page_size):
-                node = node.children.get(self._page_tokens(token_ids, i))
-                if node is None or node.page_idx is None:
+        """Physical pages of the longest cached prefix of ``token_ids`` (whole pages only)."""
+        with self._mutex:
+            pages: List[int] = []
+            link = self.ROOT
+            for n in range(len(token_ids) // self._page_size):
+                link = self._links.get((link, self._span(token_ids, n)))
+                page = self._page_of.get(link) if link is not None else None
+                if page is None:
                     break
-                hits.append(node.page_idx)
-            return hits
+                pages.append(page)
+            return pages
+
+    def _forget_page(self, page: int, unlink: bool):
+        link = self._where.pop(page, None)
+        if link is None:
+            return
+        self._page_of.pop(link, None)
+        if unlink:
+            key = self._key_of.pop(link, None)
+            if key is not None and self._links.get(key) == link:
+                del self._links[key]
 
     def record(self, page_idx: int, token_ids: List[int], logical_page_idx: int):
-        with self._lock:
+        """Enter physical page ``page_idx`` as page number ``logical_page_idx`` of the sequence ``token_ids``."""
+        with self._mutex:
             if logical_page_idx >= len(token_ids) // self._page_size:
-                return
-            stale = self._page_to_node.pop(page_idx, None)
-            if stale is not None and stale.parent is not None:
-                stale.parent.children.pop(stale.tokens, None)
-            node = self._root
-            for i in range(logical_page_idx + 1):
-                key = self._page_tokens(token_ids, i)
-                nxt = node.children.get(key)
+                return  # that page is not full yet
+            probe = self.ROOT
+            for n in range(logical_page_idx + 1):
+                probe = self._links.get((probe, self._span(token_ids, n)))
+                if probe is None:
+                    break
+            if probe is not None and self._where.get(page_idx) == probe:
+                return  # already entered exactly there: keep the link (and whatever is chained behind it)
+            self._forget_page(page_idx, unlink=True)  # the page may have been indexed under other tokens before
+            link = self.ROOT
+            for n in range(logical_page_idx + 1):
+                key = (link, self._span(token_ids, n))
+                nxt = self._links.get(key)
                 if nxt is None:
-                    nxt = node.children[key] = RadixNode(node, key)
-                node = nxt
-            if node.page_idx is not None and node.page_idx != page_idx:
-                self._page_to_node.pop(node.page_idx, None)
-            node.page_idx = page_idx
-            self._page_to_node[page_idx] = node
+                    nxt = self._next_id
+                    self._next_id += 1
+                    self._links[key] = nxt
+                    self._key_of[nxt] = key
+                link = nxt
+            old = self._page_of.get(link)
+            if old is not None and old != page_idx:
+                self._where.pop(old, None)
+            self._page_of[link] = page_idx
+            self._where[page_idx] = link
 
     def evict(self, idx: int):
-        with self._lock:
-            node = self._page_to_node.pop(idx, None)
-            if node is None:
-                return
-            node.page_idx = None
-            if node.parent is not None:
-                node.parent.children.pop(node.tokens, None)
+        with self._mutex:
+            self._forget_page(idx, unlink=True)
 
     def has_page(self, idx: int) -> bool:
-        with self._lock:
-            return idx in self._page_to_node
+        with self._mutex:
+            return idx in self._where
 
     def release(self, pages: List[int]) -> None:
-        with self._lock:
-            for p in pages:
-                node = self._page_to_node.get(p)
-                if node is not None and node.lock_ref:
-                    node.lock_ref -= 1
+        """Kept for interface parity: pages are protected by the allocator's reference counts, not by the index."""
 
 
 class AllocationStrategy:

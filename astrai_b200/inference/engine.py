@@ -18,47 +18,80 @@ from astrai_b200.inference.scheduler import InferenceScheduler
 from astrai_b200.inference.task import STOP
 
 
+class _PromptStream:
+    """Text of one prompt's answer: pieces as they arrive and whether the end marker has been seen."""
+
+    __slots__ = ("pieces", "closed")
+
+    def __init__(self):
+        self.pieces: List[str] = []
+        self.closed = False
+
+
 class GenerateResult:
-    """Thread-safe accumulator: the scheduler thread appends text pieces, callers drain or wait for completion."""
+    """Hand-over point between the scheduler thread (producer) and the caller of ``generate`` (consumer).
+
+    Every piece goes into one arrival-ordered inbox (a ``queue.SimpleQueue`` of ``(prompt index, piece)``) that
+    streaming consumers drain, and into the per-prompt stream that blocking consumers join at the end.  A
+    countdown of open prompts releases ``wait_completion``.  Same calls as ``astrai/inference/engine.py:18-66``:
+    ``append``, ``pop_all``, ``wait``, ``wait_completion``, ``get_results``.
+    """
 
     def __init__(self, count: int = 1):
-        self._cond = threading.Condition()
-        self._event = threading.Event()
-        self.tokens: List[Tuple[int, Any]] = []
-        self.results: List[str] = [""] * count
-        self._done = [False] * count
-        self._completed, self._total = 0, count
+        import queue
+
+        self._empty = queue.Empty
+        self._inbox: "queue.SimpleQueue[Tuple[int, Any]]" = queue.SimpleQueue()
+        self._held_back: List[Tuple[int, Any]] = []  # items taken by wait() before pop_all() asked for them
+        self._streams = [_PromptStream() for _ in range(count)]
+        self._open = count
+        self._finished = threading.Event()
+        self._guard = threading.Lock()
+        if count == 0:
+            self._finished.set()
 
     def append(self, token, idx: int = 0):
-        with self._cond:
-            self.tokens.append((idx, token))
-            if token is STOP:
-                if not self._done[idx]:
-                    self._done[idx] = True
-                    self._completed += 1
-                    self._cond.notify_all()
-            else:
-                self.results[idx] += token
-            self._event.set()
+        stream = self._streams[idx]
+        if token is STOP:
+            with self._guard:
+                if not stream.closed:
+                    stream.closed = True
+                    self._open -= 1
+                    if self._open <= 0:
+                        self._finished.set()
+        else:
+            stream.pieces.append(token)
+        self._inbox.put((idx, token))
 
     def pop_all(self) -> List[Tuple[int, Any]]:
-        with self._cond:
-            out, self.tokens = self.tokens, []
-            if not out:
-                self._event.clear()
-            return out
+        with self._guard:
+            out, self._held_back = self._held_back, []
+        while True:
+            try:
+                out.append(self._inbox.get_nowait())
+            except self._empty:
+                return out
 
     def wait(self, timeout: Optional[float] = None) -> bool:
-        return self._event.wait(timeout=timeout)
+        """Block until something can be popped (True) or ``timeout`` seconds passed (False)."""
+        with self._guard:
+            if self._held_back:
+                return True
+        try:
+            item = self._inbox.get(timeout=timeout)
+        except self._empty:
+            return False
+        with self._guard:
+            self._held_back.append(item)
+        return True
 
     def wait_completion(self, timeout: float = 300.0):
-        with self._cond:
-            if not self._cond.wait_for(lambda: self._completed >= self._total, timeout=timeout):
-                raise TimeoutError(f"Generation timeout after {timeout}s ({self._completed}/{self._total} completed)")
+        if not self._finished.wait(timeout=timeout):
+            done = sum(s.closed for s in self._streams)
+            raise TimeoutError(f"generation still running after {timeout:g} s: {done} of {len(self._streams)} prompts finished")
 
     def get_results(self) -> List[str]:
-        with self._cond:
-            return list(self.results)
+        return ["".join(s.pieces) for s in self._streams]
 
 
 class InferenceEngine:

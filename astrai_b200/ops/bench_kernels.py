@@ -1,4 +1,4 @@
-"""Kernel timing harness: ``python -m astrai_b200.ops.bench_kernels {gemm,skinny,flash,fp8,quant,sample,mma,decode}``.
+"""Kernel timing harness: ``python -m astrai_b200.ops.bench_kernels {gemm,skinny,flash,fp8,quant,sample,decode}``.
 
 CUDA events on the launching stream, 3 warm-ups, median of N timed launches, a 256 MB buffer written between timed
 launches to flush the 126 MB L2.  Library kernels (cuBLAS through ``torch.matmul``, cuDNN / flash through SDPA) are
@@ -166,21 +166,6 @@ def bench_sample():
         print(f"  B={b:3d} V={v:6d}: {fused * 1e3:7.1f} | {plain * 1e3:7.1f}")
 
 
-def bench_mma():
-    from astrai_b200.ops import native
-
-    native.require()
-    like = torch.empty(1, device="cuda")
-    reps = 512
-    print("tcgen05.mma issue probe (M=128, K=16 bf16, A/B from shared memory): clk per instruction, FLOP/clk/SM")
-    for lean in (True, False):
-        for n in (64, 128, 256):
-            torch.ops.astrai_b200.mma_issue_bench(like, n, reps, lean)
-            cyc = int(torch.ops.astrai_b200.mma_issue_bench(like, n, reps, lean).item())
-            per = cyc / (reps * 4)
-            print(f"  N={n:3d} {'lean issue   ' if lean else 'rebuilt descs'}: {per:6.1f} clk  {2 * 128 * n * 16 / per:6.0f} FLOP/clk")
-
-
 def bench_decode():
     t = _timer()
     op = torch.ops.astrai_b200
@@ -212,7 +197,7 @@ def bench_decode():
 
 
 if __name__ == "__main__":
-    table = {"gemm": bench_gemm, "skinny": bench_skinny, "flash": bench_flash, "fp8": bench_fp8, "quant": bench_quant, "sample": bench_sample, "mma": bench_mma, "decode": bench_decode}
+    table = {"gemm": bench_gemm, "skinny": bench_skinny, "flash": bench_flash, "fp8": bench_fp8, "quant": bench_quant, "sample": bench_sample, "decode": bench_decode}
     which = [a for a in sys.argv[1:] if not a.startswith("--")] or list(table)
     for name in which:
         table[name]()

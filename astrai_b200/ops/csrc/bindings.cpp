@@ -750,15 +750,6 @@ Tensor int8_gemm(const Tensor& a, const Tensor& b, const Tensor& row_scale, cons
   return out;
 }
 
-Tensor mma_issue_bench(const Tensor& like, int64_t n, int64_t reps, bool lean) {
-  const c10::cuda::CUDAGuard guard(like.device());
-  Tensor out = at::zeros({1}, like.options().dtype(at::kLong));
-  count();
-  TORCH_CHECK(ab::mma_issue_bench((int)n, (int)reps, lean, reinterpret_cast<long long*>(out.data_ptr<int64_t>()), stream()) == 0,
-              "mma_issue_bench: n must be 64, 128 or 256");
-  return out;
-}
-
 // ---- mixture of experts
 std::tuple<Tensor, Tensor, Tensor, Tensor, Tensor> moe_router(const Tensor& logits, int64_t k, bool renorm) {
   CHECK_CUDA_CONTIG(logits);
@@ -1002,7 +993,6 @@ TORCH_LIBRARY(astrai_b200, m) {
   m.def("fp8_gemm_block(Tensor a, Tensor sa_t, Tensor b, Tensor sb, Tensor? bias) -> Tensor", &fp8_gemm_block);
   m.def("int8_quantize_rows(Tensor x) -> (Tensor, Tensor)", &int8_quantize_rows);
   m.def("int8_gemm(Tensor a, Tensor b, Tensor row_scale, Tensor col_scale, Tensor? bias) -> Tensor", &int8_gemm);
-  m.def("mma_issue_bench(Tensor like, int n, int reps, bool lean) -> Tensor", &mma_issue_bench);
   m.def("moe_router(Tensor logits, int k, bool renorm) -> (Tensor, Tensor, Tensor, Tensor, Tensor)", &moe_router);
   m.def("moe_plan(Tensor counts, int max_tiles) -> (Tensor, Tensor, Tensor, Tensor)", &moe_plan);
   m.def("moe_permute(Tensor x, Tensor idx, Tensor counts, Tensor offsets, Tensor(a!) cursors, int max_rows) -> (Tensor, Tensor)", &moe_permute);

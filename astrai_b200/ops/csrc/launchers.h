@@ -233,7 +233,4 @@ int gemm_skinny_splits(int N, int K, int tok);
 int gemm_skinny(const void* X, const void* W, void* Y, int M, int N, int K, long long ldx, long long ldw, long long ldy,
                 int* status, cudaStream_t st);
 
-// Issue-rate probe (bench_mma.cu): `reps` x 4 MMAs of shape 128 x n x 16; total SM clocks written to out_cycles[0].
-int mma_issue_bench(int n, int reps, bool lean, long long* out_cycles, cudaStream_t st);
-
 }  // namespace ab

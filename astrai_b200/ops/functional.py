@@ -47,21 +47,47 @@ def _tma_ok(t: Tensor) -> bool:
     )
 
 
+GEMM_REPACKS = 0  # operands copied into a TMA-addressable layout since import (a non-zero value in a hot loop is a layout bug)
+
+
+def _tma_repack(t: Tensor) -> Tensor:
+    """A copy of 2-D ``t`` that TMA can address: unit inner stride, 16-byte aligned base, row stride a multiple of 8
+    elements.  The copy keeps the logical shape (the padding lives in the row stride only)."""
+    global GEMM_REPACKS
+    GEMM_REPACKS += 1
+    rows, cols = t.shape
+    buf = torch.zeros((rows, -(-cols // 8) * 8), dtype=torch.bfloat16, device=t.device)
+    view = buf[:, :cols]
+    view.copy_(t)
+    return view
+
+
 def gemm(a: Tensor, b: Tensor, out: Optional[Tensor] = None, a_kmajor: bool = True, b_kmajor: bool = True,
          out_f32: bool = False, accumulate: bool = False) -> Tensor:
     """``D[M,N] (+)= op(A) @ op(B)`` on tcgen05.
 
     ``a`` is stored ``[M,K]`` (``a_kmajor``) or ``[K,M]``; ``b`` is stored ``[N,K]`` (``b_kmajor``) or ``[K,N]``.
-    Operands that TMA cannot address (unaligned base, row stride not a multiple of 8 elements) go through
-    ``torch.matmul`` with the same fp32-accumulate semantics.
+    On CUDA the product always runs on the tcgen05 kernel: an operand that TMA cannot address (unaligned base, row
+    stride not a multiple of 8 elements, strided inner dimension) is first copied into an addressable layout (counted
+    in ``GEMM_REPACKS``), and a non-bf16 operand is an error.  The plain-PyTorch statement below is the CPU path.
     """
-    if a.is_cuda and _tma_ok(a) and _tma_ok(b) and (out is None or out.stride(-1) == 1):
+    if a.is_cuda:
+        if a.dtype != torch.bfloat16 or b.dtype != torch.bfloat16 or a.dim() != 2 or b.dim() != 2:
+            raise TypeError("ops.gemm on CUDA takes 2-D bf16 operands")
         native.require()
+        a = a if _tma_ok(a) else _tma_repack(a)
+        b = b if _tma_ok(b) else _tma_repack(b)
+        if out is not None and out.stride(-1) != 1:
+            tmp = _ops().gemm(a, b, None, a_kmajor, b_kmajor, out_f32, False)
+            if accumulate:
+                out.add_(tmp)
+            else:
+                out.copy_(tmp)
+            return out
         return _ops().gemm(a, b, out, a_kmajor, b_kmajor, out_f32, accumulate)
     lhs = a if a_kmajor else a.t()
     rhs = b.t() if b_kmajor else b
-    res = (lhs.float() @ rhs.float()) if (out_f32 or not a.is_cuda) else (lhs @ rhs)
-    res = res.to(torch.float32 if out_f32 else a.dtype)
+    res = (lhs.float() @ rhs.float()).to(torch.float32 if out_f32 else a.dtype)
     if out is None:
         return res
     if accumulate:
