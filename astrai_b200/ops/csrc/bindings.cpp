@@ -319,7 +319,8 @@ void paged_decode_(const Tensor& q, const Tensor& k_buf, const Tensor& v_buf, co
   const int rc = ab::paged_decode(q.data_ptr(), k_buf.data_ptr(), v_buf.data_ptr(), req_to_token.data_ptr<int>(),
                                   req_pool_indices.data_ptr<int>(), (const long long*)seq_lens.data_ptr<int64_t>(),
                                   o_part.data_ptr<float>(), ml_part.data_ptr<float>(), counters.data_ptr<int>(), out.data_ptr(),
-                                  B, Hq, Hkv, D, (int)req_to_token.size(1), k_buf.size(0), (float)scale, (int)splits, max_splits, stream());
+                                  B, Hq, Hkv, D, (int)req_to_token.size(1), k_buf.size(0), (float)scale, (int)splits, max_splits,
+                                  (int)req_to_token.size(0), stream());
   TORCH_CHECK(rc == 0, "paged_decode launch failed with code ", rc, " (-1: more than 8 query heads per kv head, -2: splits, -3: head_dim not in {32,64,128,256})");
 }
 

@@ -64,15 +64,20 @@ paged_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __
                     const int* __restrict__ req_pool_indices, const long long* __restrict__ seq_lens,
                     float* __restrict__ o_part, float* __restrict__ ml_part, int* __restrict__ counters,
                     __nv_bfloat16* __restrict__ out, int n_q_heads, int n_kv_heads, int max_ctx, long long n_slots,
-                    float scale, int max_splits) {
+                    float scale, int max_splits, int table_rows) {
   constexpr int LPT = D / 8;
   constexpr int TPW = 32 / LPT;  // tokens per warp iteration
   const int kvh = blockIdx.x, b = blockIdx.y, split = blockIdx.z, splits = gridDim.z;
   constexpr int G = GT;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int sub = lane / LPT, dl = lane % LPT;  // token sub-group inside the warp, dim chunk of this lane
-  const long long len = seq_lens[b];
-  const int* table = req_to_token + (long long)req_pool_indices[b] * max_ctx;
+  // Host-supplied metadata is not trusted: a length beyond the table row is cut to the row, a request row outside the
+  // table (when the caller told us how many rows there are) attends to nothing.  Neither can read out of bounds.
+  long long len = seq_lens[b];
+  len = len < 0 ? 0 : (len > max_ctx ? (long long)max_ctx : len);
+  int table_row = req_pool_indices[b];
+  if (table_row < 0 || (table_rows > 0 && table_row >= table_rows)) table_row = 0, len = 0;
+  const int* table = req_to_token + (long long)table_row * max_ctx;
   const long long chunk = ((len + splits - 1) / splits + 15) / 16 * 16;
   const long long t_begin = (long long)split * chunk;
   const long long t_end = t_begin + chunk < len ? t_begin + chunk : len;
@@ -274,7 +279,7 @@ int paged_decode_splits(int batch, int n_kv_heads, long long max_len, int max_sp
 int paged_decode(const void* q, const void* k_buf, const void* v_buf, const int* req_to_token,
                  const int* req_pool_indices, const long long* seq_lens, float* o_part, float* ml_part, int* counters,
                  void* out, int batch, int n_q_heads, int n_kv_heads, int head_dim, int max_ctx, long long n_slots,
-                 float scale, int splits, int max_splits, cudaStream_t st) {
+                 float scale, int splits, int max_splits, int table_rows, cudaStream_t st) {
   if (batch == 0) return 0;
   if (n_q_heads % n_kv_heads || n_q_heads / n_kv_heads > MAXG) return -1;
   if (splits < 1 || splits > max_splits) return -2;
@@ -285,7 +290,7 @@ int paged_decode(const void* q, const void* k_buf, const void* v_buf, const int*
   paged_decode_kernel<DD, GG><<<grid, block, 0, st>>>((const __nv_bfloat16*)q, (const __nv_bfloat16*)k_buf,          \
                                                       (const __nv_bfloat16*)v_buf, req_to_token, req_pool_indices,   \
                                                       seq_lens, o_part, ml_part, counters, (__nv_bfloat16*)out,      \
-                                                      n_q_heads, n_kv_heads, max_ctx, n_slots, scale, max_splits)
+                                                      n_q_heads, n_kv_heads, max_ctx, n_slots, scale, max_splits, table_rows)
 #define AB_DEC_G(DD)                 \
   switch (gt) {                      \
     case 1: AB_DEC(DD, 1); break;    \

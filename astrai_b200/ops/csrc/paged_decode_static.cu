@@ -29,7 +29,12 @@ unsigned char* g_scratch_addr[kMaxDevices] = {nullptr};
 
 thread_local char t_error[256] = "";
 
-int fail(int code, const char* what, long long a = 0, long long b = 0) {
+int fail(int code, const char* what) {
+  snprintf(t_error, sizeof(t_error), "astrai_b200_paged_decode_noalloc: %s", what);
+  return code;
+}
+
+int fail(int code, const char* what, long long a, long long b) {
   snprintf(t_error, sizeof(t_error), "astrai_b200_paged_decode_noalloc: %s (%lld, limit %lld)", what, a, b);
   return code;
 }
@@ -99,7 +104,7 @@ extern "C" int astrai_b200_paged_decode_noalloc(const void* q, const void* k_buf
   const int splits = ab::paged_decode_splits(batch, n_kv_heads, max_len < 1 ? 1 : max_len, ASTRAI_B200_NOALLOC_MAX_SPLITS);
   const int lrc = ab::paged_decode(q, k_buf, v_buf, req_to_token, req_pool_indices, seq_lens, o_part, ml_part, counters,
                                    out, batch, n_q_heads, n_kv_heads, head_dim, max_ctx, n_slots, scale, splits,
-                                   ASTRAI_B200_NOALLOC_MAX_SPLITS, st);
+                                   ASTRAI_B200_NOALLOC_MAX_SPLITS, /*table_rows: not known to a raw-pointer caller*/ 0, st);
   if (lrc != 0) return fail(-13, "kernel launch was rejected", lrc, 0);
   return 0;
 }

@@ -21,6 +21,12 @@
 //   * The split counters are cleared on the given stream at the start of every call; partial results of the
 //     previous call are simply overwritten.
 //   * Nothing here calls cudaMalloc, cudaFree or any allocating library routine.
+//
+// Preconditions the function cannot check from raw pointers (the caller owns them):
+//   * every req_pool_indices[i] names an existing row of req_to_token (a negative entry makes that request attend to
+//     nothing; an entry past the last row reads memory that is not the table);
+//   * seq_lens[i] <= max_ctx is enforced on the device by cutting longer lengths down to max_ctx, and slot numbers
+//     outside [0, n_slots) found in the table are skipped, so neither can read outside the buffers.
 #pragma once
 
 #define ASTRAI_B200_NOALLOC_MAX_SPLITS 8

@@ -144,7 +144,7 @@ void check_decode(const DecodeCase& c, int* status) {
   int rc = 0;
   for (int rep = 0; rep < 2 && rc == 0; ++rep)  // twice: the counters must reset themselves
     rc = ab::paged_decode(dq, dk, dv, dtable, drows, dlens, dop, dml, dcnt, dout, B, c.Hq, c.Hkv, c.D, c.max_ctx, n_slots, scale, splits,
-                          max_splits, 0);
+                          max_splits, B, 0);
   CK(cudaDeviceSynchronize());
   std::vector<__nv_bfloat16> got(q.size());
   CK(cudaMemcpy(got.data(), dout, q.size() * 2, cudaMemcpyDeviceToHost));

@@ -62,11 +62,43 @@ class FusedAdamW(Optimizer):
                 "master": p_flat.float().clone() if (self.master_weights and p_flat.dtype != torch.float32) else None,
             }
             self._unit_state[unit.name] = st
-        else:  # states restored from a checkpoint arrive on the CPU
-            for k in ("exp_avg", "exp_avg_sq", "master"):
-                if isinstance(st.get(k), torch.Tensor) and st[k].device != p_flat.device:
-                    st[k] = st[k].to(p_flat.device)
+        elif "_layout" in st:
+            self._localize(unit, st, p_flat)
         return st
+
+    def _localize(self, unit, st: Dict[str, Any], p_flat: torch.Tensor):
+        """Turn a unit state that came out of a checkpoint into this rank's working state.
+
+        ``full`` layout: tensors cover the whole unit (written by an unsharded run, or gathered from every rank by
+        :meth:`state_dict`); a sharded run cuts its own ``[rank*S, (rank+1)*S)`` range out of it, after padding or
+        trimming the tail to this run's unit size (the padding of a unit depends on the world size).
+        ``shard`` layout: tensors are one rank's shard and are only valid for that rank of a run of that world size.
+        """
+        layout, saved = st.pop("_layout"), st.pop("_saved", (None, None))
+        eng = self._engine
+        world = eng.world_size if (eng is not None and self._sharded) else 1
+        rank = eng.rank if (eng is not None and self._sharded) else 0
+        n = p_flat.numel()
+        for k in ("exp_avg", "exp_avg_sq", "master"):
+            v = st.get(k)
+            if not isinstance(v, torch.Tensor):
+                continue
+            v = v.reshape(-1)
+            if layout == "full":
+                total = n * world
+                if v.numel() < total:
+                    v = torch.nn.functional.pad(v, (0, total - v.numel()))
+                v = v[rank * n:(rank + 1) * n] if world > 1 else v[:total]
+            else:
+                if tuple(saved) != (rank, world):
+                    raise RuntimeError(
+                        f"optimizer state of unit {unit.name} is shard {saved[0]} of {saved[1]} ranks, but this process is "
+                        f"rank {rank} of {world}: a per-rank optimizer file can only be loaded by the rank that wrote it")
+                if v.numel() != n:
+                    raise RuntimeError(f"optimizer shard of unit {unit.name} has {v.numel()} elements, expected {n}")
+            st[k] = v.to(device=p_flat.device, dtype=torch.float32, copy=True).contiguous()
+        if self.master_weights and p_flat.dtype != torch.float32 and st.get("master") is None:
+            st["master"] = p_flat.float().clone()
 
     @torch.no_grad()
     def step(self, closure=None):
@@ -128,30 +160,59 @@ class FusedAdamW(Optimizer):
         super().zero_grad(set_to_none=set_to_none)
 
     # -- (de)serialisation: unit states are stored under their unit names -------------------------------------------
-    def state_dict(self):
+    def _gathered(self, v: torch.Tensor, world: int) -> Optional[torch.Tensor]:
+        """Every rank's shard of one state tensor, concatenated in rank order (collective); kept on rank 0 only."""
+        import torch.distributed as dist
+
+        full = torch.empty(world * v.numel(), dtype=v.dtype, device=v.device)
+        dist.all_gather_into_tensor(full, v.contiguous())
+        return full.cpu() if dist.get_rank() == 0 else None
+
+    def state_dict(self, gather: bool = True):
+        """Optimizer state with the flat unit states under ``flat_units``.
+
+        Under the sharded executor on more than one rank this is a COLLECTIVE when ``gather`` is true: the moments
+        and master weights of every unit are all-gathered so that rank 0's dict holds whole units (``flat_layout =
+        "full"``), which any rank of any world size can load.  ``gather=False`` never communicates and returns this
+        rank's shards (``flat_layout = "shard"``, tagged with rank and world size) - the form used for an emergency
+        save while a peer is down, to be written to a per-rank file.  The reference saves rank 0's shard only and
+        cannot resume it on the other ranks (``astrai/parallel/executor.py:135-136``).
+        """
+        import torch.distributed as dist
+
         sd = super().state_dict()
-        sd["flat_units"] = {
-            name: {k: (v.detach().cpu() if isinstance(v, torch.Tensor) else v) for k, v in st.items()}
-            for name, st in self._unit_state.items()
-        }
+        eng = self._engine
+        world = eng.world_size if eng is not None else 1
+        multi = self._sharded and world > 1 and dist.is_available() and dist.is_initialized()
+        units = {}
+        for name, st in self._unit_state.items():
+            entry = {}
+            pending = "_layout" in st  # restored and not used yet: pass it through unchanged
+            for k, v in st.items():
+                if isinstance(v, torch.Tensor):
+                    v = self._gathered(v.detach(), world) if (multi and gather and not pending) else v.detach().cpu()
+                entry[k] = v
+            units[name] = entry
+        sd["flat_units"] = units
         sd["flat_sharded"] = self._sharded
-        if self._engine is not None:
-            sd["flat_rank"], sd["flat_world"] = self._engine.rank, self._engine.world_size
+        sd["flat_layout"] = "full" if (not multi or gather) else "shard"
+        if eng is not None:
+            sd["flat_rank"], sd["flat_world"] = eng.rank, eng.world_size
         return sd
 
     def load_state_dict(self, state_dict):
         state_dict = dict(state_dict)
         units = state_dict.pop("flat_units", {})
-        for k in ("flat_sharded", "flat_rank", "flat_world"):
-            state_dict.pop(k, None)
+        sharded = state_dict.pop("flat_sharded", False)
+        saved = (state_dict.pop("flat_rank", 0), state_dict.pop("flat_world", 1))
+        layout = state_dict.pop("flat_layout", None)
+        if layout is None:  # files written before the layout tag existed
+            layout = "shard" if (sharded and saved[1] > 1) else "full"
         super().load_state_dict(state_dict)
         for name, st in units.items():
-            cur = self._unit_state.get(name)
-            if cur is not None:
-                for k, v in st.items():
-                    if isinstance(v, torch.Tensor) and cur.get(k) is not None:
-                        cur[k].copy_(v)
-                    else:
-                        cur[k] = v
-            else:
-                self._unit_state[name] = {k: v for k, v in st.items()}
+            if st.get("_layout") is not None:  # a pass-through entry keeps its own tags
+                self._unit_state[name] = dict(st)
+                continue
+            entry = dict(st)
+            entry["_layout"], entry["_saved"] = layout, saved
+            self._unit_state[name] = entry

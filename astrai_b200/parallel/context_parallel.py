@@ -78,6 +78,22 @@ class CPContext:
         dev = self.flags.tensor.device
         self.chunk_state = torch.zeros(16, dtype=torch.int32, device=dev)   # landed flags | copy counters
         self.tile_counter = torch.zeros(8, dtype=torch.int32, device=dev)
+        self.active = True
+
+    def paused(self):
+        """Context manager: attention calls inside see no context parallelism (a model that runs on whole, unsharded
+        sequences next to the sharded one, e.g. a generation pass)."""
+        import contextlib
+
+        @contextlib.contextmanager
+        def cm():
+            prev, self.active = self.active, False
+            try:
+                yield
+            finally:
+                self.active = prev
+
+        return cm()
 
     # Buffers are keyed by shape and call parity.  Parity double-buffering is enough: a rank's launch n+1 cannot
     # finish before every peer's launch n+1 has started (it waits for their flags), i.e. before their launch n - the

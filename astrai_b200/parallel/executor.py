@@ -116,7 +116,13 @@ class AccumOptimizer:
     def param_groups(self):
         return self.optimizer.param_groups
 
-    def state_dict(self):
+    def state_dict(self, gather: bool = True):
+        """``gather=False`` asks a sharded optimizer for its local shard only (no communication)."""
+        if not gather:
+            try:
+                return self.optimizer.state_dict(gather=False)
+            except TypeError:
+                pass
         return self.optimizer.state_dict()
 
     def load_state_dict(self, d):
@@ -197,6 +203,18 @@ class BaseExecutor:
     # -- state --------------------------------------------------------------------------------------------------
     def unwrap_model(self, model: nn.Module):
         return model.state_dict()
+
+    def local_state_dict(self, model: nn.Module):
+        """The full model state from this rank's memory alone, without any communication, or ``None`` when the
+        parameters are sharded at rest.  Used for an emergency save while a peer is down."""
+        inner = getattr(model, "module", model)
+        return inner.state_dict()
+
+    communicates_every_micro_batch = False  # model-parallel executors set this: every forward pass has collectives
+
+    def before_param_use(self, p) -> None:
+        """Called by code that reads a parameter without calling the module that owns it (the fused projection + loss
+        reads ``lm_head.weight`` directly): makes the parameter's pending gather visible to the current stream."""
 
     def _gather_state_dict(self, model: nn.Module):
         sd = self.unwrap_model(model)
@@ -299,6 +317,11 @@ class FlatExecutor(BaseExecutor):
 
     def _before_unit_forward(self, unit: FlatUnit):
         pass
+
+    def before_param_use(self, p) -> None:
+        unit = getattr(p, "_flat_unit", None)
+        if unit is not None and self.engine is not None:
+            self._before_unit_forward(unit)
 
     def _unit_backward_done(self, unit: FlatUnit):
         if unit.ready:
@@ -544,6 +567,11 @@ class FSDPExecutor(FlatExecutor):
         for g in grads:
             g.mul_(coef)
         return total.item()
+
+    def local_state_dict(self, model):
+        if self.engine is None and self.use_distributed:
+            return None  # FSDP2 keeps DTensor shards: the full weights need the peers
+        return model.state_dict()  # flat runtime: bf16 parameters are replicated; pending gathers are not waited for
 
     def unwrap_model(self, model):
         if self.engine is not None or not self.use_distributed:

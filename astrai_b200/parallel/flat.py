@@ -57,6 +57,16 @@ class FlatUnit:
         return out
 
 
+def _fold_autograd_grad(p: nn.Parameter):
+    """A gradient that reached the parameter through autograd (an op without a wgrad kernel: stacked expert weights,
+    LoRA factors, biases, every op on the CPU path) is added to ``main_grad`` at once and dropped, so that the flat
+    buffers stay the single place where gradients live.  The native wgrad kernels return ``None`` to autograd and
+    never come through here."""
+    if p.grad is not None:
+        p.main_grad.add_(p.grad.to(p.main_grad.dtype).view_as(p.main_grad))
+        p.grad = None
+
+
 def _ordered_params(module: nn.Module, prefix: str):
     """named_parameters with q,k,v and gate,up made adjacent (fusable) inside attention / MLP modules."""
     seen = set()
@@ -142,6 +152,7 @@ class FlatParamEngine:
                 p.main_grad = unit.grad_buf[o:o + p.numel()].view(p.shape)
                 p._flat_unit = unit
                 p.grad = None
+                p.register_post_accumulate_grad_hook(_fold_autograd_grad)
 
     def _fuse(self, unit: FlatUnit, parts: List[nn.Parameter]):
         """A [sum(rows), cols] view over adjacent 2-D parameters (None if they are not back to back)."""

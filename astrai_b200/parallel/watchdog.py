@@ -1,12 +1,15 @@
 """Rank-failure detection on the host: per-rank heartbeats in the process group's key-value store and a watchdog thread.
 
-Every rank publishes ``(step, wall time)`` under ``hb/<rank>`` after each optimizer step; a daemon thread on every rank
-reads its peers' entries every ``interval_s`` and declares a peer dead when its heartbeat is older than ``timeout_s``
-(or when it has announced its own exit with :meth:`Heartbeat.leave`).  The training loop asks :meth:`Heartbeat.check`
-before launching the next step: a dead peer raises :class:`RankFailure` on the survivors *between* steps - with no
-kernel or collective of theirs in flight - so they can write an emergency checkpoint and exit instead of sitting in a
-collective until its timeout.  Nothing here touches a GPU; failures are injected on the host in the tests (a rank that
-stops beating, leaves, or raises).
+Liveness and progress are separate.  A daemon thread on every rank publishes ``(progress step, wall time)`` under
+``hb/<rank>`` every ``interval_s`` - so a long step, a validation pass or a checkpoint write never makes a healthy
+rank look dead - and reads its peers' entries: a peer is dead when its entry is older than ``timeout_s`` or when it
+has announced its own exit with :meth:`Heartbeat.leave`.  :meth:`Heartbeat.beat` only advances the progress step.
+The training loop asks :meth:`Heartbeat.check` before every micro-batch, and before a micro-batch that will issue
+collectives it calls :meth:`Heartbeat.rendezvous`: every rank adds itself to a store counter and waits until all
+ranks have arrived or one is known dead, so no survivor walks into a collective that a dead rank will never join.
+A dead peer raises :class:`RankFailure` on the survivors *between* launches; what follows (emergency checkpoint, exit)
+must then not communicate: see ``CheckpointCallback`` and ``Trainer``.  Nothing here touches a GPU; failures are
+injected on the host in the tests (a rank that stops beating, leaves, or raises).
 
 The reference has no heartbeat or watchdog: it relies on signal forwarding and on the process-group timeout
 (``astrai/parallel/setup.py:209-247``).
@@ -43,16 +46,22 @@ class Heartbeat:
         self._stop = threading.Event()
         self._thread: Optional[threading.Thread] = None
         self._lock = threading.Lock()
+        self._left = False
         self.step = 0
 
     # -- this rank -------------------------------------------------------------------------------------------------------
     def beat(self, step: Optional[int] = None):
-        """Publish "alive at `step`" (call once per optimizer step)."""
+        """Advance the progress step (call once per optimizer step) and publish it at once."""
         self.step = self.step + 1 if step is None else int(step)
-        self.store.set(f"{self.prefix}/{self.rank}", f"{self.step} {time.time():.3f}")
+        self._publish()
+
+    def _publish(self):
+        if not self._left:
+            self.store.set(f"{self.prefix}/{self.rank}", f"{self.step} {time.time():.3f}")
 
     def leave(self, reason: str = "left"):
         """Announce an orderly exit so that the peers stop waiting at once instead of after ``timeout_s``."""
+        self._left = True
         self.store.set(f"{self.prefix}/{self.rank}", f"-1 {time.time():.3f} {reason}")
 
     # -- the peers ---------------------------------------------------------------------------------------------------------
@@ -93,6 +102,7 @@ class Heartbeat:
     def _loop(self):
         while not self._stop.wait(self.interval_s):
             try:
+                self._publish()  # liveness: this process is up, whatever its main thread is busy with
                 self.scan()
             except Exception as exc:  # noqa: BLE001
                 logger.warning("heartbeat scan failed: %s", exc)
@@ -108,6 +118,10 @@ class Heartbeat:
         if self._thread is not None:
             self._thread.join(timeout=2 * self.interval_s + 1)
 
+    def dead_ranks(self) -> List[int]:
+        with self._lock:
+            return sorted(self._dead)
+
     def check(self):
         """Raise :class:`RankFailure` if a peer is known to be dead.  Call between steps, before the next launch."""
         with self._lock:
@@ -116,23 +130,59 @@ class Heartbeat:
             ranks = sorted(dead)
             raise RankFailure(ranks, "; ".join(dead[r] for r in ranks))
 
+    def rendezvous(self, tag: str, poll_s: float = 0.002):
+        """Host-side agreement before a launch that communicates: returns once every rank has reached ``tag``, raises
+        :class:`RankFailure` as soon as a peer is known dead instead.  One store add plus a few reads per call."""
+        key = f"{self.prefix}/rv/{tag}"
+        arrived = self.store.add(key, 1)
+        waited = 0.0
+        while arrived < self.world_size:
+            self.check()
+            time.sleep(poll_s)
+            waited += poll_s
+            if waited >= self.interval_s:  # do not rely on the thread alone while blocked here
+                waited = 0.0
+                self.scan()
+            arrived = self.store.add(key, 0)
+        self.check()
+
 
 class HeartbeatCallback:
-    """Trainer callback: beat after every optimizer step, check before every micro-batch, leave on exit / error.
-    A detected failure requests a stop (emergency checkpoint through the trainer's usual path) and re-raises."""
+    """Trainer callback: progress beat after every optimizer step, failure check before every micro-batch, host-side
+    rendezvous before a micro-batch that communicates, orderly leave on exit / error.
 
-    def __init__(self, timeout_s: float = 60.0, interval_s: float = 1.0):
-        self.timeout_s, self.interval_s = timeout_s, interval_s
+    On a failure the context gets ``failed_ranks`` (the checkpoint callback and the trainer then avoid every collective),
+    a stop is requested and :class:`RankFailure` is raised from ``on_batch_begin``.
+    """
+
+    def __init__(self, timeout_s: float = 60.0, interval_s: float = 1.0, every_micro_batch: bool = False):
+        self.timeout_s, self.interval_s, self.every_micro_batch = timeout_s, interval_s, every_micro_batch
         self.hb: Optional[Heartbeat] = None
+        self._micro = 0
+
+    def _failed(self, context, ranks):
+        context.failed_ranks = sorted(set(getattr(context, "failed_ranks", None) or []) | set(ranks))
+        context.request_stop()
 
     def on_train_begin(self, context):
         if dist.is_available() and dist.is_initialized() and dist.get_world_size() > 1:
             self.hb = Heartbeat(dist.get_rank(), dist.get_world_size(), timeout_s=self.timeout_s, interval_s=self.interval_s,
-                                on_failure=lambda ranks: context.request_stop()).start()
+                                on_failure=lambda ranks: self._failed(context, ranks)).start()
 
     def on_batch_begin(self, context):
-        if self.hb is not None:
+        if self.hb is None:
+            return
+        self._micro += 1
+        try:
             self.hb.check()
+            ex = context.executor
+            # data-parallel modes communicate on the micro-batch that closes an accumulation window only; model-parallel
+            # modes (tp / cp / ep / pp) in every forward pass
+            if self.every_micro_batch or ex.sync_gradients or getattr(ex, "communicates_every_micro_batch", False):
+                self.hb.rendezvous(str(self._micro))
+        except RankFailure as exc:
+            self._failed(context, exc.ranks)
+            raise
 
     def on_optimizer_step(self, context):
         if self.hb is not None:

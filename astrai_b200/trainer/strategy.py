@@ -73,6 +73,16 @@ def _fused_head(model) -> Optional[nn.Module]:
     return None
 
 
+def _head_weight(inner) -> Tensor:
+    """``lm_head.weight`` for a fused projection + loss.  The ``lm_head`` module itself is not called on that path, so its
+    forward pre-hook (where a sharded executor waits for the parameter's all-gather) never fires: ask the executor."""
+    w = inner.lm_head.weight
+    ex = getattr(inner, "_flat_executor", None)
+    if ex is not None:
+        ex.before_param_use(w)
+    return w
+
+
 def token_logprobs(model, input_ids: Tensor, input_mask: Optional[Tensor], position_ids: Optional[Tensor] = None):
     """Log-probability of ``input_ids[:, 1:]`` under the model, shape ``[B, S-1]`` fp32, plus the forward outputs."""
     ids_in, ids_out = input_ids[:, :-1], input_ids[:, 1:]
@@ -81,7 +91,7 @@ def token_logprobs(model, input_ids: Tensor, input_mask: Optional[Tensor], posit
     inner = _fused_head(model)
     if inner is not None and ids_in.is_cuda:
         out = model(ids_in, input_mask, return_logits=False)
-        lp = ops.linear_token_logprobs(out["hidden_states"], inner.lm_head.weight, ids_out)
+        lp = ops.linear_token_logprobs(out["hidden_states"], _head_weight(inner), ids_out)
     else:
         out = model(ids_in, input_mask)
         lp = torch.log_softmax(out["logits"].float(), dim=-1).gather(-1, ids_out.unsqueeze(-1)).squeeze(-1)
@@ -211,7 +221,7 @@ class _TokenCEStrategy(BaseStrategy):
         inner = _fused_head(self.model)
         if inner is not None and input_ids.is_cuda:
             out = self.model(input_ids=input_ids, return_logits=False, **fwd)
-            loss = ops.linear_cross_entropy(out["hidden_states"], inner.lm_head.weight, targets,
+            loss = ops.linear_cross_entropy(out["hidden_states"], _head_weight(inner), targets,
                                             self.label_smoothing, ignore_index)
         else:
             out = self.model(input_ids=input_ids, **fwd)

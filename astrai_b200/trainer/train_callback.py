@@ -104,7 +104,51 @@ class CheckpointCallback(TrainCallback):
                 out[name] = obj.state_dict()
         return out
 
+    def _save_without_peers(self, context, dead: List[int]):
+        """Emergency save while ``dead`` ranks are gone: nothing here may communicate (no barrier, no gather).
+
+        The lowest surviving rank writes the usual directory from its local copy of the weights (every executor whose
+        parameters are replicated or locally complete can give one; a torch-FSDP2 model cannot, its save is skipped)
+        with ``emergency`` / ``failed_ranks`` in ``meta.json``.  A sharded optimizer is not gathered: every survivor
+        writes its own shard to ``<dir>.shards/optimizer.rank<r>.pt`` (the dead ranks' shards are lost, so the directory
+        holds no ``optimizer.pt`` and does not count as complete for an automatic resume; the weights are intact).
+        """
+        self.last_ckpt_step = context.optimizer_step
+        rank, world = get_rank(), context.world_size
+        survivors = [r for r in range(world) if r not in set(dead)]
+        path = os.path.join(self.save_dir, f"epoch_{context.epoch}_step_{context.optimizer_step}")
+        extra = {}
+        if not self.weight_only:
+            sched = getattr(context, "scheduler", None)
+            if sched:
+                extra["scheduler"] = sched.state_dict()
+            opt = getattr(context, "optimizer", None)
+            if opt:
+                try:
+                    osd = opt.state_dict(gather=False)
+                except TypeError:
+                    osd = opt.state_dict()
+                if isinstance(osd, dict) and osd.get("flat_layout") == "shard":
+                    shard_dir = Path(path + ".shards")
+                    shard_dir.mkdir(parents=True, exist_ok=True)
+                    torch.save(osd, shard_dir / f"optimizer.rank{rank}.pt")
+                else:
+                    extra["optimizer"] = osd
+        if not survivors or rank != survivors[0]:
+            return
+        state_dict = context.executor.local_state_dict(context.model)
+        if state_dict is None:
+            logger.error("emergency checkpoint: this executor cannot produce the weights without its peers; nothing written")
+            return
+        meta = dict(context.config.to_dict(), emergency=True, failed_ranks=sorted(dead))
+        context.checkpoint = Checkpoint(state_dict=state_dict, epoch=context.epoch, consumed_samples=context.consumed_samples,
+                                        config=context.model_config, extra=extra, meta=meta)
+        context.checkpoint.save(path)
+
     def _save(self, context):
+        dead = getattr(context, "failed_ranks", None)
+        if dead:
+            return self._save_without_peers(context, dead)
         self.last_ckpt_step = context.optimizer_step
         extra = {} if self.weight_only else self.save_extra_fn(context)  # collective for sharded optimizers
         with context.executor.checkpoint_context(context.model) as state_dict:

@@ -112,7 +112,8 @@ class Trainer:
             raise
         finally:
             self._fire("on_train_end", context)
-            if ex.use_distributed and dist.is_initialized():
+            # a barrier would wait for a rank that is known to be gone
+            if ex.use_distributed and dist.is_initialized() and not getattr(context, "failed_ranks", None):
                 dist.barrier()
             unregister_signal_handlers()
         return context

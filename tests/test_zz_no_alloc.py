@@ -5,7 +5,10 @@ already holds the whole device, or a process that bans the CUDA allocator after 
 exports one plain-C function whose scratch lives in a fixed ``__device__`` array inside the shared object.  The
 test loads the exported symbol with ``ctypes`` (no torch binding in between), runs it twice in a row on the same
 inputs - the second call reuses whatever the first left in the shared scratch - and compares each result with
-the regular torch op, which takes caller-allocated scratch tensors.
+the regular torch op, which takes caller-allocated scratch tensors, and with a plain fp32 PyTorch statement of
+decode attention.  It also checks what the entry point is for: the free device memory reported by the driver is the
+same before and after a call (nothing was allocated), and a sequence length larger than the table row is cut to the
+row instead of reading past it.
 
 This file sorts last so that a run that stops at the first failure has already run every other test.
 """
@@ -61,6 +64,21 @@ def _regular(q, k_buf, v_buf, table, rows, seq, splits):
     return out
 
 
+def _fp32_statement(q, k_buf, v_buf, table, rows, seq):
+    """softmax(q k^T / sqrt(d)) v over each request's cached tokens, in fp32, one request at a time."""
+    b, hq, hd = q.shape
+    hkv = k_buf.shape[1]
+    out = torch.zeros(b, hq, hd, device=q.device)
+    for i in range(b):
+        n = min(int(seq[i]), table.shape[1])
+        slots = table[int(rows[i]), :n].long()
+        k = k_buf[slots].float().repeat_interleave(hq // hkv, dim=1)  # [n, hq, hd]
+        v = v_buf[slots].float().repeat_interleave(hq // hkv, dim=1)
+        p = torch.softmax(torch.einsum("hd,nhd->hn", q[i].float(), k) * hd ** -0.5, dim=-1)
+        out[i] = torch.einsum("hn,nhd->hd", p, v)
+    return out
+
+
 @pytest.mark.parametrize("hd,hq,hkv,lens", [(128, 16, 4, [1400, 37, 512]), (64, 8, 8, [300, 1])])
 def test_noalloc_entry_matches_regular_entry_twice(hd, hq, hkv, lens):
     fn, err = _symbols()
@@ -76,6 +94,37 @@ def test_noalloc_entry_matches_regular_entry_twice(hd, hq, hkv, lens):
         torch.cuda.synchronize()
         assert torch.isfinite(out.float()).all(), call
         assert (out.float() - ref.float()).abs().max().item() < 2e-2, call
+        assert (out.float() - _fp32_statement(q, k_buf, v_buf, table, rows, seq)).abs().max().item() < 2e-2, call
+
+
+def test_noalloc_entry_leaves_free_memory_unchanged():
+    fn, err = _symbols()
+    q, k_buf, v_buf, table, rows, seq = _case(128, 16, 4, [900, 64], 31)
+    out = torch.empty_like(q)
+    stream = torch.cuda.current_stream().cuda_stream
+    args = (q.data_ptr(), k_buf.data_ptr(), v_buf.data_ptr(), table.data_ptr(), rows.data_ptr(), seq.data_ptr(),
+            out.data_ptr(), 2, 16, 4, 128, table.shape[1], k_buf.shape[0], 900, 128 ** -0.5, stream)
+    assert fn(*args) == 0, err().decode()  # the first call on a device resolves the scratch address
+    torch.cuda.synchronize()
+    free_before, _ = torch.cuda.mem_get_info()
+    assert fn(*args) == 0, err().decode()
+    torch.cuda.synchronize()
+    free_after, _ = torch.cuda.mem_get_info()
+    assert free_after == free_before  # the driver handed out nothing during the call
+
+
+def test_length_beyond_the_table_row_is_cut_to_the_row():
+    fn, err = _symbols()
+    q, k_buf, v_buf, table, rows, seq = _case(128, 16, 4, [1536, 40], 32)  # request 0 fills its whole row
+    too_long = seq.clone()
+    too_long[0] = 5000  # claims more tokens than a row holds
+    out = torch.full_like(q, float("nan"))
+    rc = fn(q.data_ptr(), k_buf.data_ptr(), v_buf.data_ptr(), table.data_ptr(), rows.data_ptr(), too_long.data_ptr(),
+            out.data_ptr(), 2, 16, 4, 128, table.shape[1], k_buf.shape[0], 5000, 128 ** -0.5,
+            torch.cuda.current_stream().cuda_stream)
+    assert rc == 0, err().decode()
+    torch.cuda.synchronize()
+    assert (out.float() - _fp32_statement(q, k_buf, v_buf, table, rows, seq)).abs().max().item() < 2e-2
 
 
 def test_noalloc_entry_rejects_oversize():
