@@ -80,11 +80,10 @@ class TrainConfig(BaseConfig):
     reward_model_fn: Optional[Callable] = None
     executor_kwargs: Dict[str, Any] = field(default_factory=dict)
     strategy_kwargs: Dict[str, Any] = field(default_factory=dict)
-    sync_loss_every: int = 1
-    """Read the loss back to the host every this many micro-batches (1 = reference behaviour,
-    ``trainer.py:86``); larger values remove the per-micro-batch device->host sync."""
     heartbeat_timeout_s: Optional[float] = None
-    """If set, a watchdog thread flags ranks whose step heartbeat is older than this."""
+    """If set (multi-rank runs), the trainer adds the ``heartbeat`` callback: a rank whose liveness entry in the
+    process group's store is older than this many seconds is declared dead and the survivors stop between steps."""
+    heartbeat_interval_s: float = 1.0
 
     @field_validator("strategy")
     def _c_strategy(cls, v):
@@ -108,7 +107,7 @@ class TrainConfig(BaseConfig):
 
     @field_validator(
         "n_epoch", "batch_per_device", "grad_accum_steps", "ckpt_interval", "val_step",
-        "rollout_interval", "rollout_max_tokens", "tp_size", "cp_size", "ep_size", "sync_loss_every",
+        "rollout_interval", "rollout_max_tokens", "tp_size", "cp_size", "ep_size",
     )
     def _c_positive(cls, v):
         if v <= 0:

@@ -39,7 +39,11 @@ class Trainer:
         c = self.train_config
         # Clipping runs first so that the metric log and the progress bar of a step show that step's gradient norm
         # (the reference lists it last, which makes the logged norm lag one step behind).
-        return [
+        watch = []
+        if c.heartbeat_timeout_s and c.nprocs > 1:
+            # first in the list: its failure check runs before any other callback of a micro-batch
+            watch = [CallbackFactory.create("heartbeat", timeout_s=c.heartbeat_timeout_s, interval_s=c.heartbeat_interval_s)]
+        return watch + [
             CallbackFactory.create("gradient_checkpointing", modules=c.gradient_checkpointing_modules),
             CallbackFactory.create("gradient_clipping", c.max_grad_norm),
             CallbackFactory.create("checkpoint", c.ckpt_dir, c.ckpt_interval),

@@ -105,3 +105,18 @@ def test_fused_nvls_fsdp_matches_nccl_fsdp(tmp_path):
     for x, y in zip(a["norms"], b["norms"]):
         assert abs(x - y) / max(abs(x), 1e-6) < 2e-2, (a, b)
     assert abs(a["checksum"] - b["checksum"]) / a["checksum"] < 1e-3
+
+
+@pytest.mark.parametrize("extra", [[], ["--untied"]])
+def test_fused_fsdp_save_and_resume_matches_uninterrupted_run(tmp_path, extra):
+    """Two GPUs, fused peer-memory FSDP: train, save (optimizer shards gathered), rebuild, load, train on; the losses
+    of the steps after the resume and the final parameters must equal the uninterrupted run."""
+    _need_gpus(2)
+    out = str(tmp_path / "resume.json")
+    _torchrun(2, os.path.join(ROOT, "tests", "workers", "fsdp_resume.py"),
+              ["--out", out, "--ckpt", str(tmp_path / "ckpt"), "--device", "cuda", "--comm", "p2p", *extra], 29700 + len(extra))
+    res = json.load(open(out))
+    assert res["layout"] == "full"
+    for x, y in zip(res["a"], res["b"]):
+        assert abs(x - y) < 2e-2, res
+    assert abs(res["a_sum"] - res["b_sum"]) / res["a_sum"] < 1e-3, res

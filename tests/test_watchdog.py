@@ -59,3 +59,33 @@ def test_survivors_stop_between_steps_when_a_rank_goes_away(tmp_path, mode):
         assert res[r]["detected"] == [1], res  # found on the host, before the next collective was issued
         assert res[r]["steps"] == 3
         assert res[r]["seconds"] < (1.5 if mode == "leave" else 6.0)
+
+
+@pytest.mark.parametrize("mode", ["fsdp", "ddp"])
+def test_survivors_write_an_emergency_checkpoint_without_collectives(tmp_path, mode):
+    """Three gloo ranks train through the real Trainer; rank 1 exits silently between steps.  The survivors must
+    return within a bound (no barrier, no gather that waits for the dead rank) and leave the weights on disk."""
+    out, ckpt = str(tmp_path / "res"), str(tmp_path / "ckpt")
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=3", "--master-addr", "127.0.0.1",
+           "--master-port", "29793" if mode == "fsdp" else "29794", os.path.join(ROOT, "tests", "workers", "rank_loss_trainer.py"),
+           "--out", out, "--ckpt", ckpt, "--mode", mode]
+    proc = subprocess.run(cmd, env=dict(os.environ, MASTER_ADDR="127.0.0.1", OMP_NUM_THREADS="1"), capture_output=True, text=True,
+                          timeout=300, cwd=ROOT)
+    assert proc.returncode == 0, proc.stdout[-2000:] + proc.stderr[-3000:]
+    gone = float(open(out + ".gone").read())
+    for r in (0, 2):
+        res = json.load(open(f"{out}.{r}"))
+        assert 1 in res["failure"], res
+        assert res["returned_at"] - gone < 20.0, res  # heartbeat timeout 1.5 s + save; far below any process-group timeout
+    dirs = [d for d in os.listdir(ckpt) if d.startswith("epoch_") and not d.endswith(".shards")]
+    assert len(dirs) == 1
+    root = os.path.join(ckpt, dirs[0])
+    meta = json.load(open(os.path.join(root, "meta.json")))
+    assert meta["emergency"] is True and 1 in meta["failed_ranks"]
+    assert os.path.getsize(os.path.join(root, "model.safetensors")) > 0
+    if mode == "fsdp":  # sharded optimizer state: one file per survivor, none gathered
+        shards = sorted(os.listdir(root + ".shards"))
+        assert shards == ["optimizer.rank0.pt", "optimizer.rank2.pt"]
+        assert not os.path.exists(os.path.join(root, "optimizer.pt"))
+    else:
+        assert os.path.getsize(os.path.join(root, "optimizer.pt")) > 0
