@@ -16,10 +16,14 @@ from torch.utils.data import Sampler
 
 class RDSampler(Sampler[int]):
     def __init__(self, data_source, start_epoch: int = 0, start_iter: int = 0, seed: int = 42, drop_last: bool = False,
-                 shuffle: bool = True, process_group: Optional[dist.ProcessGroup] = None):
+                 shuffle: bool = True, process_group: Optional[dist.ProcessGroup] = None, partition=None):
+        """``partition=(index, count)`` names this rank's share explicitly (ranks of one model-parallel block pass the
+        same pair and so draw the same samples); otherwise the share follows the process group."""
         self.epoch, self.seed, self.drop_last, self.shuffle = start_epoch, seed, drop_last, shuffle
         self.num_samples = len(data_source)
-        if process_group is not None:
+        if partition is not None:
+            self.rank, self.num_replicas = int(partition[0]), int(partition[1])
+        elif process_group is not None:
             self.rank, self.num_replicas = dist.get_rank(process_group), dist.get_world_size(process_group)
         elif dist.is_available() and dist.is_initialized():
             self.rank, self.num_replicas = dist.get_rank(), dist.get_world_size()

@@ -75,7 +75,7 @@ class DeepSeekMoE(nn.Module):
         std = 0.02 / (2 * n_layers * moe_scale) ** 0.5
         self.shared_experts = nn.ModuleList(MLP(dim, shared_ffn, std) for _ in range(self.n_shared_experts))
         self.routed_experts = nn.ModuleList(MLP(dim, expert_ffn, std) for _ in range(n_routed_experts))
-        self.expert_parallel = None  # set by the EP executor: object with dispatch()/combine()
+        self.expert_parallel = False  # set by the expert-parallel executor once `routed_experts` is its stacked, sharded form
         self.stacked_experts = None  # set for serving: ([E, 2F, D] gate|up, [E, D, F] down) that the experts' weights view
 
     # ---- routing --------------------------------------------------------------------------------------------
@@ -83,7 +83,7 @@ class DeepSeekMoE(nn.Module):
         from astrai_b200.ops import moe
 
         ffn = self.routed_experts[0].gate.weight.shape[0]
-        return (self.expert_parallel is None and moe.available(x, self.n_routed_experts, self.n_activated_experts)
+        return (not self.expert_parallel and moe.available(x, self.n_routed_experts, self.n_activated_experts)
                 and ffn % 64 == 0 and all(type(m.gate).__name__ == "Linear" for m in self.routed_experts))
 
     def _forward_kernels(self, x: Tensor, with_aux: bool):
@@ -138,8 +138,6 @@ class DeepSeekMoE(nn.Module):
     def _routed(self, x: Tensor, weights: Tensor, idx: Tensor) -> Tensor:
         n, _ = x.shape
         k, e = self.n_activated_experts, self.n_routed_experts
-        if self.expert_parallel is not None:
-            return self.expert_parallel(self, x, weights, idx)
         flat = idx.reshape(-1)
         order = torch.argsort(flat, stable=True)
         counts = torch.bincount(flat, minlength=e)
@@ -150,11 +148,30 @@ class DeepSeekMoE(nn.Module):
         out.index_add_(0, src_tok, y)
         return out
 
+    def _forward_expert_parallel(self, x: Tensor, with_aux: bool):
+        """Local routing, then the routed experts of every rank of the expert-parallel group (tokens travel to the
+        experts' owners and back inside ``self.routed_experts``).  The auxiliary loss uses this rank's tokens."""
+        from astrai_b200.ops import moe
+
+        e, k = self.n_routed_experts, self.n_activated_experts
+        if moe.available(x, e, k):
+            probs, idx, weights, counts, psum = moe.route(self.router(x), k, self.norm_topk_prob)
+            aux = stats = None
+            if with_aux:
+                aux = e * ((counts.float() / idx.numel()) * (psum / x.shape[0])).sum()
+                stats = {"probs": probs.detach(), "topk_indices": idx}
+        else:
+            weights, idx, aux, stats = self.route(x, with_aux)
+            counts = torch.bincount(idx.reshape(-1), minlength=e).to(torch.int32)
+        return self.routed_experts(x, idx, weights, counts), aux, stats
+
     def forward(self, x: Tensor) -> FFNOutput:
         with_aux = self.training and torch.is_grad_enabled()
         shape = x.shape
         flat = x.reshape(-1, shape[-1])
-        if self._use_kernels(flat):
+        if self.expert_parallel:
+            out, aux, stats = self._forward_expert_parallel(flat, with_aux)
+        elif self._use_kernels(flat):
             out, aux, stats = self._forward_kernels(flat, with_aux)
         else:
             weights, idx, aux, stats = self.route(flat, with_aux)

@@ -49,12 +49,13 @@ def _sdpa_ctx():
 def dense_attention(q: Tensor, k: Tensor, v: Tensor, mask: Optional[Tensor] = None, causal: bool = False,
                     scale: Optional[float] = None) -> Tensor:
     """Softmax attention with GQA head sharing; returns ``[B,S,Hq,Dv]``."""
-    if not q.is_cuda:
-        return reference.attention(q, k, v, mask, causal, scale)
     from astrai_b200.parallel import context_parallel as cpar
 
     cp = cpar.get_context()
-    if cp is not None and cp.active:
+    if cp is None or not cp.active:
+        if not q.is_cuda:
+            return reference.attention(q, k, v, mask, causal, scale)
+    else:
         # Sequence-sharded training: the local rows are this rank's zig-zag share of the sequence and the keys of the
         # other ranks are fetched inside the attention kernel.  Only plain causal attention is sharded: a call with a
         # mask (packed-document, padding) would silently attend to the local keys only, so it is an error.
@@ -62,7 +63,7 @@ def dense_attention(q: Tensor, k: Tensor, v: Tensor, mask: Optional[Tensor] = No
             raise RuntimeError("context parallelism is on: only causal attention without a mask is sequence-sharded "
                                "(use the seq strategy, or switch context parallelism off for this call with "
                                "CPContext.paused())")
-        if not cpar.supported(q, k, v):
+        if q.is_cuda and not cpar.supported(q, k, v):
             raise RuntimeError("context parallelism is on, but this attention call is outside what the sharded "
                                "kernels take (bf16, head_dim 64 / 128, local length a multiple of 256)")
         return cpar.ring_attention(q, k, v, scale=scale, ctx=cp, comm=getattr(cp, "comm", "p2p"))

@@ -71,14 +71,17 @@ class CPContext:
             raise ValueError(f"context parallel world size must be in 2..{symm.MAX_RANKS}")
         self.arena, self.rank, self.world, self.group, self.comm = arena, rank, world, group, comm
         self.timeout_s, self.n_copy_ctas = float(timeout_s), int(n_copy_ctas)
-        self.flags = arena.alloc_flags(1)
+        self.active = True
         self._src: Dict[Tuple[int, int, int, int], symm.SymmBuffer] = {}
         self._stage: Dict[Tuple[int, int, int, int], symm.SymmBuffer] = {}
         self._epoch = {"fwd": 0, "bwd": 0}
+        if arena is None:  # no peer memory (CPU ranks): only the collective statement of the op is available
+            self.comm = "nccl"
+            return
+        self.flags = arena.alloc_flags(1)
         dev = self.flags.tensor.device
         self.chunk_state = torch.zeros(16, dtype=torch.int32, device=dev)   # landed flags | copy counters
         self.tile_counter = torch.zeros(8, dtype=torch.int32, device=dev)
-        self.active = True
 
     def paused(self):
         """Context manager: attention calls inside see no context parallelism (a model that runs on whole, unsharded
@@ -139,6 +142,47 @@ def init_context_parallel(arena_bytes: int, timeout_s: float = 60.0, group=None,
     ctx = CPContext(arena, arena.rank, arena.world_size, timeout_s=timeout_s, n_copy_ctas=n_copy_ctas, group=group)
     set_context(ctx)
     return ctx
+
+
+def init_context_parallel_group(group=None) -> CPContext:
+    """Context without peer memory (CPU / Gloo ranks, or a baseline run): attention gathers keys with collectives."""
+    rank, world = dist.get_rank(group), dist.get_world_size(group)
+    ctx = CPContext(None, rank, world, group=group, comm="nccl")
+    set_context(ctx)
+    return ctx
+
+
+class _GatherSequence(torch.autograd.Function):
+    """Local zig-zag rows ``[B, 2c, H, D]`` -> the whole sequence ``[B, S, H, D]`` on every rank; the backward pass sums
+    the ranks' gradients of the whole sequence and keeps the local rows."""
+
+    @staticmethod
+    def forward(ctx, x: Tensor, world: int, rank: int, group):
+        ctx.world, ctx.rank, ctx.group = world, rank, group
+        parts = [torch.empty_like(x) for _ in range(world)]
+        dist.all_gather(parts, x.contiguous(), group=group)
+        return zigzag_merge(parts, dim=1)
+
+    @staticmethod
+    def backward(ctx, g: Tensor):
+        g = g.contiguous().clone()
+        dist.all_reduce(g, group=ctx.group)
+        return zigzag_split(g, ctx.world, ctx.rank, dim=1), None, None, None
+
+
+def _ring_attention_plain(q: Tensor, k: Tensor, v: Tensor, cp: CPContext, scale: float) -> Tensor:
+    """Plain PyTorch statement of the sharded op (any device): gather K / V, mask by global positions."""
+    b, two_c, hq, d = q.shape
+    s = two_c * cp.world
+    k_full = _GatherSequence.apply(k, cp.world, cp.rank, cp.group)
+    v_full = _GatherSequence.apply(v, cp.world, cp.rank, cp.group)
+    g = hq // k.size(2)
+    kf, vf = k_full.repeat_interleave(g, dim=2), v_full.repeat_interleave(g, dim=2)
+    q_pos = zigzag_positions(s, cp.world, cp.rank, device=q.device)
+    mask = q_pos[:, None] >= torch.arange(s, device=q.device)[None, :]
+    out = torch.nn.functional.scaled_dot_product_attention(q.transpose(1, 2), kf.transpose(1, 2), vf.transpose(1, 2),
+                                                           attn_mask=mask, scale=scale)
+    return out.transpose(1, 2)
 
 
 # --------------------------------------------------------------------------- the op
@@ -239,6 +283,10 @@ def ring_attention(q: Tensor, k: Tensor, v: Tensor, scale: Optional[float] = Non
         raise RuntimeError("ring_attention needs a context: call init_context_parallel() first")
     if comm not in ("p2p", "nccl"):
         raise ValueError(f"unknown comm {comm!r}")
+    if not q.is_cuda or cp.arena is None and not supported(q, k, v):
+        return _ring_attention_plain(q, k, v, cp, float(scale) if scale is not None else 1.0 / math.sqrt(q.size(3)))
+    if cp.arena is None:
+        comm = "nccl"
     if not supported(q, k, v):
         raise ValueError("ring_attention: bf16 CUDA tensors [B, 2c, H, D] with D in {64, 128} and c a multiple of 128")
     scale = float(scale) if scale is not None else 1.0 / math.sqrt(q.size(3))

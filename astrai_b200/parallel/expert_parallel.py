@@ -303,3 +303,132 @@ def moe_reference(x_parts, router: Tensor, gate_up: Tensor, down: Tensor, top_k:
             out[rows] += (w[rows] * sel[rows]).sum(-1, keepdim=True) * (act @ down[e].float().t())
         outs.append(out)
     return outs
+
+
+# --------------------------------------------------------------------------- collective arm (baseline, and the CPU path)
+def _supports_all_to_all(group) -> bool:
+    import torch.distributed as dist
+
+    return dist.get_backend(group) != "gloo"
+
+
+class _AllToAllRows(torch.autograd.Function):
+    """Rows ``x`` cut into one segment per destination rank (``send``) travel to their ranks; the result is the segments
+    received from every rank in rank order (``recv``).  The backward pass is the same exchange with the roles swapped."""
+
+    @staticmethod
+    def forward(ctx, x: Tensor, send, recv, group, seg_cap: int):
+        ctx.send, ctx.recv, ctx.group, ctx.seg_cap = list(send), list(recv), group, seg_cap
+        return _exchange_rows(x, ctx.send, ctx.recv, group, seg_cap)
+
+    @staticmethod
+    def backward(ctx, g: Tensor):
+        return _exchange_rows(g.contiguous(), ctx.recv, ctx.send, ctx.group, ctx.seg_cap), None, None, None, None
+
+
+def _exchange_rows(x: Tensor, send, recv, group, seg_cap: int) -> Tensor:
+    import torch.distributed as dist
+
+    out = torch.empty((sum(recv),) + tuple(x.shape[1:]), dtype=x.dtype, device=x.device)
+    if _supports_all_to_all(group):
+        dist.all_to_all_single(out, x.contiguous(), output_split_sizes=list(recv), input_split_sizes=list(send), group=group)
+        return out
+    # Gloo has no all-to-all: every rank publishes its padded segments and each reader cuts out what was meant for it.
+    world, me = dist.get_world_size(group), dist.get_rank(group)
+    padded = torch.zeros((world, seg_cap) + tuple(x.shape[1:]), dtype=x.dtype, device=x.device)
+    at = 0
+    for d, n in enumerate(send):
+        padded[d, :n] = x[at:at + n]
+        at += n
+    everything = torch.empty((world * world,) + tuple(padded.shape[1:]), dtype=x.dtype, device=x.device)
+    dist.all_gather_into_tensor(everything, padded, group=group)
+    everything = everything.view((world,) + tuple(padded.shape))
+    at = 0
+    for s, n in enumerate(recv):
+        out[at:at + n] = everything[s, me, :n]
+        at += n
+    return out
+
+
+def ep_experts_collective(x: Tensor, idx: Tensor, weights: Tensor, counts: Tensor, w_gate_up: Tensor, w_down: Tensor,
+                          group=None) -> Tensor:
+    """The same function as :func:`ep_experts` built from library collectives: counts all-gather, token all-to-all,
+    one GEMM pair per local expert, all-to-all back, weighted sum.  Split sizes are read back to the host (one sync per
+    call), which the fused path avoids.  It is the arm the fused kernels are measured against, and the CPU path."""
+    import torch.distributed as dist
+    from astrai_b200 import ops
+
+    world, me = dist.get_world_size(group), dist.get_rank(group)
+    t, h = x.shape
+    k, n_experts = idx.shape[1], counts.numel()
+    local = n_experts // world
+    all_counts = torch.empty(world * n_experts, dtype=counts.dtype, device=counts.device)
+    dist.all_gather_into_tensor(all_counts, counts.contiguous(), group=group)
+    table = all_counts.view(world, world, local).cpu()               # [source rank, owner rank, local expert]
+    send = table[me].sum(-1).tolist()                                # rows this rank sends to each owner
+    recv = table[:, me].sum(-1).tolist()                             # rows this rank receives from each source
+    seg_cap = int(table.sum(-1).max())
+    order = torch.argsort(idx.reshape(-1), stable=True)              # (token, choice) pairs sorted by global expert
+    token_of = order // k
+    rows = _AllToAllRows.apply(x[token_of], send, recv, group, seg_cap)  # grouped by source rank, then by expert
+    mine = table[:, me]                                              # [source, local expert] row counts held here
+    seg_start = torch.zeros(world, local, dtype=torch.long)
+    flat_sizes = mine.reshape(-1).long()
+    seg_start.view(-1)[1:] = torch.cumsum(flat_sizes, 0)[:-1]
+    by_expert = [torch.cat([torch.arange(int(seg_start[s, e]), int(seg_start[s, e] + mine[s, e])) for s in range(world)])
+                 for e in range(local)]
+    perm = torch.cat(by_expert).to(x.device) if by_expert else torch.empty(0, dtype=torch.long, device=x.device)
+    sorted_rows = rows[perm]
+    outs, at = [], 0
+    f = w_gate_up.shape[1] // 2
+    for e in range(local):
+        n = int(mine[:, e].sum())
+        seg = sorted_rows[at:at + n]
+        at += n
+        if n == 0:
+            outs.append(seg.new_zeros((0, h)))
+            continue
+        hgu = ops.linear(seg, w_gate_up[e])
+        outs.append(ops.linear(ops.swiglu(hgu[:, :f], hgu[:, f:]), w_down[e]))
+    y_sorted = torch.cat(outs) if outs else sorted_rows
+    inv = torch.empty_like(perm)
+    inv[perm] = torch.arange(perm.numel(), device=perm.device)
+    y = _AllToAllRows.apply(y_sorted[inv], recv, send, group, seg_cap)  # back in this rank's expert-sorted pair order
+    y = y * weights.reshape(-1, 1)[order].to(y.dtype)
+    return torch.zeros_like(x).index_add(0, token_of, y)
+
+
+class EPExperts(nn.Module):
+    """This rank's routed experts of one MoE layer, stacked: ``gate_up [E/W, 2F, H]`` and ``down [E/W, H, F]``.
+
+    Built from the ``routed_experts`` list of a :class:`~astrai_b200.models.ffn.DeepSeekMoE` (whose place it takes under
+    the same attribute name) by the expert-parallel executor; ``comm="p2p"`` runs the fused peer-memory kernels,
+    ``"nccl"`` the collective arm."""
+
+    def __init__(self, experts, ep_size: int, ep_rank: int, comm: str = "p2p", group=None,
+                 capacity_factor: Optional[float] = 2.0):
+        super().__init__()
+        n = len(experts)
+        if n % ep_size:
+            raise ValueError(f"{n} routed experts do not divide over {ep_size} ranks")
+        self.n_experts, self.ep_size, self.ep_rank, self.comm, self.group = n, ep_size, ep_rank, comm, group
+        self.capacity_factor = capacity_factor
+        local = n // ep_size
+        mine = [experts[i] for i in range(ep_rank * local, (ep_rank + 1) * local)]
+        self.gate_up = nn.Parameter(torch.stack([torch.cat([m.gate.weight, m.up.weight], dim=0) for m in mine]).detach().clone())
+        self.down = nn.Parameter(torch.stack([m.down.weight for m in mine]).detach().clone())
+
+    def forward(self, x: Tensor, idx: Tensor, weights: Tensor, counts: Tensor) -> Tensor:
+        if self.comm == "p2p" and x.is_cuda and get_context() is not None:
+            return ep_experts(x, idx, weights, counts.int(), self.gate_up, self.down, capacity_factor=self.capacity_factor)
+        return ep_experts_collective(x, idx, weights, counts, self.gate_up, self.down, group=self.group)
+
+    def unstacked(self, prefix: str, gate_up: Tensor, down: Tensor) -> Dict[str, Tensor]:
+        """Reference checkpoint keys (``<prefix>.<j>.{gate,up,down}.weight``) for stacked tensors of ALL experts."""
+        f = gate_up.shape[1] // 2
+        out = {}
+        for j in range(gate_up.shape[0]):
+            out[f"{prefix}.{j}.gate.weight"] = gate_up[j, :f]
+            out[f"{prefix}.{j}.up.weight"] = gate_up[j, f:]
+            out[f"{prefix}.{j}.down.weight"] = down[j]
+        return out

@@ -39,6 +39,7 @@ class FlatUnit:
     grad_shard: Optional[torch.Tensor] = None  # fp32 [shard_size]: reduce-scatter result (sharded modes)
     ready: bool = False  # gradient of the current step fully accumulated
     reduced: bool = False
+    tag: str = ""  # set when an executor splits units by parameter kind (replicated / sharded): picks the reduce group
 
     def shard_range(self, rank: int):
         return rank * self.shard_size, (rank + 1) * self.shard_size
@@ -108,7 +109,10 @@ class FlatParamEngine:
     """Builds the units for a model and keeps the bookkeeping the executors need."""
 
     def __init__(self, model: nn.Module, world_size: int = 1, rank: int = 0, grad_dtype=torch.float32,
-                 units: Optional[List[List[str]]] = None, allocator: Optional[Callable] = None):
+                 units: Optional[List[List[str]]] = None, allocator: Optional[Callable] = None,
+                 tag_fn: Optional[Callable[[str, nn.Parameter], str]] = None):
+        """``tag_fn(name, param)``: when given, every unit is split into one unit per tag (``<unit>#<tag>``), so that
+        parameters whose gradients are reduced over different process groups never share a flat buffer."""
         self.model = model
         self.world_size, self.rank = world_size, rank
         self.grad_dtype = grad_dtype
@@ -116,16 +120,21 @@ class FlatParamEngine:
         self._alloc = allocator or (lambda n, dtype, device, what: torch.zeros(n, dtype=dtype, device=device))
         claimed = set()
         for names in (units or default_units(model)):
-            unit = FlatUnit(name="+".join(names), module_names=list(names))
+            by_tag: Dict[str, FlatUnit] = {}
             for mname in names:
                 mod = model.get_submodule(mname)
                 for pname, p in _ordered_params(mod, mname + "."):
                     if id(p) in claimed or not p.requires_grad:
                         continue
                     claimed.add(id(p))
+                    tag = tag_fn(pname, p) if tag_fn is not None else ""
+                    unit = by_tag.get(tag)
+                    if unit is None:
+                        base = "+".join(names)
+                        unit = by_tag[tag] = FlatUnit(name=f"{base}#{tag}" if tag else base, module_names=list(names), tag=tag)
                     unit.params.append(p)
                     unit.param_names.append(pname)
-            if unit.params:
+            for unit in by_tag.values():
                 self._layout(unit)
                 self.units.append(unit)
         self._install_fused_views()
@@ -175,16 +184,17 @@ class FlatParamEngine:
         return view
 
     def _install_fused_views(self):
-        from astrai_b200.models.attention import GQA
-        from astrai_b200.models.ffn import MLP
-
         owner: Dict[int, FlatUnit] = {id(p): u for u in self.units for p in u.params}
-        for mod in self.model.modules():
-            if isinstance(mod, GQA) and all(type(getattr(mod, n)).__name__ == "Linear" for n in ("q_proj", "k_proj", "v_proj")):
+
+        def plain(mod, names):
+            return all(type(getattr(mod, n, None)).__name__ == "Linear" for n in names)
+
+        for mod in self.model.modules():  # any attention / MLP block that declares the slot (the tensor-parallel ones too)
+            if hasattr(mod, "fused_qkv") and plain(mod, ("q_proj", "k_proj", "v_proj")):
                 parts = [mod.q_proj.weight, mod.k_proj.weight, mod.v_proj.weight]
                 unit = owner.get(id(parts[0]))
                 mod.fused_qkv = self._fuse(unit, parts) if unit is not None else None
-            elif isinstance(mod, MLP) and all(type(getattr(mod, n)).__name__ == "Linear" for n in ("gate", "up")):
+            elif hasattr(mod, "fused_gate_up") and plain(mod, ("gate", "up")):
                 parts = [mod.gate.weight, mod.up.weight]
                 unit = owner.get(id(parts[0]))
                 mod.fused_gate_up = self._fuse(unit, parts) if unit is not None else None

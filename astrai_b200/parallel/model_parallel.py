@@ -1,0 +1,342 @@
+"""Training executors for the model-parallel modes: ``tp`` (tensor + sequence parallel), ``cp`` (context parallel,
+zig-zag sequence sharding) and ``ep`` (expert parallel).
+
+The reference accepts ``--tp_size`` and silently drops it (``scripts/tools/train.py:513-519``, ``:549-550``) and knows
+the modes ``none | ddp | fsdp`` only (``astrai/config/train_config.py:15``).  Here ``parallel_mode = "tp" | "cp" | "ep"``
+with ``tp_size / cp_size / ep_size`` selects one of the executors below through the same ``ExecutorFactory`` the
+trainer already uses.  All three run on the flat-buffer runtime (fp32 ``main_grad`` filled by the wgrad kernels, clip
+coefficient on the device, fused AdamW) and differ in
+
+* how the model is rewritten at wrap time (``tp``: attention / FFN blocks become their sharded forms; ``ep``: the routed
+  experts of every MoE layer become this rank's stacked share; ``cp``: nothing, the attention op is swapped by a context),
+* how a batch is cut for this rank (:meth:`shard_batch`, called by the strategies),
+* over which ranks a parameter's gradient is summed (replicated parameters: every rank; sharded ones: the ranks that
+  hold the same shard) - units of the flat engine are split by that property,
+* how the full state dict is put back together for checkpoints (reference keys and shapes).
+
+Ranks are laid out by :mod:`astrai_b200.parallel.mesh`: blocks of ``mp_size`` consecutive ranks form one model-parallel
+group; ``world / mp_size`` such blocks are data-parallel replicas (``tp``, ``cp``) or further expert-parallel groups
+working on their own data (``ep``).  Every rank's loss is the mean over its own tokens, so a uniform ``1 / world`` factor
+(folded into the clip coefficient) turns the summed gradients into the gradient of the global mean loss.
+``comm="p2p"`` uses the fused peer-memory kernels, ``comm="nccl"`` library collectives around the same math (the
+baseline arm, and the CPU / Gloo path of the tests).
+"""
+
+from __future__ import annotations
+
+import logging
+from typing import Dict, Optional
+
+import torch
+import torch.distributed as dist
+import torch.nn as nn
+
+from astrai_b200.parallel.executor import ExecutorFactory, FlatExecutor, FSDPExecutor
+from astrai_b200.parallel.flat import FlatParamEngine, FlatUnit
+from astrai_b200.parallel.mesh import ParallelMesh, build_mesh
+from astrai_b200.parallel.setup import get_rank, get_world_size
+
+logger = logging.getLogger(__name__)
+
+REPLICATED, SHARDED = "rep", "shard"
+
+
+class ModelParallelExecutor(FlatExecutor):
+    """Shared machinery of ``tp`` and ``ep``: flat runtime, two gradient-reduction groups, group-aware gradient norm."""
+
+    communicates_every_micro_batch = True
+    mode = ""
+
+    def __init__(self, grad_accum_steps: int = 1, size: int = 0, comm: str = "p2p", overlap: bool = True,
+                 comm_timeout_s: float = 120.0, arena_bytes: Optional[int] = None):
+        super().__init__(grad_accum_steps, impl="flat", overlap=overlap)
+        if comm not in ("p2p", "nccl"):
+            raise ValueError("comm must be 'p2p' or 'nccl'")
+        self.size, self.comm, self.comm_timeout_s, self.arena_bytes = int(size), comm, float(comm_timeout_s), arena_bytes
+        self.mesh: Optional[ParallelMesh] = None
+
+    # -- to be provided by the modes -------------------------------------------------------------------------------------
+    def _convert(self, model: nn.Module) -> nn.Module:
+        raise NotImplementedError
+
+    def _is_sharded(self, name: str, p: nn.Parameter) -> bool:
+        raise NotImplementedError
+
+    def _full_state_dict(self, model: nn.Module) -> Optional[Dict[str, torch.Tensor]]:
+        raise NotImplementedError
+
+    def shard_batch(self, batch: dict) -> dict:
+        return batch
+
+    @property
+    def data_parallel_size(self) -> int:
+        return get_world_size()
+
+    @property
+    def data_parallel_rank(self) -> int:
+        return get_rank()
+
+    # -- set-up -------------------------------------------------------------------------------------------------------------
+    def _prepare_model(self, model: nn.Module) -> nn.Module:
+        self.mesh = build_mesh(self.size if self.size > 1 else None)
+        on_gpu = next(model.parameters()).is_cuda
+        if not on_gpu and self.comm == "p2p":
+            self.comm = "nccl"  # the fused kernels need CUDA peer memory; on CPU the collective arm is the only one
+        if self.use_distributed:  # one set of initial weights everywhere before anything is cut
+            for t in list(model.parameters()) + list(model.buffers()):
+                dist.broadcast(t.data, src=0)
+        model = self._convert(model)
+        self.engine = FlatParamEngine(model, 1, 0, tag_fn=lambda n, p: SHARDED if self._is_sharded(n, p) else REPLICATED)
+        model._flat_engine, model._flat_executor = self.engine, self
+        if self.use_distributed and on_gpu:
+            self._comm_stream = torch.cuda.Stream()
+        for unit in self.engine.units:
+            for mname in unit.module_names:
+                model.get_submodule(mname).register_forward_pre_hook(self._make_pre_hook(unit), with_kwargs=True)
+        return model
+
+    # -- gradients ---------------------------------------------------------------------------------------------------------
+    def _group_for(self, unit: FlatUnit):
+        """(process group, whether a reduction is needed) for this unit's gradient."""
+        m = self.mesh
+        if unit.tag == REPLICATED:
+            return None, m.world > 1                                    # every rank (WORLD)
+        return m.dp_group, (m.dp_size > 1 and m.mp_size < m.world)      # ranks holding the same shard
+
+    def _reduce_unit(self, unit: FlatUnit):
+        unit.reduced = True
+        group, needed = self._group_for(unit)
+        if not needed or not self.use_distributed:
+            return
+        if self._comm_stream is not None:
+            self._comm_stream.wait_stream(torch.cuda.current_stream())
+            with torch.cuda.stream(self._comm_stream):
+                dist.all_reduce(unit.grad_buf, group=group)
+        else:
+            dist.all_reduce(unit.grad_buf, group=group)
+
+    def _averaging_scale(self) -> float:
+        return 1.0 / get_world_size() if self.use_distributed else 1.0
+
+    def _grad_sumsq(self) -> torch.Tensor:
+        """Squared norm of the whole (unsharded) gradient: replicated units count once, sharded units are summed over
+        the model-parallel group."""
+        from astrai_b200 import ops
+
+        dev = self.engine.units[0].grad_buf.device
+        rep = torch.zeros(1, dtype=torch.float32, device=dev)
+        shard = torch.zeros(1, dtype=torch.float32, device=dev)
+        for u in self.engine.units:
+            ops.sumsq(u.grad_buf, rep if u.tag == REPLICATED else shard)
+        if self.use_distributed and self.mesh.mp_size > 1:
+            dist.all_reduce(shard, group=self.mesh.mp_group)
+        return rep + shard
+
+    # -- state ------------------------------------------------------------------------------------------------------------
+    def unwrap_model(self, model: nn.Module):
+        return self._full_state_dict(model)
+
+    def local_state_dict(self, model: nn.Module):
+        return None  # parts of the model live on other ranks
+
+
+@ExecutorFactory.register("tp")
+class TensorParallelExecutor(ModelParallelExecutor):
+    """``parallel_mode="tp"``: Megatron-style tensor parallelism with sequence-sharded activations inside blocks of
+    ``tp_size`` ranks (:mod:`astrai_b200.parallel.tp_model`), data parallelism across the blocks.
+
+    Every rank of a block reads the same batch; rank ``r`` keeps token rows ``[r*T/tp, (r+1)*T/tp)`` between the layers
+    and computes the loss on those rows, so per-token tensors of the batch other than ``input_ids`` / ``position_ids``
+    are cut to those rows by :meth:`shard_batch`.  Objectives that need whole sequences on one rank (DPO, GRPO) are
+    not sharded this way and raise."""
+
+    mode = "tp"
+    PER_TOKEN = ("target_ids", "loss_mask")
+
+    def _convert(self, model):
+        from astrai_b200.parallel import tensor_parallel as tpar
+        from astrai_b200.parallel.tp_model import shard_model_
+
+        m = self.mesh
+        if m.mp_size > 1:
+            tpar.set_group(m.mp_group, m.mp_rank, m.mp_size)
+            if self.comm == "p2p":
+                ctx = tpar.init_tensor_parallel(self.arena_bytes or (2 << 30), timeout_s=self.comm_timeout_s, group=m.mp_group)
+                ctx.group = m.mp_group
+        else:
+            tpar.set_group(None, 0, 1)
+        return shard_model_(model, m.mp_size, m.mp_rank, comm=self.comm)
+
+    def _is_sharded(self, name, p):
+        from astrai_b200.parallel.tp_model import is_sharded
+
+        return is_sharded(name)
+
+    @property
+    def data_parallel_size(self):
+        return self.mesh.dp_size if self.mesh else 1
+
+    @property
+    def data_parallel_rank(self):
+        return self.mesh.dp_rank if self.mesh else 0
+
+    def shard_batch(self, batch):
+        if "input_ids" not in batch or "target_ids" not in batch:
+            raise NotImplementedError("tensor parallelism shards token-level objectives (seq, sft); this batch has no "
+                                      "input_ids / target_ids pair")
+        tp, r = self.mesh.mp_size, self.mesh.mp_rank
+        out = dict(batch)
+        for key in self.PER_TOKEN:
+            t = batch.get(key)
+            if isinstance(t, torch.Tensor):
+                flat = t.reshape(-1)
+                local = flat.numel() // tp
+                out[key] = flat[r * local:(r + 1) * local]
+        return out
+
+    def _full_state_dict(self, model):
+        from astrai_b200.parallel.tp_model import gather_state_dict
+
+        sd = gather_state_dict(model, group=self.mesh.mp_group)
+        return sd if get_rank() == 0 else None
+
+
+@ExecutorFactory.register("ep")
+class ExpertParallelExecutor(ModelParallelExecutor):
+    """``parallel_mode="ep"``: the routed experts of every MoE layer are spread over blocks of ``ep_size`` ranks
+    (:class:`~astrai_b200.parallel.expert_parallel.EPExperts`); everything else is replicated and every rank trains on
+    its own batch, so non-expert gradients are summed over all ranks and expert gradients over the ranks that hold the
+    same experts."""
+
+    mode = "ep"
+
+    def __init__(self, grad_accum_steps: int = 1, size: int = 0, comm: str = "p2p", overlap: bool = True,
+                 comm_timeout_s: float = 120.0, arena_bytes: Optional[int] = None, capacity_factor: Optional[float] = 2.0,
+                 tokens_per_rank: Optional[int] = None):
+        super().__init__(grad_accum_steps, size, comm, overlap, comm_timeout_s, arena_bytes)
+        self.capacity_factor, self.tokens_per_rank = capacity_factor, tokens_per_rank
+
+    def _convert(self, model):
+        from astrai_b200.models.ffn import DeepSeekMoE
+        from astrai_b200.parallel import expert_parallel as epar
+
+        m = self.mesh
+        layers = [mod for mod in model.modules() if isinstance(mod, DeepSeekMoE)]
+        if not layers:
+            raise ValueError("parallel_mode='ep' needs a model with MoE layers (ffn_type='moe')")
+        if m.mp_size > 1 and self.comm == "p2p":
+            first = layers[0]
+            hidden = first.dim
+            tokens = self.tokens_per_rank or 8192
+            need = self.arena_bytes or epar.arena_bytes_for(tokens, hidden, first.n_activated_experts, m.mp_size,
+                                                            first.n_routed_experts, self.capacity_factor)
+            epar.init_expert_parallel(need, timeout_s=self.comm_timeout_s, group=m.mp_group)
+        for moe in layers:
+            experts = epar.EPExperts(moe.routed_experts, m.mp_size, m.mp_rank, comm=self.comm if m.mp_size > 1 else "nccl",
+                                     group=m.mp_group, capacity_factor=self.capacity_factor)
+            moe.routed_experts = experts
+            moe.expert_parallel = True
+        return model
+
+    def _is_sharded(self, name, p):
+        return ".routed_experts." in name
+
+    def _full_state_dict(self, model):
+        m = self.mesh
+        first = get_rank() == 0
+        out = {}
+        for name, t in model.state_dict().items():
+            if ".routed_experts." not in name:
+                if first:
+                    out[name] = t
+                continue
+            parts = [torch.empty_like(t) for _ in range(m.mp_size)]
+            if m.mp_size > 1:
+                dist.all_gather(parts, t.contiguous(), group=m.mp_group)
+            else:
+                parts = [t]
+            if first:
+                out[name] = torch.cat(parts, dim=0)
+        if not first:
+            return None
+        # stacked [E, ...] tensors back to the reference's per-expert keys
+        final = {k: v for k, v in out.items() if ".routed_experts." not in k}
+        prefixes = sorted({k.rsplit(".", 1)[0] for k in out if k.endswith(".routed_experts.gate_up")})
+        for pre in prefixes:
+            gate_up, down = out[pre + ".gate_up"], out[pre + ".down"]
+            f = gate_up.shape[1] // 2
+            for j in range(gate_up.shape[0]):
+                final[f"{pre}.{j}.gate.weight"] = gate_up[j, :f].contiguous()
+                final[f"{pre}.{j}.up.weight"] = gate_up[j, f:].contiguous()
+                final[f"{pre}.{j}.down.weight"] = down[j].contiguous()
+        return final
+
+
+@ExecutorFactory.register("cp")
+class ContextParallelExecutor(FSDPExecutor):
+    """``parallel_mode="cp"``: every sequence is cut zig-zag over blocks of ``cp_size`` ranks; attention fetches the other
+    ranks' keys inside its kernel (:mod:`astrai_b200.parallel.context_parallel`).
+
+    Parameters are replicated over all ranks, so everything outside attention is the flat FSDP runtime unchanged
+    (gradients reduce-scattered over all ranks, optimizer state sharded, parameters gathered after the update): a long
+    sequence costs activation memory, and sharding the optimizer state is what leaves room for it.  Only the token-level
+    objectives (seq, and sft without packed-document masks) can be sequence-sharded."""
+
+    communicates_every_micro_batch = True
+    mode = "cp"
+    PER_TOKEN = ("input_ids", "target_ids", "loss_mask")
+
+    def __init__(self, grad_accum_steps: int = 1, size: int = 0, comm: str = "p2p", attn_comm: Optional[str] = None,
+                 overlap: bool = True, comm_timeout_s: float = 120.0, arena_bytes: Optional[int] = None,
+                 max_tokens_per_rank: Optional[int] = None, impl: str = "flat"):
+        super().__init__(grad_accum_steps, impl=impl, overlap=overlap, comm=comm, comm_timeout_s=comm_timeout_s)
+        self.size, self.attn_comm, self.arena_bytes = int(size), attn_comm or ("nccl" if comm == "nccl" else "p2p"), arena_bytes
+        self.max_tokens_per_rank = max_tokens_per_rank
+        self.mesh: Optional[ParallelMesh] = None
+        self._cp = None
+
+    def _prepare_model(self, model):
+        from astrai_b200.parallel import context_parallel as cpar
+
+        self.mesh = build_mesh(self.size if self.size > 1 else None)
+        m = self.mesh
+        on_gpu = next(model.parameters()).is_cuda
+        if m.mp_size > 1 and on_gpu:
+            cfg = model.config
+            head_dim = cfg.hidden_size // cfg.num_attention_heads
+            tokens = self.max_tokens_per_rank or cfg.max_position_embeddings // m.mp_size * 4
+            need = self.arena_bytes or cpar.arena_bytes_for(1, tokens * m.mp_size, m.mp_size, cfg.num_key_value_heads, head_dim)
+            self._cp = cpar.init_context_parallel(need, timeout_s=self.comm_timeout_s, group=m.mp_group)
+            self._cp.comm = self.attn_comm
+        elif m.mp_size > 1:
+            self._cp = cpar.init_context_parallel_group(m.mp_group)
+        return super()._prepare_model(model)
+
+    @property
+    def data_parallel_size(self):
+        return self.mesh.dp_size if self.mesh else 1
+
+    @property
+    def data_parallel_rank(self):
+        return self.mesh.dp_rank if self.mesh else 0
+
+    def shard_batch(self, batch):
+        from astrai_b200.parallel.context_parallel import zigzag_positions, zigzag_split
+
+        if "input_ids" not in batch or "target_ids" not in batch:
+            raise NotImplementedError("context parallelism shards token-level objectives (seq); this batch has no "
+                                      "input_ids / target_ids pair")
+        if "position_ids" in batch:
+            raise NotImplementedError("packed documents (position_ids in the batch) are not sequence-sharded: attention "
+                                      "across the ranks is plain causal")
+        cp, r = self.mesh.mp_size, self.mesh.mp_rank
+        if cp == 1:
+            return batch
+        out = dict(batch)
+        b, s = batch["input_ids"].shape
+        for key in self.PER_TOKEN:
+            t = batch.get(key)
+            if isinstance(t, torch.Tensor):
+                out[key] = zigzag_split(t, cp, r, dim=1).contiguous()
+        out["position_ids"] = zigzag_positions(s, cp, r, device=batch["input_ids"].device).unsqueeze(0).expand(b, -1)
+        return out

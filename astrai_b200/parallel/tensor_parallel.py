@@ -72,11 +72,25 @@ class TPContext:
 
 
 _CTX: Optional[TPContext] = None
+_GROUP = {"group": None, "rank": 0, "world": None}  # the tensor-parallel process group when it is not WORLD
 
 
 def set_context(ctx: Optional[TPContext]):
     global _CTX
     _CTX = ctx
+
+
+def set_group(group, rank: int, world: int):
+    """Name the tensor-parallel group for the collective (``comm="nccl"``) path; ``world=None`` means WORLD."""
+    _GROUP.update(group=group, rank=rank, world=world)
+
+
+def _group_world(ctx: Optional["TPContext"]):
+    if ctx is not None:
+        return ctx.group, ctx.world
+    if _GROUP["world"] is not None:
+        return _GROUP["group"], _GROUP["world"]
+    return None, (dist.get_world_size() if dist.is_initialized() else 1)
 
 
 def get_context() -> Optional[TPContext]:
@@ -102,7 +116,7 @@ def allgather_gemm(x_local: Tensor, w: Tensor, w_kmajor: bool = True, ctx: Optio
 
     ``w`` is ``[N, K]`` (``w_kmajor``) or ``[K, N]``."""
     ctx = ctx or _CTX
-    world = ctx.world if ctx is not None else (dist.get_world_size() if dist.is_initialized() else 1)
+    group, world = _group_world(ctx)
     ms, k = x_local.shape
     m = ms * world
     n = w.shape[0] if w_kmajor else w.shape[1]
@@ -118,7 +132,7 @@ def allgather_gemm(x_local: Tensor, w: Tensor, w_kmajor: bool = True, ctx: Optio
         return y, x_full
     if world > 1:
         x_full = torch.empty((m, k), dtype=x_local.dtype, device=x_local.device)
-        dist.all_gather_into_tensor(x_full, x_local.contiguous(), group=ctx.group if ctx else None)
+        dist.all_gather_into_tensor(x_full, x_local.contiguous(), group=group)
     else:
         x_full = x_local
     from astrai_b200 import ops
@@ -131,7 +145,7 @@ def gemm_reducescatter(x: Tensor, w: Tensor, w_kmajor: bool = True, ctx: Optiona
                        comm: str = "p2p") -> Tensor:
     """Row block ``rank`` of ``sum_p x_p @ op(w_p)``: ``x [M, K_p]`` -> ``[M / world, N]``."""
     ctx = ctx or _CTX
-    world = ctx.world if ctx is not None else (dist.get_world_size() if dist.is_initialized() else 1)
+    group, world = _group_world(ctx)
     m, k = x.shape
     n = w.shape[0] if w_kmajor else w.shape[1]
     ms = m // world
@@ -151,7 +165,7 @@ def gemm_reducescatter(x: Tensor, w: Tensor, w_kmajor: bool = True, ctx: Optiona
     if world == 1:
         return full
     out = torch.empty((ms, n), dtype=full.dtype, device=full.device)
-    dist.reduce_scatter_tensor(out, full.contiguous(), group=ctx.group if ctx else None)
+    dist.reduce_scatter_tensor(out, full.contiguous(), group=group)
     return out
 
 
@@ -172,8 +186,11 @@ class _ColumnParallelFn(Function):
         gy = gy.contiguous()
         dx = gemm_reducescatter(gy, w, False, comm=ctx.comm)  # dY [M, N_r] @ W_r [N_r, K], summed over ranks, row block
         mg = getattr(w, "main_grad", None)
-        if mg is not None and gy.is_cuda:
-            ops.gemm(gy, x_full, out=mg, a_kmajor=False, b_kmajor=False, out_f32=True, accumulate=True)
+        if mg is not None:  # the flat runtime's fp32 gradient buffer: accumulate in place (wgrad epilogue on CUDA)
+            if gy.is_cuda:
+                ops.gemm(gy, x_full, out=mg, a_kmajor=False, b_kmajor=False, out_f32=True, accumulate=True)
+            else:
+                mg.add_(gy.float().t() @ x_full.float())
             return dx, None, None
         dw = ops.gemm(gy, x_full, a_kmajor=False, b_kmajor=False) if gy.is_cuda else gy.t() @ x_full
         return dx, dw, None
@@ -193,8 +210,11 @@ class _RowParallelFn(Function):
         x, w = ctx.saved_tensors
         dx, gy_full = allgather_gemm(gy_local.contiguous(), w, False, comm=ctx.comm)  # AG(dY) [M, N] @ W_p [N, K_p]
         mg = getattr(w, "main_grad", None)
-        if mg is not None and x.is_cuda:
-            ops.gemm(gy_full, x, out=mg, a_kmajor=False, b_kmajor=False, out_f32=True, accumulate=True)
+        if mg is not None:
+            if x.is_cuda:
+                ops.gemm(gy_full, x, out=mg, a_kmajor=False, b_kmajor=False, out_f32=True, accumulate=True)
+            else:
+                mg.add_(gy_full.float().t() @ x.float())
             return dx, None, None
         dw = ops.gemm(gy_full, x, a_kmajor=False, b_kmajor=False) if x.is_cuda else gy_full.t() @ x
         return dx, dw, None

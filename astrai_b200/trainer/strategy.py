@@ -166,6 +166,13 @@ class BaseStrategy:
     def compute_loss(self, batch) -> Tensor:
         return self.compute_loss_output(batch)["loss"]
 
+    def _to_rank(self, batch: Dict[str, Tensor]) -> Dict[str, Tensor]:
+        """The batch on this rank's device, cut to this rank's share when the executor shards tokens (tensor / context
+        parallelism); data-parallel executors leave it whole."""
+        batch = move_to_device(batch, self.device)
+        shard = getattr(self.executor, "shard_batch", None)
+        return shard(batch) if shard is not None else batch
+
     def compute_loss_output(self, batch) -> LossOutput:
         out = self.compute_loss(batch)
         return out if isinstance(out, dict) else {"loss": out, "metrics": DeferredMetrics(loss=out.detach())}
@@ -234,8 +241,9 @@ class SEQStrategy(_TokenCEStrategy):
     """Next-token cross-entropy over every position (mean), optional label smoothing."""
 
     def compute_loss_output(self, batch) -> LossOutput:
-        batch = move_to_device(batch, self.device)
-        return self._ce(batch["input_ids"], batch["target_ids"])
+        batch = self._to_rank(batch)
+        fwd = {"position_ids": batch["position_ids"]} if "position_ids" in batch else {}
+        return self._ce(batch["input_ids"], batch["target_ids"], **fwd)
 
 
 @StrategyFactory.register("sft")
@@ -243,7 +251,7 @@ class SFTStrategy(_TokenCEStrategy):
     """Cross-entropy on positions where ``loss_mask`` is set; attention stays inside each packed document."""
 
     def compute_loss_output(self, batch) -> LossOutput:
-        batch = move_to_device(batch, self.device)
+        batch = self._to_rank(batch)
         pos = batch["position_ids"]
         targets = batch["target_ids"].masked_fill(~batch["loss_mask"].bool(), -100)
         return self._ce(batch["input_ids"], targets, position_ids=pos, input_mask=make_doc_boundary_mask(pos))
@@ -258,7 +266,7 @@ class DPOStrategy(BaseStrategy):
         self.ref_model, self.beta, self.reduction = ref_model, beta, reduction
 
     def compute_loss_output(self, batch) -> LossOutput:
-        batch = move_to_device(batch, self.device)
+        batch = self._to_rank(batch)
         n = batch["chosen"].shape[0]
         ids = torch.cat([batch["chosen"], batch["rejected"]], dim=0)
         loss_mask = torch.cat([batch["chosen_mask"], batch["rejected_mask"]], dim=0)
@@ -301,7 +309,7 @@ class GRPOStrategy(BaseStrategy):
             self.old_model.load_state_dict(sd)
 
     def compute_loss_output(self, batch) -> LossOutput:
-        batch = move_to_device(batch, self.device)
+        batch = self._to_rank(batch)
         prompts, responses, masks, rewards = batch["prompts"], batch["responses"], batch["masks"], batch["rewards"]
         b, g, rlen = responses.shape
         resp = responses.reshape(b * g, rlen)

@@ -52,6 +52,7 @@ class TrainContext:
         self.val_loss: Optional[float] = None
         self.world_size = 1
         self.rank = 0
+        self.data_world = None  # ranks that draw different samples (set by the builder; None: every rank)
         self.kwargs: Dict[str, Any] = {}
         self._loss: Any = 0.0
         self._stop_event = threading.Event()
@@ -79,7 +80,13 @@ class TrainContext:
     @property
     def optimizer_step(self) -> int:
         c = self.config
-        return self.consumed_samples // (c.batch_per_device * self.world_size * c.grad_accum_steps)
+        return self.consumed_samples // (c.batch_per_device * self.samples_world * c.grad_accum_steps)
+
+    @property
+    def samples_world(self) -> int:
+        """How many ranks contribute distinct samples to one micro-batch of the job: the world size, except that the
+        ranks of a tensor- or context-parallel block share one batch."""
+        return self.data_world if self.data_world else self.world_size
 
 
 @dataclass
@@ -106,7 +113,8 @@ class TrainContextBuilder:
         executor = self._executor()
         ctx = TrainContext(world_size=get_world_size(), rank=get_rank(), config=self.config,
                            model_config=pre.model_config, executor=executor, epoch=pre.epoch,
-                           consumed_samples=pre.consumed_samples, checkpoint=pre.checkpoint)
+                           consumed_samples=pre.consumed_samples, checkpoint=pre.checkpoint,
+                           data_world=self._data_world())
         self._model(ctx, executor, pre)
         self._restore_optimizer(ctx)
         train_ds, val_ds = self._datasets()
@@ -116,14 +124,26 @@ class TrainContextBuilder:
         return ctx
 
     # ---------------------------------------------------------------------------------------------------------------
+    def _data_world(self) -> int:
+        from astrai_b200.parallel.mesh import data_parallel_size
+
+        c = self.config
+        return data_parallel_size(c.parallel_mode, get_world_size(), c.tp_size, c.cp_size, c.ep_size)
+
     def _executor(self) -> BaseExecutor:
         c = self.config
         mode = c.parallel_mode
-        return ExecutorFactory.create(mode, grad_accum_steps=c.grad_accum_steps, **c.executor_kwargs)
+        kw = dict(c.executor_kwargs)
+        size = {"tp": c.tp_size, "cp": c.cp_size, "ep": c.ep_size}.get(mode)
+        if size is not None:
+            import astrai_b200.parallel.model_parallel  # noqa: F401 - registers the tp / cp / ep executors
+
+            kw.setdefault("size", size)
+        return ExecutorFactory.create(mode, grad_accum_steps=c.grad_accum_steps, **kw)
 
     def _preload(self) -> _Preloaded:
         c = self.config
-        pre = _Preloaded(epoch=c.start_epoch, consumed_samples=c.start_samples * get_world_size())
+        pre = _Preloaded(epoch=c.start_epoch, consumed_samples=c.start_samples * self._data_world())
         if self._param_path:
             root = Path(self._param_path)
             if (root / "config.json").exists():
@@ -137,7 +157,7 @@ class TrainContextBuilder:
                 pre.state_dict = ck.state_dict
                 pre.model_config = ck.config or pre.model_config
                 if self._resume:
-                    per_step = c.batch_per_device * get_world_size() * c.grad_accum_steps
+                    per_step = c.batch_per_device * self._data_world() * c.grad_accum_steps
                     pre.epoch = ck.epoch
                     pre.consumed_samples = ck.consumed_samples // per_step * per_step
                     pre.checkpoint = ck
@@ -189,7 +209,11 @@ class TrainContextBuilder:
 
     def _loader(self, dataset, epoch: int, start_iter: int, shuffle: bool = True) -> DataLoader:
         c = self.config
-        sampler = RDSampler(dataset, start_epoch=epoch, start_iter=start_iter, seed=c.random_seed, shuffle=shuffle)
+        # ranks of one tensor- / context-parallel block must draw the same samples: deal by data-parallel position
+        dw = self._data_world()
+        part = (get_rank() // max(get_world_size() // dw, 1), dw) if dw != get_world_size() else None
+        sampler = RDSampler(dataset, start_epoch=epoch, start_iter=start_iter, seed=c.random_seed, shuffle=shuffle,
+                            partition=part)
         kw = dict(dataset=dataset, batch_size=c.batch_per_device, sampler=sampler, num_workers=c.num_workers,
                   pin_memory=c.pin_memory and torch.cuda.is_available(), collate_fn=c.collate_fn)
         if c.num_workers > 0:
@@ -199,9 +223,9 @@ class TrainContextBuilder:
         return DataLoader(**kw)
 
     def _dataloaders(self, ctx: TrainContext, train_ds, val_ds):
-        offset = ctx.consumed_samples // ctx.world_size
+        offset = ctx.consumed_samples // ctx.samples_world
         if self._resume and offset > 0:
-            per_replica = -(-len(train_ds) // ctx.world_size)
+            per_replica = -(-len(train_ds) // ctx.samples_world)
             if per_replica > 0:
                 ctx.epoch = offset // per_replica
         ctx.dataloader = self._loader(train_ds, ctx.epoch, offset)

@@ -78,7 +78,7 @@ class Trainer:
                 ex.backward(loss * scale)
         context.loss = loss.detach()
         context.metrics = out["metrics"]
-        context.consumed_samples += context.config.batch_per_device * context.world_size
+        context.consumed_samples += context.config.batch_per_device * context.samples_world
         self._fire("on_batch_end", context)
         if ex.sync_gradients:
             self._fire("on_optimizer_step", context)

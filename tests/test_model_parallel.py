@@ -1,0 +1,97 @@
+"""The model-parallel training modes (``parallel_mode = tp | cp | ep``) through the real Trainer on gloo ranks (CPU).
+
+Each mode trains a tiny decoder for three optimizer steps on the same global batches as a single process and must
+reproduce its losses, gradient norms and - after gathering the shards - its final weights under the reference's
+checkpoint keys and shapes.  Four ranks with blocks of two exercise the sub-groups (model-parallel x data-parallel).
+"""
+
+import json
+import os
+import subprocess
+import sys
+
+import pytest
+import torch
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+WORKER = os.path.join(ROOT, "tests", "workers", "mp_train.py")
+_PORT = [29800]
+
+
+def _run(tmp_path, name, nproc, *args):
+    out, ckpt = str(tmp_path / f"{name}.json"), str(tmp_path / f"ck_{name}")
+    env = dict(os.environ, MASTER_ADDR="127.0.0.1", OMP_NUM_THREADS="1")
+    if nproc == 1:
+        cmd = [sys.executable, WORKER, "--out", out, "--ckpt", ckpt, *args]
+        for k in ("RANK", "WORLD_SIZE", "LOCAL_RANK", "LOCAL_WORLD_SIZE"):
+            env.pop(k, None)
+    else:
+        _PORT[0] += 1
+        cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={nproc}", "--master-addr",
+               "127.0.0.1", "--master-port", str(_PORT[0]), WORKER, "--out", out, "--ckpt", ckpt, *args]
+    proc = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=600, cwd=ROOT)
+    assert proc.returncode == 0, proc.stdout[-2000:] + proc.stderr[-3000:]
+    return json.load(open(out))
+
+
+def _same(run, ref):
+    assert run["losses"] == pytest.approx(ref["losses"], abs=2e-5)
+    assert run["norms"] == pytest.approx(ref["norms"], rel=1e-4)
+    assert run["shapes"] == ref["shapes"]  # the gathered checkpoint has the unsharded keys and shapes
+    for k, v in ref["sums"].items():
+        assert run["sums"][k] == pytest.approx(v, rel=1e-4), k
+
+
+@pytest.fixture(scope="module")
+def dense_ref(tmp_path_factory):
+    return _run(tmp_path_factory.mktemp("ref"), "ref", 1, "--mode", "none")
+
+
+@pytest.fixture(scope="module")
+def moe_ref(tmp_path_factory):
+    return _run(tmp_path_factory.mktemp("refmoe"), "refmoe", 1, "--mode", "none", "--moe")
+
+
+@pytest.mark.parametrize("mode,nproc,size", [("tp", 2, 0), ("cp", 2, 0), ("tp", 4, 2), ("cp", 4, 2)])
+def test_dense_model_parallel_mode_matches_single_process(tmp_path, dense_ref, mode, nproc, size):
+    _same(_run(tmp_path, mode, nproc, "--mode", mode, "--size", str(size)), dense_ref)
+
+
+@pytest.mark.parametrize("nproc,size", [(2, 0), (4, 2)])
+def test_expert_parallel_mode_matches_single_process(tmp_path, moe_ref, nproc, size):
+    _same(_run(tmp_path, "ep", nproc, "--mode", "ep", "--moe", "--size", str(size)), moe_ref)
+
+
+def test_mesh_sizes_and_registration():
+    from astrai_b200.parallel import ExecutorFactory, data_parallel_size, model_parallel_size
+
+    assert {"tp", "cp", "ep"} <= set(ExecutorFactory.list_registered())
+    assert model_parallel_size("tp", 8, tp_size=1) == 8 and model_parallel_size("tp", 8, tp_size=4) == 4
+    assert data_parallel_size("tp", 8, tp_size=4) == 2 and data_parallel_size("cp", 8, cp_size=8) == 1
+    assert data_parallel_size("ep", 8, ep_size=8) == 8 and data_parallel_size("fsdp", 8) == 8
+
+
+def test_tensor_parallel_refuses_sequence_level_objectives():
+    from astrai_b200.parallel import ExecutorFactory
+    from astrai_b200.parallel.mesh import ParallelMesh
+
+    ex = ExecutorFactory.create("tp", grad_accum_steps=1, size=2)
+    ex.mesh = ParallelMesh(world=2, rank=0, mp_size=2)
+    with pytest.raises(NotImplementedError):
+        ex.shard_batch({"chosen": torch.zeros(2, 4), "rejected": torch.zeros(2, 4)})
+    cut = ex.shard_batch({"input_ids": torch.zeros(2, 4, dtype=torch.long), "target_ids": torch.arange(8).view(2, 4)})
+    assert cut["target_ids"].tolist() == [0, 1, 2, 3] and cut["input_ids"].shape == (2, 4)
+
+
+def test_context_parallel_batch_is_cut_zigzag_with_global_positions():
+    from astrai_b200.parallel import ExecutorFactory
+    from astrai_b200.parallel.mesh import ParallelMesh
+
+    ex = ExecutorFactory.create("cp", grad_accum_steps=1, size=2)
+    ex.mesh = ParallelMesh(world=2, rank=1, mp_size=2)
+    ids = torch.arange(16).view(2, 8)
+    cut = ex.shard_batch({"input_ids": ids, "target_ids": ids + 1})
+    assert cut["input_ids"].tolist() == [[2, 3, 4, 5], [10, 11, 12, 13]]  # chunks 1 and 2 of 4
+    assert cut["position_ids"].tolist() == [[2, 3, 4, 5]] * 2
+    with pytest.raises(NotImplementedError):
+        ex.shard_batch({"input_ids": ids, "target_ids": ids, "position_ids": ids})
