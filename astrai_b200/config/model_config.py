@@ -77,6 +77,7 @@ class AutoRegressiveLMConfig(_TrunkConfig):
     qk_nope_head_dim: Optional[int] = None
     qk_rope_head_dim: Optional[int] = None
     q_lora_rank: Optional[int] = None
+    v_head_dim: Optional[int] = None
     n_routed_experts: Optional[int] = None
     n_shared_experts: Optional[int] = None
     n_activated_experts: Optional[int] = None
@@ -96,8 +97,9 @@ class AutoRegressiveLMConfig(_TrunkConfig):
 
     def to_dict(self):
         d = super().to_dict()
-        if d.get("q_lora_rank") is None:
-            d.pop("q_lora_rank", None)  # keep reference-format config.json byte-compatible
+        for extension in ("q_lora_rank", "v_head_dim"):  # fields the reference's config.json does not have
+            if d.get(extension) is None:
+                d.pop(extension, None)
         return d
 
 

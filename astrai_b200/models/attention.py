@@ -83,12 +83,15 @@ class GQA(nn.Module):
 class MLA(nn.Module):
     def __init__(self, dim: int, n_heads: int, n_kv_heads: int, kv_lora_rank: int, qk_nope_head_dim: int,
                  qk_rope_head_dim: int, norm_eps: float, use_qk_norm: bool, use_gated_attention: bool, layer_id: int,
-                 n_layers: int = 1, q_lora_rank: Optional[int] = None):
+                 n_layers: int = 1, q_lora_rank: Optional[int] = None, v_head_dim: Optional[int] = None):
         super().__init__()
         self.dim, self.n_heads, self.n_kv_heads, self.layer_id = dim, n_heads, n_kv_heads, layer_id
         self.kv_lora_rank, self.q_lora_rank = kv_lora_rank, q_lora_rank
         self.qk_nope_head_dim, self.qk_rope_head_dim = qk_nope_head_dim, qk_rope_head_dim
         self.head_dim = qk_nope_head_dim + qk_rope_head_dim
+        # value width per head: the reference ties it to the query / key width (and so needs heads * (nope + rope) == dim);
+        # ``v_head_dim`` unties it (DeepSeek-style 192-wide scores with 128-wide values)
+        self.v_head_dim = v_head_dim or self.head_dim
         self.n_rep = n_heads // n_kv_heads
         self.use_qk_norm, self.use_gated_attention = bool(use_qk_norm), bool(use_gated_attention)
         if q_lora_rank:
@@ -102,10 +105,10 @@ class MLA(nn.Module):
             self.k_norm = RMSNorm(self.head_dim, norm_eps)
         self.kv_a_proj = Linear(dim, kv_lora_rank)
         self.kv_norm = RMSNorm(kv_lora_rank, norm_eps)
-        self.kv_b_proj = Linear(kv_lora_rank, n_kv_heads * 2 * self.head_dim)
-        self.o_proj = Linear(dim, dim, init_std=_o_std(n_layers))
+        self.kv_b_proj = Linear(kv_lora_rank, n_kv_heads * (self.head_dim + self.v_head_dim))
+        self.o_proj = Linear(n_heads * self.v_head_dim, dim, init_std=_o_std(n_layers))
         if self.use_gated_attention:
-            self.gate = Linear(dim, dim)
+            self.gate = Linear(dim, n_heads * self.v_head_dim)
 
     def forward(self, x: Tensor, rotary_emb: Tensor, attn_mask: Optional[Tensor] = None, kv_cache=None,
                 is_causal: bool = False, fwd: Optional[str] = None) -> Tensor:
@@ -116,8 +119,8 @@ class MLA(nn.Module):
         else:
             q = self.q_proj(x)
         q = q.view(*lead, self.n_heads, self.head_dim)
-        kv = self.kv_b_proj(self.kv_norm(self.kv_a_proj(x))).view(*lead, self.n_kv_heads, 2 * self.head_dim)
-        k_nope, k_rope, v = kv.split((nope, rope, self.head_dim), dim=-1)
+        kv = self.kv_b_proj(self.kv_norm(self.kv_a_proj(x))).view(*lead, self.n_kv_heads, self.head_dim + self.v_head_dim)
+        k_nope, k_rope, v = kv.split((nope, rope, self.v_head_dim), dim=-1)
         q = torch.cat((q[..., :nope], ops.rotary(q[..., nope:], rotary_emb)), dim=-1)
         k = torch.cat((k_nope, ops.rotary(k_rope, rotary_emb)), dim=-1)
         if self.use_qk_norm:

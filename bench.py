@@ -1,6 +1,11 @@
 """Headline benchmark: 1B-class dense decoder pre-training, FSDP, bf16, synthetic packed tokens.
 
-    python bench.py --gpus N --steps K --warmup W [--impl ours|reference]
+    python bench.py --gpus N --steps K --warmup W [--impl ours|reference] [--config fsdp1b|tp8b|cp8b|ep_moe] [--comm p2p|nccl]
+
+``--config`` selects one of the other training configurations (8B dense with tensor parallelism at seq 8192 / global
+batch 8, 8B dense with context parallelism at seq 65 536 / batch 1, MoE + MLA with expert parallelism at seq 4096 /
+batch 2 per GPU); ``--comm nccl`` runs the same configuration on library collectives, which is the comparison arm of
+those three (the reference cannot run them).  Without ``--config`` the run is the headline described below.
 
 Model / recipe: 24 layers, d_model 2048, 16 query / 4 KV heads (head_dim 128), SwiGLU FFN 5632, vocab 32000, tied
 embeddings, RoPE; seq 2048, batch_per_device 4, grad_accum 8 (one "step" = one optimizer step = 65 536 tokens per GPU),
@@ -38,6 +43,32 @@ MODEL = dict(vocab_size=32000, hidden_size=2048, num_hidden_layers=24, rms_norm_
 SEQ, BPD, ACCUM = 2048, 4, 8
 LR, WD, SMOOTH, CLIP = 1e-4, 0.1, 0.05, 1.0
 BASELINE_VALUE = None  # the reference publishes no training throughput
+
+_DENSE_8B = dict(vocab_size=128256, hidden_size=4096, num_hidden_layers=32, rms_norm_eps=1e-5, intermediate_size=14336,
+                 tie_word_embeddings=False, rope_theta=500000.0, num_attention_heads=32, num_key_value_heads=8)
+_MOE_MLA = dict(vocab_size=32000, hidden_size=2048, num_hidden_layers=16, rms_norm_eps=1e-6, intermediate_size=1408,
+                tie_word_embeddings=False, max_position_embeddings=4096, rope_theta=10000.0, num_attention_heads=16,
+                num_key_value_heads=16, attn_type="mla", kv_lora_rank=512, q_lora_rank=1536, qk_nope_head_dim=128,
+                qk_rope_head_dim=64, v_head_dim=128, ffn_type="moe", n_routed_experts=64, n_shared_experts=2,
+                n_activated_experts=6, moe_intermediate_size=1408, shared_expert_intermediate_size=1408)
+
+# The headline configuration (fsdp1b) and the three model-parallel configurations named beside it.  ``bpd`` is the batch a
+# rank reads per micro-batch; ranks of one tp / cp block read the same batch, so the job's global batch is bpd x accum x
+# data-parallel replicas.
+CONFIGS = {
+    "fsdp1b": dict(metric="train tok/s/box (1B dense FSDP)", label="1B dense decoder (24L d2048 16q/4kv hd128 ffn5632 v32000 tied)",
+                   model=MODEL, seq=SEQ, bpd=BPD, accum=ACCUM, mode="fsdp", smooth=SMOOTH),
+    "tp8b": dict(metric="train tok/s/box (8B dense TP, seq 8192, global batch 8)",
+                 label="8B dense decoder (32L d4096 32q/8kv hd128 ffn14336 v128256 untied)",
+                 model=dict(_DENSE_8B, max_position_embeddings=8192), seq=8192, bpd=8, accum=1, mode="tp", smooth=0.0),
+    "cp8b": dict(metric="train tok/s/box (8B dense CP, seq 65536, batch 1)",
+                 label="8B dense decoder (32L d4096 32q/8kv hd128 ffn14336 v128256 untied)",
+                 model=dict(_DENSE_8B, max_position_embeddings=65536), seq=65536, bpd=1, accum=1, mode="cp", smooth=0.0),
+    "ep_moe": dict(metric="train tok/s/box (MoE + MLA, EP, seq 4096, batch 2 per GPU)",
+                   label="MoE decoder (16L d2048, MLA 16 heads kv_lora 512 q_lora 1536 nope 128 rope 64 v 128, "
+                         "64 routed top-6 + 2 shared experts ffn 1408, v32000)",
+                   model=_MOE_MLA, seq=4096, bpd=2, accum=1, mode="ep", smooth=0.0),
+}
 
 
 # ----------------------------------------------------------------------------------------------- clocks sampling
@@ -186,19 +217,31 @@ def _quiet_progress(callbacks):
             cb.file = sys.stderr
 
 
+def _spec(args):
+    return CONFIGS[getattr(args, "config", "fsdp1b")]
+
+
+def _replicas(spec, world):
+    """Ranks that read different samples (the ranks of a tp / cp block share theirs)."""
+    return 1 if spec["mode"] in ("tp", "cp") else world
+
+
 def _emit(args, world, value_ms, e2e_ms, launches, clocks, impl, extra=None, note=None):
-    tokens_per_step = world * BPD * ACCUM * SEQ
+    spec = _spec(args)
+    SEQ, BPD, ACCUM = spec["seq"], spec["bpd"], spec["accum"]
+    readers = _replicas(spec, world)
+    tokens_per_step = readers * BPD * ACCUM * SEQ
     value = tokens_per_step * args.steps / (value_ms / 1e3) if value_ms else None
     e2e = tokens_per_step * args.steps / (e2e_ms / 1e3) if e2e_ms else None
     line = {
-        "metric": "train tok/s/box (1B dense FSDP)", "value": value if value is not None else e2e, "unit": "tokens/s",
+        "metric": spec["metric"], "value": value if value is not None else e2e, "unit": "tokens/s",
         "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
         "ms_per_step": (value_ms or e2e_ms) / args.steps, "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None if not BASELINE_VALUE else (value or e2e) / BASELINE_VALUE, "dtype": "bf16",
         "data": "synthetic uniform token ids, random-init weights", "impl": impl,
-        "config": {"model": "1B dense decoder (24L d2048 16q/4kv hd128 ffn5632 v32000 tied)", "global_batch": world * BPD * ACCUM,
-                   "seq_len": SEQ, "batch_per_device": BPD, "grad_accum": ACCUM, "parallelism": f"fsdp{world}",
-                   "optimizer": "AdamW lr1e-4 wd0.1", "label_smoothing": SMOOTH, "max_grad_norm": CLIP,
+        "config": {"model": spec["label"], "global_batch": readers * BPD * ACCUM,
+                   "seq_len": SEQ, "batch_per_device": BPD, "grad_accum": ACCUM, "parallelism": f"{spec['mode']}{world}",
+                   "optimizer": "AdamW lr1e-4 wd0.1", "label_smoothing": spec["smooth"], "max_grad_norm": CLIP,
                    "l2": "per-step working set (activations, weights, gradients > 10 GB) far exceeds the 126 MB L2; no explicit flush"},
         "clocks": clocks or {"sm_mhz": None, "sm_max_mhz": None, "reasons": []},
         "e2e": {"value": e2e, "unit": "tokens/s", "ms_per_step": (e2e_ms / args.steps) if e2e_ms else None,
@@ -225,43 +268,63 @@ def run_ours(args):
 
     rank, world, local = _dist_env()
     native.require()
-    cfg = AutoRegressiveLMConfig(**MODEL)
+    spec = _spec(args)
+    seq, bpd, accum, mode = spec["seq"], spec["bpd"], spec["accum"], spec["mode"]
+    if mode in ("tp", "cp", "ep") and world < 2:
+        raise SystemExit(f"--config {args.config} is a model-parallel configuration: launch it on 2 or more GPUs")
+    cfg = AutoRegressiveLMConfig(**spec["model"])
+    vocab = spec["model"]["vocab_size"]
     total_steps = args.warmup + args.steps
+    big = cfg.hidden_size * cfg.num_hidden_layers >= 100_000  # 8B class: build on the GPU, the host would take minutes
 
     def model_fn():
         torch.manual_seed(1234)
+        if big:
+            with torch.device("cuda", local):
+                return AutoRegressiveLM(cfg).to(torch.bfloat16)
         return AutoRegressiveLM(cfg).to(torch.bfloat16)
+
+    if mode == "fsdp":
+        exkw = {"comm": args.comm}
+    elif mode == "cp":
+        exkw = {"comm": args.comm, "attn_comm": "nccl" if args.comm == "nccl" else "p2p", "max_tokens_per_rank": 2 * bpd * seq // world}
+    elif mode == "ep":
+        exkw = {"comm": "nccl" if args.comm == "nccl" else "p2p", "tokens_per_rank": bpd * seq}
+    else:
+        exkw = {"comm": "nccl" if args.comm == "nccl" else "p2p", "arena_bytes": 6 << 30}
 
     def make_config(dataset, ckpt_dir):
         return TrainConfig(
             model_fn=model_fn, strategy="seq", dataset=dataset,
             optimizer_fn=lambda m: FusedAdamW(m.parameters(), lr=LR, betas=(0.9, 0.999), weight_decay=WD),
             scheduler_fn=lambda o: SchedulerFactory.create("cosine", o, warmup_steps=2, lr_decay_steps=10_000),
-            batch_per_device=BPD, grad_accum_steps=ACCUM, max_grad_norm=CLIP, ckpt_dir=ckpt_dir, ckpt_interval=10**9,
-            metrics=["loss", "lr", "grad_norm"], pin_memory=True, nprocs=world, parallel_mode="fsdp",
-            strategy_kwargs={"label_smoothing": SMOOTH}, master_addr=os.environ.get("MASTER_ADDR", "127.0.0.1"),
-            master_port=os.environ.get("MASTER_PORT", "29511"), executor_kwargs={"comm": args.comm},
+            batch_per_device=bpd, grad_accum_steps=accum, max_grad_norm=CLIP, ckpt_dir=ckpt_dir, ckpt_interval=10**9,
+            metrics=["loss", "lr", "grad_norm"], pin_memory=True, nprocs=world, parallel_mode=mode,
+            strategy_kwargs={"label_smoothing": spec["smooth"]}, master_addr=os.environ.get("MASTER_ADDR", "127.0.0.1"),
+            master_port=os.environ.get("MASTER_PORT", "29511"), executor_kwargs=exkw,
         )
 
     results = {}
+    readers = _replicas(spec, world)
+    reader = rank if readers == world else 0  # ranks of one tp / cp block read the same samples
     with setup_parallel(rank, world, local, "nccl", os.environ.get("MASTER_ADDR", "127.0.0.1"),
                         os.environ.get("MASTER_PORT", "29511"), "cuda"):
         dev = torch.device("cuda", local)
         # ---- (1) device-resident inputs: the step itself --------------------------------------------------------
-        n_micro = total_steps * ACCUM
+        n_micro = total_steps * accum
         # one distinct micro-batch per timed / warm-up iteration: nothing repeats inside the run, so the loss stays
         # comparable with the end-to-end arm and with the reference arm (fresh uniform tokens every step)
-        ds = _host_tokens(n_micro * BPD, SEQ, MODEL["vocab_size"], seed=1000 + rank)
+        ds = _host_tokens(n_micro * bpd, seq, vocab, seed=1000 + reader)
         trainer = Trainer(make_config(ds, tempfile.mkdtemp(prefix="bench_ckpt_")), callbacks=[])
         trainer.callbacks = [cb for cb in trainer.callbacks if type(cb).__name__ in ("GradientClippingCallback",)]
         ctx = TrainContextBuilder(trainer.train_config).build()
         ctx.model.train()
-        pool = [{k: ds.data[i * BPD:(i + 1) * BPD, sl].contiguous().to(dev)
-                 for k, sl in (("input_ids", slice(0, SEQ)), ("target_ids", slice(1, SEQ + 1)))} for i in range(n_micro)]
+        pool = [{k: ds.data[i * bpd:(i + 1) * bpd, sl].contiguous().to(dev)
+                 for k, sl in (("input_ids", slice(0, seq)), ("target_ids", slice(1, seq + 1)))} for i in range(n_micro)]
         sampler = ClockSampler(local) if rank == 0 else None
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         for i in range(n_micro):
-            if i == args.warmup * ACCUM:
+            if i == args.warmup * accum:
                 _barrier_sync()
                 if sampler:
                     sampler.start()
@@ -275,17 +338,26 @@ def run_ours(args):
         results["launches"] = native.launch_count() - c0
         results["clocks"] = sampler.stop() if sampler else None
         results["final_loss"] = ctx.loss
+        results["peak_gb"] = round(torch.cuda.max_memory_allocated(dev) / 2**30, 1)
         assert native.kernel_status(dev) == 0, "a kernel's bounded wait expired"
         # a step that produced NaN / Inf runs at low power and high clocks: its timing is not a measurement
         if not math.isfinite(float(results["final_loss"])):
             raise RuntimeError(f"training diverged during the benchmark (loss {results['final_loss']}); no number is reported")
+        if mode in ("tp", "cp", "ep"):  # the symmetric arenas of this context must go before a second one is built
+            from astrai_b200.parallel import context_parallel, expert_parallel, tensor_parallel
+
+            for mod in (tensor_parallel, context_parallel, expert_parallel):
+                mod.set_context(None)
         del ctx, trainer, pool
+        import gc
+
+        gc.collect()
         torch.cuda.empty_cache()
         # ---- (2) end to end through Trainer.train(): host data, pinned H2D per micro-batch, D2H per step -----------
         if not args.skip_e2e:
             # the trainer's sampler deals the dataset out over the ranks: size it so that every rank has all its micro-batches
-            host = _host_tokens((n_micro + 2) * BPD * world, SEQ, MODEL["vocab_size"], seed=100)
-            timer = _StepTimer(args.warmup, args.steps, ACCUM)
+            host = _host_tokens((n_micro + 2) * bpd * readers, seq, vocab, seed=100)
+            timer = _StepTimer(args.warmup, args.steps, accum)
             t2 = Trainer(make_config(host, tempfile.mkdtemp(prefix="bench_ckpt_")), callbacks=[timer])
             # keep the stock callbacks except the ones that write 2 GB checkpoints at exit
             t2.callbacks = [cb for cb in t2.callbacks if type(cb).__name__ not in ("CheckpointCallback", "MetricCallback")]
@@ -294,11 +366,16 @@ def run_ours(args):
             results["e2e_ms"] = timer.ms
     if rank == 0:
         _emit(args, world, results["value_ms"], results.get("e2e_ms"), results["launches"], results["clocks"], "ours",
-              extra={"comm": args.comm, "final_loss": round(float(results["final_loss"]), 4)})
+              extra={"comm": args.comm, "final_loss": round(float(results["final_loss"]), 4), "peak_mem_gb": results["peak_gb"]})
 
 
 # ----------------------------------------------------------------------------------------------- reference arm
 def run_reference(args):
+    if getattr(args, "config", "fsdp1b") != "fsdp1b":
+        mode = _spec(args)["mode"]
+        print(json.dumps({"impl": "reference", "unavailable": f"the reference has no {mode} parallel mode (its modes are none / ddp / fsdp); "
+                          f"the comparison arm of --config {args.config} is this repository's own --comm nccl run"}))
+        return
     ref_root = os.path.join(ROOT, "baseline", "_ref")
     if not os.path.isdir(os.path.join(ref_root, "astrai")):
         print(json.dumps({"impl": "reference", "unavailable": "baseline/_ref/astrai is missing (offline install not present)"}))
@@ -364,7 +441,10 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--comm", default=os.environ.get("ASTRAI_B200_FSDP_COMM", "p2p"), choices=["nccl", "p2p", "nvls"],
-                    help="FSDP transport: fused peer-memory kernels (p2p / nvls) or NCCL collectives")
+                    help="transport: fused peer-memory kernels (p2p; nvls for FSDP) or NCCL collectives around the same math")
+    ap.add_argument("--config", default="fsdp1b", choices=sorted(CONFIGS),
+                    help="fsdp1b: the headline 1B FSDP run; tp8b / cp8b: 8B dense with tensor / context parallelism; "
+                         "ep_moe: MoE + MLA with expert parallelism (these three need >= 2 GPUs)")
     ap.add_argument("--skip-e2e", action="store_true")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 1)

@@ -120,3 +120,36 @@ def test_fused_fsdp_save_and_resume_matches_uninterrupted_run(tmp_path, extra):
     for x, y in zip(res["a"], res["b"]):
         assert abs(x - y) < 2e-2, res
     assert abs(res["a_sum"] - res["b_sum"]) / res["a_sum"] < 1e-3, res
+
+
+def _mp_run(tmp_path, name, nproc, port, *args):
+    out = str(tmp_path / f"{name}.json")
+    script = os.path.join(ROOT, "tests", "workers", "mp_train.py")
+    common = ["--out", out, "--ckpt", str(tmp_path / f"ck_{name}"), "--device", "cuda", "--dtype", "bfloat16", "--seq", "512",
+              "--hidden", "256", "--bpd", "2", *args]
+    if nproc == 1:
+        env = {k: v for k, v in os.environ.items() if k not in ("RANK", "WORLD_SIZE", "LOCAL_RANK", "LOCAL_WORLD_SIZE")}
+        proc = subprocess.run([sys.executable, script, *common], env=env, capture_output=True, text=True, timeout=420, cwd=ROOT)
+        assert proc.returncode == 0, proc.stdout[-3000:] + proc.stderr[-3000:]
+    else:
+        _torchrun(nproc, script, common, port)
+    return json.load(open(out))
+
+
+@pytest.mark.parametrize("mode,moe", [("tp", False), ("cp", False), ("ep", True)])
+def test_model_parallel_trainer_modes_fused_and_collective_arms(tmp_path, mode, moe):
+    """parallel_mode tp / cp / ep through the real Trainer on 2 GPUs in bf16: the fused peer-memory arm and the NCCL arm
+    must both reproduce the single-GPU run (losses, gradient norms, gathered weights with the unsharded keys)."""
+    _need_gpus(2)
+    extra = ["--moe"] if moe else []
+    ref = _mp_run(tmp_path, "ref", 1, 0, "--mode", "none", *extra)
+    base = {"tp": 29720, "cp": 29730, "ep": 29740}[mode]
+    for i, comm in enumerate(("nccl", "p2p")):
+        run = _mp_run(tmp_path, f"{mode}_{comm}", 2, base + i, "--mode", mode, "--comm", comm, *extra)
+        assert run["shapes"] == ref["shapes"], comm
+        for a, b in zip(run["losses"], ref["losses"]):
+            assert abs(a - b) < 3e-2, (comm, run["losses"], ref["losses"])
+        for a, b in zip(run["norms"], ref["norms"]):
+            assert abs(a - b) / max(abs(b), 1e-6) < 5e-2, (comm, run["norms"], ref["norms"])
+        for k, v in ref["sums"].items():
+            assert abs(run["sums"][k] - v) / max(v, 1e-6) < 2e-2, (comm, k)

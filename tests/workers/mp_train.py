@@ -86,6 +86,9 @@ def main():
     bpd = global_batch // dw
     n = global_batch * accum * args.steps
     exkw = {"comm": args.comm} if args.mode in ("tp", "cp", "ep") else {}
+    if args.mode == "cp":  # the gradient / parameter transport and the attention transport are chosen together here
+        exkw["attn_comm"] = args.comm
+        exkw["max_tokens_per_rank"] = bpd * args.seq // max(world // max(dw, 1), 1) * 2
     if args.mode == "ep":
         exkw["tokens_per_rank"] = bpd * args.seq
     tc = TrainConfig(model_fn=model_fn, strategy="seq", dataset=Tokens(n, args.seq, 256),
