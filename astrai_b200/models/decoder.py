@@ -48,13 +48,23 @@ class DecoderBlock(nn.Module):
         self.mlp = FFNFactory.create(ffn_kind(config, layer_id), **kw)
 
     def forward(self, x: Tensor, rotary_emb: Tensor, attention_mask: Optional[Tensor] = None, kv_cache=None,
-                is_causal: bool = False, fwd: Optional[str] = None) -> DecoderOutput:
-        attn = self.attention(self.input_norm(x), rotary_emb, attention_mask, kv_cache, is_causal, fwd)
+                is_causal: bool = False, fwd: Optional[str] = None, pending: Optional[Tensor] = None,
+                defer_residual: bool = False) -> DecoderOutput:
+        """``pending``: the FFN output of the block before this one, not yet added to ``x`` - the add then happens inside
+        this block's first norm kernel.  ``defer_residual``: return this block's FFN output under ``"pending"`` instead
+        of adding it (the caller passes it to the next block, or to the final norm).  A stack of blocks chained this way
+        never runs a separate residual-add kernel; without the two arguments the block is ``x + attn(..) + ffn(..)``."""
+        if pending is not None:
+            x, h0 = self.input_norm(x, residual=pending)
+        else:
+            h0 = self.input_norm(x)
+        attn = self.attention(h0, rotary_emb, attention_mask, kv_cache, is_causal, fwd)
         # residual add and the norm that follows it as one pass over the rows (one kernel on CUDA)
         x, h = ops.add_rms_norm(x, attn, self.post_attention_norm.weight, self.post_attention_norm.norm_eps)
         ffn = self.mlp(h)
-        return {
-            "hidden_states": x + ffn["hidden_states"],
-            "aux_loss": ffn["aux_loss"],
-            "router_stats": ffn.get("router_stats"),
-        }
+        out = {"aux_loss": ffn["aux_loss"], "router_stats": ffn.get("router_stats")}
+        if defer_residual:
+            out["hidden_states"], out["pending"] = x, ffn["hidden_states"]
+        else:
+            out["hidden_states"] = x + ffn["hidden_states"]
+        return out

@@ -43,7 +43,10 @@ class RMSNorm(nn.Module):
         self.weight = nn.Parameter(torch.ones(dim))
         self.norm_eps = norm_eps
 
-    def forward(self, x: Tensor) -> Tensor:
+    def forward(self, x: Tensor, residual: Optional[Tensor] = None):
+        """``rms_norm(x)``; with ``residual`` the pair ``(x + residual, rms_norm(x + residual))`` from one kernel."""
+        if residual is not None:
+            return ops.add_rms_norm(x, residual, self.weight, self.norm_eps)
         return ops.rms_norm(x, self.weight, self.norm_eps)
 
 

@@ -26,8 +26,8 @@ from astrai_b200.models.layers import Embedding, Linear, RMSNorm, RotaryEmbeddin
 
 def expand_mask(mask: Optional[Tensor]) -> Optional[Tensor]:
     """[B,S] -> [B,1,1,S] (key padding); [B,S,S] -> [B,1,S,S]; 4-D unchanged."""
-    if mask is None or mask.dim() == 4:
-        return mask
+    if mask is None or not isinstance(mask, Tensor) or mask.dim() == 4:
+        return mask  # run boundaries (AttentionSegments) travel to the attention op as they are
     return mask[:, None, None, :] if mask.dim() == 2 else mask[:, None]
 
 
@@ -94,17 +94,21 @@ class AutoRegressiveLM(AutoModel):
         mask = expand_mask(input_mask)
         causal = mask is None
         aux, stats = [], []
+        pending = None  # FFN output of the previous block: added inside the next norm kernel, never on its own
         for i, layer in enumerate(self.layers):
             if trace.enabled():
                 with trace.range(f"layer{i}"):
-                    out = layer(x, rotary, mask, kv_cache, causal, fwd)
+                    out = layer(x, rotary, mask, kv_cache, causal, fwd, pending=pending, defer_residual=True)
             else:
-                out = layer(x, rotary, mask, kv_cache, causal, fwd)
-            x = out["hidden_states"]
+                out = layer(x, rotary, mask, kv_cache, causal, fwd, pending=pending, defer_residual=True)
+            x, pending = out["hidden_states"], out["pending"]
             if out.get("router_stats") is not None:
                 aux.append(out["aux_loss"])
                 stats.append(out["router_stats"])
-        hidden = self.norm(x)
+        if pending is not None:
+            _, hidden = self.norm(x, residual=pending)  # through the module: wrappers hook its call to ready the weight
+        else:
+            hidden = self.norm(x)
         result: Dict[str, Any] = {"hidden_states": hidden}
         if return_logits:
             result["logits"] = self.lm_head(hidden)

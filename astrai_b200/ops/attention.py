@@ -46,9 +46,29 @@ def _sdpa_ctx():
     return sdpa_kernel(_SDPA_BACKENDS, set_priority=True)
 
 
-def dense_attention(q: Tensor, k: Tensor, v: Tensor, mask: Optional[Tensor] = None, causal: bool = False,
+def dense_attention(q: Tensor, k: Tensor, v: Tensor, mask=None, causal: bool = False,
                     scale: Optional[float] = None) -> Tensor:
-    """Softmax attention with GQA head sharing; returns ``[B,S,Hq,Dv]``."""
+    """Softmax attention with GQA head sharing; returns ``[B,S,Hq,Dv]``.  ``mask`` is a boolean tensor (True = attend)
+    or an :class:`~astrai_b200.ops.segments.AttentionSegments` (causal inside runs of tokens), which runs on the
+    variable-length flash kernels."""
+    from astrai_b200.ops.segments import AttentionSegments
+
+    if isinstance(mask, AttentionSegments):
+        seg = mask
+        from astrai_b200.parallel import context_parallel as cpar_
+
+        cp_ = cpar_.get_context()
+        if cp_ is not None and cp_.active:
+            raise RuntimeError("context parallelism is on: packed-document / padded batches are not sequence-sharded")
+        b, s = q.shape[0], q.shape[1]
+        if (q.is_cuda and _use_flash() and flash.supported(q, k, v) and k.shape[1] == s
+                and (b, s) == (seg.batch, seg.seq_len)):
+            cu = seg.cu_seqlens(q.device)
+            out = flash.flash_attention_varlen(q.reshape(b * s, *q.shape[2:]), k.reshape(b * s, *k.shape[2:]),
+                                               v.reshape(b * s, *v.shape[2:]), cu, cu, seg.max_len, seg.max_len,
+                                               causal=True, scale=scale)
+            return out.view(b, s, *out.shape[1:])
+        mask, causal = seg.to_dense(q.device), False
     from astrai_b200.parallel import context_parallel as cpar
 
     cp = cpar.get_context()

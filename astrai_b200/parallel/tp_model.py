@@ -135,9 +135,11 @@ def _tp_forward(self, input_ids: Tensor, input_mask: Optional[Tensor] = None, kv
     rotary = self.rotary_embedding.freqs_cis[position_ids]  # [B, S, d/2, 2]: attention sees every token of the batch
     mask = expand_mask(input_mask)
     causal = mask is None
+    pending = None
     for layer in self.layers:
-        x = layer(x, rotary, mask, None, causal, None)["hidden_states"]
-    hidden = self.norm(x)
+        out = layer(x, rotary, mask, None, causal, None, pending=pending, defer_residual=True)
+        x, pending = out["hidden_states"], out["pending"]
+    _, hidden = self.norm(x, residual=pending)
     out = {"hidden_states": hidden}
     if return_logits:
         out["logits"] = self.lm_head(hidden)

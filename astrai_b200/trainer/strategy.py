@@ -19,6 +19,7 @@ from torch import Tensor
 
 from astrai_b200 import ops
 from astrai_b200.factory import BaseFactory
+from astrai_b200.ops.segments import AttentionSegments, from_position_ids, from_valid_mask
 from astrai_b200.parallel.executor import broadcast_state_dict
 
 if TYPE_CHECKING:
@@ -86,7 +87,9 @@ def _head_weight(inner) -> Tensor:
 def token_logprobs(model, input_ids: Tensor, input_mask: Optional[Tensor], position_ids: Optional[Tensor] = None):
     """Log-probability of ``input_ids[:, 1:]`` under the model, shape ``[B, S-1]`` fp32, plus the forward outputs."""
     ids_in, ids_out = input_ids[:, :-1], input_ids[:, 1:]
-    if input_mask is not None:
+    if isinstance(input_mask, AttentionSegments):
+        input_mask = input_mask.drop_last()
+    elif input_mask is not None:
         input_mask = input_mask[:, :, :-1, :-1] if input_mask.dim() == 4 else input_mask[:, :-1]
     inner = _fused_head(model)
     if inner is not None and ids_in.is_cuda:
@@ -128,6 +131,19 @@ def causal_padding_mask(key_valid: Tensor) -> Tensor:
     s = key_valid.shape[-1]
     causal = torch.ones(s, s, dtype=torch.bool, device=key_valid.device).tril()
     return key_valid.bool()[:, None, None, :] & causal[None, None]
+
+
+def doc_attention(position_ids: Tensor):
+    """Attention restriction of a packed SFT batch: run boundaries for the variable-length flash kernels (no O(S^2)
+    mask); the dense mask of :func:`make_doc_boundary_mask` is the same relation."""
+    return from_position_ids(position_ids)
+
+
+def padded_causal_attention(key_valid: Tensor):
+    """Attention restriction of a padded batch (DPO / GRPO): run boundaries when every row's real tokens are contiguous
+    (left and / or right padding), else the dense mask of :func:`causal_padding_mask` (padding inside a row)."""
+    seg = from_valid_mask(key_valid)
+    return seg if seg is not None else causal_padding_mask(key_valid)
 
 
 def moe_diagnostics(router_stats_list) -> Dict[str, Tensor]:
@@ -251,10 +267,11 @@ class SFTStrategy(_TokenCEStrategy):
     """Cross-entropy on positions where ``loss_mask`` is set; attention stays inside each packed document."""
 
     def compute_loss_output(self, batch) -> LossOutput:
+        attn = doc_attention(batch["position_ids"])  # from the host copy of the batch: no device round trip
         batch = self._to_rank(batch)
         pos = batch["position_ids"]
         targets = batch["target_ids"].masked_fill(~batch["loss_mask"].bool(), -100)
-        return self._ce(batch["input_ids"], targets, position_ids=pos, input_mask=make_doc_boundary_mask(pos))
+        return self._ce(batch["input_ids"], targets, position_ids=pos, input_mask=attn)
 
 
 @StrategyFactory.register("dpo")
@@ -266,11 +283,13 @@ class DPOStrategy(BaseStrategy):
         self.ref_model, self.beta, self.reduction = ref_model, beta, reduction
 
     def compute_loss_output(self, batch) -> LossOutput:
+        mask = padded_causal_attention(torch.cat([batch["chosen"], batch["rejected"]], dim=0).ne(0))
         batch = self._to_rank(batch)
         n = batch["chosen"].shape[0]
         ids = torch.cat([batch["chosen"], batch["rejected"]], dim=0)
         loss_mask = torch.cat([batch["chosen_mask"], batch["rejected_mask"]], dim=0)
-        mask = causal_padding_mask(ids.ne(0))
+        if isinstance(mask, Tensor):
+            mask = mask.to(ids.device)
         pol = get_logprobs(self.model, ids, mask, loss_mask, self.reduction)
         with torch.no_grad():
             ref = get_logprobs(self.ref_model, ids, mask, loss_mask, self.reduction)["logprobs"]
@@ -321,7 +340,9 @@ class GRPOStrategy(BaseStrategy):
         plen = prompt.shape[1]
         seq = torch.cat([prompt, resp], dim=-1)
         loss_mask = torch.cat([torch.zeros_like(prompt, dtype=torch.bool), rmask.bool()], dim=-1)
-        attn = causal_padding_mask(torch.cat([pmask.bool(), rmask.bool()], dim=-1))
+        attn = padded_causal_attention(torch.cat([pmask.bool(), rmask.bool()], dim=-1))
+        if isinstance(attn, Tensor):
+            attn = attn.to(seq.device)
 
         def response_logprobs(model):
             out = get_logprobs(model, seq, attn, loss_mask, "none")

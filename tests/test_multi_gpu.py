@@ -126,7 +126,7 @@ def _mp_run(tmp_path, name, nproc, port, *args):
     out = str(tmp_path / f"{name}.json")
     script = os.path.join(ROOT, "tests", "workers", "mp_train.py")
     common = ["--out", out, "--ckpt", str(tmp_path / f"ck_{name}"), "--device", "cuda", "--dtype", "bfloat16", "--seq", "512",
-              "--hidden", "256", "--bpd", "2", *args]
+              "--hidden", "256", "--bpd", "2", "--lr", "1e-3", *args]
     if nproc == 1:
         env = {k: v for k, v in os.environ.items() if k not in ("RANK", "WORLD_SIZE", "LOCAL_RANK", "LOCAL_WORLD_SIZE")}
         proc = subprocess.run([sys.executable, script, *common], env=env, capture_output=True, text=True, timeout=420, cwd=ROOT)

@@ -291,3 +291,22 @@ def test_fsdp_torch_impl_two_ranks_cpu(tmp_path):
                         model_fn=_model_untied)
     Trainer(cfg).train()
     assert latest_complete(tmp_path) is not None
+
+
+def test_attention_segments_equal_the_reference_masks():
+    """Run boundaries built on the host describe the same relation as the reference's dense boolean masks."""
+    from astrai_b200.ops.segments import from_position_ids, from_valid_mask
+    from astrai_b200.trainer.strategy import causal_padding_mask, make_doc_boundary_mask
+
+    pos = torch.tensor([[0, 1, 2, 0, 1, 0, 1, 2], [0, 1, 2, 3, 4, 5, 6, 7]])
+    seg = from_position_ids(pos)
+    assert seg.bounds == [0, 3, 5, 8, 16] and seg.max_len == 8 and seg.n_runs == 4
+    assert torch.equal(seg.to_dense(), make_doc_boundary_mask(pos))
+    short = seg.drop_last()
+    assert short.seq_len == 7 and torch.equal(short.to_dense(), make_doc_boundary_mask(pos)[:, :, :-1, :-1])
+    valid = torch.tensor([[0, 0, 1, 1, 1, 0], [1, 1, 1, 1, 1, 1]]).bool()
+    seg = from_valid_mask(valid)
+    dense, ref = seg.to_dense(), causal_padding_mask(valid)
+    rows = valid[:, None, :, None].expand_as(ref)
+    assert torch.equal(dense[rows], ref[rows])  # identical for every real query token (padding rows are never read)
+    assert from_valid_mask(torch.tensor([[1, 0, 1]]).bool()) is None  # padding in the middle: no run form

@@ -55,6 +55,7 @@ def main():
     ap.add_argument("--bpd", type=int, default=2)
     ap.add_argument("--steps", type=int, default=3)
     ap.add_argument("--dtype", default="float32")
+    ap.add_argument("--lr", type=float, default=1e-2)
     args = ap.parse_args()
 
     from astrai_b200.config import AutoRegressiveLMConfig, TrainConfig
@@ -92,7 +93,7 @@ def main():
     if args.mode == "ep":
         exkw["tokens_per_rank"] = bpd * args.seq
     tc = TrainConfig(model_fn=model_fn, strategy="seq", dataset=Tokens(n, args.seq, 256),
-                     optimizer_fn=lambda m: FusedAdamW(m.parameters(), lr=1e-2, weight_decay=0.0),
+                     optimizer_fn=lambda m: FusedAdamW(m.parameters(), lr=args.lr, weight_decay=0.0),
                      batch_per_device=bpd, grad_accum_steps=accum, ckpt_dir=args.ckpt, ckpt_interval=10**6,
                      device_type="cuda" if cuda else "cpu", backend="nccl" if cuda else "gloo", nprocs=world,
                      parallel_mode=args.mode, tp_size=args.size or 1, cp_size=args.size or 1, ep_size=args.size or 1,
