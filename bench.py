@@ -249,6 +249,8 @@ def _emit(args, world, value_ms, e2e_ms, launches, clocks, impl, extra=None, not
         "gpu_launches": launches,
     }
     line.update(extra or {})  # run facts that are not part of the benchmark's configuration (transport, last loss)
+    if getattr(args, "smoke_layers", 0):
+        line["invalid"] = f"smoke run with {args.smoke_layers} layers instead of the configuration's model"
     if note:
         line["note"] = note
     print(json.dumps(line), flush=True)
@@ -272,7 +274,7 @@ def run_ours(args):
     seq, bpd, accum, mode = spec["seq"], spec["bpd"], spec["accum"], spec["mode"]
     if mode in ("tp", "cp", "ep") and world < 2:
         raise SystemExit(f"--config {args.config} is a model-parallel configuration: launch it on 2 or more GPUs")
-    cfg = AutoRegressiveLMConfig(**spec["model"])
+    cfg = AutoRegressiveLMConfig(**dict(spec["model"], **({"num_hidden_layers": args.smoke_layers} if args.smoke_layers else {})))
     vocab = spec["model"]["vocab_size"]
     total_steps = args.warmup + args.steps
     big = cfg.hidden_size * cfg.num_hidden_layers >= 100_000  # 8B class: build on the GPU, the host would take minutes
@@ -434,7 +436,27 @@ def run_reference(args):
         _emit(args, world, None, timer.ms, 0, getattr(timer, "clocks", None), "reference", note=note)
 
 
+def _json_only_stdout():
+    """Libraries print to stdout at times (NCCL's version banner); the contract is ONE JSON line there.  Everything
+    written to file descriptor 1 from now on goes to stderr; ``print(json...)`` uses the saved descriptor."""
+    import builtins
+
+    real = os.fdopen(os.dup(1), "w")
+    os.dup2(2, 1)
+    sys.stdout = sys.stderr
+    plain_print = builtins.print
+
+    def emit(*a, **k):
+        if a and isinstance(a[0], str) and a[0].startswith("{") and "file" not in k:
+            k["file"] = real
+            k["flush"] = True
+        return plain_print(*a, **k)
+
+    builtins.print = emit
+
+
 def main():
+    _json_only_stdout()
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=6)
@@ -446,6 +468,8 @@ def main():
                     help="fsdp1b: the headline 1B FSDP run; tp8b / cp8b: 8B dense with tensor / context parallelism; "
                          "ep_moe: MoE + MLA with expert parallelism (these three need >= 2 GPUs)")
     ap.add_argument("--skip-e2e", action="store_true")
+    ap.add_argument("--smoke-layers", type=int, default=0,
+                    help="debugging aid: cut the model to this many layers (the line is then marked invalid, it is not a result)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 1)
     if args.impl == "reference":
