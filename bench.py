@@ -436,6 +436,65 @@ def run_reference(args):
         _emit(args, world, None, timer.ms, 0, getattr(timer, "clocks", None), "reference", note=note)
 
 
+# ----------------------------------------------------------------------------------------------- serving mode
+def run_serve_mode(args):
+    """``--mode serve``: the continuous-batching load test of the 1B model (paged KV cache with 16-token pages, radix prefix
+    cache, Poisson arrivals, log-normal prompts, 8 shared 1024-token prefixes, uniform output lengths, temperature 0.8 /
+    top-p 0.95 / top-k 50, seed 0) through the scheduler's public API, for this framework or (``--impl reference``) for the
+    unmodified reference package with the same request stream and the same ``max_batch_size``."""
+    import torch
+
+    from astrai_b200.cli import benchmark as B
+
+    common = dict(n_requests=args.requests, rate=args.rate, max_batch_size=args.max_batch_size, max_seq_len=8192,
+                  kv_cache_tokens=None, temperature=0.8, top_p=0.95, top_k=50, seed=0, time_scale=1.0)
+    if args.impl == "reference":
+        ref_root = os.path.join(ROOT, "baseline", "_ref")
+        if not os.path.isdir(os.path.join(ref_root, "astrai")):
+            print(json.dumps({"impl": "reference", "unavailable": "baseline/_ref/astrai is missing (offline install not present)"}))
+            return
+        sys.path.insert(0, ref_root)
+        import glob
+
+        built = glob.glob(os.path.join(ref_root, "astrai", "extension", "lib", "*.so"))
+        backend = args.ref_backend or ("cuda" if built else "flash")
+        res = B._serve_reference("1b", "cuda", backend=backend, **common)
+        launches = 0
+    else:
+        from astrai_b200.inference import InferenceScheduler
+        from astrai_b200.ops import native
+
+        native.require()
+        model = B.build_model("1b", "cuda", torch.bfloat16)
+        sched = InferenceScheduler(model, B._IdTokenizer(), max_batch_size=args.max_batch_size, max_seq_len=8192, page_size=16,
+                                   kv_cache_tokens=args.max_batch_size * 4608, paged=True, chunked_prefill=True,
+                                   max_prefill_tokens=8192)
+        reqs = B.make_requests(args.requests, args.rate, model.config.vocab_size, 0)
+        sched.run_batch([reqs[0]["ids"][:64]], max_tokens=4, temperature=0.0)  # warm-up (kernel load, graph capture)
+        c0 = native.launch_count()
+        sched.start()
+        try:
+            res = B.run_serve(sched, reqs, 0.8, 0.95, 50, 1.0)
+        finally:
+            sched.stop()
+        launches = native.launch_count() - c0
+        backend = "tcgen05"
+    line = {
+        "metric": "serve out tok/s (1B dense, paged KV 16 + radix, Poisson arrivals)", "value": res["output_tok_per_s"],
+        "unit": "tokens/s", "n_gpus": 1, "steps": args.requests, "warmup": 1, "ms_per_step": None, "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "impl": args.impl,
+        "data": "synthetic request stream (seed 0), random-init weights",
+        "ttft_ms_p50": res["ttft_ms_p50"], "ttft_ms_p99": res["ttft_ms_p99"], "tpot_ms_p50": res["tpot_ms_p50"],
+        "completed": res["completed"], "wall_s": res["wall_s"], "output_tokens": res["output_tokens"],
+        "prompt_tokens": res["prompt_tokens"], "gpu_launches": launches,
+        "config": {"model": CONFIGS["fsdp1b"]["label"], "requests": args.requests, "rate_req_per_s": args.rate,
+                   "max_batch_size": args.max_batch_size, "page_size": 16, "prefix_cache": "radix", "attention_backend": backend,
+                   "prompt_len": "lognormal mean 512 sigma 0.6 in [16, 4096]; half share one of 8 prefixes of 1024",
+                   "output_len": "uniform [64, 512]", "sampling": "temperature 0.8 top_p 0.95 top_k 50 seed 0"},
+    }
+    print(json.dumps(line), flush=True)
+
+
 def _json_only_stdout():
     """Libraries print to stdout at times (NCCL's version banner); the contract is ONE JSON line there.  Everything
     written to file descriptor 1 from now on goes to stderr; ``print(json...)`` uses the saved descriptor."""
@@ -470,8 +529,23 @@ def main():
     ap.add_argument("--skip-e2e", action="store_true")
     ap.add_argument("--smoke-layers", type=int, default=0,
                     help="debugging aid: cut the model to this many layers (the line is then marked invalid, it is not a result)")
+    ap.add_argument("--mode", default="train", choices=["train", "serve"],
+                    help="serve: the continuous-batching load test (1 GPU) instead of a training step")
+    ap.add_argument("--requests", type=int, default=2048)
+    ap.add_argument("--rate", type=float, default=32.0, help="serve: Poisson arrival rate, requests per second")
+    ap.add_argument("--max-batch-size", type=int, default=128)
+    ap.add_argument("--ref-backend", default=None, help="serve, reference arm: its attention backend (default: cuda if built, else flash)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 1)
+    if args.mode == "serve":
+        try:
+            run_serve_mode(args)
+        except Exception as exc:  # noqa: BLE001
+            if args.impl != "reference":
+                raise
+            why = f"the reference's own serving path failed on this box: {type(exc).__name__}: {exc}"
+            print(json.dumps({"impl": "reference", "unavailable": " ".join(why.split())[:300]}), flush=True)
+        return
     if args.impl == "reference":
         try:
             run_reference(args)
