@@ -107,11 +107,12 @@ class PagePool:
                 ti += list(range(n))
             tile_b, tile_i = ws.put_int(ws.q_tile_to_batch, tb), ws.put_int(ws.q_tile_to_index, ti)
             gather = None
-            if self.device.type == "cuda":  # one index for "all keys of the batch": K/V are gathered once per layer
+            in_place = not self.contiguous and self.page_size in (8, 16, 32, 64)  # the prefill kernel walks the table itself
+            if self.device.type == "cuda" and not in_place:  # one index for "all keys of the batch": gathered once per layer
                 gather = torch.cat([host[r, :n] for r, n in zip(req_indices, seq_lens)]).to(torch.int64).to(self.device, non_blocking=True)
             return KVCache(self._storage.k_buffer, self._storage.v_buffer, self._req_pool.req_to_token, rows, lens_t,
                            out_cache_loc, max(seq_lens), kv_indptr, qo, tile_b, tile_i, q_lens=q_lens, kv_lens=list(seq_lens),
-                           kv_gather_loc=gather)
+                           kv_gather_loc=gather, page_size=1 if self.contiguous else self.page_size)
         loc = [int(host[r, n - 1]) for r, n in zip(req_indices, seq_lens)]
         out_cache_loc = ws.put_int(ws.out_cache_loc, loc)
         ws.qo_indptr[: b + 1].copy_(ws.inc[: b + 1])

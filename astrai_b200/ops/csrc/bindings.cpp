@@ -362,6 +362,37 @@ std::tuple<Tensor, Tensor> flash_fwd(const Tensor& q, const Tensor& k, const Ten
   return {out, lse};
 }
 
+// Prefill over the paged KV pool without gathering: q [Tq, Hq, D] packed queries (cu_q), k_pool / v_pool [n_slots, Hkv, D],
+// kv_lens through cu_k (differences), slot table [rows, max_ctx] + req_pool_indices [batch]; causal is lower-right aligned.
+Tensor flash_fwd_paged(const Tensor& q, const Tensor& k_pool, const Tensor& v_pool, const Tensor& cu_q, const Tensor& cu_k,
+                       const Tensor& table, const Tensor& rows, int64_t page, int64_t max_q, bool causal, double scale) {
+  auto ok = [](const Tensor& t) {
+    return t.is_cuda() && t.dim() == 3 && t.scalar_type() == at::kBFloat16 && t.stride(2) == 1 && t.stride(1) == t.size(2) &&
+           t.stride(0) % 8 == 0 && (reinterpret_cast<uintptr_t>(t.data_ptr()) & 15) == 0;
+  };
+  TORCH_CHECK(ok(q) && ok(k_pool) && ok(v_pool), "flash_fwd_paged: bf16 [tokens, heads, D] tensors with adjacent heads, 16-byte aligned");
+  TORCH_CHECK(k_pool.sizes() == v_pool.sizes() && q.size(2) == k_pool.size(2), "flash_fwd_paged: shape mismatch");
+  const int D = (int)q.size(2);
+  TORCH_CHECK(D == 64 || D == 128, "flash_fwd_paged: head_dim must be 64 or 128");
+  TORCH_CHECK(page == 8 || page == 16 || page == 32 || page == 64, "flash_fwd_paged: page size must be 8, 16, 32 or 64");
+  const int64_t batch = cu_q.numel() - 1;
+  TORCH_CHECK(cu_q.is_cuda() && cu_q.scalar_type() == at::kInt && cu_k.is_cuda() && cu_k.scalar_type() == at::kInt &&
+              cu_k.numel() == batch + 1 && batch >= 1, "flash_fwd_paged: cu_q / cu_k int32 [batch+1]");
+  TORCH_CHECK(table.is_cuda() && table.scalar_type() == at::kInt && table.dim() == 2 && table.is_contiguous() &&
+              rows.is_cuda() && rows.scalar_type() == at::kInt && rows.numel() >= batch, "flash_fwd_paged: table int32 [rows, ctx], rows int32 [batch]");
+  const c10::cuda::CUDAGuard guard(q.device());
+  Tensor out = at::empty({q.size(0), q.size(1), q.size(2)}, q.options());
+  ab::PagedKv pg;
+  pg.table = table.data_ptr<int>(), pg.rows = rows.data_ptr<int>(), pg.stride = table.size(1), pg.page = (int)page;
+  count();
+  const int rc = ab::flash_fwd(q.data_ptr(), k_pool.data_ptr(), v_pool.data_ptr(), out.data_ptr(), nullptr, cu_q.data_ptr<int>(),
+                               cu_k.data_ptr<int>(), (int)batch, 0, 0, (int)max_q, q.size(0), k_pool.size(0), (int)q.size(1),
+                               (int)k_pool.size(1), D, q.stride(0), k_pool.stride(0), v_pool.stride(0), out.stride(0), (float)scale,
+                               causal, status_tensor(q.device()).data_ptr<int>(), stream(), nullptr, &pg);
+  TORCH_CHECK(rc == 0, "flash_fwd_paged launch failed with code ", rc);
+  return out;
+}
+
 std::tuple<Tensor, Tensor, Tensor> flash_bwd(const Tensor& q, const Tensor& k, const Tensor& v, const Tensor& out,
                                              const Tensor& dout, const Tensor& lse, const c10::optional<Tensor>& cu_q,
                                              const c10::optional<Tensor>& cu_k, int64_t batch, int64_t sq, int64_t sk,
@@ -980,6 +1011,7 @@ TORCH_LIBRARY(astrai_b200, m) {
   m.def("comm_wait_flags_(Tensor local_flags, int kind, int world, int skip_rank, int unit, int max_units, int epoch, float timeout_s) -> ()", &comm_wait_flags_);
   m.def("kernel_status_reset(Tensor like) -> ()", &kernel_status_reset);
   m.def("flash_fwd(Tensor q, Tensor k, Tensor v, Tensor? cu_q, Tensor? cu_k, int batch, int sq, int sk, int max_q, bool causal, float scale) -> (Tensor, Tensor)", &flash_fwd);
+  m.def("flash_fwd_paged(Tensor q, Tensor k_pool, Tensor v_pool, Tensor cu_q, Tensor cu_k, Tensor table, Tensor rows, int page, int max_q, bool causal, float scale) -> Tensor", &flash_fwd_paged);
   m.def("flash_bwd(Tensor q, Tensor k, Tensor v, Tensor out, Tensor dout, Tensor lse, Tensor? cu_q, Tensor? cu_k, int batch, int sq, int sk, int max_q, int max_k, bool causal, float scale) -> (Tensor, Tensor, Tensor)", &flash_bwd);
   m.def("cp_flash_fwd(Tensor q, Tensor k_full, Tensor v_full, int batch, int chunk, int world, int rank, float scale, int[] kv_src_ptrs, int[] flag_ptrs, int unit, int max_units, int epoch, int n_copy_ctas, Tensor? chunk_state, float timeout_s) -> (Tensor, Tensor)", &cp_flash_fwd);
   m.def("cp_flash_bwd(Tensor q, Tensor k_full, Tensor v_full, Tensor out, Tensor dout, Tensor lse, int batch, int chunk, int world, int rank, float scale, int[] stage_ptrs, int[] flag_ptrs, int unit, int max_units, int epoch, Tensor? tile_counter, float timeout_s) -> (Tensor, Tensor, Tensor)", &cp_flash_bwd);

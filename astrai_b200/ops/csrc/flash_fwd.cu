@@ -151,7 +151,7 @@ __device__ void gather_kv(const CpAttn& cp, int cta, int row_bytes, int* status)
 // One unit of work of the persistent forward kernel: a 128-row query tile of one head of one sequence.
 struct FwdItem {
   SeqInfo si;
-  int h, kvh, q0, off, n_kv;
+  int h, kvh, q0, off, n_kv, b;
 };
 // Work items are numbered heaviest first: item w covers (head x sequence) w % nbx and the (w / nbx)-th query tile counted
 // from the end of the sequence (under a causal mask the last tile sees the most keys).  Returns false when the sequence
@@ -160,7 +160,8 @@ __device__ __forceinline__ bool fwd_item(int w, int nbx, const int* cu_q, const 
                                          int causal, const CpAttn& cp, FwdItem& im) {
   const int bx = w % nbx, by = w / nbx;
   im.h = bx % Hq;
-  im.si = seq_info(cu_q, cu_k, bx / Hq, sq, sk);
+  im.b = bx / Hq;
+  im.si = seq_info(cu_q, cu_k, im.b, sq, sk);
   if (cp.world > 1) im.si.k_len = cp.k_vis;
   const int qt = (im.si.q_len + BQ - 1) / BQ - 1 - by;
   if (qt < 0) return false;
@@ -185,7 +186,7 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
                  const __grid_constant__ CUtensorMap map_v, __nv_bfloat16* __restrict__ O, float* __restrict__ lse,
                  const int* __restrict__ cu_q, const int* __restrict__ cu_k, int sq, int sk, int Hq, int Hkv, int nbx,
                  int n_items, long long o_row_stride, long long total_q, float scale_log2, int causal,
-                 int* __restrict__ status, const CpAttn cp) {
+                 int* __restrict__ status, const CpAttn cp, const PagedKv pg) {
   using C = FwdCfg<D>;
   const bool gather = cp.world > 1 && cp.kv_src[0] != nullptr;
   const int n_copy = gather ? cp.n_copy_ctas : 0;
@@ -265,14 +266,41 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
           }
           if (!mbar_wait(BAR(KE + st), ph, abort_flag)) { ok = false; break; }
           mbar_expect_tx(BAR(KF + st), C::KV_BYTES);
+          if (pg.table == nullptr) {
 #pragma unroll
-          for (int kb = 0; kb < C::NB; ++kb)
-            tma_load_2d(k_smem + st * C::KV_BYTES + kb * KBLK_BYTES, &map_k, BAR(KF + st), im.kvh * D + kb * 64, im.si.k_start + j * BKV);
+            for (int kb = 0; kb < C::NB; ++kb)
+              tma_load_2d(k_smem + st * C::KV_BYTES + kb * KBLK_BYTES, &map_k, BAR(KF + st), im.kvh * D + kb * 64, im.si.k_start + j * BKV);
+          }
+          // Paged pool: the tile's keys live in 64 / page pages; each page is `page` consecutive pool rows whose first
+          // slot the table names.  Pages past the end of the sequence load slot 0 (their scores are masked anyway).
+          int slot_of[BKV / 8];
+          if (pg.table != nullptr) {
+            const int* trow = pg.table + (long long)pg.rows[im.b] * pg.stride;
+            const int subs = BKV / pg.page;
+            for (int sp = 0; sp < subs; ++sp) {
+              const int t = j * BKV + sp * pg.page;
+              slot_of[sp] = t < im.si.k_len ? trow[t] : 0;
+            }
+            for (int sp = 0; sp < subs; ++sp)
+#pragma unroll
+              for (int kb = 0; kb < C::NB; ++kb)
+                tma_load_2d(k_smem + st * C::KV_BYTES + kb * KBLK_BYTES + sp * pg.page * 128, &map_k, BAR(KF + st),
+                            im.kvh * D + kb * 64, slot_of[sp]);
+          }
           if (!mbar_wait(BAR(VE + st), ph, abort_flag)) { ok = false; break; }
           mbar_expect_tx(BAR(VF + st), C::KV_BYTES);
+          if (pg.table == nullptr) {
 #pragma unroll
-          for (int kb = 0; kb < C::NB; ++kb)
-            tma_load_2d(v_smem + st * C::KV_BYTES + kb * KBLK_BYTES, &map_v, BAR(VF + st), im.kvh * D + kb * 64, im.si.k_start + j * BKV);
+            for (int kb = 0; kb < C::NB; ++kb)
+              tma_load_2d(v_smem + st * C::KV_BYTES + kb * KBLK_BYTES, &map_v, BAR(VF + st), im.kvh * D + kb * 64, im.si.k_start + j * BKV);
+          } else {
+            const int subs = BKV / pg.page;
+            for (int sp = 0; sp < subs; ++sp)
+#pragma unroll
+              for (int kb = 0; kb < C::NB; ++kb)
+                tma_load_2d(v_smem + st * C::KV_BYTES + kb * KBLK_BYTES + sp * pg.page * 128, &map_v, BAR(VF + st),
+                            im.kvh * D + kb * 64, slot_of[sp]);
+          }
         }
         ++tq;
       }
@@ -503,7 +531,8 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
 template <int D>
 int launch_fwd(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, void* O, float* lse, const int* cu_q,
                const int* cu_k, int batch, int sq, int sk, int max_q, int Hq, int Hkv, long long o_row_stride,
-               long long total_q, float scale, bool causal, int* status, cudaStream_t st, const CpAttn& cp) {
+               long long total_q, float scale, bool causal, int* status, cudaStream_t st, const CpAttn& cp,
+               const PagedKv& pg) {
   auto kern = flash_fwd_kernel<D>;
   static bool configured = false;
   if (!configured) {
@@ -525,7 +554,7 @@ int launch_fwd(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& 
   const dim3 grid(n_persist + n_copy, 1, 1);
   kern<<<grid, FA_THREADS, FwdCfg<D>::SMEM, st>>>(mq, mk, mv, (__nv_bfloat16*)O, lse, cu_q, cu_k, sq, sk, Hq, Hkv, nbx, n_items,
                                                   o_row_stride, total_q, scale * 1.4426950408889634f, causal ? 1 : 0,
-                                                  status, cp);
+                                                  status, cp, pg);
   return cudaGetLastError() == cudaSuccess ? 0 : -5;
 }
 
@@ -534,8 +563,15 @@ int launch_fwd(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& 
 int flash_fwd(const void* q, const void* k, const void* v, void* out, float* lse, const int* cu_q, const int* cu_k,
               int batch, int sq, int sk, int max_q, long long total_q, long long total_k, int Hq, int Hkv, int D,
               long long q_row_stride, long long k_row_stride, long long v_row_stride, long long o_row_stride, float scale,
-              bool causal, int* status, cudaStream_t st, const CpAttn* cp_in) {
+              bool causal, int* status, cudaStream_t st, const CpAttn* cp_in, const PagedKv* paged) {
   if (batch <= 0 || total_q <= 0) return 0;
+  PagedKv pg;
+  if (paged != nullptr && paged->table != nullptr) {
+    pg = *paged;
+    // the key counts must come from cu_k; a page is a whole number of 8-row swizzle atoms and divides the 64-key tile
+    if (!cu_k || !pg.rows || pg.stride <= 0 || (pg.page != 8 && pg.page != 16 && pg.page != 32 && pg.page != 64)) return -10;
+    if (cp_in != nullptr && cp_in->world > 1) return -10;
+  }
   if (Hkv <= 0 || Hq % Hkv) return -1;
   if (D != 64 && D != 128) return -3;
   CpAttn cp;
@@ -553,13 +589,14 @@ int flash_fwd(const void* q, const void* k, const void* v, void* out, float* lse
   }
   CUtensorMap mq, mk, mv;
   if (!cache().get(&mq, q, (long long)Hq * D, total_q, q_row_stride, 64, 128)) return -1000 - g_last_map_error;
-  if (!cache().get(&mk, k, (long long)Hkv * D, total_k, k_row_stride, 64, BKV)) return -2000 - g_last_map_error;
-  if (!cache().get(&mv, v, (long long)Hkv * D, total_k, v_row_stride, 64, BKV)) return -3000 - g_last_map_error;
+  const int kv_box_rows = pg.table != nullptr ? pg.page : BKV;
+  if (!cache().get(&mk, k, (long long)Hkv * D, total_k, k_row_stride, 64, kv_box_rows)) return -2000 - g_last_map_error;
+  if (!cache().get(&mv, v, (long long)Hkv * D, total_k, v_row_stride, 64, kv_box_rows)) return -3000 - g_last_map_error;
   if (D == 128)
     return launch_fwd<128>(mq, mk, mv, out, lse, cu_q, cu_k, batch, sq, sk, max_q, Hq, Hkv, o_row_stride, total_q, scale,
-                           causal, status, st, cp);
+                           causal, status, st, cp, pg);
   return launch_fwd<64>(mq, mk, mv, out, lse, cu_q, cu_k, batch, sq, sk, max_q, Hq, Hkv, o_row_stride, total_q, scale,
-                        causal, status, st, cp);
+                        causal, status, st, cp, pg);
 }
 
 }  // namespace ab

@@ -80,6 +80,17 @@ struct CpAttn {
   int* tile_counter = nullptr;  // local int[8]: tiles written per destination rank (self-resetting)
 };
 
+// Paged K / V for flash_fwd: prefill over a slot-addressed pool without gathering the keys first.  k / v are then the
+// pool [n_slots, Hkv, D]; sequence b reads key t from slot table[rows[b] * stride + t]; the `page` tokens of one page
+// (page in {8, 16, 32, 64}) sit in consecutive slots that start at a multiple of `page`, so a 64-key tile is 64 / page
+// TMA loads of `page` rows each.  cu_k still gives the key counts (differences); its offsets are not used.
+struct PagedKv {
+  const int* table = nullptr;
+  const int* rows = nullptr;
+  long long stride = 0;
+  int page = 0;
+};
+
 // Flash attention forward (flash_fwd.cu).  Packed layouts q [total_q, Hq, D], k/v [total_k, Hkv, D] with unit stride
 // in D and adjacent heads; row strides in elements.  cu_q / cu_k: int32 [batch+1] sequence boundaries or null (then
 // every sequence has sq / sk tokens).  lse [Hq, total_q] fp32 (natural log) may be null.  D in {64, 128}.
@@ -87,7 +98,7 @@ struct CpAttn {
 int flash_fwd(const void* q, const void* k, const void* v, void* out, float* lse, const int* cu_q, const int* cu_k,
               int batch, int sq, int sk, int max_q, long long total_q, long long total_k, int Hq, int Hkv, int D,
               long long q_row_stride, long long k_row_stride, long long v_row_stride, long long o_row_stride, float scale,
-              bool causal, int* status, cudaStream_t st, const CpAttn* cp = nullptr);
+              bool causal, int* status, cudaStream_t st, const CpAttn* cp = nullptr, const PagedKv* paged = nullptr);
 
 // Flash attention backward (flash_bwd.cu): dq [total_q,Hq,D], dk/dv [total_k,Hkv,D] bf16; `delta` is fp32 scratch
 // [2, Hq, total_q]; lse as written by flash_fwd.  Three launches: row-dot pre-pass, dK/dV kernel, dQ kernel.

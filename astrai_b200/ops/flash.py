@@ -77,3 +77,24 @@ def flash_attention_varlen(q: Tensor, k: Tensor, v: Tensor, cu_seqlens_q: Tensor
     batch = cu_seqlens_q.numel() - 1
     return _FlashFn.apply(q, k, v, cu_seqlens_q.int(), cu_seqlens_k.int(), batch, 0, 0, int(max_q), int(max_k),
                           bool(causal), scale)
+
+
+PAGED_PAGE_SIZES = (8, 16, 32, 64)
+
+
+@torch.no_grad()
+def flash_attention_paged(q: Tensor, k_pool: Tensor, v_pool: Tensor, cu_seqlens_q: Tensor, cu_seqlens_k: Tensor,
+                          req_to_token: Tensor, req_pool_indices: Tensor, page_size: int, max_q: int, causal: bool = True,
+                          scale: Optional[float] = None) -> Tensor:
+    """Ragged prefill straight over the paged KV pool (inference, forward only): the kernel's TMA producer walks the
+    slot table page by page, so the batch's keys are never gathered into a packed copy first.
+
+    ``q [Tq, Hq, D]`` packed queries; ``k_pool / v_pool [n_slots, Hkv, D]``; ``cu_seqlens_k`` carries the key counts
+    (cached prefix + new tokens); request ``b`` finds the slot of its key ``t`` at ``req_to_token[req_pool_indices[b], t]``
+    and the ``page_size`` tokens of a page occupy consecutive, page-aligned slots.  Causal masking is lower-right
+    aligned.  The reference's paged-prefill kernel addresses K / V the same way
+    (``csrc/kernels/attention/layout_policies.cuh:39-255``)."""
+    native.require()
+    scale = float(scale) if scale is not None else q.shape[-1] ** -0.5
+    return torch.ops.astrai_b200.flash_fwd_paged(_fix(q), k_pool, v_pool, cu_seqlens_q.int(), cu_seqlens_k.int(), req_to_token,
+                                                 req_pool_indices.int(), int(page_size), int(max_q), bool(causal), scale)

@@ -36,3 +36,5 @@ class KVCache:
     decode_splits: int = 0
     # prefill: slot of every cached + new key of the batch, request after request (the gather index of the flash path)
     kv_gather_loc: Optional[Tensor] = None
+    # tokens per page of the pool (1: slots are not grouped into pages); 8 / 16 / 32 / 64 let prefill read the pool in place
+    page_size: int = 1

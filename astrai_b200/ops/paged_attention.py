@@ -2,9 +2,11 @@
 
 Packed layout: ``q [T, Hq, D]``, ``k / v [T, Hkv, D]`` where the batch is concatenated along ``T``.
 * ``fwd="decode"`` (one new token per request): the split-KV paged kernel (``paged_attention.cu``) on CUDA;
-* ``fwd="prefill"`` (ragged, possibly with a cached prefix): K/V of the whole batch are gathered from the pool into
-  packed tensors and ONE varlen launch of the tcgen05 flash kernel (``flash_fwd.cu``, lower-right aligned causal
-  mask) serves every request; head dims other than 64 / 128 and explicit masks take a per-request SDPA loop.
+* ``fwd="prefill"`` (ragged, possibly with a cached prefix): ONE varlen launch of the tcgen05 flash kernel
+  (``flash_fwd.cu``, lower-right aligned causal mask) serves every request.  With pages of 8 / 16 / 32 / 64 tokens the
+  kernel reads K / V straight from the pool through the slot table; other page sizes (and the contiguous layout's
+  page size 1) gather the batch's keys into packed tensors first.  Head dims other than 64 / 128 and explicit masks
+  take a per-request SDPA loop.
 The CPU statement of both is the same gather + softmax and is what the tests compare against
 (semantics of ``TorchNativeBackend`` in the reference, ``astrai/extension/backend/attention.py:443-498``).
 """
@@ -100,6 +102,13 @@ def cached_attention(q: Tensor, k: Tensor, v: Tensor, kv_cache: KVCache, layer_i
             kv_cache.decode_counters, out)
         return out
     q_lens, kv_lens = _lens(kv_cache)
+    page = getattr(kv_cache, "page_size", 1) or 1
+    if (native_on and attn_mask is None and fwd == "prefill" and kv_cache.qo_indptr is not None and page in flash.PAGED_PAGE_SIZES
+            and flash.supported(q, kv_cache.k_buffer[layer_id], kv_cache.v_buffer[layer_id])):
+        # ragged prefill over the paged pool: the kernel walks the slot table itself (no gathered copy of the keys)
+        return flash.flash_attention_paged(q, kv_cache.k_buffer[layer_id], kv_cache.v_buffer[layer_id], kv_cache.qo_indptr,
+                                           kv_cache.kv_indptr, kv_cache.req_to_token, kv_cache.req_pool_indices, page,
+                                           max(q_lens), causal=True, scale=scale)
     if (native_on and attn_mask is None and fwd == "prefill" and kv_cache.kv_gather_loc is not None and kv_cache.qo_indptr is not None
             and flash.supported(q, kv_cache.k_buffer[layer_id], kv_cache.v_buffer[layer_id])):
         # ragged prefill on the tcgen05 flash kernel: gather this batch's keys / values from the pool (cached prefix

@@ -160,3 +160,48 @@ def test_flash_bwd_varlen_with_prefix():
         assert _close(dv[ks], rv, 2e-2), ("dv", i)
         assert _close(dk[ks], rk, 2e-2), ("dk", i)
         assert _close(dq[qs], rq, 2e-2), ("dq", i)
+
+
+@pytest.mark.parametrize("page,hd,hq,hkv", [(16, 128, 8, 2), (8, 64, 4, 4), (64, 128, 4, 1), (32, 64, 6, 2)])
+def test_paged_prefill_reads_the_pool_through_the_slot_table(page, hd, hq, hkv):
+    """Ragged prefill over a paged pool (cached prefix + new tokens) without gathering the keys: against the fp32
+    statement of causal attention per request, and bit-equal to the gather-then-varlen path."""
+    from astrai_b200.ops import flash
+
+    g = torch.Generator(device="cuda").manual_seed(page + hd)
+    kv_lens, q_lens = [300, 77, 1025, page], [300, 13, 129, 1]      # full prefill, prefix + chunk, long prefix, one token
+    n_pages_total = sum(-(-n // page) for n in kv_lens) + 7
+    n_slots, max_ctx = n_pages_total * page, 1088
+    k_pool = torch.randn(n_slots, hkv, hd, device="cuda", dtype=torch.bfloat16, generator=g)
+    v_pool = torch.randn(n_slots, hkv, hd, device="cuda", dtype=torch.bfloat16, generator=g)
+    perm = torch.randperm(n_pages_total, device="cuda", generator=g)
+    table = torch.full((6, max_ctx), -1, dtype=torch.int32, device="cuda")
+    rows = torch.tensor([4, 0, 2, 5], dtype=torch.int32, device="cuda")  # request rows are not in batch order
+    used = 0
+    for r, n in zip(rows.tolist(), kv_lens):
+        pages = perm[used:used + -(-n // page)]
+        used += pages.numel()
+        slots = (pages[:, None] * page + torch.arange(page, device="cuda")[None]).reshape(-1).int()
+        table[r, :slots.numel()] = slots  # whole pages are allocated, as the pool does
+    cu_q = torch.tensor([0] + list(torch.tensor(q_lens).cumsum(0)), dtype=torch.int32, device="cuda")
+    cu_k = torch.tensor([0] + list(torch.tensor(kv_lens).cumsum(0)), dtype=torch.int32, device="cuda")
+    q = torch.randn(sum(q_lens), hq, hd, device="cuda", dtype=torch.bfloat16, generator=g)
+    out = flash.flash_attention_paged(q, k_pool, v_pool, cu_q, cu_k, table, rows, page, max(q_lens))
+    gather = torch.cat([table[r, :n].long() for r, n in zip(rows.tolist(), kv_lens)])
+    packed = flash.flash_attention_varlen(q, k_pool[gather], v_pool[gather], cu_q, cu_k, max(q_lens), max(kv_lens), causal=True)
+    assert torch.equal(out, packed)
+    at = 0
+    for r, n, ql in zip(rows.tolist(), kv_lens, q_lens):
+        slots = table[r, :n].long()
+        kk = k_pool[slots].float().repeat_interleave(hq // hkv, dim=1)
+        vv = v_pool[slots].float().repeat_interleave(hq // hkv, dim=1)
+        qq = q[at:at + ql].float()
+        s = torch.einsum("qhd,khd->hqk", qq, kk) * hd ** -0.5
+        keep = torch.arange(n, device="cuda")[None, :] <= (n - ql + torch.arange(ql, device="cuda"))[:, None]
+        s = s.masked_fill(~keep[None], float("-inf"))
+        ref = torch.einsum("hqk,khd->qhd", torch.softmax(s, -1), vv)
+        assert (out[at:at + ql].float() - ref).abs().max().item() < 2e-2
+        at += ql
+    from astrai_b200.ops import native
+
+    assert native.kernel_status(torch.device("cuda")) == 0
