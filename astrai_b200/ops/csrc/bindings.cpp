@@ -298,9 +298,9 @@ int64_t paged_decode_splits(int64_t batch, int64_t n_kv_heads, int64_t max_len, 
 }
 
 // q [B, Hq, D]; scratch: o_part [>=B, Hq, max_splits, D] f32, ml_part [>=B, Hq, max_splits, 2] f32, counters int32 [>=B*Hkv] (zero)
-void paged_decode_(const Tensor& q, const Tensor& k_buf, const Tensor& v_buf, const Tensor& req_to_token,
-                   const Tensor& req_pool_indices, const Tensor& seq_lens, double scale, int64_t splits, Tensor& o_part,
-                   Tensor& ml_part, Tensor& counters, Tensor& out) {
+void paged_decode_impl(const Tensor& q, const Tensor& k_buf, const Tensor& v_buf, const Tensor& req_to_token,
+                       const Tensor& req_pool_indices, const Tensor& seq_lens, double scale, int64_t splits, Tensor& o_part,
+                       Tensor& ml_part, Tensor& counters, Tensor& out, const Tensor* k_new, const Tensor* v_new) {
   CHECK_CUDA_CONTIG(q);
   CHECK_CUDA_CONTIG(k_buf);
   CHECK_CUDA_CONTIG(v_buf);
@@ -314,14 +314,37 @@ void paged_decode_(const Tensor& q, const Tensor& k_buf, const Tensor& v_buf, co
   TORCH_CHECK(o_part.scalar_type() == at::kFloat && o_part.size(0) >= B && o_part.size(1) == Hq && o_part.size(3) == D, "paged_decode_: bad o_part scratch");
   TORCH_CHECK(ml_part.scalar_type() == at::kFloat && ml_part.size(0) >= B && ml_part.size(2) == max_splits, "paged_decode_: bad ml_part scratch");
   TORCH_CHECK(counters.scalar_type() == at::kInt && counters.numel() >= (int64_t)B * Hkv, "paged_decode_: bad counters scratch");
+  if (k_new != nullptr) {
+    TORCH_CHECK(k_new->is_cuda() && k_new->is_contiguous() && v_new->is_cuda() && v_new->is_contiguous() &&
+                k_new->scalar_type() == at::kBFloat16 && v_new->scalar_type() == at::kBFloat16 && k_new->dim() == 3 &&
+                k_new->size(0) == B && k_new->size(1) == Hkv && k_new->size(2) == D && v_new->sizes() == k_new->sizes(),
+                "paged_decode_append_: k_new / v_new must be contiguous bf16 [batch, kv_heads, head_dim]");
+  }
   const c10::cuda::CUDAGuard guard(q.device());
   count();
   const int rc = ab::paged_decode(q.data_ptr(), k_buf.data_ptr(), v_buf.data_ptr(), req_to_token.data_ptr<int>(),
                                   req_pool_indices.data_ptr<int>(), (const long long*)seq_lens.data_ptr<int64_t>(),
                                   o_part.data_ptr<float>(), ml_part.data_ptr<float>(), counters.data_ptr<int>(), out.data_ptr(),
                                   B, Hq, Hkv, D, (int)req_to_token.size(1), k_buf.size(0), (float)scale, (int)splits, max_splits,
-                                  (int)req_to_token.size(0), stream());
+                                  (int)req_to_token.size(0), stream(), k_new ? k_new->data_ptr() : nullptr,
+                                  v_new ? v_new->data_ptr() : nullptr);
   TORCH_CHECK(rc == 0, "paged_decode launch failed with code ", rc, " (-1: more than 8 query heads per kv head, -2: splits, -3: head_dim not in {32,64,128,256})");
+}
+
+void paged_decode_(const Tensor& q, const Tensor& k_buf, const Tensor& v_buf, const Tensor& req_to_token,
+                   const Tensor& req_pool_indices, const Tensor& seq_lens, double scale, int64_t splits, Tensor& o_part,
+                   Tensor& ml_part, Tensor& counters, Tensor& out) {
+  paged_decode_impl(q, k_buf, v_buf, req_to_token, req_pool_indices, seq_lens, scale, splits, o_part, ml_part, counters, out,
+                    nullptr, nullptr);
+}
+
+// Decode attention with the step's K / V append fused in: k_new / v_new [batch, Hkv, D] are read for the last position
+// and stored into the pool slot the table names for it (one launch instead of kv_append_ + paged_decode_).
+void paged_decode_append_(const Tensor& q, const Tensor& k_new, const Tensor& v_new, Tensor& k_buf, Tensor& v_buf,
+                          const Tensor& req_to_token, const Tensor& req_pool_indices, const Tensor& seq_lens, double scale,
+                          int64_t splits, Tensor& o_part, Tensor& ml_part, Tensor& counters, Tensor& out) {
+  paged_decode_impl(q, k_buf, v_buf, req_to_token, req_pool_indices, seq_lens, scale, splits, o_part, ml_part, counters, out,
+                    &k_new, &v_new);
 }
 
 // q [Tq, Hq, D], k / v [Tk, Hkv, D] packed along tokens (a dense [B,S,H,D] batch is the same memory).
@@ -1006,6 +1029,7 @@ TORCH_LIBRARY(astrai_b200, m) {
   m.def("kv_append_(Tensor k_new, Tensor v_new, Tensor(a!) k_buf, Tensor(b!) v_buf, Tensor loc) -> ()", &kv_append_);
   m.def("paged_decode_splits(int batch, int n_kv_heads, int max_len, int max_splits) -> int", &paged_decode_splits);
   m.def("paged_decode_(Tensor q, Tensor k_buf, Tensor v_buf, Tensor req_to_token, Tensor req_pool_indices, Tensor seq_lens, float scale, int splits, Tensor(a!) o_part, Tensor(b!) ml_part, Tensor(c!) counters, Tensor(d!) out) -> ()", &paged_decode_);
+  m.def("paged_decode_append_(Tensor q, Tensor k_new, Tensor v_new, Tensor(a!) k_buf, Tensor(b!) v_buf, Tensor req_to_token, Tensor req_pool_indices, Tensor seq_lens, float scale, int splits, Tensor(c!) o_part, Tensor(d!) ml_part, Tensor(e!) counters, Tensor(f!) out) -> ()", &paged_decode_append_);
   m.def("fsdp_reduce_scatter_(int[] grad_ptrs, int mc_ptr, int[] flag_ptrs, int rank, int shard_off, Tensor(a!) out, Tensor(b!) sumsq, int unit, int max_units, int epoch, float timeout_s, int max_ctas) -> ()", &fsdp_reduce_scatter_);
   m.def("fsdp_adamw_allgather_(int[] param_ptrs, int mc_ptr, int[] flag_ptrs, int rank, int shard_off, Tensor? master, Tensor g, Tensor(a!) m, Tensor(b!) v, float lr, float b1, float b2, float eps, float wd, int step, Tensor? gscale, int unit, int max_units, int epoch, Tensor(c!) block_counter, int max_ctas) -> ()", &fsdp_adamw_allgather_);
   m.def("comm_wait_flags_(Tensor local_flags, int kind, int world, int skip_rank, int unit, int max_units, int epoch, float timeout_s) -> ()", &comm_wait_flags_);

@@ -40,12 +40,15 @@ void axpy_f32(float* dst, const void* src, long long n, float alpha, bool src_bf
 void kv_append(const void* k_new, const void* v_new, void* k_buf, void* v_buf, const int* loc, long long tokens,
                int row_elems, long long n_slots, cudaStream_t st);
 int paged_decode_splits(int batch, int n_kv_heads, long long max_len, int max_splits);
+// k_new / v_new [batch, n_kv_heads, head_dim] (both or neither): fused append - the row of position seq_lens[b] - 1 is read
+// from them and written into the pool slot the table names for that position (the pool is then written, not only read).
 // table_rows: number of rows of req_to_token (a request whose req_pool_indices entry is outside [0, table_rows) attends to
 // nothing), or 0 when the caller cannot say (raw-pointer entry points); seq_lens entries are cut to [0, max_ctx].
 int paged_decode(const void* q, const void* k_buf, const void* v_buf, const int* req_to_token,
                  const int* req_pool_indices, const long long* seq_lens, float* o_part, float* ml_part, int* counters,
                  void* out, int batch, int n_q_heads, int n_kv_heads, int head_dim, int max_ctx, long long n_slots,
-                 float scale, int splits, int max_splits, int table_rows, cudaStream_t st);
+                 float scale, int splits, int max_splits, int table_rows, cudaStream_t st, const void* k_new = nullptr,
+                 const void* v_new = nullptr);
 
 // tcgen05 GEMM: D[M,N] (+)= A * B with bf16 operands and fp32 accumulation in tensor memory.
 //   a_kmajor: A is [M,K] row-major (true) or stored as [K,M] row-major (false)

@@ -64,7 +64,9 @@ paged_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __
                     const int* __restrict__ req_pool_indices, const long long* __restrict__ seq_lens,
                     float* __restrict__ o_part, float* __restrict__ ml_part, int* __restrict__ counters,
                     __nv_bfloat16* __restrict__ out, int n_q_heads, int n_kv_heads, int max_ctx, long long n_slots,
-                    float scale, int max_splits, int table_rows) {
+                    float scale, int max_splits, int table_rows, const __nv_bfloat16* __restrict__ k_new,
+                    const __nv_bfloat16* __restrict__ v_new, __nv_bfloat16* __restrict__ k_pool_w,
+                    __nv_bfloat16* __restrict__ v_pool_w) {
   constexpr int LPT = D / 8;
   constexpr int TPW = 32 / LPT;  // tokens per warp iteration
   const int kvh = blockIdx.x, b = blockIdx.y, split = blockIdx.z, splits = gridDim.z;
@@ -97,6 +99,21 @@ paged_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __
   }
 
   const long long row = (long long)n_kv_heads * D;
+  // Fused append (k_new != null): this step's key / value row of the request is not in the pool yet.  Every CTA takes
+  // the last position (len - 1) from k_new / v_new instead of the pool, so no CTA depends on another one's write, and
+  // the CTA of split 0 also stores the row into the slot the table names for that position.
+  const long long t_new = (k_new != nullptr) ? len - 1 : -1;
+  const __nv_bfloat16* k_new_row = k_new ? k_new + ((long long)b * n_kv_heads + kvh) * D : nullptr;
+  const __nv_bfloat16* v_new_row = v_new ? v_new + ((long long)b * n_kv_heads + kvh) * D : nullptr;
+  if (k_new != nullptr && split == 0 && len > 0 && threadIdx.x < 2 * (D / 8)) {
+    const long long slot = table[len - 1];
+    if (slot >= 0 && slot < n_slots) {
+      const int which = threadIdx.x / (D / 8), c = (threadIdx.x % (D / 8)) * 8;
+      const __nv_bfloat16* src = which ? v_new_row : k_new_row;
+      __nv_bfloat16* dst = (which ? v_pool_w : k_pool_w) + slot * row + (long long)kvh * D;
+      *reinterpret_cast<uint4*>(dst + c) = *reinterpret_cast<const uint4*>(src + c);
+    }
+  }
   // Each lane group takes UNR tokens per trip.  The loads of trip i + 1 (table entries, then K and V rows - two dependent
   // round trips to memory) are issued BEFORE the arithmetic of trip i, into a second register set, so the memory
   // latency of a trip hides behind the previous trip's math; within a trip the softmax state of a head is rescaled
@@ -111,8 +128,13 @@ paged_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __
       long long slot = valid ? (long long)table[t] : -1;
       live[u] = valid && slot >= 0 && slot < n_slots;  // a corrupt table entry must not fault: its score is masked
       if (!live[u]) slot = 0;
-      kraw[u] = *reinterpret_cast<const uint4*>(k_buf + slot * row + (long long)kvh * D + dl * 8);
-      vraw[u] = *reinterpret_cast<const uint4*>(v_buf + slot * row + (long long)kvh * D + dl * 8);
+      if (t == t_new) {  // the token of this step: straight from the projection's output
+        kraw[u] = *reinterpret_cast<const uint4*>(k_new_row + dl * 8);
+        vraw[u] = *reinterpret_cast<const uint4*>(v_new_row + dl * 8);
+      } else {
+        kraw[u] = *reinterpret_cast<const uint4*>(k_buf + slot * row + (long long)kvh * D + dl * 8);
+        vraw[u] = *reinterpret_cast<const uint4*>(v_buf + slot * row + (long long)kvh * D + dl * 8);
+      }
     }
   };
   auto compute_trip = [&](const uint4 (&kraw)[UNR], const uint4 (&vraw)[UNR], const bool (&live)[UNR]) {
@@ -279,8 +301,10 @@ int paged_decode_splits(int batch, int n_kv_heads, long long max_len, int max_sp
 int paged_decode(const void* q, const void* k_buf, const void* v_buf, const int* req_to_token,
                  const int* req_pool_indices, const long long* seq_lens, float* o_part, float* ml_part, int* counters,
                  void* out, int batch, int n_q_heads, int n_kv_heads, int head_dim, int max_ctx, long long n_slots,
-                 float scale, int splits, int max_splits, int table_rows, cudaStream_t st) {
+                 float scale, int splits, int max_splits, int table_rows, cudaStream_t st, const void* k_new,
+                 const void* v_new) {
   if (batch == 0) return 0;
+  if ((k_new == nullptr) != (v_new == nullptr)) return -6;
   if (n_q_heads % n_kv_heads || n_q_heads / n_kv_heads > MAXG) return -1;
   if (splits < 1 || splits > max_splits) return -2;
   const dim3 grid(n_kv_heads, batch, splits), block(DEC_WARPS * 32);
@@ -290,7 +314,10 @@ int paged_decode(const void* q, const void* k_buf, const void* v_buf, const int*
   paged_decode_kernel<DD, GG><<<grid, block, 0, st>>>((const __nv_bfloat16*)q, (const __nv_bfloat16*)k_buf,          \
                                                       (const __nv_bfloat16*)v_buf, req_to_token, req_pool_indices,   \
                                                       seq_lens, o_part, ml_part, counters, (__nv_bfloat16*)out,      \
-                                                      n_q_heads, n_kv_heads, max_ctx, n_slots, scale, max_splits, table_rows)
+                                                      n_q_heads, n_kv_heads, max_ctx, n_slots, scale, max_splits, table_rows, \
+                                                      (const __nv_bfloat16*)k_new, (const __nv_bfloat16*)v_new,     \
+                                                      (__nv_bfloat16*)const_cast<void*>(k_buf),                     \
+                                                      (__nv_bfloat16*)const_cast<void*>(v_buf))
 #define AB_DEC_G(DD)                 \
   switch (gt) {                      \
     case 1: AB_DEC(DD, 1); break;    \

@@ -1,7 +1,8 @@
 """Attention with a KV cache: append this step's K/V to the pool, then attend over the cached prefix + new tokens.
 
 Packed layout: ``q [T, Hq, D]``, ``k / v [T, Hkv, D]`` where the batch is concatenated along ``T``.
-* ``fwd="decode"`` (one new token per request): the split-KV paged kernel (``paged_attention.cu``) on CUDA;
+* ``fwd="decode"`` (one new token per request): the split-KV paged kernel (``paged_attention.cu``) on CUDA, which also
+  stores the step's K / V rows into the pool (no separate append launch);
 * ``fwd="prefill"`` (ragged, possibly with a cached prefix): ONE varlen launch of the tcgen05 flash kernel
   (``flash_fwd.cu``, lower-right aligned causal mask) serves every request.  With pages of 8 / 16 / 32 / 64 tokens the
   kernel reads K / V straight from the pool through the slot table; other page sizes (and the contiguous layout's
@@ -86,21 +87,23 @@ def cached_attention(q: Tensor, k: Tensor, v: Tensor, kv_cache: KVCache, layer_i
         raise ValueError("inference attention requires a KV cache")
     if q.dim() != 3:
         raise ValueError("packed inference tensors must be [tokens, heads, head_dim]")
-    _append(k, v, kv_cache, layer_id)
     scale = q.shape[-1] ** -0.5
     from astrai_b200.ops import backend as _backend
 
     native_on = _backend.get_backend(q.device.type) is _backend.ATTN_BACKEND.TCGEN05
     if native_on and fwd == "decode" and attn_mask is None and _decode_native_ok(q, kv_cache):
+        # one launch: the step's K / V rows are stored into the pool by the attention kernel itself (the reference fuses
+        # its append the same way, csrc/kernels/attention/layout_policies.cuh:221-254)
         b = q.shape[0]
         splits = kv_cache.decode_splits or int(torch.ops.astrai_b200.paged_decode_splits(
             b, kv_cache.k_buffer.shape[2], max(kv_cache.max_len, 1), kv_cache.decode_o_part.shape[2]))
         out = kv_cache.decode_out[:b] if kv_cache.decode_out is not None else torch.empty_like(q)
-        torch.ops.astrai_b200.paged_decode_(
-            q.contiguous(), kv_cache.k_buffer[layer_id], kv_cache.v_buffer[layer_id], kv_cache.req_to_token,
-            kv_cache.req_pool_indices, kv_cache.seq_lens, scale, splits, kv_cache.decode_o_part, kv_cache.decode_ml_part,
-            kv_cache.decode_counters, out)
+        torch.ops.astrai_b200.paged_decode_append_(
+            q.contiguous(), k.contiguous(), v.contiguous(), kv_cache.k_buffer[layer_id], kv_cache.v_buffer[layer_id],
+            kv_cache.req_to_token, kv_cache.req_pool_indices, kv_cache.seq_lens, scale, splits, kv_cache.decode_o_part,
+            kv_cache.decode_ml_part, kv_cache.decode_counters, out)
         return out
+    _append(k, v, kv_cache, layer_id)
     q_lens, kv_lens = _lens(kv_cache)
     page = getattr(kv_cache, "page_size", 1) or 1
     if (native_on and attn_mask is None and fwd == "prefill" and kv_cache.qo_indptr is not None and page in flash.PAGED_PAGE_SIZES
