@@ -657,6 +657,57 @@ void tp_gemm_reducescatter_(const Tensor& X, const Tensor& W, bool w_kmajor, std
   TORCH_CHECK(rc == 0, "gemm_reducescatter launch failed with code ", rc, " (-2: M must be a multiple of world*128, N of 32, K of 8)");
 }
 
+// The pair-tile engine (gemm_comm2.cu): the transfer runs as bulk copies issued by one extra warp of every GEMM CTA.
+void tp2_gemm_allgather_(std::vector<int64_t> xfull_ptrs, const Tensor& W, bool w_kmajor, Tensor& Y, std::vector<int64_t> flag_ptrs,
+                         Tensor& chunk_flags, Tensor& chunk_counter, int64_t rank, int64_t unit, int64_t max_units,
+                         int64_t epoch, double timeout_s) {
+  CHECK_CUDA_CONTIG(W);
+  CHECK_CUDA_CONTIG(Y);
+  TORCH_CHECK(W.scalar_type() == at::kBFloat16 && Y.scalar_type() == at::kBFloat16 && W.dim() == 2 && Y.dim() == 2, "tp2_gemm_allgather_: bf16 2-D");
+  TORCH_CHECK(chunk_flags.scalar_type() == at::kInt && chunk_flags.numel() >= 8 && chunk_counter.scalar_type() == at::kInt && chunk_counter.numel() >= 8, "tp2_gemm_allgather_: int32[8] flags / counters");
+  const int64_t N = w_kmajor ? W.size(0) : W.size(1), K = w_kmajor ? W.size(1) : W.size(0);
+  TORCH_CHECK(Y.size(1) == N, "tp2_gemm_allgather_: output columns must match the weight");
+  ab::TpGemmParams p{};
+  p.world = (int)xfull_ptrs.size(); p.rank = (int)rank; p.unit = (int)unit; p.max_units = (int)max_units; p.epoch = (int)epoch;
+  p.timeout_ns = (unsigned long long)(timeout_s * 1e9);
+  fill_ptrs(p.flags, flag_ptrs); fill_ptrs(p.x_full, xfull_ptrs);
+  p.chunk_flags = chunk_flags.data_ptr<int>(); p.chunk_counter = chunk_counter.data_ptr<int>();
+  const c10::cuda::CUDAGuard guard(W.device());
+  count();
+  const int rc = ab::gemm_allgather2(W.data_ptr(), w_kmajor, Y.data_ptr(), (int)Y.size(0), (int)N, (int)K, Y.stride(0), p,
+                                     status_tensor(W.device()).data_ptr<int>(), stream());
+  TORCH_CHECK(rc == 0, "gemm_allgather2 launch failed with code ", rc, " (-2: M must be a multiple of world*256, N of 32, K of 8)");
+}
+
+void tp2_gemm_reducescatter_(const Tensor& X, const Tensor& W, bool w_kmajor, std::vector<int64_t> part_ptrs, Tensor& gathered,
+                             Tensor& out, std::vector<int64_t> flag_ptrs, Tensor& tile_counter, Tensor& pull_counter,
+                             int64_t rank, int64_t unit, int64_t max_units, int64_t epoch, double timeout_s, int64_t phase) {
+  CHECK_CUDA_CONTIG(X);
+  CHECK_CUDA_CONTIG(W);
+  CHECK_CUDA_CONTIG(out);
+  CHECK_CUDA_CONTIG(gathered);
+  TORCH_CHECK(X.scalar_type() == at::kBFloat16 && W.scalar_type() == at::kBFloat16 && out.scalar_type() == at::kBFloat16 &&
+              gathered.scalar_type() == at::kBFloat16, "tp2_gemm_reducescatter_: bf16");
+  const int64_t N = w_kmajor ? W.size(0) : W.size(1), K = w_kmajor ? W.size(1) : W.size(0);
+  TORCH_CHECK(X.dim() == 2 && W.dim() == 2 && X.size(1) == K, "tp2_gemm_reducescatter_: inner dimensions differ");
+  TORCH_CHECK(tile_counter.scalar_type() == at::kInt && tile_counter.numel() >= 8 && pull_counter.scalar_type() == at::kInt &&
+              pull_counter.numel() >= 1, "tp2_gemm_reducescatter_: int32 counters");
+  ab::TpGemmParams p{};
+  p.world = (int)part_ptrs.size(); p.rank = (int)rank; p.unit = (int)unit; p.max_units = (int)max_units; p.epoch = (int)epoch;
+  p.fuse_reduce = (int)phase; p.timeout_ns = (unsigned long long)(timeout_s * 1e9);
+  TORCH_CHECK(phase >= 0 && phase <= 2, "tp2_gemm_reducescatter_: phase is 0, 1 or 2");
+  TORCH_CHECK(out.size(0) * p.world == X.size(0) && out.size(1) == N, "tp2_gemm_reducescatter_: output must be [M/world, N]");
+  TORCH_CHECK(gathered.numel() >= X.size(0) * N, "tp2_gemm_reducescatter_: gathered must hold world slots of [M/world, N]");
+  fill_ptrs(p.flags, flag_ptrs); fill_ptrs(p.stage, part_ptrs);
+  p.rs_out = out.data_ptr(); p.tile_counter = tile_counter.data_ptr<int>();
+  p.gathered = gathered.data_ptr(); p.pull_counter = pull_counter.data_ptr<int>();
+  const c10::cuda::CUDAGuard guard(X.device());
+  count();
+  const int rc = ab::gemm_reducescatter2(X.data_ptr(), W.data_ptr(), w_kmajor, (int)X.size(0), (int)N, (int)K, p,
+                                         status_tensor(X.device()).data_ptr<int>(), stream());
+  TORCH_CHECK(rc == 0, "gemm_reducescatter2 launch failed with code ", rc, " (-2: M must be a multiple of world*256, N of 32, K of 8)");
+}
+
 void tp_reduce_(const Tensor& stage, Tensor& out, int64_t world) {
   CHECK_CUDA_CONTIG(stage);
   CHECK_CUDA_CONTIG(out);
@@ -1043,6 +1094,8 @@ TORCH_LIBRARY(astrai_b200, m) {
   m.def("tp_gemm_allgather_(int[] xfull_ptrs, Tensor W, bool w_kmajor, Tensor(a!) Y, int[] flag_ptrs, Tensor(b!) chunk_flags, Tensor(c!) chunk_counter, int rank, int unit, int max_units, int epoch, float timeout_s, int n_copy_ctas) -> ()", &tp_gemm_allgather_);
   m.def("tp_gemm_reducescatter_(Tensor X, Tensor W, bool w_kmajor, int[] stage_ptrs, Tensor(a!) out, int[] flag_ptrs, Tensor(b!) tile_counter, int rank, int unit, int max_units, int epoch, float timeout_s, bool fuse_reduce) -> ()", &tp_gemm_reducescatter_);
   m.def("tp_reduce_(Tensor stage, Tensor(a!) out, int world) -> ()", &tp_reduce_);
+  m.def("tp2_gemm_allgather_(int[] xfull_ptrs, Tensor W, bool w_kmajor, Tensor(a!) Y, int[] flag_ptrs, Tensor(b!) chunk_flags, Tensor(c!) chunk_counter, int rank, int unit, int max_units, int epoch, float timeout_s) -> ()", &tp2_gemm_allgather_);
+  m.def("tp2_gemm_reducescatter_(Tensor X, Tensor W, bool w_kmajor, int[] part_ptrs, Tensor(a!) gathered, Tensor(b!) out, int[] flag_ptrs, Tensor(c!) tile_counter, Tensor(d!) pull_counter, int rank, int unit, int max_units, int epoch, float timeout_s, int phase) -> ()", &tp2_gemm_reducescatter_);
   m.def("fp8_quantize(Tensor x, Tensor scale, bool e5m2, bool with_transpose) -> (Tensor, Tensor, Tensor)", &fp8_quantize);
   m.def("fp8_gemm(Tensor a, Tensor b, Tensor scale_a, Tensor scale_b, Tensor? bias) -> Tensor", &fp8_gemm);
   m.def("sample_rows(Tensor logits, Tensor temps, Tensor? top_k, Tensor? top_p, Tensor? penalty, Tensor? hist, Tensor? hist_mask, bool all_greedy, int seed, int offset) -> (Tensor, Tensor, Tensor)", &sample_rows);

@@ -146,7 +146,21 @@ struct TpGemmParams {
   void* stage[8];        // reduce-scatter: staging buffer of every rank, [world][M/world, N] bf16
   void* rs_out;          // reduce-scatter: local result [M/world, N] bf16 (written by the fused reduce phase)
   int* tile_counter;     // reduce-scatter, local int[8]: epilogue-warp arrivals per destination (cleared at launch)
+  // pair-tile engine (gemm_comm2.cu), reduce-scatter by pulling: `stage[r]` is then rank r's whole partial product
+  // [M, N] in symmetric memory, `gathered` the local [world][M/world, N] buffer the peers' blocks are pulled into and
+  // `pull_counter` a local int counting the CTAs that finished pulling (cleared at launch).  fuse_reduce: 1 = product,
+  // pull and reduce in one launch; 0 = product + announcements only; 2 = pull + reduce only (the two halves let a test
+  // run several ranks on one GPU without kernels waiting for one another).
+  void* gathered;
+  int* pull_counter;
 };
+// The same two operations on the CTA-pair tile engine with in-kernel bulk-copy transfer (gemm_comm2.cu); they need
+// M % (world * 256) == 0 (tp2_shape_ok) and are the ones the tensor-parallel layers use when the shape allows.
+bool tp2_shape_ok(int M, int N, int K, int world);
+int gemm_allgather2(const void* W, bool w_kmajor, void* Y, int M, int N, int K, long long ldy, const TpGemmParams& p,
+                    int* status, cudaStream_t st);
+int gemm_reducescatter2(const void* X, const void* W, bool w_kmajor, int M, int N, int K, const TpGemmParams& p,
+                        int* status, cudaStream_t st);
 // Y[M, N] = X_full[M, K] * op(W) where row block r of X_full is pulled from rank r inside the kernel.
 // W is stored [N, K] (w_kmajor) or [K, N]; both contiguous.
 int gemm_allgather(const void* W, bool w_kmajor, void* Y, int M, int N, int K, long long ldy, const TpGemmParams& p,

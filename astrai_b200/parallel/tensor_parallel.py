@@ -39,7 +39,11 @@ class TPContext:
     MAX_UNITS = 64
 
     def __init__(self, arena, rank: int, world: int, timeout_s: float = 60.0, n_copy_ctas: int = 16,
-                 fuse_reduce: bool = True, group=None):
+                 fuse_reduce: bool = True, group=None, engine: str = "pair"):
+        """``engine="pair"``: the CTA-pair kernels with in-kernel bulk-copy transfer (``ops/csrc/gemm_comm2.cu``) whenever
+        a row block is a whole number of 256-row pair tiles, else (and with ``engine="single"``) the one-CTA-per-tile
+        kernels with copy CTAs and epilogue peer stores (``gemm_comm.cu``)."""
+        self.engine = engine
         self.arena, self.rank, self.world = arena, rank, world
         self.timeout_s, self.n_copy_ctas, self.fuse_reduce = float(timeout_s), int(n_copy_ctas), bool(fuse_reduce)
         self.group = group
@@ -51,6 +55,8 @@ class TPContext:
         self.chunk_flags = torch.zeros(8, dtype=torch.int32, device=dev)
         self.chunk_counter = torch.zeros(8, dtype=torch.int32, device=dev)
         self.tile_counter = torch.zeros(8, dtype=torch.int32, device=dev)
+        self.pull_counter = torch.zeros(1, dtype=torch.int32, device=dev)
+        self._gathered: Dict[Tuple[int, int], Tensor] = {}
 
     # The pools are keyed by shape and parity; allocation order must be identical on every rank (it is: the same
     # model code runs everywhere), because a sub-buffer is identified by its offset in the arena.
@@ -65,6 +71,16 @@ class TPContext:
         if key not in self._stage:
             self._stage[key] = self.arena.alloc(self.world * rows * n, torch.bfloat16, zero=False)
         return self._stage[key]
+
+    def gathered_buffer(self, rows: int, n: int) -> Tensor:
+        """Local (not peer-visible) landing area of the pulled partial blocks: ``[world, rows, n]`` bf16."""
+        key = (rows, n)
+        if key not in self._gathered:
+            self._gathered[key] = torch.empty(self.world * rows * n, dtype=torch.bfloat16, device=self.flags.tensor.device)
+        return self._gathered[key]
+
+    def pair_engine(self, m: int) -> bool:
+        return self.engine == "pair" and m % (self.world * 256) == 0
 
     def next_epoch(self, kind: str) -> int:
         self._epoch[kind] += 1
@@ -126,9 +142,14 @@ def allgather_gemm(x_local: Tensor, w: Tensor, w_kmajor: bool = True, ctx: Optio
         x_full = buf.tensor.view(m, k)
         x_full[ctx.rank * ms:(ctx.rank + 1) * ms].copy_(x_local)
         y = torch.empty((m, n), dtype=torch.bfloat16, device=x_local.device)
-        torch.ops.astrai_b200.tp_gemm_allgather_(buf.peer_ptrs, w.contiguous(), w_kmajor, y, ctx.flags.peer_ptrs,
-                                                 ctx.chunk_flags, ctx.chunk_counter, ctx.rank, 0, ctx.MAX_UNITS, epoch,
-                                                 ctx.timeout_s, ctx.n_copy_ctas)
+        if ctx.pair_engine(m):
+            torch.ops.astrai_b200.tp2_gemm_allgather_(buf.peer_ptrs, w.contiguous(), w_kmajor, y, ctx.flags.peer_ptrs,
+                                                      ctx.chunk_flags, ctx.chunk_counter, ctx.rank, 0, ctx.MAX_UNITS, epoch,
+                                                      ctx.timeout_s)
+        else:
+            torch.ops.astrai_b200.tp_gemm_allgather_(buf.peer_ptrs, w.contiguous(), w_kmajor, y, ctx.flags.peer_ptrs,
+                                                     ctx.chunk_flags, ctx.chunk_counter, ctx.rank, 0, ctx.MAX_UNITS, epoch,
+                                                     ctx.timeout_s, ctx.n_copy_ctas)
         return y, x_full
     if world > 1:
         x_full = torch.empty((m, k), dtype=x_local.dtype, device=x_local.device)
@@ -153,6 +174,12 @@ def gemm_reducescatter(x: Tensor, w: Tensor, w_kmajor: bool = True, ctx: Optiona
         epoch = ctx.next_epoch("rs")
         st = ctx.stage_buffer(ms, n, epoch & 1)
         out = torch.empty((ms, n), dtype=torch.bfloat16, device=x.device)
+        if ctx.pair_engine(m) and ctx.fuse_reduce:
+            # the staging area doubles as this rank's whole partial product [M, N]; the peers' blocks are pulled from it
+            torch.ops.astrai_b200.tp2_gemm_reducescatter_(x.contiguous(), w.contiguous(), w_kmajor, st.peer_ptrs,
+                                                          ctx.gathered_buffer(ms, n), out, ctx.flags.peer_ptrs, ctx.tile_counter,
+                                                          ctx.pull_counter, ctx.rank, 1, ctx.MAX_UNITS, epoch, ctx.timeout_s, 1)
+            return out
         torch.ops.astrai_b200.tp_gemm_reducescatter_(x.contiguous(), w.contiguous(), w_kmajor, st.peer_ptrs, out,
                                                      ctx.flags.peer_ptrs, ctx.tile_counter, ctx.rank, 1, ctx.MAX_UNITS, epoch,
                                                      ctx.timeout_s, ctx.fuse_reduce)
