@@ -165,6 +165,21 @@ void embedding_bwd_(const Tensor& ids, const Tensor& g, Tensor& grad_table) {
                     (int)grad_table.size(1), grad_table.size(0), is_bf16(g), stream());
 }
 
+void embedding_bwd_sorted_(const Tensor& sorted_ids, const Tensor& perm, const Tensor& g, Tensor& grad_table) {
+  CHECK_CUDA_CONTIG(sorted_ids);
+  CHECK_CUDA_CONTIG(perm);
+  CHECK_CUDA_CONTIG(g);
+  CHECK_CUDA_CONTIG(grad_table);
+  TORCH_CHECK(grad_table.scalar_type() == at::kFloat, "embedding_bwd_sorted_: fp32 accumulation buffer expected");
+  TORCH_CHECK(sorted_ids.scalar_type() == at::kLong && perm.scalar_type() == at::kLong && perm.numel() == sorted_ids.numel(),
+              "embedding_bwd_sorted_: int64 ids and permutation of the same length");
+  const c10::cuda::CUDAGuard guard(g.device());
+  count();
+  ab::embedding_bwd_sorted((const long long*)sorted_ids.data_ptr<int64_t>(), (const long long*)perm.data_ptr<int64_t>(),
+                           g.data_ptr(), grad_table.data_ptr<float>(), sorted_ids.numel(), (int)grad_table.size(1),
+                           grad_table.size(0), is_bf16(g), stream());
+}
+
 // logits [rows, V] (unit column stride).  Writes the gradient over `logits` when in_place_grad (scaled by grad_scale[0]).
 std::tuple<Tensor, Tensor> ce_rows(Tensor& logits, const Tensor& targets, double smoothing, int64_t ignore_index,
                                    const c10::optional<Tensor>& grad_scale, bool in_place_grad) {
@@ -1069,6 +1084,7 @@ TORCH_LIBRARY(astrai_b200, m) {
   m.def("swiglu_bwd(Tensor dy, Tensor gate, Tensor up) -> Tensor", &swiglu_bwd);
   m.def("embedding_fwd(Tensor ids, Tensor table) -> Tensor", &embedding_fwd);
   m.def("embedding_bwd_(Tensor ids, Tensor g, Tensor(a!) grad_table) -> ()", &embedding_bwd_);
+  m.def("embedding_bwd_sorted_(Tensor sorted_ids, Tensor perm, Tensor g, Tensor(a!) grad_table) -> ()", &embedding_bwd_sorted_);
   m.def("ce_rows(Tensor(a!) logits, Tensor targets, float smoothing, int ignore_index, Tensor? grad_scale, bool in_place_grad) -> (Tensor, Tensor)", &ce_rows);
   m.def("logprob_bwd_(Tensor(a!) logits, Tensor targets, Tensor logprob, Tensor g_rows) -> ()", &logprob_bwd_);
   m.def("sumsq_(Tensor x, Tensor(a!) out) -> ()", &sumsq_);

@@ -424,6 +424,36 @@ __global__ void embedding_bwd_kernel(const long long* __restrict__ ids, const T*
   }
 }
 
+// Deterministic form: `sorted` are the token ids in ascending order and `perm[j]` the position in the batch of sorted
+// entry j.  One CTA per sorted position; the CTA at the head of a run of equal ids sums that run's gradient rows in run
+// order (a fixed order, whatever the scheduling) and adds the sum to the id's row - no atomics, no two CTAs per row.
+template <typename T>
+__global__ void embedding_bwd_sorted_kernel(const long long* __restrict__ sorted, const long long* __restrict__ perm,
+                                            const T* __restrict__ g, float* __restrict__ grad_table, long long tokens,
+                                            int dim, long long vocab) {
+  const long long i = blockIdx.x;
+  const long long id = sorted[i];
+  if (id < 0 || id >= vocab) return;
+  if (i > 0 && sorted[i - 1] == id) return;  // not the head of its run
+  for (int c = threadIdx.x; c < dim; c += blockDim.x) {
+    float acc = 0.f;
+    for (long long j = i; j < tokens && sorted[j] == id; ++j) acc += to_f(g[perm[j] * dim + c]);
+    grad_table[id * dim + c] += acc;
+  }
+}
+
+void embedding_bwd_sorted(const long long* sorted, const long long* perm, const void* g, float* grad_table, long long tokens,
+                          int dim, long long vocab, bool is_bf16, cudaStream_t st) {
+  if (tokens == 0) return;
+  const int threads = dim >= 256 ? 256 : 64;
+  if (is_bf16)
+    embedding_bwd_sorted_kernel<__nv_bfloat16><<<(unsigned)tokens, threads, 0, st>>>(sorted, perm, (const __nv_bfloat16*)g,
+                                                                                      grad_table, tokens, dim, vocab);
+  else
+    embedding_bwd_sorted_kernel<float><<<(unsigned)tokens, threads, 0, st>>>(sorted, perm, (const float*)g, grad_table, tokens,
+                                                                              dim, vocab);
+}
+
 void embedding_fwd(const long long* ids, const void* table, void* out, long long tokens, int dim, long long vocab,
                    bool is_bf16, cudaStream_t st) {
   if (tokens == 0) return;

@@ -24,6 +24,9 @@ void embedding_fwd(const long long* ids, const void* table, void* out, long long
                    bool is_bf16, cudaStream_t st);
 void embedding_bwd(const long long* ids, const void* g, float* grad_table, long long tokens, int dim, long long vocab,
                    bool is_bf16, cudaStream_t st);
+// Deterministic variant: ids sorted ascending with the permutation that sorted them; equal ids are summed in run order.
+void embedding_bwd_sorted(const long long* sorted, const long long* perm, const void* g, float* grad_table, long long tokens,
+                          int dim, long long vocab, bool is_bf16, cudaStream_t st);
 
 void ce_rows(const void* logits, void* dlogits, const long long* targets, float* loss, float* logprob,
              const float* grad_scale, long long rows, int V, long long ld, float smoothing, long long ignore_index,

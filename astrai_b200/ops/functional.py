@@ -362,12 +362,16 @@ class _EmbeddingFn(Function):
     def backward(ctx, gy: Tensor):
         (ids,) = ctx.saved_tensors
         table = ctx.table
+        # Sorted segmented reduce: rows of equal ids are summed in a fixed order by one CTA each, so the gradient of a
+        # tied embedding / lm_head weight is the same bits on every run (an atomic scatter-add is not).
+        sorted_ids, perm = torch.sort(ids.reshape(-1), stable=True)
+        g2 = gy.reshape(-1, gy.shape[-1]).contiguous()
         mg = _main_grad(table)
         if mg is not None:
-            _ops().embedding_bwd_(ids.contiguous(), gy.contiguous(), mg)
+            _ops().embedding_bwd_sorted_(sorted_ids, perm, g2, mg)
             return None, None
         acc = torch.zeros(table.shape, dtype=torch.float32, device=table.device)
-        _ops().embedding_bwd_(ids.contiguous(), gy.contiguous(), acc)
+        _ops().embedding_bwd_sorted_(sorted_ids, perm, g2, acc)
         return None, acc.to(table.dtype)
 
 

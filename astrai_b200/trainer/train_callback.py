@@ -107,7 +107,9 @@ class CheckpointCallback(TrainCallback):
     def _save_without_peers(self, context, dead: List[int]):
         """Emergency save while ``dead`` ranks are gone: nothing here may communicate (no barrier, no gather).
 
-        The lowest surviving rank writes the usual directory from its local copy of the weights (every executor whose
+        ONE survivor writes the usual directory from its local copy of the weights: the first to create
+        ``<dir>.writer`` (an exclusive create on the shared file system - survivors may disagree about who is still
+        alive, because a rank that has finished its own emergency save and left looks gone as well).  Every executor whose
         parameters are replicated or locally complete can give one; a torch-FSDP2 model cannot, its save is skipped)
         with ``emergency`` / ``failed_ranks`` in ``meta.json``.  A sharded optimizer is not gathered: every survivor
         writes its own shard to ``<dir>.shards/optimizer.rank<r>.pt`` (the dead ranks' shards are lost, so the directory
@@ -134,16 +136,24 @@ class CheckpointCallback(TrainCallback):
                     torch.save(osd, shard_dir / f"optimizer.rank{rank}.pt")
                 else:
                     extra["optimizer"] = osd
-        if not survivors or rank != survivors[0]:
+        if not survivors or (Path(path) / "meta.json").exists():
             return
         state_dict = context.executor.local_state_dict(context.model)
         if state_dict is None:
             logger.error("emergency checkpoint: this executor cannot produce the weights without its peers; nothing written")
             return
-        meta = dict(context.config.to_dict(), emergency=True, failed_ranks=sorted(dead))
-        context.checkpoint = Checkpoint(state_dict=state_dict, epoch=context.epoch, consumed_samples=context.consumed_samples,
-                                        config=context.model_config, extra=extra, meta=meta)
-        context.checkpoint.save(path)
+        os.makedirs(self.save_dir, exist_ok=True)
+        try:
+            os.close(os.open(path + ".writer", os.O_CREAT | os.O_EXCL | os.O_WRONLY))
+        except FileExistsError:
+            return  # another survivor is writing (or has written) this step
+        try:
+            meta = dict(context.config.to_dict(), emergency=True, failed_ranks=sorted(dead), written_by_rank=rank)
+            context.checkpoint = Checkpoint(state_dict=state_dict, epoch=context.epoch, consumed_samples=context.consumed_samples,
+                                            config=context.model_config, extra=extra, meta=meta)
+            context.checkpoint.save(path)
+        finally:
+            os.unlink(path + ".writer")
 
     def _save(self, context):
         dead = getattr(context, "failed_ranks", None)

@@ -146,3 +146,21 @@ def test_fused_tp_kernels_leave_guard_words_around_flag_planes_untouched():
     assert (guard[:64] == CANARY).all() and (guard[72:] == CANARY).all()
     whole = arena._all.view(torch.int32)
     assert int((whole == CANARY).sum()) == world * 3 * 64  # every guard word of every emulated rank survived
+
+
+def test_embedding_backward_is_a_fixed_order_sum():
+    from astrai_b200 import ops
+
+    g = torch.Generator(device="cuda").manual_seed(5)
+    table = torch.randn(512, 256, device="cuda", generator=g).bfloat16()
+    ids = torch.randint(0, 40, (4, 300), device="cuda", generator=g)  # few distinct ids: long runs of equal rows
+    gy = torch.randn(4, 300, 256, device="cuda", generator=g).bfloat16()
+
+    def run():
+        t = table.clone().requires_grad_(True)
+        ops.embedding(ids, t).backward(gy)
+        return t.grad
+
+    _twice(run)
+    ref = torch.zeros(512, 256, device="cuda").index_add_(0, ids.reshape(-1), gy.reshape(-1, 256).float())
+    assert (run().float() - ref).abs().max().item() < 0.05 * ref.abs().max().item()
