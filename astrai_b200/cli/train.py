@@ -95,6 +95,8 @@ def build_train_config(o: Dict[str, Any]):
     executor_kwargs: Dict[str, Any] = {}
     if o["parallel_mode"] == "fsdp":
         executor_kwargs["comm"] = o["fsdp_comm"]
+        if o.get("fsdp_reshard"):  # full-shard placement: library collectives, buffers released at rest
+            executor_kwargs.update(comm="nccl", reshard=True, impl="flat")
     elif o["parallel_mode"] in ("tp", "ep"):
         executor_kwargs["comm"] = o.get("mp_comm") or "p2p"
     elif o["parallel_mode"] == "cp":
@@ -124,7 +126,7 @@ def plan(o: Dict[str, Any]) -> Dict[str, Any]:
     """What ``--dry-run`` prints: the merged options that matter, without touching data or devices."""
     keys = ("train_type", "data_root_path", "param_path", "resume", "n_epoch", "batch_per_device", "grad_accum_steps",
             "max_lr", "warmup_ratio", "max_grad_norm", "optimizer", "weight_decay", "schedule_type", "window_size", "stride",
-            "ckpt_dir", "ckpt_interval", "nprocs", "parallel_mode", "fsdp_comm", "tp_size", "cp_size", "ep_size", "mp_comm", "backend", "fp8", "metrics",
+            "ckpt_dir", "ckpt_interval", "nprocs", "parallel_mode", "fsdp_comm", "fsdp_reshard", "tp_size", "cp_size", "ep_size", "mp_comm", "backend", "fp8", "metrics",
             "label_smoothing", "gradient_checkpointing", "random_seed")
     out = {k: (list(o[k]) if isinstance(o[k], tuple) else o[k]) for k in keys}
     out["tokens_per_optimizer_step"] = o["batch_per_device"] * o["grad_accum_steps"] * o["nprocs"] * (o["window_size"] or 0)
@@ -187,6 +189,9 @@ def plan(o: Dict[str, Any]) -> Dict[str, Any]:
 @click.option("--parallel_mode", type=click.Choice(["none", "ddp", "fsdp", "tp", "cp", "ep"]), default="fsdp",
               help="tp / cp / ep: tensor-, context- or expert-parallel blocks of --tp_size / --cp_size / --ep_size ranks.")
 @click.option("--fsdp_comm", type=click.Choice(["nccl", "p2p", "nvls"]), default="p2p", help="FSDP transport: NCCL or fused peer-memory kernels.")
+@click.option("--fsdp_reshard", is_flag=True, default=False,
+              help="FSDP full-shard placement: parameters and gradients are whole only while their block computes "
+                   "(gathers and reduce-scatters every micro-batch; NCCL transport).")
 @click.option("--device_type", type=str, default="cuda")
 @click.option("--start_method", type=click.Choice(["spawn", "fork", "forkserver"]), default="spawn")
 @click.option("--backend", type=click.Choice(["nccl", "gloo"]), default="nccl")

@@ -506,15 +506,26 @@ class FSDPExecutor(FlatExecutor):
     ``comm="p2p"`` the reduce-scatter, the AdamW update and the all-gather of a unit run as fused kernels over
     NVLink peer memory (:mod:`astrai_b200.parallel.fused_fsdp`).  ``impl="torch"`` applies FSDP2 ``fully_shard``
     to each direct child exactly as the reference does (``executor.py:338-361``).
+
+    ``reshard=True`` (flat runtime, library collectives) is the full-shard placement: parameters and gradients are whole
+    only while their unit computes, every micro-batch gathers and reduce-scatters
+    (:mod:`astrai_b200.parallel.fsdp_reshard`).  The default keeps bf16 parameters and the fp32 gradient buffer whole
+    on every rank and shards the optimizer state and master weights; it communicates once per optimizer step.
     """
 
     sharded = True
 
     def __init__(self, grad_accum_steps: int = 1, impl: str = "auto", overlap: bool = True, comm: str = "nccl",
-                 comm_timeout_s: float = 120.0, mesh: Optional[Any] = None, mp_policy: Optional[Any] = None, reshard_after_forward: bool = False):
+                 comm_timeout_s: float = 120.0, mesh: Optional[Any] = None, mp_policy: Optional[Any] = None,
+                 reshard_after_forward: bool = False, reshard: bool = False):
         super().__init__(grad_accum_steps, impl, overlap)
         if comm not in ("nccl", "p2p", "nvls"):
             raise ValueError("comm must be 'nccl', 'p2p' or 'nvls'")
+        if reshard and comm != "nccl":
+            raise ValueError("reshard=True releases and re-creates the unit buffers, which symmetric memory cannot do: use comm='nccl'")
+        self.reshard = bool(reshard)
+        self._rs: Optional[Any] = None
+        self.communicates_every_micro_batch = self.reshard
         self.comm = comm
         self.comm_timeout_s = float(comm_timeout_s)
         self._mesh, self._mp_policy, self._reshard_after_forward = mesh, mp_policy, reshard_after_forward
@@ -569,11 +580,16 @@ class FSDPExecutor(FlatExecutor):
         return total.item()
 
     def local_state_dict(self, model):
-        if self.engine is None and self.use_distributed:
-            return None  # FSDP2 keeps DTensor shards: the full weights need the peers
+        if (self.engine is None or self._rs is not None) and self.use_distributed:
+            return None  # FSDP2 DTensor shards / parameters released at rest: the full weights need the peers
         return model.state_dict()  # flat runtime: bf16 parameters are replicated; pending gathers are not waited for
 
     def unwrap_model(self, model):
+        if self._rs is not None:
+            self._rs.unshard_all()  # collective: every rank passes through here (checkpoint_context)
+            sd = {k: v.clone() for k, v in model.state_dict().items()} if (get_rank() == 0 or not self.use_distributed) else None
+            self._rs.release_all()
+            return sd
         if self.engine is not None or not self.use_distributed:
             self._wait_all_gathers()
             return model.state_dict() if (get_rank() == 0 or not self.use_distributed) else None
@@ -621,6 +637,15 @@ class FSDPExecutor(FlatExecutor):
         if self.use_distributed:
             for u in eng.units:  # rank 0's initial weights everywhere
                 dist.broadcast(u.param_buf, src=0)
+        if self.reshard:
+            from astrai_b200.parallel.fsdp_reshard import ReshardRuntime
+
+            self._rs = ReshardRuntime(eng, self._comm_stream, reshard_after_forward=True)
+            for u in eng.units:
+                for mname in u.module_names:
+                    model.get_submodule(mname).register_forward_hook(lambda mod, args, out, u=u: self._rs.after_forward(u, out))
+            return
+        if self.use_distributed:
             if self.comm != "nccl":
                 from astrai_b200.parallel.fused_fsdp import FusedFSDP
 
@@ -630,8 +655,31 @@ class FSDPExecutor(FlatExecutor):
     def _averaging_scale(self) -> float:
         return 1.0 / get_world_size() if self.use_distributed else 1.0
 
+    def _unit_backward_done(self, unit: FlatUnit):
+        if self._rs is None:
+            return super()._unit_backward_done(unit)
+        if not unit.ready:  # every micro-batch: the full gradient buffer does not outlive the unit's backward pass
+            unit.ready = True
+            self._reduce_unit(unit)
+
+    def backward(self, loss: torch.Tensor, gradient: Optional[torch.Tensor] = None):
+        if self._rs is None:
+            return super().backward(loss, gradient)
+        for u in self.engine.units:
+            u.ready = u.reduced = False
+        self._rs.begin_backward()
+        loss.backward(gradient)
+        for u in reversed(self.engine.units):  # what no hook saw finish (the embedding's unit), and unused units
+            u.ready = True
+            if not u.reduced:
+                self._reduce_unit(u)
+        self._rs.finish()
+
     def _reduce_unit(self, unit: FlatUnit):
         unit.reduced = True
+        if self._rs is not None:
+            self._rs.reduce(unit)
+            return
         if not self.use_distributed:
             unit.grad_shard = unit.grad_buf[: unit.shard_size]
             return
@@ -647,6 +695,9 @@ class FSDPExecutor(FlatExecutor):
 
     def _after_flat_update(self):
         """Parameters of every unit were updated in the owner's shard only: gather them, overlapped with what follows."""
+        if self._rs is not None:
+            self._rs.release_all()  # whatever is still whole holds the old values; the next forward pass gathers
+            return
         if not self.use_distributed:
             return
         if self._fused is not None and self._fused.gathers_in_update:
@@ -682,6 +733,9 @@ class FSDPExecutor(FlatExecutor):
             self.clip_grad_norm(None, None)
 
     def _before_unit_forward(self, unit: FlatUnit):
+        if self._rs is not None:
+            self._rs.before_forward(unit)
+            return
         if self._fused is not None:
             self._fused.wait_params(unit)
         ev = self._gather_events.pop(unit.name, None)
@@ -698,5 +752,8 @@ class FSDPExecutor(FlatExecutor):
     def _zero_grad(self, optimizer) -> bool:
         if self.engine is None:
             return False
+        if self._rs is not None:
+            self._rs.zero_accumulators()  # the full buffers are created zeroed for each backward pass
+            return True
         self.engine.zero_grad()  # the full buffers; the update consumed the reduced shards
         return True

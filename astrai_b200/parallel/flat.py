@@ -37,6 +37,7 @@ class FlatUnit:
     grad_buf: Optional[torch.Tensor] = None
     shard_size: int = 0
     grad_shard: Optional[torch.Tensor] = None  # fp32 [shard_size]: reduce-scatter result (sharded modes)
+    local_shard: Optional[torch.Tensor] = None  # this rank's parameter shard when the full buffer is released at rest
     ready: bool = False  # gradient of the current step fully accumulated
     reduced: bool = False
     tag: str = ""  # set when an executor splits units by parameter kind (replicated / sharded): picks the reduce group
@@ -45,6 +46,8 @@ class FlatUnit:
         return rank * self.shard_size, (rank + 1) * self.shard_size
 
     def param_shard(self, rank: int) -> torch.Tensor:
+        if self.local_shard is not None:
+            return self.local_shard
         a, b = self.shard_range(rank)
         return self.param_buf[a:b]
 

@@ -288,6 +288,8 @@ def run_ours(args):
 
     if mode == "fsdp":
         exkw = {"comm": args.comm}
+        if args.fsdp_reshard:  # full-shard placement (parameters / gradients whole only while their block computes)
+            exkw = {"comm": "nccl", "reshard": True, "impl": "flat"}
     elif mode == "cp":
         exkw = {"comm": args.comm, "attn_comm": "nccl" if args.comm == "nccl" else "p2p", "max_tokens_per_rank": 2 * bpd * seq // world}
     elif mode == "ep":
@@ -368,7 +370,8 @@ def run_ours(args):
             results["e2e_ms"] = timer.ms
     if rank == 0:
         _emit(args, world, results["value_ms"], results.get("e2e_ms"), results["launches"], results["clocks"], "ours",
-              extra={"comm": args.comm, "final_loss": round(float(results["final_loss"]), 4), "peak_mem_gb": results["peak_gb"]})
+              extra={"comm": "nccl" if args.fsdp_reshard else args.comm, "fsdp_placement": "full-shard" if args.fsdp_reshard else "replicated",
+                     "final_loss": round(float(results["final_loss"]), 4), "peak_mem_gb": results["peak_gb"]})
 
 
 # ----------------------------------------------------------------------------------------------- reference arm
@@ -527,6 +530,8 @@ def main():
                     help="fsdp1b: the headline 1B FSDP run; tp8b / cp8b: 8B dense with tensor / context parallelism; "
                          "ep_moe: MoE + MLA with expert parallelism (these three need >= 2 GPUs)")
     ap.add_argument("--skip-e2e", action="store_true")
+    ap.add_argument("--fsdp-reshard", action="store_true",
+                    help="fsdp1b: the full-shard placement instead of the default replicated parameters + sharded optimizer state")
     ap.add_argument("--smoke-layers", type=int, default=0,
                     help="debugging aid: cut the model to this many layers (the line is then marked invalid, it is not a result)")
     ap.add_argument("--mode", default="train", choices=["train", "serve"],

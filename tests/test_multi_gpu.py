@@ -153,3 +153,21 @@ def test_model_parallel_trainer_modes_fused_and_collective_arms(tmp_path, mode, 
             assert abs(a - b) / max(abs(b), 1e-6) < 5e-2, (comm, run["norms"], ref["norms"])
         for k, v in ref["sums"].items():
             assert abs(run["sums"][k] - v) / max(v, 1e-6) < 2e-2, (comm, k)
+
+
+def test_full_shard_fsdp_matches_replicated_fsdp(tmp_path):
+    """``reshard=True`` on 2 GPUs (bf16, NCCL gathers / reduce-scatters on the side stream, storages released and
+    re-created around every unit): same losses, norms and weights as the replicated placement, nothing whole at rest."""
+    _need_gpus(2)
+    out = str(tmp_path / "reshard.json")
+    _torchrun(2, os.path.join(ROOT, "tests", "workers", "fsdp_reshard.py"), ["--out", out, "--device", "cuda", "--layers", "4"], 29690)
+    res = json.load(open(out))
+    for x, y in zip(res["a"], res["b"]):
+        assert abs(x - y) < 2e-2, res
+    for x, y in zip(res["a_norms"], res["b_norms"]):
+        assert abs(x - y) / max(abs(x), 1e-6) < 2e-2, res
+    assert abs(res["a_eval"] - res["b_eval"]) < 2e-2
+    assert res["max_weight_diff"] < 2e-2
+    info = res["info"]
+    assert info["at_rest_after_prepare"] == 0 and info["between_micro_batches"] == 0 and info["at_rest_after_save"] == 0
+    assert info["peak_units"] <= 2 + (info["units"] - 4)
