@@ -9,6 +9,9 @@ step performs exactly one device->host transfer (the sampled ids).
 
 from __future__ import annotations
 
+import bisect
+import dataclasses
+
 import logging
 import time
 from contextlib import contextmanager
@@ -147,6 +150,7 @@ class Executor:
                                              max_prefill_tokens=min(self.max_prefill_tokens, 1 << 20))
         self._decode_cache: Optional[DecodeSteadyState] = None
         self._graph_ctx = CudaGraphContext()
+        self._buckets: List[int] = []
         self._graph_supported = (self.device.type == "cuda" and self.dtype == torch.bfloat16
                                  and head_dim in (32, 64, 128, 256) and 1 <= cfg.num_attention_heads // cfg.num_key_value_heads <= 8)
         if enable_cuda_graph and self._graph_supported:
@@ -159,12 +163,40 @@ class Executor:
     def cuda_graph_enabled(self) -> bool:
         return self._graph_ctx.enabled and self._graph_supported
 
+    @staticmethod
+    def decode_buckets(b_max: int) -> List[int]:
+        """Batch sizes that get a decode graph: 1, 2, 4, every multiple of 8 up to 64, every multiple of 16 above, and
+        the maximum.  A step of ``b`` requests replays the graph of the smallest bucket ``>= b`` with the extra rows
+        padded (sequence length 0: they read no keys and store nothing), so no graph is ever captured while serving and
+        at most a third of the rows of a step are padding (an eighth from 32 requests on)."""
+        sizes = {1, 2, 4} | set(range(8, 65, 8)) | set(range(80, b_max + 1, 16)) | {b_max}
+        return sorted(x for x in sizes if x <= b_max)
+
+    def _decode_splits(self, rows: int) -> int:
+        """KV splits baked into the graph of a bucket: one wave of two CTAs per SM whatever the context length (a graph
+        outlives the lengths it was captured with; splits that fall beyond a short sequence return at once)."""
+        base = max(rows * self.model.config.num_key_value_heads, 1)
+        return max(1, min(148 * 2 // base, self._workspace.decode_o_part.shape[2]))
+
+    def _padded(self, kv, b: int, rows: int):
+        """The step's cache view widened to ``rows`` >= ``b`` rows of the workspace (the caller zeroed rows ``b..``)."""
+        ws = self._workspace
+        return dataclasses.replace(kv, req_pool_indices=ws.req_pool_indices[:rows], seq_lens=ws.seq_lens[:rows],
+                                   out_cache_loc=ws.out_cache_loc[:rows], qo_indptr=ws.qo_indptr[: rows + 1],
+                                   decode_splits=self._decode_splits(rows))
+
+    def _zero_padding(self, b: int, rows: int):
+        ws = self._workspace
+        if rows > b:
+            for buf in (ws.input_ids, ws.position_ids, ws.seq_lens, ws.req_pool_indices):
+                buf[b:rows].zero_()
+
     def _warmup(self):
-        """Run a short prefill and capture one decode graph per power-of-two batch size (and the maximum)."""
+        """Capture one decode graph per bucket of :meth:`decode_buckets` (live step, capture, replay)."""
         tc, ws, b_max = self.task_cache, self._workspace, self.kv_cache.max_batch_size
-        sizes = sorted({1 << i for i in range(b_max.bit_length()) if (1 << i) <= b_max} | {b_max})
+        self._buckets: List[int] = []
         with torch.inference_mode():
-            for b in sizes:
+            for b in self.decode_buckets(b_max):
                 ids = [f"_warmup_{b}_{i}" for i in range(b)]
                 if not all(tc.task_alloc(t, [0]) for t in ids):
                     for t in ids:
@@ -173,7 +205,7 @@ class Executor:
                 for step in range(3):  # live, capture, replay
                     for t in ids:
                         tc.task_extend(t, step)
-                    kv = tc.bind(ids, ws)
+                    kv = self._padded(tc.bind(ids, ws), b, b)
                     ws.put_long(ws.position_ids, [step] * b)
                     tokens = ws.fill_input_ids([0] * b)
                     self._graph_ctx.forward(self.model, key=(b,), input_ids=tokens, kv_cache=kv,
@@ -181,6 +213,13 @@ class Executor:
                 for t in ids:
                     tc.task_free(t)
                 torch.cuda.synchronize()
+                if self._graph_ctx.has_graph((b,)):
+                    self._buckets.append(b)
+
+    def _bucket(self, b: int) -> int:
+        """Smallest captured bucket that holds ``b`` requests (``b`` itself when there is none)."""
+        i = bisect.bisect_left(self._buckets, b)
+        return self._buckets[i] if i < len(self._buckets) else b
 
     # -- sampling ---------------------------------------------------------------------------------------------------------
     def _sample(self, logits: Tensor, tasks: List[Task], return_logprobs: bool, info: Optional[SamplingBatchInfo] = None):
@@ -270,9 +309,12 @@ class Executor:
             ws.put_long(ws.position_ids, positions)
         self._decode_cache = DecodeSteadyState(sig, positions, info)
         with torch.inference_mode(), timed(f"execute_decode forward b={b}", logger):
-            kwargs = dict(input_ids=tokens, kv_cache=kv, position_ids=ws.position_ids[:b], fwd="decode")
             if self.cuda_graph_enabled:
-                out = self._graph_ctx.forward(self.model, key=(b,), **kwargs)
+                rows = self._bucket(b)
+                if not steady:
+                    self._zero_padding(b, rows)
+                out = self._graph_ctx.forward(self.model, key=(rows,), input_ids=ws.input_ids[:rows], kv_cache=self._padded(kv, b, rows),
+                                              position_ids=ws.position_ids[:rows], fwd="decode")
             else:
-                out = self.model(**kwargs)
-        return self._sample(out["logits"], tasks, return_logprobs, info=info)
+                out = self.model(input_ids=tokens, kv_cache=kv, position_ids=ws.position_ids[:b], fwd="decode")
+        return self._sample(out["logits"][:b], tasks, return_logprobs, info=info)

@@ -103,18 +103,26 @@ def build(verbose: bool = False, force: bool = False) -> Path:
     return LIB
 
 
-def build_standalone() -> Path:
-    """Link the torch-free attention check (``csrc/standalone/attn_check.cu`` + the two attention kernels' objects)."""
+STANDALONE = {
+    # torch-free check binaries: main source -> the kernel sources it links
+    "attn_check": ("flash_fwd.cu", "paged_attention.cu"),
+    "quant_paged_check": ("gemm_tcgen05.cu", "gemm_tcgen05_2cta.cu", "gemm_fp8.cu", "gemm_fp8_block.cu", "flash_fwd.cu"),
+}
+
+
+def build_standalone(which: str = "attn_check") -> Path:
+    """Link one of the torch-free check programs (``csrc/standalone/<which>.cu`` + the objects of the kernels it calls)."""
     OUT.mkdir(exist_ok=True)
-    objs = [_compile_one(SRC / "flash_fwd.cu", False), _compile_one(SRC / "paged_attention.cu", False)]
-    main_src = SRC / "standalone" / "attn_check.cu"
-    exe = OUT / "attn_check"
+    objs = [_compile_one(SRC / name, False) for name in STANDALONE[which]]
+    main_src = SRC / "standalone" / f"{which}.cu"
+    exe = OUT / which
     _run([_nvcc(), *NVCC_FLAGS, "-I", str(SRC), str(main_src), *map(str, objs), "-o", str(exe), "-lcudart"])
     return exe
 
 
 if __name__ == "__main__":
     if "--standalone" in sys.argv:
-        print(build_standalone())
+        for name in STANDALONE:
+            print(build_standalone(name))
     else:
         print(build(verbose="-v" in sys.argv, force="--force" in sys.argv))

@@ -324,6 +324,37 @@ def test_engine_on_gpu_graph_replay_matches_eager(tmp_path):
     assert agree or sum(a == b for a, b in zip(logits.argmax(-1).tolist(), ref[1])) >= 10  # bf16 near-ties may flip
 
 
+def test_padded_decode_graph_buckets_match_eager(tmp_path):
+    """Nine requests of different lengths decode on the 16-row graph (seven padded rows of length 0), five requests on the
+    8-row graph; every token equals the eager run."""
+    import sys
+
+    sys.path.insert(0, str(__import__("pathlib").Path(__file__).parent))
+    from helpers import build_tokenizer_dir
+
+    from astrai_b200.config import AutoRegressiveLMConfig
+    from astrai_b200.inference import InferenceScheduler
+    from astrai_b200.inference.runtime.executor import Executor
+    from astrai_b200.models import AutoRegressiveLM
+    from astrai_b200.tokenize import AutoTokenizer
+
+    assert Executor.decode_buckets(128) == [1, 2, 4, 8, 16, 24, 32, 40, 48, 56, 64, 80, 96, 112, 128]
+    assert Executor.decode_buckets(12) == [1, 2, 4, 8, 12]
+    tok = AutoTokenizer.from_pretrained(build_tokenizer_dir(str(tmp_path)))
+    cfg = AutoRegressiveLMConfig(vocab_size=1024, hidden_size=256, num_hidden_layers=2, rms_norm_eps=1e-6, intermediate_size=512,
+                                 tie_word_embeddings=True, max_position_embeddings=256, rope_theta=10000.0,
+                                 num_attention_heads=4, num_key_value_heads=2)
+    torch.manual_seed(3)
+    model = AutoRegressiveLM(cfg).to("cuda", torch.bfloat16).eval()
+    prompts = [list(range(10 + 7 * i, 10 + 7 * i + 5 + 9 * i)) for i in range(9)]
+    eager = InferenceScheduler(model, tok, max_batch_size=16, max_seq_len=256, enable_cuda_graph=False)
+    ref = eager.run_batch(prompts, max_tokens=20, temperature=0.0)
+    graphed = InferenceScheduler(model, tok, max_batch_size=16, max_seq_len=256, enable_cuda_graph=True)
+    assert graphed._executor._buckets == [1, 2, 4, 8, 16]
+    assert graphed.run_batch(prompts, max_tokens=20, temperature=0.0) == ref
+    assert graphed.run_batch(prompts[:5], max_tokens=20, temperature=0.0) == ref[:5]  # bucket 8, three padded rows
+
+
 @pytest.mark.parametrize("m,n,k", [(1, 2048, 2048), (16, 3072, 2048), (17, 2048, 5632), (64, 11264, 2048), (33, 32000, 2048), (5, 384, 200), (100, 3072, 2048), (256, 2048, 5632), (200, 11264, 2048)])
 def test_skinny_gemm_matches_fp32(m, n, k):
     """Decode-sized batches take the split-K kernel with the weight as the MMA's M operand."""

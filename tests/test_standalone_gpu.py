@@ -1,4 +1,4 @@
-"""The torch-free attention check binary (CPU fp32 reference inside the program) builds and passes on the GPU."""
+"""The torch-free check binaries (CPU fp32 references inside the programs) build and pass on the GPU."""
 
 import subprocess
 
@@ -7,10 +7,11 @@ import pytest
 pytestmark = pytest.mark.gpu
 
 
-def test_standalone_attention_check_passes():
+@pytest.mark.parametrize("which", ["attn_check", "quant_paged_check"])
+def test_standalone_check_passes(which):
     from astrai_b200.ops.build import build_standalone
 
-    exe = build_standalone()
+    exe = build_standalone(which)
     proc = subprocess.run([str(exe)], capture_output=True, text=True, timeout=300)
     assert proc.returncode == 0, proc.stdout[-3000:] + proc.stderr[-2000:]
     assert "all checks passed" in proc.stdout and "FAIL" not in proc.stdout
