@@ -30,6 +30,9 @@ from astrai_b200.cli.common import flatten_sections, load_yaml, merge_config, to
 @click.option("--chunked_prefill/--no-chunked_prefill", default=False,
               help="Spread long prompts over several steps (at most --max_prefill_tokens prompt tokens per step).")
 @click.option("--max_prefill_tokens", type=int, default=8192)
+@click.option("--prefill_defer_steps", type=int, default=8,
+              help="Under load (32 or more requests decoding) new prompts wait up to this many decode steps so that "
+                   "several are prefilled in one forward; 0 prefills every prompt at once.")
 @click.option("--reload", is_flag=True, default=False)
 @click.pass_context
 def serve_command(ctx: click.Context, config: Optional[str], **opts):
@@ -39,7 +42,7 @@ def serve_command(ctx: click.Context, config: Optional[str], **opts):
 
     engine_kwargs = {"enable_cuda_graph": o["cuda_graph"], "paged": o["page_size"] > 1, "page_size": o["page_size"],
                      "kv_cache_tokens": o["kv_cache_tokens"], "chunked_prefill": o["chunked_prefill"],
-                     "max_prefill_tokens": o["max_prefill_tokens"]}
+                     "max_prefill_tokens": o["max_prefill_tokens"], "prefill_defer_steps": o["prefill_defer_steps"]}
     run_server(param_path=Path(o["param_path"]), host=o["host"], port=o["port"], reload=o["reload"], device=o["device"],
                dtype=torch_dtype(o["dtype"]), max_batch_size=o["max_batch_size"], max_seq_len=o["max_seq_len"], **engine_kwargs)
 

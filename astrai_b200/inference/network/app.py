@@ -81,7 +81,10 @@ class MessagesRequest(BaseModel):
 
 def create_engine(param_path: Path, device: str = "cuda", dtype: torch.dtype = torch.bfloat16, max_batch_size: int = 16,
                   max_seq_len: Optional[int] = None, page_size: int = 16, kv_cache_tokens: Optional[int] = None,
-                  paged: bool = True, max_prefill_tokens: int = 8192, enable_cuda_graph: bool = True) -> InferenceEngine:
+                  paged: bool = True, max_prefill_tokens: int = 8192, enable_cuda_graph: bool = True,
+                  **scheduler_kwargs) -> InferenceEngine:
+    """Model + tokenizer from ``param_path`` behind an engine.  ``scheduler_kwargs`` go to the scheduler unchanged
+    (``chunked_prefill``, ``prefill_defer_steps`` ...)."""
     from astrai_b200.models import AutoModel
     from astrai_b200.tokenize import AutoTokenizer
 
@@ -92,7 +95,7 @@ def create_engine(param_path: Path, device: str = "cuda", dtype: torch.dtype = t
     model = AutoModel.from_pretrained(param_path).to(device=device, dtype=dtype).eval()
     return InferenceEngine(model=model, tokenizer=tokenizer, max_batch_size=max_batch_size, max_seq_len=max_seq_len,
                            enable_cuda_graph=enable_cuda_graph, page_size=page_size, kv_cache_tokens=kv_cache_tokens,
-                           paged=paged, max_prefill_tokens=max_prefill_tokens)
+                           paged=paged, max_prefill_tokens=max_prefill_tokens, **scheduler_kwargs)
 
 
 @asynccontextmanager

@@ -222,7 +222,10 @@ class Executor:
         return self._buckets[i] if i < len(self._buckets) else b
 
     # -- sampling ---------------------------------------------------------------------------------------------------------
-    def _sample(self, logits: Tensor, tasks: List[Task], return_logprobs: bool, info: Optional[SamplingBatchInfo] = None):
+    def _sample(self, logits: Tensor, tasks: List[Task], return_logprobs: bool, info: Optional[SamplingBatchInfo] = None,
+                wait: bool = True):
+        """Launch the sampler; ``wait=False`` returns a zero-argument callable that reads the tokens back (the one
+        device -> host transfer of a step), so the caller can queue more work behind the launch first."""
         info = info or build_sampling_info(tasks, self.device)
         hist = hist_mask = None
         if info.has_freq:
@@ -237,21 +240,26 @@ class Executor:
         out = sample(logits, temperature=info.temperatures, top_k=info.top_ks, top_p=info.top_ps,
                      frequency_penalty=info.freq_penalties, input_ids=hist, input_mask=hist_mask,
                      return_logprobs=return_logprobs, hints=info.hints)
-        if not return_logprobs:
-            return out.tolist()
-        tokens, logp = out
-        tokens, logp = tokens.tolist(), logp.tolist()
-        for t, lp in zip(tasks, logp):
-            t.output_logprobs.append(float(lp))
-        return list(zip(tokens, logp))
+
+        def finish():
+            if not return_logprobs:
+                return out.tolist()
+            tokens, logp = out
+            tokens, logp = tokens.tolist(), logp.tolist()
+            for t, lp in zip(tasks, logp):
+                t.output_logprobs.append(float(lp))
+            return list(zip(tokens, logp))
+
+        return finish() if wait else finish
 
     # -- prefill ------------------------------------------------------------------------------------------------------------
     def execute_prefill(self, tasks: List[Task], prompt_len: Optional[int] = None, start_pos: Optional[int] = None,
-                        return_logprobs: bool = False, end_positions: Optional[Dict[str, int]] = None):
+                        return_logprobs: bool = False, end_positions: Optional[Dict[str, int]] = None, wait: bool = True):
         """Packed prefill of ``tasks`` (any mix of lengths).  Each request recomputes positions ``[start, end)`` where
         ``start`` is where its previous chunk stopped, else ``min(cached prefix, len - 1)``, unless ``start_pos`` forces
         one value for all; ``end`` is the prompt length unless ``end_positions[task_id]`` stops the chunk earlier
-        (chunked prefill).  Only requests whose chunk reaches the end of the prompt are sampled and returned."""
+        (chunked prefill).  Only requests whose chunk reaches the end of the prompt are sampled and returned.
+        ``wait=False``: the second element of the result is a callable that reads the sampled tokens back."""
         tasks = sorted(tasks, key=lambda t: t.task_id)
         ids = [t.task_id for t in tasks]
         lens = [len(t.prompt_ids) for t in tasks]
@@ -261,8 +269,9 @@ class Executor:
             starts = [t.prefill_pos if t.prefill_pos is not None else min(self.task_cache.task_cached(t.task_id), n - 1)
                       for t, n in zip(tasks, lens)]
         ends = [min(n, (end_positions or {}).get(t.task_id, n)) for t, n in zip(tasks, lens)]
+        nothing = ([], []) if wait else ([], list)
         if any(s >= e for s, e in zip(starts, ends)):
-            return [], []
+            return nothing
         for t, s in zip(tasks, starts):
             if t.prefill_start is None:
                 t.prefill_start = s
@@ -285,15 +294,16 @@ class Executor:
             out = self.model(input_ids, position_ids=position_ids, kv_cache=kv, fwd="prefill",
                              **({"return_logits": False} if fused else {}))
             if not complete:
-                return [], []
+                return nothing
             rows = torch.tensor(last, dtype=torch.long, device=self.device)
             logits = self.model.lm_head(out["hidden_states"][rows]) if fused else out["logits"][rows]
-        return complete, self._sample(logits, complete, return_logprobs)
+            return complete, self._sample(logits, complete, return_logprobs, wait=wait)
 
     # -- decode -------------------------------------------------------------------------------------------------------------
-    def execute_decode(self, tasks: List[Task], return_logprobs: bool = False):
+    def execute_decode(self, tasks: List[Task], return_logprobs: bool = False, wait: bool = True):
+        """One token for every task.  ``wait=False`` returns a callable that reads the sampled tokens back."""
         if not tasks:
-            return []
+            return [] if wait else list
         b, ws = len(tasks), self._workspace
         tokens = ws.fill_input_ids([t.output_ids[-1] if t.output_ids else t.prompt_ids[-1] for t in tasks])
         ids = [t.task_id for t in tasks]
@@ -317,4 +327,4 @@ class Executor:
                                               position_ids=ws.position_ids[:rows], fwd="decode")
             else:
                 out = self.model(input_ids=tokens, kv_cache=kv, position_ids=ws.position_ids[:b], fwd="decode")
-        return self._sample(out["logits"][:b], tasks, return_logprobs, info=info)
+            return self._sample(out["logits"][:b], tasks, return_logprobs, info=info, wait=wait)

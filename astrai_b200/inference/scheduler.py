@@ -27,7 +27,8 @@ class InferenceScheduler:
     def __init__(self, model, tokenizer, max_batch_size: int = 16, max_seq_len: Optional[int] = None, device=None,
                  dtype=None, cache: Optional[PagePool] = None, enable_cuda_graph: bool = True, backend=None,
                  page_size: int = 16, kv_cache_tokens: Optional[int] = None, paged: bool = True,
-                 max_prefill_tokens: int = 8192, chunked_prefill: bool = False):
+                 max_prefill_tokens: int = 8192, chunked_prefill: bool = False, prefill_defer_steps: int = 8,
+                 prefill_defer_min_batch: int = 32, prefill_defer_tokens: int = 2048):
         cfg = model.config
         if max_seq_len is None:
             max_seq_len = cfg.max_position_embeddings
@@ -48,6 +49,13 @@ class InferenceScheduler:
         # chunked prefill: at most max_prefill_tokens prompt tokens per step over all requests; a long prompt takes
         # several steps and the running requests keep decoding in between (the reference never mixes the two)
         self.chunked_prefill = chunked_prefill
+        # Admission of new prompts under load: a prefill forward is hundreds of eager launches whatever its size, so with
+        # at least `prefill_defer_min_batch` requests decoding, newly arrived prompts wait until `prefill_defer_tokens`
+        # prompt tokens are pending or `prefill_defer_steps` decode steps have passed, and are then prefilled together
+        # (0 steps = never wait).  With a small decode batch a new prompt is prefilled at once.
+        self.prefill_defer_steps, self.prefill_defer_min_batch = int(prefill_defer_steps), int(prefill_defer_min_batch)
+        self.prefill_defer_tokens = int(prefill_defer_tokens)
+        self._steps_since_prefill = 0
         self._backend_name = "tcgen05" if self.device.type == "cuda" else "torch_native"
         self._stop_event = threading.Event()
         self._loop_thread: Optional[threading.Thread] = None
@@ -97,47 +105,66 @@ class InferenceScheduler:
             left -= take
         return group, ends
 
+    def _defer_prefill(self, fresh: List[Task], n_decoding: int) -> bool:
+        if not fresh or self.prefill_defer_steps <= 0 or n_decoding < self.prefill_defer_min_batch:
+            return False
+        if self._steps_since_prefill >= self.prefill_defer_steps:
+            return False
+        pending = 0
+        for t in fresh:
+            done = t.prefill_pos if t.prefill_pos is not None else min(self._task_cache.task_cached(t.task_id), len(t.prompt_ids) - 1)
+            pending += len(t.prompt_ids) - done
+        return pending < self.prefill_defer_tokens
+
     def _step(self, tasks: List[Task], return_logprobs: bool = False) -> Tuple[List[Task], List[Task]]:
-        """Advance every task by one token.  Returns (tasks that produced a token, tasks aborted for lack of room)."""
-        produced: List[Task] = []
+        """Advance every task by one token.  Returns (tasks that produced a token, tasks aborted for lack of room).
+
+        The decode forward of the requests that are past their prompt is launched first (one graph replay) and the
+        prefill forward of the new prompts is issued while it runs; the sampled tokens of both are read back afterwards,
+        so the host time of the prefill launches overlaps the decode step on the GPU."""
         fresh = [t for t in tasks if not t.prefill_done and t.prompt_ids]
-        done_now = set()
-        if self.chunked_prefill:
-            group, ends = self._prefill_chunk(fresh)
-            plan = [(group, ends)] if group else []
-        else:
-            plan = [(g, None) for g in self._prefill_batches(fresh)]
-        for group, ends in plan:
-            for t in group:
-                t.input_tokens = len(t.prompt_ids)
-            with self._metrics.record([t.task_id for t in group], "prefill"):
-                ordered, outs = self._executor.execute_prefill(group, return_logprobs=return_logprobs, end_positions=ends)
-            for t, o in zip(ordered, outs):
-                t.output_ids.append(o[0] if return_logprobs else o)
-                t.output_tokens += 1
-                t.mark_prefill_done()
-                done_now.add(t.task_id)
-                produced.append(t)
-                # pages fully covered by the prompt become shareable from the first recomputed page on
-                self._task_cache.task_record_hashes(t.task_id, t.prompt_ids, (t.prefill_start or 0) // self._cache.page_size)
         decode, aborted = [], []
         for t in tasks:
-            if t.task_id in done_now or not t.prefill_done:
+            if not t.prefill_done:
                 continue
             if self._task_cache.task_extend(t.task_id, t.next_pos):
                 decode.append(t)
             else:
                 t.status = TaskStatus.ABORTED
                 aborted.append(t)
-        if decode:
-            with self._metrics.record([t.task_id for t in decode], "decode"):
-                outs = self._executor.execute_decode(decode, return_logprobs=return_logprobs)
-            for t, o in zip(decode, outs):
-                t.output_ids.append(o[0] if return_logprobs else o)
-                t.output_tokens += 1
-                t.advance_kv()
-                produced.append(t)
-        return produced, aborted
+        if self._defer_prefill(fresh, len(decode)):
+            plan = []
+            self._steps_since_prefill += 1
+        elif self.chunked_prefill:
+            group, ends = self._prefill_chunk(fresh)
+            plan = [(group, ends)] if group else []
+        else:
+            plan = [(g, None) for g in self._prefill_batches(fresh)]
+        if plan:
+            self._steps_since_prefill = 0
+        first: List[Task] = []
+        with self._metrics.record([t.task_id for t in decode], "decode"):
+            read_decode = self._executor.execute_decode(decode, return_logprobs=return_logprobs, wait=False) if decode else None
+            for group, ends in plan:
+                for t in group:
+                    t.input_tokens = len(t.prompt_ids)
+                with self._metrics.record([t.task_id for t in group], "prefill"):
+                    ordered, read = self._executor.execute_prefill(group, return_logprobs=return_logprobs, end_positions=ends,
+                                                                   wait=False)
+                    outs = read()
+                for t, o in zip(ordered, outs):
+                    t.output_ids.append(o[0] if return_logprobs else o)
+                    t.output_tokens += 1
+                    t.mark_prefill_done()
+                    first.append(t)
+                    # pages fully covered by the prompt become shareable from the first recomputed page on
+                    self._task_cache.task_record_hashes(t.task_id, t.prompt_ids, (t.prefill_start or 0) // self._cache.page_size)
+            if read_decode is not None:
+                for t, o in zip(decode, read_decode()):
+                    t.output_ids.append(o[0] if return_logprobs else o)
+                    t.output_tokens += 1
+                    t.advance_kv()
+        return first + decode, aborted
 
     def _retire(self, stop_ids):
         for task in self._task_mgr.remove_finished_tasks(stop_ids):

@@ -1,0 +1,487 @@
+"""Serving building blocks in isolation: the producer / consumer hand-over of ``generate``, tasks and their queues, the
+protocol builders' wire formats, and the synchronous ``run_batch`` path (behaviours the reference checks in
+``tests/inference/test_engine.py``, ``test_task.py``, ``test_protocol.py`` and ``test_scheduler.py``)."""
+
+import json
+import threading
+import time
+from types import SimpleNamespace
+
+import pytest
+import torch
+
+from helpers import build_tokenizer_dir, tiny_config
+
+
+# ------------------------------------------------------------------------------------------------- GenerateResult
+def test_result_collects_pieces_per_prompt_and_in_arrival_order():
+    from astrai_b200.inference.engine import GenerateResult
+    from astrai_b200.inference.task import STOP
+
+    r = GenerateResult(count=2)
+    r.append("a", 0)
+    r.append("x", 1)
+    r.append("b", 0)
+    assert r.pop_all() == [(0, "a"), (1, "x"), (0, "b")] and r.pop_all() == []
+    r.append(STOP, 1)
+    r.append("c", 0)
+    assert r.get_results() == ["abc", "x"]
+    assert [i for i, t in r.pop_all() if t is STOP] == [1]
+
+
+def test_result_completion_counts_each_prompt_once():
+    from astrai_b200.inference.engine import GenerateResult
+    from astrai_b200.inference.task import STOP
+
+    r = GenerateResult(count=2)
+    r.append(STOP, 0)
+    r.append(STOP, 0)  # a second end marker for the same prompt must not release the waiter
+    with pytest.raises(TimeoutError, match="1 of 2"):
+        r.wait_completion(timeout=0.05)
+    r.append(STOP, 1)
+    r.wait_completion(timeout=0.05)
+    GenerateResult(count=0).wait_completion(timeout=0.01)  # nothing to wait for
+
+
+def test_result_wait_blocks_until_a_producer_delivers():
+    from astrai_b200.inference.engine import GenerateResult
+
+    r = GenerateResult()
+    assert r.wait(timeout=0.02) is False
+    t0 = time.time()
+    threading.Timer(0.05, lambda: r.append("late")).start()
+    assert r.wait(timeout=2.0) is True and time.time() - t0 < 1.5
+    assert r.wait(timeout=0.0) is True  # what wait() took out of the inbox is still there for pop_all()
+    assert r.pop_all() == [(0, "late")]
+
+
+def test_result_is_safe_under_concurrent_producers():
+    from astrai_b200.inference.engine import GenerateResult
+    from astrai_b200.inference.task import STOP
+
+    n, per = 8, 200
+    r = GenerateResult(count=n)
+
+    def produce(i):
+        for k in range(per):
+            r.append(f"{k},", i)
+        r.append(STOP, i)
+
+    threads = [threading.Thread(target=produce, args=(i,)) for i in range(n)]
+    for t in threads:
+        t.start()
+    r.wait_completion(timeout=10)
+    for t in threads:
+        t.join()
+    assert r.get_results() == ["".join(f"{k}," for k in range(per))] * n
+    assert len(r.pop_all()) == n * (per + 1)
+
+
+# ---------------------------------------------------------------------------------------------------------- tasks
+class _Tok:
+    stop_ids = [2]
+
+    def encode(self, text):
+        return [ord(c) % 50 + 3 for c in text]
+
+    def decode(self, ids):
+        return "".join(chr(97 + i % 26) for i in ids)
+
+
+def test_task_lifecycle_fields():
+    from astrai_b200.inference.task import Task, TaskStatus
+
+    t = Task("t", [5, 6, 7], max_tokens=2)
+    assert t.status is TaskStatus.PENDING and t.next_pos == 0 and not t.prefill_done
+    t.input_tokens = 3
+    t.mark_prefill_done()
+    assert t.prefill_done and t.next_pos == 3
+    t.advance_kv()
+    assert t.next_pos == 4
+    assert not t.is_finished({2})
+    t.output_ids.append(9)
+    t.output_tokens = 1
+    assert not t.is_finished({2})
+    t.output_ids.append(2)
+    assert t.is_finished({2})  # stop id
+    u = Task("u", [1], max_tokens=1)
+    u.output_ids.append(8)
+    u.output_tokens = 1
+    assert u.is_finished(set())  # budget reached
+    assert not Task("v", [1], max_tokens=None).is_finished({2})
+
+
+def test_manager_truncates_long_prompts_from_the_left_and_caps_max_tokens():
+    from astrai_b200.inference.task import TaskManager
+
+    m = TaskManager(_Tok(), max_batch_size=2, max_seq_len=8)
+    long = m.make_task(list(range(20)), max_tokens=5)
+    assert long.prompt_ids == list(range(12, 20)) and long.max_tokens == 0  # the last 8 tokens, no room to generate
+    short = m.make_task([1, 2, 3], max_tokens=100)
+    assert short.max_tokens == 5
+    assert m.make_task([1, 2, 3], max_tokens=None).max_tokens == 5
+    assert m.make_task([1, 2, 3], max_tokens=2).max_tokens == 2
+
+
+def test_manager_queues_are_fifo_and_rejections_go_back_to_the_front():
+    from astrai_b200.inference.task import TaskManager, TaskStatus
+
+    m = TaskManager(_Tok(), max_batch_size=4, max_seq_len=32)
+    ids = [m.add_task([i + 3]) for i in range(5)]
+    assert m.get_stats()["waiting_queue"] == 5 and m.has_work()
+    got = m.pull_candidates(3)
+    assert [t.task_id for t in got] == ids[:3]
+    m.activate(got[0])
+    assert got[0].status is TaskStatus.RUNNING and m.get_stats()["active_tasks"] == 1
+    m.return_to_waiting(got[1:])
+    assert [t.task_id for t in m.get_waiting_tasks()] == ids[1:]  # original order restored
+    assert m.pull_candidates(10)[0].task_id == ids[1]
+
+
+def test_manager_accepts_text_or_ids_and_registers_callbacks():
+    from astrai_b200.inference.task import TaskManager
+
+    m = TaskManager(_Tok(), max_seq_len=64)
+    seen = []
+    a = m.add_task("hey", stream_callback=seen.append)
+    b = m.add_task([7, 8, 9])
+    tasks = {t.task_id: t for t in m.get_waiting_tasks()}
+    assert tasks[a].prompt_ids == _Tok().encode("hey") and tasks[b].prompt_ids == [7, 8, 9]
+    m.invoke_callback(a, "x")
+    m.invoke_callback(b, "ignored")  # no callback registered: a no-op
+    assert seen == ["x"]
+
+
+def test_manager_remove_task_from_either_queue():
+    from astrai_b200.inference.task import TaskManager
+
+    m = TaskManager(_Tok(), max_seq_len=64)
+    a, b = m.add_task([3]), m.add_task([4])
+    first = m.pull_candidates(1)[0]
+    m.activate(first)
+    assert [t.task_id for t in m.remove_task(a)] == [a]  # active tasks are handed back so their cache can be freed
+    assert m.remove_task(b) == [] and not m.has_work()
+    assert m.remove_task("unknown") == []
+
+
+def test_manager_retires_finished_and_aborted_tasks_and_counts_tokens():
+    from astrai_b200.inference.task import TaskManager, TaskStatus
+
+    m = TaskManager(_Tok(), max_seq_len=64)
+    for i in range(3):
+        m.add_task([i + 3], max_tokens=4)
+    a, b, c = m.pull_candidates(3)
+    for t in (a, b, c):
+        m.activate(t)
+    a.output_ids, a.output_tokens = [9, 2], 2          # stop id
+    b.status = TaskStatus.ABORTED                      # ran out of cache
+    c.output_ids, c.output_tokens = [9], 1             # still running
+    done = m.remove_finished_tasks({2})
+    assert {t.task_id for t in done} == {a.task_id, b.task_id} and a.status is TaskStatus.FINISHED
+    assert [t.task_id for t in m.get_active_tasks()] == [c.task_id]
+    assert m.get_stats()["total_tokens"] == 2  # aborted tasks do not count
+
+
+def test_manager_wait_returns_on_wake_and_on_new_work():
+    from astrai_b200.inference.task import TaskManager
+
+    m = TaskManager(_Tok(), max_seq_len=64)
+    t0 = time.time()
+    threading.Timer(0.05, m.wake).start()
+    m.wait_for_tasks(timeout=5.0)
+    assert time.time() - t0 < 2.0
+    m.add_task([3])
+    t0 = time.time()
+    m.wait_for_tasks(timeout=5.0)  # work is queued: returns at once
+    assert time.time() - t0 < 0.5
+    m.clear_queues()
+    assert not m.has_work()
+
+
+# ------------------------------------------------------------------------------------------------------- protocol
+def test_stop_checker_matches_substrings_and_ignores_empty_sequences():
+    from astrai_b200.inference.network.protocol import StopChecker
+
+    c = StopChecker(["END", "", "\n\n"])
+    assert c.check("the END is near") == "END" and c.check("a\n\nb") == "\n\n" and c.check("nothing") is None
+    assert StopChecker([]).check("anything") is None and StopChecker([""]).check("") is None
+
+
+def test_sse_helpers():
+    from astrai_b200.inference.network.protocol import GenContext, StopInfo, sse_done, sse_event
+
+    assert sse_done() == "data: [DONE]\n\n"
+    ev = sse_event({"a": "é"}, event="message_start")
+    assert ev.startswith("event: message_start\ndata: ") and json.loads(ev.split("data: ", 1)[1]) == {"a": "é"} and "é" in ev
+    assert sse_event({"a": 1}).startswith("data: ")
+    ctx = GenContext("id", 1, "m")
+    assert (ctx.prompt_tokens, ctx.completion_tokens) == (0, 0)
+    assert StopInfo().matched is None and StopInfo("x", "ax", "a").yielded == "a"
+
+
+class _ChatTok:
+    def apply_chat_template(self, messages, tokenize=False, tools=None):
+        return "|".join(f"{m['role']}:{m['content']}" for m in messages) + (f"|tools={len(tools)}" if tools else "")
+
+    def encode(self, text):
+        return list(text.encode())
+
+
+def _data(event: str):
+    return json.loads(event.split("data: ", 1)[1])
+
+
+def test_openai_builder_formats():
+    from astrai_b200.inference.network.app import ChatCompletionRequest, ChatMessage
+    from astrai_b200.inference.network.openai import OpenAIResponseBuilder
+    from astrai_b200.inference.network.protocol import StopInfo
+
+    b = OpenAIResponseBuilder()
+    req = ChatCompletionRequest(model="m1", messages=[ChatMessage(role="system", content="be brief"), ChatMessage(role="user", content="hi")],
+                                stop="END")
+    prompt, ctx, stops = b.prepare(req, SimpleNamespace(tokenizer=_ChatTok()))
+    assert prompt == "system:be brief|user:hi" and stops == ["END"] and ctx.model == "m1" and ctx.resp_id.startswith("chatcmpl-")
+    assert b.prepare(ChatCompletionRequest(messages=[ChatMessage(role="user", content="x")], stop=["a", "b"]),
+                     SimpleNamespace(tokenizer=_ChatTok()))[2] == ["a", "b"]
+    assert b.prepare(ChatCompletionRequest(messages=[ChatMessage(role="user", content="x")]),
+                     SimpleNamespace(tokenizer=_ChatTok()))[2] == []
+    prompt, ctx, _ = b.prepare(req, SimpleNamespace(tokenizer=_ChatTok()))
+    start = _data(b.format_stream_start(ctx)[0])
+    assert start["object"] == "chat.completion.chunk" and start["choices"][0]["delta"] == {"role": "assistant"}
+    assert start["created"] == ctx.created and start["id"] == ctx.resp_id
+    chunk = _data(b.format_chunk("tok")[0])
+    assert chunk["choices"][0]["delta"] == {"content": "tok"} and chunk["choices"][0]["finish_reason"] is None and chunk["created"] == 0
+    ctx.prompt_tokens, ctx.completion_tokens = 7, 3
+    end = b.format_stream_end(ctx, StopInfo())
+    assert _data(end[0])["choices"][0]["finish_reason"] == "stop" and _data(end[0])["choices"][0]["delta"] == {}
+    assert _data(end[1]) == {"prompt_tokens": 7, "completion_tokens": 3, "total_tokens": 10}
+    full = b.format_response(ctx, "answer", StopInfo())
+    assert full["object"] == "chat.completion" and full["choices"][0]["message"] == {"role": "assistant", "content": "answer"}
+    assert full["choices"][0]["finish_reason"] == "stop" and full["usage"]["total_tokens"] == 10
+
+
+def test_openai_builder_warns_about_ignored_parameters(caplog):
+    from astrai_b200.inference.network.app import ChatCompletionRequest, ChatMessage
+    from astrai_b200.inference.network.openai import OpenAIResponseBuilder
+
+    eng = SimpleNamespace(tokenizer=_ChatTok())
+    with caplog.at_level("WARNING"):
+        OpenAIResponseBuilder().prepare(ChatCompletionRequest(messages=[ChatMessage(role="user", content="x")]), eng)
+    assert "not supported" not in caplog.text  # defaults are silent
+    with caplog.at_level("WARNING"):
+        OpenAIResponseBuilder().prepare(ChatCompletionRequest(messages=[ChatMessage(role="user", content="x")], n=2, user="u",
+                                                              presence_penalty=0.5), eng)
+    for name in ("'n'", "'user'", "'presence_penalty'"):
+        assert name in caplog.text
+
+
+def test_anthropic_builder_prepare_and_stream_events():
+    from astrai_b200.inference.network.anthropic import AnthropicResponseBuilder, first_text
+    from astrai_b200.inference.network.app import AnthropicMessage, MessagesRequest
+    from astrai_b200.inference.network.protocol import StopInfo
+
+    assert first_text("plain") == "plain"
+    assert first_text([{"type": "image", "source": {}}, {"type": "text", "text": "second"}]) == "second"
+    assert first_text([]) == "" and first_text([{"type": "image"}]) == ""
+    b = AnthropicResponseBuilder()
+    req = MessagesRequest(model="claude-ish", system="sys", stop_sequences=["STOP"],
+                          messages=[AnthropicMessage(role="user", content=[{"type": "text", "text": "hello"}]),
+                                    AnthropicMessage(role="assistant", content=[{"type": "image"}])])
+    prompt, ctx, stops = b.prepare(req, SimpleNamespace(tokenizer=_ChatTok()))
+    assert prompt == "system:sys|user:hello" and stops == ["STOP"] and ctx.resp_id.startswith("msg_")  # the empty turn is dropped
+    ctx.prompt_tokens = 4
+    start = b.format_stream_start(ctx)
+    assert [e.split("\n")[0] for e in start] == ["event: message_start", "event: content_block_start"]
+    assert _data(start[0])["message"]["usage"] == {"input_tokens": 4} and _data(start[0])["message"]["content"] == []
+    assert _data(b.format_chunk("hi")[0])["delta"] == {"type": "text_delta", "text": "hi"}
+    ctx.completion_tokens = 2
+    end = b.format_stream_end(ctx, StopInfo())
+    assert [e.split("\n")[0] for e in end] == ["event: content_block_stop", "event: message_delta", "event: message_stop"]
+    assert _data(end[1])["delta"] == {"stop_reason": "end_turn", "stop_sequence": None} and _data(end[1])["usage"] == {"output_tokens": 2}
+
+
+def test_anthropic_stop_sequence_trims_and_flushes_unsent_text():
+    from astrai_b200.inference.network.anthropic import AnthropicResponseBuilder
+    from astrai_b200.inference.network.protocol import GenContext, StopInfo
+
+    b, ctx = AnthropicResponseBuilder(), GenContext("msg_1", 0, "m", 3, 5)
+    # "Hello wor" was streamed, the piece "ld STOP tail" completed the stop sequence: "ld " must still reach the client
+    end = b.format_stream_end(ctx, StopInfo(matched="STOP", body="Hello world STOP tail", yielded="Hello wor"))
+    assert _data(end[0])["delta"]["text"] == "ld " and end[1].startswith("event: content_block_stop")
+    assert _data(end[2])["delta"] == {"stop_reason": "stop_sequence", "stop_sequence": "STOP"}
+    # everything before the stop sequence was already sent: no extra delta
+    end = b.format_stream_end(ctx, StopInfo(matched="STOP", body="abcSTOP", yielded="abc"))
+    assert end[0].startswith("event: content_block_stop")
+    full = b.format_response(ctx, "Hello world STOP tail", StopInfo(matched="STOP", body="Hello world STOP tail"))
+    assert full["content"] == [{"type": "text", "text": "Hello world "}] and full["stop_reason"] == "stop_sequence"
+    assert full["usage"] == {"input_tokens": 3, "output_tokens": 5}
+    plain = b.format_response(ctx, "all of it", StopInfo())
+    assert plain["content"][0]["text"] == "all of it" and plain["stop_reason"] == "end_turn" and plain["stop_sequence"] is None
+
+
+# ------------------------------------------------------------------------------------------------------ run_batch
+@pytest.fixture(scope="module")
+def served(tmp_path_factory):
+    from astrai_b200.models import AutoRegressiveLM
+    from astrai_b200.tokenize import AutoTokenizer
+
+    tok = AutoTokenizer.from_pretrained(build_tokenizer_dir(str(tmp_path_factory.mktemp("tok"))))
+    torch.manual_seed(0)
+    model = AutoRegressiveLM(tiny_config(vocab_size=512, hidden_size=32, intermediate_size=64, max_position_embeddings=128)).eval()
+    return model, tok
+
+
+def _sched(served, **kw):
+    from astrai_b200.inference import InferenceScheduler
+
+    model, tok = served
+    return InferenceScheduler(model, tok, enable_cuda_graph=False, **{"max_batch_size": 4, "max_seq_len": 64, **kw})
+
+
+def test_run_batch_edge_cases(served):
+    s = _sched(served)
+    assert s.run_batch([], max_tokens=4) == []
+    assert s.run_batch([[5, 6, 7]], max_tokens=0) == [[]]
+    out = s.run_batch([[5, 6, 7], [], [9] * 100], max_tokens=3, temperature=0.0)
+    assert len(out[0]) == 3 and out[1] == []  # an empty prompt yields nothing
+    assert len(out[2]) <= 3  # the over-long prompt keeps its tail and whatever room is left
+    assert s.get_stats()["active_tasks"] == 0 and s.get_stats()["waiting_queue"] == 0
+
+
+def test_run_batch_logprobs_are_aligned_with_tokens(served):
+    model, _ = served
+    s = _sched(served)
+    prompt = [11, 12, 13, 14]
+    toks, lps = s.run_batch([prompt], max_tokens=5, temperature=0.0, return_logprobs=True)[0]
+    assert len(toks) == len(lps) == 5 and all(lp <= 0 for lp in lps)
+    with torch.no_grad():
+        logits = model(torch.tensor([prompt + toks[:-1]]))["logits"][0, len(prompt) - 1:].float()
+    ref = torch.log_softmax(logits, -1).gather(1, torch.tensor(toks)[:, None])[:, 0]
+    assert torch.allclose(torch.tensor(lps), ref, atol=1e-4)
+
+
+def test_run_batch_more_prompts_than_batch_slots(served):
+    """The synchronous path takes what fits at once (one cache row per prompt) and answers the rest with empty lists, as
+    the reference's ``run_batch`` does; the prompts it takes decode exactly as they do alone."""
+    s = _sched(served, max_batch_size=2)
+    prompts = [[20 + i, 21 + i, 22 + i] for i in range(5)]
+    together = s.run_batch(prompts, max_tokens=4, temperature=0.0)
+    alone = [_sched(served, max_batch_size=1).run_batch([p], max_tokens=4, temperature=0.0)[0] for p in prompts]
+    assert together[:2] == alone[:2] and together[2:] == [[], [], []]
+    assert s.run_batch(prompts[2:4], max_tokens=4, temperature=0.0) == alone[2:4]  # the rows were given back
+
+
+def test_decode_steps_do_not_leak_state_between_batches(served):
+    s = _sched(served)
+    a = s.run_batch([[30, 31, 32], [40, 41]], max_tokens=6, temperature=0.0)
+    b = s.run_batch([[40, 41]], max_tokens=6, temperature=0.0)  # same request alone, after the first batch is gone
+    assert b[0] == a[1]
+    c = s.run_batch([[50], [30, 31, 32]], max_tokens=6, temperature=0.0)
+    assert c[1] == a[0]
+
+
+def test_streaming_callbacks_deliver_text_then_stop(served):
+    from astrai_b200.inference.task import STOP
+
+    s = _sched(served)
+    s.start()
+    try:
+        got, done = [], threading.Event()
+
+        def cb(piece):
+            got.append(piece)
+            if piece is STOP:
+                done.set()
+
+        s.add_task([60, 61, 62], max_tokens=5, temperature=0.0, stream_callback=cb)
+        assert done.wait(timeout=30)
+        assert got[-1] is STOP and got.count(STOP) == 1 and all(isinstance(p, str) for p in got[:-1])
+        stats = s.get_stats()
+        assert stats["total_tasks"] == 1 and stats["active_tasks"] == 0
+    finally:
+        s.stop()
+
+
+# ------------------------------------------------------------------------------------- admission policy under load
+def test_prefill_is_deferred_only_under_load(served):
+    from astrai_b200.inference.task import Task
+
+    s = _sched(served, max_batch_size=64, prefill_defer_steps=4, prefill_defer_min_batch=8, prefill_defer_tokens=100)
+    fresh = [Task("f", list(range(3, 23)))]
+    assert not s._defer_prefill([], 50)                      # nothing waiting
+    assert not s._defer_prefill(fresh, 7)                    # small decode batch: prefill at once
+    assert s._defer_prefill(fresh, 8)                        # under load: wait for company
+    assert not s._defer_prefill([Task("g", list(range(3, 200)))], 8)  # enough prompt tokens pending for a forward of their own
+    s._steps_since_prefill = 4
+    assert not s._defer_prefill(fresh, 8)                    # waited long enough
+    off = _sched(served, prefill_defer_steps=0)
+    assert not off._defer_prefill(fresh, 1000)
+
+
+def test_deferred_admission_does_not_change_greedy_outputs(served):
+    """Prompts that arrive while others decode are held back for a few steps under the deferral policy; every request
+    still gets exactly the tokens it gets alone."""
+    from astrai_b200.inference.task import STOP
+
+    prompts = [[30 + i, 31 + i, 32 + i, 33 + i] for i in range(6)]
+    alone = [_sched(served, max_batch_size=1).run_batch([p], max_tokens=12, temperature=0.0)[0] for p in prompts]
+    model, tok = served
+    s = _sched(served, max_batch_size=8, prefill_defer_steps=3, prefill_defer_min_batch=2, prefill_defer_tokens=1000)
+    got = {i: [] for i in range(len(prompts))}
+    done = {i: threading.Event() for i in range(len(prompts))}
+    tasks = {}
+
+    def make_cb(i):
+        def cb(piece):
+            if piece is STOP:
+                done[i].set()
+        return cb
+
+    s.start()
+    try:
+        for i, p in enumerate(prompts):
+            tasks[i] = s.add_task(p, max_tokens=12, temperature=0.0, stream_callback=make_cb(i))
+            time.sleep(0.01)  # staggered arrivals: later prompts meet a running decode batch
+        for ev in done.values():
+            assert ev.wait(timeout=60)
+    finally:
+        s.stop()
+    # token ids are not streamed (text is); compare through the scheduler's own bookkeeping of finished tasks
+    finished = {t["task_id"]: t for t in s.get_stats().get("recent_tasks", [])}
+    assert len(finished) == len(prompts) and all(t["output_tokens"] == 12 for t in finished.values())
+    again = _sched(served, max_batch_size=8, prefill_defer_steps=3, prefill_defer_min_batch=2, prefill_defer_tokens=1000)
+    assert again.run_batch(prompts, max_tokens=12, temperature=0.0) == alone
+
+
+def test_create_engine_takes_the_serve_cli_options(tmp_path, served):
+    """The options the serve command forwards reach the scheduler, and the engine built from a model directory answers
+    over HTTP."""
+    from fastapi.testclient import TestClient
+
+    from astrai_b200.inference.network import get_app
+    from astrai_b200.inference.network.app import create_engine
+    from astrai_b200.serialization import Checkpoint
+
+    model, _ = served
+    d = tmp_path / "params"
+    build_tokenizer_dir(str(d))
+    Checkpoint(state_dict=model.state_dict(), config=model.config.to_dict()).save(str(d))
+    with pytest.raises(FileNotFoundError):
+        create_engine(tmp_path / "nowhere", device="cpu")
+    eng = create_engine(d, device="cpu", dtype=torch.float32, max_batch_size=2, max_seq_len=64, page_size=4, paged=True,
+                        enable_cuda_graph=False, chunked_prefill=True, max_prefill_tokens=16, prefill_defer_steps=0)
+    try:
+        assert eng.scheduler.chunked_prefill and eng.scheduler.max_prefill_tokens == 16 and eng.scheduler.prefill_defer_steps == 0
+        app = get_app()
+        app.state.server_config = {"_test": True}
+        with TestClient(app) as c:
+            app.state.engine = eng
+            assert c.get("/health").json() == {"status": "ok", "model_loaded": True}
+            r = c.post("/v1/chat/completions", json={"messages": [{"role": "user", "content": "hello"}], "max_tokens": 4})
+            assert r.status_code == 200 and r.json()["choices"][0]["message"]["role"] == "assistant"
+            assert r.json()["usage"]["completion_tokens"] <= 4
+            r = c.post("/v1/messages", json={"messages": [{"role": "user", "content": "hello"}], "max_tokens": 4, "stream": True})
+            assert r.status_code == 200 and "event: message_stop" in r.text and r.text.rstrip().endswith("data: [DONE]")
+            app.state.engine = None
+    finally:
+        eng.shutdown()
