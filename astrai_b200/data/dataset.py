@@ -10,7 +10,7 @@ from __future__ import annotations
 
 from functools import partial
 from pathlib import Path
-from typing import Callable, Dict, List, Optional
+from typing import Any, Callable, Dict, List, Optional
 
 import torch
 from torch import Tensor
@@ -70,6 +70,19 @@ def dpo_processor(record: dict, tokenizer, max_len: int = 2048) -> Dict[str, Ten
         "chosen_mask": torch.tensor(res["chosen_mask"], dtype=torch.bool),
         "rejected_mask": torch.tensor(res["rejected_mask"], dtype=torch.bool),
     }
+
+
+def pretokenized_processor(record: dict) -> Dict[str, Any]:
+    """A record of id lists (as the pipeline's JSONL writer stores them) as tensors; nested lists stay lists of tensors."""
+    out: Dict[str, Any] = {}
+    for key, value in record.items():
+        if not isinstance(value, list):
+            continue
+        if value and isinstance(value[0], list):
+            out[key] = [torch.tensor(v) for v in value]
+        else:
+            out[key] = torch.tensor(value)
+    return out
 
 
 def dpo_collate_fn(batch: List[Dict[str, Tensor]]) -> Dict[str, Tensor]:
@@ -155,6 +168,10 @@ class DatasetFactory(BaseFactory["BaseDataset"]):
             store.load(load_path, processor=processor, **kwargs)
         elif storage_type == "jsonl":
             transform = cls._jsonl_transform(load_path, tokenizer_path)
+            if transform is None and cls._is_pretokenized(train_type, load_path):
+                # shards written by the preprocessing pipeline with storage_format "jsonl": token ids, not text
+                store.load(load_path, processor=pretokenized_processor, **kwargs)
+                return cls.create(train_type, store=store)
             if transform is None:
                 raise FileNotFoundError(
                     "JSONL dataset config not found. Expected dataset_config.json alongside *.jsonl files, pass "
@@ -163,6 +180,21 @@ class DatasetFactory(BaseFactory["BaseDataset"]):
         else:
             store.load(load_path, **kwargs)
         return cls.create(train_type, store=store)
+
+    @classmethod
+    def _is_pretokenized(cls, train_type: str, path: str) -> bool:
+        """True when the first record already holds id lists under every key the dataset type needs."""
+        from astrai_b200.data.storage import JsonlSource
+
+        try:
+            required = cls._entries[train_type].required_keys
+        except (KeyError, AttributeError):
+            return False
+        records = JsonlSource(path).load()
+        if not records or not required:
+            return False
+        first = records[0]
+        return all(isinstance(first.get(k), list) for k in required)
 
     @staticmethod
     def _lazy_processor(train_type, storage_type, tokenizer_path, max_len) -> Optional[Callable]:

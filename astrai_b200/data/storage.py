@@ -3,7 +3,8 @@
 A store answers two kinds of question (reference ``astrai/dataset/storage.py:67-601``):
 * stream access - the data as one long token river cut into windows: ``num_samples = 0 if total <= w else
   (total - 1 - w) // stride + 1``; window ``i`` covers ``[min(i*stride, total-1-w), +w)``;
-* record access - the i-th record (bin shards with ``offsets`` in ``meta.json``, or one JSONL line).
+* record access - the i-th record (bin shards with ``offsets`` in ``meta.json`` - any number of shards, records are
+  numbered shard after shard, where the reference gives up on more than one shard - or one JSONL line).
 """
 
 from __future__ import annotations
@@ -46,7 +47,7 @@ class Store:
     def __init__(self, window_size: int = 0, stride: Optional[int] = None):
         self._data: Dict[str, list] = {}
         self._cum: Dict[str, List[int]] = {}
-        self._offsets: Dict[str, List[int]] = {}
+        self._offsets: Dict[str, List[Tuple[int, int, int]]] = {}
         self._length = 0
         self._num_records = 0
         self._window_size = int(window_size)
@@ -101,7 +102,7 @@ class Store:
         return [k for k, segs in self._data.items() if not (segs and isinstance(segs[0], list))]
 
     # -- registration ---------------------------------------------------------------------------------------------
-    def _normalize(self, raw: Dict[str, list], offsets: Optional[Dict[str, List[int]]] = None):
+    def _normalize(self, raw: Dict[str, list], offsets: Optional[Dict[str, list]] = None):
         lengths = []
         for key, segs in raw.items():
             self._data[key] = segs
@@ -116,16 +117,22 @@ class Store:
             self._cum[key] = cum
             lengths.append(total)
         self._length = min(lengths) if lengths else 0
-        usable: Dict[str, List[int]] = {}
-        for key, off in (offsets or {}).items():
+        # record index per key: (segment, begin, end) of every record.  `offsets[key]` holds one cumulative list per
+        # segment (shard) in segment order; a key whose shards do not all carry offsets has no record mode.
+        usable: Dict[str, List[Tuple[int, int, int]]] = {}
+        for key, per_seg in (offsets or {}).items():
             segs = self._data.get(key, [])
-            if len(segs) == 1 and len(off) > 1:
-                usable[key] = off
-            elif len(segs) > 1:
-                logger.warning("Key '%s' has %d segments with offsets: record mode disabled for it (merge shards or use JSONL).", key, len(segs))
+            if per_seg and not isinstance(per_seg[0], (list, tuple)):
+                per_seg = [per_seg]
+            if len(per_seg) != len(segs):
+                logger.warning("Key '%s': %d of %d shards carry record offsets: record mode disabled for it.", key, len(per_seg), len(segs))
+                continue
+            index = [(si, off[i], off[i + 1]) for si, off in enumerate(per_seg) for i in range(len(off) - 1)]
+            if index:
+                usable[key] = index
         self._offsets = usable
         if usable:
-            self._num_records = min(len(v) - 1 for v in usable.values())
+            self._num_records = min(len(v) for v in usable.values())
         elif self.segments_are_records:
             flat = [len(s) for s in self._data.values() if not (s and isinstance(s[0], list))]
             self._num_records = min(flat) if flat else 0
@@ -162,10 +169,10 @@ class Store:
         return {k: self._record(k, index) for k in keys}
 
     def _record(self, key: str, index: int):
-        off = self._offsets.get(key)
-        if off:
-            hi = off[index + 1] if index + 1 < len(off) else self._data[key][0].shape[0]
-            return self._data[key][0][off[index]:hi]
+        index_of = self._offsets.get(key)
+        if index_of:
+            seg, lo, hi = index_of[index]
+            return self._data[key][seg][lo:hi]
         return self._data[key][index]
 
 
@@ -182,19 +189,20 @@ class MmapStore(Store):
         if not metas:
             raise FileNotFoundError(f"No meta.json found under {path}")
         raw: Dict[str, list] = {}
-        offsets: Dict[str, List[int]] = {}
+        offsets: Dict[str, List[List[int]]] = {}
         for meta in metas:
             shard = str(Path(meta).parent)
             for k, segs in load_bin(shard).items():
                 raw.setdefault(k, []).extend(segs)
             for k, off in load_bin_offsets(shard).items():
-                offsets.setdefault(k, []).extend(off)
+                offsets.setdefault(k, []).append(off)
         self._load_path = path
         self._normalize(raw, offsets=offsets or None)
 
 
 class JsonlSource:
-    """Raw dict records from one ``.jsonl`` file or every ``*.jsonl`` of a directory (bad lines are skipped)."""
+    """Raw dict records from one ``.jsonl`` file or every ``*.jsonl`` below a directory, in path order (bad lines are
+    skipped)."""
 
     def __init__(self, path: str):
         self.path = Path(path)
@@ -202,7 +210,7 @@ class JsonlSource:
 
     def load(self) -> List[dict]:
         if self._records is None:
-            files = [self.path] if self.path.is_file() else sorted(self.path.glob("*.jsonl"))
+            files = [self.path] if self.path.is_file() else sorted(self.path.rglob("*.jsonl"))
             out: List[dict] = []
             for f in files:
                 with open(f, "r", encoding="utf-8") as fh:

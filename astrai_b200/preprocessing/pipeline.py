@@ -52,9 +52,16 @@ class Pipeline:
                     data = json.load(fh)
                     yield from (data if isinstance(data, list) else [data])
                 else:
-                    for line in fh:
-                        if line.strip():
-                            yield json.loads(line)
+                    for n, line in enumerate(fh, 1):
+                        if not line.strip():
+                            continue
+                        try:
+                            rec = json.loads(line)
+                        except json.JSONDecodeError:
+                            logger.warning("%s:%d is not valid JSON, skipped", path, n)
+                            continue
+                        if isinstance(rec, dict):
+                            yield rec
 
     def _batches(self, size: int):
         batch = []
@@ -130,18 +137,38 @@ class Pipeline:
                 if pos:
                     tensors["position_ids"] = [torch.tensor(pos, dtype=torch.int32)]
             idx = shard_idx[domain]
-            self._writer.save(self.output_dir, domain, idx, tensors)
+            # multi-output records (preference pairs ...) are read back one by one: keep their boundaries in the shard
+            record_keys = list(tensors) if getattr(self.config.input, "sources", None) else None
+            self._writer.save(self.output_dir, domain, idx, tensors, record_keys=record_keys)
             shard_idx[domain] = idx + 1
             first = "sequence" if "sequence" in tensors else next(iter(tensors))
-            logger.info("saved %s/shard_%04d (%d tokens)", domain, idx, sum(t.numel() for t in tensors[first]))
+            logger.info("saved %s/shard_%04d (%d records)", domain, idx, len(tensors[first]))
 
     def _to_tensors(self, keys: Dict[str, list]) -> Dict[str, List[torch.Tensor]]:
+        """Columns of id lists as tensors.  Per-record columns give one tensor per record; a record that is itself a list
+        of lists (a group of responses) is flattened for ``bin`` shards, as the reference does, and kept as a list of
+        tensors for ``jsonl`` shards, which can store the boundaries.  The dtype is the configured one, else float32
+        for columns that hold floats (rewards) and int32 for the rest."""
+        keep_nested = self.config.output.storage_format == "jsonl"
         out: Dict[str, List[torch.Tensor]] = {}
         for key, column in keys.items():
-            dtype = DTYPES.get(self.config.output.dtype.get(key, "int32"), torch.int32)
+            name = self.config.output.dtype.get(key)
+            if name is not None:
+                dtype = DTYPES.get(name, torch.int32)
+            else:
+                probe = column
+                while probe and isinstance(probe[0], list):
+                    probe = probe[0]
+                dtype = torch.float32 if (probe and isinstance(probe[0], float)) else torch.int32
             if column and isinstance(column[0], list):
-                out[key] = [torch.tensor(list(chain.from_iterable(rec)) if rec and isinstance(rec[0], list) else rec, dtype=dtype)
-                            for rec in column]
+                recs = []
+                for rec in column:
+                    if rec and isinstance(rec[0], list):
+                        recs.append([torch.tensor(r, dtype=dtype) for r in rec] if keep_nested
+                                    else torch.tensor(list(chain.from_iterable(rec)), dtype=dtype))
+                    else:
+                        recs.append(torch.tensor(rec, dtype=dtype))
+                out[key] = recs
             else:
                 out[key] = [torch.tensor(list(chain.from_iterable(column)), dtype=dtype)]
         return out

@@ -5,7 +5,7 @@ from __future__ import annotations
 import logging
 import os
 import shutil
-from typing import Dict, List
+from typing import Dict, List, Optional
 
 import torch
 
@@ -16,7 +16,9 @@ logger = logging.getLogger(__name__)
 
 
 class StoreWriter:
-    def save(self, output_dir: str, domain: str, shard_idx: int, tensors: Dict[str, List[torch.Tensor]]) -> None:
+    def save(self, output_dir: str, domain: str, shard_idx: int, tensors: Dict[str, List[torch.Tensor]],
+             record_keys: Optional[List[str]] = None) -> None:
+        """``record_keys``: columns whose per-record boundaries must survive (preference pairs, response groups)."""
         raise NotImplementedError
 
 
@@ -26,10 +28,10 @@ class StoreWriterFactory(BaseFactory["StoreWriter"]):
 
 @StoreWriterFactory.register("bin")
 class BinWriter(StoreWriter):
-    def save(self, output_dir, domain, shard_idx, tensors):
+    def save(self, output_dir, domain, shard_idx, tensors, record_keys=None):
         path = os.path.join(output_dir, domain, f"shard_{shard_idx:04d}")
         try:
-            save_bin(path, tensors)
+            save_bin(path, tensors, record_keys=record_keys)
         except Exception:
             shutil.rmtree(path, ignore_errors=True)  # never leave a half-written shard behind
             logger.error("Failed to write shard %s/shard_%04d, cleaned up partial output", domain, shard_idx, exc_info=True)
@@ -40,7 +42,11 @@ class BinWriter(StoreWriter):
 class JsonlWriter(StoreWriter):
     """One JSON object per record with plain lists; readable by ``JsonlStore`` in processor mode."""
 
-    def save(self, output_dir, domain, shard_idx, tensors):
+    @staticmethod
+    def _plain(value):
+        return [t.tolist() for t in value] if isinstance(value, (list, tuple)) else value.tolist()
+
+    def save(self, output_dir, domain, shard_idx, tensors, record_keys=None):
         import json
 
         os.makedirs(os.path.join(output_dir, domain), exist_ok=True)
@@ -48,5 +54,5 @@ class JsonlWriter(StoreWriter):
         n = max(len(v) for v in tensors.values())
         with open(path, "w", encoding="utf-8") as fh:
             for i in range(n):
-                row = {k: (v[i].tolist() if i < len(v) else None) for k, v in tensors.items()}
+                row = {k: (self._plain(v[i]) if i < len(v) else None) for k, v in tensors.items()}
                 fh.write(json.dumps(row) + "\n")

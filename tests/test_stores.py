@@ -197,12 +197,24 @@ def test_record_offsets_slice_single_records_back_out(tmp_path):
         store.fetch_record(4, "chosen")
 
 
-def test_sharded_offsets_disable_record_mode_with_a_warning(tmp_path, caplog):
+def test_records_are_numbered_across_shards(tmp_path):
     from astrai_b200.data import MmapStore
     from astrai_b200.serialization import save_bin
 
-    for i in range(2):
-        save_bin(str(tmp_path / f"shard_{i}"), {"chosen": [torch.tensor([1, 2]), torch.tensor([3])]}, record_keys=["chosen"])
+    save_bin(str(tmp_path / "shard_0"), {"chosen": [torch.tensor([1, 2]), torch.tensor([3])]}, record_keys=["chosen"])
+    save_bin(str(tmp_path / "shard_1"), {"chosen": [torch.tensor([4, 5, 6]), torch.tensor([7]), torch.tensor([8, 9])]}, record_keys=["chosen"])
+    store = MmapStore()
+    store.load(str(tmp_path))
+    assert store.num_records == 5
+    assert [store.fetch_record(i, "chosen").tolist() for i in range(5)] == [[1, 2], [3], [4, 5, 6], [7], [8, 9]]
+
+
+def test_shards_without_offsets_disable_record_mode_with_a_warning(tmp_path, caplog):
+    from astrai_b200.data import MmapStore
+    from astrai_b200.serialization import save_bin
+
+    save_bin(str(tmp_path / "shard_0"), {"chosen": [torch.tensor([1, 2]), torch.tensor([3])]}, record_keys=["chosen"])
+    save_bin(str(tmp_path / "shard_1"), {"chosen": [torch.tensor([4, 5, 6])]})  # an old shard: no offsets
     store = MmapStore()
     with caplog.at_level("WARNING"):
         store.load(str(tmp_path))
