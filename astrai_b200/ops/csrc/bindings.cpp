@@ -675,9 +675,10 @@ void tp_gemm_reducescatter_(const Tensor& X, const Tensor& W, bool w_kmajor, std
 // The pair-tile engine (gemm_comm2.cu): the transfer runs as bulk copies issued by one extra warp of every GEMM CTA.
 void tp2_gemm_allgather_(std::vector<int64_t> xfull_ptrs, const Tensor& W, bool w_kmajor, Tensor& Y, std::vector<int64_t> flag_ptrs,
                          Tensor& chunk_flags, Tensor& chunk_counter, int64_t rank, int64_t unit, int64_t max_units,
-                         int64_t epoch, double timeout_s) {
+                         int64_t epoch, double timeout_s, int64_t copy_slots) {
   CHECK_CUDA_CONTIG(W);
   CHECK_CUDA_CONTIG(Y);
+  TORCH_CHECK(copy_slots >= 0 && copy_slots <= 3, "tp2_gemm_allgather_: copy_slots is 0 (choose from the shape), 1, 2 or 3");
   TORCH_CHECK(W.scalar_type() == at::kBFloat16 && Y.scalar_type() == at::kBFloat16 && W.dim() == 2 && Y.dim() == 2, "tp2_gemm_allgather_: bf16 2-D");
   TORCH_CHECK(chunk_flags.scalar_type() == at::kInt && chunk_flags.numel() >= 8 && chunk_counter.scalar_type() == at::kInt && chunk_counter.numel() >= 8, "tp2_gemm_allgather_: int32[8] flags / counters");
   const int64_t N = w_kmajor ? W.size(0) : W.size(1), K = w_kmajor ? W.size(1) : W.size(0);
@@ -687,6 +688,7 @@ void tp2_gemm_allgather_(std::vector<int64_t> xfull_ptrs, const Tensor& W, bool 
   p.timeout_ns = (unsigned long long)(timeout_s * 1e9);
   fill_ptrs(p.flags, flag_ptrs); fill_ptrs(p.x_full, xfull_ptrs);
   p.chunk_flags = chunk_flags.data_ptr<int>(); p.chunk_counter = chunk_counter.data_ptr<int>();
+  p.copy_slots = (int)copy_slots;
   const c10::cuda::CUDAGuard guard(W.device());
   count();
   const int rc = ab::gemm_allgather2(W.data_ptr(), w_kmajor, Y.data_ptr(), (int)Y.size(0), (int)N, (int)K, Y.stride(0), p,
@@ -696,7 +698,9 @@ void tp2_gemm_allgather_(std::vector<int64_t> xfull_ptrs, const Tensor& W, bool 
 
 void tp2_gemm_reducescatter_(const Tensor& X, const Tensor& W, bool w_kmajor, std::vector<int64_t> part_ptrs, Tensor& gathered,
                              Tensor& out, std::vector<int64_t> flag_ptrs, Tensor& tile_counter, Tensor& pull_counter,
-                             int64_t rank, int64_t unit, int64_t max_units, int64_t epoch, double timeout_s, int64_t phase) {
+                             int64_t rank, int64_t unit, int64_t max_units, int64_t epoch, double timeout_s, int64_t phase,
+                             int64_t copy_slots) {
+  TORCH_CHECK(copy_slots >= 0 && copy_slots <= 3, "tp2_gemm_reducescatter_: copy_slots is 0 (choose from the shape), 1, 2 or 3");
   CHECK_CUDA_CONTIG(X);
   CHECK_CUDA_CONTIG(W);
   CHECK_CUDA_CONTIG(out);
@@ -716,6 +720,7 @@ void tp2_gemm_reducescatter_(const Tensor& X, const Tensor& W, bool w_kmajor, st
   fill_ptrs(p.flags, flag_ptrs); fill_ptrs(p.stage, part_ptrs);
   p.rs_out = out.data_ptr(); p.tile_counter = tile_counter.data_ptr<int>();
   p.gathered = gathered.data_ptr(); p.pull_counter = pull_counter.data_ptr<int>();
+  p.copy_slots = (int)copy_slots;
   const c10::cuda::CUDAGuard guard(X.device());
   count();
   const int rc = ab::gemm_reducescatter2(X.data_ptr(), W.data_ptr(), w_kmajor, (int)X.size(0), (int)N, (int)K, p,
@@ -1110,8 +1115,8 @@ TORCH_LIBRARY(astrai_b200, m) {
   m.def("tp_gemm_allgather_(int[] xfull_ptrs, Tensor W, bool w_kmajor, Tensor(a!) Y, int[] flag_ptrs, Tensor(b!) chunk_flags, Tensor(c!) chunk_counter, int rank, int unit, int max_units, int epoch, float timeout_s, int n_copy_ctas) -> ()", &tp_gemm_allgather_);
   m.def("tp_gemm_reducescatter_(Tensor X, Tensor W, bool w_kmajor, int[] stage_ptrs, Tensor(a!) out, int[] flag_ptrs, Tensor(b!) tile_counter, int rank, int unit, int max_units, int epoch, float timeout_s, bool fuse_reduce) -> ()", &tp_gemm_reducescatter_);
   m.def("tp_reduce_(Tensor stage, Tensor(a!) out, int world) -> ()", &tp_reduce_);
-  m.def("tp2_gemm_allgather_(int[] xfull_ptrs, Tensor W, bool w_kmajor, Tensor(a!) Y, int[] flag_ptrs, Tensor(b!) chunk_flags, Tensor(c!) chunk_counter, int rank, int unit, int max_units, int epoch, float timeout_s) -> ()", &tp2_gemm_allgather_);
-  m.def("tp2_gemm_reducescatter_(Tensor X, Tensor W, bool w_kmajor, int[] part_ptrs, Tensor(a!) gathered, Tensor(b!) out, int[] flag_ptrs, Tensor(c!) tile_counter, Tensor(d!) pull_counter, int rank, int unit, int max_units, int epoch, float timeout_s, int phase) -> ()", &tp2_gemm_reducescatter_);
+  m.def("tp2_gemm_allgather_(int[] xfull_ptrs, Tensor W, bool w_kmajor, Tensor(a!) Y, int[] flag_ptrs, Tensor(b!) chunk_flags, Tensor(c!) chunk_counter, int rank, int unit, int max_units, int epoch, float timeout_s, int copy_slots=0) -> ()", &tp2_gemm_allgather_);
+  m.def("tp2_gemm_reducescatter_(Tensor X, Tensor W, bool w_kmajor, int[] part_ptrs, Tensor(a!) gathered, Tensor(b!) out, int[] flag_ptrs, Tensor(c!) tile_counter, Tensor(d!) pull_counter, int rank, int unit, int max_units, int epoch, float timeout_s, int phase, int copy_slots=0) -> ()", &tp2_gemm_reducescatter_);
   m.def("fp8_quantize(Tensor x, Tensor scale, bool e5m2, bool with_transpose) -> (Tensor, Tensor, Tensor)", &fp8_quantize);
   m.def("fp8_gemm(Tensor a, Tensor b, Tensor scale_a, Tensor scale_b, Tensor? bias) -> Tensor", &fp8_gemm);
   m.def("sample_rows(Tensor logits, Tensor temps, Tensor? top_k, Tensor? top_p, Tensor? penalty, Tensor? hist, Tensor? hist_mask, bool all_greedy, int seed, int offset) -> (Tensor, Tensor, Tensor)", &sample_rows);

@@ -48,11 +48,15 @@ using cpx::flag_slot;
 using cpx::ld_acquire_gpu;
 using cpx::st_release_gpu;
 
-constexpr int BM = 128, BN = 256, BNH = BN / 2, BK = 64, STAGES = 6, UMMA_K = 16;
+constexpr int BM = 128, BN = 256, BNH = BN / 2, BK = 64, UMMA_K = 16;
 constexpr int A_BYTES = BM * BK * 2, B_BYTES = BNH * BK * 2, STAGE_BYTES = A_BYTES + B_BYTES;  // 32 KB
 constexpr int PIECE = 32768;                                                                    // one bulk copy
 constexpr int NUM_THREADS = 224;  // producer, MMA, 4 epilogue warps, comm warp
-constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + PIECE + 1024 + 256;
+// Shared memory is split between the GEMM's operand ring (STAGES x 32 KB) and the comm lane's copy slots (SLOTS x 32 KB),
+// seven 32 KB units in all.  What the comm lane can move is (bytes in flight) / (latency of a peer read), and the
+// bytes in flight are its slots: one slot per CTA sustains about 350 GB/s into a GPU, well below the link.  Shapes
+// whose transfer is long next to their arithmetic therefore trade operand stages for copy slots.
+constexpr int smem_bytes(int stages, int slots) { return (stages + slots) * STAGE_BYTES + 1024 + 256; }
 enum : int { MODE_AG = 1, MODE_RS = 2 };
 enum : int { ERR2_PRODUCER = 56, ERR2_MMA = 57, ERR2_EPILOGUE = 58, ERR2_COMM = 59, ERR2_REDUCE = 60 };
 constexpr int KIND_AG = 2, KIND_RS = 3;  // flag planes (astrai_b200/parallel/symm.py)
@@ -78,26 +82,37 @@ __device__ __forceinline__ Tile2 tile_of(int t, int tiles_m_blk, int tiles_n, in
 }
 
 // Move `bytes` (a multiple of 16) from `src` (possibly a peer's memory) to local `dst`: this CTA's share of the 32 KB
-// pieces (piece index cta, cta + n_ctas, ...), one at a time through the shared-memory slot.
+// pieces (piece index cta, cta + n_ctas, ...) through SLOTS shared-memory slots, so that up to SLOTS peer reads are in
+// flight while an earlier piece is written out.  `phases` holds one parity bit per slot's mbarrier and lives across calls.
+template <int SLOTS>
 __device__ __forceinline__ bool copy_share(const uint8_t* src, uint8_t* dst, long long bytes, int cta, int n_ctas,
-                                           uint32_t slot, uint32_t bar, uint32_t& phase, volatile int* abort_flag) {
+                                           uint32_t slot0, uint32_t bar0, uint32_t& phases, volatile int* abort_flag) {
   const long long n_pieces = (bytes + PIECE - 1) / PIECE;
-  for (long long pc = cta; pc < n_pieces; pc += n_ctas) {
-    const long long off = pc * PIECE;
-    const uint32_t len = (uint32_t)min((long long)PIECE, bytes - off);
-    mbar_expect_tx(bar, len);
-    bulk_load(slot, src + off, len, bar);
-    if (!mbar_wait(bar, phase, abort_flag)) return false;
-    phase ^= 1u;
-    bulk_store(dst + off, slot, len);
+  const long long mine = cta < n_pieces ? (n_pieces - cta + n_ctas - 1) / n_ctas : 0;
+  auto off_of = [&](long long k) { return (cta + k * n_ctas) * (long long)PIECE; };
+  auto len_of = [&](long long k) { return (uint32_t)min((long long)PIECE, bytes - off_of(k)); };
+  auto issue = [&](long long k) {
+    const int s = (int)(k % SLOTS);
+    mbar_expect_tx(bar0 + 8u * s, len_of(k));
+    bulk_load(slot0 + (uint32_t)s * PIECE, src + off_of(k), len_of(k), bar0 + 8u * s);
+  };
+  for (long long k = 0; k < mine && k < SLOTS; ++k) issue(k);
+  for (long long k = 0; k < mine; ++k) {
+    const int s = (int)(k % SLOTS);
+    if (!mbar_wait(bar0 + 8u * s, (phases >> s) & 1u, abort_flag)) return false;
+    phases ^= 1u << s;
+    bulk_store(dst + off_of(k), slot0 + (uint32_t)s * PIECE, len_of(k));
     bulk_commit();
-    bulk_wait_read();  // the slot may be overwritten by the next load
+    if (k + SLOTS < mine) {
+      bulk_wait_read();  // the store has read the slot: the next peer read may land in it
+      issue(k + SLOTS);
+    }
   }
   bulk_wait_all();  // every store of this share has landed
   return true;
 }
 
-template <int MODE, bool B_K>
+template <int MODE, bool B_K, int STAGES, int SLOTS>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(NUM_THREADS, 1)
 gemm2_comm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                   __nv_bfloat16* __restrict__ D, int M, int N, int K, long long ldd, const TpGemmParams p,
@@ -105,15 +120,15 @@ gemm2_comm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
   extern __shared__ uint8_t smem_raw[];
   const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   uint8_t* aligned = smem_raw + (base - smem_u32(smem_raw));
-  const uint32_t slot = base + STAGES * STAGE_BYTES;  // the comm lane's 32 KB piece
-  uint64_t* bars = reinterpret_cast<uint64_t*>(aligned + STAGES * STAGE_BYTES + PIECE);
+  const uint32_t slot = base + STAGES * STAGE_BYTES;  // the comm lane's 32 KB pieces
+  uint64_t* bars = reinterpret_cast<uint64_t*>(aligned + (STAGES + SLOTS) * STAGE_BYTES);
   const uint32_t bar0 = smem_u32(bars);
   auto full_bar = [&](int s) { return bar0 + 8u * s; };
   auto empty_bar = [&](int s) { return bar0 + 8u * (STAGES + s); };
   auto tfull_bar = [&](int b) { return bar0 + 8u * (2 * STAGES + b); };
   auto tempty_bar = [&](int b) { return bar0 + 8u * (2 * STAGES + 2 + b); };
-  const uint32_t copy_bar = bar0 + 8u * (2 * STAGES + 4);
-  uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 5);
+  const uint32_t copy_bar = bar0 + 8u * (2 * STAGES + 4);  // SLOTS barriers, one per copy slot
+  uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 4 + SLOTS);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_holder + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -137,7 +152,7 @@ gemm2_comm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
       mbar_init(tfull_bar(b), 1);
       mbar_init(tempty_bar(b), 8);  // 4 epilogue warps x 2 CTAs arrive on the leader's copy
     }
-    mbar_init(copy_bar, 1);
+    for (int c = 0; c < SLOTS; ++c) mbar_init(copy_bar + 8u * c, 1);
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -376,7 +391,7 @@ gemm2_comm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
           }
           const uint8_t* from = reinterpret_cast<const uint8_t*>(p.x_full[src]) + (long long)src * blk_bytes;
           uint8_t* to = reinterpret_cast<uint8_t*>(p.x_full[p.rank]) + (long long)src * blk_bytes;
-          ok = copy_share(from, to, blk_bytes, cta, n_ctas, slot, copy_bar, cphase, abort_flag);
+          ok = copy_share<SLOTS>(from, to, blk_bytes, cta, n_ctas, slot, copy_bar, cphase, abort_flag);
           if (!ok) break;
           fence_async_global();
           __threadfence();
@@ -396,7 +411,7 @@ gemm2_comm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
           }
           const uint8_t* from = reinterpret_cast<const uint8_t*>(p.stage[src]) + (long long)p.rank * blk_bytes;
           uint8_t* to = reinterpret_cast<uint8_t*>(p.gathered) + (long long)src * blk_bytes;
-          ok = copy_share(from, to, blk_bytes, cta, n_ctas, slot, copy_bar, cphase, abort_flag);
+          ok = copy_share<SLOTS>(from, to, blk_bytes, cta, n_ctas, slot, copy_bar, cphase, abort_flag);
         }
         if (ok) {
           fence_async_global();
@@ -420,21 +435,22 @@ gemm2_comm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
   }
 }
 
-template <int MODE, bool B_K>
-int launch(const CUtensorMap& ma, const CUtensorMap& mb, void* D, int M, int N, int K, long long ldd, const TpGemmParams& p,
-           int* status, cudaStream_t st) {
-  auto kern = gemm2_comm_kernel<MODE, B_K>;
+template <int MODE, bool B_K, int STAGES, int SLOTS>
+int launch_cfg(const CUtensorMap& ma, const CUtensorMap& mb, void* D, int M, int N, int K, long long ldd, const TpGemmParams& p,
+               int* status, cudaStream_t st) {
+  auto kern = gemm2_comm_kernel<MODE, B_K, STAGES, SLOTS>;
+  constexpr int SMEM = smem_bytes(STAGES, SLOTS);
   static bool configured = false;
   static int max_pairs = 0;
   if (!configured) {
-    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES) != cudaSuccess) return -4;
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM) != cudaSuccess) return -4;
     int dev = 0, sms = 0;
     cudaGetDevice(&dev);
     cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(sms, 1, 1);
     cfg.blockDim = dim3(NUM_THREADS, 1, 1);
-    cfg.dynamicSmemBytes = SMEM_BYTES;
+    cfg.dynamicSmemBytes = SMEM;
     int clusters = 0;
     if (cudaOccupancyMaxActiveClusters(&clusters, kern, &cfg) != cudaSuccess || clusters <= 0) {
       cudaGetLastError();
@@ -448,8 +464,29 @@ int launch(const CUtensorMap& ma, const CUtensorMap& mb, void* D, int M, int N, 
   const int tiles = (M / (2 * BM)) * ((N + BN - 1) / BN);
   int pairs = tiles < max_pairs ? tiles : max_pairs;
   if (pairs < 1) pairs = 1;
-  kern<<<2 * pairs, NUM_THREADS, SMEM_BYTES, st>>>(ma, mb, (__nv_bfloat16*)D, M, N, K, ldd, p, status);
+  kern<<<2 * pairs, NUM_THREADS, SMEM, st>>>(ma, mb, (__nv_bfloat16*)D, M, N, K, ldd, p, status);
   return cudaGetLastError() == cudaSuccess ? 0 : -5;
+}
+
+// Copy slots for this shape: the time the transfer needs at the rate one slot per CTA sustains (about 350 GB/s) against
+// the time of the arithmetic at the sustained tensor rate.  A transfer that would finish well inside the product keeps
+// all six operand stages; otherwise stages are traded for slots (each slot adds about as much again, up to the link).
+int copy_slots(int M, int N, int K, int world, bool rs) {
+  if (world <= 1) return 1;
+  const double flops = 2.0 * M * (double)N * K;
+  const double bytes = (double)(world - 1) / world * M * (double)(rs ? N : K) * 2.0;
+  const double t_math = flops / 1.38e15, t_copy1 = bytes / 350e9;
+  if (t_copy1 <= 0.8 * t_math) return 1;
+  return t_copy1 <= 1.7 * t_math ? 2 : 3;
+}
+
+template <int MODE, bool B_K>
+int launch(const CUtensorMap& ma, const CUtensorMap& mb, void* D, int M, int N, int K, long long ldd, const TpGemmParams& p,
+           int* status, cudaStream_t st) {
+  int slots = p.copy_slots > 0 ? p.copy_slots : copy_slots(M, N, K, p.world, MODE == MODE_RS);
+  if (slots >= 3) return launch_cfg<MODE, B_K, 4, 3>(ma, mb, D, M, N, K, ldd, p, status, st);
+  if (slots == 2) return launch_cfg<MODE, B_K, 5, 2>(ma, mb, D, M, N, K, ldd, p, status, st);
+  return launch_cfg<MODE, B_K, 6, 1>(ma, mb, D, M, N, K, ldd, p, status, st);
 }
 
 int check(const TpGemmParams& p, int M, int N, int K) {

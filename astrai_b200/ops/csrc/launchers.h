@@ -156,6 +156,9 @@ struct TpGemmParams {
   // run several ranks on one GPU without kernels waiting for one another).
   void* gathered;
   int* pull_counter;
+  // pair-tile engine: shared-memory copy slots of the comm lane (1..3, each taken from the GEMM's operand stages);
+  // 0 lets the launcher choose from the shape (transfer time against arithmetic time).
+  int copy_slots = 0;
 };
 // The same two operations on the CTA-pair tile engine with in-kernel bulk-copy transfer (gemm_comm2.cu); they need
 // M % (world * 256) == 0 (tp2_shape_ok) and are the ones the tensor-parallel layers use when the shape allows.

@@ -10,8 +10,9 @@ receive over NVLink at the measured peer-copy rate:
 
     t_roof = max(FLOPs / 1378.7 TFLOP/s, bytes / 770 GB/s)        fraction = t_roof / t_measured
 
-* ``tp_ag`` / ``tp_rs``: all-gather -> GEMM and GEMM -> reduce-scatter of the 8B model's gate|up and down projections
-  under tensor parallelism with sequence-sharded activations (65 536 tokens per step);
+* ``tp_ag`` / ``tp_rs``: all-gather -> GEMM and GEMM -> reduce-scatter of the 8B model's MLP (gate|up, down) and
+  attention (q|k|v, o_proj) projections under tensor parallelism with sequence-sharded activations (65 536 tokens per
+  step); the attention projections have a quarter of the MLP's FLOPs for the same bytes, so they are NVLink-bound;
 * ``cp``: causal attention forward + backward of one 65 536-token sequence sharded zig-zag over the ranks (32 query / 8 kv
   heads of 128);
 * ``ep``: one MoE layer forward + backward (8 192 tokens per rank, 64 experts, top-6, hidden 2048, expert FFN 1408);
@@ -62,7 +63,7 @@ def _row(name, what, flops, link_bytes, ms):
     return out
 
 
-def bench_tp(world, rank, dev, iters, which):
+def bench_tp(world, rank, dev, iters, which, slots=(0,)):
     from astrai_b200.parallel import tensor_parallel as tpar
 
     m, d, ffn = 65536, 4096, 14336
@@ -70,20 +71,29 @@ def bench_tp(world, rank, dev, iters, which):
     ctx = tpar.init_tensor_parallel(4 << 30, timeout_s=60.0)
     g = torch.Generator(device="cuda").manual_seed(rank)
     rows = []
+    qkv = (32 + 8 + 8) * 128  # 32 query and 8 + 8 key / value heads of 128
     if which == "tp_ag":
-        n = 2 * ffn // world
         x = torch.randn(ms_rows, d, device=dev, dtype=torch.bfloat16, generator=g)
-        w = torch.randn(n, d, device=dev, dtype=torch.bfloat16, generator=g) * 0.02
-        ms = {c: _time(lambda c=c: tpar.allgather_gemm(x, w, True, ctx=ctx, comm=c), iters) for c in ("nccl", "p2p")}
-        rows.append(_row("TP all-gather -> GEMM (gate|up forward)", f"[{m}x{d}] x [{n}x{d}]^T, tp{world}",
-                         2.0 * m * n * d, (world - 1) / world * m * d * 2, ms))
+        for name, n in (("gate|up forward", 2 * ffn // world), ("q|k|v forward", qkv // world)):
+            w = torch.randn(n, d, device=dev, dtype=torch.bfloat16, generator=g) * 0.02
+            ms = {"nccl": _time(lambda: tpar.allgather_gemm(x, w, True, ctx=ctx, comm="nccl"), iters)}
+            for sl in slots:  # 0: the launcher's own choice; 1..3: forced number of copy slots
+                ctx.copy_slots = sl
+                ms["p2p" if sl == 0 else f"p2p_slots{sl}"] = _time(lambda: tpar.allgather_gemm(x, w, True, ctx=ctx, comm="p2p"), iters)
+            ctx.copy_slots = 0
+            rows.append(_row(f"TP all-gather -> GEMM ({name})", f"[{m}x{d}] x [{n}x{d}]^T, tp{world}",
+                             2.0 * m * n * d, (world - 1) / world * m * d * 2, ms))
     else:
-        k = ffn // world
-        x = torch.randn(m, k, device=dev, dtype=torch.bfloat16, generator=g)
-        w = torch.randn(d, k, device=dev, dtype=torch.bfloat16, generator=g) * 0.02
-        ms = {c: _time(lambda c=c: tpar.gemm_reducescatter(x, w, True, ctx=ctx, comm=c), iters) for c in ("nccl", "p2p")}
-        rows.append(_row("TP GEMM -> reduce-scatter (down forward)", f"[{m}x{k}] x [{d}x{k}]^T, tp{world}",
-                         2.0 * m * d * k, (world - 1) / world * m * d * 2, ms))
+        for name, k in (("down forward", ffn // world), ("o_proj forward", d // world)):
+            x = torch.randn(m, k, device=dev, dtype=torch.bfloat16, generator=g)
+            w = torch.randn(d, k, device=dev, dtype=torch.bfloat16, generator=g) * 0.02
+            ms = {"nccl": _time(lambda: tpar.gemm_reducescatter(x, w, True, ctx=ctx, comm="nccl"), iters)}
+            for sl in slots:
+                ctx.copy_slots = sl
+                ms["p2p" if sl == 0 else f"p2p_slots{sl}"] = _time(lambda: tpar.gemm_reducescatter(x, w, True, ctx=ctx, comm="p2p"), iters)
+            ctx.copy_slots = 0
+            rows.append(_row(f"TP GEMM -> reduce-scatter ({name})", f"[{m}x{k}] x [{d}x{k}]^T, tp{world}",
+                             2.0 * m * d * k, (world - 1) / world * m * d * 2, ms))
     tpar.set_context(None)
     return rows
 
@@ -186,6 +196,7 @@ def main(argv=None):
     ap.add_argument("--ops", default="tp_ag,tp_rs,cp,ep,fsdp")
     ap.add_argument("--iters", type=int, default=10)
     ap.add_argument("--out", default=None)
+    ap.add_argument("--tp-slots", default="0", help="tp_ag / tp_rs: comma list of copy-slot counts to time (0 = the launcher's choice)")
     args = ap.parse_args(argv)
     from astrai_b200.ops import native
     from astrai_b200.parallel.setup import setup_parallel
@@ -199,7 +210,7 @@ def main(argv=None):
         for op in args.ops.split(","):
             try:
                 if op in ("tp_ag", "tp_rs"):
-                    rows += bench_tp(world, rank, dev, args.iters, op)
+                    rows += bench_tp(world, rank, dev, args.iters, op, tuple(int(v) for v in args.tp_slots.split(",")))
                 elif op == "cp":
                     rows += bench_cp(world, rank, dev, args.iters)
                 elif op == "ep":

@@ -44,6 +44,7 @@ class TPContext:
         a row block is a whole number of 256-row pair tiles, else (and with ``engine="single"``) the one-CTA-per-tile
         kernels with copy CTAs and epilogue peer stores (``gemm_comm.cu``)."""
         self.engine = engine
+        self.copy_slots = 0  # pair engine: shared-memory copy slots of the comm lane; 0 = chosen from the shape per call
         self.arena, self.rank, self.world = arena, rank, world
         self.timeout_s, self.n_copy_ctas, self.fuse_reduce = float(timeout_s), int(n_copy_ctas), bool(fuse_reduce)
         self.group = group
@@ -64,6 +65,13 @@ class TPContext:
         key = (m, k, parity)
         if key not in self._gather:
             self._gather[key] = self.arena.alloc(m * k, torch.bfloat16, zero=False)
+        return self._gather[key]
+
+    def own_rows_buffer(self, ms: int, k: int, parity: int) -> symm.SymmBuffer:
+        """This rank's ``[ms, k]`` rows of an all-gather, where the peers' copy warps read them."""
+        key = ("own", ms, k, parity)
+        if key not in self._gather:
+            self._gather[key] = self.arena.alloc(ms * k, torch.bfloat16, zero=False)
         return self._gather[key]
 
     def stage_buffer(self, rows: int, n: int, parity: int) -> symm.SymmBuffer:
@@ -138,19 +146,29 @@ def allgather_gemm(x_local: Tensor, w: Tensor, w_kmajor: bool = True, ctx: Optio
     n = w.shape[0] if w_kmajor else w.shape[1]
     if comm == "p2p" and ctx is not None and _fusable(m, world, x_local, w) and n % 32 == 0 and k % 8 == 0:
         epoch = ctx.next_epoch("ag")
+        y = torch.empty((m, n), dtype=torch.bfloat16, device=x_local.device)
+        if ctx.pair_engine(m):
+            # Only this rank's own rows live in symmetric memory (where the peers read them); the gathered matrix is
+            # a plain tensor of this call, so autograd can keep it for the weight gradient without a copy.  The kernel
+            # reads rank r's rows at `ptr[r] + r * block` and writes them at `ptr[rank] + r * block`: the peers'
+            # pointers are therefore biased back by their block offset and this rank's pointer is the new tensor.
+            own = ctx.own_rows_buffer(ms, k, epoch & 1)
+            own.tensor.view(ms, k).copy_(x_local)
+            x_full = torch.empty((m, k), dtype=torch.bfloat16, device=x_local.device)
+            x_full[ctx.rank * ms:(ctx.rank + 1) * ms].copy_(x_local)
+            blk = ms * k * 2
+            ptrs = [x_full.data_ptr() if r == ctx.rank else own.peer_ptrs[r] - r * blk for r in range(world)]
+            torch.ops.astrai_b200.tp2_gemm_allgather_(ptrs, w.contiguous(), w_kmajor, y, ctx.flags.peer_ptrs,
+                                                      ctx.chunk_flags, ctx.chunk_counter, ctx.rank, 0, ctx.MAX_UNITS, epoch,
+                                                      ctx.timeout_s, ctx.copy_slots)
+            return y, x_full
         buf = ctx.gather_buffer(m, k, epoch & 1)
         x_full = buf.tensor.view(m, k)
         x_full[ctx.rank * ms:(ctx.rank + 1) * ms].copy_(x_local)
-        y = torch.empty((m, n), dtype=torch.bfloat16, device=x_local.device)
-        if ctx.pair_engine(m):
-            torch.ops.astrai_b200.tp2_gemm_allgather_(buf.peer_ptrs, w.contiguous(), w_kmajor, y, ctx.flags.peer_ptrs,
-                                                      ctx.chunk_flags, ctx.chunk_counter, ctx.rank, 0, ctx.MAX_UNITS, epoch,
-                                                      ctx.timeout_s)
-        else:
-            torch.ops.astrai_b200.tp_gemm_allgather_(buf.peer_ptrs, w.contiguous(), w_kmajor, y, ctx.flags.peer_ptrs,
-                                                     ctx.chunk_flags, ctx.chunk_counter, ctx.rank, 0, ctx.MAX_UNITS, epoch,
-                                                     ctx.timeout_s, ctx.n_copy_ctas)
-        return y, x_full
+        torch.ops.astrai_b200.tp_gemm_allgather_(buf.peer_ptrs, w.contiguous(), w_kmajor, y, ctx.flags.peer_ptrs,
+                                                 ctx.chunk_flags, ctx.chunk_counter, ctx.rank, 0, ctx.MAX_UNITS, epoch,
+                                                 ctx.timeout_s, ctx.n_copy_ctas)
+        return y, x_full.clone()  # the symmetric buffer is reused two calls later: hand out a copy
     if world > 1:
         x_full = torch.empty((m, k), dtype=x_local.dtype, device=x_local.device)
         dist.all_gather_into_tensor(x_full, x_local.contiguous(), group=group)
@@ -178,7 +196,8 @@ def gemm_reducescatter(x: Tensor, w: Tensor, w_kmajor: bool = True, ctx: Optiona
             # the staging area doubles as this rank's whole partial product [M, N]; the peers' blocks are pulled from it
             torch.ops.astrai_b200.tp2_gemm_reducescatter_(x.contiguous(), w.contiguous(), w_kmajor, st.peer_ptrs,
                                                           ctx.gathered_buffer(ms, n), out, ctx.flags.peer_ptrs, ctx.tile_counter,
-                                                          ctx.pull_counter, ctx.rank, 1, ctx.MAX_UNITS, epoch, ctx.timeout_s, 1)
+                                                          ctx.pull_counter, ctx.rank, 1, ctx.MAX_UNITS, epoch, ctx.timeout_s, 1,
+                                                          ctx.copy_slots)
             return out
         torch.ops.astrai_b200.tp_gemm_reducescatter_(x.contiguous(), w.contiguous(), w_kmajor, st.peer_ptrs, out,
                                                      ctx.flags.peer_ptrs, ctx.tile_counter, ctx.rank, 1, ctx.MAX_UNITS, epoch,
@@ -201,7 +220,7 @@ class _ColumnParallelFn(Function):
     @staticmethod
     def forward(ctx, x_local, w, comm):
         y, x_full = allgather_gemm(x_local, w, True, comm=comm)
-        ctx.save_for_backward(x_full.clone() if comm == "p2p" and _CTX is not None else x_full, w)
+        ctx.save_for_backward(x_full, w)
         ctx.comm = comm
         return y
 

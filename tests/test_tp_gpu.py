@@ -85,9 +85,11 @@ def test_gemm_reducescatter_matches_torch(world, ms, kp, n, w_kmajor):
 
 @pytest.mark.parametrize("world,ms,k,n,w_kmajor", [(2, 256, 256, 512, True), (4, 512, 320, 288, True), (2, 256, 192, 256, False),
                                                    (8, 256, 128, 96, True)])
-def test_pair_engine_allgather_gemm_matches_torch(world, ms, k, n, w_kmajor):
+@pytest.mark.parametrize("slots", [1, 2, 3])
+def test_pair_engine_allgather_gemm_matches_torch(world, ms, k, n, w_kmajor, slots):
     """The CTA-pair kernel whose extra warp pulls the peers' row blocks with bulk copies (ranks emulated on one GPU,
-    announcements preset so that no kernel waits for another)."""
+    announcements preset so that no kernel waits for another).  ``slots``: copy slots of the comm lane, each taken from
+    the GEMM's operand stages (6 + 1, 5 + 2, 4 + 3)."""
     ops = torch.ops.astrai_b200
     m = world * ms
     arena = _arena(world, m * k * 2 + (1 << 20))
@@ -107,7 +109,7 @@ def test_pair_engine_allgather_gemm_matches_torch(world, ms, k, n, w_kmajor):
         y = torch.empty(m, n, device="cuda", dtype=torch.bfloat16)
         cf, cc = torch.zeros(8, dtype=torch.int32, device="cuda"), torch.zeros(8, dtype=torch.int32, device="cuda")
         for epoch in (1, 1):  # twice: counters reset themselves, flags stay at the epoch
-            ops.tp2_gemm_allgather_(bufs[r].peer_ptrs, w, w_kmajor, y, flags[r].peer_ptrs, cf, cc, r, 0, MAX_UNITS, epoch, 0.5)
+            ops.tp2_gemm_allgather_(bufs[r].peer_ptrs, w, w_kmajor, y, flags[r].peer_ptrs, cf, cc, r, 0, MAX_UNITS, epoch, 0.5, slots)
         ref = x_full @ ws[r].float().t()
         assert torch.equal(bufs[r].tensor.view(m, k).float(), x_full), r
         assert (y.float() - ref).abs().max().item() < 0.05 * ref.abs().max().item() + 1e-2, r
@@ -119,7 +121,8 @@ def test_pair_engine_allgather_gemm_matches_torch(world, ms, k, n, w_kmajor):
 
 @pytest.mark.parametrize("world,ms,kp,n,w_kmajor", [(2, 256, 256, 512, True), (4, 256, 192, 320, True), (2, 512, 128, 256, False),
                                                     (8, 256, 64, 128, True)])
-def test_pair_engine_gemm_reducescatter_matches_torch(world, ms, kp, n, w_kmajor):
+@pytest.mark.parametrize("slots", [1, 2, 3])
+def test_pair_engine_gemm_reducescatter_matches_torch(world, ms, kp, n, w_kmajor, slots):
     """Reduce-scatter by pulling: phase 0 of every rank (partial product + announcements), then phase 2 of every rank
     (pull the peers' blocks with bulk copies, sum in fp32), so that no kernel waits for another one on this one GPU."""
     ops = torch.ops.astrai_b200
@@ -141,7 +144,7 @@ def test_pair_engine_gemm_reducescatter_matches_torch(world, ms, kp, n, w_kmajor
         for r in range(world):
             w = ws[r] if w_kmajor else ws[r].t().contiguous()
             ops.tp2_gemm_reducescatter_(xs[r], w, w_kmajor, parts[r].peer_ptrs, gath[r], outs[r], flags[r].peer_ptrs, tcs[r], pcs[r],
-                                        r, 1, MAX_UNITS, 3, 0.5, phase)
+                                        r, 1, MAX_UNITS, 3, 0.5, phase, slots)
     full = sum(x.float() @ w.float().t() for x, w in zip(xs, ws))
     for r in range(world):
         ref = full[r * ms:(r + 1) * ms]
