@@ -62,6 +62,9 @@ class DeepSeekMoE(nn.Module):
                  moe_intermediate_size: Optional[int] = None, shared_expert_intermediate_size: Optional[int] = None,
                  norm_topk_prob: bool = True):
         super().__init__()
+        if not n_routed_experts or not n_activated_experts:
+            raise ValueError("a mixture-of-experts layer needs n_routed_experts and n_activated_experts "
+                             f"(got {n_routed_experts!r} and {n_activated_experts!r})")
         self.dim = dim
         self.n_routed_experts = n_routed_experts
         self.n_shared_experts = n_shared_experts or 0
