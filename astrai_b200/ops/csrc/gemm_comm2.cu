@@ -112,6 +112,47 @@ __device__ __forceinline__ bool copy_share(const uint8_t* src, uint8_t* dst, lon
   return true;
 }
 
+// out[v] = sum over the W sources of their vector v (fp32 accumulation, bf16 in and out); source `rank` is `own`, source
+// s != rank is slot s of `gath`.  VPT adjacent vectors of every source per thread and trip; W <= WMAX.
+template <int VPT, int WMAX>
+__device__ __forceinline__ void reduce_slots(const __nv_bfloat16* own, const __nv_bfloat16* gath, void* out, int W, int rank,
+                                             long long slot_elems, long long n_vec, long long tid, long long nthr) {
+  for (long long v = VPT * tid; v < n_vec; v += VPT * nthr) {
+    uint4 raw[WMAX][VPT];
+#pragma unroll
+    for (int s = 0; s < WMAX; ++s) {
+      if (s < W) {
+        const __nv_bfloat16* src = (s == rank) ? own : gath + (long long)s * slot_elems;
+#pragma unroll
+        for (int u = 0; u < VPT; ++u) raw[s][u] = __ldcg(reinterpret_cast<const uint4*>(src) + v + u);
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < VPT; ++u) {
+      float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+      for (int s = 0; s < WMAX; ++s) {
+        if (s < W) {
+          const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw[s][u]);
+#pragma unroll
+          for (int q = 0; q < 4; ++q) {
+            const float2 f = __bfloat1622float2(h[q]);
+            acc[2 * q] += f.x, acc[2 * q + 1] += f.y;
+          }
+        }
+      }
+      uint4 pk;
+      uint32_t* pw = reinterpret_cast<uint32_t*>(&pk);
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        const __nv_bfloat162 h = __floats2bfloat162_rn(acc[2 * q], acc[2 * q + 1]);
+        pw[q] = *reinterpret_cast<const uint32_t*>(&h);
+      }
+      reinterpret_cast<uint4*>(out)[v + u] = pk;
+    }
+  }
+}
+
 template <int MODE, bool B_K, int STAGES, int SLOTS>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(NUM_THREADS, 1)
 gemm2_comm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
@@ -295,8 +336,10 @@ gemm2_comm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
       __syncwarp();
       if (lane == 0) mbar_arrive_cluster(buf ? tempty_leader1 : tempty_leader0);  // the accumulator is free at once
       if (MODE == MODE_RS) {
-        // count warp arrivals per row block; the last one tells the block's owner that this rank's partial is complete
-        __threadfence_system();
+        // count warp arrivals per row block; the last one tells the block's owner that this rank's partial is complete.
+        // Every warp orders its stores before its arrival at GPU scope; the last arriver's system-scope fence then
+        // carries all of them to the peer together with the flag (fences are cumulative).
+        __threadfence();
         __syncwarp();
         if (lane == 0) {
           const int done = atomicAdd(&p.tile_counter[tl.block], 1);
@@ -333,43 +376,12 @@ gemm2_comm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
         const __nv_bfloat16* own = reinterpret_cast<const __nv_bfloat16*>(p.stage[p.rank]) + (long long)p.rank * slot_elems;
         const __nv_bfloat16* gath = reinterpret_cast<const __nv_bfloat16*>(p.gathered);
         const long long tid = (long long)cta * 128 + (warp - 2) * 32 + lane, nthr = (long long)n_ctas * 128;
-        // Two adjacent 16-byte vectors of every source per trip, all loads issued before the first add: with up to
-        // 16 independent loads per thread the sum runs at memory speed instead of at one load latency per source.
-        // (N is a multiple of 32, so the vector count is even.)
-        for (long long v = 2 * tid; v < n_vec; v += 2 * nthr) {
-          uint4 raw[MAX_RANKS][2];
-#pragma unroll
-          for (int s = 0; s < MAX_RANKS; ++s) {
-            if (s < W) {
-              const __nv_bfloat16* src = (s == p.rank) ? own : gath + (long long)s * slot_elems;
-              raw[s][0] = __ldcg(reinterpret_cast<const uint4*>(src) + v);
-              raw[s][1] = __ldcg(reinterpret_cast<const uint4*>(src) + v + 1);
-            }
-          }
-#pragma unroll
-          for (int u = 0; u < 2; ++u) {
-            float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-#pragma unroll
-            for (int s = 0; s < MAX_RANKS; ++s) {
-              if (s < W) {
-                const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw[s][u]);
-#pragma unroll
-                for (int q = 0; q < 4; ++q) {
-                  const float2 f = __bfloat1622float2(h[q]);
-                  acc[2 * q] += f.x, acc[2 * q + 1] += f.y;
-                }
-              }
-            }
-            uint4 pk;
-            uint32_t* pw = reinterpret_cast<uint32_t*>(&pk);
-#pragma unroll
-            for (int q = 0; q < 4; ++q) {
-              const __nv_bfloat162 h = __floats2bfloat162_rn(acc[2 * q], acc[2 * q + 1]);
-              pw[q] = *reinterpret_cast<const uint32_t*>(&h);
-            }
-            reinterpret_cast<uint4*>(p.rs_out)[v + u] = pk;
-          }
-        }
+        // About 16 independent 16-byte loads per thread and trip, all issued before the first add, whatever the number
+        // of ranks: with few sources a thread takes more vectors of each (the sum then runs at memory speed instead of
+        // at one load latency per trip).  N is a multiple of 32 and Ms of 256, so the vector count divides by 8.
+        if (W <= 2) reduce_slots<8, 2>(own, gath, p.rs_out, W, p.rank, slot_elems, n_vec, tid, nthr);
+        else if (W <= 4) reduce_slots<4, 4>(own, gath, p.rs_out, W, p.rank, slot_elems, n_vec, tid, nthr);
+        else reduce_slots<2, MAX_RANKS>(own, gath, p.rs_out, W, p.rank, slot_elems, n_vec, tid, nthr);
       }
     }
   } else {
