@@ -73,10 +73,16 @@ def _(r, kw):
         return True
     except ValueError:
         return False
+@register("detectable_format:general_punctuation")
+def _(r, kw): return not any(mark and mark in r for mark in kw.get("punctuation_blacklist", []))
+@register("detectable_format:number_highlighted_words")
+def _(r, kw): return len(re.findall(r"\*[^\s\*](?:[^\*]*[^\s\*])?\*", r)) >= int(kw.get("num_highlights", 1))
 @register("punctuation:no_comma")
 def _(r, kw): return "," not in r
 @register("startend:end_checker")
 def _(r, kw): return r.strip().lower().endswith(str(kw["end_phrase"]).strip().lower())
+@register("startend:start_checker")
+def _(r, kw): return re.search(r"^\s*" + re.escape(str(kw["starter"])), r, re.M) is not None
 @register("startend:quotation")
 def _(r, kw): return len(r.strip()) > 1 and r.strip()[0] == '"' and r.strip()[-1] == '"'
 @register("change_case:english_capital")
@@ -99,6 +105,11 @@ def _(r, kw):
         return False
     words = re.findall(r"\b\w+\b", ps[n - 1])
     return bool(words) and words[0].lower() == str(kw["first_word"]).lower()
+@register("length_constraints:nth_word_checker")
+def _(r, kw):
+    words = re.findall(r"\b\w+\b", r)
+    n = int(kw.get("nth_word", 1))
+    return 1 <= n <= len(words) and words[n - 1].lower() == str(kw.get("target_word", "")).lower()
 @register("combination:repeat_prompt")
 def _(r, kw): return r.strip().lower().startswith(str(kw["prompt_to_repeat"]).strip().lower())
 @register("combination:two_responses")

@@ -81,3 +81,49 @@ def test_model_scoring_on_tiny_model(tmp_path):
     assert it2["choices"][ans] == "4" and "2+2?" in build_prompt(item["question"], item["choices"], "elementary_math")
     res = evaluate_subject(model, tok, [item, item], "elementary_math", "cpu", batch_size=2)
     assert res["n"] == 2 and 0.0 <= res["accuracy"] <= 1.0
+
+
+IFEVAL_CASES = [
+    ("keywords:existence", {"keywords": ["alpha", "Beta"]}, "Alpha and beta are here", "only alpha"),
+    ("keywords:frequency", {"keyword": "cat", "relation": "at least", "frequency": 2}, "cat, Cat!", "one cat"),
+    ("keywords:forbidden_words", {"forbidden_words": ["bad"]}, "a badge is fine", "this is bad"),
+    ("keywords:letter_frequency", {"letter": "z", "let_relation": "less than", "let_frequency": 2}, "zebra", "pizza"),
+    ("detectable_content:number_placeholders", {"num_placeholders": 2}, "[name] lives at [address]", "[name] only"),
+    ("detectable_content:postscript", {"postscript_marker": "P.S."}, "body\nP.S. one more thing", "body without it"),
+    ("detectable_format:number_bullet_lists", {"num_bullets": 2}, "- a\n- b", "- a\n- b\n- c"),
+    ("detectable_format:number_highlighted_sections", {"num_highlights": 2}, "*one* and *two*", "*one* only"),
+    ("detectable_format:number_highlighted_words", {"num_highlights": 2}, "a *b* c *d e* f", "* not closed and *x*"),
+    ("detectable_format:general_punctuation", {"punctuation_blacklist": ["!", ";"]}, "calm, quiet.", "loud!"),
+    ("detectable_format:multiple_sections", {"section_spliter": "Part", "num_sections": 2}, "Part 1\nx\nPart 2\ny", "Part 1 only"),
+    ("detectable_format:title", {}, "<<A title>>\ntext", "no title"),
+    ("detectable_format:json_format", {}, '```json\n{"a": [1, 2]}\n```', "{not json}"),
+    ("punctuation:no_comma", {}, "no commas here", "one, comma"),
+    ("startend:end_checker", {"end_phrase": "The end."}, "story. the end.", "the end. not"),
+    ("startend:start_checker", {"starter": "Dear team"}, "  Dear team, hello", "Hello, Dear team"),
+    ("startend:quotation", {}, '"quoted"', 'not "quoted'),
+    ("change_case:english_capital", {}, "ALL CAPS 123", "Not all caps"),
+    ("change_case:english_lowercase", {}, "all lower 123", "Not lower"),
+    ("change_case:capital_word_frequency", {"capital_relation": "at least", "capital_frequency": 2}, "NASA and ESA", "NASA only"),
+    ("length_constraints:number_words", {"relation": "at least", "num_words": 3}, "one two three", "one two"),
+    ("length_constraints:number_sentences", {"relation": "at most", "num_sentences": 2}, "One. Two.", "One. Two. Three."),
+    ("length_constraints:number_paragraphs", {"num_paragraphs": 2}, "first\n\nsecond", "only one"),
+    ("length_constraints:nth_paragraph_first_word", {"num_paragraphs": 2, "nth_paragraph": 2, "first_word": "then"}, "a b\n\nThen c", "a b\n\nc then"),
+    ("length_constraints:nth_word_checker", {"nth_word": 3, "target_word": "fox"}, "the quick FOX jumps", "the quick brown fox"),
+    ("combination:repeat_prompt", {"prompt_to_repeat": "Say hi"}, "say hi\nhi!", "hi! say hi"),
+    ("combination:two_responses", {}, "one ****** two", "same ****** same"),
+]
+
+
+@pytest.mark.parametrize("instruction,kwargs,good,bad", IFEVAL_CASES, ids=[c[0] for c in IFEVAL_CASES])
+def test_every_ifeval_instruction_accepts_and_rejects(instruction, kwargs, good, bad):
+    from astrai_b200.eval.ifeval import verify_response
+
+    assert verify_response(good, instruction, kwargs) is True
+    assert verify_response(bad, instruction, kwargs) is False
+
+
+def test_ifeval_covers_the_27_instruction_kinds():
+    from astrai_b200.eval import ifeval
+
+    registry = next(v for v in vars(ifeval).values() if isinstance(v, dict) and "punctuation:no_comma" in v)
+    assert len(registry) == 27 and {c[0] for c in IFEVAL_CASES} == set(registry)
