@@ -85,7 +85,8 @@ def build_train_config(o: Dict[str, Any]):
     from astrai_b200.parallel.mesh import data_parallel_size
 
     # ranks of one tensor- / context-parallel block read the same samples: they count once
-    readers = data_parallel_size(o["parallel_mode"], o["nprocs"], o["tp_size"] or 1, o.get("cp_size") or 1, o.get("ep_size") or 1)
+    readers = data_parallel_size(o["parallel_mode"], o["nprocs"], o["tp_size"] or 1, o.get("cp_size") or 1, o.get("ep_size") or 1,
+                                 o.get("pp_size") or 1)
     total_steps = compute_total_steps(len(dataset), readers, o["batch_per_device"], o["grad_accum_steps"], o["n_epoch"])
     opt_kw, sched_kw = optimizer_kwargs(o), scheduler_kwargs(o, total_steps)
 
@@ -99,6 +100,9 @@ def build_train_config(o: Dict[str, Any]):
             executor_kwargs.update(comm="nccl", reshard=True, impl="flat")
     elif o["parallel_mode"] in ("tp", "ep"):
         executor_kwargs["comm"] = o.get("mp_comm") or "p2p"
+    elif o["parallel_mode"] == "pp":
+        if o.get("pp_chunks"):
+            executor_kwargs["chunks"] = o["pp_chunks"]
     elif o["parallel_mode"] == "cp":
         executor_kwargs["attn_comm"] = o.get("mp_comm") or "p2p"
         executor_kwargs["comm"] = o["fsdp_comm"]
@@ -114,7 +118,7 @@ def build_train_config(o: Dict[str, Any]):
         ckpt_interval=o["ckpt_interval"], metrics=list(o["metrics"]), random_seed=o["random_seed"], num_workers=o["num_workers"],
         pin_memory=o["pin_memory"], nprocs=o["nprocs"], backend=o["backend"], master_addr=o["master_addr"],
         master_port=str(o["master_port"]), parallel_mode=o["parallel_mode"], tp_size=o["tp_size"] or 1,
-        cp_size=o.get("cp_size") or 1, ep_size=o.get("ep_size") or 1,
+        cp_size=o.get("cp_size") or 1, ep_size=o.get("ep_size") or 1, pp_size=o.get("pp_size") or 1,
         start_method=o["start_method"], device_type=o["device_type"], val_split=o["val_split"], val_step=o["val_step"],
         neftune_alpha=o["neftune_alpha"], rollout_interval=o["rollout_interval"], rollout_temperature=o["rollout_temperature"],
         rollout_top_k=o["rollout_top_k"], rollout_top_p=o["rollout_top_p"], rollout_max_tokens=o["rollout_max_tokens"],
@@ -126,7 +130,7 @@ def plan(o: Dict[str, Any]) -> Dict[str, Any]:
     """What ``--dry-run`` prints: the merged options that matter, without touching data or devices."""
     keys = ("train_type", "data_root_path", "param_path", "resume", "n_epoch", "batch_per_device", "grad_accum_steps",
             "max_lr", "warmup_ratio", "max_grad_norm", "optimizer", "weight_decay", "schedule_type", "window_size", "stride",
-            "ckpt_dir", "ckpt_interval", "nprocs", "parallel_mode", "fsdp_comm", "fsdp_reshard", "tp_size", "cp_size", "ep_size", "mp_comm", "backend", "fp8", "metrics",
+            "ckpt_dir", "ckpt_interval", "nprocs", "parallel_mode", "fsdp_comm", "fsdp_reshard", "tp_size", "cp_size", "ep_size", "pp_size", "pp_chunks", "mp_comm", "backend", "fp8", "metrics",
             "label_smoothing", "gradient_checkpointing", "random_seed")
     out = {k: (list(o[k]) if isinstance(o[k], tuple) else o[k]) for k in keys}
     out["tokens_per_optimizer_step"] = o["batch_per_device"] * o["grad_accum_steps"] * o["nprocs"] * (o["window_size"] or 0)
@@ -186,8 +190,9 @@ def plan(o: Dict[str, Any]) -> Dict[str, Any]:
 @click.option("--dry-run", "dry_run", is_flag=True, default=False, help="Validate and print the plan; do not train.")
 # distributed
 @click.option("--nprocs", type=int, default=1)
-@click.option("--parallel_mode", type=click.Choice(["none", "ddp", "fsdp", "tp", "cp", "ep"]), default="fsdp",
-              help="tp / cp / ep: tensor-, context- or expert-parallel blocks of --tp_size / --cp_size / --ep_size ranks.")
+@click.option("--parallel_mode", type=click.Choice(["none", "ddp", "fsdp", "tp", "cp", "ep", "pp"]), default="fsdp",
+              help="tp / cp / ep / pp: tensor-, context-, expert- or pipeline-parallel blocks of --tp_size / --cp_size / "
+                   "--ep_size / --pp_size ranks.")
 @click.option("--fsdp_comm", type=click.Choice(["nccl", "p2p", "nvls"]), default="p2p", help="FSDP transport: NCCL or fused peer-memory kernels.")
 @click.option("--fsdp_reshard", is_flag=True, default=False,
               help="FSDP full-shard placement: parameters and gradients are whole only while their block computes "
@@ -200,6 +205,8 @@ def plan(o: Dict[str, Any]) -> Dict[str, Any]:
 @click.option("--tp_size", type=int, default=None, help="Tensor-parallel size inside one NVSwitch domain (<= 8); default: all ranks.")
 @click.option("--cp_size", type=int, default=None, help="Context-parallel size (ranks that share one sequence); default: all ranks.")
 @click.option("--ep_size", type=int, default=None, help="Expert-parallel size (ranks that share one set of experts); default: all ranks.")
+@click.option("--pp_size", type=int, default=None, help="Pipeline stages (ranks that hold one model replica layer range by layer range); default: all ranks.")
+@click.option("--pp_chunks", type=int, default=None, help="pp: pieces a per-device batch is cut into for the 1F1B schedule (default: the number of stages, at most the batch).")
 @click.option("--mp_comm", type=click.Choice(["p2p", "nccl"]), default="p2p",
               help="tp / cp / ep transport: fused peer-memory kernels or library collectives around the same math.")
 @click.option("--fp8/--no-fp8", default=False, help="Run linear layers on fp8 tensor cores (delayed per-tensor scaling).")

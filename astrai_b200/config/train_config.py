@@ -15,7 +15,7 @@ from pydantic.dataclasses import dataclass
 from astrai_b200.config.base import BaseConfig, one_of
 
 TRAIN_TYPES = ("seq", "sft", "dpo", "grpo", "online_grpo", "online_dpo")
-PARALLEL_MODES = ("none", "ddp", "fsdp", "tp", "cp", "ep")
+PARALLEL_MODES = ("none", "ddp", "fsdp", "tp", "cp", "ep", "pp")
 BACKENDS = ("nccl", "gloo")
 START_METHODS = ("spawn", "fork", "forkserver")
 COMPILE_MODES = ("default", "reduce-overhead", "max-autotune")
@@ -65,6 +65,7 @@ class TrainConfig(BaseConfig):
     tp_size: int = 1
     cp_size: int = 1
     ep_size: int = 1
+    pp_size: int = 1
     start_method: str = "spawn"
     device_type: str = "cuda"
     val_dataset: Optional[Any] = None
@@ -107,7 +108,7 @@ class TrainConfig(BaseConfig):
 
     @field_validator(
         "n_epoch", "batch_per_device", "grad_accum_steps", "ckpt_interval", "val_step",
-        "rollout_interval", "rollout_max_tokens", "tp_size", "cp_size", "ep_size",
+        "rollout_interval", "rollout_max_tokens", "tp_size", "cp_size", "ep_size", "pp_size",
     )
     def _c_positive(cls, v):
         if v <= 0:

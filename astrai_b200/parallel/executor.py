@@ -117,16 +117,20 @@ class AccumOptimizer:
         return self.optimizer.param_groups
 
     def state_dict(self, gather: bool = True):
-        """``gather=False`` asks a sharded optimizer for its local shard only (no communication)."""
+        """``gather=False`` asks a sharded optimizer for its local shard only (no communication).  Executors whose ranks
+        hold different parameters (pipeline stages) put the ranks' states together (``pack_optimizer_state``)."""
         if not gather:
             try:
                 return self.optimizer.state_dict(gather=False)
             except TypeError:
                 pass
-        return self.optimizer.state_dict()
+        state = self.optimizer.state_dict()
+        pack = getattr(self.executor, "pack_optimizer_state", None)
+        return pack(state) if pack is not None else state
 
     def load_state_dict(self, d):
-        self.optimizer.load_state_dict(d)
+        unpack = getattr(self.executor, "unpack_optimizer_state", None)
+        self.optimizer.load_state_dict(unpack(d) if unpack is not None else d)
 
 
 class AccumScheduler:

@@ -69,18 +69,20 @@ def build_mesh(mp_size: Optional[int] = None) -> ParallelMesh:
     return mesh
 
 
-def model_parallel_size(parallel_mode: str, world: int, tp_size: int = 1, cp_size: int = 1, ep_size: int = 1) -> int:
+def model_parallel_size(parallel_mode: str, world: int, tp_size: int = 1, cp_size: int = 1, ep_size: int = 1,
+                        pp_size: int = 1) -> int:
     """Ranks per model-parallel block for a training mode.  A size of 1 (the configuration default) next to a
     model-parallel mode means "the whole job"."""
-    size = {"tp": tp_size, "cp": cp_size, "ep": ep_size}.get(parallel_mode)
+    size = {"tp": tp_size, "cp": cp_size, "ep": ep_size, "pp": pp_size}.get(parallel_mode)
     if size is None:
         return 1
     return world if size <= 1 else min(int(size), world)
 
 
-def data_parallel_size(parallel_mode: str, world: int, tp_size: int = 1, cp_size: int = 1, ep_size: int = 1) -> int:
-    """How many ranks draw different samples: the tensor- or context-parallel ranks of one block share their batch;
-    every other mode (expert parallelism included) gives each rank a batch of its own."""
-    if parallel_mode in ("tp", "cp"):
-        return max(world // model_parallel_size(parallel_mode, world, tp_size, cp_size, ep_size), 1)
+def data_parallel_size(parallel_mode: str, world: int, tp_size: int = 1, cp_size: int = 1, ep_size: int = 1,
+                       pp_size: int = 1) -> int:
+    """How many ranks draw different samples: the tensor-, context- or pipeline-parallel ranks of one block share their
+    batch; every other mode (expert parallelism included) gives each rank a batch of its own."""
+    if parallel_mode in ("tp", "cp", "pp"):
+        return max(world // model_parallel_size(parallel_mode, world, tp_size, cp_size, ep_size, pp_size), 1)
     return world

@@ -340,3 +340,135 @@ class ContextParallelExecutor(FSDPExecutor):
                 out[key] = zigzag_split(t, cp, r, dim=1).contiguous()
         out["position_ids"] = zigzag_positions(s, cp, r, device=batch["input_ids"].device).unsqueeze(0).expand(b, -1)
         return out
+
+
+@ExecutorFactory.register("pp")
+class PipelineParallelExecutor(ModelParallelExecutor):
+    """``parallel_mode="pp"``: the decoder is cut into ``pp_size`` contiguous layer ranges (:mod:`astrai_b200.parallel.pipeline`);
+    rank ``r`` of a block holds stage ``r`` only, the blocks are data-parallel replicas.
+
+    Every rank of a block reads the same batch (the first stage uses the token ids, the last one the targets).  One
+    trainer micro-batch is one non-interleaved 1F1B window: the per-device batch is cut into ``chunks`` pieces whose
+    forward and backward passes interleave across the stages (:meth:`pipeline_step`, which the trainer calls instead of
+    strategy + backward).  The objective is next-token cross-entropy (``seq``); the other strategies are refused.
+    Gradients accumulate in the flat runtime's fp32 buffers; every parameter lives on exactly one stage, so gradients are
+    summed over the data-parallel group only and the gradient norm is summed over the stages.  Checkpoints are put back
+    together with the reference's keys: every stage sends its tensors to the first one.
+
+    The transport is point-to-point messages between neighbours (NCCL on GPUs, Gloo on the CPU): there is no fused
+    kernel on this path, and on CUDA the last stage computes logits and loss separately (no fused projection + loss)."""
+
+    mode = "pp"
+
+    def __init__(self, grad_accum_steps: int = 1, size: int = 0, chunks: int = 0, comm: str = "nccl", overlap: bool = True,
+                 comm_timeout_s: float = 120.0, label_smoothing: float = 0.0, aux_loss_coef: float = 0.0):
+        super().__init__(grad_accum_steps, size, "nccl", overlap, comm_timeout_s)
+        self.chunks, self.label_smoothing, self.aux_loss_coef = int(chunks), float(label_smoothing), float(aux_loss_coef)
+        self._pipe = None
+        self._keys: Dict[str, str] = {}
+
+    # -- set-up -------------------------------------------------------------------------------------------------------------
+    def _convert(self, model):
+        from astrai_b200 import ops
+        from astrai_b200.parallel.pipeline import PipelineParallel
+
+        m = self.mesh
+        if m.mp_size <= 1:
+            raise ValueError("pipeline parallelism needs at least two stages (pp_size >= 2 and as many ranks)")
+        if len(model.layers) < m.mp_size:
+            raise ValueError(f"{len(model.layers)} decoder layers cannot be cut into {m.mp_size} stages")
+        group = m.mp_group if m.mp_group is not None else dist.group.WORLD
+
+        def loss_fn(logits, targets):
+            return ops.cross_entropy(logits, targets, label_smoothing=self.label_smoothing)
+
+        self._pipe = PipelineParallel(model, group=group, loss_fn=loss_fn, aux_loss_coef=self.aux_loss_coef)
+        stage = self._pipe.stage
+        full = {id(v): k for k, v in model.state_dict(keep_vars=True).items()}
+        self._keys = {k: full[id(v)] for k, v in stage.state_dict(keep_vars=True).items() if id(v) in full}
+        mine = {id(p) for p in stage.parameters()}
+        for p in model.parameters():  # what other stages own leaves this rank's memory
+            if id(p) not in mine:
+                p.data = torch.empty(0, dtype=p.dtype, device=p.device)
+        stage.config = model.config
+        return stage
+
+    def _is_sharded(self, name, p):
+        return True  # every parameter exists on one stage only
+
+    def _averaging_scale(self) -> float:
+        return 1.0 / self.mesh.dp_size if (self.use_distributed and self.mesh is not None) else 1.0
+
+    def _unit_backward_done(self, unit):
+        pass  # several pieces are in flight per window: units are reduced once, after the window (pipeline_step)
+
+    @property
+    def data_parallel_size(self) -> int:
+        return self.mesh.dp_size if self.mesh is not None else 1
+
+    @property
+    def data_parallel_rank(self) -> int:
+        return self.mesh.dp_rank if self.mesh is not None else 0
+
+    # -- one micro-batch of the trainer = one 1F1B window ------------------------------------------------------------------
+    def pipeline_step(self, model, batch: dict, loss_scale: float) -> dict:
+        unknown = set(batch) - {"input_ids", "target_ids", "position_ids"}
+        if unknown or "target_ids" not in batch:
+            raise NotImplementedError("pipeline parallelism trains the next-token objective (strategy 'seq'): a batch of "
+                                      f"input_ids / target_ids; got keys {sorted(batch)}")
+        stage = self._pipe.stage
+        dev = next(stage.parameters()).device
+        ids, targets = batch["input_ids"].to(dev), batch["target_ids"].to(dev)
+        n = ids.shape[0]
+        chunks = self.chunks if self.chunks > 0 else min(self.mesh.mp_size, n)
+        if n % chunks:
+            raise ValueError(f"a per-device batch of {n} cannot be cut into {chunks} pipeline pieces")
+        for u in self.engine.units:
+            u.ready = u.reduced = False
+        loss = self._pipe.train_step(ids if stage.first else None, targets if stage.last else None, chunks,
+                                     micro_shape=(n // chunks, ids.shape[1]), loss_scale=loss_scale)
+        if self.gradient_state.sync_gradients:
+            for u in reversed(self.engine.units):
+                u.ready = True
+                self._reduce_unit(u)
+            self._finish_reductions()
+        # the window's mean loss is known on the last stage: hand it to the other stages for logging
+        value = loss.detach().float().reshape(1) if loss is not None else torch.zeros(1, device=dev)
+        last = self.mesh.mp_ranks()[-1]
+        dist.broadcast(value, src=last, group=self.mesh.mp_group)
+        from astrai_b200.trainer.strategy import DeferredMetrics
+
+        return {"loss": value[0], "metrics": DeferredMetrics(loss=value[0])}
+
+    # -- state ------------------------------------------------------------------------------------------------------------------
+    def _full_state_dict(self, model):
+        """Every stage of the first block sends its tensors (under the whole model's keys) to the block's first rank."""
+        m = self.mesh
+        if m.dp_rank != 0:
+            return None
+        mine = {self._keys[k]: v.detach().cpu() for k, v in model.state_dict().items() if k in self._keys}
+        parts = [None] * m.mp_size if m.mp_rank == 0 else None
+        dist.gather_object(mine, parts, dst=m.mp_ranks()[0], group=m.mp_group)
+        if parts is None:
+            return None
+        merged: Dict[str, torch.Tensor] = {}
+        for part in parts:
+            merged.update(part)
+        return merged
+
+    def pack_optimizer_state(self, state):
+        """The optimizer state of every stage of the first block, gathered on its first rank (``None`` elsewhere)."""
+        m = self.mesh
+        if m.dp_rank != 0:
+            return None
+        parts = [None] * m.mp_size if m.mp_rank == 0 else None
+        dist.gather_object(state, parts, dst=m.mp_ranks()[0], group=m.mp_group)
+        return {"pipeline_stages": parts} if parts is not None else None
+
+    def unpack_optimizer_state(self, state):
+        if isinstance(state, dict) and "pipeline_stages" in state:
+            stages = state["pipeline_stages"]
+            if len(stages) != self.mesh.mp_size:
+                raise RuntimeError(f"the checkpoint holds optimizer state of {len(stages)} pipeline stages, this run has {self.mesh.mp_size}")
+            return stages[self.mesh.mp_rank]
+        return state

@@ -121,8 +121,9 @@ class PipelineParallel:
                 work.wait()
 
     def train_step(self, input_ids: Optional[Tensor], targets: Optional[Tensor], n_micro: int,
-                   micro_shape: Optional[Tuple[int, int]] = None, dtype: Optional[torch.dtype] = None) -> Optional[Tensor]:
-        """One accumulation window.  ``input_ids`` ``[B, S]`` is needed on the first stage, ``targets`` ``[B, S]`` on the
+                   micro_shape: Optional[Tuple[int, int]] = None, dtype: Optional[torch.dtype] = None,
+                   loss_scale: float = 1.0) -> Optional[Tensor]:
+        """One accumulation window (gradients are those of ``loss_scale`` times the mean loss over the window).  ``input_ids`` ``[B, S]`` is needed on the first stage, ``targets`` ``[B, S]`` on the
         last; ``B`` must be a multiple of ``n_micro``.  Stages in the middle pass ``micro_shape = (B / n_micro, S)``.
         Returns the mean loss on the last stage, ``None`` elsewhere.  Gradients are left in ``.grad``."""
         st = self.stage
@@ -157,9 +158,9 @@ class PipelineParallel:
                 losses.append(loss.detach())
                 if aux is not None and self.aux_loss_coef:
                     loss = loss + self.aux_loss_coef * aux
-                y = loss / n_micro
+                y = loss * (loss_scale / n_micro)
             elif aux is not None and self.aux_loss_coef:  # the stage's own share of the auxiliary loss
-                (self.aux_loss_coef * aux / n_micro).backward(retain_graph=True)
+                (self.aux_loss_coef * aux * (loss_scale / n_micro)).backward(retain_graph=True)
             live.append((x, y))
             return y
 

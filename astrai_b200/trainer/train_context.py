@@ -128,13 +128,13 @@ class TrainContextBuilder:
         from astrai_b200.parallel.mesh import data_parallel_size
 
         c = self.config
-        return data_parallel_size(c.parallel_mode, get_world_size(), c.tp_size, c.cp_size, c.ep_size)
+        return data_parallel_size(c.parallel_mode, get_world_size(), c.tp_size, c.cp_size, c.ep_size, c.pp_size)
 
     def _executor(self) -> BaseExecutor:
         c = self.config
         mode = c.parallel_mode
         kw = dict(c.executor_kwargs)
-        size = {"tp": c.tp_size, "cp": c.cp_size, "ep": c.ep_size}.get(mode)
+        size = {"tp": c.tp_size, "cp": c.cp_size, "ep": c.ep_size, "pp": c.pp_size}.get(mode)
         if size is not None:
             import astrai_b200.parallel.model_parallel  # noqa: F401 - registers the tp / cp / ep executors
 

@@ -63,7 +63,12 @@ class Trainer:
         scale = 1.0 / ex.grad_accum_steps
         flat = getattr(ex, "engine", None) is not None
         self._fire("on_batch_begin", context)
-        if flat:
+        if hasattr(ex, "pipeline_step"):
+            # pipeline parallelism: forward and backward of the batch's pieces interleave across the stages inside the call
+            with trace.range("pipeline"):
+                out = ex.pipeline_step(context.model, batch, scale)
+            loss = out["loss"]
+        elif flat:
             # promise the loss gradient so the fused head bakes 1/accum into dX and accumulates dW in place
             with trace.range("forward"), ops.assume_loss_grad(scale):
                 out = context.strategy(batch)

@@ -1,4 +1,4 @@
-"""The model-parallel training modes (``parallel_mode = tp | cp | ep``) through the real Trainer on gloo ranks (CPU).
+"""The model-parallel training modes (``parallel_mode = tp | cp | ep | pp``) through the real Trainer on gloo ranks (CPU).
 
 Each mode trains a tiny decoder for three optimizer steps on the same global batches as a single process and must
 reproduce its losses, gradient norms and - after gathering the shards - its final weights under the reference's
@@ -57,6 +57,30 @@ def test_dense_model_parallel_mode_matches_single_process(tmp_path, dense_ref, m
     _same(_run(tmp_path, mode, nproc, "--mode", mode, "--size", str(size)), dense_ref)
 
 
+@pytest.mark.parametrize("nproc,size,extra", [(2, 0, []), (4, 2, []), (2, 0, ["--chunks", "4"])])
+def test_pipeline_parallel_mode_matches_single_process(tmp_path, dense_ref, nproc, size, extra):
+    """Two stages (one decoder layer each) on two ranks, two such pipelines on four; 1F1B over 2 or 4 pieces of the batch."""
+    run = _run(tmp_path, "pp", nproc, "--mode", "pp", "--size", str(size), *extra)
+    _same(run, dense_ref)
+    assert run["optimizer_stages"] == 2  # the checkpoint carries the optimizer state of both stages
+
+
+def test_pipeline_executor_hands_each_stage_its_own_optimizer_state_and_refuses_other_objectives():
+    from astrai_b200.parallel import ExecutorFactory
+    from astrai_b200.parallel.mesh import ParallelMesh
+
+    ex = ExecutorFactory.create("pp", grad_accum_steps=1, size=2)
+    ex.mesh = ParallelMesh(world=4, rank=3, mp_size=2)  # second stage of the second pipeline
+    assert ex.data_parallel_size == 2 and ex.data_parallel_rank == 1 and ex._averaging_scale() in (1.0, 0.5)
+    saved = {"pipeline_stages": [{"stage": 0}, {"stage": 1}]}
+    assert ex.unpack_optimizer_state(saved) == {"stage": 1}
+    assert ex.unpack_optimizer_state({"plain": True}) == {"plain": True}  # a checkpoint of another mode passes through
+    with pytest.raises(RuntimeError, match="3 pipeline stages"):
+        ex.unpack_optimizer_state({"pipeline_stages": [1, 2, 3]})
+    with pytest.raises(NotImplementedError, match="next-token"):
+        ex.pipeline_step(None, {"chosen": torch.zeros(1, 2), "rejected": torch.zeros(1, 2)}, 1.0)
+
+
 @pytest.mark.parametrize("nproc,size", [(2, 0), (4, 2)])
 def test_expert_parallel_mode_matches_single_process(tmp_path, moe_ref, nproc, size):
     _same(_run(tmp_path, "ep", nproc, "--mode", "ep", "--moe", "--size", str(size)), moe_ref)
@@ -65,7 +89,8 @@ def test_expert_parallel_mode_matches_single_process(tmp_path, moe_ref, nproc, s
 def test_mesh_sizes_and_registration():
     from astrai_b200.parallel import ExecutorFactory, data_parallel_size, model_parallel_size
 
-    assert {"tp", "cp", "ep"} <= set(ExecutorFactory.list_registered())
+    assert {"tp", "cp", "ep", "pp"} <= set(ExecutorFactory.list_registered())
+    assert model_parallel_size("pp", 8, pp_size=4) == 4 and data_parallel_size("pp", 8, pp_size=4) == 2
     assert model_parallel_size("tp", 8, tp_size=1) == 8 and model_parallel_size("tp", 8, tp_size=4) == 4
     assert data_parallel_size("tp", 8, tp_size=4) == 2 and data_parallel_size("cp", 8, cp_size=8) == 1
     assert data_parallel_size("ep", 8, ep_size=8) == 8 and data_parallel_size("fsdp", 8) == 8

@@ -155,6 +155,21 @@ def test_model_parallel_trainer_modes_fused_and_collective_arms(tmp_path, mode, 
             assert abs(run["sums"][k] - v) / max(v, 1e-6) < 2e-2, (comm, k)
 
 
+def test_pipeline_parallel_trainer_mode_matches_single_gpu(tmp_path):
+    """parallel_mode pp through the real Trainer on 2 GPUs in bf16 (two stages, 1F1B over two pieces, NCCL point-to-point
+    messages, gradients in the flat runtime's fp32 buffers): losses, norms and gathered weights of the single-GPU run."""
+    _need_gpus(2)
+    ref = _mp_run(tmp_path, "ref", 1, 0, "--mode", "none")
+    run = _mp_run(tmp_path, "pp", 2, 29760, "--mode", "pp")
+    assert run["shapes"] == ref["shapes"] and run["optimizer_stages"] == 2
+    for a, b in zip(run["losses"], ref["losses"]):
+        assert abs(a - b) < 3e-2, (run["losses"], ref["losses"])
+    for a, b in zip(run["norms"], ref["norms"]):
+        assert abs(a - b) / max(abs(b), 1e-6) < 5e-2, (run["norms"], ref["norms"])
+    for k, v in ref["sums"].items():
+        assert abs(run["sums"][k] - v) / max(v, 1e-6) < 2e-2, k
+
+
 def test_full_shard_fsdp_matches_replicated_fsdp(tmp_path):
     """``reshard=True`` on 2 GPUs (bf16, NCCL gathers / reduce-scatters on the side stream, storages released and
     re-created around every unit): same losses, norms and weights as the replicated placement, nothing whole at rest."""

@@ -1,5 +1,5 @@
 """Worker of the model-parallel trainer tests: runs the real ``Trainer`` for a few optimizer steps in one of the modes
-``tp | cp | ep`` (``--mode``, ``--size``) and writes the per-step losses, the gradient norms and the final (gathered,
+``tp | cp | ep | pp`` (``--mode``, ``--size``) and writes the per-step losses, the gradient norms and the final (gathered,
 unsharded) state dict's checksums to ``--out``.  With ``--mode none`` and one process it produces the single-process
 reference over the same global batches.  Runs on gloo ranks (CPU) or NCCL ranks (GPU); launched by torchrun."""
 
@@ -56,6 +56,8 @@ def main():
     ap.add_argument("--steps", type=int, default=3)
     ap.add_argument("--dtype", default="float32")
     ap.add_argument("--lr", type=float, default=1e-2)
+    ap.add_argument("--chunks", type=int, default=0)
+    ap.add_argument("--layers", type=int, default=2)
     args = ap.parse_args()
 
     from astrai_b200.config import AutoRegressiveLMConfig, TrainConfig
@@ -68,7 +70,7 @@ def main():
     dtype = getattr(torch, args.dtype)
     extra = dict(ffn_type="moe", n_routed_experts=4, n_shared_experts=1, n_activated_experts=2,
                  moe_intermediate_size=args.hidden * 2) if args.moe else {}
-    cfg = AutoRegressiveLMConfig(vocab_size=256, hidden_size=args.hidden, num_hidden_layers=2, rms_norm_eps=1e-6,
+    cfg = AutoRegressiveLMConfig(vocab_size=256, hidden_size=args.hidden, num_hidden_layers=args.layers, rms_norm_eps=1e-6,
                                  intermediate_size=args.hidden * 2, tie_word_embeddings=False,
                                  max_position_embeddings=args.seq, rope_theta=10000.0,
                                  num_attention_heads=max(args.hidden // (128 if cuda else 8), 2),
@@ -82,11 +84,13 @@ def main():
     # the same global batch in every run: ranks of one tp / cp block share their samples, so the per-device batch of
     # those modes is the single-process one; ep ranks (and plain data parallelism) split it
     from astrai_b200.parallel.mesh import data_parallel_size
-    dw = data_parallel_size(args.mode, world, args.size, args.size, args.size)
+    dw = data_parallel_size(args.mode, world, args.size, args.size, args.size, args.size)
     global_batch = args.bpd * 2
     bpd = global_batch // dw
     n = global_batch * accum * args.steps
     exkw = {"comm": args.comm} if args.mode in ("tp", "cp", "ep") else {}
+    if args.mode == "pp" and args.chunks:
+        exkw["chunks"] = args.chunks
     if args.mode == "cp":  # the gradient / parameter transport and the attention transport are chosen together here
         exkw["attn_comm"] = args.comm
         exkw["max_tokens_per_rank"] = bpd * args.seq // max(world // max(dw, 1), 1) * 2
@@ -96,7 +100,7 @@ def main():
                      optimizer_fn=lambda m: FusedAdamW(m.parameters(), lr=args.lr, weight_decay=0.0),
                      batch_per_device=bpd, grad_accum_steps=accum, ckpt_dir=args.ckpt, ckpt_interval=10**6,
                      device_type="cuda" if cuda else "cpu", backend="nccl" if cuda else "gloo", nprocs=world,
-                     parallel_mode=args.mode, tp_size=args.size or 1, cp_size=args.size or 1, ep_size=args.size or 1,
+                     parallel_mode=args.mode, tp_size=args.size or 1, cp_size=args.size or 1, ep_size=args.size or 1, pp_size=args.size or 1,
                      executor_kwargs=exkw, max_grad_norm=1.0, moe_aux_loss_coef=0.0,
                      master_addr=os.environ.get("MASTER_ADDR", "127.0.0.1"), master_port=os.environ.get("MASTER_PORT", "29500"))
     rec = Record()
@@ -117,11 +121,14 @@ def main():
         from pathlib import Path
 
         last = sorted(Path(args.ckpt).glob("epoch_*"), key=lambda p: p.stat().st_mtime)[-1]
-        sd = Checkpoint.load(last).state_dict
+        ck = Checkpoint.load(last)
+        sd = ck.state_dict
+        opt_state = ck.extra.get("optimizer")
+        stages = len(opt_state["pipeline_stages"]) if isinstance(opt_state, dict) and "pipeline_stages" in opt_state else 0
         sums = {k: float(v.float().abs().sum()) for k, v in sd.items()}
         shapes = {k: list(v.shape) for k, v in sd.items()}
         with open(args.out, "w") as fh:
-            json.dump({"losses": rec.losses, "norms": rec.norms, "sums": sums, "shapes": shapes}, fh)
+            json.dump({"losses": rec.losses, "norms": rec.norms, "sums": sums, "shapes": shapes, "optimizer_stages": stages}, fh)
 
 
 if __name__ == "__main__":
