@@ -130,7 +130,7 @@ def plan(o: Dict[str, Any]) -> Dict[str, Any]:
     """What ``--dry-run`` prints: the merged options that matter, without touching data or devices."""
     keys = ("train_type", "data_root_path", "param_path", "resume", "n_epoch", "batch_per_device", "grad_accum_steps",
             "max_lr", "warmup_ratio", "max_grad_norm", "optimizer", "weight_decay", "schedule_type", "window_size", "stride",
-            "ckpt_dir", "ckpt_interval", "nprocs", "parallel_mode", "fsdp_comm", "fsdp_reshard", "tp_size", "cp_size", "ep_size", "pp_size", "pp_chunks", "mp_comm", "backend", "fp8", "metrics",
+            "ckpt_dir", "ckpt_interval", "nprocs", "parallel_mode", "fsdp_comm", "fsdp_reshard", "tp_size", "cp_size", "ep_size", "pp_size", "pp_chunks", "mp_comm", "backend", "fp8", "fp8_recipe", "metrics",
             "label_smoothing", "gradient_checkpointing", "random_seed")
     out = {k: (list(o[k]) if isinstance(o[k], tuple) else o[k]) for k in keys}
     out["tokens_per_optimizer_step"] = o["batch_per_device"] * o["grad_accum_steps"] * o["nprocs"] * (o["window_size"] or 0)
@@ -209,7 +209,9 @@ def plan(o: Dict[str, Any]) -> Dict[str, Any]:
 @click.option("--pp_chunks", type=int, default=None, help="pp: pieces a per-device batch is cut into for the 1F1B schedule (default: the number of stages, at most the batch).")
 @click.option("--mp_comm", type=click.Choice(["p2p", "nccl"]), default="p2p",
               help="tp / cp / ep transport: fused peer-memory kernels or library collectives around the same math.")
-@click.option("--fp8/--no-fp8", default=False, help="Run linear layers on fp8 tensor cores (delayed per-tensor scaling).")
+@click.option("--fp8/--no-fp8", default=False, help="Run linear layers on fp8 tensor cores.")
+@click.option("--fp8_recipe", type=click.Choice(["delayed", "dynamic", "block"]), default="delayed",
+              help="fp8 scaling: per-tensor from the amax history, per-tensor measured on the tensor, or per 1x128 / 128x128 block.")
 # strategy specific
 @click.option("--dpo_beta", type=float, default=0.1)
 @click.option("--label_smoothing", type=float, default=0.0)
@@ -244,7 +246,8 @@ def train(**o):
     click.echo(f"training plan: {total_steps} optimizer steps, parallel_mode={cfg.parallel_mode}, nprocs={cfg.nprocs}")
     trainer = Trainer(cfg)
     if o.get("fp8"):
-        with fp8_mod.fp8_autocast():
+        recipe = {"delayed": fp8_mod.DelayedScaling, "dynamic": fp8_mod.DynamicScaling, "block": fp8_mod.BlockScaling}[o.get("fp8_recipe") or "delayed"]()
+        with fp8_mod.fp8_autocast(recipe=recipe):
             trainer.train(o["param_path"], resume=o["resume"])
     else:
         trainer.train(o["param_path"], resume=o["resume"])

@@ -68,6 +68,18 @@ class DynamicScaling(FP8Recipe):
     measure_first = True
 
 
+@dataclass
+class BlockScaling(FP8Recipe):
+    """One scale per 1 x 128 block of the activations / gradients and per 128 x 128 block of the weights, measured on the
+    tensor itself (E4M3 everywhere): no history, no per-layer state.  Served by :mod:`astrai_b200.ops.fp8_block`;
+    ``backward`` chooses quantised (``"fp8"``) or bf16 gradient products."""
+
+    history_len: int = 1
+    margin: int = 0
+    measure_first = True
+    backward: str = "fp8"
+
+
 class FP8TensorMeta:
     """amax rings and current scales of the three operands of one linear layer (weight, input, output gradient)."""
 
@@ -219,6 +231,12 @@ def fp8_linear(x: Tensor, weight: Tensor, bias: Optional[Tensor] = None) -> Tens
     """``x @ weight.T (+ bias)`` on fp8 tensor cores under the active :func:`fp8_autocast` recipe."""
     st = autocast_state()
     recipe = st.recipe or DelayedScaling()
+    if isinstance(recipe, BlockScaling):
+        from astrai_b200.ops import fp8_block
+
+        if weight.shape[1] % fp8_block.BLOCK == 0:
+            return fp8_block.fp8_block_linear(x, weight, bias, backward=recipe.backward)
+        recipe = DynamicScaling()  # a width the block kernels do not take: per-tensor scaling measured on the tensor
     return _FP8LinearFn.apply(x, weight, bias, meta_for(weight, recipe), st.fp8_format)
 
 

@@ -2,8 +2,12 @@
 
 Finer scales than the per-tensor recipe of ``ops/fp8.py`` keep outlier channels from flattening everything else; the
 GEMM (``ops/csrc/gemm_fp8_block.cu``) runs each 128-wide K block into a fresh tensor-memory accumulator and promotes the
-partial sums with ``sa[m, kb] * sb[n / 128, kb]`` in registers.  The forward product is quantised; the backward pass of
-:func:`fp8_block_linear` runs in bf16 on the saved high-precision operands.  The reference's fp8 path is per-tensor only
+partial sums with ``sa[m, kb] * sb[n / 128, kb]`` in registers.  :func:`fp8_block_linear` quantises the forward product
+and, where the shapes allow (the contraction sizes of the two gradient products - the layer's output width and the token
+count - are multiples of 128), both gradient products as well: the operand that is contracted over its rows is
+transposed first and quantised along its new rows, so all three products run on the one block GEMM.  Other shapes, and
+``backward="bf16"``, take bf16 gradients from the saved high-precision operands.  ``fp8_autocast(recipe=BlockScaling())``
+routes every eligible linear layer here.  The reference's fp8 path is per-tensor only
 (``astrai/extension/fp8.py:61-105``; ``csrc/kernels/fp8/mm.cu:49-54``).
 """
 
@@ -84,30 +88,58 @@ def mm_fp8_block(a_q: Tensor, sa_t: Tensor, b_q: Tensor, sb: Tensor, bias: Optio
     return out.to(torch.bfloat16)
 
 
+def _block_product(a: Tensor, b: Tensor) -> Tensor:
+    """``a [M, K] @ b [N, K].T`` with ``a`` quantised per 1 x 128 block and ``b`` per 128 x 128 block (bf16 result)."""
+    a_q, sa_t = quantize_act_block(a)
+    b_q, sb = quantize_weight_block(b)
+    return mm_fp8_block(a_q, sa_t, b_q, sb)
+
+
 class _Fp8BlockLinearFn(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, x: Tensor, w: Tensor, bias: Optional[Tensor]):
+    def forward(ctx, x: Tensor, w: Tensor, bias: Optional[Tensor], backward: str):
         shape = x.shape
         x2 = x.reshape(-1, shape[-1])
         a_q, sa_t = quantize_act_block(x2)
         b_q, sb = quantize_weight_block(w)
         ctx.save_for_backward(x2, w)
-        ctx.has_bias, ctx.shape = bias is not None, shape
+        ctx.has_bias, ctx.shape, ctx.mode, ctx.w_ref = bias is not None, shape, backward, w
         return mm_fp8_block(a_q, sa_t, b_q, sb, bias).view(*shape[:-1], w.shape[0])
 
     @staticmethod
     def backward(ctx, gy: Tensor):
         x2, w = ctx.saved_tensors
         g2 = gy.reshape(-1, gy.shape[-1])
-        gx = (g2 @ w.to(g2.dtype)).view(ctx.shape) if ctx.needs_input_grad[0] else None
-        gw = (g2.t() @ x2.to(g2.dtype)).to(w.dtype) if ctx.needs_input_grad[1] else None
+        m, n = g2.shape
+        quantised = ctx.mode == "fp8" and n % BLOCK == 0 and m % BLOCK == 0
+        gx = gw = None
+        if ctx.needs_input_grad[0]:
+            if quantised:  # dX [M, K] = dY [M, N] @ W [N, K]: contraction over N, the second operand is W^T [K, N]
+                gx = _block_product(g2.to(torch.bfloat16).contiguous(), w.to(torch.bfloat16).t().contiguous()).to(g2.dtype)
+            else:
+                gx = g2 @ w.to(g2.dtype)
+            gx = gx.view(ctx.shape)
+        if ctx.needs_input_grad[1]:
+            if quantised:  # dW [N, K] = dY^T [N, M] @ X [M, K]: contraction over M, operands dY^T and X^T [K, M]
+                gw = _block_product(g2.to(torch.bfloat16).t().contiguous(), x2.to(torch.bfloat16).t().contiguous())
+            else:
+                gw = g2.t() @ x2.to(g2.dtype)
+            mg = getattr(ctx.w_ref, "main_grad", None)
+            if mg is not None:  # the flat runtime's fp32 gradient buffer
+                mg.add_(gw.float())
+                gw = None
+            else:
+                gw = gw.to(w.dtype)
         gb = g2.sum(0) if ctx.has_bias and ctx.needs_input_grad[2] else None
-        return gx, gw, gb
+        return gx, gw, gb, None
 
 
-def fp8_block_linear(x: Tensor, weight: Tensor, bias: Optional[Tensor] = None) -> Tensor:
-    """``x @ weight.T`` with both operands quantised block-wise on the fly (forward), bf16 gradients."""
-    return _Fp8BlockLinearFn.apply(x, weight, bias)
+def fp8_block_linear(x: Tensor, weight: Tensor, bias: Optional[Tensor] = None, backward: str = "fp8") -> Tensor:
+    """``x @ weight.T`` with both operands quantised block-wise on the fly.  ``backward="fp8"`` (default) quantises the two
+    gradient products the same way when their contraction sizes are multiples of 128; ``"bf16"`` keeps them in bf16."""
+    if backward not in ("fp8", "bf16"):
+        raise ValueError("backward must be 'fp8' or 'bf16'")
+    return _Fp8BlockLinearFn.apply(x, weight, bias, backward)
 
 
 class Fp8BlockLinear(nn.Module):

@@ -237,7 +237,8 @@ def _emit(args, world, value_ms, e2e_ms, launches, clocks, impl, extra=None, not
         "metric": spec["metric"], "value": value if value is not None else e2e, "unit": "tokens/s",
         "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
         "ms_per_step": (value_ms or e2e_ms) / args.steps, "higher_is_better": True, "scaling": "weak",
-        "vs_baseline": None if not BASELINE_VALUE else (value or e2e) / BASELINE_VALUE, "dtype": "bf16",
+        "vs_baseline": None if not BASELINE_VALUE else (value or e2e) / BASELINE_VALUE,
+        "dtype": f"fp8 ({args.fp8_recipe} scaling) linears, bf16 elsewhere" if getattr(args, "fp8_recipe", None) else "bf16",
         "data": "synthetic uniform token ids, random-init weights", "impl": impl,
         "config": {"model": spec["label"], "global_batch": readers * BPD * ACCUM,
                    "seq_len": SEQ, "batch_per_device": BPD, "grad_accum": ACCUM, "parallelism": f"{spec['mode']}{world}",
@@ -530,6 +531,9 @@ def main():
                     help="fsdp1b: the headline 1B FSDP run; tp8b / cp8b: 8B dense with tensor / context parallelism; "
                          "ep_moe: MoE + MLA with expert parallelism (these three need >= 2 GPUs)")
     ap.add_argument("--skip-e2e", action="store_true")
+    ap.add_argument("--fp8-recipe", default=None, choices=["delayed", "dynamic", "block"],
+                    help="run the linear layers on fp8 tensor cores with this scaling recipe (the line then says dtype fp8; "
+                         "not the headline configuration, which is bf16)")
     ap.add_argument("--fsdp-reshard", action="store_true",
                     help="fsdp1b: the full-shard placement instead of the default replicated parameters + sharded optimizer state")
     ap.add_argument("--smoke-layers", type=int, default=0,
@@ -558,6 +562,12 @@ def main():
             if int(os.environ.get("RANK", "0")) == 0:
                 why = f"the reference's own code path failed on this box: {type(exc).__name__}: {exc}"
                 print(json.dumps({"impl": "reference", "unavailable": " ".join(why.split())[:300]}), flush=True)
+    elif args.fp8_recipe:
+        from astrai_b200.ops import fp8
+
+        recipe = {"delayed": fp8.DelayedScaling, "dynamic": fp8.DynamicScaling, "block": fp8.BlockScaling}[args.fp8_recipe]()
+        with fp8.fp8_autocast(recipe=recipe):
+            run_ours(args)
     else:
         run_ours(args)
 

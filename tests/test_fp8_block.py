@@ -57,3 +57,74 @@ def test_block_gemm_matches_dequantised_matmul(m, n, k, bias):
     full = x.float() @ w.float().t()
     assert (got - (full + (bv.float() if bias else 0))).abs().max().item() < 0.05 * full.abs().max().item()
     assert native.kernel_status(torch.device("cuda")) == 0
+
+
+@pytest.mark.parametrize("backward", ["fp8", "bf16"])
+def test_block_linear_gradients_track_bf16(backward):
+    """All three products of the layer (forward, input gradient, weight gradient) on the block-scaled path against plain
+    arithmetic on the same operands (CPU statement of the kernels)."""
+    from astrai_b200.ops.fp8_block import fp8_block_linear
+
+    torch.manual_seed(3)
+    x = (torch.randn(2, 128, 256) * 0.5).requires_grad_(True)   # 256 tokens: a multiple of 128, so the weight gradient is quantised too
+    w = torch.nn.Parameter(torch.randn(384, 256) * 0.05)
+    b = torch.nn.Parameter(torch.randn(384) * 0.1)
+    y = fp8_block_linear(x, w, b, backward=backward)
+    ref = torch.nn.functional.linear(x, w, b)
+    assert (y.float() - ref).abs().max() < 0.05 * ref.abs().max()
+    gy = torch.randn_like(ref)
+    y.float().backward(gy)
+    gx, gw, gb = torch.autograd.grad(ref, (x, w, b), gy)
+    tol = 0.06 if backward == "fp8" else 0.02
+    assert (x.grad - gx).abs().max() < tol * gx.abs().max()
+    assert (w.grad - gw).abs().max() < tol * gw.abs().max()
+    assert torch.allclose(b.grad, gb, atol=0.05, rtol=0.02)
+
+
+def test_block_backward_falls_back_for_ragged_token_counts_and_feeds_main_grad():
+    from astrai_b200.ops.fp8_block import fp8_block_linear
+
+    torch.manual_seed(4)
+    x = torch.randn(100, 128, requires_grad=True)  # 100 tokens: the gradient products stay in bf16
+    w = torch.nn.Parameter(torch.randn(128, 128) * 0.05)
+    w.main_grad = torch.zeros(128, 128)
+    y = fp8_block_linear(x, w)
+    gy = torch.randn_like(y, dtype=torch.float32)
+    y.float().backward(gy)
+    assert w.grad is None and (w.main_grad - gy.t() @ x.detach()).abs().max() < 0.02 * (gy.t() @ x.detach()).abs().max()
+    with pytest.raises(ValueError):
+        fp8_block_linear(x, w, backward="int4")
+
+
+def test_block_recipe_routes_linears_through_the_block_path():
+    from astrai_b200 import ops
+    from astrai_b200.ops import fp8
+
+    torch.manual_seed(5)
+    x, w = torch.randn(128, 256), torch.randn(128, 256) * 0.05
+    plain = ops.linear(x, w)
+    with fp8.fp8_autocast(recipe=fp8.BlockScaling()):
+        block = ops.linear(x, w)
+        narrow = ops.linear(torch.randn(16, 64), torch.randn(32, 64))  # 64 columns: per-tensor scaling instead
+    assert block.dtype == torch.bfloat16 and narrow.shape == (16, 32)
+    diff = (block.float() - plain).abs().max()
+    assert 0 < diff < 0.05 * plain.abs().max()  # quantised, and close
+    assert fp8.BlockScaling().measure_first and fp8.BlockScaling(backward="bf16").backward == "bf16"
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("m,n,k", [(256, 384, 256), (1024, 2048, 512)])
+def test_block_linear_backward_on_the_kernels_tracks_bf16(m, n, k):
+    """Forward and both gradient products through the block GEMM on the GPU against fp32 arithmetic on the operands."""
+    from astrai_b200.ops.fp8_block import fp8_block_linear
+
+    torch.manual_seed(6)
+    x = (torch.randn(m, k, device="cuda") * 0.5).bfloat16().requires_grad_(True)
+    w = (torch.randn(n, k, device="cuda") * 0.05).bfloat16().requires_grad_(True)
+    y = fp8_block_linear(x, w)
+    gy = torch.randn(m, n, device="cuda").bfloat16()
+    y.backward(gy)
+    xf, wf, gf = x.detach().float(), w.detach().float(), gy.float()
+    ref_y, ref_gx, ref_gw = xf @ wf.t(), gf @ wf, gf.t() @ xf
+    for got, ref in ((y, ref_y), (x.grad, ref_gx), (w.grad, ref_gw)):
+        assert (got.float() - ref).abs().max().item() < 0.06 * ref.abs().max().item()
