@@ -1,7 +1,7 @@
 #!/usr/bin/env bash
 # Checks to run before a commit: deploy/pre_commit.sh [--fast] [--fix]
 #
-#   1. no build product or scratch file is staged (*.so, *.o, build/, _work/, gpurun_out/)
+#   1. no build product or ignored scratch file is staged (*.so, *.o, build/, anything .gitignore lists)
 #   2. every shell script parses (bash -n), every Python file compiles
 #   3. formatting and import order with ruff when it is installed (--fix rewrites instead of complaining)
 #   4. the CUDA sources compile for sm_100a (skipped with --fast, or when nvcc is absent)
@@ -13,8 +13,11 @@ cd "${REPO_DIR}"
 
 say "1/5 staged files"
 if git rev-parse --git-dir >/dev/null 2>&1; then
-    bad="$(git diff --cached --name-only | grep -E '(\.so|\.o|\.a)$|(^|/)build/|^_work/|^gpurun_out/' || true)"
-    [[ -z "${bad}" ]] || fail "build products or scratch files are staged:"$'\n'"${bad}"
+    staged="$(git diff --cached --name-only)"
+    bad="$(grep -E '(\.so|\.o|\.a)$|(^|/)build/' <<<"${staged}" || true)"
+    # a file that .gitignore lists can still be staged with `git add -f`: refuse those as well
+    ignored="$([[ -z "${staged}" ]] || git check-ignore --no-index ${staged} 2>/dev/null || true)"
+    [[ -z "${bad}${ignored}" ]] || fail "build products or ignored scratch files are staged:"$'\n'"${bad}${ignored}"
 fi
 
 say "2/5 syntax"
