@@ -113,7 +113,9 @@ class PagePool:
             return KVCache(self._storage.k_buffer, self._storage.v_buffer, self._req_pool.req_to_token, rows, lens_t,
                            out_cache_loc, max(seq_lens), kv_indptr, qo, tile_b, tile_i, q_lens=q_lens, kv_lens=list(seq_lens),
                            kv_gather_loc=gather, page_size=1 if self.contiguous else self.page_size)
-        loc = [int(host[r, n - 1]) for r, n in zip(req_indices, seq_lens)]
+        # slot of every request's newest position: one gather over the host table (a Python loop over the requests costs
+        # more than the rest of the step's bookkeeping at large batch sizes)
+        loc = host[torch.as_tensor(req_indices, dtype=torch.long), torch.as_tensor(seq_lens, dtype=torch.long) - 1]
         out_cache_loc = ws.put_int(ws.out_cache_loc, loc)
         ws.qo_indptr[: b + 1].copy_(ws.inc[: b + 1])
         max_len = max(seq_lens)

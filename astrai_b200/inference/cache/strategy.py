@@ -157,15 +157,63 @@ class RadixCache:
                 pages.append(page)
             return pages
 
-    def _forget_page(self, page: int, unlink: bool):
+    def _forget_page(self, page: int, unlink: bool) -> bool:
+        """Returns whether a link left the index (the chain a caller is walking may then be broken)."""
         link = self._where.pop(page, None)
         if link is None:
-            return
+            return False
         self._page_of.pop(link, None)
         if unlink:
             key = self._key_of.pop(link, None)
             if key is not None and self._links.get(key) == link:
                 del self._links[key]
+                return True
+        return False
+
+    def _descend(self, token_ids, pages: int) -> int:
+        """The link reached after ``pages`` whole pages of ``token_ids``, creating the links that are missing."""
+        link = self.ROOT
+        for n in range(pages):
+            key = (link, self._span(token_ids, n))
+            nxt = self._links.get(key)
+            if nxt is None:
+                nxt = self._next_id
+                self._next_id += 1
+                self._links[key] = nxt
+                self._key_of[nxt] = key
+            link = nxt
+        return link
+
+    def record_chain(self, pages: List[int], token_ids: List[int], start: int = 0):
+        """``record(pages[i], token_ids, i)`` for every full page ``i >= start``, in one walk along the chain instead of one
+        walk from the root per page (a 4 096-token sequence is 256 pages: 256 steps instead of 33 000)."""
+        with self._mutex:
+            full = min(len(token_ids) // self._page_size, len(pages))
+            if start >= full:
+                return
+            link = self._descend(token_ids, start)
+            for n in range(start, full):
+                page = pages[n]
+                key = (link, self._span(token_ids, n))
+                nxt = self._links.get(key)
+                if nxt is not None and self._where.get(page) == nxt:
+                    link = nxt  # already entered exactly there: keep the link and whatever is chained behind it
+                    continue
+                if self._forget_page(page, unlink=True):  # the page was indexed under other tokens; the chain may have lost a link
+                    link = self._descend(token_ids, n)
+                    key = (link, self._span(token_ids, n))
+                    nxt = self._links.get(key)
+                if nxt is None:
+                    nxt = self._next_id
+                    self._next_id += 1
+                    self._links[key] = nxt
+                    self._key_of[nxt] = key
+                old = self._page_of.get(nxt)
+                if old is not None and old != page:
+                    self._where.pop(old, None)
+                self._page_of[nxt] = page
+                self._where[page] = nxt
+                link = nxt
 
     def record(self, page_idx: int, token_ids: List[int], logical_page_idx: int):
         """Enter physical page ``page_idx`` as page number ``logical_page_idx`` of the sequence ``token_ids``."""
@@ -296,5 +344,4 @@ class PagedStrategy(AllocationStrategy):
     def record_hashes(self, state, prompt_ids, start):
         if self._prefix is None:
             return
-        for i in range(start, min(len(prompt_ids) // self._page_size, len(state.pages))):
-            self._prefix.record(state.pages[i], prompt_ids, i)
+        self._prefix.record_chain(state.pages, prompt_ids, start)

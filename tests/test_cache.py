@@ -310,3 +310,33 @@ def test_decode_bind_after_alloc_or_free_is_rebuilt():
     mgr.task_extend("a", 3)
     mgr.bind(["a"], ws)
     assert not mgr.bind_was_steady  # the batch composition may have changed in between
+
+
+def test_record_chain_equals_page_by_page_recording():
+    """The one-walk form used by the serving loop leaves the index exactly as the page-by-page form does, over random
+    sequences with shared prefixes, re-recordings, page reuse under other tokens and evictions in between."""
+    import random
+
+    from astrai_b200.inference.cache.strategy import RadixCache
+
+    rng = random.Random(0)
+    ps = 4
+    a, b = RadixCache(ps), RadixCache(ps)
+    prefixes = [[rng.randrange(50) for _ in range(ps * rng.randrange(1, 4))] for _ in range(3)]
+    free = list(range(200))
+    for step in range(300):
+        seq = list(rng.choice(prefixes)) + [rng.randrange(50) for _ in range(rng.randrange(0, 5 * ps))]
+        n_pages = -(-len(seq) // ps)
+        pages = [free.pop(rng.randrange(len(free))) if (free and rng.random() < 0.7) else rng.randrange(200) for _ in range(n_pages)]
+        start = rng.randrange(0, n_pages + 1)
+        for i in range(start, min(len(seq) // ps, len(pages))):
+            a.record(pages[i], seq, i)
+        b.record_chain(pages, seq, start)
+        if rng.random() < 0.3:
+            victim = rng.randrange(200)
+            a.evict(victim)
+            b.evict(victim)
+            free.append(victim)
+        probe = list(rng.choice(prefixes)) + [rng.randrange(50) for _ in range(ps)]
+        assert a.lookup(probe) == b.lookup(probe) and a.lookup(seq) == b.lookup(seq), step
+        assert a._where == b._where and a._page_of == b._page_of and a._links == b._links, step
