@@ -48,6 +48,7 @@ class EPContext:
         dev = self.flags.tensor.device
         self.done_counter = torch.zeros(1, dtype=torch.int32, device=dev)
         self._tile_flags: Dict[Tuple[str, int], Tensor] = {}
+        self.last_dropped: Optional[Tensor] = None  # pairs dropped by the capacity limit in the latest call (0-d tensor)
 
     # Every call has an all-to-all synchronisation of its own (the counts exchange / the gradient announcement), so a
     # buffer of call n is free again when call n + 2 starts: two parities are enough.  Allocation order is the same on
@@ -86,6 +87,37 @@ def row_capacity(tokens: int, top_k: int, world: int, local_experts: int, capaci
     here) is reserved; with one, ``capacity_factor x`` the balanced share, and a step that exceeds it raises."""
     pairs = tokens * top_k * world if capacity_factor is None else int(tokens * top_k * capacity_factor)
     return -(-pairs // TILE) * TILE + local_experts * TILE
+
+
+def limit_rows_per_rank(idx: Tensor, weights: Tensor, n_experts: int, world: int, capacity_factor: float):
+    """Token dropping for a capacity-bounded exchange, without a host synchronisation.
+
+    Of this rank's ``T x k`` (token, choice) pairs at most ``floor(capacity_factor * T * k / world)`` may go to the experts of
+    any one rank; with every sender keeping to that, no receiver's buffer of ``capacity_factor * T * k`` rows can overflow.
+    Pairs beyond a destination's limit (in token order) are *dropped*: their routing weight becomes 0 (so they add
+    nothing to the output and receive no gradient) and they are re-addressed to the first expert of a rank that still has
+    room, because the exchange moves a dense ``[T, k]`` table.  Returns ``(idx, weights, counts [E] int32, dropped)`` with
+    ``dropped`` a 0-d tensor (the number of dropped pairs, for logging); kept pairs are returned unchanged.
+    Needs ``capacity_factor >= 1`` (otherwise the pairs cannot all be placed)."""
+    if capacity_factor < 1.0:
+        raise ValueError("capacity_factor must be at least 1: every pair has to be placed somewhere")
+    t, k = idx.shape
+    local = n_experts // world
+    cap = int(capacity_factor * t * k) // world
+    flat = idx.reshape(-1).long()
+    dst = flat // local                                                            # destination rank of every pair
+    onehot = torch.nn.functional.one_hot(dst, world)                               # [T*k, W]
+    pos = (onehot.cumsum(0) * onehot).sum(1) - 1                                   # position among the pairs of its rank
+    over = pos >= cap
+    sent = onehot.sum(0)                                                           # pairs per destination before the limit
+    room = (cap - sent).clamp(min=0)                                               # free rows per destination
+    # the j-th dropped pair takes the j-th free row, destinations in rank order
+    j = over.long().cumsum(0) - 1
+    new_dst = torch.searchsorted(room.cumsum(0), j.clamp(min=0), right=True).clamp(max=world - 1)
+    new_flat = torch.where(over, new_dst * local, flat)
+    keep = (~over).to(weights.dtype).view(t, k)
+    counts = torch.bincount(new_flat, minlength=n_experts).to(torch.int32)
+    return new_flat.view(t, k).to(idx.dtype), weights * keep, counts, over.sum()
 
 
 def arena_bytes_for(tokens: int, hidden: int, top_k: int, world: int, n_experts: int,
@@ -224,8 +256,10 @@ def ep_experts(x: Tensor, idx: Tensor, weights: Tensor, counts: Tensor, w_gate_u
 
     ``w_gate_up`` ``[E / W, 2F, H]`` and ``w_down`` ``[E / W, H, F]`` are this rank's experts; ``idx`` / ``counts`` use
     global expert numbers (rank ``d`` owns ``[d * E / W, (d + 1) * E / W)``).  The sorted buffers hold
-    ``capacity_factor`` times the balanced share of rows (``None``: the worst case, every pair of every rank); a step
-    whose routing sends more rows to one rank records error 72 in the kernel status word instead of overflowing.
+    ``capacity_factor`` times the balanced share of rows (``None``: the worst case, every pair of every rank).  With a
+    capacity factor every sender keeps to its share of each receiver's buffer (:func:`limit_rows_per_rank`: pairs beyond
+    it are dropped, i.e. contribute nothing), so a receiver cannot overflow; error 72 of the kernel status word remains
+    as the check behind that.
     """
     ep = ctx or get_context()
     if ep is None:
@@ -236,6 +270,8 @@ def ep_experts(x: Tensor, idx: Tensor, weights: Tensor, counts: Tensor, w_gate_u
     if not (x.is_cuda and x.dtype == torch.bfloat16 and x.shape[1] % 64 == 0 and w_gate_up.shape[1] % 64 == 0):
         raise ValueError("ep_experts: bf16 CUDA activations with hidden and intermediate sizes that are multiples of 64")
     r_cap = row_capacity(x.shape[0], idx.shape[1], ep.world, n_experts // ep.world, capacity_factor)
+    if capacity_factor is not None and ep.world > 1:
+        idx, weights, counts, ep.last_dropped = limit_rows_per_rank(idx, weights, n_experts, ep.world, capacity_factor)
     return _EPExpertsFn.apply(x.contiguous(), idx, weights, counts, w_gate_up, w_down, ep, r_cap)
 
 

@@ -120,3 +120,40 @@ def test_context_parallel_batch_is_cut_zigzag_with_global_positions():
     assert cut["position_ids"].tolist() == [[2, 3, 4, 5]] * 2
     with pytest.raises(NotImplementedError):
         ex.shard_batch({"input_ids": ids, "target_ids": ids, "position_ids": ids})
+
+
+def test_capacity_limit_drops_only_the_overflow_and_keeps_every_rank_within_its_share():
+    from astrai_b200.parallel.expert_parallel import limit_rows_per_rank
+
+    torch.manual_seed(0)
+    t, k, e, world = 64, 2, 8, 4                      # 128 pairs, 32 per destination when balanced
+    idx = torch.randint(0, e, (t, k))
+    idx[:40] = torch.tensor([0, 1])                   # 80 pairs pile up on rank 0 (experts 0 and 1)
+    w = torch.rand(t, k, requires_grad=True)
+    new_idx, new_w, counts, dropped = limit_rows_per_rank(idx, w, e, world, capacity_factor=1.5)
+    cap = int(1.5 * t * k) // world                   # 48 rows of every receiver belong to this sender
+    per_rank = counts.view(world, e // world).sum(1)
+    assert int(counts.sum()) == t * k and int(per_rank.max()) <= cap
+    kept = new_w != 0
+    assert torch.equal(new_idx[kept], idx[kept]) and torch.equal(new_w[kept], w[kept].detach())  # kept pairs are untouched
+    sent_to_0 = ((idx // 2) == 0)
+    assert int(dropped) == int(sent_to_0.sum()) - cap == int((~kept).sum())
+    flat_keep = kept.reshape(-1)[sent_to_0.reshape(-1)]
+    assert flat_keep[:cap].all() and not flat_keep[cap:].any()                 # the first `cap` pairs in token order stay
+    assert ((new_idx[~kept] // 2) != 0).all()                                   # the dropped ones were re-addressed elsewhere
+    new_w.sum().backward()
+    assert torch.equal(w.grad != 0, kept)                                       # dropped pairs get no gradient
+    same_idx, same_w, same_counts, none = limit_rows_per_rank(idx, w.detach(), e, world, capacity_factor=4.0)
+    assert torch.equal(same_idx, idx) and torch.equal(same_w, w.detach()) and int(none) == 0
+    assert torch.equal(same_counts, torch.bincount(idx.reshape(-1), minlength=e).int())
+    with pytest.raises(ValueError, match="at least 1"):
+        limit_rows_per_rank(idx, w, e, world, capacity_factor=0.5)
+
+
+def test_capacity_limit_places_every_pair_even_at_factor_one():
+    from astrai_b200.parallel.expert_parallel import limit_rows_per_rank
+
+    t, k, e, world = 32, 4, 8, 2
+    idx = torch.zeros(t, k, dtype=torch.long)         # everything wants expert 0
+    _, w, counts, dropped = limit_rows_per_rank(idx, torch.ones(t, k), e, world, capacity_factor=1.0)
+    assert counts.view(world, -1).sum(1).tolist() == [64, 64] and int(dropped) == 64 and int((w == 0).sum()) == 64
