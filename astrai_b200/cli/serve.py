@@ -33,6 +33,9 @@ from astrai_b200.cli.common import flatten_sections, load_yaml, merge_config, to
 @click.option("--prefill_defer_steps", type=int, default=8,
               help="Under load (32 or more requests decoding) new prompts wait up to this many decode steps so that "
                    "several are prefilled in one forward; 0 prefills every prompt at once.")
+@click.option("--tp_size", type=int, default=1,
+              help="Tensor-parallel serving: one replica over this many GPUs; start the command under "
+                   "`python -m torch.distributed.run --nproc-per-node TP_SIZE -m astrai_b200.cli.serve ...`.")
 @click.option("--reload", is_flag=True, default=False)
 @click.pass_context
 def serve_command(ctx: click.Context, config: Optional[str], **opts):
@@ -42,7 +45,7 @@ def serve_command(ctx: click.Context, config: Optional[str], **opts):
 
     engine_kwargs = {"enable_cuda_graph": o["cuda_graph"], "paged": o["page_size"] > 1, "page_size": o["page_size"],
                      "kv_cache_tokens": o["kv_cache_tokens"], "chunked_prefill": o["chunked_prefill"],
-                     "max_prefill_tokens": o["max_prefill_tokens"], "prefill_defer_steps": o["prefill_defer_steps"]}
+                     "max_prefill_tokens": o["max_prefill_tokens"], "prefill_defer_steps": o["prefill_defer_steps"], "tp_size": o["tp_size"]}
     run_server(param_path=Path(o["param_path"]), host=o["host"], port=o["port"], reload=o["reload"], device=o["device"],
                dtype=torch_dtype(o["dtype"]), max_batch_size=o["max_batch_size"], max_seq_len=o["max_seq_len"], **engine_kwargs)
 

@@ -101,7 +101,18 @@ class InferenceEngine:
         self.scheduler = InferenceScheduler(model=model, tokenizer=tokenizer, max_batch_size=max_batch_size,
                                             max_seq_len=max_seq_len, cache=cache, enable_cuda_graph=enable_cuda_graph,
                                             backend=backend, **scheduler_kwargs)
-        self.scheduler.start()
+        # tensor-parallel serving: only the replica's first rank runs the loop in a thread and talks to callers; the
+        # other ranks run it in the foreground through follow()
+        control = getattr(self.scheduler, "_control", None)
+        self.leader = control is None or control.leader
+        if self.leader:
+            self.scheduler.start()
+
+    def follow(self):
+        """Ranks of a tensor-parallel replica other than the first: serve until the first rank shuts the replica down."""
+        if self.leader:
+            raise RuntimeError("follow() is for the ranks that do not face clients")
+        self.scheduler.follow()
 
     def __enter__(self):
         return self

@@ -149,10 +149,48 @@ async def create_message(request: MessagesRequest):
     return await ProtocolHandler(request, _engine(), AnthropicResponseBuilder()).handle()
 
 
+def run_tensor_parallel_server(param_path: Path, tp_size: int, host: str = "0.0.0.0", port: int = 8000, device: str = "cuda",
+                               dtype: torch.dtype = torch.bfloat16, max_batch_size: int = 16, max_seq_len: Optional[int] = None,
+                               **engine_kwargs):
+    """One serving replica over ``tp_size`` processes (launch with ``python -m torch.distributed.run --nproc-per-node
+    tp_size -m astrai_b200.cli.serve --tp_size tp_size ...``): every rank loads the checkpoint and keeps its share of every
+    layer; the first rank runs the HTTP front end, the others follow its scheduling loop until it shuts down."""
+    import os
+
+    import uvicorn
+
+    from astrai_b200.parallel.setup import setup_parallel
+
+    rank, world = int(os.environ.get("RANK", "0")), int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", str(rank)))
+    if world != tp_size:
+        raise RuntimeError(f"--tp_size {tp_size} needs exactly that many processes (torchrun --nproc-per-node {tp_size}); found {world}")
+    cuda = str(device).startswith("cuda")
+    with setup_parallel(rank, world, local, "nccl" if cuda else "gloo", os.environ.get("MASTER_ADDR", "127.0.0.1"),
+                        os.environ.get("MASTER_PORT", "29500"), "cuda" if cuda else "cpu"):
+        engine = create_engine(param_path, device=f"cuda:{local}" if cuda else "cpu", dtype=dtype, max_batch_size=max_batch_size,
+                               max_seq_len=max_seq_len, tp_size=tp_size, **engine_kwargs)
+        if rank != 0:
+            engine.follow()
+            return
+        app = get_app()
+        app.state.server_config = {"_test": True}  # the engine exists already: the lifespan hook must not build another
+        app.state.engine = engine
+        try:
+            uvicorn.run(app, host=host, port=port)
+        finally:
+            app.state.engine = None
+            engine.shutdown()
+
+
 def run_server(param_path: Path, host: str = "0.0.0.0", port: int = 8000, reload: bool = False, device: str = "cuda",
                dtype: torch.dtype = torch.bfloat16, max_batch_size: int = 16, max_seq_len: Optional[int] = None, **engine_kwargs):
     import uvicorn
 
+    tp_size = int(engine_kwargs.pop("tp_size", 1) or 1)
+    if tp_size > 1:
+        return run_tensor_parallel_server(param_path, tp_size, host=host, port=port, device=device, dtype=dtype,
+                                          max_batch_size=max_batch_size, max_seq_len=max_seq_len, **engine_kwargs)
     app = get_app()
     app.state.server_config = {"device": device, "dtype": dtype, "param_path": param_path, "max_batch_size": max_batch_size,
                                "max_seq_len": max_seq_len, **engine_kwargs}

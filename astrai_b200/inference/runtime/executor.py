@@ -135,14 +135,16 @@ def fuse_projection_weights(model) -> int:
 
 class Executor:
     def __init__(self, model, kv_cache: PagePool, task_cache: TaskCacheManager, device=None, dtype=None,
-                 enable_cuda_graph: bool = True, max_prefill_tokens: Optional[int] = None):
-        self.model, self.kv_cache, self.task_cache = model, kv_cache, task_cache
+                 enable_cuda_graph: bool = True, max_prefill_tokens: Optional[int] = None, control=None):
+        """``control``: a :class:`~astrai_b200.parallel.tp_inference.ReplicatedControl` when several ranks run this executor
+        in lockstep on their shares of one model; the first rank's sampled tokens are then used by all."""
+        self.model, self.kv_cache, self.task_cache, self.control = model, kv_cache, task_cache, control
         if next(model.parameters()).is_cuda and not model.training:
             fuse_projection_weights(model)
         p = next(model.parameters())
         self.device = torch.device(device) if device is not None else p.device
         self.dtype = dtype or p.dtype
-        cfg = model.config
+        cfg = self._cfg = getattr(model, "local_config", None) or model.config  # a tensor-parallel rank sizes for its own heads
         head_dim = cfg.hidden_size // cfg.num_attention_heads
         self.max_prefill_tokens = max_prefill_tokens or kv_cache.max_batch_size * kv_cache.max_seq_len
         self._workspace = InferenceWorkspace(kv_cache.max_batch_size, kv_cache.max_seq_len, cfg.num_attention_heads,
@@ -175,7 +177,7 @@ class Executor:
     def _decode_splits(self, rows: int) -> int:
         """KV splits baked into the graph of a bucket: one wave of two CTAs per SM whatever the context length (a graph
         outlives the lengths it was captured with; splits that fall beyond a short sequence return at once)."""
-        base = max(rows * self.model.config.num_key_value_heads, 1)
+        base = max(rows * self._cfg.num_key_value_heads, 1)
         return max(1, min(148 * 2 // base, self._workspace.decode_o_part.shape[2]))
 
     def _padded(self, kv, b: int, rows: int):
@@ -240,6 +242,8 @@ class Executor:
         out = sample(logits, temperature=info.temperatures, top_k=info.top_ks, top_p=info.top_ps,
                      frequency_penalty=info.freq_penalties, input_ids=hist, input_mask=hist_mask,
                      return_logprobs=return_logprobs, hints=info.hints)
+        if self.control is not None:  # one random stream decides for every rank of the replica
+            self.control.share_tokens(*(out if return_logprobs else (out,)))
 
         def finish():
             if not return_logprobs:

@@ -28,8 +28,18 @@ class InferenceScheduler:
                  dtype=None, cache: Optional[PagePool] = None, enable_cuda_graph: bool = True, backend=None,
                  page_size: int = 16, kv_cache_tokens: Optional[int] = None, paged: bool = True,
                  max_prefill_tokens: int = 8192, chunked_prefill: bool = False, prefill_defer_steps: int = 8,
-                 prefill_defer_min_batch: int = 32, prefill_defer_tokens: int = 2048):
-        cfg = model.config
+                 prefill_defer_min_batch: int = 32, prefill_defer_tokens: int = 2048, tp_group=None, tp_size: int = 1):
+        """``tp_size > 1`` (or a ``tp_group``): tensor-parallel serving - the model is cut over the ranks of the group,
+        every rank runs this scheduler in lockstep and the first rank alone talks to clients
+        (:mod:`astrai_b200.parallel.tp_inference`; the other ranks call :meth:`follow`)."""
+        self._control = None
+        if tp_group is not None or tp_size > 1:
+            from astrai_b200.parallel.tp_inference import ReplicatedControl, shard_for_inference_
+
+            self._control = ReplicatedControl(tp_group)
+            if getattr(model, "tp_size", 1) == 1:
+                shard_for_inference_(model, self._control.world, self._control.rank, tp_group)
+        cfg = getattr(model, "local_config", None) or model.config
         if max_seq_len is None:
             max_seq_len = cfg.max_position_embeddings
         if max_seq_len is None:
@@ -44,7 +54,11 @@ class InferenceScheduler:
         self._task_cache = TaskCacheManager(self._cache)
         self._task_mgr = TaskManager(tokenizer, max_batch_size, max_seq_len, metrics=self._metrics)
         self._executor = Executor(model, self._cache, self._task_cache, self.device, self.dtype, enable_cuda_graph,
-                                  max_prefill_tokens=max_prefill_tokens)
+                                  max_prefill_tokens=max_prefill_tokens, control=self._control)
+        self._staged: List[dict] = []      # tensor-parallel serving, first rank: requests not yet shared with the others
+        self._cancelled: List[str] = []
+        self._stage_lock = threading.Lock()
+        self._batch_serial = 0
         self.max_prefill_tokens = max_prefill_tokens
         # chunked prefill: at most max_prefill_tokens prompt tokens per step over all requests; a long prompt takes
         # several steps and the running requests keep decoding in between (the reference never mixes the two)
@@ -62,11 +76,54 @@ class InferenceScheduler:
 
     # -- public surface -----------------------------------------------------------------------------------------------------
     def add_task(self, prompt, **kwargs) -> str:
-        return self._task_mgr.add_task(prompt, **kwargs)
+        if self._control is None:
+            return self._task_mgr.add_task(prompt, **kwargs)
+        if not self._control.leader:
+            raise RuntimeError("requests enter a tensor-parallel replica through its first rank")
+        # staged: the request joins the queue of every rank at the start of the next loop iteration, in arrival order
+        callback = kwargs.pop("stream_callback", None)
+        backend = kwargs.pop("backend", None)
+        ids = self._task_mgr.tokenizer.encode(prompt) if isinstance(prompt, str) else list(prompt)
+        task = self._task_mgr.make_task(ids, kwargs.pop("max_tokens", None), **kwargs)
+        spec = {"task_id": task.task_id, "prompt_ids": task.prompt_ids, "max_tokens": task.max_tokens, "temperature": task.temperature,
+                "top_p": task.top_p, "top_k": task.top_k, "frequency_penalty": task.frequency_penalty, "rep_window": task.rep_window}
+        with self._stage_lock:
+            self._staged.append(spec)
+            if callback is not None:
+                self._task_mgr.register_callback(task.task_id, callback)
+        self._task_mgr.wake()
+        return task.task_id
 
     def remove_task(self, task_id: str):
+        if self._control is not None:
+            with self._stage_lock:
+                self._cancelled.append(task_id)
+            return
         for task in self._task_mgr.remove_task(task_id):
             self._task_cache.task_free(task.task_id)
+
+    def _share_requests(self) -> bool:
+        """Tensor-parallel serving: bring the queues of every rank up to date with what reached the first rank since the
+        last iteration.  Returns False when the replica is to stop."""
+        payload = None
+        if self._control.leader:
+            with self._stage_lock:
+                payload = {"new": self._staged, "cancelled": self._cancelled, "stop": self._stop_event.is_set()}
+                self._staged, self._cancelled = [], []
+        payload = self._control.share(payload)
+        for spec in payload["new"]:
+            self._task_mgr.enqueue(Task(spec["task_id"], list(spec["prompt_ids"]), spec["max_tokens"], spec["temperature"], spec["top_p"],
+                                        spec["top_k"], spec["frequency_penalty"], spec["rep_window"]))
+        for task_id in payload["cancelled"]:
+            for task in self._task_mgr.remove_task(task_id):
+                self._task_cache.task_free(task.task_id)
+        return not payload["stop"]
+
+    def follow(self):
+        """Run the scheduling loop on the calling thread until the first rank stops the replica (ranks other than the first)."""
+        self._stop_event.clear()
+        self._run_generation_loop()
+        self._abort_and_clear(free_waiting=True)
 
     def get_stats(self) -> Dict[str, Any]:
         return self._task_mgr.get_stats()
@@ -190,12 +247,21 @@ class InferenceScheduler:
         tok = self._task_mgr.tokenizer
         stop_ids = set(tok.stop_ids)
         try:
-            while not self._stop_event.is_set():
+            while True:
+                if self._control is not None:
+                    if not self._share_requests():
+                        break
+                elif self._stop_event.is_set():
+                    break
                 self._retire(stop_ids)
                 self._refill()
                 active = self._task_mgr.get_active_tasks()
                 if not active:
-                    if not self._task_mgr.has_work():
+                    if self._control is not None:
+                        # only the first rank idles (briefly, until a request is staged); the others wait in the next broadcast
+                        if self._control.leader and not self._staged and not self._stop_event.is_set():
+                            self._task_mgr.wait_for_wake(timeout=0.02)
+                    elif not self._task_mgr.has_work():
                         self._task_mgr.wait_for_tasks(timeout=1.0)
                     else:
                         self._stop_event.wait(0.001)  # waiting requests do not fit yet
@@ -252,7 +318,9 @@ class InferenceScheduler:
             if len(ids) >= self.max_seq_len or budget <= 0:
                 tasks.append(None)
                 continue
-            task = Task(f"batch_{uuid.uuid4().hex[:8]}", list(ids), budget, temperature, top_p, top_k, frequency_penalty, rep_window)
+            self._batch_serial += 1  # ids must sort alike on every rank of a tensor-parallel replica: a counter, not a random id
+            name = f"batch_{self._batch_serial:012d}" if self._control is not None else f"batch_{uuid.uuid4().hex[:8]}"
+            task = Task(name, list(ids), budget, temperature, top_p, top_k, frequency_penalty, rep_window)
             if not self._task_cache.task_alloc(task.task_id, task.prompt_ids):
                 tasks.append(None)
                 continue

@@ -118,6 +118,24 @@ class TaskManager:
         self._task_event.set()
         return task.task_id
 
+    def enqueue(self, task: Task):
+        """Append an already built task (tensor-parallel serving: the first rank built it, every rank queues it)."""
+        with self._lock:
+            self.waiting_queue.append(task)
+            self._total_tasks += 1
+        if self._metrics is not None:
+            self._metrics.register(task.task_id)
+        self._task_event.set()
+
+    def register_callback(self, task_id: str, callback: Callable):
+        with self._lock:
+            self._callbacks[task_id] = callback
+
+    def wait_for_wake(self, timeout: float):
+        """Sleep until :meth:`wake` (or a new task) or ``timeout`` seconds, whatever the queues hold."""
+        self._task_event.clear()
+        self._task_event.wait(timeout=timeout)
+
     def remove_task(self, task_id: str) -> List[Task]:
         with self._lock:
             gone = [t for t in self.active_tasks if t.task_id == task_id]

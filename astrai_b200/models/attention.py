@@ -73,7 +73,7 @@ class GQA(nn.Module):
         q, k, v = self._project(x, rotary_emb)
         if self.use_qk_norm:
             q, k = self.q_norm(q), self.k_norm(k)
-        out = attention(q, k, v, kv_cache, self.layer_id, attn_mask, is_causal, fwd).reshape(*x.shape[:-1], self.dim)
+        out = attention(q, k, v, kv_cache, self.layer_id, attn_mask, is_causal, fwd).reshape(*x.shape[:-1], self.n_heads * self.head_dim)
         if self.use_gated_attention:
             out = out * torch.sigmoid(self.gate(x))
         return self.o_proj(out)
