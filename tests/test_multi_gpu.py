@@ -170,6 +170,20 @@ def test_pipeline_parallel_trainer_mode_matches_single_gpu(tmp_path):
         assert abs(run["sums"][k] - v) / max(v, 1e-6) < 2e-2, k
 
 
+def test_tensor_parallel_serving_on_two_gpus(tmp_path):
+    """One serving replica over 2 GPUs in bf16 with CUDA-graph decode (the all-reduces of the cut blocks are inside the
+    graphs): every request finishes, and the greedy streams start like the single-GPU ones (bf16 sums in another order
+    may flip a near-tie later on)."""
+    _need_gpus(2)
+    out = str(tmp_path / "tp_serve.json")
+    _torchrun(2, os.path.join(ROOT, "tests", "workers", "tp_serve.py"), ["--out", out, "--device", "cuda"], 29765, timeout=150)
+    res = json.load(open(out))
+    assert res["finished"] and res["local_heads"] == 2 and res["pool_heads"] == 1 and res["sampled_pieces"] == 6
+    same_start = sum(g.split(">")[:2] == w.split(">")[:2] for g, w in zip(res["got"], res["want"]))
+    assert same_start >= 4, res
+    assert all(g.count("<") == w.count("<") for g, w in zip(res["got"], res["want"]))
+
+
 def test_full_shard_fsdp_matches_replicated_fsdp(tmp_path):
     """``reshard=True`` on 2 GPUs (bf16, NCCL gathers / reduce-scatters on the side stream, storages released and
     re-created around every unit): same losses, norms and weights as the replicated placement, nothing whole at rest."""
