@@ -52,7 +52,13 @@ def load_json(path: PathLike, broadcast: bool = False) -> dict:
 
 
 def save_safetensors(state_dict: dict, path: PathLike):
-    st.save_file({k: v.detach().contiguous().cpu() for k, v in state_dict.items()}, str(path))
+    """Every tensor is written from storage of its own: a device tensor is copied by the transfer, a host tensor is cloned
+    (views of one flat buffer, or one tensor under two names, would otherwise be refused by the file format)."""
+    def own(t):
+        t = t.detach()
+        return t.contiguous().cpu() if t.device.type != "cpu" else t.contiguous().clone()
+
+    st.save_file({k: own(v) for k, v in state_dict.items()}, str(path))
 
 
 def load_safetensors(path: PathLike, broadcast: bool = False) -> dict:
@@ -182,7 +188,9 @@ class Checkpoint:
         meta = load_json(root / META_FILE, broadcast)
         config = load_json(root / CONFIG_FILE, broadcast)
         sd = load_state_dict(root / WEIGHTS_FILE, broadcast=broadcast)
-        extra = {f.stem: load_torch(f, broadcast=broadcast) for f in sorted(root.glob("*.pt"))}
+        # which extra files exist is rank 0's knowledge too: the other ranks may not see the directory at all
+        names = _object_from_rank0(lambda: sorted(f.name for f in root.glob("*.pt")), broadcast)
+        extra = {Path(n).stem: load_torch(root / n, broadcast=broadcast) for n in names}
         return cls(sd, meta.get("epoch", 0), meta.get("consumed_samples", 0), extra, meta, config)
 
     @classmethod
