@@ -18,14 +18,13 @@ def preprocess_command(input_files, output_dir, config, tokenizer_path, batch_si
     """Run the preprocessing pipeline over INPUT_FILES and write ``<output_dir>/<domain>/shard_NNNN/``."""
     from astrai_b200.config import PipelineConfig
     from astrai_b200.preprocessing import Pipeline
-    from astrai_b200.tokenize import AutoTokenizer
 
     cfg = PipelineConfig.from_file(config)
     if batch_size is not None:
         cfg.preprocessing.batch_size = batch_size
-    stats = Pipeline(cfg, list(input_files), output_dir, AutoTokenizer.from_pretrained(tokenizer_path)).run()
-    if stats:
-        click.echo(str(stats))
+    click.echo(f"Preprocessing {len(input_files)} file(s) -> {output_dir}")
+    kept = Pipeline(cfg, list(input_files), output_dir, tokenizer_path).run()
+    click.echo(f"Done: {kept} record(s) kept.")
 
 
 if __name__ == "__main__":
