@@ -350,7 +350,10 @@ class PipelineParallelExecutor(ModelParallelExecutor):
     Every rank of a block reads the same batch (the first stage uses the token ids, the last one the targets).  One
     trainer micro-batch is one non-interleaved 1F1B window: the per-device batch is cut into ``chunks`` pieces whose
     forward and backward passes interleave across the stages (:meth:`pipeline_step`, which the trainer calls instead of
-    strategy + backward).  The objective is next-token cross-entropy (``seq``); the other strategies are refused.
+    strategy + backward; :meth:`pipeline_eval` for validation batches).  The objectives are the token cross-entropies:
+    ``seq`` (every position) and ``sft`` (positions of the loss mask, attention inside each packed document; the loss
+    is the mean over the trained tokens of the whole per-device batch, whatever the cut into pieces).  The preference
+    and policy-gradient strategies, which need reference models, are refused.
     Gradients accumulate in the flat runtime's fp32 buffers; every parameter lives on exactly one stage, so gradients are
     summed over the data-parallel group only and the gradient norm is summed over the stages.  Checkpoints are put back
     together with the reference's keys: every stage sends its tensors to the first one.
@@ -411,34 +414,76 @@ class PipelineParallelExecutor(ModelParallelExecutor):
         return self.mesh.dp_rank if self.mesh is not None else 0
 
     # -- one micro-batch of the trainer = one 1F1B window ------------------------------------------------------------------
-    def pipeline_step(self, model, batch: dict, loss_scale: float) -> dict:
-        unknown = set(batch) - {"input_ids", "target_ids", "position_ids"}
+    def _pieces(self, batch: dict):
+        """The batch as the pipeline takes it: ids, targets (masked positions set to the ignored index), the number of
+        pieces, per-piece forward keyword arguments and per-piece loss weights."""
+        from astrai_b200.trainer.strategy import doc_attention
+
+        unknown = set(batch) - {"input_ids", "target_ids", "position_ids", "loss_mask"}
         if unknown or "target_ids" not in batch:
-            raise NotImplementedError("pipeline parallelism trains the next-token objective (strategy 'seq'): a batch of "
-                                      f"input_ids / target_ids; got keys {sorted(batch)}")
+            raise NotImplementedError("pipeline parallelism trains the token cross-entropy objectives (strategies 'seq' and "
+                                      f"'sft'): a batch of input_ids / target_ids [/ position_ids / loss_mask]; got keys {sorted(batch)}")
         stage = self._pipe.stage
         dev = next(stage.parameters()).device
-        ids, targets = batch["input_ids"].to(dev), batch["target_ids"].to(dev)
+        ids, targets = batch["input_ids"], batch["target_ids"]
         n = ids.shape[0]
         chunks = self.chunks if self.chunks > 0 else min(self.mesh.mp_size, n)
         if n % chunks:
             raise ValueError(f"a per-device batch of {n} cannot be cut into {chunks} pipeline pieces")
+        weights = None
+        if "loss_mask" in batch:  # the supervised objective: a mean over the trained tokens of the whole batch
+            keep = batch["loss_mask"].bool()
+            targets = targets.masked_fill(~keep.to(targets.device), -100)
+            counts = keep.reshape(chunks, -1).sum(1).double().cpu()  # the loader's batch lives on the host: no device wait
+            weights = (counts / counts.sum().clamp(min=1)).tolist()
+        kwargs = [{} for _ in range(chunks)]
+        if "position_ids" in batch:
+            packed = "loss_mask" in batch  # packed documents attend inside themselves, as in the supervised strategy
+            for kw, pos in zip(kwargs, batch["position_ids"].chunk(chunks, dim=0)):
+                kw["position_ids"] = pos.to(dev)
+                if packed:
+                    kw["attention"] = doc_attention(pos)
+        return ids.to(dev), targets.to(dev), chunks, kwargs, weights
+
+    def pipeline_step(self, model, batch: dict, loss_scale: float) -> dict:
+        ids, targets, chunks, kwargs, weights = self._pieces(batch)
+        stage = self._pipe.stage
         for u in self.engine.units:
             u.ready = u.reduced = False
         loss = self._pipe.train_step(ids if stage.first else None, targets if stage.last else None, chunks,
-                                     micro_shape=(n // chunks, ids.shape[1]), loss_scale=loss_scale)
+                                     micro_shape=(ids.shape[0] // chunks, ids.shape[1]), loss_scale=loss_scale,
+                                     micro_kwargs=kwargs, weights=weights)
         if self.gradient_state.sync_gradients:
             for u in reversed(self.engine.units):
                 u.ready = True
                 self._reduce_unit(u)
             self._finish_reductions()
-        # the window's mean loss is known on the last stage: hand it to the other stages for logging
-        value = loss.detach().float().reshape(1) if loss is not None else torch.zeros(1, device=dev)
-        last = self.mesh.mp_ranks()[-1]
-        dist.broadcast(value, src=last, group=self.mesh.mp_group)
+        return self._shared_loss(loss, ids.device)
+
+    def _shared_loss(self, loss, dev) -> dict:
+        """The loss is known on the last stage: hand it to the other stages (logging, validation averages)."""
         from astrai_b200.trainer.strategy import DeferredMetrics
 
+        value = loss.detach().float().reshape(1) if loss is not None else torch.zeros(1, device=dev)
+        dist.broadcast(value, src=self.mesh.mp_ranks()[-1], group=self.mesh.mp_group)
         return {"loss": value[0], "metrics": DeferredMetrics(loss=value[0])}
+
+    @torch.no_grad()
+    def pipeline_eval(self, model, batch: dict) -> dict:
+        """Loss of one batch without gradients (validation): one forward through the stages, piece by piece."""
+        from astrai_b200 import ops
+
+        stage = self._pipe.stage
+        ids, targets, chunks, kwargs, weights = self._pieces(batch)
+        weights = weights or [1.0 / chunks] * chunks
+        total = None
+        shape = (ids.shape[0] // chunks, ids.shape[1])
+        for i, (x, t) in enumerate(zip(ids.chunk(chunks), targets.chunk(chunks))):
+            logits = self._pipe.forward_only(x if stage.first else None, micro_shape=shape, **kwargs[i])
+            if stage.last:
+                piece = ops.cross_entropy(logits, t, label_smoothing=self.label_smoothing) * weights[i]
+                total = piece if total is None else total + piece
+        return self._shared_loss(total, ids.device)
 
     # -- state ------------------------------------------------------------------------------------------------------------------
     def _full_state_dict(self, model):

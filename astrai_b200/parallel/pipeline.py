@@ -69,27 +69,36 @@ class PipelineStage(nn.Module):
         self.norm = model.norm if self.last else None
         self.lm_head = model.lm_head if self.last else None
         self.hidden_size = model.config.hidden_size
+        # the whole model reports the MEAN of its layers' router losses: every stage contributes its layers' share of it
+        n_routed = sum(1 for layer in model.layers if hasattr(getattr(layer, "mlp", None), "router"))
+        self.aux_scale = 1.0 / max(n_routed, 1)
 
     def owned_keys(self, model: nn.Module) -> List[str]:
         """State-dict keys of the full model that live on this stage."""
         mine = {id(p) for p in self.parameters()}
         return [k for k, v in model.state_dict(keep_vars=True).items() if id(v) in mine]
 
-    def forward(self, x: Tensor, position_ids: Optional[Tensor] = None):
-        """First stage: ``x`` are token ids ``[B, S]``; later stages: hidden states ``[B, S, H]``.
-        Returns hidden states, or logits on the last stage, plus the summed router auxiliary loss (or ``None``)."""
+    def forward(self, x: Tensor, position_ids: Optional[Tensor] = None, attention=None):
+        """First stage: ``x`` are token ids ``[B, S]``; later stages: hidden states ``[B, S, H]``.  ``attention`` is what
+        the whole model takes as ``input_mask`` (a padding / dense mask or the run boundaries of packed documents);
+        without it attention is causal.  Returns hidden states, or logits on the last stage, plus this stage's share of
+        the model's router auxiliary loss (its layers' losses over the model's number of routed layers; ``None`` if it
+        has none): summed over the stages that is the mean the whole model reports."""
+        from astrai_b200.models.lm import expand_mask
+
         if self.first:
             x = self.embed_tokens(x)
         rotary = self.rotary_embedding(x, position_ids)
+        mask = expand_mask(attention)
         aux = None
         for layer in self.layers:
-            out = layer(x, rotary, None, None, True, None)
+            out = layer(x, rotary, mask, None, mask is None, None)
             x = out["hidden_states"]
             if out.get("aux_loss") is not None:
                 aux = out["aux_loss"] if aux is None else aux + out["aux_loss"]
         if self.last:
             x = self.lm_head(self.norm(x))
-        return x, aux
+        return x, (aux * self.aux_scale if aux is not None else None)
 
 
 def _default_loss(logits: Tensor, targets: Tensor) -> Tensor:
@@ -122,11 +131,24 @@ class PipelineParallel:
 
     def train_step(self, input_ids: Optional[Tensor], targets: Optional[Tensor], n_micro: int,
                    micro_shape: Optional[Tuple[int, int]] = None, dtype: Optional[torch.dtype] = None,
-                   loss_scale: float = 1.0) -> Optional[Tensor]:
-        """One accumulation window (gradients are those of ``loss_scale`` times the mean loss over the window).  ``input_ids`` ``[B, S]`` is needed on the first stage, ``targets`` ``[B, S]`` on the
-        last; ``B`` must be a multiple of ``n_micro``.  Stages in the middle pass ``micro_shape = (B / n_micro, S)``.
-        Returns the mean loss on the last stage, ``None`` elsewhere.  Gradients are left in ``.grad``."""
+                   loss_scale: float = 1.0, micro_kwargs: Optional[Sequence[dict]] = None,
+                   weights: Optional[Sequence[float]] = None) -> Optional[Tensor]:
+        """One accumulation window (gradients are those of ``loss_scale`` times the window's loss).  ``input_ids``
+        ``[B, S]`` is needed on the first stage, ``targets`` ``[B, S]`` on the last; ``B`` must be a multiple of
+        ``n_micro``.  Stages in the middle pass ``micro_shape = (B / n_micro, S)``.
+
+        ``micro_kwargs[i]`` are keyword arguments of the stage's forward for piece ``i`` (``position_ids``,
+        ``attention``), the same on every stage.  ``weights[i]`` is the share of piece ``i`` in the window's loss
+        (default ``1 / n_micro`` each: the mean of the pieces' means); an objective that averages over a varying number
+        of tokens per piece passes that piece's share of the tokens, which makes the window's loss the mean over all
+        its tokens.  Returns the window's loss on the last stage, ``None`` elsewhere.  Gradients are left in ``.grad``."""
         st = self.stage
+        if weights is None:
+            weights = [1.0 / n_micro] * n_micro
+        if micro_kwargs is None:
+            micro_kwargs = [{}] * n_micro
+        if len(weights) != n_micro or len(micro_kwargs) != n_micro:
+            raise ValueError(f"{n_micro} pieces need {n_micro} weights and keyword sets")
         dev = next(st.parameters()).device
         dtype = dtype or next(st.parameters()).dtype
         if st.first:
@@ -152,13 +174,13 @@ class PipelineParallel:
             return x.requires_grad_(True)
 
         def forward(i, x):
-            y, aux = st(x)
+            y, aux = st(x, **micro_kwargs[i])
             if st.last:
                 loss = self.loss_fn(y, micro_tg[i])
-                losses.append(loss.detach())
-                if aux is not None and self.aux_loss_coef:
-                    loss = loss + self.aux_loss_coef * aux
-                y = loss * (loss_scale / n_micro)
+                losses.append(loss.detach() * weights[i])
+                y = loss * (loss_scale * weights[i])
+                if aux is not None and self.aux_loss_coef:  # the auxiliary loss is a plain mean over the pieces
+                    y = y + aux * (self.aux_loss_coef * loss_scale / n_micro)
             elif aux is not None and self.aux_loss_coef:  # the stage's own share of the auxiliary loss
                 (self.aux_loss_coef * aux * (loss_scale / n_micro)).backward(retain_graph=True)
             live.append((x, y))
@@ -205,12 +227,13 @@ class PipelineParallel:
             gx = backward(gy)
             if not st.first:
                 self._exchange([(gx, self._prev)], [])
-        return torch.stack(losses).mean() if st.last else None
+        return torch.stack(losses).sum() if st.last else None
 
     @torch.no_grad()
     def forward_only(self, input_ids: Optional[Tensor], micro_shape: Optional[Tuple[int, int]] = None,
-                     dtype: Optional[torch.dtype] = None) -> Optional[Tensor]:
-        """Evaluation pass of one batch through the stages; logits on the last stage, ``None`` elsewhere."""
+                     dtype: Optional[torch.dtype] = None, **stage_kwargs) -> Optional[Tensor]:
+        """Evaluation pass of one batch through the stages; logits on the last stage, ``None`` elsewhere.
+        ``stage_kwargs`` (``position_ids``, ``attention``) go to every stage's forward."""
         st = self.stage
         dev = next(st.parameters()).device
         dtype = dtype or next(st.parameters()).dtype
@@ -219,7 +242,7 @@ class PipelineParallel:
         else:
             x = torch.empty((micro_shape[0], micro_shape[1], st.hidden_size), dtype=dtype, device=dev)
             self._exchange([], [(x, self._prev)])
-        y, _ = st(x)
+        y, _ = st(x, **stage_kwargs)
         if st.last:
             return y
         self._exchange([(y, self._next)], [])

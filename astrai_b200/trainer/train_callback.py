@@ -269,9 +269,11 @@ class MetricCallback(TrainCallback):
     def _validate(self, context) -> float:
         context.model.eval()
         total, batches = 0.0, 0
+        staged = getattr(getattr(context, "executor", None), "pipeline_eval", None)  # pipeline stages compute the loss between them
         with torch.no_grad():
             for batch in context.val_dataloader:
-                total += float(context.strategy(batch)["loss"].item())
+                out = staged(context.model, batch) if staged is not None else context.strategy(batch)
+                total += float(out["loss"].item())
                 batches += 1
         context.model.train()
         if context.world_size > 1 and dist.is_initialized():

@@ -65,6 +65,31 @@ def test_pipeline_parallel_mode_matches_single_process(tmp_path, dense_ref, npro
     assert run["optimizer_stages"] == 2  # the checkpoint carries the optimizer state of both stages
 
 
+@pytest.fixture(scope="module")
+def sft_ref(tmp_path_factory):
+    return _run(tmp_path_factory.mktemp("refsft"), "refsft", 1, "--mode", "none", "--strategy", "sft", "--val", "--label_smoothing", "0.1")
+
+
+@pytest.mark.parametrize("extra", [[], ["--chunks", "4"]])
+def test_pipeline_parallel_supervised_objective_and_validation(tmp_path, sft_ref, extra):
+    """Packed documents with position ids and an uneven loss mask, label smoothing from the strategy's options, a held-out
+    quarter scored after training: the pipeline's losses, norms, weights and validation loss are the single process's,
+    whatever the number of pieces."""
+    run = _run(tmp_path, "ppsft", 2, "--mode", "pp", "--strategy", "sft", "--val", "--label_smoothing", "0.1", *extra)
+    _same(run, sft_ref)
+    assert len(run["val"]) == 1 and run["val"] == pytest.approx(sft_ref["val"], abs=2e-5)
+
+
+def test_pipeline_mode_is_refused_for_objectives_with_reference_models(tmp_path):
+    from astrai_b200.config import TrainConfig
+    from astrai_b200.trainer.train_context import TrainContextBuilder
+
+    cfg = TrainConfig(model_fn=lambda: None, strategy="dpo", dataset=[0], optimizer_fn=lambda m: None, ckpt_dir=str(tmp_path),
+                      parallel_mode="pp", pp_size=2, nprocs=2, device_type="cpu", backend="gloo")
+    with pytest.raises(ValueError, match="'seq' and 'sft'"):
+        TrainContextBuilder(cfg)._executor()
+
+
 def test_pipeline_executor_hands_each_stage_its_own_optimizer_state_and_refuses_other_objectives():
     from astrai_b200.parallel import ExecutorFactory
     from astrai_b200.parallel.mesh import ParallelMesh
@@ -77,7 +102,7 @@ def test_pipeline_executor_hands_each_stage_its_own_optimizer_state_and_refuses_
     assert ex.unpack_optimizer_state({"plain": True}) == {"plain": True}  # a checkpoint of another mode passes through
     with pytest.raises(RuntimeError, match="3 pipeline stages"):
         ex.unpack_optimizer_state({"pipeline_stages": [1, 2, 3]})
-    with pytest.raises(NotImplementedError, match="next-token"):
+    with pytest.raises(NotImplementedError, match="token cross-entropy"):
         ex.pipeline_step(None, {"chosen": torch.zeros(1, 2), "rejected": torch.zeros(1, 2)}, 1.0)
 
 

@@ -26,9 +26,23 @@ class Tokens(torch.utils.data.Dataset):
         return {"input_ids": row[:-1], "target_ids": row[1:]}
 
 
+class PackedChats(Tokens):
+    """Rows of two or three packed documents (position ids restart) with an uneven share of trained tokens per row."""
+
+    def __getitem__(self, i):
+        row = self.data[i]
+        seq = row.numel() - 1
+        g = torch.Generator().manual_seed(1000 + i)
+        cuts = sorted(torch.randperm(seq - 1, generator=g)[: 1 + i % 2].add(1).tolist())
+        pos = torch.cat([torch.arange(b - a) for a, b in zip([0] + cuts, cuts + [seq])])
+        keep = torch.rand(seq, generator=g) < (0.15 + 0.2 * (i % 4))
+        keep[0] = True
+        return {"input_ids": row[:-1], "target_ids": row[1:], "position_ids": pos, "loss_mask": keep}
+
+
 class Record:
     def __init__(self):
-        self.losses, self.norms = [], []
+        self.losses, self.norms, self.val = [], [], []
 
     def on_optimizer_step(self, context):
         import torch.distributed as dist
@@ -39,6 +53,12 @@ class Record:
             loss /= dist.get_world_size()
         self.losses.append(float(loss))
         self.norms.append(float(context.grad_norm) if context.grad_norm is not None else None)
+
+    def on_train_end(self, context):
+        if getattr(context, "val_dataloader", None) is not None:
+            from astrai_b200.trainer.train_callback import MetricCallback
+
+            self.val.append(MetricCallback(context.config.ckpt_dir, 10**6, ["loss"])._validate(context))
 
 
 def main():
@@ -58,6 +78,9 @@ def main():
     ap.add_argument("--lr", type=float, default=1e-2)
     ap.add_argument("--chunks", type=int, default=0)
     ap.add_argument("--layers", type=int, default=2)
+    ap.add_argument("--strategy", default="seq", choices=["seq", "sft"])
+    ap.add_argument("--val", action="store_true", help="hold a quarter of the data out and report its loss after training")
+    ap.add_argument("--label_smoothing", type=float, default=0.0)
     args = ap.parse_args()
 
     from astrai_b200.config import AutoRegressiveLMConfig, TrainConfig
@@ -88,6 +111,9 @@ def main():
     global_batch = args.bpd * 2
     bpd = global_batch // dw
     n = global_batch * accum * args.steps
+    data_cls = PackedChats if args.strategy == "sft" else Tokens
+    if args.val:
+        n = n * 4 // 3  # the held-out quarter comes off the end
     exkw = {"comm": args.comm} if args.mode in ("tp", "cp", "ep") else {}
     if args.mode == "pp" and args.chunks:
         exkw["chunks"] = args.chunks
@@ -96,7 +122,9 @@ def main():
         exkw["max_tokens_per_rank"] = bpd * args.seq // max(world // max(dw, 1), 1) * 2
     if args.mode == "ep":
         exkw["tokens_per_rank"] = bpd * args.seq
-    tc = TrainConfig(model_fn=model_fn, strategy="seq", dataset=Tokens(n, args.seq, 256),
+    tc = TrainConfig(model_fn=model_fn, strategy=args.strategy, dataset=data_cls(n, args.seq, 256),
+                     val_split=0.25 if args.val else None, val_step=10**6,
+                     strategy_kwargs={"label_smoothing": args.label_smoothing} if args.label_smoothing else {},
                      optimizer_fn=lambda m: FusedAdamW(m.parameters(), lr=args.lr, weight_decay=0.0),
                      batch_per_device=bpd, grad_accum_steps=accum, ckpt_dir=args.ckpt, ckpt_interval=10**6,
                      device_type="cuda" if cuda else "cpu", backend="nccl" if cuda else "gloo", nprocs=world,
@@ -128,7 +156,7 @@ def main():
         sums = {k: float(v.float().abs().sum()) for k, v in sd.items()}
         shapes = {k: list(v.shape) for k, v in sd.items()}
         with open(args.out, "w") as fh:
-            json.dump({"losses": rec.losses, "norms": rec.norms, "sums": sums, "shapes": shapes, "optimizer_stages": stages}, fh)
+            json.dump({"losses": rec.losses, "norms": rec.norms, "val": rec.val, "sums": sums, "shapes": shapes, "optimizer_stages": stages}, fh)
 
 
 if __name__ == "__main__":

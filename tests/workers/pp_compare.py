@@ -17,6 +17,7 @@ def main():
     ap.add_argument("--out", required=True)
     ap.add_argument("--micro", type=int, default=4)
     ap.add_argument("--moe", action="store_true")
+    ap.add_argument("--sft", action="store_true", help="packed documents with a loss mask: the loss is a mean over the trained tokens")
     args = ap.parse_args()
     dist.init_process_group("gloo")
     rank, world = dist.get_rank(), dist.get_world_size()
@@ -35,18 +36,52 @@ def main():
     targets = torch.randint(0, 97, (8, 16))
     coef = 0.01 if args.moe else 0.0
 
-    # whole model, same micro-batching (the loss is a mean of per-micro-batch means)
-    total = 0.0
-    for xi, ti in zip(ids.chunk(args.micro), targets.chunk(args.micro)):
-        out = ref(xi)
-        loss = torch.nn.functional.cross_entropy(out["logits"].reshape(-1, 97).float(), ti.reshape(-1))
-        total += loss.item() / args.micro
-        if args.moe:
-            loss = loss + coef * out["aux_loss"] * len(ref.layers)  # the model reports the mean over layers, the stages sum
-        (loss / args.micro).backward()
+    kwargs = weights = None
+    if args.sft:
+        from astrai_b200.trainer.strategy import doc_attention
 
-    pp = PipelineParallel(model, aux_loss_coef=coef)
-    loss = pp.train_step(ids if rank == 0 else None, targets if rank == world - 1 else None, args.micro, micro_shape=(8 // args.micro, 16))
+        # rows of two or three packed documents of different lengths; about a third of the tokens are trained, unevenly
+        g = torch.Generator().manual_seed(5)
+        cuts = [sorted(torch.randperm(15, generator=g)[: 1 + r % 2].add(1).tolist()) for r in range(8)]
+        pos = torch.stack([torch.cat([torch.arange(b - a) for a, b in zip([0] + c, c + [16])]) for c in cuts])
+        keep = torch.rand(8, 16, generator=g) < torch.linspace(0.1, 0.7, 8)[:, None]
+        targets = targets.masked_fill(~keep, -100)
+        # the whole batch's mean over its trained tokens, accumulated piece by piece (the router loss is not a sum over
+        # tokens, so the whole model must see the same pieces as the stages for its gradients to be comparable)
+        n_trained = int(keep.sum())
+        total = 0.0
+        for xi, ti, pi in zip(ids.chunk(args.micro), targets.chunk(args.micro), pos.chunk(args.micro)):
+            out = ref(xi, input_mask=doc_attention(pi), position_ids=pi)
+            loss = torch.nn.functional.cross_entropy(out["logits"].reshape(-1, 97).float(), ti.reshape(-1), ignore_index=-100,
+                                                     reduction="sum") / n_trained
+            total += loss.item()
+            if args.moe:
+                loss = loss + coef * out["aux_loss"] / args.micro
+            loss.backward()
+        if not args.moe:  # and in one piece: the same number
+            whole = ref(ids, input_mask=doc_attention(pos), position_ids=pos)["logits"]
+            one = torch.nn.functional.cross_entropy(whole.reshape(-1, 97).float(), targets.reshape(-1), ignore_index=-100)
+            assert abs(one.item() - total) < 1e-5, (one.item(), total)
+        kwargs = [{"position_ids": p, "attention": doc_attention(p)} for p in pos.chunk(args.micro)]
+        counts = keep.reshape(args.micro, -1).sum(1).double()
+        weights = (counts / counts.sum()).tolist()
+    else:
+        # whole model, same micro-batching (the loss is a mean of per-micro-batch means)
+        total = 0.0
+        for xi, ti in zip(ids.chunk(args.micro), targets.chunk(args.micro)):
+            out = ref(xi)
+            loss = torch.nn.functional.cross_entropy(out["logits"].reshape(-1, 97).float(), ti.reshape(-1))
+            total += loss.item() / args.micro
+            if args.moe:
+                loss = loss + coef * out["aux_loss"]  # the stages' shares add up to the model's mean over its layers
+            (loss / args.micro).backward()
+
+    def loss_fn(logits, t):
+        return torch.nn.functional.cross_entropy(logits.reshape(-1, logits.size(-1)).float(), t.reshape(-1), ignore_index=-100)
+
+    pp = PipelineParallel(model, aux_loss_coef=coef, loss_fn=loss_fn)
+    loss = pp.train_step(ids if rank == 0 else None, targets if rank == world - 1 else None, args.micro, micro_shape=(8 // args.micro, 16),
+                         micro_kwargs=kwargs, weights=weights)
     ref_grads = dict(ref.named_parameters())
     worst = 0.0
     for key in pp.stage.owned_keys(model):
