@@ -134,19 +134,27 @@ class InferenceEngine:
 
     def generate_async(self, prompt: str, max_tokens: Optional[int] = None, temperature: float = 1.0, top_p: float = 1.0,
                        top_k: int = 50, frequency_penalty: float = 0.0, rep_window: int = 64) -> AsyncGenerator[str, None]:
-        gen = self._generate([prompt], False, True, max_tokens, temperature, top_p, top_k, frequency_penalty, rep_window)
+        """Pieces of the answer as an async generator.  Closing it early (``aclose()``, or the consuming coroutine being
+        cancelled: a stop sequence matched, the client went away) takes the request out of the scheduler, so that an
+        answer nobody reads does not keep a batch slot until ``max_tokens``."""
+        result, task_ids = self._submit([prompt], max_tokens, temperature, top_p, top_k, frequency_penalty, rep_window)
+        gen = self._stream(result, task_ids, False)
 
         async def agen():
             loop = asyncio.get_event_loop()
-            while True:
-                piece = await loop.run_in_executor(None, next, gen, None)
-                if piece is None:
-                    return
-                yield piece
+            try:
+                while True:
+                    piece = await loop.run_in_executor(None, next, gen, None)
+                    if piece is None:
+                        return
+                    yield piece
+            finally:
+                # not gen.close(): a worker thread may be inside next(gen) right now; ending the streams lets it return
+                self._cancel(result, task_ids)
 
         return agen()
 
-    def _generate(self, prompts, batch, stream, max_tokens, temperature, top_p, top_k, frequency_penalty, rep_window):
+    def _submit(self, prompts, max_tokens, temperature, top_p, top_k, frequency_penalty, rep_window):
         result = GenerateResult(count=len(prompts))
         task_ids = [
             self.scheduler.add_task(prompt=p, max_tokens=max_tokens, temperature=temperature, top_p=top_p, top_k=top_k,
@@ -154,18 +162,19 @@ class InferenceEngine:
                                     stream_callback=lambda tok, i=i: result.append(tok, i))
             for i, p in enumerate(prompts)
         ]
-        if not stream:
-            try:
-                result.wait_completion()
-            finally:
-                for tid in task_ids:
-                    self.scheduler.remove_task(tid)
-            out = result.get_results()
-            return out if batch else out[0]
+        return result, task_ids
 
-        def gen():
-            open_streams = len(prompts)
-            closed = [False] * len(prompts)
+    def _cancel(self, result: GenerateResult, task_ids: List[str]):
+        """Take the requests out (finished ones are gone already: nothing happens) and end their streams."""
+        for tid in task_ids:
+            self.scheduler.remove_task(tid)
+        for i in range(len(task_ids)):
+            result.append(STOP, i)
+
+    def _stream(self, result: GenerateResult, task_ids: List[str], batch: bool):
+        open_streams = len(task_ids)
+        closed = [False] * len(task_ids)
+        try:
             while open_streams > 0:
                 for idx, tok in result.pop_all():
                     if tok is STOP:
@@ -176,8 +185,22 @@ class InferenceEngine:
                         yield (idx, tok) if batch else tok
                 if open_streams > 0:
                     result.wait(timeout=0.05)
+        finally:  # a consumer that stops reading (break, close(), garbage collection) gives the batch slots back
+            for tid, done in zip(task_ids, closed):
+                if not done:
+                    self.scheduler.remove_task(tid)
 
-        return gen()
+    def _generate(self, prompts, batch, stream, max_tokens, temperature, top_p, top_k, frequency_penalty, rep_window):
+        result, task_ids = self._submit(prompts, max_tokens, temperature, top_p, top_k, frequency_penalty, rep_window)
+        if stream:
+            return self._stream(result, task_ids, batch)
+        try:
+            result.wait_completion()
+        finally:
+            for tid in task_ids:
+                self.scheduler.remove_task(tid)
+        out = result.get_results()
+        return out if batch else out[0]
 
     def get_stats(self) -> Dict[str, Any]:
         return self.scheduler.get_stats()

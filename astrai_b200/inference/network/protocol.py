@@ -7,6 +7,7 @@ the accumulated text and the matching piece is not emitted; a stream always ends
 from __future__ import annotations
 
 import json
+from contextlib import aclosing
 from dataclasses import dataclass
 from typing import Any, AsyncGenerator, Dict, List, Optional, Tuple, Union
 
@@ -88,17 +89,20 @@ class ProtocolHandler:
         body = sent = ""
         matched = None
         ids: List[int] = []
-        async for piece in agen:
-            body += piece
-            new_ids = self.engine.tokenizer.encode(piece)
-            ids.extend(new_ids)
-            matched = checker.check(body)
-            if matched:
-                break
-            ctx.completion_tokens += 1
-            for ev in self.builder.format_chunk(piece, body=body, current_token_ids=ids, delta_token_ids=new_ids):
-                yield ev
-            sent += piece
+        # closing the generator (a stop sequence matched, or the client went away and this coroutine was cancelled) takes
+        # the request out of the scheduler
+        async with aclosing(agen) as pieces:
+            async for piece in pieces:
+                body += piece
+                new_ids = self.engine.tokenizer.encode(piece)
+                ids.extend(new_ids)
+                matched = checker.check(body)
+                if matched:
+                    break
+                ctx.completion_tokens += 1
+                for ev in self.builder.format_chunk(piece, body=body, current_token_ids=ids, delta_token_ids=new_ids):
+                    yield ev
+                sent += piece
         for ev in self.builder.format_stream_end(ctx, StopInfo(matched, body, sent)):
             yield ev
         yield sse_done()
@@ -106,10 +110,11 @@ class ProtocolHandler:
     async def _collect(self, agen: AsyncGenerator, ctx: GenContext, stops: List[str]) -> Dict[str, Any]:
         checker = StopChecker(stops)
         body, matched = "", None
-        async for piece in agen:
-            body += piece
-            matched = checker.check(body)
-            if matched:
-                break
-            ctx.completion_tokens += 1
+        async with aclosing(agen) as pieces:
+            async for piece in pieces:
+                body += piece
+                matched = checker.check(body)
+                if matched:
+                    break
+                ctx.completion_tokens += 1
         return self.builder.format_response(ctx, body, StopInfo(matched, body))

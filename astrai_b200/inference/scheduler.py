@@ -95,12 +95,32 @@ class InferenceScheduler:
         return task.task_id
 
     def remove_task(self, task_id: str):
+        """Take a request out, wherever it is.  Its callback hears nothing more from now on; while the scheduling loop runs,
+        the request itself leaves at the top of the loop's next iteration, on the loop's thread (its cache pages may be in
+        use by the step in flight, and the page tables have one writer)."""
         if self._control is not None:
             with self._stage_lock:
                 self._cancelled.append(task_id)
             return
+        running = self._loop_thread is not None and self._loop_thread.is_alive() and threading.current_thread() is not self._loop_thread
+        if not running:
+            self._drop(task_id)
+        elif self._task_mgr.silence(task_id):
+            with self._stage_lock:
+                self._cancelled.append(task_id)
+            self._task_mgr.wake()
+
+    def _drop(self, task_id: str):
         for task in self._task_mgr.remove_task(task_id):
             self._task_cache.task_free(task.task_id)
+
+    def _apply_cancellations(self):
+        if not self._cancelled:
+            return
+        with self._stage_lock:
+            gone, self._cancelled = self._cancelled, []
+        for task_id in gone:
+            self._drop(task_id)
 
     def _share_requests(self) -> bool:
         """Tensor-parallel serving: bring the queues of every rank up to date with what reached the first rank since the
@@ -115,8 +135,7 @@ class InferenceScheduler:
             self._task_mgr.enqueue(Task(spec["task_id"], list(spec["prompt_ids"]), spec["max_tokens"], spec["temperature"], spec["top_p"],
                                         spec["top_k"], spec["frequency_penalty"], spec["rep_window"]))
         for task_id in payload["cancelled"]:
-            for task in self._task_mgr.remove_task(task_id):
-                self._task_cache.task_free(task.task_id)
+            self._drop(task_id)
         return not payload["stop"]
 
     def follow(self):
@@ -253,6 +272,8 @@ class InferenceScheduler:
                         break
                 elif self._stop_event.is_set():
                     break
+                else:
+                    self._apply_cancellations()
                 self._retire(stop_ids)
                 self._refill()
                 active = self._task_mgr.get_active_tasks()

@@ -136,6 +136,13 @@ class TaskManager:
         self._task_event.clear()
         self._task_event.wait(timeout=timeout)
 
+    def silence(self, task_id: str) -> bool:
+        """Stop delivering to the task's callback; True when the task is still queued or running (so that removing it is
+        worth a trip through the scheduling loop)."""
+        with self._lock:
+            self._callbacks.pop(task_id, None)
+            return any(t.task_id == task_id for t in self.active_tasks) or any(t.task_id == task_id for t in self.waiting_queue)
+
     def remove_task(self, task_id: str) -> List[Task]:
         with self._lock:
             gone = [t for t in self.active_tasks if t.task_id == task_id]

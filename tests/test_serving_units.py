@@ -485,3 +485,160 @@ def test_create_engine_takes_the_serve_cli_options(tmp_path, served):
             app.state.engine = None
     finally:
         eng.shutdown()
+
+
+# ------------------------------------------------------------------------------------- abandoned answers are cancelled
+def _wait_until(cond, timeout=20.0):
+    end = time.time() + timeout
+    while time.time() < end:
+        if cond():
+            return True
+        time.sleep(0.01)
+    return False
+
+
+def _slow_down(scheduler, seconds=0.01):
+    """Make every scheduling step take a while, so that a test can act while an answer is still being generated."""
+    step = scheduler._step
+
+    def slow(*args, **kwargs):
+        time.sleep(seconds)
+        return step(*args, **kwargs)
+
+    scheduler._step = slow
+
+
+def test_remove_task_during_generation_goes_through_the_loop_and_frees_the_slot(served):
+    s = _sched(served, max_batch_size=2)
+    _slow_down(s)
+    s.start()
+    try:
+        heard = []
+        tid = s.add_task([60, 61, 62], max_tokens=50, temperature=0.0, stream_callback=heard.append)
+        assert _wait_until(lambda: len(heard) >= 2)
+        s.remove_task(tid)
+        count = len(heard)
+        assert _wait_until(lambda: s.get_stats()["active_tasks"] == 0)
+        time.sleep(0.1)
+        assert len(heard) == count  # silenced at once: nothing after the call returned, not even the end marker
+        assert s._cancelled == []
+        s.remove_task(tid)  # unknown by now: nothing is staged
+        s.remove_task("never-existed")
+        assert s._cancelled == []
+        # the freed slot and pages serve the next requests
+        done = threading.Event()
+        s.add_task([60, 61, 62], max_tokens=3, temperature=0.0, stream_callback=lambda p: done.set() if not isinstance(p, str) else None)
+        assert done.wait(timeout=30)
+    finally:
+        s.stop()
+
+
+def test_waiting_request_can_be_cancelled_before_it_runs(served):
+    s = _sched(served, max_batch_size=1)
+    _slow_down(s)
+    s.start()
+    try:
+        first, second = [], []
+        a = s.add_task([60, 61, 62], max_tokens=40, temperature=0.0, stream_callback=first.append)
+        b = s.add_task([70, 71], max_tokens=40, temperature=0.0, stream_callback=second.append)
+        assert _wait_until(lambda: len(first) >= 2)
+        s.remove_task(b)
+        assert _wait_until(lambda: s.get_stats()["waiting_queue"] == 0)
+        s.remove_task(a)
+        assert _wait_until(lambda: s.get_stats()["active_tasks"] == 0)
+        assert second == []
+    finally:
+        s.stop()
+
+
+def test_abandoned_stream_gives_its_batch_slot_back(served):
+    from astrai_b200.inference import InferenceEngine
+
+    model, tok = served
+    engine = InferenceEngine(model, tok, max_batch_size=2, max_seq_len=96, enable_cuda_graph=False)
+    _slow_down(engine.scheduler)
+    try:
+        stream = engine.generate("hello", stream=True, max_tokens=80, temperature=0.0)
+        assert isinstance(next(stream), str)
+        assert engine.get_stats()["active_tasks"] == 1
+        stream.close()  # the consumer walks away
+        assert _wait_until(lambda: engine.get_stats()["active_tasks"] == 0)
+        # a stream that is read to its end removes nothing twice and leaves nothing behind
+        assert "".join(engine.generate("hello", stream=True, max_tokens=4, temperature=0.0)) == engine.generate("hello", max_tokens=4, temperature=0.0)
+        assert engine.get_stats()["active_tasks"] == 0 and engine.scheduler._cancelled == []
+    finally:
+        engine.shutdown()
+
+
+def test_closing_the_async_generator_cancels_the_request(served):
+    import asyncio
+
+    from astrai_b200.inference import InferenceEngine
+
+    model, tok = served
+    engine = InferenceEngine(model, tok, max_batch_size=2, max_seq_len=96, enable_cuda_graph=False)
+    _slow_down(engine.scheduler)
+
+    async def read_two_then_leave():
+        agen = engine.generate_async("hello", max_tokens=80, temperature=0.0)
+        got = []
+        async for piece in agen:
+            got.append(piece)
+            if len(got) == 2:
+                break
+        await agen.aclose()
+        return got
+
+    async def cancelled_in_mid_read():
+        agen = engine.generate_async("hello there", max_tokens=80, temperature=0.0)
+
+        async def reader():
+            async for _ in agen:
+                pass
+
+        task = asyncio.ensure_future(reader())
+        await asyncio.sleep(0.2)
+        task.cancel()
+        with pytest.raises(asyncio.CancelledError):
+            await task
+
+    try:
+        assert len(asyncio.run(read_two_then_leave())) == 2
+        assert _wait_until(lambda: engine.get_stats()["active_tasks"] == 0)
+        asyncio.run(cancelled_in_mid_read())
+        assert _wait_until(lambda: engine.get_stats()["active_tasks"] == 0)
+        assert engine.generate("hello", max_tokens=3, temperature=0.0) is not None  # the engine still serves
+    finally:
+        engine.shutdown()
+
+
+def test_http_stop_sequence_ends_the_generation_not_only_the_answer(served):
+    """A matched stop sequence answers the client at once; the request must not keep decoding up to max_tokens."""
+    from fastapi.testclient import TestClient
+
+    from astrai_b200.inference import InferenceEngine
+    from astrai_b200.inference.network import app as app_mod
+
+    model, tok = served
+    engine = InferenceEngine(model, tok, max_batch_size=2, max_seq_len=120, enable_cuda_graph=False)
+    _slow_down(engine.scheduler, 0.005)
+    app = app_mod.get_app()
+    old = app.state.engine, app.state.server_config
+    app.state.engine, app.state.server_config = engine, {"_test": True}
+    try:
+        client = TestClient(app)
+        full = client.post("/v1/chat/completions", json={"messages": [{"role": "user", "content": "hi"}], "max_tokens": 12, "temperature": 0.0}).json()
+        text = full["choices"][0]["message"]["content"]
+        assert len(text) >= 4
+        stop = text[2:4]
+        before = engine.get_stats()["total_tokens"]
+        cut = client.post("/v1/chat/completions", json={"messages": [{"role": "user", "content": "hi"}], "max_tokens": 100, "temperature": 0.0,
+                                                        "stop": [stop]}).json()
+        # this wire format keeps the piece that completed the stop sequence in the answer (as the reference does)
+        assert cut["choices"][0]["finish_reason"] == "stop" and cut["choices"][0]["message"]["content"] == text[:4]
+        assert cut["usage"]["completion_tokens"] < 12
+        assert _wait_until(lambda: engine.get_stats()["active_tasks"] == 0, timeout=0.3)  # 100 more steps would take half a second
+        assert engine.get_stats()["total_tokens"] - before < 100
+    finally:
+        app.state.engine, app.state.server_config = old
+        engine.shutdown()
