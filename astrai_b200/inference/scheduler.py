@@ -272,9 +272,9 @@ class InferenceScheduler:
                         break
                 elif self._stop_event.is_set():
                     break
-                else:
+                self._retire(stop_ids)  # first: a request that has just finished is counted and its pages are indexed
+                if self._control is None:
                     self._apply_cancellations()
-                self._retire(stop_ids)
                 self._refill()
                 active = self._task_mgr.get_active_tasks()
                 if not active:

@@ -642,3 +642,21 @@ def test_http_stop_sequence_ends_the_generation_not_only_the_answer(served):
     finally:
         app.state.engine, app.state.server_config = old
         engine.shutdown()
+
+
+def test_finished_requests_are_counted_even_when_the_caller_removes_them_at_once(served):
+    """``generate`` removes its requests as soon as the last piece arrived, which is before the loop has retired them:
+    the removal must not swallow the token count or the prefix index entry of a request that finished."""
+    from astrai_b200.inference import InferenceEngine
+
+    model, tok = served
+    engine = InferenceEngine(model, tok, max_batch_size=2, max_seq_len=96, enable_cuda_graph=False)
+    try:
+        for n in range(1, 6):
+            engine.generate("count me", max_tokens=4, temperature=0.0)
+            assert _wait_until(lambda: engine.get_stats()["active_tasks"] == 0)
+            stats = engine.get_stats()
+            assert stats["total_tasks"] == n and 0 < stats["total_tokens"] <= 4 * n
+            assert stats["total_tokens"] >= n
+    finally:
+        engine.shutdown()
