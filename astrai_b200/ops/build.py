@@ -120,9 +120,21 @@ def build_standalone(which: str = "attn_check") -> Path:
     return exe
 
 
-if __name__ == "__main__":
-    if "--standalone" in sys.argv:
+def main(argv=None) -> int:
+    """``python -m astrai_b200.ops.build [-v] [--force] [--standalone]``: build the extension (or the torch-free test
+    programs) in the source tree and print what was written."""
+    argv = sys.argv[1:] if argv is None else list(argv)
+    unknown = [a for a in argv if a not in ("-v", "--force", "--standalone")]
+    if unknown:
+        print(f"unknown option(s): {' '.join(unknown)}\nusage: python -m astrai_b200.ops.build [-v] [--force] [--standalone]", file=sys.stderr)
+        return 2
+    if "--standalone" in argv:
         for name in STANDALONE:
             print(build_standalone(name))
     else:
-        print(build(verbose="-v" in sys.argv, force="--force" in sys.argv))
+        print(build(verbose="-v" in argv, force="--force" in argv))
+    return 0
+
+
+if __name__ == "__main__":
+    raise SystemExit(main())
