@@ -14,6 +14,7 @@ from astrai_b200.ops.functional import (
     gemm,
     linear,
     linear_cross_entropy,
+    loss_denominator,
     linear_token_logprobs,
     qkv_rope,
     rms_norm,
@@ -25,6 +26,6 @@ from astrai_b200.ops.functional import (
 
 __all__ = [
     "ATTN_BACKEND", "attn_backend", "get_backend", "DelayedScaling", "DynamicScaling", "FP8Format", "fp8", "fp8_autocast", "adamw_", "add_rms_norm", "assume_loss_grad", "clip_coef", "cross_entropy", "dense_attention", "embedding", "gemm", "linear",
-    "linear_cross_entropy", "linear_token_logprobs", "native", "qkv_rope", "reference", "rms_norm", "rotary",
+    "linear_cross_entropy", "linear_token_logprobs", "loss_denominator", "native", "qkv_rope", "reference", "rms_norm", "rotary",
     "sumsq", "swiglu", "swiglu_fused",
 ]

@@ -382,7 +382,7 @@ def embedding(ids: Tensor, table: Tensor) -> Tensor:
 
 
 # --------------------------------------------------------------------------- losses
-_LOSS_GRAD = {"scale": None}
+_LOSS_GRAD = {"scale": None, "denominator": None}
 
 
 @contextlib.contextmanager
@@ -401,6 +401,27 @@ def assume_loss_grad(scale: Optional[float]):
         _LOSS_GRAD["scale"] = prev
 
 
+@contextlib.contextmanager
+def loss_denominator(count: Optional[Tensor]):
+    """Inside, a mean cross-entropy divides its sum by ``count`` (a scalar tensor) instead of by the number of targets it
+    is given.  For a rank that holds a slice of a batch's tokens and whose gradients are then averaged over the ranks of
+    the slice group: with ``count`` = trained tokens of the whole batch / ranks, the average of the ranks' losses (and
+    gradients) is the mean over all trained tokens, however unevenly they fall on the slices.  ``None`` changes nothing."""
+    prev = _LOSS_GRAD["denominator"]
+    _LOSS_GRAD["denominator"] = count
+    try:
+        yield
+    finally:
+        _LOSS_GRAD["denominator"] = prev
+
+
+def _mean_denominator(targets: Tensor, ignore_index: int) -> Tensor:
+    count = _LOSS_GRAD["denominator"]
+    if count is not None:
+        return count.to(device=targets.device, dtype=torch.float32).reshape(()).clamp(min=1e-6)
+    return (targets != ignore_index).sum().clamp(min=1).float()
+
+
 def cross_entropy(logits: Tensor, targets: Tensor, label_smoothing: float = 0.0, ignore_index: int = -100,
                   reduction: str = "mean") -> Tensor:
     """Cross-entropy over the last dim of ``logits`` (any leading shape), fp32 math.
@@ -415,15 +436,14 @@ def cross_entropy(logits: Tensor, targets: Tensor, label_smoothing: float = 0.0,
         return rows.view(targets.shape)
     if reduction == "sum":
         return rows.sum()
-    n = (targets.reshape(-1) != ignore_index).sum().clamp(min=1)
-    return rows.sum() / n
+    return rows.sum() / _mean_denominator(targets.reshape(-1), ignore_index)
 
 
 class _LinearCEFn(Function):
     @staticmethod
     def forward(ctx, h: Tensor, w: Tensor, targets: Tensor, smoothing: float, ignore_index: int, chunk: int, w_ref):
         t, d = h.shape
-        n_valid = (targets != ignore_index).sum().clamp(min=1).float()
+        n_valid = _mean_denominator(targets, ignore_index)
         baked = _LOSS_GRAD["scale"]
         need_grad = ctx.needs_input_grad[0] or ctx.needs_input_grad[1]
         gscale = ((baked if baked is not None else 1.0) / n_valid).reshape(1).contiguous()

@@ -192,6 +192,10 @@ class TensorParallelExecutor(ModelParallelExecutor):
                 flat = t.reshape(-1)
                 local = flat.numel() // tp
                 out[key] = flat[r * local:(r + 1) * local]
+        if isinstance(batch.get("loss_mask"), torch.Tensor) and tp > 1:
+            # a masked mean: every rank divides by 1/tp of the batch's trained tokens, so that the average over the block
+            # is the mean over all of them (the ranks' own counts differ)
+            out["loss_denominator"] = batch["loss_mask"].bool().sum().float() / tp
         return out
 
     def _full_state_dict(self, model):

@@ -271,7 +271,9 @@ class SFTStrategy(_TokenCEStrategy):
         batch = self._to_rank(batch)
         pos = batch["position_ids"]
         targets = batch["target_ids"].masked_fill(~batch["loss_mask"].bool(), -100)
-        return self._ce(batch["input_ids"], targets, position_ids=pos, input_mask=attn)
+        # ranks that hold slices of one batch's tokens divide by their share of ALL trained tokens, not by their own count
+        with ops.loss_denominator(batch.get("loss_denominator")):
+            return self._ce(batch["input_ids"], targets, position_ids=pos, input_mask=attn)
 
 
 @StrategyFactory.register("dpo")

@@ -222,3 +222,33 @@ def test_two_epochs_continue_the_step_count_and_reshuffle(tmp_path):
     assert [r["step"] for r in steps] == list(range(1, 13)) and [r["epoch"] for r in steps] == [0] * 6 + [1] * 6
     assert [r["epoch"] for r in rows if r["type"] == "epoch"] == [0, 1]
     assert steps[-1]["consumed_samples"] == 48
+
+
+def test_loss_denominator_turns_slice_means_into_the_mean_over_all_trained_tokens():
+    """Two ranks hold halves of a batch with 1 and 5 trained tokens: with the shared denominator the average of their
+    losses (and of their gradients) is the whole batch's mean; without it, it is not."""
+    from astrai_b200 import ops
+
+    torch.manual_seed(0)
+    logits = torch.randn(12, 9, requires_grad=True)
+    targets = torch.randint(0, 9, (12,))
+    keep = torch.tensor([1, 0, 0, 0, 0, 0, 1, 1, 0, 1, 1, 1], dtype=torch.bool)
+    targets = targets.masked_fill(~keep, -100)
+    whole = ops.cross_entropy(logits, targets)
+    whole.backward()
+    ref_grad, logits.grad = logits.grad.clone(), None
+
+    halves = []
+    with ops.loss_denominator(keep.sum().float() / 2):
+        for r in range(2):
+            halves.append(ops.cross_entropy(logits[r * 6:(r + 1) * 6], targets[r * 6:(r + 1) * 6]))
+    (sum(halves) / 2).backward()
+    assert float(sum(halves) / 2) == pytest.approx(float(whole), rel=1e-6)
+    assert torch.allclose(logits.grad, ref_grad, atol=1e-7)
+
+    plain = [ops.cross_entropy(logits[r * 6:(r + 1) * 6], targets[r * 6:(r + 1) * 6]) for r in range(2)]
+    assert abs(float(sum(plain) / 2) - float(whole)) > 1e-3  # the slices' own counts weight the tokens unevenly
+    with ops.loss_denominator(None):
+        assert float(ops.cross_entropy(logits, targets)) == pytest.approx(float(whole))
+    # the context ends with the block
+    assert float(ops.cross_entropy(logits[:6], targets[:6])) == pytest.approx(float(plain[0]))

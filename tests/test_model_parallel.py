@@ -80,6 +80,14 @@ def test_pipeline_parallel_supervised_objective_and_validation(tmp_path, sft_ref
     assert len(run["val"]) == 1 and run["val"] == pytest.approx(sft_ref["val"], abs=2e-5)
 
 
+def test_tensor_parallel_supervised_objective_is_the_mean_over_all_trained_tokens(tmp_path, sft_ref):
+    """The ranks of a tensor-parallel block hold slices of the batch's tokens with different numbers of trained tokens; the
+    block's loss, gradients and validation loss must still be those of one process that sees the whole batch."""
+    run = _run(tmp_path, "tpsft", 2, "--mode", "tp", "--strategy", "sft", "--val", "--label_smoothing", "0.1")
+    _same(run, sft_ref)
+    assert run["val"] == pytest.approx(sft_ref["val"], abs=2e-5)
+
+
 def test_pipeline_mode_is_refused_for_objectives_with_reference_models(tmp_path):
     from astrai_b200.config import TrainConfig
     from astrai_b200.trainer.train_context import TrainContextBuilder
