@@ -107,3 +107,9 @@ def test_modules_and_files_named_in_the_guides_exist():
         assert os.path.exists(os.path.join(ROOT, path)), path
     for link in re.findall(r"\]\(((?:guides|developer)/[\w\-]+\.md)\)", _read("get-started.md")):
         assert os.path.exists(os.path.join(DOCS, link)), link
+
+
+def test_options_page_is_what_the_generator_writes():
+    from astrai_b200.cli.options_doc import render
+
+    assert _read("guides", "params.md") == render(), "run: python -m astrai_b200.cli.options_doc > docs/guides/params.md"
