@@ -5,8 +5,8 @@ The reference exposes ``ATTN_BACKEND`` (torch_native / cuda / flash), a context 
 framework has one architecture, so the choice is between the hand-written sm_100a kernels (``TCGEN05``, the default on
 CUDA: flash forward / backward, ragged prefill, paged decode) and the plain-PyTorch statement (``TORCH_NATIVE``:
 SDPA, the only choice on CPU and the oracle / baseline on GPU).  The reference's names ``cuda`` and ``flash`` are
-accepted as aliases of ``TCGEN05``.  Selection order: explicit context > ``ASTR_BACKEND`` (or ``ASTRAI_B200_ATTN``) >
-default; a call the kernels do not cover (arbitrary boolean mask, head dim outside 64 / 128 for dense attention) falls
+accepted as aliases of ``TCGEN05``.  Selection order, as in the reference (``attention.py:204-217``): the process-wide
+``ASTR_BACKEND`` (or ``ASTRAI_B200_ATTN``) > the innermost ``attn_backend(...)`` context > default; a call the kernels do not cover (arbitrary boolean mask, head dim outside 64 / 128 for dense attention) falls
 back to ``TORCH_NATIVE`` unless the backend was chosen explicitly, in which case it raises.
 """
 
@@ -43,11 +43,15 @@ def _environment() -> Optional[ATTN_BACKEND]:
     return ATTN_BACKEND.parse(raw) if raw else None
 
 
-def get_backend(device_type: str = "cuda") -> ATTN_BACKEND:
-    """The backend a call on ``device_type`` would use right now."""
+def get_backend(device_type: str = "cuda", use_default: bool = True) -> Optional[ATTN_BACKEND]:
+    """The backend a call on ``device_type`` would use right now.  ``use_default=False`` returns only what the
+    environment or a context named (``None`` if neither did)."""
+    chosen = _environment() or _current.get()
+    if not use_default:
+        return chosen
     if device_type != "cuda":
         return ATTN_BACKEND.TORCH_NATIVE
-    return _current.get() or _environment() or ATTN_BACKEND.TCGEN05
+    return chosen or ATTN_BACKEND.TCGEN05
 
 
 def explicit() -> bool:

@@ -150,14 +150,30 @@ def test_attention_backend_selection(monkeypatch):
     monkeypatch.delenv("ASTRAI_B200_ATTN", raising=False)
     assert backend.get_backend("cpu") is backend.ATTN_BACKEND.TORCH_NATIVE
     assert backend.get_backend("cuda") is backend.ATTN_BACKEND.TCGEN05 and not backend.explicit()
+    assert backend.get_backend("cuda", use_default=False) is None
+    with backend.attn_backend("torch_native"):
+        assert backend.get_backend("cuda") is backend.ATTN_BACKEND.TORCH_NATIVE and backend.explicit()
+        assert backend.get_backend("cuda", use_default=False) is backend.ATTN_BACKEND.TORCH_NATIVE
+        with backend.attn_backend(backend.ATTN_BACKEND.TCGEN05):  # contexts nest and unwind
+            assert backend.get_backend("cuda") is backend.ATTN_BACKEND.TCGEN05
+        assert backend.get_backend("cuda") is backend.ATTN_BACKEND.TORCH_NATIVE
+    assert backend.get_backend("cuda") is backend.ATTN_BACKEND.TCGEN05
+    # the environment is a process-wide override: it wins over a context, as in the reference
     monkeypatch.setenv("ASTR_BACKEND", "torch_native")
     assert backend.get_backend("cuda") is backend.ATTN_BACKEND.TORCH_NATIVE and backend.explicit()
     with backend.attn_backend("cuda"):  # the reference's name for its kernel backend
-        assert backend.get_backend("cuda") is backend.ATTN_BACKEND.TCGEN05
+        assert backend.get_backend("cuda") is backend.ATTN_BACKEND.TORCH_NATIVE
+        assert backend.get_backend("cuda", use_default=False) is backend.ATTN_BACKEND.TORCH_NATIVE
+    monkeypatch.delenv("ASTR_BACKEND")
+    monkeypatch.setenv("ASTRAI_B200_ATTN", "sdpa")
     assert backend.get_backend("cuda") is backend.ATTN_BACKEND.TORCH_NATIVE
+    monkeypatch.delenv("ASTRAI_B200_ATTN")
+    with backend.attn_backend("cuda"):
+        assert backend.get_backend("cuda") is backend.ATTN_BACKEND.TCGEN05
+    with pytest.raises(ValueError):
+        with backend.attn_backend("unknown"):
+            pass
     assert backend.ATTN_BACKEND.parse("flash") is backend.ATTN_BACKEND.TCGEN05
-    import pytest
-
     with pytest.raises(ValueError):
         backend.ATTN_BACKEND.parse("metal")
     assert backend.is_available("torch_native")
