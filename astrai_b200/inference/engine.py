@@ -155,11 +155,17 @@ class InferenceEngine:
         return agen()
 
     def _submit(self, prompts, max_tokens, temperature, top_p, top_k, frequency_penalty, rep_window):
+        from astrai_b200.ops.backend import get_backend
+
         result = GenerateResult(count=len(prompts))
+        # a back end chosen by the caller (`with attn_backend(...)`: a per-thread selection) travels with the request to
+        # the scheduling thread; None leaves the request on the scheduler's own
+        chosen = get_backend(use_default=False)
+        extra = {"backend": chosen} if chosen is not None else {}
         task_ids = [
             self.scheduler.add_task(prompt=p, max_tokens=max_tokens, temperature=temperature, top_p=top_p, top_k=top_k,
                                     frequency_penalty=frequency_penalty, rep_window=rep_window,
-                                    stream_callback=lambda tok, i=i: result.append(tok, i))
+                                    stream_callback=lambda tok, i=i: result.append(tok, i), **extra)
             for i, p in enumerate(prompts)
         ]
         return result, task_ids

@@ -155,6 +155,10 @@ class Executor:
         self._buckets: List[int] = []
         self._graph_supported = (self.device.type == "cuda" and self.dtype == torch.bfloat16
                                  and head_dim in (32, 64, 128, 256) and 1 <= cfg.num_attention_heads // cfg.num_key_value_heads <= 8)
+        from astrai_b200.ops import backend as attn_backends
+
+        # decode graphs hold the kernels of the back end that was active at capture: steps under another one run eagerly
+        self._graph_backend = attn_backends.get_backend(self.device.type)
         if enable_cuda_graph and self._graph_supported:
             self._graph_ctx.set_enabled(True)
             self._warmup()
@@ -322,8 +326,11 @@ class Executor:
             info = build_sampling_info(tasks, self.device)
             ws.put_long(ws.position_ids, positions)
         self._decode_cache = DecodeSteadyState(sig, positions, info)
+        from astrai_b200.ops import backend as attn_backends
+
+        use_graph = self.cuda_graph_enabled and attn_backends.get_backend(self.device.type) is self._graph_backend
         with torch.inference_mode(), timed(f"execute_decode forward b={b}", logger):
-            if self.cuda_graph_enabled:
+            if use_graph:
                 rows = self._bucket(b)
                 if not steady:
                     self._zero_padding(b, rows)

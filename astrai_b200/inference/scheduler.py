@@ -8,6 +8,7 @@ bounded by ``max_prefill_tokens``; requests that cannot be given cache pages wai
 
 from __future__ import annotations
 
+import contextlib
 import logging
 import threading
 import uuid
@@ -19,6 +20,7 @@ from astrai_b200.inference.cache import PagePool, TaskCacheManager
 from astrai_b200.inference.metrics import MetricsCollector
 from astrai_b200.inference.runtime.executor import Executor
 from astrai_b200.inference.task import STOP, Task, TaskManager, TaskStatus
+from astrai_b200.ops import backend as attn_backends
 
 logger = logging.getLogger(__name__)
 
@@ -53,8 +55,13 @@ class InferenceScheduler:
         self._metrics = MetricsCollector()
         self._task_cache = TaskCacheManager(self._cache)
         self._task_mgr = TaskManager(tokenizer, max_batch_size, max_seq_len, metrics=self._metrics)
-        self._executor = Executor(model, self._cache, self._task_cache, self.device, self.dtype, enable_cuda_graph,
-                                  max_prefill_tokens=max_prefill_tokens, control=self._control)
+        # `backend`: the attention back end of this scheduler's forwards (name or ATTN_BACKEND; None = the process default).
+        # Context selections are per thread, so the loop thread enters it itself; decode graphs are captured under it.
+        self._backend = attn_backends.ATTN_BACKEND.parse(backend) if backend is not None else None
+        with self._backend_context():
+            self._executor = Executor(model, self._cache, self._task_cache, self.device, self.dtype, enable_cuda_graph,
+                                      max_prefill_tokens=max_prefill_tokens, control=self._control)
+            self._backend_name = attn_backends.get_backend(self.device.type).value
         self._staged: List[dict] = []      # tensor-parallel serving, first rank: requests not yet shared with the others
         self._cancelled: List[str] = []
         self._stage_lock = threading.Lock()
@@ -70,9 +77,12 @@ class InferenceScheduler:
         self.prefill_defer_steps, self.prefill_defer_min_batch = int(prefill_defer_steps), int(prefill_defer_min_batch)
         self.prefill_defer_tokens = int(prefill_defer_tokens)
         self._steps_since_prefill = 0
-        self._backend_name = "tcgen05" if self.device.type == "cuda" else "torch_native"
         self._stop_event = threading.Event()
         self._loop_thread: Optional[threading.Thread] = None
+
+    def _backend_context(self, backend=None):
+        chosen = backend if backend is not None else self._backend
+        return attn_backends.attn_backend(chosen) if chosen is not None else contextlib.nullcontext()
 
     # -- public surface -----------------------------------------------------------------------------------------------------
     def add_task(self, prompt, **kwargs) -> str:
@@ -192,12 +202,27 @@ class InferenceScheduler:
             pending += len(t.prompt_ids) - done
         return pending < self.prefill_defer_tokens
 
-    def _step(self, tasks: List[Task], return_logprobs: bool = False) -> Tuple[List[Task], List[Task]]:
+    def _step(self, tasks: List[Task], return_logprobs: bool = False, one_backend: bool = False) -> Tuple[List[Task], List[Task]]:
         """Advance every task by one token.  Returns (tasks that produced a token, tasks aborted for lack of room).
 
         The decode forward of the requests that are past their prompt is launched first (one graph replay) and the
         prefill forward of the new prompts is issued while it runs; the sampled tokens of both are read back afterwards,
-        so the host time of the prefill launches overlaps the decode step on the GPU."""
+        so the host time of the prefill launches overlaps the decode step on the GPU.
+
+        Requests that were submitted under an attention back end of their own (``Task.backend``, captured from the
+        submitting thread's ``attn_backend(...)`` context) are stepped group by group under that back end, as the
+        reference does (``astrai/inference/scheduler.py:125-214``)."""
+        if not one_backend and any(t.backend is not None for t in tasks):
+            groups: Dict[Any, List[Task]] = {}
+            for t in tasks:
+                groups.setdefault(t.backend, []).append(t)
+            stepped, aborted = [], []
+            for backend, group in groups.items():
+                with self._backend_context(backend):
+                    done, gone = self._step(group, return_logprobs, one_backend=True)
+                stepped += done
+                aborted += gone
+            return stepped, aborted
         fresh = [t for t in tasks if not t.prefill_done and t.prompt_ids]
         decode, aborted = [], []
         for t in tasks:
@@ -263,6 +288,10 @@ class InferenceScheduler:
             self._task_mgr.return_to_waiting(rejected)
 
     def _run_generation_loop(self):
+        with self._backend_context():
+            self._generation_loop()
+
+    def _generation_loop(self):
         tok = self._task_mgr.tokenizer
         stop_ids = set(tok.stop_ids)
         try:

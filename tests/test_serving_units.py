@@ -660,3 +660,77 @@ def test_finished_requests_are_counted_even_when_the_caller_removes_them_at_once
             assert stats["total_tokens"] >= n
     finally:
         engine.shutdown()
+
+
+# ------------------------------------------------------------------------------ attention back end per scheduler / request
+def test_scheduler_backend_is_active_on_the_loop_thread_and_named(served, monkeypatch):
+    from astrai_b200.ops import backend as ab
+
+    monkeypatch.delenv("ASTR_BACKEND", raising=False)
+    monkeypatch.delenv("ASTRAI_B200_ATTN", raising=False)
+    s = _sched(served, backend="torch_native")
+    assert s.backend_name == "torch_native" and ab.get_backend("cuda", use_default=False) is None  # nothing leaks to this thread
+    seen = []
+    step = s._step
+    s._step = lambda *a, **k: (seen.append(ab.get_backend("cuda", use_default=False)), step(*a, **k))[1]
+    done = threading.Event()
+    s.start()
+    try:
+        s.add_task([60, 61], max_tokens=2, temperature=0.0, stream_callback=lambda p: done.set() if not isinstance(p, str) else None)
+        assert done.wait(timeout=30)
+    finally:
+        s.stop()
+    assert seen and set(seen) == {ab.ATTN_BACKEND.TORCH_NATIVE}
+    assert _sched(served).backend_name == "torch_native"  # a CPU model: the only back end there is
+    with pytest.raises(ValueError):
+        _sched(served, backend="metal")
+
+
+def test_requests_are_stepped_in_groups_of_their_own_backend(served, monkeypatch):
+    """A request carries the back end its submitter had selected; a step runs one forward group per back end, each under
+    that selection, and the tokens are what they are without any selection (on the CPU every back end is the same math)."""
+    from astrai_b200.inference.task import Task
+    from astrai_b200.ops import backend as ab
+
+    monkeypatch.delenv("ASTR_BACKEND", raising=False)
+    monkeypatch.delenv("ASTRAI_B200_ATTN", raising=False)
+    plain = _sched(served).run_batch([[30, 31, 32], [40, 41], [50, 51, 52, 53]], max_tokens=5, temperature=0.0)
+
+    s = _sched(served)
+    calls = []
+    decode, prefill = s._executor.execute_decode, s._executor.execute_prefill
+    s._executor.execute_decode = lambda tasks, **k: (calls.append(("decode", ab.get_backend("cuda", use_default=False), len(tasks))), decode(tasks, **k))[1]
+    s._executor.execute_prefill = lambda tasks, **k: (calls.append(("prefill", ab.get_backend("cuda", use_default=False), len(tasks))), prefill(tasks, **k))[1]
+    tasks = [Task("a", [30, 31, 32], 5, 0.0, backend=ab.ATTN_BACKEND.TORCH_NATIVE), Task("b", [40, 41], 5, 0.0),
+             Task("c", [50, 51, 52, 53], 5, 0.0, backend=ab.ATTN_BACKEND.TORCH_NATIVE)]
+    for t in tasks:
+        assert s._task_cache.task_alloc(t.task_id, t.prompt_ids)
+    for _ in range(5):
+        stepped, aborted = s._step(tasks)
+        assert len(stepped) == 3 and not aborted
+    assert [t.output_ids for t in tasks] == plain
+    assert {c for c in calls if c[0] == "prefill"} == {("prefill", ab.ATTN_BACKEND.TORCH_NATIVE, 2), ("prefill", None, 1)}
+    assert [c for c in calls if c[0] == "decode"].count(("decode", ab.ATTN_BACKEND.TORCH_NATIVE, 2)) == 4
+    assert [c for c in calls if c[0] == "decode"].count(("decode", None, 1)) == 4
+    assert ab.get_backend("cuda", use_default=False) is None
+
+
+def test_generate_hands_the_callers_backend_to_the_request(served, monkeypatch):
+    from astrai_b200.inference import InferenceEngine
+    from astrai_b200.ops import backend as ab
+
+    monkeypatch.delenv("ASTR_BACKEND", raising=False)
+    monkeypatch.delenv("ASTRAI_B200_ATTN", raising=False)
+    model, tok = served
+    engine = InferenceEngine(model, tok, max_batch_size=2, max_seq_len=96, enable_cuda_graph=False)
+    seen = []
+    add = engine.scheduler.add_task
+    engine.scheduler.add_task = lambda *a, **k: (seen.append(k.get("backend")), add(*a, **k))[1]
+    try:
+        first = engine.generate("hello", max_tokens=3, temperature=0.0)
+        with ab.attn_backend("torch_native"):
+            second = engine.generate("hello", max_tokens=3, temperature=0.0)
+            streamed = "".join(engine.generate("hello", stream=True, max_tokens=3, temperature=0.0))
+        assert seen == [None, ab.ATTN_BACKEND.TORCH_NATIVE, ab.ATTN_BACKEND.TORCH_NATIVE] and first == second == streamed
+    finally:
+        engine.shutdown()
