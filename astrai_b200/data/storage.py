@@ -14,7 +14,7 @@ import glob
 import json
 import logging
 from pathlib import Path
-from typing import Callable, Dict, List, Optional, Tuple, Union
+from typing import Callable, Dict, List, Optional, Protocol, Tuple, Union, runtime_checkable
 
 import torch
 from torch import Tensor
@@ -37,6 +37,23 @@ def detect_format(load_path: str) -> str:
     if glob.glob(str(root / "**" / "*.jsonl"), recursive=True):
         return "jsonl"
     raise FileNotFoundError(f"No supported data files found at {load_path}")
+
+
+@runtime_checkable
+class Streamable(Protocol):
+    """A store that serves token ranges of its concatenated keys (``fetch(begin, end, keys)``): windows for ``seq`` /
+    ``sft``.  The reference states this as a mixin class (``astrai/dataset/storage.py:314-330``); here it is a
+    structural type, so ``isinstance(store, Streamable)`` asks the same question of any store."""
+
+    def fetch(self, begin: int, end: int, keys): ...
+
+
+@runtime_checkable
+class Recordable(Protocol):
+    """A store that serves whole records (``fetch_record(index, keys)``): preference pairs, response groups
+    (``astrai/dataset/storage.py:361-373``)."""
+
+    def fetch_record(self, index: int, keys): ...
 
 
 class Store:

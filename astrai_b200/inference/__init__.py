@@ -1,6 +1,7 @@
 from astrai_b200.inference.cache import KVCache, PagePool, TaskCacheManager
 from astrai_b200.inference.engine import GenerateResult, InferenceEngine
 from astrai_b200.inference.metrics import MetricsCollector
+from astrai_b200.inference.runtime.executor import Executor
 from astrai_b200.inference.runtime.sample import SamplingPipeline, sample
 from astrai_b200.inference.scheduler import InferenceScheduler
 from astrai_b200.inference.task import STOP, Task, TaskManager, TaskStatus
@@ -19,6 +20,6 @@ def run_server(*args, **kwargs):
 
 
 __all__ = [
-    "GenerateResult", "InferenceEngine", "InferenceScheduler", "KVCache", "MetricsCollector", "PagePool", "STOP",
+    "Executor", "GenerateResult", "InferenceEngine", "InferenceScheduler", "KVCache", "MetricsCollector", "PagePool", "STOP",
     "SamplingPipeline", "Task", "TaskCacheManager", "TaskManager", "TaskStatus", "get_app", "run_server", "sample",
 ]

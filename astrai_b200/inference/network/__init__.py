@@ -1,6 +1,6 @@
 from astrai_b200.inference.network.anthropic import AnthropicResponseBuilder
 from astrai_b200.inference.network.app import (
-    AnthropicMessage, ChatCompletionRequest, ChatMessage, MessagesRequest, create_engine, get_app, run_server,
+    AnthropicMessage, ChatCompletionRequest, ChatMessage, FunctionDef, MessagesRequest, ToolDef, create_engine, get_app, run_server,
 )
 from astrai_b200.inference.network.openai import OpenAIResponseBuilder
 from astrai_b200.inference.network.protocol import (
@@ -9,7 +9,7 @@ from astrai_b200.inference.network.protocol import (
 from astrai_b200.inference.network.tool_parser import BaseToolParser, SimpleJsonToolParser, ToolParserFactory
 
 __all__ = [
-    "AnthropicMessage", "AnthropicResponseBuilder", "BaseToolParser", "ChatCompletionRequest", "ChatMessage", "GenContext",
+    "AnthropicMessage", "AnthropicResponseBuilder", "BaseToolParser", "ChatCompletionRequest", "ChatMessage", "FunctionDef", "GenContext",
     "MessagesRequest", "OpenAIResponseBuilder", "ProtocolHandler", "ResponseBuilder", "SimpleJsonToolParser", "StopChecker",
-    "StopInfo", "ToolParserFactory", "create_engine", "get_app", "run_server", "sse_done", "sse_event",
+    "StopInfo", "ToolDef", "ToolParserFactory", "create_engine", "get_app", "run_server", "sse_done", "sse_event",
 ]

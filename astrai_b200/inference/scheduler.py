@@ -57,11 +57,12 @@ class InferenceScheduler:
         self._task_mgr = TaskManager(tokenizer, max_batch_size, max_seq_len, metrics=self._metrics)
         # `backend`: the attention back end of this scheduler's forwards (name or ATTN_BACKEND; None = the process default).
         # Context selections are per thread, so the loop thread enters it itself; decode graphs are captured under it.
-        self._backend = attn_backends.ATTN_BACKEND.parse(backend) if backend is not None else None
+        self._backend = attn_backends.resolve(backend) if backend is not None else None
         with self._backend_context():
             self._executor = Executor(model, self._cache, self._task_cache, self.device, self.dtype, enable_cuda_graph,
                                       max_prefill_tokens=max_prefill_tokens, control=self._control)
-            self._backend_name = attn_backends.get_backend(self.device.type).value
+            active = attn_backends.get_backend(self.device.type)
+            self._backend_name = active.value if isinstance(active, attn_backends.ATTN_BACKEND) else type(active).__name__
         self._staged: List[dict] = []      # tensor-parallel serving, first rank: requests not yet shared with the others
         self._cancelled: List[str] = []
         self._stage_lock = threading.Lock()

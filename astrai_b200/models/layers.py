@@ -77,6 +77,16 @@ def rope_table(dim: int, max_len: int, base: float = 10000.0, device=None) -> Te
     return torch.stack((ang.cos(), ang.sin()), dim=-1)
 
 
+def get_rotary_emb(dim: int, max_len: int, base: float = 10000.0, device=None) -> Tensor:
+    """The (cos, sin) table ``[max_len, dim / 2, 2]`` under the reference's name (``astrai/model/components/rope.py:8-24``)."""
+    return rope_table(dim, max_len, base, device)
+
+
+def apply_rotary_emb(x: Tensor, freqs_cis: Tensor) -> Tensor:
+    """Rotate ``x [..., heads, head_dim]`` by ``freqs_cis [..., head_dim / 2, 2]`` (adjacent pairs, fp32 math)."""
+    return ops.rotary(x, freqs_cis)
+
+
 class RotaryEmbedding(nn.Module):
     """Position -> (cos, sin) rows.  ``rope_scaling={"type": "ntk", "factor": f}`` rescales the base by
     ``f ** (dim / (dim - 2))``; other types are accepted and leave the base alone, as in the reference."""

@@ -2,8 +2,20 @@
 
 from astrai_b200.ops import fp8, native, reference
 from astrai_b200.ops.fp8 import DelayedScaling, DynamicScaling, FP8Format, fp8_autocast
-from astrai_b200.ops.attention import dense_attention
-from astrai_b200.ops.backend import ATTN_BACKEND, attn_backend, get_backend
+from astrai_b200.ops.attention import attention, dense_attention
+from astrai_b200.ops.attn_api import TensorLayout, apply_rotary_emb, attn_decode, attn_paged_decode, attn_prefill
+from astrai_b200.ops.backend import (
+    ATTN_BACKEND,
+    AttentionBackend,
+    AttentionBackendFactory,
+    CudaBackend,
+    FlashAttnBackend,
+    Tcgen05Backend,
+    TorchNativeBackend,
+    attn_backend,
+    get_backend,
+)
+from astrai_b200.ops.native import KERNEL_NAMES, kernel_available as is_available
 from astrai_b200.ops.functional import (
     adamw_,
     add_rms_norm,
@@ -25,7 +37,9 @@ from astrai_b200.ops.functional import (
 )
 
 __all__ = [
-    "ATTN_BACKEND", "attn_backend", "get_backend", "DelayedScaling", "DynamicScaling", "FP8Format", "fp8", "fp8_autocast", "adamw_", "add_rms_norm", "assume_loss_grad", "clip_coef", "cross_entropy", "dense_attention", "embedding", "gemm", "linear",
+    "ATTN_BACKEND", "AttentionBackend", "AttentionBackendFactory", "CudaBackend", "FlashAttnBackend", "KERNEL_NAMES", "Tcgen05Backend",
+    "TensorLayout", "TorchNativeBackend", "apply_rotary_emb", "attention", "attn_backend", "attn_decode", "attn_paged_decode", "attn_prefill",
+    "get_backend", "is_available", "DelayedScaling", "DynamicScaling", "FP8Format", "fp8", "fp8_autocast", "adamw_", "add_rms_norm", "assume_loss_grad", "clip_coef", "cross_entropy", "dense_attention", "embedding", "gemm", "linear",
     "linear_cross_entropy", "linear_token_logprobs", "loss_denominator", "native", "qkv_rope", "reference", "rms_norm", "rotary",
     "sumsq", "swiglu", "swiglu_fused",
 ]

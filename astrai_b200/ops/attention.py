@@ -112,6 +112,11 @@ def attention(q: Tensor, k: Tensor, v: Tensor, kv_cache=None, layer_id: int = 0,
     ``fwd=None``: dense ``[B,S,H,D]`` tensors, no cache.  ``fwd in {"prefill","decode"}``: packed ``[T,H,D]``
     tensors plus a :class:`~astrai_b200.ops.kv.KVCache`; new K/V are appended to the pool first.
     """
+    from astrai_b200.ops import backend
+
+    own = backend.current_custom()
+    if own is not None:  # a registered back end that computes attention itself
+        return own.forward(q, k, v, kv_cache, layer_id, attn_mask, is_causal, fwd)
     if fwd is None:
         return dense_attention(q, k, v, attn_mask, is_causal)
     from astrai_b200.ops.paged_attention import cached_attention

@@ -67,7 +67,24 @@ def launch_count() -> int:
     return int(require().launch_count())
 
 
-KERNEL_NAMES = (
-    "gemm", "rmsnorm_fwd", "rmsnorm_bwd", "rope", "swiglu_fwd", "swiglu_bwd", "embedding_fwd", "embedding_bwd_",
-    "ce_rows", "logprob_bwd_", "sumsq_", "clip_coef_", "adamw_", "axpy_f32_",
-)
+def _op_names():
+    """Names under ``torch.ops.astrai_b200``, read from the binding source (one ``m.def("name(...)")`` per operator)."""
+    import re
+
+    src = Path(__file__).resolve().parent / "csrc" / "bindings.cpp"
+    try:
+        return tuple(sorted(set(re.findall(r'm\.def\("([A-Za-z0-9_]+)\(', src.read_text()))))
+    except OSError:
+        return ()
+
+
+KERNEL_NAMES = _op_names()
+
+
+def kernel_available(name: str = "") -> bool:
+    """True if the extension is loaded and (when ``name`` is given) has that operator; never raises, never builds."""
+    if name and name not in KERNEL_NAMES:
+        return False
+    if not _state["loaded"] and not _LIB.exists():
+        return False
+    return load(build_if_missing=False)

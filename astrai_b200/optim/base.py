@@ -17,6 +17,35 @@ class OptimizerFactory(BaseFactory[Optimizer]):
     """Built-in training optimizers by name."""
 
 
+def composite_step(sub_optimizers, closure=None):
+    """One step of several optimizers that together stand for one: the closure runs once (with gradients enabled), before
+    any of them steps; ``None`` entries are skipped."""
+    loss = None
+    if closure is not None:
+        with torch.enable_grad():
+            loss = closure()
+    for sub in sub_optimizers:
+        if sub is not None:
+            sub.step()
+    return loss
+
+
+def composite_zero_grad(sub_optimizers, set_to_none: bool = True) -> None:
+    for sub in sub_optimizers:
+        if sub is not None:
+            sub.zero_grad(set_to_none=set_to_none)
+
+
+def composite_state_dict(named_sub_optimizers: Dict[str, Optional[Optimizer]]) -> dict:
+    """``{name: state dict}`` with the empty slots kept as ``None`` (a model without matrices has no matrix optimizer)."""
+    return {name: (sub.state_dict() if sub is not None else None) for name, sub in named_sub_optimizers.items()}
+
+
+def refresh_param_groups(sub_optimizers) -> List[dict]:
+    """The parameter groups of all parts, in order: what a learning-rate scheduler iterates over."""
+    return [g for sub in sub_optimizers if sub is not None for g in sub.param_groups]
+
+
 class CompositeOptimizer(Optimizer):
     """Routes disjoint parameter sets through named sub-optimizers; behaves as one optimizer."""
 
@@ -29,24 +58,17 @@ class CompositeOptimizer(Optimizer):
         return [s for s in self._subs.values() if s is not None]
 
     def _collect_groups(self):
-        return [g for s in self._live() for g in s.param_groups]
+        return refresh_param_groups(self._subs.values())
 
     @torch.no_grad()
     def step(self, closure=None):
-        loss = None
-        if closure is not None:
-            with torch.enable_grad():
-                loss = closure()
-        for s in self._live():
-            s.step()
-        return loss
+        return composite_step(self._subs.values(), closure)
 
     def zero_grad(self, set_to_none: bool = True):
-        for s in self._live():
-            s.zero_grad(set_to_none=set_to_none)
+        composite_zero_grad(self._subs.values(), set_to_none)
 
     def state_dict(self) -> Dict[str, Any]:
-        return {name: (s.state_dict() if s is not None else None) for name, s in self._subs.items()}
+        return composite_state_dict(self._subs)
 
     def load_state_dict(self, state_dict: Dict[str, Any]):
         missing = [n for n in self._subs if n not in state_dict]

@@ -12,6 +12,9 @@ from typing import Any, Dict, List, Optional
 from jinja2 import Template
 
 
+MessageType = Dict[str, Any]  # one chat message: {"role": ..., "content": ...} plus whatever the template reads
+
+
 class ChatTemplate:
     def __init__(self, name: str = "", template_str: str = "", description: str = "",
                  default_variables: Optional[Dict[str, Any]] = None, special_tokens: Optional[Dict[str, str]] = None):

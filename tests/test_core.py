@@ -177,3 +177,29 @@ def test_attention_backend_selection(monkeypatch):
     with pytest.raises(ValueError):
         backend.ATTN_BACKEND.parse("metal")
     assert backend.is_available("torch_native")
+
+
+def test_every_public_name_of_the_reference_packages_exists_here():
+    """The names the reference's packages export (their ``__all__`` lists, read once and written down here) resolve in the
+    corresponding packages of this framework."""
+    import importlib
+
+    expected = {
+        "astrai_b200.data": ["Streamable", "Recordable", "Store", "StoreFactory", "MmapStore", "JsonlStore", "DatasetFactory", "RDSampler"],
+        "astrai_b200.inference": ["Executor", "InferenceEngine", "InferenceScheduler", "KVCache", "Task", "TaskManager", "sample"],
+        "astrai_b200.tokenize": ["AutoTokenizer", "ChatTemplate", "MessageType", "Message", "Messages"],
+        "astrai_b200.optim": ["composite_state_dict", "composite_step", "composite_zero_grad", "refresh_param_groups", "OptimizerFactory",
+                              "Mano", "ManoAdamW", "MuonAdamW", "NAdamW", "Nora", "NoraNAdamW", "OptimizerParameterGroups", "nora_direction",
+                              "nora_lr_scale", "partition_optimizer_parameters"],
+        "astrai_b200.ops": ["ATTN_BACKEND", "AttentionBackend", "AttentionBackendFactory", "CudaBackend", "TorchNativeBackend",
+                            "FlashAttnBackend", "TensorLayout", "attention", "attn_backend", "get_backend", "attn_decode", "attn_paged_decode",
+                            "attn_prefill", "is_available", "KERNEL_NAMES", "apply_rotary_emb"],
+        "astrai_b200.inference.network": ["FunctionDef", "ToolDef", "ChatCompletionRequest", "MessagesRequest", "ProtocolHandler"],
+        "astrai_b200.models": ["apply_rotary_emb", "get_rotary_emb", "RotaryEmbedding", "AutoModel", "AutoRegressiveLM", "GQA", "MLA", "MLP",
+                               "DeepSeekMoE"],
+    }
+    for module, names in expected.items():
+        mod = importlib.import_module(module)
+        missing = [n for n in names if not hasattr(mod, n)]
+        assert not missing, (module, missing)
+        assert set(names) <= set(mod.__all__), (module, sorted(set(names) - set(mod.__all__)))

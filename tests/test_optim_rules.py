@@ -265,3 +265,28 @@ def test_train_config_records_the_optimizer_name_and_hyperparameters():
     d = cfg.to_dict()
     assert d["optimizer_name"] == "nora_nadamw" and d["optimizer_hyperparameters"] == {"lr": 2e-4, "nora_lr": 5e-3}
     assert "model_fn" not in d and "optimizer_fn" not in d  # callables never reach meta.json
+
+
+def test_composite_helpers_under_the_references_names():
+    from astrai_b200.optim import composite_state_dict, composite_step, composite_zero_grad, refresh_param_groups
+
+    a, b = torch.nn.Parameter(torch.ones(2)), torch.nn.Parameter(torch.ones(3))
+    first, second = torch.optim.SGD([a], lr=0.5), torch.optim.SGD([b], lr=0.25)
+    ran = []
+
+    def closure():
+        ran.append(torch.is_grad_enabled())
+        loss = a.sum() + b.sum()
+        loss.backward()
+        return loss
+
+    with torch.no_grad():
+        loss = composite_step([first, None, second], closure)
+    assert ran == [True] and float(loss) == 5.0  # once, with gradients on
+    assert torch.allclose(a, torch.full((2,), 0.5)) and torch.allclose(b, torch.full((3,), 0.75))
+    assert [g["lr"] for g in refresh_param_groups([first, None, second])] == [0.5, 0.25]
+    state = composite_state_dict({"m": first, "none": None, "rest": second})
+    assert state["none"] is None and set(state["m"]) == {"state", "param_groups"}
+    composite_zero_grad([first, None, second])
+    assert a.grad is None and b.grad is None
+    composite_zero_grad([first, second], set_to_none=False)

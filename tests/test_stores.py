@@ -371,3 +371,11 @@ def test_sampler_partitions_are_disjoint_and_cover_the_data():
     dropped = [list(RDSampler(data, seed=9, partition=(i, 4), drop_last=True)) for i in range(4)]
     assert sum(len(p) for p in dropped) == 40 and len({x for p in dropped for x in p}) == 40
     assert len(RDSampler(data, seed=9, partition=(0, 4), drop_last=True)) == 10
+
+
+def test_stores_satisfy_the_stream_and_record_protocols(tmp_path):
+    from astrai_b200.data import MmapStore, Recordable, Streamable
+
+    store = MmapStore()
+    assert isinstance(store, Streamable) and isinstance(store, Recordable)
+    assert not isinstance(object(), Streamable) and not isinstance([], Recordable)
