@@ -123,15 +123,20 @@ def grpo_collate_fn(batch: List[Dict[str, Tensor]]) -> Dict[str, Tensor]:
 
 
 # ------------------------------------------------------------------------------------------- datasets
+def validate_keys(store: Store, required: List[str]) -> None:
+    """``KeyError`` naming the keys of ``required`` that ``store`` lacks (``astrai/dataset/dataset.py:260-270``)."""
+    missing = [k for k in required if k not in set(store.keys)]
+    if missing:
+        raise KeyError(f"Store at {getattr(store, '_load_path', '?')} is missing required keys {missing}; "
+                       f"available keys are {sorted(store.keys)}.")
+
+
 class BaseDataset(Dataset):
     required_keys: List[str] = []
 
     def __init__(self, store: Store):
         self.store = store
-        missing = [k for k in self.required_keys if k not in set(store.keys)]
-        if missing:
-            raise KeyError(f"Store at {getattr(store, '_load_path', '?')} is missing required keys {missing}; "
-                           f"available keys are {sorted(store.keys)}.")
+        validate_keys(store, self.required_keys)
 
     def __len__(self) -> int:
         return len(self.store)

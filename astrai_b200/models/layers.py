@@ -77,6 +77,11 @@ def rope_table(dim: int, max_len: int, base: float = 10000.0, device=None) -> Te
     return torch.stack((ang.cos(), ang.sin()), dim=-1)
 
 
+def ntk_base(base: float, dim: int, factor: float) -> float:
+    """NTK-aware rescaling of the rotary base for a context ``factor`` times longer (``astrai/model/components/rope.py:27-28``)."""
+    return base * factor ** (dim / (dim - 2))
+
+
 def get_rotary_emb(dim: int, max_len: int, base: float = 10000.0, device=None) -> Tensor:
     """The (cos, sin) table ``[max_len, dim / 2, 2]`` under the reference's name (``astrai/model/components/rope.py:8-24``)."""
     return rope_table(dim, max_len, base, device)
@@ -95,7 +100,7 @@ class RotaryEmbedding(nn.Module):
         super().__init__()
         self.dim, self.max_len, self.rope_scaling = dim, max_len, rope_scaling
         if rope_scaling is not None and rope_scaling.get("type", "ntk") == "ntk":
-            base = base * rope_scaling.get("factor", 1.0) ** (dim / (dim - 2))
+            base = ntk_base(base, dim, rope_scaling.get("factor", 1.0))
         self.base = base
         self.register_buffer("freqs_cis", rope_table(dim, max_len, base), persistent=False)
 

@@ -31,6 +31,9 @@ def expand_mask(mask: Optional[Tensor]) -> Optional[Tensor]:
     return mask[:, None, None, :] if mask.dim() == 2 else mask[:, None]
 
 
+process_attention_mask = expand_mask  # the reference's name (``astrai/model/transformer.py:17-26``)
+
+
 def _init_module(m: nn.Module):
     if hasattr(m, "reset_parameters"):
         m.reset_parameters()

@@ -3,7 +3,10 @@
 from astrai_b200.ops import fp8, native, reference
 from astrai_b200.ops.fp8 import DelayedScaling, DynamicScaling, FP8Format, fp8_autocast
 from astrai_b200.ops.attention import attention, dense_attention
-from astrai_b200.ops.attn_api import TensorLayout, apply_rotary_emb, attn_decode, attn_paged_decode, attn_prefill
+from astrai_b200.ops.attn_api import (
+    TensorLayout, apply_rotary_emb, attn_decode, attn_paged_decode, attn_paged_prefill, attn_prefill, flash_attn_available, repeat_kv,
+    rotary_emb,
+)
 from astrai_b200.ops.backend import (
     ATTN_BACKEND,
     AttentionBackend,
@@ -38,7 +41,7 @@ from astrai_b200.ops.functional import (
 
 __all__ = [
     "ATTN_BACKEND", "AttentionBackend", "AttentionBackendFactory", "CudaBackend", "FlashAttnBackend", "KERNEL_NAMES", "Tcgen05Backend",
-    "TensorLayout", "TorchNativeBackend", "apply_rotary_emb", "attention", "attn_backend", "attn_decode", "attn_paged_decode", "attn_prefill",
+    "TensorLayout", "TorchNativeBackend", "apply_rotary_emb", "attention", "attn_backend", "attn_decode", "attn_paged_decode", "attn_paged_prefill", "attn_prefill", "flash_attn_available", "repeat_kv", "rotary_emb",
     "get_backend", "is_available", "DelayedScaling", "DynamicScaling", "FP8Format", "fp8", "fp8_autocast", "adamw_", "add_rms_norm", "assume_loss_grad", "clip_coef", "cross_entropy", "dense_attention", "embedding", "gemm", "linear",
     "linear_cross_entropy", "linear_token_logprobs", "loss_denominator", "native", "qkv_rope", "reference", "rms_norm", "rotary",
     "sumsq", "swiglu", "swiglu_fused",

@@ -92,3 +92,42 @@ def apply_rotary_emb(x: Tensor, freqs_cis: Tensor) -> Tensor:
     from astrai_b200.ops.functional import rotary
 
     return rotary(x, freqs_cis)
+
+
+def attn_paged_prefill(q: Tensor, k_cache: Tensor, v_cache: Tensor, req_to_token: Tensor, req_pool_indices: Tensor,
+                       kv_indptr: Tensor, qo_indptr: Tensor, q_tile_to_batch: Optional[Tensor] = None,
+                       q_tile_to_index: Optional[Tensor] = None, mask: Optional[Tensor] = None, is_causal: bool = True) -> Tensor:
+    """Ragged prefill over a flat K / V pool that already holds every key of the batch: request ``i`` has queries
+    ``q[qo_indptr[i]:qo_indptr[i + 1]]`` (its LAST positions) and ``kv_indptr[i + 1] - kv_indptr[i]`` keys in row
+    ``req_pool_indices[i]`` of the slot table.  The tile maps of the reference's kernel are accepted and not needed (the
+    kernels here derive their work list from the offsets)."""
+    from astrai_b200.ops.kv import KVCache
+    from astrai_b200.ops.paged_attention import cached_attention
+
+    q_ptr, kv_ptr = qo_indptr.tolist(), kv_indptr.tolist()
+    q_lens = [b - a for a, b in zip(q_ptr[:-1], q_ptr[1:])]
+    kv_lens = [b - a for a, b in zip(kv_ptr[:-1], kv_ptr[1:])]
+    rows = req_pool_indices.to(torch.long)
+    # the slots of the query positions, request after request: their K / V are rewritten with what the pool holds
+    loc = torch.cat([req_to_token[r, n - m:n] for r, m, n in zip(rows.tolist(), q_lens, kv_lens)]).to(torch.long)
+    cache = KVCache(k_buffer=k_cache[None], v_buffer=v_cache[None], req_to_token=req_to_token, req_pool_indices=req_pool_indices,
+                    seq_lens=torch.tensor(kv_lens, dtype=req_pool_indices.dtype, device=q.device), out_cache_loc=loc,
+                    max_len=max(kv_lens), kv_indptr=kv_indptr, qo_indptr=qo_indptr, q_lens=q_lens, kv_lens=kv_lens)
+    return cached_attention(q, k_cache[loc], v_cache[loc], cache, 0, mask, is_causal, "prefill")
+
+
+def repeat_kv(x: Tensor, n_rep: int) -> Tensor:
+    """``[..., kv_heads, head_dim]`` -> ``[..., kv_heads * n_rep, head_dim]``: every key / value head repeated for the
+    query heads that share it (``astrai/extension/backend/attention.py:244-253``)."""
+    return x if n_rep == 1 else x.repeat_interleave(n_rep, dim=-2)
+
+
+def rotary_emb(x: Tensor, freqs_cis: Tensor) -> Tensor:
+    return apply_rotary_emb(x, freqs_cis)
+
+
+def flash_attn_available() -> bool:
+    """Whether the flash-attention kernels can run here: the ones of this package, on a GPU with the extension loaded."""
+    from astrai_b200.ops import backend
+
+    return backend.is_available(backend.ATTN_BACKEND.TCGEN05)

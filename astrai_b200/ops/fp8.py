@@ -102,6 +102,29 @@ class FP8TensorMeta:
         self.idx[kind] = (self.idx[kind] + 1) % self.hist[kind].numel()
         self.scale[kind].copy_(self.recipe.scale_from_history(self.hist[kind], fmt))
 
+    # the per-operand spellings of the reference (``astrai/extension/fp8.py:163-187``)
+    def update_w(self, amax: Tensor, fmt: str):
+        self.update("w", amax, fmt)
+
+    def update_x(self, amax: Tensor, fmt: str):
+        self.update("x", amax, fmt)
+
+    def update_g(self, amax: Tensor, fmt: str):
+        self.update("g", amax, fmt)
+
+    def init_w(self, t: Tensor, fmt: str):
+        self.seed("w", t, fmt)
+
+    def init_x(self, t: Tensor, fmt: str):
+        self.seed("x", t, fmt)
+
+    def init_g(self, t: Tensor, fmt: str):
+        self.seed("g", t, fmt)
+
+    w_scale = property(lambda self: self.scale["w"])
+    x_scale = property(lambda self: self.scale["x"])
+    g_scale = property(lambda self: self.scale["g"])
+
 
 @dataclass
 class _AutocastState:
@@ -111,7 +134,8 @@ class _AutocastState:
     update_interval: int = 1
 
 
-_STATE: contextvars.ContextVar[_AutocastState] = contextvars.ContextVar("astrai_b200_fp8", default=_AutocastState())
+_PROCESS_WIDE = _AutocastState()  # what holds outside every fp8_autocast block, in every thread (fp8_linear_enable)
+_STATE: contextvars.ContextVar[_AutocastState] = contextvars.ContextVar("astrai_b200_fp8", default=_PROCESS_WIDE)
 
 
 def autocast_state() -> _AutocastState:
@@ -128,6 +152,41 @@ def fp8_autocast(enabled: bool = True, update_interval: int = 1, recipe: Optiona
         yield
     finally:
         _STATE.reset(token)
+
+
+class FP8State:
+    """What is in force for fp8 right now, in the shape of the reference's global state object
+    (``astrai/extension/fp8.py:190-223``): ``enabled``, ``recipe``, ``fp8_format`` read the innermost
+    :func:`fp8_autocast`; scaling state lives on the weights themselves (``get_weight_meta``)."""
+
+    enabled = property(lambda self: autocast_state().enabled)
+    recipe = property(lambda self: autocast_state().recipe or DelayedScaling())
+    fp8_format = property(lambda self: autocast_state().fp8_format)
+
+    def get_weight_meta(self, w: Tensor) -> FP8TensorMeta:
+        return meta_for(w, self.recipe)
+
+    def reset(self, *weights: Tensor) -> None:
+        """Forget the scaling history of ``weights`` (their next use seeds it again)."""
+        for w in weights:
+            if hasattr(w, "_fp8_meta"):
+                del w._fp8_meta
+
+
+def fp8_state() -> FP8State:
+    return FP8State()
+
+
+def fp8_linear_enable(enabled: bool = True, recipe: Optional[FP8Recipe] = None) -> None:
+    """Process-wide switch (the reference's ``fp8_linear_enable``, ``astrai/extension/fp8.py:338-345``): linear layers run
+    on fp8 wherever no :func:`fp8_autocast` block says otherwise, in every thread."""
+    _PROCESS_WIDE.enabled = bool(enabled)
+    if recipe is not None or _PROCESS_WIDE.recipe is None:
+        _PROCESS_WIDE.recipe = recipe or DelayedScaling()
+
+
+def fp8_linear_enabled() -> bool:
+    return autocast_state().enabled
 
 
 def meta_for(weight: Tensor, recipe: FP8Recipe) -> FP8TensorMeta:
@@ -244,3 +303,10 @@ def eligible(x: Tensor, weight: Tensor) -> bool:
     """fp8 takes 2-D-flattenable bf16 CUDA linears whose K and N are multiples of 16."""
     return (x.is_cuda and x.dtype == torch.bfloat16 and weight.dtype == torch.bfloat16 and weight.shape[1] % 16 == 0
             and weight.shape[0] % 16 == 0 and (x.numel() // x.shape[-1]) % 16 == 0)
+
+
+# the reference's names for the same operations (``astrai/extension/fp8.py``, ``astrai/extension/ops/fp8.py``)
+fp8_quantize = quantize_bf16
+fp8_gemm = mm_fp8
+fp8_linear_forward = linear_forward_fp8
+fp8_linear_backward = linear_backward_fp8

@@ -161,11 +161,39 @@ def _spawn_local(func, world_size, backend, addr, port, device_type, start_metho
                 p.join()
 
 
+class LaunchStrategy:
+    """How ``func`` gets its ranks (the reference's ``LaunchStrategy`` classes, ``astrai/parallel/setup.py:138-247``)."""
+
+    def __init__(self, world_size: int, backend: str, master_addr: str, master_port: str, device_type: str, start_method: str = "spawn"):
+        self.world_size, self.backend, self.master_addr, self.master_port = world_size, backend, master_addr, str(master_port)
+        self.device_type, self.start_method = device_type, start_method
+
+    def launch(self, func: Callable, **kwargs):
+        raise NotImplementedError
+
+
+class TorchrunStrategy(LaunchStrategy):
+    """The ranks exist already (torchrun, SLURM, Kubernetes set RANK / WORLD_SIZE / LOCAL_RANK): join them."""
+
+    def launch(self, func: Callable, **kwargs):
+        _run_under_external_launcher(func, self.backend, self.master_addr, self.master_port, self.device_type, kwargs)
+
+
+class LocalStrategy(LaunchStrategy):
+    """Start ``world_size`` processes on this node (none for a world of one), forward stop signals to them, reap them."""
+
+    def launch(self, func: Callable, **kwargs):
+        _spawn_local(func, self.world_size, self.backend, self.master_addr, self.master_port, self.device_type, self.start_method, kwargs)
+
+
+def launch_strategy(world_size: int, backend: str = "nccl", master_addr: str = "127.0.0.1", master_port: Optional[str] = None,
+                    device_type: str = "cuda", start_method: str = "spawn") -> LaunchStrategy:
+    port = str(master_port) if master_port is not None else find_free_port()
+    kind = TorchrunStrategy if launched_externally() else LocalStrategy
+    return kind(world_size, backend, master_addr, port, device_type, start_method)
+
+
 def spawn_parallel_fn(func: Callable, world_size: int, backend: str = "nccl", master_addr: str = "127.0.0.1",
                       master_port: Optional[str] = None, device_type: str = "cuda", start_method: str = "spawn", **kwargs):
     """Run ``func(**kwargs)`` on ``world_size`` ranks (here, or inside an already-launched rank)."""
-    port = str(master_port) if master_port is not None else find_free_port()
-    if launched_externally():
-        _run_under_external_launcher(func, backend, master_addr, port, device_type, kwargs)
-    else:
-        _spawn_local(func, world_size, backend, master_addr, port, device_type, start_method, kwargs)
+    launch_strategy(world_size, backend, master_addr, master_port, device_type, start_method).launch(func, **kwargs)

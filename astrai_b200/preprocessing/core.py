@@ -26,7 +26,8 @@ def primary_ids(result: dict) -> List[int]:
     return []
 
 
-def _dtype_of(values: list) -> torch.dtype:
+def infer_dtype(values: list) -> torch.dtype:
+    """float32 for a column of floats (rewards), int32 for everything else."""
     return torch.float32 if values and isinstance(values[0], float) else torch.int32
 
 
@@ -46,8 +47,8 @@ def to_per_record_tensors(raw: Dict[str, list]) -> Dict[str, list]:
     for key, column in raw.items():
         if column and isinstance(column[0], list):
             out[key] = [
-                [torch.tensor(sub, dtype=_dtype_of(sub)) for sub in rec] if rec and isinstance(rec[0], list)
-                else torch.tensor(rec, dtype=_dtype_of(rec))
+                [torch.tensor(sub, dtype=infer_dtype(sub)) for sub in rec] if rec and isinstance(rec[0], list)
+                else torch.tensor(rec, dtype=infer_dtype(rec))
                 for rec in column
             ]
         else:

@@ -239,3 +239,51 @@ def test_kernel_names_and_availability():
     assert {"gemm", "flash_fwd", "flash_bwd", "paged_decode_append_", "sample_rows", "adamw_"} <= set(ops.KERNEL_NAMES)
     assert ops.is_available("no_such_kernel") is False
     assert isinstance(ops.is_available("gemm"), bool) and isinstance(ops.is_available(), bool)
+
+
+def test_attn_paged_prefill_attends_from_the_last_positions_of_each_request():
+    from astrai_b200 import ops
+
+    torch.manual_seed(4)
+    hq, hkv, d, slots = 4, 2, 8, 48
+    k_pool, v_pool = torch.randn(slots, hkv, d), torch.randn(slots, hkv, d)
+    table = torch.zeros(4, 16, dtype=torch.int32)
+    perm = torch.randperm(slots).int()
+    table[1, :10], table[3, :6] = perm[:10], perm[10:16]
+    rows = torch.tensor([3, 1], dtype=torch.int32)
+    kv_indptr, qo_indptr = torch.tensor([0, 6, 16], dtype=torch.int32), torch.tensor([0, 6, 9], dtype=torch.int32)  # 6 of 6, last 3 of 10
+    q = torch.randn(9, hq, d)
+    before = k_pool.clone()
+    out = ops.attn_paged_prefill(q, k_pool, v_pool, table, rows, kv_indptr, qo_indptr)
+    assert out.shape == (9, hq, d) and torch.equal(k_pool, before)  # the pool is read, not changed
+    for i, (row, m, n, start) in enumerate(((3, 6, 6, 0), (1, 3, 10, 6))):
+        idx = table[row, :n].long()
+        keep = torch.ones(m, n, dtype=torch.bool).tril(diagonal=n - m)[None, None]
+        want = _ref_attention(q[start:start + m][None], k_pool[idx][None], v_pool[idx][None], keep)[0]
+        assert torch.allclose(out[start:start + m], want, atol=1e-5), i
+
+
+def test_small_helpers_under_the_references_names():
+    from astrai_b200 import ops
+    from astrai_b200.data.dataset import validate_keys
+    from astrai_b200.models.layers import ntk_base
+    from astrai_b200.models.lm import process_attention_mask
+    from astrai_b200.preprocessing.core import infer_dtype
+
+    x = torch.arange(2 * 3 * 4.0).view(2, 3, 4)
+    assert ops.repeat_kv(x, 1) is x and ops.repeat_kv(x, 2).shape == (2, 6, 4)
+    assert torch.equal(ops.repeat_kv(x, 2)[:, 0], x[:, 0]) and torch.equal(ops.repeat_kv(x, 2)[:, 1], x[:, 0])
+    assert isinstance(ops.flash_attn_available(), bool)
+    assert ntk_base(10000.0, 64, 1.0) == 10000.0 and ntk_base(10000.0, 64, 4.0) == pytest.approx(10000.0 * 4 ** (64 / 62))
+    m2, m3, m4 = torch.ones(2, 5), torch.ones(2, 5, 5), torch.ones(2, 1, 5, 5)
+    assert process_attention_mask(None) is None and process_attention_mask(m2).shape == (2, 1, 1, 5)
+    assert process_attention_mask(m3).shape == (2, 1, 5, 5) and process_attention_mask(m4) is m4
+    assert infer_dtype([0.5]) is torch.float32 and infer_dtype([1, 2]) is torch.int32 and infer_dtype([]) is torch.int32
+
+    class Has:
+        keys = ["sequence", "loss_mask"]
+
+    validate_keys(Has(), ["sequence"])
+    validate_keys(Has(), [])
+    with pytest.raises(KeyError, match="position_ids"):
+        validate_keys(Has(), ["sequence", "position_ids"])

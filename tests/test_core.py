@@ -203,3 +203,22 @@ def test_every_public_name_of_the_reference_packages_exists_here():
         missing = [n for n in names if not hasattr(mod, n)]
         assert not missing, (module, missing)
         assert set(names) <= set(mod.__all__), (module, sorted(set(names) - set(mod.__all__)))
+
+
+def test_launch_strategy_is_chosen_from_the_environment(monkeypatch):
+    from astrai_b200.parallel import LaunchStrategy, LocalStrategy, TorchrunStrategy, launch_strategy
+
+    for name in ("RANK", "WORLD_SIZE", "LOCAL_RANK", "LOCAL_WORLD_SIZE", "TORCHELASTIC_RUN_ID"):
+        monkeypatch.delenv(name, raising=False)
+    local = launch_strategy(1, backend="gloo", device_type="cpu")
+    assert isinstance(local, LocalStrategy) and isinstance(local, LaunchStrategy) and local.master_port.isdigit()
+    seen = {}
+    local.launch(lambda **kw: seen.update(kw), value=3)  # a world of one runs in this process
+    assert seen == {"value": 3}
+    monkeypatch.setenv("RANK", "0")
+    monkeypatch.setenv("WORLD_SIZE", "1")
+    monkeypatch.setenv("MASTER_ADDR", "127.0.0.1")
+    external = launch_strategy(1, backend="gloo", device_type="cpu", master_port="29733")
+    assert isinstance(external, TorchrunStrategy) and external.master_port == "29733"
+    with pytest.raises(NotImplementedError):
+        LaunchStrategy(1, "gloo", "127.0.0.1", "1", "cpu").launch(print)

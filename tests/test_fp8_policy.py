@@ -127,3 +127,50 @@ def test_a_new_recipe_type_gets_a_fresh_meta_and_the_same_type_keeps_it():
 def test_only_bf16_cuda_multiples_of_16_are_eligible():
     x, w = torch.randn(32, 32), torch.randn(32, 32)
     assert not fp8.eligible(x, w)  # CPU tensors stay on the regular path
+
+
+def test_state_object_and_per_operand_spellings_of_the_reference():
+    from astrai_b200.ops import fp8
+
+    state = fp8.fp8_state()
+    assert state.enabled is False and isinstance(state.recipe, fp8.DelayedScaling) and state.fp8_format is fp8.FP8Format.HYBRID
+    w = torch.nn.Parameter(torch.randn(8, 8))
+    with fp8.fp8_autocast(recipe=fp8.DynamicScaling(), fp8_format=fp8.FP8Format.E4M3):
+        assert state.enabled is True and isinstance(state.recipe, fp8.DynamicScaling) and state.fp8_format.bwd() == "e4m3"
+        meta = state.get_weight_meta(w)
+        assert state.get_weight_meta(w) is meta  # kept on the weight
+    assert state.enabled is False
+    meta.init_w(w, "e4m3")
+    assert meta.seeded["w"] and float(meta.w_scale) == pytest.approx(float(w.abs().max()) / 448.0, rel=1e-5)
+    meta.update_x(torch.tensor(4.48), "e4m3")
+    meta.update_g(torch.tensor(57.344), "e5m2")
+    assert float(meta.x_scale) == pytest.approx(0.01, rel=1e-5) and float(meta.g_scale) == pytest.approx(0.001, rel=1e-5)
+    meta.init_x(torch.full((3,), 2.0), "e4m3")
+    meta.init_g(torch.full((3,), 2.0), "e5m2")
+    meta.update_w(torch.tensor(448.0), "e4m3")
+    assert float(meta.w_scale) == pytest.approx(1.0)
+    state.reset(w)
+    assert not hasattr(w, "_fp8_meta") and state.get_weight_meta(w) is not meta
+
+
+def test_process_wide_switch_reaches_other_threads_and_yields_to_a_block():
+    import threading
+
+    from astrai_b200.ops import fp8
+
+    assert fp8.fp8_linear_enabled() is False
+    fp8.fp8_linear_enable(True)
+    try:
+        seen = []
+        t = threading.Thread(target=lambda: seen.append((fp8.fp8_linear_enabled(), type(fp8.autocast_state().recipe).__name__)))
+        t.start()
+        t.join()
+        assert seen == [(True, "DelayedScaling")] and fp8.fp8_linear_enabled() is True
+        with fp8.fp8_autocast(enabled=False):
+            assert fp8.fp8_linear_enabled() is False
+        fp8.fp8_linear_enable(True, recipe=fp8.DynamicScaling())
+        assert isinstance(fp8.fp8_state().recipe, fp8.DynamicScaling)
+    finally:
+        fp8.fp8_linear_enable(False, recipe=fp8.DelayedScaling())
+    assert fp8.fp8_linear_enabled() is False
+    assert fp8.fp8_quantize is fp8.quantize_bf16 and fp8.fp8_gemm is fp8.mm_fp8
