@@ -444,13 +444,17 @@ class DDPExecutor(FlatExecutor):
     def __init__(self, grad_accum_steps: int = 1, impl: str = "auto", overlap: bool = True, dim: int = 0,
                  broadcast_buffers: bool = True, init_sync: bool = True, process_group=None, bucket_cap_mb: int = 25,
                  find_unused_parameters: bool = False, gradient_as_bucket_view: bool = False,
-                 static_graph: bool = False, mixed_precision=None, device_mesh=None):
+                 static_graph: bool = False, mixed_precision=None, device_mesh=None, check_reduction: bool = False,
+                 delay_all_reduce_named_params=None, param_to_hook_all_reduce=None):
         super().__init__(grad_accum_steps, impl, overlap)
+        # the last three only mean something to ``impl="torch"`` (they are DistributedDataParallel's own arguments)
         self._ddp_kwargs = dict(dim=dim, broadcast_buffers=broadcast_buffers, init_sync=init_sync,
                                 process_group=process_group, bucket_cap_mb=bucket_cap_mb,
                                 find_unused_parameters=find_unused_parameters,
                                 gradient_as_bucket_view=gradient_as_bucket_view, static_graph=static_graph,
-                                mixed_precision=mixed_precision, device_mesh=device_mesh)
+                                mixed_precision=mixed_precision, device_mesh=device_mesh, check_reduction=check_reduction,
+                                delay_all_reduce_named_params=delay_all_reduce_named_params,
+                                param_to_hook_all_reduce=param_to_hook_all_reduce)
         self._group = process_group
 
     def _prepare_model(self, model):
