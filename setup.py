@@ -13,7 +13,7 @@ import sys
 import warnings
 from pathlib import Path
 
-from setuptools import setup
+from setuptools import Distribution, setup
 from setuptools.command.build_py import build_py as _build_py
 
 ROOT = Path(__file__).resolve().parent
@@ -50,5 +50,43 @@ class build_py(_build_py):
         super().run()
 
 
+def _carries_extension() -> bool:
+    return (ROOT / "astrai_b200" / "ops" / "_C.so").exists() or want_extension()
+
+
+class PlatformDistribution(Distribution):
+    """Makes the wheel a platform wheel (files installed as platform-specific) when it carries ``_C.so``."""
+
+    def has_ext_modules(self):
+        return _carries_extension()
+
+
+def _commands():
+    commands = {"build_py": build_py}
+    try:
+        from setuptools.command.bdist_wheel import bdist_wheel as _bdist_wheel
+    except ImportError:  # older setuptools: the command lives in the `wheel` package
+        try:
+            from wheel.bdist_wheel import bdist_wheel as _bdist_wheel
+        except ImportError:
+            return commands
+
+    class bdist_wheel(_bdist_wheel):
+        """A wheel that carries ``_C.so`` is tied to the platform (not to a Python version: the library is loaded with
+        ``torch.ops.load_library``, it is not an import module)."""
+
+        def finalize_options(self):
+            super().finalize_options()
+            if _carries_extension():
+                self.root_is_pure = False
+
+        def get_tag(self):
+            python, abi, plat = super().get_tag()
+            return ("py3", "none", plat) if not self.root_is_pure else (python, abi, plat)
+
+    commands["bdist_wheel"] = bdist_wheel
+    return commands
+
+
 if __name__ == "__main__":
-    setup(cmdclass={"build_py": build_py})
+    setup(cmdclass=_commands(), distclass=PlatformDistribution)
