@@ -142,3 +142,71 @@ def test_custom_filter_value():
     x = _logits(2, 8, seed=9)
     out = TopKStrategy(2).apply(x, filter_value=-1e4)
     assert (out == -1e4).sum() == 12 and torch.isfinite(out).all()
+
+
+# ---- edges of the individual rules --------------------------------------------------------------------------------------
+def test_rules_that_are_switched_off_return_their_input_untouched():
+    x = _logits()
+    assert TemperatureStrategy(1.0).apply(x) is x
+    assert TopKStrategy(0).apply(x) is x
+    assert TopPStrategy(1.0).apply(x) is x
+    assert TopPStrategy(torch.ones(3)).apply(x) is x
+    assert FrequencyPenaltyStrategy(0.0).apply(x, input_ids=torch.zeros(3, 2, dtype=torch.long)) is x
+    assert FrequencyPenaltyStrategy(1.5).apply(x) is x  # nothing was generated yet
+
+
+def test_top_p_zero_keeps_only_the_most_likely_token():
+    x = _logits(rows=4, vocab=9, seed=3)
+    out = TopPStrategy(0.0).apply(x)
+    kept = torch.isfinite(out)
+    assert kept.sum(-1).tolist() == [1, 1, 1, 1] and torch.equal(out.argmax(-1), x.argmax(-1))
+
+
+def test_top_k_larger_than_the_vocabulary_keeps_everything():
+    x = _logits(vocab=5)
+    assert torch.equal(TopKStrategy(50).apply(x), x)
+    assert torch.equal(TopKStrategy(torch.tensor([50, 50, 50])).apply(x), x)
+
+
+def test_frequency_penalty_ignores_padded_history_and_follows_the_sign():
+    x = torch.zeros(2, 6)
+    history = torch.tensor([[1, 1, 4, 0], [2, 0, 0, 0]])
+    valid = torch.tensor([[1, 1, 1, 0], [1, 0, 0, 0]], dtype=torch.bool)
+    out = FrequencyPenaltyStrategy(0.5).apply(x, input_ids=history, input_mask=valid)
+    assert out[0].tolist() == [0.0, -1.0, 0.0, 0.0, -0.5, 0.0]  # token 1 twice, token 4 once; the padding zero is not counted
+    assert out[1].tolist() == [0.0, 0.0, -0.5, 0.0, 0.0, 0.0]
+    unmasked = FrequencyPenaltyStrategy(0.5).apply(x, input_ids=history)
+    assert unmasked[0, 0].item() == -0.5 and unmasked[1, 0].item() == -1.5  # without a mask every entry counts
+    boosted = FrequencyPenaltyStrategy(-1.0).apply(x, input_ids=history, input_mask=valid)
+    assert boosted[0, 1].item() == 2.0 and boosted[0, 4].item() == 1.0  # a negative penalty favours repeats
+    per_row = FrequencyPenaltyStrategy(torch.tensor([1.0, 0.0])).apply(x, input_ids=history, input_mask=valid)
+    assert per_row[0, 1].item() == -2.0 and per_row[1].abs().sum().item() == 0.0
+
+
+def test_penalty_in_the_pipeline_changes_what_greedy_like_sampling_picks():
+    x = torch.tensor([[2.0, 1.9, 0.0, 0.0]])
+    history = torch.tensor([[0, 0, 0]])
+    plain = sample(x, temperature=1.0, top_k=1)
+    penalised = sample(x, temperature=1.0, top_k=0, top_p=1.0, frequency_penalty=100.0, input_ids=history,
+                       generator=torch.Generator().manual_seed(0))
+    assert plain.item() == 0 and penalised.item() != 0
+    # top-k runs BEFORE the penalty: with k = 1 the only survivor is token 0, whatever its penalty
+    assert sample(x, temperature=1.0, top_k=1, frequency_penalty=100.0, input_ids=history).item() == 0
+
+
+def test_logprobs_are_log_probabilities_of_the_returned_tokens():
+    x = _logits(rows=5, vocab=20, seed=9)
+    g = torch.Generator().manual_seed(4)
+    tokens, logp = sample(x, temperature=0.7, top_k=6, top_p=0.9, return_logprobs=True, generator=g)
+    assert tokens.shape == logp.shape == (5,) and (logp <= 0).all() and torch.isfinite(logp).all()
+    filtered = SamplingPipeline([TemperatureStrategy(0.7), TopKStrategy(6), TopPStrategy(0.9)]).apply(x.float())
+    assert torch.allclose(logp, torch.log_softmax(filtered, -1).gather(-1, tokens[:, None])[:, 0], atol=1e-6)
+    greedy_tokens, greedy_logp = sample(x, temperature=0.0, return_logprobs=True)
+    assert torch.equal(greedy_tokens, x.argmax(-1))
+    assert torch.allclose(greedy_logp, torch.log_softmax(x, -1).max(-1).values, atol=1e-6)  # of the RAW distribution
+
+
+def test_mixed_zero_and_positive_temperatures_are_not_the_greedy_shortcut():
+    x = torch.tensor([[0.0, 5.0, 1.0], [0.0, 5.0, 1.0]])
+    out = sample(x, temperature=torch.tensor([0.0, 1.0]), generator=torch.Generator().manual_seed(0))
+    assert out[0].item() == 1  # a zero temperature is clamped to 1e-8: that row is as good as argmax
