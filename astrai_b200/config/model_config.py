@@ -26,7 +26,13 @@ class ConfigFactory(BaseFactory[BaseConfig]):
     DEFAULT_TYPE = "autoregressive_lm"
 
     @classmethod
-    def load(cls, raw: Dict[str, Any]) -> BaseConfig:
+    def load(cls, raw) -> BaseConfig:
+        """The config object for a ``config.json`` dictionary (or the path of such a file), by its ``model_type``."""
+        if not isinstance(raw, dict):
+            import json
+
+            with open(raw, "r", encoding="utf-8") as fh:
+                raw = json.load(fh)
         kind = raw.get("model_type") or cls.DEFAULT_TYPE
         return cls.get_component_class(kind).from_dict(raw)
 
