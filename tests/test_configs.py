@@ -99,7 +99,7 @@ def test_train_config_rejects_bad_values(field, value):
 
 
 def test_train_config_to_dict_holds_only_what_json_can_hold():
-    c = _train(optimizer_name="fused_adamw", optimizer_hyperparameters={"lr": 1e-3}, executor_kwargs={"comm": "nccl"})
+    c = _train(dataset=object(), optimizer_name="fused_adamw", optimizer_hyperparameters={"lr": 1e-3}, executor_kwargs={"comm": "nccl"})
     d = c.to_dict()
     json.dumps(d)  # no callables, no datasets
     assert d["strategy"] == "seq" and d["optimizer_name"] == "fused_adamw" and d["optimizer_hyperparameters"] == {"lr": 1e-3}
