@@ -192,62 +192,129 @@ def benchmark():
     """Inference benchmarks on random-init weights."""
 
 
+def _model_options(fn):
+    """Options shared by ``prefill`` and ``decode``: which model, in which precision, over which cache, on which back end
+    (the reference's ``--ckpt / --config / --dtype / --cache / --backend / --compare``, ``scripts/tools/benchmark.py:409-455``)."""
+    for opt in reversed([
+        click.option("--preset", type=click.Choice(sorted(PRESETS)), default="1b", help="Architecture when neither --ckpt nor --config is given."),
+        click.option("--ckpt", type=click.Path(exists=True, file_okay=False), default=None, help="Model directory to load instead of random weights."),
+        click.option("--config", "config_path", type=click.Path(exists=True, dir_okay=False), default=None,
+                     help="Model config JSON: random weights of that architecture."),
+        click.option("--device", default="cuda"),
+        click.option("--dtype", type=click.Choice(["bfloat16", "float16", "float32"]), default=None, help="Default: bfloat16 on CUDA, float32 on the CPU."),
+        click.option("--cache", type=click.Choice(["paged", "contiguous"]), default="paged", help="KV cache layout."),
+        click.option("--backend", type=str, default=None, help="Attention back end (tcgen05, torch_native, or a registered name); default: the process default."),
+        click.option("--compare", is_flag=True, default=False, help="Run under tcgen05 and torch_native and print both with their ratio."),
+    ]):
+        fn = opt(fn)
+    return fn
+
+
+def _load_model(preset, ckpt, config_path, device, dtype):
+    import torch
+
+    from astrai_b200.cli.common import torch_dtype
+
+    dt = torch_dtype(dtype) if dtype else (torch.bfloat16 if device != "cpu" else torch.float32)
+    if ckpt:
+        from astrai_b200.models import AutoModel
+
+        return AutoModel.from_pretrained(ckpt).to(device=device, dtype=dt).eval(), os.path.basename(os.path.normpath(ckpt))
+    if config_path:
+        from astrai_b200.config import AutoRegressiveLMConfig
+        from astrai_b200.models import AutoRegressiveLM
+
+        torch.manual_seed(0)
+        return AutoRegressiveLM(AutoRegressiveLMConfig.from_file(config_path)).to(device=device, dtype=dt).eval(), os.path.basename(config_path)
+    return build_model(preset, device, dt), preset
+
+
+def _arms(backend, compare):
+    return ["tcgen05", "torch_native"] if compare else [backend]
+
+
+def _report(rows, key):
+    for row in rows:
+        click.echo(json.dumps(row))
+    if len(rows) == 2:
+        click.echo(json.dumps({"compare": key, rows[0]["backend"] + "_over_" + rows[1]["backend"]: rows[0][key] / max(rows[1][key], 1e-12)}))
+
+
+def _scheduler(model, batch_size, max_seq_len, cache, backend, **kw):
+    from astrai_b200.inference import InferenceScheduler
+
+    return InferenceScheduler(model, _IdTokenizer(), max_batch_size=batch_size, max_seq_len=max_seq_len, paged=cache == "paged",
+                              page_size=16 if cache == "paged" else 1, backend=backend, **kw)
+
+
+def _sync(device):
+    import torch
+
+    if device != "cpu":
+        torch.cuda.synchronize()
+
+
 @benchmark.command()
-@click.option("--preset", type=click.Choice(sorted(PRESETS)), default="1b")
-@click.option("--device", default="cuda")
+@_model_options
 @click.option("--batch_size", type=int, default=8)
 @click.option("--prompt_len", type=int, default=1024)
 @click.option("--trials", type=int, default=5)
-def prefill(preset, device, batch_size, prompt_len, trials):
+def prefill(preset, ckpt, config_path, device, dtype, cache, backend, compare, batch_size, prompt_len, trials):
     """Tokens/s of packed prefill forwards through the scheduler's executor."""
     import torch
 
-    from astrai_b200.inference import InferenceScheduler
+    from astrai_b200.ops import backend as attn_backends
 
-    model = build_model(preset, device, torch.bfloat16 if device != "cpu" else torch.float32)
-    sched = InferenceScheduler(model, _IdTokenizer(), max_batch_size=batch_size, max_seq_len=prompt_len + 8)
+    model, name = _load_model(preset, ckpt, config_path, device, dtype)
     g = torch.Generator().manual_seed(0)
     prompts = [torch.randint(2, model.config.vocab_size, (prompt_len,), generator=g).tolist() for _ in range(batch_size)]
-    times = []
-    for i in range(trials + 3):
-        if device != "cpu":
-            torch.cuda.synchronize()
-        t0 = time.perf_counter()
-        sched.run_batch(prompts, max_tokens=1, temperature=0.0)
-        if device != "cpu":
-            torch.cuda.synchronize()
-        if i >= 3:
-            times.append(time.perf_counter() - t0)
-    best = min(times)
-    click.echo(json.dumps({"benchmark": "prefill", "preset": preset, "batch": batch_size, "prompt_len": prompt_len,
-                           "tok_per_s": batch_size * prompt_len / best, "ms": best * 1e3}))
+    rows = []
+    for arm in _arms(backend, compare):
+        sched = _scheduler(model, batch_size, prompt_len + 8, cache, arm)
+        times = []
+        with sched._backend_context():
+            for i in range(trials + 3):
+                _sync(device)
+                t0 = time.perf_counter()
+                sched.run_batch(prompts, max_tokens=1, temperature=0.0)
+                _sync(device)
+                if i >= 3:
+                    times.append(time.perf_counter() - t0)
+        best = min(times)
+        rows.append({"benchmark": "prefill", "model": name, "backend": sched.backend_name, "cache": cache, "batch": batch_size,
+                     "prompt_len": prompt_len, "tok_per_s": batch_size * prompt_len / best, "ms": best * 1e3})
+        del sched
+    _report(rows, "tok_per_s")
 
 
 @benchmark.command()
-@click.option("--preset", type=click.Choice(sorted(PRESETS)), default="1b")
-@click.option("--device", default="cuda")
+@_model_options
 @click.option("--batch_size", type=int, default=16)
 @click.option("--prompt_len", type=int, default=128)
 @click.option("--gen_len", type=int, default=256)
 @click.option("--cuda_graph/--no-cuda_graph", default=True)
-def decode(preset, device, batch_size, prompt_len, gen_len, cuda_graph):
+def decode(preset, ckpt, config_path, device, dtype, cache, backend, compare, batch_size, prompt_len, gen_len, cuda_graph):
     """Decode tokens/s through scheduler + sampler (+ CUDA graphs)."""
     import torch
 
-    from astrai_b200.inference import InferenceScheduler
-
-    model = build_model(preset, device, torch.bfloat16 if device != "cpu" else torch.float32)
-    sched = InferenceScheduler(model, _IdTokenizer(), max_batch_size=batch_size, max_seq_len=prompt_len + gen_len + 8,
-                               enable_cuda_graph=cuda_graph)
+    model, name = _load_model(preset, ckpt, config_path, device, dtype)
     g = torch.Generator().manual_seed(0)
     prompts = [torch.randint(2, model.config.vocab_size, (prompt_len,), generator=g).tolist() for _ in range(batch_size)]
-    sched.run_batch(prompts, max_tokens=8, temperature=0.0)  # warm-up (graph capture included)
-    t0 = time.perf_counter()
-    out = sched.run_batch(prompts, max_tokens=gen_len, temperature=0.0)
-    dt = time.perf_counter() - t0
-    n = sum(len(o[0]) if isinstance(o, tuple) else len(o) for o in out)
-    click.echo(json.dumps({"benchmark": "decode", "preset": preset, "batch": batch_size, "gen_len": gen_len,
-                           "tok_per_s": n / dt, "ms_per_step": dt * 1e3 / max(gen_len, 1)}))
+    rows = []
+    for arm in _arms(backend, compare):
+        sched = _scheduler(model, batch_size, prompt_len + gen_len + 8, cache, arm, enable_cuda_graph=cuda_graph)
+        with sched._backend_context():
+            sched.run_batch(prompts, max_tokens=8, temperature=0.0)  # warm-up
+            _sync(device)
+            t0 = time.perf_counter()
+            out = sched.run_batch(prompts, max_tokens=gen_len, temperature=0.0)
+            _sync(device)
+            dt = time.perf_counter() - t0
+        n = sum(len(o[0]) if isinstance(o, tuple) else len(o) for o in out)
+        rows.append({"benchmark": "decode", "model": name, "backend": sched.backend_name, "cache": cache, "cuda_graph": sched.cuda_graph_enabled,
+                     "batch": batch_size, "gen_len": gen_len, "tok_per_s": n / dt, "ms_per_step": dt * 1e3 / max(gen_len, 1)})
+        del sched
+    _report(rows, "tok_per_s")
 
 
 @benchmark.command()

@@ -59,3 +59,33 @@ def test_serve_load_generator_on_cpu():
     finally:
         sched.stop()
     assert res["completed"] == 5 and res["output_tokens"] >= 15 and res["ttft_ms_p50"] > 0 and res["tpot_ms_p50"] > 0
+
+
+def test_benchmark_tool_takes_the_references_model_cache_and_backend_options(tmp_path):
+    from astrai_b200.cli.benchmark import PRESETS, benchmark
+
+    cfg = tmp_path / "arch.json"
+    cfg.write_text(json.dumps({**PRESETS["tiny"], "num_hidden_layers": 1, "rms_norm_eps": 1e-6, "tie_word_embeddings": True, "rope_theta": 10000.0}))
+    res = CliRunner().invoke(benchmark, ["prefill", "--config", str(cfg), "--device", "cpu", "--cache", "contiguous", "--backend", "torch_native",
+                                         "--batch_size", "2", "--prompt_len", "24", "--trials", "1"])
+    assert res.exit_code == 0, (res.output, res.exception)
+    row = json.loads(res.output.strip().splitlines()[-1])
+    assert row["benchmark"] == "prefill" and row["model"] == "arch.json" and row["cache"] == "contiguous" and row["backend"] == "torch_native"
+    assert row["tok_per_s"] > 0
+
+    res = CliRunner().invoke(benchmark, ["decode", "--preset", "tiny", "--device", "cpu", "--dtype", "float32", "--compare", "--batch_size", "2",
+                                         "--prompt_len", "8", "--gen_len", "4"])
+    assert res.exit_code == 0, (res.output, res.exception)
+    lines = [json.loads(line) for line in res.output.strip().splitlines()]
+    assert [r.get("benchmark") for r in lines] == ["decode", "decode", None] and lines[0]["cache"] == "paged"
+    assert "compare" in lines[2] and any("_over_" in k for k in lines[2])
+    assert lines[0]["cuda_graph"] is False  # a CPU model captures nothing
+
+    from astrai_b200.config import AutoRegressiveLMConfig
+    from astrai_b200.models import AutoRegressiveLM
+
+    model_dir = tmp_path / "model"
+    AutoRegressiveLM(AutoRegressiveLMConfig.from_file(cfg)).save_pretrained(str(model_dir))
+    res = CliRunner().invoke(benchmark, ["decode", "--ckpt", str(model_dir), "--device", "cpu", "--batch_size", "1", "--prompt_len", "4", "--gen_len", "2"])
+    assert res.exit_code == 0, (res.output, res.exception)
+    assert json.loads(res.output.strip().splitlines()[-1])["model"] == "model"
