@@ -116,7 +116,8 @@ def build_train_config(o: Dict[str, Any]):
         max_grad_norm=o["max_grad_norm"], gradient_checkpointing_modules=[DecoderBlock] if o["gradient_checkpointing"] else [],
         compile_mode=o["compile"], start_epoch=o["start_epoch"], start_samples=o["start_samples"], ckpt_dir=o["ckpt_dir"],
         ckpt_interval=o["ckpt_interval"], metrics=list(o["metrics"]), random_seed=o["random_seed"], num_workers=o["num_workers"],
-        pin_memory=o["pin_memory"], nprocs=o["nprocs"], backend=o["backend"], master_addr=o["master_addr"],
+        pin_memory=o["pin_memory"], persistent_workers=o.get("persistent_workers", True), moe_aux_loss_coef=o.get("moe_aux_loss_coef", 0.01),
+        nprocs=o["nprocs"], backend=o["backend"], master_addr=o["master_addr"],
         master_port=str(o["master_port"]), parallel_mode=o["parallel_mode"], tp_size=o["tp_size"] or 1,
         cp_size=o.get("cp_size") or 1, ep_size=o.get("ep_size") or 1, pp_size=o.get("pp_size") or 1,
         start_method=o["start_method"], device_type=o["device_type"], val_split=o["val_split"], val_step=o["val_step"],
@@ -177,6 +178,7 @@ def plan(o: Dict[str, Any]) -> Dict[str, Any]:
 @click.option("--random_seed", type=int, default=3407, help="Seed of the shuffling and of the validation split.")
 @click.option("--num_workers", type=int, default=4, help="Data-loader worker processes.")
 @click.option("--pin_memory/--no-pin_memory", default=True, help="Page-locked host batches.")
+@click.option("--persistent_workers/--no-persistent_workers", default=True, help="Keep the data-loader workers alive between epochs.")
 # checkpoints / validation / logging
 @click.option("--ckpt_interval", type=int, default=5000, help="Optimizer steps between checkpoints.")
 @click.option("--ckpt_dir", type=str, default="checkpoint", help="Where checkpoints and metric logs go.")
@@ -218,6 +220,7 @@ def plan(o: Dict[str, Any]) -> Dict[str, Any]:
 @click.option("--group_size", type=int, default=4, help="grpo: responses per prompt.")
 @click.option("--grpo_clip_eps", type=float, default=0.2, help="grpo: clip range of the probability ratio.")
 @click.option("--grpo_kl_coef", type=float, default=0.01, help="grpo: weight of the KL term against the reference model.")
+@click.option("--moe_aux_loss_coef", type=float, default=0.01, help="Weight of the mixture-of-experts load-balancing loss (0 = off).")
 @click.option("--neftune_alpha", type=float, default=0.0, help="NEFTune noise on the embeddings while training (0 = off).")
 # rollout
 @click.option("--rollout_interval", type=int, default=512, help="online_*: samples between two rounds of generation.")
