@@ -734,3 +734,37 @@ def test_generate_hands_the_callers_backend_to_the_request(served, monkeypatch):
         assert seen == [None, ab.ATTN_BACKEND.TORCH_NATIVE, ab.ATTN_BACKEND.TORCH_NATIVE] and first == second == streamed
     finally:
         engine.shutdown()
+
+
+def test_http_rejects_malformed_requests_before_they_reach_the_engine(served):
+    from fastapi.testclient import TestClient
+
+    from astrai_b200.inference import InferenceEngine
+    from astrai_b200.inference.network import app as app_mod
+
+    model, tok = served
+    engine = InferenceEngine(model, tok, max_batch_size=2, max_seq_len=96, enable_cuda_graph=False)
+    app = app_mod.get_app()
+    old = app.state.engine, app.state.server_config
+    app.state.engine, app.state.server_config = engine, {"_test": True}
+    try:
+        client = TestClient(app)
+        before = engine.get_stats()["total_tasks"]
+        ok = {"messages": [{"role": "user", "content": "hi"}]}
+        for bad in ({}, {"messages": "hi"}, {**ok, "max_tokens": 0}, {**ok, "temperature": 2.5}, {**ok, "top_p": 1.5}, {**ok, "top_k": 0},
+                    {**ok, "frequency_penalty": 3.0}, {"messages": [{"content": "no role"}]}):
+            assert client.post("/v1/chat/completions", json=bad).status_code == 422, bad
+        for bad in ({}, {"messages": [{"role": "user"}]}, {"messages": [{"role": "user", "content": "x"}], "max_tokens": 0},
+                    {"messages": [{"role": "user", "content": "x"}], "stop_sequences": "END"}):
+            assert client.post("/v1/messages", json=bad).status_code == 422, bad
+        assert client.post("/v1/chat/completions", content=b"{not json", headers={"content-type": "application/json"}).status_code == 422
+        assert engine.get_stats()["total_tasks"] == before
+        assert client.get("/nowhere").status_code == 404 and client.get("/v1/chat/completions").status_code == 405
+        # an empty conversation is a valid request: the model answers the bare generation prompt
+        r = client.post("/v1/chat/completions", json={"messages": [], "max_tokens": 2, "temperature": 0.0})
+        assert r.status_code == 200 and r.json()["usage"]["completion_tokens"] <= 2
+        stats = client.get("/stats").json()
+        assert {"total_tasks", "total_tokens", "active_tasks", "waiting_queue"} <= set(stats) and stats["total_tasks"] == before + 1
+    finally:
+        app.state.engine, app.state.server_config = old
+        engine.shutdown()
