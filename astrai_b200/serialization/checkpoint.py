@@ -125,10 +125,26 @@ def load_model_weights(save_directory: PathLike) -> dict:
 REQUIRED_FOR_RESUME = (META_FILE, CONFIG_FILE, WEIGHTS_FILE, "optimizer.pt", "scheduler.pt")
 
 
-def is_complete(ckpt_dir: PathLike, need=REQUIRED_FOR_RESUME) -> bool:
-    """True when every file a resume needs exists and is non-empty (the rule of the reference's
-    ``scripts/docker/lib/train-common.sh:25-66``)."""
+def is_complete(ckpt_dir: PathLike, need=None) -> bool:
+    """True when a run can resume from ``ckpt_dir``: every file it needs exists and is non-empty.
+
+    A checkpoint written here lists its files in ``meta.json`` (``files``): those must all be there, the optimizer state
+    among them (a run without a learning-rate scheduler writes no ``scheduler.pt`` and is complete without it).  A
+    directory without that list is held to the fixed set of the reference's tooling
+    (``scripts/docker/lib/train-common.sh:25-66``: meta, config, weights, optimizer, scheduler)."""
     root = Path(ckpt_dir)
+    if need is None:
+        need = REQUIRED_FOR_RESUME
+        meta_path = root / META_FILE
+        if meta_path.is_file() and meta_path.stat().st_size > 0:
+            try:
+                listed = json.loads(meta_path.read_text(encoding="utf-8")).get("files")
+            except (OSError, ValueError, AttributeError):
+                listed = None  # not this writer's file: the fixed set decides
+            if isinstance(listed, list) and listed:
+                if "optimizer.pt" not in listed:
+                    return False
+                need = [META_FILE, *listed]
     return all((root / n).is_file() and (root / n).stat().st_size > 0 for n in need)
 
 
@@ -171,8 +187,9 @@ class Checkpoint:
         save_safetensors(self.state_dict, tmp / WEIGHTS_FILE)
         for name, obj in self.extra.items():
             save_torch(obj, tmp / f"{name}.pt")
+        written = sorted(p.name for p in tmp.iterdir())
         meta = {"epoch": self.epoch, "consumed_samples": self.consumed_samples,
-                "timestamp": time.strftime("%Y-%m-%dT%H:%M:%S"), **self.meta}
+                "timestamp": time.strftime("%Y-%m-%dT%H:%M:%S"), **self.meta, "files": written}
         save_json(meta, tmp / META_FILE)  # last: its presence marks a complete checkpoint
         if final.exists():
             # keep files other writers placed there (metric.jsonl), replace ours

@@ -126,3 +126,29 @@ def test_rank_zero_reads_and_every_rank_receives(tmp_path):
         assert res["keys"] == sorted(_state()) and res["sum"] == pytest.approx(want_sum) and res["bsd_sum"] == pytest.approx(want_sum)
         assert res["extra"] == ["optimizer", "scheduler"] and res["opt_step"] == 5 and res["config"] == {"hidden_size": 4}
         assert "torch.bfloat16" in res["dtypes"]  # dtypes survive the wire
+
+
+def test_completeness_follows_the_checkpoints_own_file_list(tmp_path):
+    """A run without a scheduler writes no scheduler.pt and can still be resumed; a checkpoint without optimizer state, or
+    with one of its listed files missing or empty, cannot."""
+    import os
+
+    from astrai_b200.serialization import Checkpoint, is_complete, latest_complete
+
+    weights = {"w": torch.ones(2, 2)}
+    full = tmp_path / "epoch_0_step_1"
+    Checkpoint(state_dict=weights, extra={"optimizer": {"state": {}}, "scheduler": {"last_epoch": 1}}, config={"a": 1}).save(full)
+    no_sched = tmp_path / "epoch_0_step_2"
+    Checkpoint(state_dict=weights, extra={"optimizer": {"state": {}}}, config={"a": 1}).save(no_sched)
+    weights_only = tmp_path / "epoch_0_step_3"
+    Checkpoint(state_dict=weights, config={"a": 1}).save(weights_only)
+    assert is_complete(full) and is_complete(no_sched) and not is_complete(weights_only)
+    assert latest_complete(tmp_path) == no_sched
+    import json
+
+    assert json.load(open(no_sched / "meta.json"))["files"] == ["config.json", "model.safetensors", "optimizer.pt"]
+    os.truncate(no_sched / "optimizer.pt", 0)
+    assert not is_complete(no_sched) and latest_complete(tmp_path) == full
+    os.remove(full / "scheduler.pt")  # listed but gone
+    assert not is_complete(full) and latest_complete(tmp_path) is None
+    assert is_complete(weights_only, need=["meta.json", "model.safetensors"])  # an explicit list still decides alone
