@@ -2,6 +2,8 @@
 
 import json
 
+import pytest
+
 from click.testing import CliRunner
 
 from astrai_b200.cli import runtime
@@ -89,3 +91,83 @@ def test_benchmark_tool_takes_the_references_model_cache_and_backend_options(tmp
     res = CliRunner().invoke(benchmark, ["decode", "--ckpt", str(model_dir), "--device", "cpu", "--batch_size", "1", "--prompt_len", "4", "--gen_len", "2"])
     assert res.exit_code == 0, (res.output, res.exception)
     assert json.loads(res.output.strip().splitlines()[-1])["model"] == "model"
+
+
+# ---- how the options become a training configuration -------------------------------------------------------------------------
+def _options(tmp_path, *argv):
+    """The merged option dictionary the command would train with (what --dry-run sees, before it is cut down to the plan)."""
+    import click
+
+    from astrai_b200.cli.common import flatten_sections, load_yaml, merge_config
+    from astrai_b200.cli.train import SECTIONS
+
+    ctx = train_command.make_context("train", list(argv))
+    return merge_config(ctx, dict(ctx.params), flatten_sections(load_yaml(ctx.params.get("config")), SECTIONS))
+
+
+def _tiny_run(tmp_path):
+    import torch
+
+    from astrai_b200.serialization import save_bin
+
+    params, data = tmp_path / "params", tmp_path / "data"
+    params.mkdir()
+    (params / "config.json").write_text(json.dumps(dict(vocab_size=64, hidden_size=16, num_hidden_layers=2, num_attention_heads=2,
+                                                        num_key_value_heads=1, intermediate_size=32, max_position_embeddings=16,
+                                                        rms_norm_eps=1e-6, rope_theta=10000.0, tie_word_embeddings=False)))
+    save_bin(str(data / "shard_0000"), {"sequence": [torch.arange(0, 64).repeat(20).int()]})
+    return ["--train_type", "seq", "--data_root_path", str(data), "--param_path", str(params), "--device_type", "cpu"]
+
+
+def test_optimizer_scheduler_and_strategy_options_reach_their_constructors(tmp_path):
+    from astrai_b200.cli.train import optimizer_kwargs, scheduler_kwargs, strategy_kwargs
+
+    base = _tiny_run(tmp_path)
+    o = _options(tmp_path, *base, "--optimizer", "muon_adamw", "--muon_momentum", "0.9", "--no-muon_nesterov", "--muon_ns_steps", "3")
+    assert optimizer_kwargs(o) == {"lr": 3e-4, "weight_decay": 0.1, "muon_momentum": 0.9, "muon_nesterov": False, "muon_ns_steps": 3,
+                                   "muon_adjust_lr": "match_rms_adamw"}
+    o = _options(tmp_path, *base, "--optimizer", "nora_nadamw", "--nora_lr", "0.01", "--max_lr", "1e-3")
+    assert optimizer_kwargs(o) == {"lr": 1e-3, "weight_decay": 0.1, "nora_lr": 0.01, "nora_beta": 0.95, "nora_momentum": 0.95, "nora_weight_decay": 0.0}
+    o = _options(tmp_path, *base, "--optimizer", "mano_adamw", "--no-mano_nesterov")
+    assert optimizer_kwargs(o)["mano_nesterov"] is False and "muon_momentum" not in optimizer_kwargs(o)
+    assert set(optimizer_kwargs(_options(tmp_path, *base, "--optimizer", "fused_adamw"))) == {"lr", "weight_decay"}
+
+    o = _options(tmp_path, *base, "--schedule_type", "sgdr", "--t_mult", "3", "--min_rate", "0.2", "--warmup_ratio", "0.1")
+    assert scheduler_kwargs(o, 200) == {"warmup_steps": 20, "min_rate": 0.2, "cycle_length": 180, "t_mult": 3}
+    o = _options(tmp_path, *base, "--schedule_type", "sgdr", "--cycle_length", "40")
+    assert scheduler_kwargs(o, 200)["cycle_length"] == 40
+    o = _options(tmp_path, *base, "--schedule_type", "wsd", "--stable_steps", "50", "--decay_steps", "10", "--warmup_ratio", "0")
+    assert scheduler_kwargs(o, 100) == {"warmup_steps": 0, "stable_steps": 50, "decay_steps": 10}
+    assert scheduler_kwargs(_options(tmp_path, *base), 100) == {"warmup_steps": 5, "lr_decay_steps": 95}
+
+    assert strategy_kwargs(_options(tmp_path, *base, "--label_smoothing", "0.1")) == {"label_smoothing": 0.1}
+    assert strategy_kwargs(_options(tmp_path, *base[:1], "dpo", *base[2:], "--dpo_beta", "0.3")) == {"beta": 0.3}
+    assert strategy_kwargs(_options(tmp_path, *base[:1], "online_grpo", *base[2:], "--group_size", "8", "--grpo_kl_coef", "0.05")) == {
+        "clip_eps": 0.2, "kl_coef": 0.05, "group_size": 8}
+
+
+@pytest.mark.parametrize("argv,expect", [
+    (["--parallel_mode", "fsdp", "--fsdp_comm", "nvls"], {"comm": "nvls"}),
+    (["--parallel_mode", "fsdp", "--fsdp_reshard"], {"comm": "nccl", "reshard": True, "impl": "flat"}),
+    (["--parallel_mode", "tp", "--tp_size", "2", "--mp_comm", "nccl"], {"comm": "nccl"}),
+    (["--parallel_mode", "ep"], {"comm": "p2p"}),
+    (["--parallel_mode", "pp", "--pp_size", "2", "--pp_chunks", "4"], {"chunks": 4}),
+    (["--parallel_mode", "cp", "--cp_size", "2", "--fsdp_comm", "nccl"], {"attn_comm": "p2p", "comm": "nccl"}),
+    (["--parallel_mode", "ddp"], {}),
+])
+def test_parallel_options_become_executor_arguments(tmp_path, argv, expect):
+    from astrai_b200.cli.train import build_train_config
+
+    cfg, steps = build_train_config(_options(tmp_path, *_tiny_run(tmp_path), "--nprocs", "2", "--window_size", "16", "--batch_per_device", "2",
+                                             "--grad_accum_steps", "2", "--n_epoch", "3", "--gradient_checkpointing", "--moe_aux_loss_coef", "0.05",
+                                             "--no-persistent_workers", *argv))
+    assert cfg.executor_kwargs == expect and cfg.parallel_mode == argv[1] and cfg.nprocs == 2
+    assert cfg.moe_aux_loss_coef == 0.05 and cfg.persistent_workers is False and len(cfg.gradient_checkpointing_modules) == 1
+    # 1280 tokens in windows of 16 -> 79 samples; ranks of one model-parallel block read the same samples
+    readers = 1 if argv[1] in ("tp", "pp", "cp") else 2
+    per_rank = -(-len(cfg.dataset) // readers)
+    assert steps == max(-(-per_rank // 2) // 2, 1) * 3
+    model = cfg.model_fn()
+    assert model.config.hidden_size == 16 and next(model.parameters()).dtype.is_floating_point
+    sched = cfg.scheduler_fn(cfg.optimizer_fn(model))
+    assert sched.get_last_lr()[0] <= 3e-4
