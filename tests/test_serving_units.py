@@ -768,3 +768,56 @@ def test_http_rejects_malformed_requests_before_they_reach_the_engine(served):
     finally:
         app.state.engine, app.state.server_config = old
         engine.shutdown()
+
+
+def test_submit_stream_and_cancel_from_many_threads_leaks_nothing(served):
+    """Callers on eight threads submit, read a little, walk away, finish, or cancel by id, all at once; afterwards every
+    page and every request row is back, nothing is queued, and the engine still answers."""
+    import random
+
+    from astrai_b200.inference import InferenceEngine
+
+    model, tok = served
+    engine = InferenceEngine(model, tok, max_batch_size=4, max_seq_len=64, enable_cuda_graph=False, kv_cache_tokens=4 * 64, page_size=16)
+    pool = engine.scheduler._cache
+    pages_at_rest = pool.allocator.available()
+    errors, finished = [], []
+
+    def caller(seed):
+        rng = random.Random(seed)
+        try:
+            for i in range(6):
+                prompt = "hello " * rng.randint(1, 4) + str(seed)
+                kind = rng.choice(["full", "abandon", "cancel_id", "stream_full"])
+                if kind == "full":
+                    finished.append(engine.generate(prompt, max_tokens=rng.randint(1, 6), temperature=0.0))
+                elif kind == "stream_full":
+                    finished.append("".join(engine.generate(prompt, stream=True, max_tokens=rng.randint(1, 6), temperature=0.0)))
+                elif kind == "abandon":
+                    stream = engine.generate(prompt, stream=True, max_tokens=30, temperature=0.0)
+                    for n, _ in enumerate(stream):
+                        if n >= rng.randint(0, 2):
+                            break
+                    stream.close()
+                else:
+                    tid = engine.scheduler.add_task(prompt, max_tokens=30, temperature=0.0, stream_callback=lambda piece: None)
+                    time.sleep(rng.random() * 0.02)
+                    engine.scheduler.remove_task(tid)
+        except Exception as exc:  # noqa: BLE001 - reported below
+            errors.append(repr(exc))
+
+    try:
+        threads = [threading.Thread(target=caller, args=(s,)) for s in range(8)]
+        for t in threads:
+            t.start()
+        for t in threads:
+            t.join(timeout=120)
+        assert not any(t.is_alive() for t in threads) and errors == []
+        assert _wait_until(lambda: engine.get_stats()["active_tasks"] == 0 and engine.get_stats()["waiting_queue"] == 0, timeout=30)
+        assert _wait_until(lambda: pool.allocator.available() == pages_at_rest, timeout=10)  # retained prefix pages count as available
+        assert engine.scheduler._cancelled == [] and all(isinstance(x, str) for x in finished)
+        assert engine.generate("still here", max_tokens=2, temperature=0.0) is not None
+        # every request row is free again: a full batch can be admitted
+        assert len(engine.generate(["a", "b", "c", "d"], max_tokens=1, temperature=0.0)) == 4
+    finally:
+        engine.shutdown()
