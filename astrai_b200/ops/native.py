@@ -88,3 +88,12 @@ def kernel_available(name: str = "") -> bool:
     if not _state["loaded"] and not _LIB.exists():
         return False
     return load(build_if_missing=False)
+
+
+def get_module(name: str):
+    """The loaded operator ``torch.ops.astrai_b200.<name>``, or ``None`` when the extension (or that operator) is not there -
+    the lookup of the reference's loader (``astrai/extension/loader.py:51-54``), one namespace instead of one module per
+    kernel."""
+    if not kernel_available(name):
+        return None
+    return getattr(torch.ops.astrai_b200, name, None)
