@@ -39,8 +39,8 @@ def test_1f1b_schedule_properties(stages, micro):
         assert peak == min(stages - s, micro)  # activation memory bound of 1F1B
 
 
-@pytest.mark.parametrize("stages,micro,moe,sft", [(2, 4, False, False), (3, 2, False, False), (4, 4, False, False), (2, 2, True, False),
-                                                  (2, 4, False, True), (3, 2, True, True)])
+@pytest.mark.parametrize("stages,micro,moe,sft", [(3, 2, False, False), (4, 4, False, False), (2, 2, True, False), (2, 4, False, True),
+                                                  (3, 2, True, True)])
 def test_pipeline_step_matches_whole_model(tmp_path, stages, micro, moe, sft):
     """Gradients and loss of one 1F1B window equal those of the whole model; with ``sft`` the batch holds packed documents
     with position ids and an uneven loss mask, and the whole model sees the batch in ONE piece (mean over trained tokens)."""
