@@ -147,8 +147,10 @@ class TensorParallelExecutor(ModelParallelExecutor):
 
     Every rank of a block reads the same batch; rank ``r`` keeps token rows ``[r*T/tp, (r+1)*T/tp)`` between the layers
     and computes the loss on those rows, so per-token tensors of the batch other than ``input_ids`` / ``position_ids``
-    are cut to those rows by :meth:`shard_batch`.  Objectives that need whole sequences on one rank (DPO, GRPO) are
-    not sharded this way and raise."""
+    are cut to those rows by :meth:`shard_batch`.  Objectives over whole sequences (DPO, GRPO) keep the batch whole on
+    every rank: each rank scores its token rows and the per-token log-probabilities are gathered over the block
+    (``trainer/strategy.py::token_logprobs``), so every rank evaluates the same loss; the frozen reference / behaviour
+    models are whole replicas."""
 
     mode = "tp"
     PER_TOKEN = ("target_ids", "loss_mask")
@@ -180,10 +182,39 @@ class TensorParallelExecutor(ModelParallelExecutor):
     def data_parallel_rank(self):
         return self.mesh.dp_rank if self.mesh else 0
 
+    @staticmethod
+    def _widen(t: torch.Tensor, width: int) -> torch.Tensor:
+        return t if t.shape[-1] == width else torch.nn.functional.pad(t, (0, width - t.shape[-1]))
+
+    def pad_sequences(self, batch):
+        """Sequence-level batches (preference pairs, response groups) keep whole sequences on every rank, but the model
+        still cuts the batch's ``rows x length`` tokens into equal row blocks: widen the sequences with padding (id 0,
+        mask 0) until the token count divides over the block.  Called by the strategies before they build masks."""
+        tp = self.mesh.mp_size if self.mesh is not None else 1
+        if tp <= 1:
+            return batch
+        out = dict(batch)
+        if "chosen" in batch and "rejected" in batch:
+            rows, length = 2 * batch["chosen"].shape[0], max(batch["chosen"].shape[1], batch["rejected"].shape[1])
+            while rows * length % tp:
+                length += 1
+            for key in ("chosen", "rejected", "chosen_mask", "rejected_mask"):
+                out[key] = self._widen(batch[key], length)
+        elif "responses" in batch and "prompts" in batch:
+            b, g, rlen = batch["responses"].shape
+            plen = batch["prompts"].shape[1]
+            while b * g * (plen + rlen) % tp:
+                rlen += 1
+            for key in ("responses", "masks"):
+                out[key] = self._widen(batch[key], rlen)
+        return out
+
     def shard_batch(self, batch):
         if "input_ids" not in batch or "target_ids" not in batch:
-            raise NotImplementedError("tensor parallelism shards token-level objectives (seq, sft); this batch has no "
-                                      "input_ids / target_ids pair")
+            if ("chosen" in batch and "rejected" in batch) or ("responses" in batch and "prompts" in batch):
+                return batch  # whole sequences everywhere: the model cuts token rows itself, log-probabilities are gathered
+            raise NotImplementedError("tensor parallelism takes token-level batches (input_ids / target_ids), preference pairs "
+                                      f"(chosen / rejected) or response groups (prompts / responses); got keys {sorted(batch)}")
         tp, r = self.mesh.mp_size, self.mesh.mp_rank
         out = dict(batch)
         for key in self.PER_TOKEN:

@@ -216,6 +216,36 @@ def gemm_reducescatter(x: Tensor, w: Tensor, w_kmajor: bool = True, ctx: Optiona
 
 
 # --------------------------------------------------------------------------- autograd + modules
+class _GatherRowValues(Function):
+    """Per-row scalars of this rank's token rows -> the values of every row of the block, on every rank.
+
+    For objectives that are not sums over tokens (sequence log-probabilities of preference and policy-gradient losses):
+    every rank then computes the SAME loss from the same full vector.  The executors average gradients over the ranks
+    of a block (their convention is one partial loss per rank), so the backward hands this rank's slice of the incoming
+    gradient back multiplied by the block size: summed over the block and divided by its size, that is the gradient of
+    the loss counted once."""
+
+    @staticmethod
+    def forward(ctx, values, group, rank, world):
+        ctx.rank, ctx.world, ctx.n = rank, world, values.numel()
+        full = torch.empty(world * values.numel(), dtype=values.dtype, device=values.device)
+        dist.all_gather_into_tensor(full, values.contiguous(), group=group)
+        return full
+
+    @staticmethod
+    def backward(ctx, g):
+        return g[ctx.rank * ctx.n:(ctx.rank + 1) * ctx.n] * float(ctx.world), None, None, None
+
+
+def gather_row_values(values: Tensor) -> Tensor:
+    """``[rows / tp]`` values of the local token rows -> ``[rows]`` on every rank of the tensor-parallel group
+    (differentiable; see :class:`_GatherRowValues`)."""
+    group, world = _group_world(get_context())
+    if world <= 1:
+        return values
+    return _GatherRowValues.apply(values, group, dist.get_rank(group), world)
+
+
 class _ColumnParallelFn(Function):
     @staticmethod
     def forward(ctx, x_local, w, comm):

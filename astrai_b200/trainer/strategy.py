@@ -84,8 +84,30 @@ def _head_weight(inner) -> Tensor:
     return w
 
 
+def _token_logprobs_tensor_parallel(model, inner, input_ids: Tensor, input_mask):
+    """The same ``[B, S-1]`` log-probabilities from a tensor-parallel model: every rank scores its own token rows of the
+    whole ``[B, S]`` input (the target of a position is the next token; the last position of a row has none) and the
+    per-token values are gathered, so that sequence-level objectives see whole sequences on every rank."""
+    from astrai_b200.parallel.tensor_parallel import gather_row_values
+
+    b, s = input_ids.shape
+    tp, rank = inner._tp_size, inner._tp_rank
+    local = b * s // tp
+    targets = torch.cat([input_ids[:, 1:], input_ids.new_zeros(b, 1)], dim=1).reshape(-1)[rank * local:(rank + 1) * local]
+    if getattr(inner, "supports_fused_head", False) and input_ids.is_cuda:
+        out = model(input_ids, input_mask, return_logits=False)
+        lp = ops.linear_token_logprobs(out["hidden_states"], _head_weight(inner), targets)
+    else:
+        out = model(input_ids, input_mask)
+        lp = torch.log_softmax(out["logits"].float(), dim=-1).gather(-1, targets.unsqueeze(-1)).squeeze(-1)
+    return gather_row_values(lp).view(b, s)[:, :-1], out
+
+
 def token_logprobs(model, input_ids: Tensor, input_mask: Optional[Tensor], position_ids: Optional[Tensor] = None):
     """Log-probability of ``input_ids[:, 1:]`` under the model, shape ``[B, S-1]`` fp32, plus the forward outputs."""
+    sharded = getattr(model, "module", model)
+    if getattr(sharded, "_tp_size", 1) > 1:
+        return _token_logprobs_tensor_parallel(model, sharded, input_ids, input_mask)
     ids_in, ids_out = input_ids[:, :-1], input_ids[:, 1:]
     if isinstance(input_mask, AttentionSegments):
         input_mask = input_mask.drop_last()
@@ -189,6 +211,12 @@ class BaseStrategy:
         shard = getattr(self.executor, "shard_batch", None)
         return shard(batch) if shard is not None else batch
 
+    def _whole_sequences(self, batch: Dict[str, Tensor]) -> Dict[str, Tensor]:
+        """A sequence-level batch as the executor needs it laid out (a tensor-parallel block pads the sequences so that the
+        batch's tokens divide over its ranks); other executors leave it alone."""
+        pad = getattr(self.executor, "pad_sequences", None)
+        return pad(batch) if pad is not None else batch
+
     def compute_loss_output(self, batch) -> LossOutput:
         out = self.compute_loss(batch)
         return out if isinstance(out, dict) else {"loss": out, "metrics": DeferredMetrics(loss=out.detach())}
@@ -285,6 +313,7 @@ class DPOStrategy(BaseStrategy):
         self.ref_model, self.beta, self.reduction = ref_model, beta, reduction
 
     def compute_loss_output(self, batch) -> LossOutput:
+        batch = self._whole_sequences(batch)
         mask = padded_causal_attention(torch.cat([batch["chosen"], batch["rejected"]], dim=0).ne(0))
         batch = self._to_rank(batch)
         n = batch["chosen"].shape[0]
@@ -330,7 +359,7 @@ class GRPOStrategy(BaseStrategy):
             self.old_model.load_state_dict(sd)
 
     def compute_loss_output(self, batch) -> LossOutput:
-        batch = self._to_rank(batch)
+        batch = self._to_rank(self._whole_sequences(batch))
         prompts, responses, masks, rewards = batch["prompts"], batch["responses"], batch["masks"], batch["rewards"]
         b, g, rlen = responses.shape
         resp = responses.reshape(b * g, rlen)

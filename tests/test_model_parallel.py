@@ -88,6 +88,46 @@ def test_tensor_parallel_supervised_objective_is_the_mean_over_all_trained_token
     assert run["val"] == pytest.approx(sft_ref["val"], abs=2e-5)
 
 
+@pytest.mark.parametrize("strategy", ["dpo", "grpo"])
+def test_tensor_parallel_sequence_level_objectives_match_single_process(tmp_path, strategy):
+    """Preference pairs and scored response groups: every rank scores its token rows, the per-token log-probabilities are
+    gathered over the block and every rank evaluates the same loss against whole frozen reference models."""
+    ref = _run(tmp_path, f"ref{strategy}", 1, "--mode", "none", "--strategy", strategy)
+    run = _run(tmp_path, f"tp{strategy}", 2, "--mode", "tp", "--strategy", strategy)
+    _same(run, ref)
+
+
+def test_tensor_parallel_pads_sequence_level_batches_until_their_tokens_divide():
+    from astrai_b200.parallel import ExecutorFactory
+    from astrai_b200.parallel.mesh import ParallelMesh
+
+    ex = ExecutorFactory.create("tp", grad_accum_steps=1, size=8)
+    ex.mesh = ParallelMesh(world=8, rank=3, mp_size=8)
+    pairs = {"chosen": torch.ones(3, 5, dtype=torch.long), "rejected": torch.ones(3, 5, dtype=torch.long),
+             "chosen_mask": torch.ones(3, 5, dtype=torch.bool), "rejected_mask": torch.ones(3, 5, dtype=torch.bool)}
+    out = ex.pad_sequences(pairs)
+    assert out["chosen"].shape == (3, 8) and (6 * 8) % 8 == 0  # 6 rows: the first length from 5 up whose tokens divide by 8
+    assert out["chosen"][:, 5:].eq(0).all() and not out["chosen_mask"][:, 5:].any() and out["chosen"][:, :5].eq(1).all()
+    assert ex.shard_batch(out) is out  # whole sequences stay on every rank
+    groups = {"prompts": torch.ones(2, 3, dtype=torch.long), "responses": torch.ones(2, 3, 4, dtype=torch.long),
+              "masks": torch.ones(2, 3, 4, dtype=torch.bool), "rewards": torch.zeros(2, 3)}
+    out = ex.pad_sequences(groups)
+    assert out["responses"].shape == (2, 3, 5) and (6 * (3 + 5)) % 8 == 0 and not out["masks"][..., 4:].any()
+    assert out["prompts"] is groups["prompts"] and out["rewards"] is groups["rewards"]
+    even = {"chosen": torch.ones(4, 8, dtype=torch.long), "rejected": torch.ones(4, 8, dtype=torch.long),
+            "chosen_mask": torch.ones(4, 8, dtype=torch.bool), "rejected_mask": torch.ones(4, 8, dtype=torch.bool)}
+    assert ex.pad_sequences(even)["chosen"] is even["chosen"]  # nothing to do
+    ex.mesh = ParallelMesh(world=1, rank=0, mp_size=1)
+    assert ex.pad_sequences(pairs) is pairs
+
+
+def test_gathered_row_values_are_the_identity_outside_a_group():
+    from astrai_b200.parallel.tensor_parallel import gather_row_values
+
+    v = torch.arange(4.0, requires_grad=True)
+    assert gather_row_values(v) is v
+
+
 def test_pipeline_mode_is_refused_for_objectives_with_reference_models(tmp_path):
     from astrai_b200.config import TrainConfig
     from astrai_b200.trainer.train_context import TrainContextBuilder
@@ -129,14 +169,14 @@ def test_mesh_sizes_and_registration():
     assert data_parallel_size("ep", 8, ep_size=8) == 8 and data_parallel_size("fsdp", 8) == 8
 
 
-def test_tensor_parallel_refuses_sequence_level_objectives():
+def test_tensor_parallel_cuts_token_level_batches_and_refuses_unknown_ones():
     from astrai_b200.parallel import ExecutorFactory
     from astrai_b200.parallel.mesh import ParallelMesh
 
     ex = ExecutorFactory.create("tp", grad_accum_steps=1, size=2)
     ex.mesh = ParallelMesh(world=2, rank=0, mp_size=2)
     with pytest.raises(NotImplementedError):
-        ex.shard_batch({"chosen": torch.zeros(2, 4), "rejected": torch.zeros(2, 4)})
+        ex.shard_batch({"texts": torch.zeros(2, 4)})
     cut = ex.shard_batch({"input_ids": torch.zeros(2, 4, dtype=torch.long), "target_ids": torch.arange(8).view(2, 4)})
     assert cut["target_ids"].tolist() == [0, 1, 2, 3] and cut["input_ids"].shape == (2, 4)
 

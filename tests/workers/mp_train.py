@@ -40,6 +40,51 @@ class PackedChats(Tokens):
         return {"input_ids": row[:-1], "target_ids": row[1:], "position_ids": pos, "loss_mask": keep}
 
 
+class Pairs(torch.utils.data.Dataset):
+    """Preference pairs with a shared masked prompt and right padding of uneven length (token id 0)."""
+
+    def __init__(self, n, seq, vocab, seed=0):
+        g = torch.Generator().manual_seed(seed)
+        self.chosen = torch.randint(3, vocab, (n, seq), generator=g)
+        self.rejected = torch.randint(3, vocab, (n, seq), generator=g)
+        self.rejected[:, :4] = self.chosen[:, :4]
+        self.cmask = torch.zeros(n, seq, dtype=torch.bool)
+        self.rmask = torch.zeros(n, seq, dtype=torch.bool)
+        for i in range(n):
+            lc, lr = seq - (i % 5), seq - ((i + 2) % 7)
+            self.chosen[i, lc:], self.rejected[i, lr:] = 0, 0
+            self.cmask[i, 4:lc], self.rmask[i, 4:lr] = True, True
+
+    def __len__(self):
+        return self.chosen.shape[0]
+
+    def __getitem__(self, i):
+        return {"chosen": self.chosen[i], "rejected": self.rejected[i], "chosen_mask": self.cmask[i], "rejected_mask": self.rmask[i]}
+
+
+class Groups(torch.utils.data.Dataset):
+    """Prompts (left-padded) with three scored responses each (right-padded)."""
+
+    def __init__(self, n, seq, vocab, seed=0):
+        g = torch.Generator().manual_seed(seed)
+        plen, rlen = seq // 2, seq // 2 - 1  # an odd total length on purpose
+        self.prompts = torch.randint(3, vocab, (n, plen), generator=g)
+        self.responses = torch.randint(3, vocab, (n, 3, rlen), generator=g)
+        self.masks = torch.ones(n, 3, rlen, dtype=torch.bool)
+        self.rewards = torch.rand(n, 3, generator=g)
+        for i in range(n):
+            self.prompts[i, : i % 3] = 0
+            cut = rlen - (i % 4)
+            self.responses[i, 1, cut:] = 0
+            self.masks[i, 1, cut:] = False
+
+    def __len__(self):
+        return self.prompts.shape[0]
+
+    def __getitem__(self, i):
+        return {"prompts": self.prompts[i], "responses": self.responses[i], "masks": self.masks[i], "rewards": self.rewards[i]}
+
+
 class Record:
     def __init__(self):
         self.losses, self.norms, self.val = [], [], []
@@ -78,7 +123,7 @@ def main():
     ap.add_argument("--lr", type=float, default=1e-2)
     ap.add_argument("--chunks", type=int, default=0)
     ap.add_argument("--layers", type=int, default=2)
-    ap.add_argument("--strategy", default="seq", choices=["seq", "sft"])
+    ap.add_argument("--strategy", default="seq", choices=["seq", "sft", "dpo", "grpo"])
     ap.add_argument("--val", action="store_true", help="hold a quarter of the data out and report its loss after training")
     ap.add_argument("--label_smoothing", type=float, default=0.0)
     args = ap.parse_args()
@@ -111,7 +156,8 @@ def main():
     global_batch = args.bpd * 2
     bpd = global_batch // dw
     n = global_batch * accum * args.steps
-    data_cls = PackedChats if args.strategy == "sft" else Tokens
+    data_cls = {"sft": PackedChats, "dpo": Pairs, "grpo": Groups}.get(args.strategy, Tokens)
+    objective = {"dpo": {"beta": 0.5}, "grpo": {"group_size": 3, "clip_eps": 0.2, "kl_coef": 0.05}}.get(args.strategy, {})
     if args.val:
         n = n * 4 // 3  # the held-out quarter comes off the end
     exkw = {"comm": args.comm} if args.mode in ("tp", "cp", "ep") else {}
@@ -124,7 +170,7 @@ def main():
         exkw["tokens_per_rank"] = bpd * args.seq
     tc = TrainConfig(model_fn=model_fn, strategy=args.strategy, dataset=data_cls(n, args.seq, 256),
                      val_split=0.25 if args.val else None, val_step=10**6,
-                     strategy_kwargs={"label_smoothing": args.label_smoothing} if args.label_smoothing else {},
+                     strategy_kwargs={"label_smoothing": args.label_smoothing} if args.label_smoothing else objective,
                      optimizer_fn=lambda m: FusedAdamW(m.parameters(), lr=args.lr, weight_decay=0.0),
                      batch_per_device=bpd, grad_accum_steps=accum, ckpt_dir=args.ckpt, ckpt_interval=10**6,
                      device_type="cuda" if cuda else "cpu", backend="nccl" if cuda else "gloo", nprocs=world,
