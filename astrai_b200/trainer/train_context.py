@@ -255,6 +255,11 @@ class TrainContextBuilder:
             return
         if not ctx.strategy.supports_online():
             raise ValueError(f"Strategy '{c.strategy}' does not support online rollout")
+        if c.parallel_mode in ("tp", "cp", "pp"):
+            # responses are sampled by the serving scheduler from the training model itself; the sharded training forms of
+            # these modes have no KV-cache forward
+            raise ValueError(f"online rollouts sample from the training model, which parallel_mode '{c.parallel_mode}' cuts into "
+                             "a training-only form; use none / ddp / fsdp / ep, or train offline on sampled data")
         from astrai_b200.inference.scheduler import InferenceScheduler
         from astrai_b200.tokenize import AutoTokenizer
         from astrai_b200.trainer.rollout import RolloutGenerator, RolloutRunner

@@ -82,3 +82,21 @@ def test_offline_strategy_name_with_online_data_is_refused(tmp_path):
 
     with pytest.raises(ValueError):
         TrainConfig(strategy="online_sft", model_fn=_model, dataset=Instructions(), optimizer_fn=_adamw)
+
+
+def test_online_rollouts_are_refused_where_the_training_model_has_no_serving_forward(tmp_path):
+    from astrai_b200.config import TrainConfig
+    from astrai_b200.trainer.train_context import TrainContextBuilder
+
+    class Strategy:
+        def supports_online(self):
+            return True
+
+    class Ctx:
+        strategy = Strategy()
+
+    for mode in ("tp", "cp", "pp"):
+        cfg = TrainConfig(strategy="online_grpo", model_fn=_model, dataset=Instructions(), optimizer_fn=_adamw, parallel_mode=mode,
+                          nprocs=2, device_type="cpu", backend="gloo", ckpt_dir=str(tmp_path))
+        with pytest.raises(ValueError, match="online rollouts sample from the training model"):
+            TrainContextBuilder(cfg)._rollout(Ctx(), {})
