@@ -96,7 +96,7 @@ def test_online_rollouts_are_refused_where_the_training_model_has_no_serving_for
         strategy = Strategy()
 
     for mode in ("tp", "cp", "pp"):
-        cfg = TrainConfig(strategy="online_grpo", model_fn=_model, dataset=Instructions(), optimizer_fn=_adamw, parallel_mode=mode,
+        cfg = TrainConfig(strategy="online_grpo", model_fn=_model, dataset=Instructions(), optimizer_fn=_adamw, parallel_mode=mode, reward_model_fn=LongerIsBetter,
                           nprocs=2, device_type="cpu", backend="gloo", ckpt_dir=str(tmp_path))
         with pytest.raises(ValueError, match="online rollouts sample from the training model"):
             TrainContextBuilder(cfg)._rollout(Ctx(), {})
