@@ -207,7 +207,7 @@ def plan(o: Dict[str, Any]) -> Dict[str, Any]:
 @click.option("--tp_size", type=int, default=None, help="Tensor-parallel size inside one NVSwitch domain (<= 8); default: all ranks.")
 @click.option("--cp_size", type=int, default=None, help="Context-parallel size (ranks that share one sequence); default: all ranks.")
 @click.option("--ep_size", type=int, default=None, help="Expert-parallel size (ranks that share one set of experts); default: all ranks.")
-@click.option("--pp_size", type=int, default=None, help="Pipeline stages (ranks that hold one model replica layer range by layer range); default: all ranks. Trains --train_type seq and sft.")
+@click.option("--pp_size", type=int, default=None, help="Pipeline stages (ranks that hold one model replica layer range by layer range); default: all ranks. Trains --train_type seq, sft, dpo and grpo.")
 @click.option("--pp_chunks", type=int, default=None, help="pp: pieces a per-device batch is cut into for the 1F1B schedule (default: the number of stages, at most the batch).")
 @click.option("--mp_comm", type=click.Choice(["p2p", "nccl"]), default="p2p",
               help="tp / cp / ep transport: fused peer-memory kernels or library collectives around the same math.")

@@ -387,8 +387,9 @@ class PipelineParallelExecutor(ModelParallelExecutor):
     forward and backward passes interleave across the stages (:meth:`pipeline_step`, which the trainer calls instead of
     strategy + backward; :meth:`pipeline_eval` for validation batches).  The objectives are the token cross-entropies:
     ``seq`` (every position) and ``sft`` (positions of the loss mask, attention inside each packed document; the loss
-    is the mean over the trained tokens of the whole per-device batch, whatever the cut into pieces).  The preference
-    and policy-gradient strategies, which need reference models, are refused.
+    is the mean over the trained tokens of the whole per-device batch, whatever the cut into pieces), and the
+    sequence-level ones on prepared data: ``dpo`` (a piece holds whole pairs) and ``grpo`` (a piece holds whole response
+    groups), for which the last stage scores every piece with the strategy's whole frozen models before the window.
     Gradients accumulate in the flat runtime's fp32 buffers; every parameter lives on exactly one stage, so gradients are
     summed over the data-parallel group only and the gradient norm is summed over the stages.  Checkpoints are put back
     together with the reference's keys: every stage sends its tensors to the first one.
@@ -480,14 +481,101 @@ class PipelineParallelExecutor(ModelParallelExecutor):
                     kw["attention"] = doc_attention(pos)
         return ids.to(dev), targets.to(dev), chunks, kwargs, weights
 
-    def pipeline_step(self, model, batch: dict, loss_scale: float) -> dict:
-        ids, targets, chunks, kwargs, weights = self._pieces(batch)
+    def _chunks_of(self, n: int, what: str) -> int:
+        chunks = self.chunks if self.chunks > 0 else min(self.mesh.mp_size, n)
+        if n % chunks:
+            raise ValueError(f"a per-device batch of {n} {what} cannot be cut into {chunks} pipeline pieces")
+        return chunks
+
+    def _preference_pieces(self, batch: dict, strategy):
+        """Preference pairs: a piece is ``m`` chosen answers followed by their ``m`` rejected ones, so that every piece's
+        loss is a mean over whole pairs and the window's loss the mean over all of them.  The last stage scores the pieces
+        with the frozen reference model first."""
+        from astrai_b200.trainer.strategy import dpo_loss, get_logprobs, logprobs_from_logits, padded_causal_attention, reduce_logprobs
+
+        stage = self._pipe.stage
+        dev = next(stage.parameters()).device
+        n = batch["chosen"].shape[0]
+        chunks = self._chunks_of(n, "pairs")
+        m = n // chunks
+        ids, keep, kwargs, targets = [], [], [], []
+        for i in range(chunks):
+            rows = slice(i * m, (i + 1) * m)
+            piece = torch.cat([batch["chosen"][rows], batch["rejected"][rows]], dim=0)
+            mask = torch.cat([batch["chosen_mask"][rows], batch["rejected_mask"][rows]], dim=0)
+            attn = padded_causal_attention(piece.ne(0))  # from the host copy
+            attn = attn.to(dev) if isinstance(attn, torch.Tensor) else attn
+            ids.append(piece.to(dev))
+            keep.append(mask.to(dev))
+            kwargs.append({"attention": attn})
+            if stage.last:
+                with torch.no_grad():
+                    ref = get_logprobs(strategy.ref_model, ids[-1], attn, keep[-1], strategy.reduction)["logprobs"]
+                targets.append({"ids": ids[-1], "keep": keep[-1], "ref": ref})
+
+        def loss_fn(logits, t):
+            policy = reduce_logprobs(logprobs_from_logits(logits, t["ids"]), t["keep"], strategy.reduction)
+            return dpo_loss(policy, t["ref"], strategy.beta)
+
+        return torch.cat(ids, dim=0), targets, chunks, kwargs, None, loss_fn
+
+    def _group_pieces(self, batch: dict, strategy):
+        """Scored response groups: a piece is the groups of ``b / chunks`` prompts; every piece contributes its sums over
+        response tokens divided by the batch's token count, so the pieces add up to the batch's loss."""
+        from astrai_b200.trainer.strategy import get_logprobs, grpo_terms, logprobs_from_logits, padded_causal_attention, reduce_logprobs
+
+        stage = self._pipe.stage
+        dev = next(stage.parameters()).device
+        prompts, responses, masks, rewards = batch["prompts"], batch["responses"], batch["masks"], batch["rewards"]
+        b, g, rlen = responses.shape
+        plen = prompts.shape[1]
+        pmask = batch.get("prompt_mask")
+        pmask = prompts.ne(0) if pmask is None else pmask
+        chunks = self._chunks_of(b, "prompts")
+        m = b // chunks
+        count = masks.bool().sum().clamp(min=1).float().item()  # the loader's batch lives on the host
+        ids, kwargs, targets = [], [], []
+        for i in range(chunks):
+            rows = slice(i * m, (i + 1) * m)
+            prompt = prompts[rows][:, None].expand(-1, g, -1).reshape(m * g, plen)
+            valid = torch.cat([pmask[rows][:, None].expand(-1, g, -1).reshape(m * g, plen).bool(), masks[rows].reshape(m * g, rlen).bool()], dim=-1)
+            seq = torch.cat([prompt, responses[rows].reshape(m * g, rlen)], dim=-1)
+            keep = torch.cat([torch.zeros(m * g, plen, dtype=torch.bool), masks[rows].reshape(m * g, rlen).bool()], dim=-1)
+            attn = padded_causal_attention(valid)
+            attn = attn.to(dev) if isinstance(attn, torch.Tensor) else attn
+            ids.append(seq.to(dev))
+            kwargs.append({"attention": attn})
+            if stage.last:
+                keep_d = keep.to(dev)
+
+                def frozen(model, seq_d=ids[-1], attn=attn, keep_d=keep_d):
+                    with torch.no_grad():
+                        return get_logprobs(model, seq_d, attn, keep_d, "none")["logprobs"][:, plen - 1:].reshape(m, g, -1)
+
+                targets.append({"ids": ids[-1], "keep": keep_d, "old": frozen(strategy.old_model), "ref": frozen(strategy.ref_model),
+                                "rewards": rewards[rows].to(dev), "tok": masks[rows].to(dev).float()})
+
+        def loss_fn(logits, t):
+            lp = reduce_logprobs(logprobs_from_logits(logits, t["ids"]), t["keep"], "none")[:, plen - 1:].reshape(m, g, -1)
+            surrogate, kl = grpo_terms(lp, t["old"], t["ref"], t["rewards"], t["tok"], strategy.clip_eps)
+            return (surrogate + strategy.kl_coef * kl) / count
+
+        return torch.cat(ids, dim=0), targets, chunks, kwargs, [1.0] * chunks, loss_fn
+
+    def pipeline_step(self, model, batch: dict, loss_scale: float, strategy=None) -> dict:
+        loss_fn = None
+        if "chosen" in batch and "rejected" in batch:
+            ids, targets, chunks, kwargs, weights, loss_fn = self._preference_pieces(batch, strategy)
+        elif "responses" in batch and "prompts" in batch:
+            ids, targets, chunks, kwargs, weights, loss_fn = self._group_pieces(batch, strategy)
+        else:
+            ids, targets, chunks, kwargs, weights = self._pieces(batch)
         stage = self._pipe.stage
         for u in self.engine.units:
             u.ready = u.reduced = False
         loss = self._pipe.train_step(ids if stage.first else None, targets if stage.last else None, chunks,
                                      micro_shape=(ids.shape[0] // chunks, ids.shape[1]), loss_scale=loss_scale,
-                                     micro_kwargs=kwargs, weights=weights)
+                                     micro_kwargs=kwargs, weights=weights, loss_fn=loss_fn)
         if self.gradient_state.sync_gradients:
             for u in reversed(self.engine.units):
                 u.ready = True

@@ -132,7 +132,7 @@ class PipelineParallel:
     def train_step(self, input_ids: Optional[Tensor], targets: Optional[Tensor], n_micro: int,
                    micro_shape: Optional[Tuple[int, int]] = None, dtype: Optional[torch.dtype] = None,
                    loss_scale: float = 1.0, micro_kwargs: Optional[Sequence[dict]] = None,
-                   weights: Optional[Sequence[float]] = None) -> Optional[Tensor]:
+                   weights: Optional[Sequence[float]] = None, loss_fn: Optional[Callable] = None) -> Optional[Tensor]:
         """One accumulation window (gradients are those of ``loss_scale`` times the window's loss).  ``input_ids``
         ``[B, S]`` is needed on the first stage, ``targets`` ``[B, S]`` on the last; ``B`` must be a multiple of
         ``n_micro``.  Stages in the middle pass ``micro_shape = (B / n_micro, S)``.
@@ -141,7 +141,9 @@ class PipelineParallel:
         ``attention``), the same on every stage.  ``weights[i]`` is the share of piece ``i`` in the window's loss
         (default ``1 / n_micro`` each: the mean of the pieces' means); an objective that averages over a varying number
         of tokens per piece passes that piece's share of the tokens, which makes the window's loss the mean over all
-        its tokens.  Returns the window's loss on the last stage, ``None`` elsewhere.  Gradients are left in ``.grad``."""
+        its tokens.  ``targets`` may also be a list with one object per piece and ``loss_fn(logits, object)`` the objective
+        of this window (sequence-level losses carry ids, masks and reference values per piece).  Returns the window's
+        loss on the last stage, ``None`` elsewhere.  Gradients are left in ``.grad``."""
         st = self.stage
         if weights is None:
             weights = [1.0 / n_micro] * n_micro
@@ -154,9 +156,11 @@ class PipelineParallel:
         if st.first:
             micro_in = input_ids.chunk(n_micro, dim=0)
             micro_shape = tuple(micro_in[0].shape)
+        loss_fn = loss_fn or self.loss_fn
         if st.last and targets is not None:
-            micro_tg = targets.chunk(n_micro, dim=0)
-            micro_shape = micro_shape or tuple(micro_tg[0].shape)
+            micro_tg = list(targets) if isinstance(targets, (list, tuple)) else targets.chunk(n_micro, dim=0)
+            if micro_shape is None:
+                micro_shape = tuple(micro_tg[0].shape)
         if micro_shape is None:
             raise ValueError("a middle stage needs micro_shape")
         act_shape = (micro_shape[0], micro_shape[1], st.hidden_size)
@@ -176,7 +180,7 @@ class PipelineParallel:
         def forward(i, x):
             y, aux = st(x, **micro_kwargs[i])
             if st.last:
-                loss = self.loss_fn(y, micro_tg[i])
+                loss = loss_fn(y, micro_tg[i])
                 losses.append(loss.detach() * weights[i])
                 y = loss * (loss_scale * weights[i])
                 if aux is not None and self.aux_loss_coef:  # the auxiliary loss is a plain mean over the pieces

@@ -123,19 +123,47 @@ def token_logprobs(model, input_ids: Tensor, input_mask: Optional[Tensor], posit
     return lp, out
 
 
+def reduce_logprobs(lp: Tensor, loss_mask: Tensor, reduction: str) -> Tensor:
+    """``lp [B, S-1]`` masked by ``loss_mask[:, 1:]`` and summed / averaged per sequence, or left per token."""
+    if reduction not in ("mean", "sum", "none"):
+        raise ValueError(f"reduction must be one of ['mean', 'sum', 'none'], got '{reduction}'")
+    m = loss_mask[:, 1:].to(lp.dtype)
+    if reduction == "sum":
+        return (lp * m).sum(-1)
+    if reduction == "mean":
+        return (lp * m).sum(-1) / m.sum(-1).clamp(min=1.0)
+    return lp * m
+
+
 def get_logprobs(model, input_ids: Tensor, attn_mask: Tensor, loss_mask: Tensor, reduction: str) -> LogprobsOutput:
     """Masked (and optionally reduced) next-token log-probabilities (reference ``strategy.py:33-84``)."""
     if reduction not in ("mean", "sum", "none"):
         raise ValueError(f"reduction must be one of ['mean', 'sum', 'none'], got '{reduction}'")
     lp, out = token_logprobs(model, input_ids, attn_mask)
-    m = loss_mask[:, 1:].to(lp.dtype)
-    if reduction == "sum":
-        lp = (lp * m).sum(-1)
-    elif reduction == "mean":
-        lp = (lp * m).sum(-1) / m.sum(-1).clamp(min=1.0)
-    else:
-        lp = lp * m
-    return {"logprobs": lp, "aux_loss": out.get("aux_loss"), "router_stats": out.get("router_stats")}
+    return {"logprobs": reduce_logprobs(lp, loss_mask, reduction), "aux_loss": out.get("aux_loss"), "router_stats": out.get("router_stats")}
+
+
+def logprobs_from_logits(logits: Tensor, input_ids: Tensor) -> Tensor:
+    """``[B, S-1]`` log-probability of ``input_ids[:, 1:]`` from logits of ALL ``S`` positions (the last one predicts nothing)."""
+    return torch.log_softmax(logits[:, :-1].float(), dim=-1).gather(-1, input_ids[:, 1:].unsqueeze(-1)).squeeze(-1)
+
+
+def dpo_loss(policy: Tensor, reference: Tensor, beta: float) -> Tensor:
+    """``policy`` / ``reference`` ``[2n]``: sequence log-probabilities of ``n`` chosen answers, then of the ``n`` rejected ones."""
+    n = policy.shape[0] // 2
+    margin = (policy[:n] - policy[n:]) - (reference[:n] - reference[n:])
+    return -F.logsigmoid(beta * margin).mean()
+
+
+def grpo_terms(lp_pol: Tensor, lp_old: Tensor, lp_ref: Tensor, rewards: Tensor, tok: Tensor, clip_eps: float):
+    """Sums over the response tokens ``tok [b, g, L]`` of the clipped surrogate and of the k3 KL estimate (not yet divided
+    by a token count, not yet weighted): the two numerators of the GRPO loss."""
+    eps = 1e-8
+    adv = ((rewards - rewards.mean(-1, keepdim=True)) / (rewards.std(-1, keepdim=True, unbiased=False) + eps))[..., None]
+    ratio = torch.exp(lp_pol - lp_old)
+    surrogate = -torch.min(ratio * adv, ratio.clamp(1 - clip_eps, 1 + clip_eps) * adv)
+    r = torch.exp(lp_ref - lp_pol)
+    return (surrogate * tok).sum(), ((r - torch.log(r + eps) - 1.0) * tok).sum()
 
 
 def make_doc_boundary_mask(position_ids: Tensor) -> Tensor:
@@ -324,9 +352,7 @@ class DPOStrategy(BaseStrategy):
         pol = get_logprobs(self.model, ids, mask, loss_mask, self.reduction)
         with torch.no_grad():
             ref = get_logprobs(self.ref_model, ids, mask, loss_mask, self.reduction)["logprobs"]
-        pi = pol["logprobs"]
-        margin = (pi[:n] - pi[n:]) - (ref[:n] - ref[n:])
-        loss = -F.logsigmoid(self.beta * margin).mean()
+        loss = dpo_loss(pol["logprobs"], ref, self.beta)
         return self._loss_output(loss, {"dpo_loss": loss}, pol["aux_loss"], pol.get("router_stats"))
 
     def supports_online(self) -> bool:
@@ -385,13 +411,9 @@ class GRPOStrategy(BaseStrategy):
             lp_ref, _ = response_logprobs(self.ref_model)
         tok = rmask.reshape(b, g, -1).float()
         count = tok.sum().clamp(min=1.0)
-        eps = 1e-8
-        adv = ((rewards - rewards.mean(-1, keepdim=True)) / (rewards.std(-1, keepdim=True, unbiased=False) + eps))[..., None]
-        ratio = torch.exp(lp_pol - lp_old)
-        surrogate = -torch.min(ratio * adv, ratio.clamp(1 - self.clip_eps, 1 + self.clip_eps) * adv)
-        policy_loss = (surrogate * tok).sum() / count
-        r = torch.exp(lp_ref - lp_pol)
-        kl = self.kl_coef * ((r - torch.log(r + eps) - 1.0) * tok).sum() / count
+        surrogate_sum, kl_sum = grpo_terms(lp_pol, lp_old, lp_ref, rewards, tok, self.clip_eps)
+        policy_loss = surrogate_sum / count
+        kl = self.kl_coef * kl_sum / count
         return self._loss_output(policy_loss + kl, {"policy_loss": policy_loss, "kl_loss": kl},
                                  pol["aux_loss"], pol.get("router_stats"))
 

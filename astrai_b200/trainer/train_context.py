@@ -140,8 +140,8 @@ class TrainContextBuilder:
 
             kw.setdefault("size", size)
         if mode == "pp":  # the last stage computes the loss itself: it takes the objective's options from the strategy's
-            if c.strategy not in ("seq", "sft"):
-                raise ValueError(f"parallel_mode 'pp' trains the strategies 'seq' and 'sft', not {c.strategy!r}")
+            if c.strategy not in ("seq", "sft", "dpo", "grpo"):
+                raise ValueError(f"parallel_mode 'pp' trains the strategies 'seq', 'sft', 'dpo' and 'grpo' on prepared data, not {c.strategy!r}")
             kw.setdefault("label_smoothing", float(c.strategy_kwargs.get("label_smoothing", 0.0) or 0.0))
             kw.setdefault("aux_loss_coef", float(c.strategy_kwargs.get("moe_aux_loss_coef", c.moe_aux_loss_coef)))
         return ExecutorFactory.create(mode, grad_accum_steps=c.grad_accum_steps, **kw)

@@ -66,7 +66,7 @@ class Trainer:
         if hasattr(ex, "pipeline_step"):
             # pipeline parallelism: forward and backward of the batch's pieces interleave across the stages inside the call
             with trace.range("pipeline"):
-                out = ex.pipeline_step(context.model, batch, scale)
+                out = ex.pipeline_step(context.model, batch, scale, strategy=context.strategy)
             loss = out["loss"]
         elif flat:
             # promise the loss gradient so the fused head bakes 1/accum into dX and accumulates dW in place

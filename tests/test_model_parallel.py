@@ -128,13 +128,22 @@ def test_gathered_row_values_are_the_identity_outside_a_group():
     assert gather_row_values(v) is v
 
 
-def test_pipeline_mode_is_refused_for_objectives_with_reference_models(tmp_path):
+@pytest.mark.parametrize("strategy,extra", [("dpo", ["--chunks", "4"]), ("grpo", [])])
+def test_pipeline_parallel_sequence_level_objectives_match_single_process(tmp_path, strategy, extra):
+    """A piece of the 1F1B window holds whole preference pairs / whole response groups; the last stage scores them with
+    whole frozen models and the pieces' losses add up to the batch's."""
+    ref = _run(tmp_path, f"ref{strategy}", 1, "--mode", "none", "--strategy", strategy)
+    run = _run(tmp_path, f"pp{strategy}", 2, "--mode", "pp", "--strategy", strategy, *extra)
+    _same(run, ref)
+
+
+def test_pipeline_mode_is_refused_for_online_objectives(tmp_path):
     from astrai_b200.config import TrainConfig
     from astrai_b200.trainer.train_context import TrainContextBuilder
 
-    cfg = TrainConfig(model_fn=lambda: None, strategy="dpo", dataset=[0], optimizer_fn=lambda m: None, ckpt_dir=str(tmp_path),
-                      parallel_mode="pp", pp_size=2, nprocs=2, device_type="cpu", backend="gloo")
-    with pytest.raises(ValueError, match="'seq' and 'sft'"):
+    cfg = TrainConfig(model_fn=lambda: None, strategy="online_dpo", dataset=[0], optimizer_fn=lambda m: None, ckpt_dir=str(tmp_path),
+                      parallel_mode="pp", pp_size=2, nprocs=2, device_type="cpu", backend="gloo", reward_model_fn=lambda: None)
+    with pytest.raises(ValueError, match="on prepared data"):
         TrainContextBuilder(cfg)._executor()
 
 
@@ -151,7 +160,7 @@ def test_pipeline_executor_hands_each_stage_its_own_optimizer_state_and_refuses_
     with pytest.raises(RuntimeError, match="3 pipeline stages"):
         ex.unpack_optimizer_state({"pipeline_stages": [1, 2, 3]})
     with pytest.raises(NotImplementedError, match="token cross-entropy"):
-        ex.pipeline_step(None, {"chosen": torch.zeros(1, 2), "rejected": torch.zeros(1, 2)}, 1.0)
+        ex.pipeline_step(None, {"texts": torch.zeros(1, 2)}, 1.0)
 
 
 @pytest.mark.parametrize("nproc,size", [(2, 0), (4, 2)])
