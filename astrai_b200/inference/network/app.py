@@ -1,4 +1,4 @@
-"""FastAPI application: ``POST /v1/chat/completions``, ``POST /v1/messages``, ``GET /health``, ``GET /stats``.
+"""FastAPI application: ``POST /v1/chat/completions``, ``POST /v1/messages``, ``GET /health``, ``GET /stats``, ``GET /v1/models``.
 
 Request schemas and defaults follow ``astrai/inference/network/app.py:33-206`` (OpenAI: temperature 1.0, top_p 1.0,
 top_k 50, max_tokens 2048; Anthropic: max_tokens 1024; 503 ``{"detail": "Engine not initialized"}`` before the engine
@@ -137,6 +137,15 @@ async def health():
 @router.get("/stats")
 async def stats():
     return _engine().get_stats()
+
+
+@router.get("/v1/models")
+async def models():
+    """The one model this server holds, in the shape OpenAI clients list models in (not a route of the reference; clients
+    such as SDKs and UIs call it before their first request)."""
+    _engine()
+    name = Path(str(get_app().state.server_config.get("param_path") or "astrai")).name or "astrai"
+    return {"object": "list", "data": [{"id": name, "object": "model", "created": 0, "owned_by": "astrai_b200"}]}
 
 
 @router.post("/v1/chat/completions")

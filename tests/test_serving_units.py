@@ -760,6 +760,8 @@ def test_http_rejects_malformed_requests_before_they_reach_the_engine(served):
         assert client.post("/v1/chat/completions", content=b"{not json", headers={"content-type": "application/json"}).status_code == 422
         assert engine.get_stats()["total_tasks"] == before
         assert client.get("/nowhere").status_code == 404 and client.get("/v1/chat/completions").status_code == 405
+        listed = client.get("/v1/models").json()
+        assert listed["object"] == "list" and [m["object"] for m in listed["data"]] == ["model"] and listed["data"][0]["id"]
         # an empty conversation is a valid request: the model answers the bare generation prompt
         r = client.post("/v1/chat/completions", json={"messages": [], "max_tokens": 2, "temperature": 0.0})
         assert r.status_code == 200 and r.json()["usage"]["completion_tokens"] <= 2
