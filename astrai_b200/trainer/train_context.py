@@ -246,6 +246,13 @@ class TrainContextBuilder:
             kw["ref_model"] = create_ref_model(c.model_fn, executor=executor, model=ctx.model, device=device)
         if c.strategy in ("grpo", "online_grpo"):
             kw["old_model"] = create_ref_model(c.model_fn, executor=executor, model=ctx.model, device=device)
+        stage = getattr(getattr(executor, "_pipe", None), "stage", None)
+        if stage is not None and not stage.last:
+            # pipeline stages: only the last one scores with the frozen models (building them was a collective: the weights
+            # were gathered from every stage); the others give the memory back
+            for name in ("ref_model", "old_model"):
+                if name in kw:
+                    kw[name] = None
         ctx.strategy = StrategyFactory.create(c.strategy, model=ctx.model, device=device, executor=executor, **kw)
         return kw
 
