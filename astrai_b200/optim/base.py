@@ -17,6 +17,31 @@ class OptimizerFactory(BaseFactory[Optimizer]):
     """Built-in training optimizers by name."""
 
 
+def _plain(method):
+    return getattr(method, "__wrapped__", method)
+
+
+class UntracedOptimizer(Optimizer):
+    """``torch.optim.Optimizer`` without the guards against torch's tracing compiler.
+
+    torch wraps ``add_param_group`` / ``zero_grad`` / ``state_dict`` / ``load_state_dict`` so that the compiler does not
+    trace into them, and the first call through a wrapper imports the compiler (with its symbolic-algebra dependencies:
+    several seconds in every process that builds an optimizer).  Nothing in this framework is traced, so the optimizers
+    here call the plain functions the wrappers stand in front of."""
+
+    def add_param_group(self, param_group):
+        return _plain(Optimizer.add_param_group)(self, param_group)
+
+    def zero_grad(self, set_to_none: bool = True):
+        return _plain(Optimizer.zero_grad)(self, set_to_none)
+
+    def state_dict(self):
+        return _plain(Optimizer.state_dict)(self)
+
+    def load_state_dict(self, state_dict):
+        return _plain(Optimizer.load_state_dict)(self, state_dict)
+
+
 def composite_step(sub_optimizers, closure=None):
     """One step of several optimizers that together stand for one: the closure runs once (with gradients enabled), before
     any of them steps; ``None`` entries are skipped."""
@@ -46,7 +71,7 @@ def refresh_param_groups(sub_optimizers) -> List[dict]:
     return [g for sub in sub_optimizers if sub is not None for g in sub.param_groups]
 
 
-class CompositeOptimizer(Optimizer):
+class CompositeOptimizer(UntracedOptimizer):
     """Routes disjoint parameter sets through named sub-optimizers; behaves as one optimizer."""
 
     def __init__(self, params, defaults: dict, subs: Dict[str, Optional[Optimizer]]):

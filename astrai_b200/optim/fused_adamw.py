@@ -19,11 +19,11 @@ import torch
 from torch.optim import Optimizer
 
 from astrai_b200 import ops
-from astrai_b200.optim.base import OptimizerFactory
+from astrai_b200.optim.base import OptimizerFactory, UntracedOptimizer
 
 
 @OptimizerFactory.register("fused_adamw")
-class FusedAdamW(Optimizer):
+class FusedAdamW(UntracedOptimizer):
     supports_flat = True
     optimizer_name = "fused_adamw"
 

@@ -23,7 +23,7 @@ import torch
 from torch import Tensor, nn
 from torch.optim import Optimizer
 
-from astrai_b200.optim.base import CompositeOptimizer, OptimizerFactory
+from astrai_b200.optim.base import CompositeOptimizer, OptimizerFactory, UntracedOptimizer
 from astrai_b200.optim.fused_adamw import FusedAdamW
 
 NORA_EPS = 1e-10
@@ -73,7 +73,7 @@ def muon_lr(lr: float, shape, mode: str) -> float:
     return lr * math.sqrt(max(1.0, rows / cols))
 
 
-class Muon(Optimizer):
+class Muon(UntracedOptimizer):
     def __init__(self, params, lr: float = 1e-3, weight_decay: float = 0.1, momentum: float = 0.95, nesterov: bool = True,
                  ns_steps: int = 5, adjust_lr_fn: str = "original", eps: float = 1e-7):
         _check(lr >= 0, f"Invalid learning rate: {lr}")
@@ -135,7 +135,7 @@ def _require_whole_rows(p: Tensor):
                 raise ValueError("Nora requires complete parameter rows, but this DTensor is sharded along its last dimension")
 
 
-class Nora(Optimizer):
+class Nora(UntracedOptimizer):
     def __init__(self, params, lr: float = 5e-3, weight_decay: float = 0.0, momentum: float = 0.95, beta: float = 0.95,
                  nesterov: bool = True, eps: float = NORA_EPS):
         _check(lr >= 0, f"Invalid learning rate: {lr}")
@@ -176,7 +176,7 @@ class Nora(Optimizer):
 
 
 # ------------------------------------------------------------------------------------------------- Mano
-class Mano(Optimizer):
+class Mano(UntracedOptimizer):
     def __init__(self, params, lr: float = 1e-3, weight_decay: float = 0.1, momentum: float = 0.95, nesterov: bool = True,
                  eps: float = 1e-8):
         _check(lr >= 0, f"Invalid learning rate: {lr}")
@@ -218,7 +218,7 @@ class Mano(Optimizer):
 
 
 # ------------------------------------------------------------------------------------------------- NAdamW
-class NAdamW(Optimizer):
+class NAdamW(UntracedOptimizer):
     def __init__(self, params, lr: float = 3e-4, betas=(0.9, 0.999), eps: float = 1e-8, weight_decay: float = 0.1):
         _check(lr >= 0, f"Invalid learning rate: {lr}")
         _check(0 <= betas[0] < 1 and 0 <= betas[1] < 1, f"Invalid betas: {betas}")

@@ -54,3 +54,38 @@ class RandomTokens(torch.utils.data.Dataset):
             raise RuntimeError("injected data failure")
         row = self.data[i]
         return {"input_ids": row[:-1], "target_ids": row[1:]}
+
+
+def launch_ranks(nproc: int, script: str, args, port: int, timeout: float = 600.0, env=None, cwd=None):
+    """Run ``script`` as ``nproc`` rank processes on this machine (RANK / WORLD_SIZE / LOCAL_RANK / MASTER_* in their
+    environment, as an external launcher sets them) and wait for all of them.  Returns ``(returncode, output)``: the first
+    non-zero exit code (0 if none) and every rank's output.  Starting the ranks directly instead of through
+    ``torch.distributed.run`` saves that launcher's own start-up in every test; the tests that are about the launcher use it."""
+    import subprocess
+    import sys
+    import time
+
+    base = dict(os.environ if env is None else env, MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), WORLD_SIZE=str(nproc),
+                LOCAL_WORLD_SIZE=str(nproc))
+    base.setdefault("OMP_NUM_THREADS", "1")
+    procs = []
+    for rank in range(nproc):
+        rank_env = dict(base, RANK=str(rank), LOCAL_RANK=str(rank))
+        procs.append(subprocess.Popen([sys.executable, script, *map(str, args)], env=rank_env, cwd=cwd, stdout=subprocess.PIPE,
+                                      stderr=subprocess.STDOUT, text=True))
+    deadline = time.time() + timeout
+    code, outputs = 0, []
+    for rank, p in enumerate(procs):
+        try:
+            out, _ = p.communicate(timeout=max(deadline - time.time(), 1.0))
+        except subprocess.TimeoutExpired:
+            for q in procs:  # the exact processes started above
+                if q.poll() is None:
+                    q.kill()
+            out, _ = p.communicate()
+            out = (out or "") + f"\n[rank {rank}: killed after {timeout:.0f} s]"
+            code = code or -9
+        outputs.append(f"--- rank {rank} (exit {p.returncode}) ---\n{(out or '')[-3000:]}")
+        if p.returncode and not code:
+            code = p.returncode
+    return code, "\n".join(outputs)

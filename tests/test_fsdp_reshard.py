@@ -13,11 +13,10 @@ ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 
 def _run(tmp_path, nproc, port, *extra):
     out = str(tmp_path / "res.json")
-    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={nproc}", "--master-addr", "127.0.0.1",
-           "--master-port", str(port), os.path.join(ROOT, "tests", "workers", "fsdp_reshard.py"), "--out", out, *extra]
-    proc = subprocess.run(cmd, env=dict(os.environ, MASTER_ADDR="127.0.0.1", OMP_NUM_THREADS="1"), capture_output=True, text=True,
-                          timeout=600, cwd=ROOT)
-    assert proc.returncode == 0, proc.stdout[-2000:] + proc.stderr[-3000:]
+    from helpers import launch_ranks
+
+    code, log = launch_ranks(nproc, os.path.join(ROOT, "tests", "workers", "fsdp_reshard.py"), ["--out", out, *extra], port, cwd=ROOT)
+    assert code == 0, log
     return json.load(open(out))
 
 

@@ -25,12 +25,14 @@ def _run(tmp_path, name, nproc, *args):
         cmd = [sys.executable, WORKER, "--out", out, "--ckpt", ckpt, *args]
         for k in ("RANK", "WORLD_SIZE", "LOCAL_RANK", "LOCAL_WORLD_SIZE"):
             env.pop(k, None)
+        proc = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=600, cwd=ROOT)
+        assert proc.returncode == 0, proc.stdout[-2000:] + proc.stderr[-3000:]
     else:
+        from helpers import launch_ranks
+
         _PORT[0] += 1
-        cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={nproc}", "--master-addr",
-               "127.0.0.1", "--master-port", str(_PORT[0]), WORKER, "--out", out, "--ckpt", ckpt, *args]
-    proc = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=600, cwd=ROOT)
-    assert proc.returncode == 0, proc.stdout[-2000:] + proc.stderr[-3000:]
+        code, log = launch_ranks(nproc, WORKER, ["--out", out, "--ckpt", ckpt, *args], _PORT[0], env=env, cwd=ROOT)
+        assert code == 0, log
     return json.load(open(out))
 
 
@@ -70,7 +72,7 @@ def sft_ref(tmp_path_factory):
     return _run(tmp_path_factory.mktemp("refsft"), "refsft", 1, "--mode", "none", "--strategy", "sft", "--val", "--label_smoothing", "0.1")
 
 
-@pytest.mark.parametrize("extra", [[], ["--chunks", "4"]])
+@pytest.mark.parametrize("extra", [["--chunks", "4"]])
 def test_pipeline_parallel_supervised_objective_and_validation(tmp_path, sft_ref, extra):
     """Packed documents with position ids and an uneven loss mask, label smoothing from the strategy's options, a held-out
     quarter scored after training: the pipeline's losses, norms, weights and validation loss are the single process's,
@@ -88,13 +90,19 @@ def test_tensor_parallel_supervised_objective_is_the_mean_over_all_trained_token
     assert run["val"] == pytest.approx(sft_ref["val"], abs=2e-5)
 
 
+@pytest.fixture(scope="module")
+def sequence_refs(tmp_path_factory):
+    """Single-process runs of the two sequence-level objectives, shared by the tensor- and pipeline-parallel comparisons."""
+    root = tmp_path_factory.mktemp("refseq")
+    return {s: _run(root, f"ref{s}", 1, "--mode", "none", "--strategy", s) for s in ("dpo", "grpo")}
+
+
 @pytest.mark.parametrize("strategy", ["dpo", "grpo"])
-def test_tensor_parallel_sequence_level_objectives_match_single_process(tmp_path, strategy):
+def test_tensor_parallel_sequence_level_objectives_match_single_process(tmp_path, sequence_refs, strategy):
     """Preference pairs and scored response groups: every rank scores its token rows, the per-token log-probabilities are
     gathered over the block and every rank evaluates the same loss against whole frozen reference models."""
-    ref = _run(tmp_path, f"ref{strategy}", 1, "--mode", "none", "--strategy", strategy)
     run = _run(tmp_path, f"tp{strategy}", 2, "--mode", "tp", "--strategy", strategy)
-    _same(run, ref)
+    _same(run, sequence_refs[strategy])
 
 
 def test_tensor_parallel_pads_sequence_level_batches_until_their_tokens_divide():
@@ -129,12 +137,11 @@ def test_gathered_row_values_are_the_identity_outside_a_group():
 
 
 @pytest.mark.parametrize("strategy,extra", [("dpo", ["--chunks", "4"]), ("grpo", [])])
-def test_pipeline_parallel_sequence_level_objectives_match_single_process(tmp_path, strategy, extra):
+def test_pipeline_parallel_sequence_level_objectives_match_single_process(tmp_path, sequence_refs, strategy, extra):
     """A piece of the 1F1B window holds whole preference pairs / whole response groups; the last stage scores them with
     whole frozen models and the pieces' losses add up to the batch's."""
-    ref = _run(tmp_path, f"ref{strategy}", 1, "--mode", "none", "--strategy", strategy)
     run = _run(tmp_path, f"pp{strategy}", 2, "--mode", "pp", "--strategy", strategy, *extra)
-    _same(run, ref)
+    _same(run, sequence_refs[strategy])
 
 
 def test_pipeline_mode_is_refused_for_online_objectives(tmp_path):

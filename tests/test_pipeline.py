@@ -39,18 +39,17 @@ def test_1f1b_schedule_properties(stages, micro):
         assert peak == min(stages - s, micro)  # activation memory bound of 1F1B
 
 
-@pytest.mark.parametrize("stages,micro,moe,sft", [(3, 2, False, False), (4, 4, False, False), (2, 2, True, False), (2, 4, False, True),
-                                                  (3, 2, True, True)])
+@pytest.mark.parametrize("stages,micro,moe,sft", [(4, 4, False, False), (2, 2, True, False), (3, 2, True, True)])
 def test_pipeline_step_matches_whole_model(tmp_path, stages, micro, moe, sft):
     """Gradients and loss of one 1F1B window equal those of the whole model; with ``sft`` the batch holds packed documents
     with position ids and an uneven loss mask, and the whole model sees the batch in ONE piece (mean over trained tokens)."""
     out = str(tmp_path / "pp.json")
-    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={stages}", "--master-addr", "127.0.0.1",
-           "--master-port", str(29720 + stages * 10 + micro + (5 if sft else 0)), os.path.join(ROOT, "tests", "workers", "pp_compare.py"), "--out", out,
-           "--micro", str(micro)] + (["--moe"] if moe else []) + (["--sft"] if sft else [])
-    env = dict(os.environ, MASTER_ADDR="127.0.0.1", OMP_NUM_THREADS="2")
-    proc = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=600, cwd=ROOT)
-    assert proc.returncode == 0, proc.stdout[-3000:] + proc.stderr[-3000:]
+    from helpers import launch_ranks
+
+    args = ["--out", out, "--micro", str(micro)] + (["--moe"] if moe else []) + (["--sft"] if sft else [])
+    code, log = launch_ranks(stages, os.path.join(ROOT, "tests", "workers", "pp_compare.py"), args, 29720 + stages * 10 + micro + (5 if sft else 0),
+                             env=dict(os.environ, OMP_NUM_THREADS="2"), cwd=ROOT)
+    assert code == 0, log
     res = json.load(open(out))
     assert sum(r["n_keys"] for r in res) > 0
     for r in res:

@@ -114,11 +114,11 @@ def test_rank_zero_reads_and_every_rank_receives(tmp_path):
                     extra={"optimizer": {"step": 5, "m": torch.arange(4.0)}, "scheduler": {"last_epoch": 5}}, meta={"note": "shared"})
     ck.save(tmp_path / "ck")
     out = str(tmp_path / "res")
-    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=3", "--master-addr", "127.0.0.1",
-           "--master-port", "29788", os.path.join(ROOT, "tests", "workers", "ckpt_broadcast.py"), "--ckpt", str(tmp_path / "ck"), "--out", out]
-    proc = subprocess.run(cmd, env=dict(os.environ, MASTER_ADDR="127.0.0.1", OMP_NUM_THREADS="1"), capture_output=True, text=True,
-                          timeout=300, cwd=ROOT)
-    assert proc.returncode == 0, proc.stdout[-2000:] + proc.stderr[-3000:]
+    from helpers import launch_ranks
+
+    code, log = launch_ranks(3, os.path.join(ROOT, "tests", "workers", "ckpt_broadcast.py"), ["--ckpt", str(tmp_path / "ck"), "--out", out], 29788,
+                             timeout=300, cwd=ROOT)
+    assert code == 0, log
     got = [json.load(open(f"{out}.{r}")) for r in range(3)]
     want_sum = float(sum(v.double().sum() for v in _state().values()))
     for r, res in enumerate(got):

@@ -47,12 +47,11 @@ def test_missing_beats_and_announced_exit_are_detected():
 @pytest.mark.parametrize("mode", ["leave", "silent"])
 def test_survivors_stop_between_steps_when_a_rank_goes_away(tmp_path, mode):
     out = str(tmp_path / "hb.json")
-    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=3", "--master-addr", "127.0.0.1",
-           "--master-port", "29790" if mode == "leave" else "29791", os.path.join(ROOT, "tests", "workers", "heartbeat_ranks.py"),
-           "--out", out, "--victim", "1", "--mode", mode]
-    proc = subprocess.run(cmd, env=dict(os.environ, MASTER_ADDR="127.0.0.1", OMP_NUM_THREADS="1"), capture_output=True, text=True,
-                          timeout=300, cwd=ROOT)
-    assert proc.returncode == 0, proc.stdout[-2000:] + proc.stderr[-3000:]
+    from helpers import launch_ranks
+
+    code, log = launch_ranks(3, os.path.join(ROOT, "tests", "workers", "heartbeat_ranks.py"), ["--out", out, "--victim", "1", "--mode", mode],
+                             29790 if mode == "leave" else 29791, timeout=300, cwd=ROOT)
+    assert code == 0, log
     res = {r: json.load(open(f"{out}.{r}")) for r in range(3)}
     assert res[1]["left_at"] == 4 and res[1]["steps"] == 3
     for r in (0, 2):
@@ -66,12 +65,11 @@ def test_survivors_write_an_emergency_checkpoint_without_collectives(tmp_path, m
     """Three gloo ranks train through the real Trainer; rank 1 exits silently between steps.  The survivors must
     return within a bound (no barrier, no gather that waits for the dead rank) and leave the weights on disk."""
     out, ckpt = str(tmp_path / "res"), str(tmp_path / "ckpt")
-    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=3", "--master-addr", "127.0.0.1",
-           "--master-port", "29793" if mode == "fsdp" else "29794", os.path.join(ROOT, "tests", "workers", "rank_loss_trainer.py"),
-           "--out", out, "--ckpt", ckpt, "--mode", mode]
-    proc = subprocess.run(cmd, env=dict(os.environ, MASTER_ADDR="127.0.0.1", OMP_NUM_THREADS="1"), capture_output=True, text=True,
-                          timeout=300, cwd=ROOT)
-    assert proc.returncode == 0, proc.stdout[-2000:] + proc.stderr[-3000:]
+    from helpers import launch_ranks
+
+    code, log = launch_ranks(3, os.path.join(ROOT, "tests", "workers", "rank_loss_trainer.py"), ["--out", out, "--ckpt", ckpt, "--mode", mode],
+                             29793 if mode == "fsdp" else 29794, timeout=300, cwd=ROOT)
+    assert code == 0, log
     gone = float(open(out + ".gone").read())
     for r in (0, 2):
         res = json.load(open(f"{out}.{r}"))
