@@ -113,3 +113,19 @@ def test_options_page_is_what_the_generator_writes():
     from astrai_b200.cli.options_doc import render
 
     assert _read("guides", "params.md") == render(), "run: python -m astrai_b200.cli.options_doc > docs/guides/params.md"
+
+
+def test_runtime_section_examples_produce_exports(tmp_path):
+    import yaml
+
+    from astrai_b200.cli import runtime
+
+    blocks = [b for b in _blocks(_read("developer", "docker.md"), "yaml") if b.lstrip().startswith("runtime:")]
+    assert len(blocks) == 2
+    flat = runtime.exports("train", yaml.safe_load(blocks[0]), tmp_path)
+    assert "export ASTRAI_GPUS=0,1,2,3" in flat and "export ASTRAI_AUTO_RESUME=1" in flat and "export ASTRAI_MAX_HOURS=47.5" in flat
+    nested_cfg = yaml.safe_load(blocks[1])
+    nested = runtime.exports("train", nested_cfg, tmp_path)
+    assert "export ASTRAI_NPROCS=4" in nested and "export ASTRAI_CONTAINER=pretrain-1b" in nested
+    assert any(line.startswith("export ASTRAI_DATA_DIR=" + str(tmp_path)) for line in nested)  # resolved against the config's directory
+    assert runtime.environment_of(nested_cfg) == {"NCCL_DEBUG": "WARN"}
