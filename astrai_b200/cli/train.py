@@ -131,7 +131,8 @@ def plan(o: Dict[str, Any]) -> Dict[str, Any]:
     """What ``--dry-run`` prints: the merged options that matter, without touching data or devices."""
     keys = ("train_type", "data_root_path", "param_path", "resume", "n_epoch", "batch_per_device", "grad_accum_steps",
             "max_lr", "warmup_ratio", "max_grad_norm", "optimizer", "weight_decay", "schedule_type", "window_size", "stride",
-            "ckpt_dir", "ckpt_interval", "nprocs", "parallel_mode", "fsdp_comm", "fsdp_reshard", "tp_size", "cp_size", "ep_size", "pp_size", "pp_chunks", "mp_comm", "backend", "fp8", "fp8_recipe", "metrics",
+            "ckpt_dir", "ckpt_interval", "nprocs", "parallel_mode", "fsdp_comm", "fsdp_reshard", "tp_size", "cp_size", "ep_size",
+            "pp_size", "pp_chunks", "mp_comm", "backend", "fp8", "fp8_recipe", "metrics",
             "label_smoothing", "gradient_checkpointing", "random_seed")
     out = {k: (list(o[k]) if isinstance(o[k], tuple) else o[k]) for k in keys}
     out["tokens_per_optimizer_step"] = o["batch_per_device"] * o["grad_accum_steps"] * o["nprocs"] * (o["window_size"] or 0)
@@ -139,12 +140,18 @@ def plan(o: Dict[str, Any]) -> Dict[str, Any]:
 
 
 @click.command(context_settings={"show_default": True, "max_content_width": 110})
-@click.option("--config", "-c", type=click.Path(exists=True, dir_okay=False), default=None, help="YAML file; explicit options win.")
+@click.option("--config", "-c", type=click.Path(exists=True, dir_okay=False), default=None,
+              help="YAML file; explicit options win.")
 # basic
-@click.option("--train_type", type=click.Choice(["seq", "sft", "dpo", "grpo", "online_grpo", "online_dpo"]), default=None, help="Objective: next-token (seq), masked supervised (sft), preference pairs (dpo), groups of scored responses (grpo), or the last two with responses sampled during training (online_*).")
-@click.option("--data_root_path", type=str, default=None, help="Directory written by the preprocessing step (or raw .jsonl files for sft / dpo).")
+@click.option("--train_type", type=click.Choice(["seq", "sft", "dpo", "grpo", "online_grpo", "online_dpo"]), default=None,
+              help="Objective: next-token (seq), masked supervised (sft), preference pairs (dpo), groups of scored responses "
+                   "(grpo), or the last two with responses sampled during training (online_*).")
+@click.option("--data_root_path", type=str, default=None,
+              help="Directory written by the preprocessing step (or raw .jsonl files for sft / dpo).")
 @click.option("--param_path", type=str, default=None, help="Model directory (config.json [+ weights]) or checkpoint.")
-@click.option("--resume/--no-resume", default=False, help="Continue the run whose checkpoint --param_path names: optimizer, scheduler, epoch and position in the data.")
+@click.option("--resume/--no-resume", default=False,
+              help="Continue the run whose checkpoint --param_path names: optimizer, scheduler, epoch and position in the "
+                   "data.")
 @click.option("--n_epoch", type=int, default=1, help="Passes over the data.")
 @click.option("--batch_per_device", type=int, default=1, help="Samples per micro-batch on every data-parallel rank.")
 @click.option("--grad_accum_steps", type=int, default=1, help="Micro-batches per optimizer step.")
@@ -153,12 +160,16 @@ def plan(o: Dict[str, Any]) -> Dict[str, Any]:
 @click.option("--max_lr", type=float, default=3e-4, help="Peak learning rate.")
 @click.option("--max_grad_norm", type=click.FloatRange(min=0, min_open=True), default=1.0, help="Gradient-norm clip.")
 # optimizer
-@click.option("--optimizer", type=click.Choice(["muon_adamw", "nora_nadamw", "mano_adamw", "fused_adamw"]), default="muon_adamw", help="muon_adamw / nora_nadamw / mano_adamw: a matrix rule on the decoder blocks' 2-D weights, AdamW or NAdamW elsewhere; fused_adamw: AdamW everywhere, one kernel per parameter buffer.")
-@click.option("--weight_decay", type=float, default=0.1, help="Decoupled weight decay (not applied to norms, biases and embeddings by the composite optimizers).")
+@click.option("--optimizer", type=click.Choice(["muon_adamw", "nora_nadamw", "mano_adamw", "fused_adamw"]), default="muon_adamw",
+              help="muon_adamw / nora_nadamw / mano_adamw: a matrix rule on the decoder blocks' 2-D weights, AdamW or NAdamW "
+                   "elsewhere; fused_adamw: AdamW everywhere, one kernel per parameter buffer.")
+@click.option("--weight_decay", type=float, default=0.1,
+              help="Decoupled weight decay (not applied to norms, biases and embeddings by the composite optimizers).")
 @click.option("--muon_momentum", type=float, default=0.95, help="muon_adamw: momentum.")
 @click.option("--muon_nesterov/--no-muon_nesterov", default=True, help="muon_adamw: Nesterov momentum.")
 @click.option("--muon_ns_steps", type=int, default=5, help="muon_adamw: Newton-Schulz iterations of the orthogonalisation.")
-@click.option("--muon_adjust_lr", type=click.Choice(["original", "match_rms_adamw"]), default="match_rms_adamw", help="muon_adamw: learning-rate scaling per matrix shape.")
+@click.option("--muon_adjust_lr", type=click.Choice(["original", "match_rms_adamw"]), default="match_rms_adamw",
+              help="muon_adamw: learning-rate scaling per matrix shape.")
 @click.option("--nora_lr", type=float, default=5e-3, help="nora_nadamw: learning rate of the matrix rule.")
 @click.option("--nora_beta", type=float, default=0.95, help="nora_nadamw: second-moment decay of the matrix rule.")
 @click.option("--nora_momentum", type=float, default=0.95, help="nora_nadamw: momentum of the matrix rule.")
@@ -166,19 +177,26 @@ def plan(o: Dict[str, Any]) -> Dict[str, Any]:
 @click.option("--mano_momentum", type=float, default=0.95, help="mano_adamw: momentum.")
 @click.option("--mano_nesterov/--no-mano_nesterov", default=True, help="mano_adamw: Nesterov momentum.")
 # scheduler
-@click.option("--schedule_type", type=click.Choice(["cosine", "sgdr", "wsd"]), default="cosine", help="Learning-rate curve after the warm-up.")
-@click.option("--min_rate", type=float, default=None, help="Floor of the curve as a fraction of --max_lr (default: the scheduler's own).")
-@click.option("--cycle_length", type=int, default=None, help="sgdr: steps of the first cycle (default: all steps after the warm-up).")
+@click.option("--schedule_type", type=click.Choice(["cosine", "sgdr", "wsd"]), default="cosine",
+              help="Learning-rate curve after the warm-up.")
+@click.option("--min_rate", type=float, default=None,
+              help="Floor of the curve as a fraction of --max_lr (default: the scheduler's own).")
+@click.option("--cycle_length", type=int, default=None,
+              help="sgdr: steps of the first cycle (default: all steps after the warm-up).")
 @click.option("--t_mult", type=int, default=2, help="sgdr: every cycle is this many times longer than the one before.")
-@click.option("--stable_steps", type=int, default=None, help="wsd: steps at --max_lr (default: 80 % of the steps after the warm-up).")
+@click.option("--stable_steps", type=int, default=None,
+              help="wsd: steps at --max_lr (default: 80 % of the steps after the warm-up).")
 @click.option("--decay_steps", type=int, default=None, help="wsd: steps of the final decay (default: the rest).")
 # data
-@click.option("--window_size", type=int, default=None, help="Tokens per training sample (default: the model's max_position_embeddings).")
-@click.option("--stride", type=int, default=None, help="seq / sft: distance between the starts of two windows (default: the window).")
+@click.option("--window_size", type=int, default=None,
+              help="Tokens per training sample (default: the model's max_position_embeddings).")
+@click.option("--stride", type=int, default=None,
+              help="seq / sft: distance between the starts of two windows (default: the window).")
 @click.option("--random_seed", type=int, default=3407, help="Seed of the shuffling and of the validation split.")
 @click.option("--num_workers", type=int, default=4, help="Data-loader worker processes.")
 @click.option("--pin_memory/--no-pin_memory", default=True, help="Page-locked host batches.")
-@click.option("--persistent_workers/--no-persistent_workers", default=True, help="Keep the data-loader workers alive between epochs.")
+@click.option("--persistent_workers/--no-persistent_workers", default=True,
+              help="Keep the data-loader workers alive between epochs.")
 # checkpoints / validation / logging
 @click.option("--ckpt_interval", type=int, default=5000, help="Optimizer steps between checkpoints.")
 @click.option("--ckpt_dir", type=str, default="checkpoint", help="Where checkpoints and metric logs go.")
@@ -186,29 +204,43 @@ def plan(o: Dict[str, Any]) -> Dict[str, Any]:
 @click.option("--start_samples", type=int, default=0, help="Samples per rank to skip in the first epoch (without --resume).")
 @click.option("--val_split", type=float, default=None, help="Hold this fraction of the data out and log its loss.")
 @click.option("--val_step", type=int, default=1000, help="Optimizer steps between validation passes.")
-@click.option("--metrics", multiple=True, default=("loss", "lr", "grad_norm", "grad_snr"), help="Columns of metric.jsonl: loss, lr, grad_norm, grad_snr, val_loss, moe_aux_loss, router_entropy, dead_expert_fraction, load_imbalance_mean, load_imbalance_max.")
-@click.option("--gradient_checkpointing/--no-gradient_checkpointing", default=False, help="Recompute every decoder block in the backward pass.")
-@click.option("--compile", type=click.Choice(["default", "reduce-overhead", "max-autotune"]), default=None, help="Wrap the model in torch.compile with this mode (kept for configs of the reference; off by default, the kernels here are hand-written).")
+@click.option("--metrics", multiple=True, default=("loss", "lr", "grad_norm", "grad_snr"),
+              help="Columns of metric.jsonl: loss, lr, grad_norm, grad_snr, val_loss, moe_aux_loss, router_entropy, "
+                   "dead_expert_fraction, load_imbalance_mean, load_imbalance_max.")
+@click.option("--gradient_checkpointing/--no-gradient_checkpointing", default=False,
+              help="Recompute every decoder block in the backward pass.")
+@click.option("--compile", type=click.Choice(["default", "reduce-overhead", "max-autotune"]), default=None,
+              help="Wrap the model in torch.compile with this mode (kept for configs of the reference; off by default, the "
+                   "kernels here are hand-written).")
 @click.option("--dry-run", "dry_run", is_flag=True, default=False, help="Validate and print the plan; do not train.")
 # distributed
 @click.option("--nprocs", type=int, default=1, help="Ranks to spawn on this node (ignored under torchrun).")
 @click.option("--parallel_mode", type=click.Choice(["none", "ddp", "fsdp", "tp", "cp", "ep", "pp"]), default="fsdp",
               help="tp / cp / ep / pp: tensor-, context-, expert- or pipeline-parallel blocks of --tp_size / --cp_size / "
                    "--ep_size / --pp_size ranks.")
-@click.option("--fsdp_comm", type=click.Choice(["nccl", "p2p", "nvls"]), default="p2p", help="FSDP transport: NCCL or fused peer-memory kernels.")
+@click.option("--fsdp_comm", type=click.Choice(["nccl", "p2p", "nvls"]), default="p2p",
+              help="FSDP transport: NCCL or fused peer-memory kernels.")
 @click.option("--fsdp_reshard", is_flag=True, default=False,
               help="FSDP full-shard placement: parameters and gradients are whole only while their block computes "
                    "(gathers and reduce-scatters every micro-batch; NCCL transport).")
 @click.option("--device_type", type=str, default="cuda", help="cuda, or cpu for debugging with --backend gloo.")
-@click.option("--start_method", type=click.Choice(["spawn", "fork", "forkserver"]), default="spawn", help="How local ranks are started.")
+@click.option("--start_method", type=click.Choice(["spawn", "fork", "forkserver"]), default="spawn",
+              help="How local ranks are started.")
 @click.option("--backend", type=click.Choice(["nccl", "gloo"]), default="nccl", help="torch.distributed backend.")
 @click.option("--master_addr", type=str, default="127.0.0.1", help="Rendezvous address.")
 @click.option("--master_port", type=int, default=29500, help="Rendezvous port.")
-@click.option("--tp_size", type=int, default=None, help="Tensor-parallel size inside one NVSwitch domain (<= 8); default: all ranks.")
-@click.option("--cp_size", type=int, default=None, help="Context-parallel size (ranks that share one sequence); default: all ranks.")
-@click.option("--ep_size", type=int, default=None, help="Expert-parallel size (ranks that share one set of experts); default: all ranks.")
-@click.option("--pp_size", type=int, default=None, help="Pipeline stages (ranks that hold one model replica layer range by layer range); default: all ranks. Trains --train_type seq, sft, dpo and grpo.")
-@click.option("--pp_chunks", type=int, default=None, help="pp: pieces a per-device batch is cut into for the 1F1B schedule (default: the number of stages, at most the batch).")
+@click.option("--tp_size", type=int, default=None,
+              help="Tensor-parallel size inside one NVSwitch domain (<= 8); default: all ranks.")
+@click.option("--cp_size", type=int, default=None,
+              help="Context-parallel size (ranks that share one sequence); default: all ranks.")
+@click.option("--ep_size", type=int, default=None,
+              help="Expert-parallel size (ranks that share one set of experts); default: all ranks.")
+@click.option("--pp_size", type=int, default=None,
+              help="Pipeline stages (ranks that hold one model replica layer range by layer range); default: all ranks. "
+                   "Trains --train_type seq, sft, dpo and grpo.")
+@click.option("--pp_chunks", type=int, default=None,
+              help="pp: pieces a per-device batch is cut into for the 1F1B schedule (default: the number of stages, at most "
+                   "the batch).")
 @click.option("--mp_comm", type=click.Choice(["p2p", "nccl"]), default="p2p",
               help="tp / cp / ep transport: fused peer-memory kernels or library collectives around the same math.")
 @click.option("--fp8/--no-fp8", default=False, help="Run linear layers on fp8 tensor cores.")
@@ -220,7 +252,8 @@ def plan(o: Dict[str, Any]) -> Dict[str, Any]:
 @click.option("--group_size", type=int, default=4, help="grpo: responses per prompt.")
 @click.option("--grpo_clip_eps", type=float, default=0.2, help="grpo: clip range of the probability ratio.")
 @click.option("--grpo_kl_coef", type=float, default=0.01, help="grpo: weight of the KL term against the reference model.")
-@click.option("--moe_aux_loss_coef", type=float, default=0.01, help="Weight of the mixture-of-experts load-balancing loss (0 = off).")
+@click.option("--moe_aux_loss_coef", type=float, default=0.01,
+              help="Weight of the mixture-of-experts load-balancing loss (0 = off).")
 @click.option("--neftune_alpha", type=float, default=0.0, help="NEFTune noise on the embeddings while training (0 = off).")
 # rollout
 @click.option("--rollout_interval", type=int, default=512, help="online_*: samples between two rounds of generation.")
@@ -249,7 +282,8 @@ def train(**o):
     click.echo(f"training plan: {total_steps} optimizer steps, parallel_mode={cfg.parallel_mode}, nprocs={cfg.nprocs}")
     trainer = Trainer(cfg)
     if o.get("fp8"):
-        recipe = {"delayed": fp8_mod.DelayedScaling, "dynamic": fp8_mod.DynamicScaling, "block": fp8_mod.BlockScaling}[o.get("fp8_recipe") or "delayed"]()
+        recipes = {"delayed": fp8_mod.DelayedScaling, "dynamic": fp8_mod.DynamicScaling, "block": fp8_mod.BlockScaling}
+        recipe = recipes[o.get("fp8_recipe") or "delayed"]()
         with fp8_mod.fp8_autocast(recipe=recipe):
             trainer.train(o["param_path"], resume=o["resume"])
     else:

@@ -40,9 +40,11 @@ from astrai_b200.ops.functional import (
 )
 
 __all__ = [
-    "ATTN_BACKEND", "AttentionBackend", "AttentionBackendFactory", "CudaBackend", "FlashAttnBackend", "KERNEL_NAMES", "Tcgen05Backend",
-    "TensorLayout", "TorchNativeBackend", "apply_rotary_emb", "attention", "attn_backend", "attn_decode", "attn_paged_decode", "attn_paged_prefill", "attn_prefill", "flash_attn_available", "repeat_kv", "rotary_emb",
-    "get_backend", "is_available", "DelayedScaling", "DynamicScaling", "FP8Format", "fp8", "fp8_autocast", "adamw_", "add_rms_norm", "assume_loss_grad", "clip_coef", "cross_entropy", "dense_attention", "embedding", "gemm", "linear",
-    "linear_cross_entropy", "linear_token_logprobs", "loss_denominator", "native", "qkv_rope", "reference", "rms_norm", "rotary",
-    "sumsq", "swiglu", "swiglu_fused",
+    "adamw_", "add_rms_norm", "apply_rotary_emb", "assume_loss_grad", "attention", "AttentionBackend",
+    "AttentionBackendFactory", "ATTN_BACKEND", "attn_backend", "attn_decode", "attn_paged_decode", "attn_paged_prefill",
+    "attn_prefill", "clip_coef", "cross_entropy", "CudaBackend", "DelayedScaling", "dense_attention", "DynamicScaling",
+    "embedding", "flash_attn_available", "FlashAttnBackend", "fp8", "fp8_autocast", "FP8Format", "gemm", "get_backend",
+    "is_available", "KERNEL_NAMES", "linear", "linear_cross_entropy", "linear_token_logprobs", "loss_denominator",
+    "native", "qkv_rope", "reference", "repeat_kv", "rms_norm", "rotary", "rotary_emb", "sumsq", "swiglu",
+    "swiglu_fused", "Tcgen05Backend", "TensorLayout", "TorchNativeBackend",
 ]

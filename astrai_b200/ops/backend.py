@@ -6,7 +6,8 @@ framework has one architecture, so the choice is between the hand-written sm_100
 CUDA: flash forward / backward, ragged prefill, paged decode) and the plain-PyTorch statement (``TORCH_NATIVE``:
 SDPA, the only choice on CPU and the oracle / baseline on GPU).  The reference's names ``cuda`` and ``flash`` are
 accepted as aliases of ``TCGEN05``.  Selection order, as in the reference (``attention.py:204-217``): the process-wide
-``ASTR_BACKEND`` (or ``ASTRAI_B200_ATTN``) > the innermost ``attn_backend(...)`` context > default; a call the kernels do not cover (arbitrary boolean mask, head dim outside 64 / 128 for dense attention) falls
+``ASTR_BACKEND`` (or ``ASTRAI_B200_ATTN``) > the innermost ``attn_backend(...)`` context > default; a call the kernels
+do not cover (arbitrary boolean mask, head dim outside 64 / 128 for dense attention) falls
 back to ``TORCH_NATIVE`` unless the backend was chosen explicitly, in which case it raises.
 """
 
