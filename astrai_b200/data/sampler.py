@@ -42,8 +42,9 @@ class RDSampler(Sampler[int]):
             order = torch.randperm(self.num_samples, generator=g).tolist()
         else:
             order = list(range(self.num_samples))
-        if not self.drop_last and len(order) < self.total_size:
-            order += order[: self.total_size - len(order)]
+        if not self.drop_last and order and len(order) < self.total_size:
+            missing = self.total_size - len(order)  # wrap around, more than once when there are fewer samples than ranks
+            order += (order * (-(-missing // len(order))))[:missing]
         mine = order[self.rank:self.total_size:self.num_replicas]
         self._pending = mine[self.iter:]
 

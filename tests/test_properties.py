@@ -1,0 +1,225 @@
+"""Property-based checks (hypothesis, fixed seed): invariants that must hold for any input, not only the hand-picked ones."""
+
+import json
+import random
+
+import pytest
+import torch
+from hypothesis import HealthCheck, given, settings
+from hypothesis import strategies as st
+
+PROFILE = settings(max_examples=60, deadline=None, derandomize=True, suppress_health_check=[HealthCheck.too_slow])
+
+
+# ------------------------------------------------------------------------------------------------ paged pool + prefix index
+class _PoolModel:
+    """What the pool promises, stated naively: which token sequence every page of every live request holds."""
+
+    def __init__(self):
+        self.content = {}  # physical page -> tuple of the tokens whose K / V it holds (full pages only)
+
+
+@PROFILE
+@given(st.lists(st.tuples(st.sampled_from(["alloc", "extend", "finish", "drop"]), st.integers(0, 5), st.integers(1, 40)), min_size=1, max_size=60),
+       st.integers(0, 3))
+def test_paged_pool_never_hands_a_page_to_two_requests_and_prefix_hits_hold_the_right_tokens(ops, seed):
+    from astrai_b200.inference.cache import PagePool, TaskCacheManager
+
+    page = 4
+    pool = PagePool(n_layers=1, n_kv_heads=1, head_dim=2, max_batch_size=4, max_seq_len=48, device="cpu", dtype=torch.float32,
+                    page_size=page, n_tokens=page * 20)
+    mgr = TaskCacheManager(pool)
+    rng = random.Random(seed)
+    live = {}          # task id -> list of token ids whose K / V are in the cache
+    holds = {}         # physical page -> tokens it was last filled with (as the index may remember them)
+    serial = 0
+    for kind, which, n in ops:
+        if kind == "alloc":
+            serial += 1
+            # prompts share prefixes: they are cut from three fixed streams
+            stream = [(which * 7 + i * (which + 1)) % 11 for i in range(64)]
+            prompt = stream[: max(1, min(n, 40))]
+            tid = f"t{serial}"
+            if mgr.task_alloc(tid, prompt):
+                state = mgr.state(tid)
+                # the cached prefix is whole pages, strictly shorter than the prompt, and holds exactly these tokens
+                assert state.cached % page == 0 and state.cached < len(prompt) + page
+                for i in range(state.cached // page):
+                    assert holds.get(state.pages[i]) == tuple(prompt[i * page:(i + 1) * page])
+                mgr.task_record_hashes(tid, prompt, state.cached // page)
+                for i in range(len(prompt) // page):
+                    holds[state.pages[i]] = tuple(prompt[i * page:(i + 1) * page])
+                live[tid] = list(prompt)
+        elif live:
+            tid = sorted(live)[which % len(live)]
+            if kind == "extend":
+                for _ in range(min(n, 6)):
+                    pos = len(live[tid])
+                    if not mgr.task_extend(tid, pos):
+                        break
+                    live[tid].append(rng.randrange(11))
+            else:
+                if kind == "finish":  # a finished request leaves its full pages in the index
+                    state = mgr.state(tid)
+                    mgr.task_record_hashes(tid, live[tid])
+                    for i in range(len(live[tid]) // page):
+                        holds[state.pages[i]] = tuple(live[tid][i * page:(i + 1) * page])
+                mgr.task_free(tid)
+                del live[tid]
+        # invariants after every operation
+        owners = {}
+        for tid, tokens in live.items():
+            state = mgr.state(tid)
+            assert state.length == len(tokens) and len(state.pages) * page >= len(tokens)
+            for i, p in enumerate(state.pages):
+                owners.setdefault(p, []).append((tid, i))
+        for p, users in owners.items():
+            assert pool.allocator.ref_count(p) == len(users)
+            if len(users) > 1:  # a shared page is a shared prefix page: the same position, the same tokens, full
+                assert len({i for _, i in users}) == 1
+                i = users[0][1]
+                spans = {tuple(live[t][i * page:(i + 1) * page]) for t, _ in users}
+                assert len(spans) == 1 and len(next(iter(spans))) == page
+        in_use = len(owners)
+        assert pool.allocator.available() == 20 - in_use
+    for tid in list(live):
+        mgr.task_free(tid)
+    assert pool.allocator.available() == 20
+
+
+# ----------------------------------------------------------------------------------------------------------- packing
+@PROFILE
+@given(st.lists(st.integers(1, 30), min_size=1, max_size=40), st.integers(4, 24), st.sampled_from(["keep_start", "keep_end"]))
+def test_bfd_bins_hold_every_document_once_and_never_overflow(lengths, limit, mode):
+    from astrai_b200.preprocessing.packing import plan_bfd
+
+    docs = [[i] * n for i, n in enumerate(lengths)]
+    bins = plan_bfd(docs, limit, mode)
+    seen = sorted(i for b in bins for i in b)
+    assert seen == list(range(len(docs)))
+    for b in bins:
+        assert sum(min(lengths[i], limit) for i in b) <= limit
+    # no two bins could have been merged at the time the later one was opened: every bin after the first is more than
+    # the room left in some earlier one only if ... (best fit): at least, no bin is empty
+    assert all(b for b in bins)
+
+
+@PROFILE
+@given(st.lists(st.lists(st.integers(1, 99), min_size=1, max_size=25), min_size=1, max_size=12), st.integers(4, 16),
+       st.sampled_from(["simple", "bfd", "bfd_split"]))
+def test_packers_keep_columns_aligned_and_lose_tokens_only_by_truncation(docs, limit, name):
+    from astrai_b200.preprocessing.packing import PackingStrategyFactory
+
+    keys = {"sequence": [list(d) for d in docs], "loss_mask": [[t % 2 for t in d] for d in docs]}
+    out = PackingStrategyFactory.create(name).apply(keys, limit, "keep_start")
+    assert len(out["sequence"]) == len(out["loss_mask"])
+    for seq, mask in zip(out["sequence"], out["loss_mask"]):
+        assert len(seq) == len(mask) and [t % 2 for t in seq] == mask  # the mask travelled with its tokens
+        assert len(seq) <= limit
+    kept = sorted(t for seq in out["sequence"] for t in seq)
+    if name == "bfd_split":  # long documents are cut into pieces, nothing is lost
+        assert kept == sorted(t for d in docs for t in d)
+    else:  # "simple" does not pack at all, "bfd" packs whole documents: both cut a long document to the limit
+        assert kept == sorted(t for d in docs for t in d[:limit])
+    if name == "simple":
+        assert out["sequence"] == [d[:limit] for d in docs]
+
+
+# ------------------------------------------------------------------------------------------------- tool-call parser
+@PROFILE
+@given(st.lists(st.integers(1, 9), min_size=1, max_size=40), st.booleans(), st.integers(0, 2))
+def test_tool_parser_gives_the_same_calls_for_any_chunking(cuts, with_text, n_calls):
+    from astrai_b200.inference.network import ToolParserFactory
+
+    calls = [{"name": f"fn_{i}", "arguments": {"x": i, "s": 'a "quoted" } brace', "nested": {"k": [1, 2, {"z": "}"}]}}} for i in range(n_calls)]
+    text = ("Let me look that up. " if with_text else "") + " ".join(json.dumps(c, ensure_ascii=False) for c in calls)
+    whole = ToolParserFactory.create("simple_json").parse_complete(text) or {}
+    parser = ToolParserFactory.create("simple_json")
+    names, args, content, pos, i = {}, {}, "", 0, 0
+    while pos < len(text):
+        pos = min(pos + cuts[i % len(cuts)], len(text))
+        i += 1
+        for delta in parser.feed(text[:pos]):  # the parser is handed everything generated so far
+            content += delta.get("content", "")
+            for tc in delta.get("tool_calls", []):
+                fn = tc.get("function", {})
+                if fn.get("name"):
+                    assert tc["index"] not in names  # the name comes once, before any argument text
+                    names[tc["index"]] = fn["name"]
+                args[tc["index"]] = args.get(tc["index"], "") + fn.get("arguments", "")
+    got = [{"name": names[k], "arguments": json.loads("{" + args[k] + "}")} for k in sorted(names)]  # deltas carry the inner text
+    assert got == calls
+    # as in the reference, "arguments" is the text between the outer braces of the arguments object
+    whole_calls = [{"name": c["function"]["name"], "arguments": json.loads("{" + c["function"]["arguments"] + "}")}
+                   for c in whole.get("tool_calls", [])]
+    assert whole_calls == calls
+    if with_text:
+        assert content.strip() == "Let me look that up."
+    elif calls:
+        assert content.strip() == ""
+    assert parser.has_tool_calls == bool(calls)
+
+
+# --------------------------------------------------------------------------------------------------------- sampler
+@PROFILE
+@given(st.integers(1, 97), st.integers(1, 6), st.integers(0, 5), st.integers(0, 3), st.booleans())
+def test_sampler_ranks_cover_the_data_and_a_resumed_rank_continues_where_it_stopped(n, world, seed, epoch, shuffle):
+    from astrai_b200.data import RDSampler
+
+    data = list(range(n))
+    per_rank = []
+    for rank in range(world):
+        s = RDSampler(data, partition=(rank, world), seed=seed, shuffle=shuffle, start_epoch=epoch)
+        assert len(s) == -(-n // world)
+        idx = list(s)
+        assert len(idx) == -(-n // world)
+        per_rank.append(idx)
+        cut = len(idx) // 2
+        resumed = RDSampler(data, partition=(rank, world), seed=seed, shuffle=shuffle, start_epoch=epoch, start_iter=cut)
+        assert list(resumed) == idx[cut:]
+    flat = [i for idx in per_rank for i in idx]
+    assert set(flat) == set(data)                       # everything is drawn
+    assert len(flat) - n < world                        # padding by wrapping: fewer than one extra sample per rank
+    if n % world == 0:                                  # no padding: the ranks' shares are disjoint
+        assert len(set(flat)) == len(flat)
+
+
+# ------------------------------------------------------------------------------------------------ streaming detokeniser
+@pytest.fixture(scope="module")
+def tokenizer(tmp_path_factory):
+    from astrai_b200.tokenize import AutoTokenizer
+    from helpers import build_tokenizer_dir
+
+    return AutoTokenizer.from_pretrained(build_tokenizer_dir(str(tmp_path_factory.mktemp("tok"))))
+
+
+@PROFILE
+@given(st.lists(st.sampled_from(list("abc xyz,.!?\n") + ["é", "ß", "漢", "字", "🙂", "the ", "quick ", "hello world"]), max_size=30))
+def test_streamed_pieces_add_up_to_the_decoded_text(tokenizer, parts):
+    text = "".join(parts)
+    from astrai_b200.inference.task import StreamDecoder
+
+    ids = tokenizer.encode(text)
+    decoder = StreamDecoder(tokenizer)
+    pieces = [decoder.push(i) for i in ids]
+    assert all(isinstance(p, str) for p in pieces)
+    joined = "".join(pieces)
+    whole = tokenizer.decode(ids)
+    assert whole.startswith(joined)  # nothing wrong is ever emitted; an unfinished multi-byte character may be held back
+    assert "�" not in joined
+    if ids and whole and not whole.endswith("�"):
+        assert joined == whole
+
+
+# ------------------------------------------------------------------------------------------------------ stop sequences
+@PROFILE
+@given(st.lists(st.text(alphabet="ab|", min_size=0, max_size=3), max_size=4), st.text(alphabet="ab|", max_size=12))
+def test_stop_checker_finds_a_sequence_exactly_when_one_occurs(stops, text):
+    from astrai_b200.inference.network import StopChecker
+
+    found = StopChecker(stops).check(text)
+    real = [s for s in stops if s]
+    if found is None:
+        assert not any(s in text for s in real)
+    else:
+        assert found in real and found in text
