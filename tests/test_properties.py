@@ -223,3 +223,98 @@ def test_stop_checker_finds_a_sequence_exactly_when_one_occurs(stops, text):
         assert not any(s in text for s in real)
     else:
         assert found in real and found in text
+
+
+# ------------------------------------------------------------------------------ continuous batching does not change answers
+@pytest.fixture(scope="module")
+def tiny_lm():
+    from astrai_b200.models import AutoRegressiveLM
+    from helpers import tiny_config
+
+    torch.manual_seed(0)
+    return AutoRegressiveLM(tiny_config(vocab_size=256, hidden_size=32, intermediate_size=64, max_position_embeddings=128)).eval()
+
+
+class _Ids:
+    stop_ids = [1]
+
+    def encode(self, text):
+        return [int(t) for t in str(text).split()]
+
+    def decode(self, ids, skip_special_tokens=True):
+        return " ".join(map(str, ids))
+
+
+_ALONE = {}
+
+
+def _alone(model, prompt, budget):
+    """Greedy answer of one prompt on its own, contiguous cache, whole-prompt prefill: the statement to agree with."""
+    from astrai_b200.inference import InferenceScheduler
+
+    key = (tuple(prompt), budget)
+    if key not in _ALONE:
+        s = InferenceScheduler(model, _Ids(), max_batch_size=1, max_seq_len=96, enable_cuda_graph=False, paged=False, page_size=1)
+        _ALONE[key] = s.run_batch([list(prompt)], max_tokens=budget, temperature=0.0)[0]
+    return _ALONE[key]
+
+
+@settings(max_examples=25, deadline=None, derandomize=True, suppress_health_check=[HealthCheck.too_slow, HealthCheck.function_scoped_fixture])
+@given(st.lists(st.tuples(st.integers(0, 2), st.integers(1, 30), st.integers(1, 8)), min_size=1, max_size=6),
+       st.sampled_from([4, 8, 16]), st.booleans(), st.sampled_from([8, 24, 4096]), st.integers(1, 6))
+def test_answers_do_not_depend_on_batch_mates_page_size_or_prefill_chunking(tiny_lm, requests, page, chunked, prefill_budget, slots):
+    from astrai_b200.inference import InferenceScheduler
+
+    # prompts are cut from three streams, so that several share page-aligned prefixes and hit the prefix index
+    prompts = [[(stream * 37 + i * (stream + 3)) % 250 + 2 for i in range(n)] for stream, n, _ in requests]
+    budgets = [b for _, _, b in requests]
+    sched = InferenceScheduler(tiny_lm, _Ids(), max_batch_size=slots, max_seq_len=96, enable_cuda_graph=False, paged=True, page_size=page,
+                               kv_cache_tokens=96 * 8, chunked_prefill=chunked, max_prefill_tokens=prefill_budget)
+    want = [_alone(tiny_lm, p, b) for p, b in zip(prompts, budgets)]
+    # the synchronous path takes one budget for the batch: group the requests by budget, twice over to reuse cached prefixes
+    for _ in range(2):
+        for budget in sorted(set(budgets)):
+            group = [i for i, b in enumerate(budgets) if b == budget]
+            for start in range(0, len(group), slots):
+                part = group[start:start + slots]
+                got = sched.run_batch([prompts[i] for i in part], max_tokens=budget, temperature=0.0)
+                assert got == [want[i] for i in part]
+    assert sched._cache.allocator.available() == 96 * 8 // page  # every page came back
+
+
+@settings(max_examples=8, deadline=None, derandomize=True, suppress_health_check=[HealthCheck.too_slow, HealthCheck.function_scoped_fixture])
+@given(st.lists(st.tuples(st.integers(0, 2), st.integers(1, 30), st.integers(1, 8), st.integers(0, 3)), min_size=1, max_size=10),
+       st.sampled_from([4, 16]), st.booleans(), st.integers(1, 4), st.sampled_from([0, 2]))
+def test_the_serving_loop_gives_every_request_its_own_answer_whenever_it_arrives(tiny_lm, requests, page, chunked, slots, defer):
+    import threading
+    import time
+
+    from astrai_b200.inference import InferenceScheduler
+    from astrai_b200.inference.task import STOP
+
+    prompts = [[(stream * 37 + i * (stream + 3)) % 250 + 2 for i in range(n)] for stream, n, _, _ in requests]
+    want = [_alone(tiny_lm, p, b) for p, (_, _, b, _) in zip(prompts, requests)]
+    sched = InferenceScheduler(tiny_lm, _Ids(), max_batch_size=slots, max_seq_len=96, enable_cuda_graph=False, paged=True, page_size=page,
+                               kv_cache_tokens=96 * 6, chunked_prefill=chunked, max_prefill_tokens=16, prefill_defer_steps=defer,
+                               prefill_defer_min_batch=1, prefill_defer_tokens=64)
+    got = [[] for _ in prompts]
+    done = [threading.Event() for _ in prompts]
+
+    def collector(i):
+        def on_piece(piece):
+            if piece is STOP:
+                done[i].set()
+            else:
+                got[i].extend(int(t) for t in piece.split())
+        return on_piece
+
+    sched.start()
+    try:
+        for i, (prompt, (_, _, budget, pause)) in enumerate(zip(prompts, requests)):
+            sched.add_task(prompt, max_tokens=budget, temperature=0.0, stream_callback=collector(i))
+            time.sleep(pause * 0.003)  # some arrive together, some while others decode
+        assert all(e.wait(timeout=60) for e in done)
+    finally:
+        sched.stop()
+    assert got == want
+    assert sched._cache.allocator.available() == 96 * 6 // page
