@@ -318,3 +318,135 @@ def test_the_serving_loop_gives_every_request_its_own_answer_whenever_it_arrives
         sched.stop()
     assert got == want
     assert sched._cache.allocator.available() == 96 * 6 // page
+
+
+# ------------------------------------------------------------------------------------------- learning-rate schedules
+@PROFILE
+@given(st.sampled_from(["cosine", "sgdr", "wsd"]), st.integers(0, 20), st.integers(1, 60), st.floats(0.0, 0.5), st.integers(0, 90))
+def test_schedules_stay_in_bounds_warm_up_monotonically_and_resume_exactly(kind, warmup, span, floor, resume_at):
+    from astrai_b200.trainer import SchedulerFactory
+
+    def make():
+        opt = torch.optim.SGD([torch.nn.Parameter(torch.zeros(1))], lr=2.0)
+        extra = {"cosine": {"lr_decay_steps": span}, "sgdr": {"cycle_length": span, "t_mult": 2},
+                 "wsd": {"stable_steps": span // 2, "decay_steps": max(span - span // 2, 1)}}[kind]
+        return opt, SchedulerFactory.create(kind, opt, warmup_steps=warmup, min_rate=floor, **extra)
+
+    opt, sched = make()
+    lrs = []
+    for _ in range(100):
+        lrs.append(opt.param_groups[0]["lr"])
+        opt.step()
+        sched.step()
+    assert all(2.0 * floor - 1e-9 <= lr <= 2.0 + 1e-9 for lr in lrs)
+    assert all(b >= a - 1e-12 for a, b in zip(lrs[:warmup], lrs[1:warmup + 1]))  # never falls while warming up
+    if warmup < 100:
+        assert lrs[warmup] == pytest.approx(2.0)  # the peak is reached right after the warm-up
+    # a scheduler rebuilt from the state saved after `resume_at` steps continues the same curve
+    opt2, sched2 = make()
+    for _ in range(resume_at):
+        opt2.step()
+        sched2.step()
+    state = sched2.state_dict()
+    opt3, sched3 = make()
+    sched3.load_state_dict(state)
+    for g, lr in zip(opt3.param_groups, sched3.get_last_lr()):
+        g["lr"] = lr
+    tail = []
+    for _ in range(100 - resume_at):
+        tail.append(opt3.param_groups[0]["lr"])
+        opt3.step()
+        sched3.step()
+    assert tail == pytest.approx(lrs[resume_at:], abs=1e-12)
+
+
+# ------------------------------------------------------------------------------------------------- sampling filters
+@PROFILE
+@given(st.integers(1, 4), st.integers(2, 40), st.integers(0, 45), st.floats(0.05, 1.0), st.floats(0.1, 3.0), st.integers(0, 10))
+def test_filters_keep_the_most_likely_tokens_and_enough_probability_mass(rows, vocab, k, p, temperature, seed):
+    from astrai_b200.inference.runtime.sample import SamplingPipeline, TemperatureStrategy, TopKStrategy, TopPStrategy
+
+    logits = torch.randn(rows, vocab, generator=torch.Generator().manual_seed(seed)) * 3
+    scaled = logits / temperature
+    after_k = TopKStrategy(k).apply(TemperatureStrategy(temperature).apply(logits))
+    kept_k = torch.isfinite(after_k)
+    for r in range(rows):
+        n = int(kept_k[r].sum())
+        assert n >= 1 and (k <= 0 or k >= vocab or n >= min(k, vocab))       # ties may keep more than k, never fewer
+        if 0 < k < vocab:
+            assert scaled[r][kept_k[r]].min() >= scaled[r][~kept_k[r]].max() if (~kept_k[r]).any() else True
+    out = SamplingPipeline([TemperatureStrategy(temperature), TopKStrategy(k), TopPStrategy(p)]).apply(logits)
+    kept = torch.isfinite(out)
+    probs_after_k = torch.softmax(after_k, -1)
+    for r in range(rows):
+        assert kept[r].any() and (kept[r] <= kept_k[r]).all()                  # top-p only removes
+        assert kept[r][out[r].argmax()] and out[r].argmax() == logits[r].argmax()  # the most likely token always survives
+        mass = float(probs_after_k[r][kept[r]].sum())
+        assert mass >= min(p, 1.0) - 1e-5                                      # the kept set carries at least p of the mass
+        if (~kept[r] & kept_k[r]).any():                                       # whatever was removed is no likelier than what stayed
+            assert probs_after_k[r][kept[r]].min() >= probs_after_k[r][~kept[r] & kept_k[r]].max() - 1e-7
+
+
+# --------------------------------------------------------------------------------- packed-document attention relations
+@PROFILE
+@given(st.lists(st.lists(st.integers(1, 6), min_size=1, max_size=5), min_size=1, max_size=4))
+def test_run_boundaries_describe_the_same_relation_as_the_dense_document_mask(doc_lengths):
+    from astrai_b200.ops.segments import from_position_ids
+    from astrai_b200.trainer.strategy import make_doc_boundary_mask
+
+    width = max(sum(row) for row in doc_lengths)
+    rows = []
+    for row in doc_lengths:
+        pos = [i for n in row for i in range(n)]
+        pos += list(range(width - len(pos)))  # the tail is one more document (possibly empty)
+        rows.append(pos)
+    position_ids = torch.tensor(rows)
+    seg = from_position_ids(position_ids)
+    assert torch.equal(seg.to_dense(), make_doc_boundary_mask(position_ids))
+    assert seg.bounds[0] == 0 and seg.bounds[-1] == len(rows) * width and seg.bounds == sorted(set(seg.bounds))
+    assert seg.max_len == max(b - a for a, b in zip(seg.bounds[:-1], seg.bounds[1:]))
+    if width > 1:  # the inputs of a next-token objective lose their last column; so do the runs
+        assert torch.equal(seg.drop_last().to_dense(), make_doc_boundary_mask(position_ids)[:, :, :-1, :-1])
+
+
+# ------------------------------------------------------------------------------------------------ zig-zag sequence sharding
+@PROFILE
+@given(st.integers(1, 4), st.integers(1, 5), st.integers(1, 3))
+def test_zigzag_split_and_merge_are_inverse_and_balance_causal_work(world, chunk, batch):
+    from astrai_b200.parallel.context_parallel import zigzag_merge, zigzag_positions, zigzag_split
+
+    seq = 2 * world * chunk
+    x = torch.arange(batch * seq * 3).view(batch, seq, 3)
+    parts = [zigzag_split(x, world, r) for r in range(world)]
+    assert all(p.shape == (batch, 2 * chunk, 3) for p in parts)
+    assert torch.equal(zigzag_merge(parts), x)
+    for r in range(world):
+        pos = zigzag_positions(seq, world, r)
+        assert torch.equal(parts[r][0, :, 0] // 3, pos)  # a rank's rows sit at exactly these positions
+    work = [int(zigzag_positions(seq, world, r).add(1).sum()) for r in range(world)]
+    assert len(set(work)) == 1  # keys visible to a rank's queries under causal attention: the same for every rank
+
+
+# -------------------------------------------------------------------------------------------- expert capacity limit
+@PROFILE
+@given(st.integers(1, 24), st.integers(1, 3), st.sampled_from([(4, 2), (8, 4), (6, 3), (4, 4)]), st.floats(1.0, 3.0), st.integers(0, 20))
+def test_capacity_limit_never_overfills_a_destination_and_only_drops_what_does_not_fit(tokens, k, shape, factor, seed):
+    from astrai_b200.parallel.expert_parallel import limit_rows_per_rank
+
+    experts, world = shape
+    g = torch.Generator().manual_seed(seed)
+    idx = torch.randint(0, experts, (tokens, k), generator=g)
+    if seed % 3 == 0:
+        idx[: tokens // 2 + 1] = 0  # a hot expert
+    w = torch.rand(tokens, k, generator=g) + 0.1
+    new_idx, new_w, counts, dropped = limit_rows_per_rank(idx, w, experts, world, factor)
+    cap = int(factor * tokens * k) // world
+    local = experts // world
+    per_rank = counts.view(world, local).sum(1)
+    assert int(counts.sum()) == tokens * k and (per_rank <= max(cap, 0)).all() or cap * world < tokens * k
+    kept = new_w > 0
+    assert torch.equal(new_idx[kept], idx[kept]) and torch.equal(new_w[kept], w[kept])  # kept pairs are untouched
+    assert int((~kept).sum()) == int(dropped)
+    sent = torch.bincount((idx // local).flatten(), minlength=world)
+    assert int(dropped) == int((sent - cap).clamp(min=0).sum())  # exactly the overflow is dropped, nothing more
+    assert torch.equal(counts, torch.bincount(new_idx.flatten(), minlength=experts).int())
