@@ -450,3 +450,58 @@ def test_capacity_limit_never_overfills_a_destination_and_only_drops_what_does_n
     sent = torch.bincount((idx // local).flatten(), minlength=world)
     assert int(dropped) == int((sent - cap).clamp(min=0).sum())  # exactly the overflow is dropped, nothing more
     assert torch.equal(counts, torch.bincount(new_idx.flatten(), minlength=experts).int())
+
+
+# -------------------------------------------------------------------------------------------------- training windows
+@PROFILE
+@given(st.lists(st.integers(1, 40), min_size=1, max_size=5), st.integers(1, 24), st.integers(1, 30))
+def test_windows_tile_the_token_stream_across_shards_and_shift_targets_by_one(tmp_path_factory, shard_sizes, window, stride):
+    from astrai_b200.data import DatasetFactory
+    from astrai_b200.serialization import save_bin
+
+    root = tmp_path_factory.mktemp("windows")
+    total, start = sum(shard_sizes), 0
+    for i, n in enumerate(shard_sizes):  # the stream 0, 1, 2, ... cut into shards of uneven size
+        save_bin(str(root / f"shard_{i:04d}"), {"sequence": [torch.arange(start, start + n, dtype=torch.int32)]})
+        start += n
+    ds = DatasetFactory.load("seq", str(root), window_size=window, stride=stride)
+    want = 0 if total <= window else (total - 1 - window) // stride + 1
+    assert len(ds) == want
+    covered = set()
+    for i in range(len(ds)):
+        item = ds[i]
+        x, y = item["input_ids"].tolist(), item["target_ids"].tolist()
+        assert len(x) == len(y) == window and y == [t + 1 for t in x]        # next-token targets
+        assert x == list(range(x[0], x[0] + window)) and x[-1] <= total - 2   # contiguous, across shard boundaries, inside the data
+        assert x[0] == min(i * stride, total - 1 - window)
+        covered.update(x)
+    if want and stride <= window:
+        assert covered == set(range(0, max(covered) + 1)) and max(covered) >= total - 1 - stride  # no holes; the tail is short of a stride
+
+
+# ------------------------------------------------------------------------------------------------------ chat masking
+@settings(max_examples=40, deadline=None, derandomize=True, suppress_health_check=[HealthCheck.too_slow, HealthCheck.function_scoped_fixture])
+@given(st.lists(st.tuples(st.sampled_from(["system", "user", "assistant", "tool"]), st.sampled_from(["hello world", "the quick brown fox", "a", "é ß", "x " * 9])),
+                min_size=1, max_size=7),
+       st.sampled_from(["mask", "train"]), st.integers(4, 80))
+def test_chat_records_train_exactly_the_roles_the_config_names(tokenizer, turns, default, limit):
+    from astrai_b200.config import PipelineConfig
+    from astrai_b200.preprocessing import MaskBuilderFactory
+
+    cfg = PipelineConfig.from_dict({"input": {"sections": [{"field": "messages", "action": "$role", "template": True}]},
+                                    "mask": {"user": "mask", "assistant": "train"}, "mask_default": default,
+                                    "preprocessing": {"max_seq_len": limit}})
+    messages = [{"role": r, "content": c} for r, c in turns]
+    builder = MaskBuilderFactory.create("single")
+    rec = builder.build({"messages": messages}, cfg, tokenizer)
+    pieces = [tokenizer.encode(tokenizer.apply_chat_template([m], tokenize=False, add_generation_prompt=False), add_special_tokens=False)
+              for m in messages]
+    ids = [tokenizer.bos_token_id] + [t for p in pieces for t in p]
+    trains = {"user": 0, "assistant": 1}
+    mask = [0] + [trains.get(m["role"], int(default == "train")) for m, p in zip(messages, pieces) for _ in p]
+    assert rec is not None and rec["sequence"] == ids[:limit]
+    if "loss_mask" in rec:
+        assert rec["loss_mask"] == mask[:limit]
+    else:  # every token trains: the mask is left out
+        assert all(mask[:limit])
+    assert builder.build_batch([{"messages": messages}, {"messages": messages[:1]}], cfg, tokenizer)[0] == rec
