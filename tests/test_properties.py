@@ -505,3 +505,76 @@ def test_chat_records_train_exactly_the_roles_the_config_names(tokenizer, turns,
     else:  # every token trains: the mask is left out
         assert all(mask[:limit])
     assert builder.build_batch([{"messages": messages}, {"messages": messages[:1]}], cfg, tokenizer)[0] == rec
+
+
+# --------------------------------------------------------------------------------------- padding never changes a loss
+def _frozen_copy(model):
+    import copy
+
+    return copy.deepcopy(model).requires_grad_(False).eval()
+
+
+@settings(max_examples=15, deadline=None, derandomize=True, suppress_health_check=[HealthCheck.too_slow, HealthCheck.function_scoped_fixture])
+@given(st.integers(1, 3), st.integers(5, 12), st.integers(0, 5), st.integers(0, 4), st.integers(0, 30))
+def test_preference_loss_does_not_depend_on_the_amount_of_padding(tiny_lm, pairs, length, extra_right, shorter, seed):
+    from astrai_b200.data import dpo_collate_fn
+    from astrai_b200.trainer import StrategyFactory
+
+    g = torch.Generator().manual_seed(seed)
+    items = []
+    for i in range(pairs):
+        n_c, n_r = length - (i * shorter) % 4, length - ((i + 1) * shorter) % 3
+        chosen, rejected = torch.randint(2, 250, (n_c,), generator=g), torch.randint(2, 250, (n_r,), generator=g)
+        rejected[:3] = chosen[:3]
+        cm, rm = torch.ones(n_c, dtype=torch.bool), torch.ones(n_r, dtype=torch.bool)
+        cm[:3], rm[:3] = False, False
+        items.append({"chosen": chosen, "rejected": rejected, "chosen_mask": cm, "rejected_mask": rm})
+    batch = dpo_collate_fn(items)
+    wide = {k: torch.nn.functional.pad(v, (0, extra_right)) for k, v in batch.items()}
+    policy = _frozen_copy(tiny_lm).train()
+    with torch.no_grad():  # move the policy away from the reference so that the margin is not identically zero
+        for p in policy.parameters():
+            p.add_(0.05 * torch.randn(p.shape, generator=g))
+    s = StrategyFactory.create("dpo", model=policy, device="cpu", ref_model=_frozen_copy(tiny_lm), beta=0.3)
+    a, b = float(s(batch)["loss"]), float(s(wide)["loss"])
+    assert a == pytest.approx(b, abs=2e-5) and abs(a - 0.6931) > 1e-6
+    # one pair at a time: the batch loss is the mean of the pairs' losses
+    singles = [float(s(dpo_collate_fn([it]))["loss"]) for it in items]
+    assert a == pytest.approx(sum(singles) / len(singles), abs=2e-5)
+
+
+@settings(max_examples=12, deadline=None, derandomize=True, suppress_health_check=[HealthCheck.too_slow, HealthCheck.function_scoped_fixture])
+@given(st.integers(1, 2), st.integers(2, 3), st.integers(3, 7), st.integers(3, 7), st.integers(0, 4), st.integers(0, 3), st.integers(0, 30))
+def test_group_loss_does_not_depend_on_the_amount_of_padding(tiny_lm, prompts, group, plen, rlen, extra_left, extra_right, seed):
+    from astrai_b200.data import grpo_collate_fn
+    from astrai_b200.trainer import StrategyFactory
+
+    g = torch.Generator().manual_seed(seed)
+    items = []
+    for i in range(prompts):
+        p = torch.randint(2, 250, (plen - i % 2,), generator=g)
+        resp = [torch.randint(2, 250, (rlen - (i + j) % 3,), generator=g) for j in range(group)]
+        items.append({"prompts": p, "responses": resp, "masks": [torch.ones_like(r, dtype=torch.bool) for r in resp],
+                      "rewards": torch.rand(group, generator=g)})
+    batch = grpo_collate_fn(items)
+    wide = dict(batch)
+    wide["prompts"] = torch.nn.functional.pad(batch["prompts"], (extra_left, 0))
+    wide["prompt_mask"] = torch.nn.functional.pad(batch["prompt_mask"], (extra_left, 0))
+    wide["responses"] = torch.nn.functional.pad(batch["responses"], (0, extra_right))
+    wide["masks"] = torch.nn.functional.pad(batch["masks"], (0, extra_right))
+    policy = _frozen_copy(tiny_lm).train()
+    with torch.no_grad():
+        for p in policy.parameters():
+            p.add_(0.05 * torch.randn(p.shape, generator=g))
+
+    class Exec:
+        use_distributed = False
+
+        def unwrap_model(self, m):
+            return m.state_dict()
+
+    s = StrategyFactory.create("grpo", model=policy, device="cpu", old_model=_frozen_copy(tiny_lm), ref_model=_frozen_copy(tiny_lm),
+                               group_size=group, clip_eps=0.2, kl_coef=0.05, executor=Exec())
+    a, b = s(batch), s(wide)
+    assert float(a["loss"]) == pytest.approx(float(b["loss"]), abs=2e-5)
+    assert float(a["metrics"]["kl_loss"]) == pytest.approx(float(b["metrics"]["kl_loss"]), abs=2e-5) and float(a["metrics"]["kl_loss"]) > 0
