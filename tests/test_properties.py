@@ -578,3 +578,48 @@ def test_group_loss_does_not_depend_on_the_amount_of_padding(tiny_lm, prompts, g
     a, b = s(batch), s(wide)
     assert float(a["loss"]) == pytest.approx(float(b["loss"]), abs=2e-5)
     assert float(a["metrics"]["kl_loss"]) == pytest.approx(float(b["metrics"]["kl_loss"]), abs=2e-5) and float(a["metrics"]["kl_loss"]) > 0
+
+
+# ------------------------------------------------------------------------------------ packing never leaks across documents
+@settings(max_examples=15, deadline=None, derandomize=True, suppress_health_check=[HealthCheck.too_slow, HealthCheck.function_scoped_fixture])
+@given(st.lists(st.lists(st.integers(2, 9), min_size=1, max_size=4), min_size=1, max_size=3), st.integers(0, 30))
+def test_packed_supervised_loss_is_the_token_weighted_mean_of_the_documents_alone(tiny_lm, rows, seed):
+    """Rows of packed documents (positions restart, attention stays inside a document): the batch loss must be what the
+    documents give one by one - the sum of their trained tokens' losses over the number of trained tokens."""
+    from astrai_b200.trainer import StrategyFactory
+
+    g = torch.Generator().manual_seed(seed)
+    width = max(sum(r) for r in rows)
+    model = _frozen_copy(tiny_lm)
+    strategy = StrategyFactory.create("sft", model=model, device="cpu")
+    ids = torch.zeros(len(rows), width + 1, dtype=torch.long)
+    pos = torch.zeros(len(rows), width, dtype=torch.long)
+    keep = torch.zeros(len(rows), width, dtype=torch.bool)
+    total, count = 0.0, 0
+    for r, lens in enumerate(rows):
+        lens = list(lens) + ([width - sum(lens)] if sum(lens) < width else [])  # the rest of the row is one more document
+        start = 0
+        for n in lens:
+            doc = torch.randint(2, 250, (n + 1,), generator=g)
+            trained = torch.rand(n, generator=g) < 0.6
+            ids[r, start:start + n + 1] = doc  # the next document overwrites the last token: it is only ever a target
+            pos[r, start:start + n] = torch.arange(n)
+            keep[r, start:start + n] = trained
+            start += n
+        # the documents alone, with the tokens as they ended up in the row
+        start = 0
+        for n in lens:
+            x, y = ids[r, start:start + n][None], ids[r, start + 1:start + n + 1][None]
+            k = keep[r, start:start + n][None]
+            if k.any():
+                logits = model(x)["logits"].float()
+                rows_loss = torch.nn.functional.cross_entropy(logits[0], y[0], reduction="none")
+                total += float((rows_loss * k[0]).sum())
+                count += int(k.sum())
+            start += n
+    if count == 0:
+        return
+    batch = {"input_ids": ids[:, :-1], "target_ids": ids[:, 1:], "position_ids": pos, "loss_mask": keep}
+    with torch.no_grad():
+        loss = float(strategy(batch)["loss"])
+    assert loss == pytest.approx(total / count, abs=3e-5)
