@@ -133,11 +133,15 @@ class InferenceEngine:
         return self._generate(prompts, batch, stream, max_tokens, temperature, top_p, top_k, frequency_penalty, rep_window)
 
     def generate_async(self, prompt: str, max_tokens: Optional[int] = None, temperature: float = 1.0, top_p: float = 1.0,
-                       top_k: int = 50, frequency_penalty: float = 0.0, rep_window: int = 64) -> AsyncGenerator[str, None]:
+                       top_k: int = 50, frequency_penalty: float = 0.0, rep_window: int = 64,
+                       usage: Optional[dict] = None) -> AsyncGenerator[str, None]:
         """Pieces of the answer as an async generator.  Closing it early (``aclose()``, or the consuming coroutine being
         cancelled: a stop sequence matched, the client went away) takes the request out of the scheduler, so that an
-        answer nobody reads does not keep a batch slot until ``max_tokens``."""
-        result, task_ids = self._submit([prompt], max_tokens, temperature, top_p, top_k, frequency_penalty, rep_window)
+        answer nobody reads does not keep a batch slot until ``max_tokens``.  A ``usage`` dict holds, by the time the
+        generator ends on its own, ``completion_tokens`` (tokens generated, which the pieces of text undercount) and
+        ``finish_reason`` (``stop`` or ``length``)."""
+        result, task_ids = self._submit([prompt], max_tokens, temperature, top_p, top_k, frequency_penalty, rep_window,
+                                        on_finish=usage.update if usage is not None else None)
         gen = self._stream(result, task_ids, False)
 
         async def agen():
@@ -154,7 +158,7 @@ class InferenceEngine:
 
         return agen()
 
-    def _submit(self, prompts, max_tokens, temperature, top_p, top_k, frequency_penalty, rep_window):
+    def _submit(self, prompts, max_tokens, temperature, top_p, top_k, frequency_penalty, rep_window, on_finish=None):
         from astrai_b200.ops.backend import get_backend
 
         result = GenerateResult(count=len(prompts))
@@ -162,6 +166,8 @@ class InferenceEngine:
         # the scheduling thread; None leaves the request on the scheduler's own
         chosen = get_backend(use_default=False)
         extra = {"backend": chosen} if chosen is not None else {}
+        if on_finish is not None:
+            extra["finish_callback"] = on_finish
         task_ids = [
             self.scheduler.add_task(prompt=p, max_tokens=max_tokens, temperature=temperature, top_p=top_p, top_k=top_k,
                                     frequency_penalty=frequency_penalty, rep_window=rep_window,

@@ -50,6 +50,14 @@ class AnthropicResponseBuilder(ResponseBuilder):
     def format_chunk(self, token, **kw):
         return [_delta(token)]
 
+    @staticmethod
+    def _stop_reason(ctx, stop) -> str:
+        """``stop_sequence``, ``max_tokens`` (the engine ran out of token budget or context; the reference says
+        ``end_turn`` there too) or ``end_turn``."""
+        if stop.matched:
+            return "stop_sequence"
+        return "max_tokens" if ctx.finish_reason == "length" else "end_turn"
+
     def format_stream_end(self, ctx, stop):
         events = []
         if stop.matched:
@@ -58,7 +66,7 @@ class AnthropicResponseBuilder(ResponseBuilder):
                 events.append(_delta(pending))
         events.append(sse_event({"type": "content_block_stop", "index": 0}, event="content_block_stop"))
         events.append(sse_event({"type": "message_delta",
-                                 "delta": {"stop_reason": "stop_sequence" if stop.matched else "end_turn",
+                                 "delta": {"stop_reason": self._stop_reason(ctx, stop),
                                            "stop_sequence": stop.matched},
                                  "usage": {"output_tokens": ctx.completion_tokens}}, event="message_delta"))
         events.append(sse_event({"type": "message_stop"}, event="message_stop"))
@@ -69,5 +77,5 @@ class AnthropicResponseBuilder(ResponseBuilder):
             content = content[: content.rfind(stop.matched)]
         return {"id": ctx.resp_id, "type": "message", "role": "assistant", "model": ctx.model,
                 "content": [{"type": "text", "text": content}],
-                "stop_reason": "stop_sequence" if stop.matched else "end_turn", "stop_sequence": stop.matched,
+                "stop_reason": self._stop_reason(ctx, stop), "stop_sequence": stop.matched,
                 "usage": {"input_tokens": ctx.prompt_tokens, "output_tokens": ctx.completion_tokens}}

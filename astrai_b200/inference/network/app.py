@@ -1,4 +1,4 @@
-"""FastAPI application: ``POST /v1/chat/completions``, ``POST /v1/messages``, ``GET /health``, ``GET /stats``, ``GET /v1/models``.
+"""FastAPI application: ``POST /v1/chat/completions``, ``POST /v1/messages``, ``GET /health``, ``GET /stats``, ``GET /v1/models``, ``POST /v1/completions``.
 
 Request schemas and defaults follow ``astrai/inference/network/app.py:33-206`` (OpenAI: temperature 1.0, top_p 1.0,
 top_k 50, max_tokens 2048; Anthropic: max_tokens 1024; 503 ``{"detail": "Engine not initialized"}`` before the engine
@@ -60,6 +60,19 @@ class ChatCompletionRequest(BaseModel):
     user: Optional[str] = None
     tools: Optional[List[ToolDef]] = None
     tool_choice: Optional[Union[str, Dict[str, Any]]] = "auto"
+
+
+class CompletionRequest(BaseModel):
+    model: str = "astrai"
+    prompt: Union[str, List[str]]
+    max_tokens: Optional[int] = Field(default=16, ge=1)
+    temperature: Optional[float] = Field(default=1.0, ge=0.0, le=2.0)
+    top_p: Optional[float] = Field(default=1.0, ge=0.0, le=1.0)
+    top_k: Optional[int] = Field(default=50, ge=1)
+    frequency_penalty: Optional[float] = Field(default=0.0, ge=-2.0, le=2.0)
+    stream: Optional[bool] = False
+    stop: Optional[Union[str, List[str]]] = None
+    echo: Optional[bool] = False
 
 
 class AnthropicMessage(BaseModel):
@@ -151,6 +164,13 @@ async def models():
 @router.post("/v1/chat/completions")
 async def chat_completion(request: ChatCompletionRequest):
     return await ProtocolHandler(request, _engine(), OpenAIResponseBuilder()).handle()
+
+
+@router.post("/v1/completions")
+async def completion(request: CompletionRequest):
+    from astrai_b200.inference.network.completions import CompletionResponseBuilder
+
+    return await ProtocolHandler(request, _engine(), CompletionResponseBuilder()).handle()
 
 
 @router.post("/v1/messages")

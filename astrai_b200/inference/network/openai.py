@@ -1,7 +1,8 @@
 """OpenAI ``/v1/chat/completions`` wire format (reference ``astrai/inference/network/openai.py:51-277``).
 
 Stream: role chunk -> content / tool-call chunks (``created: 0`` on middle chunks) -> finish chunk
-(``finish_reason`` ``stop`` or ``tool_calls``) -> a bare usage object.  ``n``, ``presence_penalty``, ``logit_bias`` and
+(``finish_reason`` ``stop``, ``tool_calls``, or ``length`` when the engine ran out of token budget or context: the
+reference says ``stop`` there too) -> a bare usage object.  ``n``, ``presence_penalty``, ``logit_bias`` and
 ``user`` are accepted and ignored with a warning.
 """
 
@@ -69,13 +70,17 @@ class OpenAIResponseBuilder(ResponseBuilder):
         return {"prompt_tokens": ctx.prompt_tokens, "completion_tokens": ctx.completion_tokens,
                 "total_tokens": ctx.prompt_tokens + ctx.completion_tokens}
 
+    @staticmethod
+    def _plain_reason(ctx: GenContext, stop) -> str:
+        return "length" if stop.matched is None and ctx.finish_reason == "length" else "stop"
+
     def format_stream_end(self, ctx, stop):
-        reason = "tool_calls" if (self._parser is not None and self._parser.has_tool_calls) else "stop"
+        reason = "tool_calls" if (self._parser is not None and self._parser.has_tool_calls) else self._plain_reason(ctx, stop)
         return [self._chunk({}, ctx.created, reason), sse_event(self._usage(ctx))]
 
     def format_response(self, ctx, content, stop):
         message: Dict[str, Any] = {"role": "assistant", "content": content}
-        reason = "stop"
+        reason = self._plain_reason(ctx, stop)
         parsed = self._parser.parse_complete(content) if self._parser is not None else None
         if parsed and parsed.get("tool_calls"):
             message = {"role": "assistant", "content": parsed.get("content"), "tool_calls": parsed["tool_calls"]}

@@ -8,7 +8,7 @@ from __future__ import annotations
 
 import json
 from contextlib import aclosing
-from dataclasses import dataclass
+from dataclasses import dataclass, field
 from typing import Any, AsyncGenerator, Dict, List, Optional, Tuple, Union
 
 from fastapi.responses import StreamingResponse
@@ -31,6 +31,15 @@ class GenContext:
     model: str
     prompt_tokens: int = 0
     completion_tokens: int = 0
+    finish_reason: Optional[str] = None  # "stop" / "length" once the engine ran the request to its end; None if cut short
+    engine_usage: Dict[str, Any] = field(default_factory=dict)
+
+    def settle(self, matched: Optional[str]):
+        """After the last piece: take the engine's token count (the handler counted pieces of text, and a token that gives
+        no text of its own was not among them) unless a stop sequence ended the answer before the engine did."""
+        if matched is None and self.engine_usage:
+            self.completion_tokens = max(self.completion_tokens, int(self.engine_usage.get("completion_tokens", 0)))
+            self.finish_reason = self.engine_usage.get("finish_reason")
 
 
 @dataclass
@@ -76,7 +85,8 @@ class ProtocolHandler:
         ctx.prompt_tokens = len(self.engine.tokenizer.encode(prompt))
         r = self.request
         agen = self.engine.generate_async(prompt=prompt, max_tokens=r.max_tokens, temperature=r.temperature, top_p=r.top_p,
-                                          top_k=r.top_k, frequency_penalty=getattr(r, "frequency_penalty", 0.0) or 0.0)
+                                          top_k=r.top_k, frequency_penalty=getattr(r, "frequency_penalty", 0.0) or 0.0,
+                                          usage=ctx.engine_usage)
         if r.stream:
             return StreamingResponse(self._events(agen, ctx, stops), media_type="text/event-stream",
                                      headers={"Cache-Control": "no-cache", "Connection": "keep-alive"})
@@ -103,6 +113,7 @@ class ProtocolHandler:
                 for ev in self.builder.format_chunk(piece, body=body, current_token_ids=ids, delta_token_ids=new_ids):
                     yield ev
                 sent += piece
+        ctx.settle(matched)
         for ev in self.builder.format_stream_end(ctx, StopInfo(matched, body, sent)):
             yield ev
         yield sse_done()
@@ -117,4 +128,5 @@ class ProtocolHandler:
                 if matched:
                     break
                 ctx.completion_tokens += 1
+        ctx.settle(matched)
         return self.builder.format_response(ctx, body, StopInfo(matched, body))

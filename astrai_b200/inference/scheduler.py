@@ -92,7 +92,7 @@ class InferenceScheduler:
         if not self._control.leader:
             raise RuntimeError("requests enter a tensor-parallel replica through its first rank")
         # staged: the request joins the queue of every rank at the start of the next loop iteration, in arrival order
-        callback = kwargs.pop("stream_callback", None)
+        callback, on_finish = kwargs.pop("stream_callback", None), kwargs.pop("finish_callback", None)
         backend = kwargs.pop("backend", None)
         ids = self._task_mgr.tokenizer.encode(prompt) if isinstance(prompt, str) else list(prompt)
         task = self._task_mgr.make_task(ids, kwargs.pop("max_tokens", None), **kwargs)
@@ -100,8 +100,8 @@ class InferenceScheduler:
                 "top_p": task.top_p, "top_k": task.top_k, "frequency_penalty": task.frequency_penalty, "rep_window": task.rep_window}
         with self._stage_lock:
             self._staged.append(spec)
-            if callback is not None:
-                self._task_mgr.register_callback(task.task_id, callback)
+            if callback is not None or on_finish is not None:
+                self._task_mgr.register_callback(task.task_id, callback, on_finish)
         self._task_mgr.wake()
         return task.task_id
 
@@ -325,6 +325,7 @@ class InferenceScheduler:
                     if text:
                         self._task_mgr.invoke_callback(t.task_id, text)
                     if t.is_finished(stop_ids):
+                        self._task_mgr.report_finish(t, stop_ids)
                         self._task_mgr.invoke_callback(t.task_id, STOP)
         except Exception as exc:  # noqa: BLE001 - every waiter must be released
             self._stop_event.set()

@@ -89,6 +89,7 @@ class TaskManager:
         self.waiting_queue: Deque[Task] = deque()
         self.active_tasks: List[Task] = []
         self._callbacks: Dict[str, Callable] = {}
+        self._finish_callbacks: Dict[str, Callable] = {}
         self._task_event = threading.Event()
         self._lock = threading.Lock()
         self._total_tasks = self._total_tokens = 0
@@ -103,8 +104,10 @@ class TaskManager:
 
     def add_task(self, prompt, max_tokens: Optional[int] = None, temperature: float = 1.0, top_p: float = 1.0,
                  top_k: int = 50, frequency_penalty: float = 0.0, rep_window: int = 64, backend=None,
-                 stream_callback: Optional[Callable] = None) -> str:
-        """``prompt`` is text (tokenised here) or an already tokenised id list."""
+                 stream_callback: Optional[Callable] = None, finish_callback: Optional[Callable] = None) -> str:
+        """``prompt`` is text (tokenised here) or an already tokenised id list.  ``stream_callback`` hears every piece of
+        text and then ``STOP``; ``finish_callback`` hears, once and before that ``STOP``, how a request that ran to its end
+        ended (see :meth:`report_finish`)."""
         ids = self.tokenizer.encode(prompt) if isinstance(prompt, str) else list(prompt)
         task = self.make_task(ids, max_tokens, temperature=temperature, top_p=top_p, top_k=top_k,
                               frequency_penalty=frequency_penalty, rep_window=rep_window, backend=backend)
@@ -113,6 +116,8 @@ class TaskManager:
             self._total_tasks += 1
             if stream_callback:
                 self._callbacks[task.task_id] = stream_callback
+            if finish_callback:
+                self._finish_callbacks[task.task_id] = finish_callback
         if self._metrics is not None:
             self._metrics.register(task.task_id)
         self._task_event.set()
@@ -127,9 +132,22 @@ class TaskManager:
             self._metrics.register(task.task_id)
         self._task_event.set()
 
-    def register_callback(self, task_id: str, callback: Callable):
+    def register_callback(self, task_id: str, callback: Optional[Callable], finish_callback: Optional[Callable] = None):
         with self._lock:
-            self._callbacks[task_id] = callback
+            if callback is not None:
+                self._callbacks[task_id] = callback
+            if finish_callback is not None:
+                self._finish_callbacks[task_id] = finish_callback
+
+    def report_finish(self, task: Task, stop_ids):
+        """Tell the request's ``finish_callback`` the number of tokens generated (text pieces undercount them: a token
+        that completes a character only later, or a special token, gives no text) and why generation ended: ``stop`` for
+        an end-of-sequence token, ``length`` for a spent token budget or a full context."""
+        with self._lock:
+            cb = self._finish_callbacks.pop(task.task_id, None)
+        if cb:
+            ended = bool(task.output_ids) and task.output_ids[-1] in stop_ids
+            cb({"completion_tokens": task.output_tokens, "finish_reason": "stop" if ended else "length"})
 
     def wait_for_wake(self, timeout: float):
         """Sleep until :meth:`wake` (or a new task) or ``timeout`` seconds, whatever the queues hold."""
@@ -141,6 +159,7 @@ class TaskManager:
         worth a trip through the scheduling loop)."""
         with self._lock:
             self._callbacks.pop(task_id, None)
+            self._finish_callbacks.pop(task_id, None)
             return any(t.task_id == task_id for t in self.active_tasks) or any(t.task_id == task_id for t in self.waiting_queue)
 
     def remove_task(self, task_id: str) -> List[Task]:
@@ -149,6 +168,7 @@ class TaskManager:
             self.waiting_queue = deque(t for t in self.waiting_queue if t.task_id != task_id)
             self.active_tasks = [t for t in self.active_tasks if t.task_id != task_id]
             self._callbacks.pop(task_id, None)
+            self._finish_callbacks.pop(task_id, None)
         return gone
 
     def invoke_callback(self, task_id: str, token):
@@ -177,6 +197,9 @@ class TaskManager:
                 for t in done:
                     self._metrics.mark_finished(t.task_id, t.input_tokens, t.output_tokens)
             self.active_tasks = [t for t in self.active_tasks if t.status not in (TaskStatus.FINISHED, TaskStatus.ABORTED)]
+            for t in done:  # both have heard their last (the loop sends STOP in the iteration before the one that retires)
+                self._callbacks.pop(t.task_id, None)
+                self._finish_callbacks.pop(t.task_id, None)
             return done
 
     def pull_candidates(self, n: int) -> List[Task]:
@@ -216,6 +239,7 @@ class TaskManager:
             self.waiting_queue.clear()
             self.active_tasks.clear()
             self._callbacks.clear()
+            self._finish_callbacks.clear()
 
     def wake(self):
         self._task_event.set()

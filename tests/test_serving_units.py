@@ -823,3 +823,99 @@ def test_submit_stream_and_cancel_from_many_threads_leaks_nothing(served):
         assert len(engine.generate(["a", "b", "c", "d"], max_tokens=1, temperature=0.0)) == 4
     finally:
         engine.shutdown()
+
+
+def test_text_completions_route(served):
+    """Plain text in and out: no chat template around the prompt, the text ends before a stop sequence, the finish reason
+    tells a spent budget from an end, streams carry the same text in pieces."""
+    from fastapi.testclient import TestClient
+
+    from astrai_b200.inference import InferenceEngine
+    from astrai_b200.inference.network import app as app_mod
+
+    PROMPT = "the quick brown fox"
+    model, tok = served
+    engine = InferenceEngine(model, tok, max_batch_size=2, max_seq_len=96, enable_cuda_graph=False)
+    app = app_mod.get_app()
+    old = app.state.engine, app.state.server_config
+    app.state.engine, app.state.server_config = engine, {"_test": True}
+    try:
+        client = TestClient(app)
+        r = client.post("/v1/completions", json={"prompt": PROMPT, "max_tokens": 8, "temperature": 0.0}).json()
+        text = r["choices"][0]["text"]
+        assert r["object"] == "text_completion" and r["id"].startswith("cmpl-")
+        ids = engine.scheduler.run_batch([tok.encode(PROMPT)], max_tokens=8, temperature=0.0)[0]
+        spent = len(ids) == 8 and ids[-1] not in tok.stop_ids
+        # tokens, not pieces of text (this random model emits tokens that decode to nothing on their own)
+        assert r["usage"] == {"prompt_tokens": len(tok.encode(PROMPT)), "completion_tokens": len(ids),
+                              "total_tokens": len(tok.encode(PROMPT)) + len(ids)}
+        assert r["choices"][0]["finish_reason"] == ("length" if spent else "stop")
+        assert text == engine.generate(PROMPT, max_tokens=8, temperature=0.0)  # the bare prompt, not a chat turn
+        echoed = client.post("/v1/completions", json={"prompt": [PROMPT[:4], PROMPT[4:]], "max_tokens": 8, "temperature": 0.0, "echo": True}).json()
+        assert echoed["choices"][0]["text"] == PROMPT + text
+        assert len(text) >= 4  # this prompt's greedy continuation has text to cut
+        stop = text[2:4]
+        cut = client.post("/v1/completions", json={"prompt": PROMPT, "max_tokens": 50, "temperature": 0.0, "stop": stop}).json()
+        assert cut["choices"][0]["text"] == text[:text.index(stop)] and cut["choices"][0]["finish_reason"] == "stop"
+        with client.stream("POST", "/v1/completions", json={"prompt": PROMPT, "max_tokens": 50, "temperature": 0.0, "stop": [stop],
+                                                            "stream": True}) as resp:
+            events = [line[6:] for line in resp.iter_lines() if line.startswith("data: ")]
+        assert events[-1] == "[DONE]"
+        chunks = [json.loads(e) for e in events[:-1]]
+        assert "".join(c["choices"][0]["text"] for c in chunks) == text[:text.index(stop)]
+        assert chunks[-1]["choices"][0]["finish_reason"] == "stop" and chunks[-1]["usage"]["completion_tokens"] >= 1
+        assert all(c["choices"][0]["finish_reason"] is None for c in chunks[:-1])
+        assert client.post("/v1/completions", json={"max_tokens": 3}).status_code == 422
+        # the chat protocols name a spent budget too
+        chat = client.post("/v1/chat/completions", json={"messages": [{"role": "user", "content": PROMPT}], "max_tokens": 5, "temperature": 0.0}).json()
+        msg = client.post("/v1/messages", json={"messages": [{"role": "user", "content": PROMPT}], "max_tokens": 5, "temperature": 0.0}).json()
+        assert chat["usage"]["completion_tokens"] == msg["usage"]["output_tokens"] <= 5
+        if chat["usage"]["completion_tokens"] == 5:
+            assert chat["choices"][0]["finish_reason"] == "length" and msg["stop_reason"] == "max_tokens"
+        else:  # ended by an end-of-sequence token
+            assert chat["choices"][0]["finish_reason"] == "stop" and msg["stop_reason"] == "end_turn"
+    finally:
+        app.state.engine, app.state.server_config = old
+        engine.shutdown()
+
+
+def test_finish_callback_reports_tokens_and_reason(served):
+    """The scheduler tells a finished request's ``finish_callback`` the number of generated tokens and whether an
+    end-of-sequence token or the budget ended it, before the stream's STOP; a cancelled request hears nothing."""
+    from astrai_b200.inference.task import STOP
+
+    model, tok = served
+    s = _sched(served)
+    s.start()
+    try:
+        log, done = [], threading.Event()
+
+        def heard(x):
+            log.append(x)
+            if x is STOP:
+                done.set()
+
+        s.add_task(prompt="the quick brown fox", max_tokens=5, temperature=0.0, stream_callback=heard, finish_callback=heard)
+        assert done.wait(30)
+        info = log[-2]
+        assert log[-1] is STOP and isinstance(info, dict) and set(info) == {"completion_tokens", "finish_reason"}
+        assert 1 <= info["completion_tokens"] <= 5
+        assert info["finish_reason"] == ("length" if info["completion_tokens"] == 5 else "stop")
+        assert sum(isinstance(x, dict) for x in log) == 1
+        mgr = s._task_mgr
+        deadline = time.time() + 10
+        while (mgr._callbacks or mgr._finish_callbacks) and time.time() < deadline:
+            time.sleep(0.01)  # the loop forgets both callbacks when it retires the request
+        assert not mgr._callbacks and not mgr._finish_callbacks
+
+        quiet = []
+        _slow_down(s)
+        tid = s.add_task(prompt="the quick brown fox", max_tokens=40, temperature=0.0, stream_callback=lambda x: None, finish_callback=quiet.append)
+        time.sleep(0.05)
+        s.remove_task(tid)
+        deadline = time.time() + 10
+        while s.get_stats()["active_tasks"] and time.time() < deadline:
+            time.sleep(0.01)
+        assert quiet == [] and not mgr._finish_callbacks
+    finally:
+        s.stop()
