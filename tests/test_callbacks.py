@@ -243,11 +243,11 @@ def test_loss_denominator_turns_slice_means_into_the_mean_over_all_trained_token
         for r in range(2):
             halves.append(ops.cross_entropy(logits[r * 6:(r + 1) * 6], targets[r * 6:(r + 1) * 6]))
     (sum(halves) / 2).backward()
-    assert float(sum(halves) / 2) == pytest.approx(float(whole), rel=1e-6)
+    assert float((sum(halves) / 2).detach()) == pytest.approx(float(whole.detach()), rel=1e-6)
     assert torch.allclose(logits.grad, ref_grad, atol=1e-7)
 
     plain = [ops.cross_entropy(logits[r * 6:(r + 1) * 6], targets[r * 6:(r + 1) * 6]) for r in range(2)]
-    assert abs(float(sum(plain) / 2) - float(whole)) > 1e-3  # the slices' own counts weight the tokens unevenly
+    assert abs(float((sum(plain) / 2).detach()) - float(whole.detach())) > 1e-3  # the slices' own counts weight the tokens unevenly
     with ops.loss_denominator(None):
         assert float(ops.cross_entropy(logits, targets)) == pytest.approx(float(whole))
     # the context ends with the block
