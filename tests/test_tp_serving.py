@@ -84,6 +84,7 @@ def test_serve_command_with_two_tensor_parallel_processes_answers_over_http(tmp_
     messages = [{"role": "user", "content": "hello"}]
     with InferenceEngine(model, tok, max_batch_size=2, max_seq_len=96, enable_cuda_graph=False) as eng:
         want = eng.generate(tok.apply_chat_template(messages, tokenize=False), max_tokens=6, temperature=0.0)
+        want_ids = eng.scheduler.run_batch([tok.encode(tok.apply_chat_template(messages, tokenize=False))], max_tokens=6, temperature=0.0)[0]
     port = 18473
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr", "127.0.0.1",
            "--master-port", "29779", "-m", "astrai_b200.cli.serve", "--tp_size", "2", "--device", "cpu", "--dtype", "float32",
@@ -108,6 +109,9 @@ def test_serve_command_with_two_tensor_parallel_processes_answers_over_http(tmp_
         with urllib.request.urlopen(req, timeout=60) as r:
             answer = json.load(r)
         assert answer["choices"][0]["message"]["content"] == want
+        # the finish report reaches the first rank's handler through the staged (every-rank) request path too
+        assert answer["usage"]["completion_tokens"] == len(want_ids)
+        assert answer["choices"][0]["finish_reason"] == ("stop" if want_ids[-1] in tok.stop_ids else "length")
     finally:
         os.killpg(proc.pid, signal.SIGTERM)  # the exact process group started above
         try:
