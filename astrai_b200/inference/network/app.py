@@ -15,7 +15,7 @@ from typing import Any, Dict, List, Optional, Union
 
 import torch
 from fastapi import APIRouter, FastAPI, HTTPException
-from pydantic import BaseModel, Field
+from pydantic import BaseModel, Field, model_validator
 
 from astrai_b200.inference.engine import InferenceEngine
 from astrai_b200.inference.network.anthropic import AnthropicResponseBuilder
@@ -53,6 +53,7 @@ class ChatCompletionRequest(BaseModel):
     stream: Optional[bool] = False
     stop: Optional[Union[str, List[str]]] = None
     max_tokens: Optional[int] = Field(default=2048, ge=1)
+    max_completion_tokens: Optional[int] = Field(default=None, ge=1)  # the newer OpenAI name; wins over max_tokens when given
     n: Optional[int] = Field(default=1, ge=1)
     presence_penalty: Optional[float] = Field(default=0.0, ge=-2.0, le=2.0)
     frequency_penalty: Optional[float] = Field(default=0.0, ge=-2.0, le=2.0)
@@ -60,6 +61,12 @@ class ChatCompletionRequest(BaseModel):
     user: Optional[str] = None
     tools: Optional[List[ToolDef]] = None
     tool_choice: Optional[Union[str, Dict[str, Any]]] = "auto"
+
+    @model_validator(mode="after")
+    def _one_token_budget(self):
+        if self.max_completion_tokens is not None:
+            self.max_tokens = self.max_completion_tokens
+        return self
 
 
 class CompletionRequest(BaseModel):

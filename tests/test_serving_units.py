@@ -870,6 +870,9 @@ def test_text_completions_route(served):
         chat = client.post("/v1/chat/completions", json={"messages": [{"role": "user", "content": PROMPT}], "max_tokens": 5, "temperature": 0.0}).json()
         msg = client.post("/v1/messages", json={"messages": [{"role": "user", "content": PROMPT}], "max_tokens": 5, "temperature": 0.0}).json()
         assert chat["usage"]["completion_tokens"] == msg["usage"]["output_tokens"] <= 5
+        newer = client.post("/v1/chat/completions", json={"messages": [{"role": "user", "content": PROMPT}], "max_tokens": 40,
+                                                          "max_completion_tokens": 5, "temperature": 0.0}).json()
+        assert newer["usage"] == chat["usage"] and newer["choices"][0]["message"] == chat["choices"][0]["message"]
         if chat["usage"]["completion_tokens"] == 5:
             assert chat["choices"][0]["finish_reason"] == "length" and msg["stop_reason"] == "max_tokens"
         else:  # ended by an end-of-sequence token
