@@ -92,6 +92,8 @@ class Heartbeat:
             else:
                 continue
             with self._lock:
+                if peer in self._dead:
+                    continue  # the other scanner (the thread, or a caller of scan) reported it a moment ago
                 self._dead[peer] = why
             logger.error("heartbeat: rank %d %s", peer, why)
             if self.on_failure is not None:
