@@ -61,10 +61,18 @@ def launch_ranks(nproc: int, script: str, args, port: int, timeout: float = 600.
     environment, as an external launcher sets them) and wait for all of them.  Returns ``(returncode, output)``: the first
     non-zero exit code (0 if none) and every rank's output.  Starting the ranks directly instead of through
     ``torch.distributed.run`` saves that launcher's own start-up in every test; the tests that are about the launcher use it."""
+    import socket
     import subprocess
     import sys
     import time
 
+    # the asked-for port if it can be had; otherwise (a run a moment ago still holds it) one the system picks
+    with socket.socket(socket.AF_INET, socket.SOCK_STREAM) as probe:
+        try:
+            probe.bind(("127.0.0.1", int(port)))
+        except OSError:
+            probe.bind(("127.0.0.1", 0))
+            port = probe.getsockname()[1]
     base = dict(os.environ if env is None else env, MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), WORLD_SIZE=str(nproc),
                 LOCAL_WORLD_SIZE=str(nproc))
     base.setdefault("OMP_NUM_THREADS", "1")
